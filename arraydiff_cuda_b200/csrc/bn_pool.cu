@@ -1,0 +1,395 @@
+// Spatial batch normalisation (training statistics, optional fused ReLU) and max pooling
+// on strided 4-D views.  HBM-bound.
+//
+// Statistics are a two-stage, order-fixed reduction: stage 1 writes per-split partial sums
+// to caller scratch, stage 2 combines them in double.  No atomics, so results are
+// reproducible run to run.  Threads walk the tensor along its fastest axis (x for
+// NCHW-like views, channel for NHWC-like views) so that warps read whole sectors.
+#include "common.cuh"
+
+namespace adk {
+
+constexpr int kBnMaxSplits = 128;
+
+struct BView { const char* base; long long sn, sc, sy, sx; };
+static BView bview(const ad_tensor4* t) { return BView{(const char*)t->base, t->sn, t->sc, t->sy, t->sx}; }
+
+// partial[split][0..C) = sum a, partial[split][C..2C) = sum b, where (a, b) is
+//   MODE 0: (x, x^2)                      -- forward statistics
+//   MODE 1: (g, g * xhat), g = dy masked   -- backward reductions
+struct BnRed {
+  BView x, dy;
+  uint32_t N, C, H, W;
+  int relu;
+  const float *gamma, *beta, *mean, *invstd;
+};
+
+template <typename T, int MODE>
+__device__ __forceinline__ void bn_term(const BnRed& p, uint32_t n, uint32_t c, uint32_t y, uint32_t x, float& a,
+                                        float& b) {
+  const long long ox = n * p.x.sn + c * p.x.sc + y * p.x.sy + x * p.x.sx;
+  const float xv = ld_f((const T*)p.x.base + ox);
+  if (MODE == 0) {
+    a += xv;
+    b = fmaf(xv, xv, b);
+  } else {
+    const long long od = n * p.dy.sn + c * p.dy.sc + y * p.dy.sy + x * p.dy.sx;
+    float g = ld_f((const T*)p.dy.base + od);
+    const float xhat = (xv - p.mean[c]) * p.invstd[c];
+    if (p.relu && fmaf(p.gamma[c], xhat, p.beta[c]) <= 0.f) g = 0.f;
+    a += g;
+    b = fmaf(g, xhat, b);
+  }
+}
+
+// NCHW-like: block (256) per (channel, split); threads stride over (n, y, x).
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256) bn_reduce_xfast(BnRed p, float* partial) {
+  const uint32_t c = blockIdx.x, split = blockIdx.y, nsplit = gridDim.y;
+  const size_t per = (size_t)p.N * p.H * p.W;
+  float a = 0.f, b = 0.f;
+  for (size_t i = (size_t)split * 256 + threadIdx.x; i < per; i += (size_t)nsplit * 256) {
+    uint32_t x = (uint32_t)(i % p.W);
+    size_t r = i / p.W;
+    uint32_t y = (uint32_t)(r % p.H), n = (uint32_t)(r / p.H);
+    bn_term<T, MODE>(p, n, c, y, x, a, b);
+  }
+  __shared__ float sa[8], sb[8];
+  a = warp_sum(a); b = warp_sum(b);
+  if ((threadIdx.x & 31) == 0) { sa[threadIdx.x >> 5] = a; sb[threadIdx.x >> 5] = b; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float ta = 0.f, tb = 0.f;
+    for (int w = 0; w < 8; ++w) { ta += sa[w]; tb += sb[w]; }
+    partial[(size_t)split * 2 * p.C + c] = ta;
+    partial[(size_t)split * 2 * p.C + p.C + c] = tb;
+  }
+}
+
+// NHWC-like: block (32 channels x 8 pixel lanes) per (channel group, split).
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256) bn_reduce_cfast(BnRed p, float* partial) {
+  const uint32_t c = blockIdx.x * 32 + threadIdx.x, split = blockIdx.y, nsplit = gridDim.y;
+  const size_t per = (size_t)p.N * p.H * p.W;
+  float a = 0.f, b = 0.f;
+  if (c < p.C)
+    for (size_t i = (size_t)split * 8 + threadIdx.y; i < per; i += (size_t)nsplit * 8) {
+      uint32_t x = (uint32_t)(i % p.W);
+      size_t r = i / p.W;
+      uint32_t y = (uint32_t)(r % p.H), n = (uint32_t)(r / p.H);
+      bn_term<T, MODE>(p, n, c, y, x, a, b);
+    }
+  __shared__ float sa[8][33], sb[8][33];
+  sa[threadIdx.y][threadIdx.x] = a;
+  sb[threadIdx.y][threadIdx.x] = b;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < p.C) {
+    float ta = 0.f, tb = 0.f;
+    for (int w = 0; w < 8; ++w) { ta += sa[w][threadIdx.x]; tb += sb[w][threadIdx.x]; }
+    partial[(size_t)split * 2 * p.C + c] = ta;
+    partial[(size_t)split * 2 * p.C + p.C + c] = tb;
+  }
+}
+
+// sums[0..2C) = sum over splits (double accumulate).
+__global__ void bn_combine(uint32_t C2, int nsplit, const float* __restrict__ partial, float* sums) {
+  uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= C2) return;
+  double t = 0.0;
+  for (int s = 0; s < nsplit; ++s) t += (double)partial[(size_t)s * C2 + i];
+  sums[i] = (float)t;
+}
+
+// mean / invstd / var from sums; double arithmetic for the cancellation in E[x^2]-E[x]^2.
+__global__ void bn_finalize(uint32_t C, int nsplit, const float* __restrict__ partial_or_sums, double count, float eps,
+                            float* mean, float* invstd, float* var) {
+  uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  double s = 0.0, ss = 0.0;
+  for (int k = 0; k < nsplit; ++k) {
+    s += (double)partial_or_sums[(size_t)k * 2 * C + c];
+    ss += (double)partial_or_sums[(size_t)k * 2 * C + C + c];
+  }
+  double m = s / count, v = ss / count - m * m;
+  if (v < 0.0) v = 0.0;
+  if (mean) mean[c] = (float)m;
+  if (invstd) invstd[c] = (float)(1.0 / sqrt(v + (double)eps));
+  if (var) var[c] = (float)v;
+}
+
+struct BnApply {
+  BView x, dy, out;
+  uint32_t N, C, H, W;
+  int c_fastest, relu, accumulate;
+  const float *gamma, *beta, *mean, *invstd;
+  const float* partial;  // backward: combined sums [2C]
+  int nsplit;
+  double count;
+};
+
+// MODE 0: y = relu?(gamma*(x-mean)*invstd+beta)
+// MODE 1: dx (+)= gamma*invstd*(g - mean(g) - xhat*mean(g*xhat))
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256) bn_apply(BnApply p) {
+  const size_t total = (size_t)p.N * p.C * p.H * p.W, nt = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nt) {
+    uint32_t n, c, y, x;
+    size_t r = i;
+    if (p.c_fastest) {
+      c = (uint32_t)(r % p.C); r /= p.C; x = (uint32_t)(r % p.W); r /= p.W; y = (uint32_t)(r % p.H); n = (uint32_t)(r / p.H);
+    } else {
+      x = (uint32_t)(r % p.W); r /= p.W; y = (uint32_t)(r % p.H); r /= p.H; c = (uint32_t)(r % p.C); n = (uint32_t)(r / p.C);
+    }
+    const float xv = ld_f((const T*)p.x.base + (n * p.x.sn + c * p.x.sc + y * p.x.sy + x * p.x.sx));
+    T* op = (T*)p.out.base + (n * p.out.sn + c * p.out.sc + y * p.out.sy + x * p.out.sx);
+    const float xhat = (xv - p.mean[c]) * p.invstd[c];
+    if (MODE == 0) {
+      float v = fmaf(p.gamma[c], xhat, p.beta[c]);
+      if (p.relu) v = fmaxf(v, 0.f);
+      st_f(op, v);
+    } else {
+      float g = ld_f((const T*)p.dy.base + (n * p.dy.sn + c * p.dy.sc + y * p.dy.sy + x * p.dy.sx));
+      if (p.relu && fmaf(p.gamma[c], xhat, p.beta[c]) <= 0.f) g = 0.f;
+      const float m1 = (float)((double)p.partial[c] / p.count), m2 = (float)((double)p.partial[p.C + c] / p.count);
+      float v = p.gamma[c] * p.invstd[c] * (g - m1 - xhat * m2);
+      if (p.accumulate) v += ld_f(op);
+      st_f(op, v);
+    }
+  }
+}
+
+__global__ void bn_param_grads(uint32_t C, const float* __restrict__ sums, float* dgamma, float* dbeta) {
+  uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  if (dbeta) dbeta[c] += sums[c];
+  if (dgamma) dgamma[c] += sums[C + c];
+}
+
+static int pick_splits(const ad_tensor4* x, bool cfast) {
+  const size_t per = (size_t)x->N * x->H * x->W;
+  const size_t groups = cfast ? (x->C + 31) / 32 : x->C;
+  size_t want = ((size_t)kNumSMs * 4 + groups - 1) / groups;  // ~4 blocks per SM overall
+  size_t maxs = (per + (cfast ? 8 : 256) * 4 - 1) / ((cfast ? 8 : 256) * 4);
+  if (want > maxs) want = maxs;
+  if (want > (size_t)kBnMaxSplits) want = kBnMaxSplits;
+  if (want < 1) want = 1;
+  return (int)want;
+}
+
+template <int MODE>
+static int launch_reduce(const BnRed& p, const ad_tensor4* x, float* partial, int& nsplit, cudaStream_t s) {
+  const bool cfast = x->sc == 1 && x->C > 1;
+  nsplit = pick_splits(x, cfast);
+  if (cfast) {
+    dim3 grid((x->C + 31) / 32, nsplit), block(32, 8);
+    AD_DISPATCH_DTYPE(x->dtype, (bn_reduce_cfast<T, MODE><<<grid, block, 0, s>>>(p, partial)));
+  } else {
+    dim3 grid(x->C, nsplit);
+    AD_DISPATCH_DTYPE(x->dtype, (bn_reduce_xfast<T, MODE><<<grid, 256, 0, s>>>(p, partial)));
+  }
+  count_launch();
+  return launch_status();
+}
+
+static bool dims_eq(const ad_tensor4* a, const ad_tensor4* b) {
+  return a->N == b->N && a->C == b->C && a->H == b->H && a->W == b->W && a->dtype == b->dtype;
+}
+
+// ------------------------------------------------------------------ max pooling
+struct PoolP {
+  BView x, y, dy, dx;
+  uint32_t N, C, H, W, P, Q, kh, kw, sh, sw;
+  int c_fastest, accumulate;
+};
+
+template <typename T>
+__device__ __forceinline__ uint32_t window_argmax(const PoolP& p, uint32_t n, uint32_t c, uint32_t q, uint32_t s, float& best) {
+  uint32_t bi = 0;
+  best = -INFINITY;
+  for (uint32_t i = 0; i < p.kh; ++i)
+    for (uint32_t j = 0; j < p.kw; ++j) {
+      const uint32_t yy = q * p.sh + i, xx = s * p.sw + j;
+      const float v = ld_f((const T*)p.x.base + (n * p.x.sn + c * p.x.sc + yy * p.x.sy + xx * p.x.sx));
+      if (v > best || (i == 0 && j == 0)) { best = v; bi = yy * p.W + xx; }
+    }
+  return bi;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) maxpool_fwd_kernel(PoolP p) {
+  const size_t total = (size_t)p.N * p.C * p.P * p.Q, nt = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nt) {
+    uint32_t n, c, q, s;
+    size_t r = i;
+    if (p.c_fastest) {
+      c = (uint32_t)(r % p.C); r /= p.C; s = (uint32_t)(r % p.Q); r /= p.Q; q = (uint32_t)(r % p.P); n = (uint32_t)(r / p.P);
+    } else {
+      s = (uint32_t)(r % p.Q); r /= p.Q; q = (uint32_t)(r % p.P); r /= p.P; c = (uint32_t)(r % p.C); n = (uint32_t)(r / p.C);
+    }
+    float best;
+    window_argmax<T>(p, n, c, q, s, best);
+    st_f((T*)p.y.base + (n * p.y.sn + c * p.y.sc + q * p.y.sy + s * p.y.sx), best);
+  }
+}
+
+// One thread per INPUT element gathers from the windows that contain it; a window
+// contributes iff its first maximum is this element.  No atomics -> reproducible.
+template <typename T>
+__global__ void __launch_bounds__(256) maxpool_bwd_kernel(PoolP p) {
+  const size_t total = (size_t)p.N * p.C * p.H * p.W, nt = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nt) {
+    uint32_t n, c, y, x;
+    size_t r = i;
+    if (p.c_fastest) {
+      c = (uint32_t)(r % p.C); r /= p.C; x = (uint32_t)(r % p.W); r /= p.W; y = (uint32_t)(r % p.H); n = (uint32_t)(r / p.H);
+    } else {
+      x = (uint32_t)(r % p.W); r /= p.W; y = (uint32_t)(r % p.H); r /= p.H; c = (uint32_t)(r % p.C); n = (uint32_t)(r / p.C);
+    }
+    float acc = 0.f;
+    // windows q with q*sh <= y <= q*sh + kh - 1
+    const uint32_t q_lo = y + 1 > p.kh ? (y + 1 - p.kh + p.sh - 1) / p.sh : 0;
+    const uint32_t s_lo = x + 1 > p.kw ? (x + 1 - p.kw + p.sw - 1) / p.sw : 0;
+    for (uint32_t q = q_lo; q < p.P && q * p.sh <= y; ++q)
+      for (uint32_t s = s_lo; s < p.Q && s * p.sw <= x; ++s) {
+        float best;
+        if (window_argmax<T>(p, n, c, q, s, best) == y * p.W + x)
+          acc += ld_f((const T*)p.dy.base + (n * p.dy.sn + c * p.dy.sc + q * p.dy.sy + s * p.dy.sx));
+      }
+    T* op = (T*)p.dx.base + (n * p.dx.sn + c * p.dx.sc + y * p.dx.sy + x * p.dx.sx);
+    if (p.accumulate) acc += ld_f(op);
+    st_f(op, acc);
+  }
+}
+
+}  // namespace adk
+
+using namespace adk;
+
+extern "C" size_t ad_bn_scratch_bytes(uint32_t C) { return (size_t)(kBnMaxSplits + 1) * 2 * C * sizeof(float); }
+
+extern "C" int ad_bn_partial_stats(const ad_tensor4* x, float* sums, void* scratch, size_t scratch_bytes, void* stream) {
+  if (!x || !x->base || !sums || !scratch) return AD_ERR_BAD_ARG;
+  if (scratch_bytes < ad_bn_scratch_bytes(x->C)) return AD_ERR_SCRATCH;
+  cudaStream_t s = as_stream(stream);
+  BnRed p{bview(x), bview(x), x->N, x->C, x->H, x->W, 0, nullptr, nullptr, nullptr, nullptr};
+  int nsplit = 1;
+  int st = launch_reduce<0>(p, x, (float*)scratch, nsplit, s);
+  if (st != AD_OK) return st;
+  bn_combine<<<(2 * x->C + 255) / 256, 256, 0, s>>>(2 * x->C, nsplit, (const float*)scratch, sums);
+  count_launch();
+  return launch_status();
+}
+
+extern "C" int ad_bn_finalize_apply(const ad_tensor4* x, const ad_tensor4* y, const float* sums, double count,
+                                    const float* gamma, const float* beta, float* save_mean, float* save_invstd,
+                                    float* batch_var, float eps, int32_t relu, void* stream) {
+  if (!x || !y || !x->base || !y->base || !sums || !gamma || !beta || !save_mean || !save_invstd) return AD_ERR_BAD_ARG;
+  if (!dims_eq(x, y) || count <= 0.0) return AD_ERR_BAD_ARG;
+  cudaStream_t s = as_stream(stream);
+  bn_finalize<<<(x->C + 127) / 128, 128, 0, s>>>(x->C, 1, sums, count, eps, save_mean, save_invstd, batch_var);
+  count_launch();
+  BnApply a{bview(x), bview(x), bview(y), x->N, x->C, x->H, x->W, y->sc == 1 && y->C > 1, relu, 0,
+            gamma, beta, save_mean, save_invstd, nullptr, 1, count};
+  const size_t total = (size_t)x->N * x->C * x->H * x->W;
+  AD_DISPATCH_DTYPE(x->dtype, (bn_apply<T, 0><<<grid_for(total, 256, 16), 256, 0, s>>>(a)));
+  count_launch();
+  return launch_status();
+}
+
+extern "C" int ad_bn_fwd_train(const ad_tensor4* x, const ad_tensor4* y, const float* gamma, const float* beta,
+                               float* save_mean, float* save_invstd, float* batch_var, float eps, int32_t relu,
+                               void* scratch, size_t scratch_bytes, void* stream) {
+  if (!x || !y || !x->base || !y->base || !gamma || !beta || !save_mean || !save_invstd || !scratch) return AD_ERR_BAD_ARG;
+  if (!dims_eq(x, y)) return AD_ERR_BAD_ARG;
+  if (scratch_bytes < ad_bn_scratch_bytes(x->C)) return AD_ERR_SCRATCH;
+  const size_t total = (size_t)x->N * x->C * x->H * x->W;
+  if (total == 0) return AD_OK;
+  cudaStream_t s = as_stream(stream);
+  BnRed p{bview(x), bview(x), x->N, x->C, x->H, x->W, 0, nullptr, nullptr, nullptr, nullptr};
+  int nsplit = 1;
+  int st = launch_reduce<0>(p, x, (float*)scratch, nsplit, s);
+  if (st != AD_OK) return st;
+  const double count = (double)x->N * x->H * x->W;
+  bn_finalize<<<(x->C + 127) / 128, 128, 0, s>>>(x->C, nsplit, (const float*)scratch, count, eps, save_mean,
+                                                 save_invstd, batch_var);
+  count_launch();
+  BnApply a{bview(x), bview(x), bview(y), x->N, x->C, x->H, x->W, y->sc == 1 && y->C > 1, relu, 0,
+            gamma, beta, save_mean, save_invstd, nullptr, 1, count};
+  AD_DISPATCH_DTYPE(x->dtype, (bn_apply<T, 0><<<grid_for(total, 256, 16), 256, 0, s>>>(a)));
+  count_launch();
+  return launch_status();
+}
+
+extern "C" int ad_bn_bwd(const ad_tensor4* x, const ad_tensor4* dy, const ad_tensor4* dx, const float* gamma,
+                         const float* beta, const float* save_mean, const float* save_invstd, float* dgamma,
+                         float* dbeta, int32_t relu, int32_t accumulate_dx, void* scratch, size_t scratch_bytes,
+                         void* stream) {
+  if (!x || !dy || !dx || !x->base || !dy->base || !dx->base || !gamma || !beta || !save_mean || !save_invstd || !scratch)
+    return AD_ERR_BAD_ARG;
+  if (!dims_eq(x, dy) || !dims_eq(x, dx)) return AD_ERR_BAD_ARG;
+  if (scratch_bytes < ad_bn_scratch_bytes(x->C)) return AD_ERR_SCRATCH;
+  const size_t total = (size_t)x->N * x->C * x->H * x->W;
+  if (total == 0) return AD_OK;
+  cudaStream_t s = as_stream(stream);
+  BnRed p{bview(x), bview(dy), x->N, x->C, x->H, x->W, relu, gamma, beta, save_mean, save_invstd};
+  int nsplit = 1;
+  float* partial = (float*)scratch;
+  int st = launch_reduce<1>(p, x, partial, nsplit, s);
+  if (st != AD_OK) return st;
+  float* sums = partial + (size_t)kBnMaxSplits * 2 * x->C;
+  bn_combine<<<(2 * x->C + 255) / 256, 256, 0, s>>>(2 * x->C, nsplit, partial, sums);
+  count_launch();
+  if (dgamma || dbeta) {
+    bn_param_grads<<<(x->C + 127) / 128, 128, 0, s>>>(x->C, sums, dgamma, dbeta);
+    count_launch();
+  }
+  BnApply a{bview(x), bview(dy), bview(dx), x->N, x->C, x->H, x->W, dx->sc == 1 && dx->C > 1, relu, accumulate_dx,
+            gamma, beta, save_mean, save_invstd, sums, 1, (double)x->N * x->H * x->W};
+  AD_DISPATCH_DTYPE(x->dtype, (bn_apply<T, 1><<<grid_for(total, 256, 16), 256, 0, s>>>(a)));
+  count_launch();
+  return launch_status();
+}
+
+static int pool_params(const ad_tensor4* x, const ad_tensor4* y, uint32_t kh, uint32_t kw, uint32_t sh, uint32_t sw,
+                       PoolP& p) {
+  if (!x || !y || !x->base || !y->base || kh == 0 || kw == 0 || sh == 0 || sw == 0) return AD_ERR_BAD_ARG;
+  if (x->H < kh || x->W < kw) return AD_ERR_BAD_ARG;
+  const uint32_t P = (x->H - kh) / sh + 1, Q = (x->W - kw) / sw + 1;
+  if (y->N != x->N || y->C != x->C || y->H != P || y->W != Q || y->dtype != x->dtype) return AD_ERR_BAD_ARG;
+  p.x = bview(x);
+  p.N = x->N; p.C = x->C; p.H = x->H; p.W = x->W; p.P = P; p.Q = Q;
+  p.kh = kh; p.kw = kw; p.sh = sh; p.sw = sw;
+  return AD_OK;
+}
+
+extern "C" int ad_maxpool2d_fwd(const ad_tensor4* x, const ad_tensor4* y, uint32_t kh, uint32_t kw, uint32_t sh,
+                                uint32_t sw, void* stream) {
+  PoolP p{};
+  int st = pool_params(x, y, kh, kw, sh, sw, p);
+  if (st != AD_OK) return st;
+  p.y = bview(y);
+  p.c_fastest = y->sc == 1 && y->C > 1;
+  const size_t total = (size_t)p.N * p.C * p.P * p.Q;
+  if (total == 0) return AD_OK;
+  AD_DISPATCH_DTYPE(x->dtype, (maxpool_fwd_kernel<T><<<grid_for(total, 256, 16), 256, 0, as_stream(stream)>>>(p)));
+  count_launch();
+  return launch_status();
+}
+
+extern "C" int ad_maxpool2d_bwd(const ad_tensor4* x, const ad_tensor4* dy, const ad_tensor4* dx, uint32_t kh,
+                                uint32_t kw, uint32_t sh, uint32_t sw, int32_t accumulate, void* stream) {
+  PoolP p{};
+  int st = pool_params(x, dy, kh, kw, sh, sw, p);
+  if (st != AD_OK) return st;
+  if (!dx || !dx->base || dx->N != x->N || dx->C != x->C || dx->H != x->H || dx->W != x->W || dx->dtype != x->dtype)
+    return AD_ERR_BAD_ARG;
+  p.dy = bview(dy);
+  p.dx = bview(dx);
+  p.c_fastest = dx->sc == 1 && dx->C > 1;
+  p.accumulate = accumulate;
+  const size_t total = (size_t)p.N * p.C * p.H * p.W;
+  if (total == 0) return AD_OK;
+  AD_DISPATCH_DTYPE(x->dtype, (maxpool_bwd_kernel<T><<<grid_for(total, 256, 16), 256, 0, as_stream(stream)>>>(p)));
+  count_launch();
+  return launch_status();
+}

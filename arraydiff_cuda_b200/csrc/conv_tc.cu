@@ -1,0 +1,739 @@
+// Implicit-GEMM convolution on the 5th-generation tensor cores (tcgen05.mma, accumulators in
+// tensor memory), operands staged by TMA tile loads into 128-byte-swizzled shared memory.
+// NHWC bf16 activations, KRSC bf16 filters, fp32 accumulate.
+//
+//   forward / data gradient   conv_tc_fwd_kernel
+//       GEMM  M = 128 output pixels (a TH x TW patch of one image), N = BN output channels,
+//       K = taps x channels walked in 64-channel slabs.  For every (tap, slab) ONE 4-D TMA box
+//       load fetches the shifted (dilated, strided) activation patch [128 pixels][64 ch], which
+//       lands exactly in the K-major SWIZZLE_128B operand layout, so no im2col is materialised.
+//       The data gradient of a stride-1 convolution is the same kernel run over dy with the
+//       taps mirrored and the filter transposed to C,R,S,K.
+//       Persistent CTAs (one per SM) loop over tiles; warp 0 = TMA producer, warp 1 = MMA
+//       issuer (one elected thread), warps 2-5 = epilogue.  Two accumulators in tensor memory
+//       let the epilogue of tile i overlap the MMAs of tile i+1.
+//   filter gradient           conv_tc_wgrad_kernel
+//       GEMM  M = 128 output channels of dy, N = BN input channels of x, K = pixels.  Both
+//       operands are the NHWC tiles as TMA delivers them ([pixel][64 ch] rows), consumed as
+//       MN-major operands.  The pixel range is split across CTAs; each split writes an fp32
+//       partial to caller scratch and a second kernel sums the partials in a fixed order
+//       (reproducible, no atomics).
+//
+// Every mbarrier wait is bounded; on expiry the kernel raises an abort flag, all roles leave
+// their loops, tensor memory is freed and AD_ERR_TIMEOUT is written to a status word.
+// No TMA load here uses cluster multicast.
+#include "common.cuh"
+#include "tc_common.cuh"
+
+#include <mutex>
+
+namespace adk {
+namespace tc {
+
+EncodeTiledFn get_encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+    else
+      cudaGetLastError();
+  });
+  return fn;
+}
+
+int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                   const uint32_t* box, const uint32_t* elem_strides) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return AD_ERR_CUDA;
+  if (((uintptr_t)base & 15u) != 0) return AD_ERR_ALIGN;
+  cuuint64_t gdim[5], gstr[5];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bx[i] = box[i];
+    es[i] = elem_strides[i];
+    if (box[i] == 0 || box[i] > 256) return AD_ERR_UNSUPPORTED;
+  }
+  for (int i = 1; i < rank; ++i) {
+    gstr[i - 1] = strides_bytes[i];
+    if (strides_bytes[i] % 16) return AD_ERR_ALIGN;
+  }
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, bx, es,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? AD_OK : AD_ERR_CUDA;
+}
+
+constexpr int kTileM = 128;         // pixels (fwd) / dy channels (wgrad) per tile = TMEM lanes
+constexpr int kSlabBytes = 16384;   // one [128 rows][64 bf16] swizzled operand slab
+constexpr int kThreads = 192;       // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
+
+struct FwdParams {
+  uint32_t NI, OP, OQ, OC;  // output: images, rows, cols, channels
+  uint32_t CK;              // reduction channels per tap (multiple of 64)
+  uint32_t kh, kw, sh, sw, dh, dw;
+  int32_t offy, offx;       // input row = oy*sh + r*dh + offy
+  uint32_t TH, TW, tiles_y, tiles_x, tiles_n;
+  long long out_pitch, out_plane;  // elements between output rows / images
+  __nv_bfloat16* out;
+  const float* bias;
+  int32_t relu, accumulate;
+  int32_t* status;
+};
+
+struct SmemCtl {
+  unsigned long long full[8], empty[8], tfull[2], tempty[2];
+  uint32_t tmem_base;
+  volatile int abort_flag;
+};
+
+__device__ __forceinline__ uint32_t pow2_cols(uint32_t c) {
+  uint32_t p = 32;
+  while (p < c) p <<= 1;
+  return p;
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                   const FwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  constexpr uint32_t kStageBytes = kSlabBytes + BN * 128;
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  SmemCtl* ctl = (SmemCtl*)(smem + (size_t)STAGES * kStageBytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t tiles_m = p.NI * p.tiles_y * p.tiles_x;
+  const uint32_t total_tiles = tiles_m * p.tiles_n;
+  const uint32_t slabs = p.CK / 64;
+  const uint32_t kiters = p.kh * p.kw * slabs;
+  constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // BN in {32,64,128,256} -> power of two
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&ctl->full[s]), 1);
+      mbar_init(smem_u32(&ctl->empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&ctl->tfull[a]), 1);
+      mbar_init(smem_u32(&ctl->tempty[a]), 4);
+    }
+    ctl->abort_flag = 0;
+    mbar_init_fence();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  volatile int* abortf = &ctl->abort_flag;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      for (uint32_t tile = blockIdx.x; tile < total_tiles && !*abortf; tile += gridDim.x) {
+        const uint32_t tn = tile / tiles_m, tm = tile % tiles_m;
+        const uint32_t tx = tm % p.tiles_x, ty = (tm / p.tiles_x) % p.tiles_y, n = tm / (p.tiles_x * p.tiles_y);
+        const int x0 = (int)(tx * p.TW * p.sw) + p.offx, y0 = (int)(ty * p.TH * p.sh) + p.offy;
+        bool ok = true;
+        for (uint32_t r = 0; r < p.kh && ok; ++r)
+          for (uint32_t s = 0; s < p.kw && ok; ++s)
+            for (uint32_t cb = 0; cb < slabs; ++cb) {
+              if (!mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1u, abortf)) { ok = false; break; }
+              const uint32_t full = smem_u32(&ctl->full[stage]);
+              uint8_t* st = smem + (size_t)stage * kStageBytes;
+              mbar_expect_tx(full, kStageBytes);
+              tma_load_4d(smem_u32(st), &map_a, full, (int)(cb * 64), x0 + (int)(s * p.dw), y0 + (int)(r * p.dh), (int)n);
+              tma_load_2d(smem_u32(st + kSlabBytes), &map_b, full, (int)((r * p.kw + s) * p.CK + cb * 64), (int)(tn * BN));
+              if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_bf16(BN, 0, 0);
+      uint32_t stage = 0, phase = 0, it = 0;
+      for (uint32_t tile = blockIdx.x; tile < total_tiles && !*abortf; tile += gridDim.x, ++it) {
+        const uint32_t acc = it & 1u, acc_phase = (it >> 1) & 1u;
+        if (!mbar_wait(smem_u32(&ctl->tempty[acc]), acc_phase ^ 1u, abortf)) break;
+        tc_fence_after();
+        const uint32_t d = tmem_base + acc * BN;
+        bool ok = true;
+        for (uint32_t k = 0; k < kiters; ++k) {
+          if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abortf)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + (size_t)stage * kStageBytes);
+          const uint64_t da = smem_desc_sw128(sa, 16, 1024), db = smem_desc_sw128(sa + kSlabBytes, 16, 1024);
+#pragma unroll
+          for (uint32_t kk = 0; kk < 4; ++kk)  // 4 x (K = 16 bf16 = 32 bytes) inside the 128-byte row
+            umma_bf16(d, da + 2 * kk, db + 2 * kk, idesc, (k | kk) != 0u);
+          umma_commit(smem_u32(&ctl->empty[stage]));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(smem_u32(&ctl->tfull[acc]));
+      }
+    }
+  } else {
+    const uint32_t q = (uint32_t)warp & 3u;  // TMEM lane quarter this warp may read
+    uint32_t it = 0;
+    for (uint32_t tile = blockIdx.x; tile < total_tiles && !*abortf; tile += gridDim.x, ++it) {
+      const uint32_t acc = it & 1u, acc_phase = (it >> 1) & 1u;
+      const uint32_t tn = tile / tiles_m, tm = tile % tiles_m;
+      const uint32_t tx = tm % p.tiles_x, ty = (tm / p.tiles_x) % p.tiles_y, n = tm / (p.tiles_x * p.tiles_y);
+      if (!mbar_wait(smem_u32(&ctl->tfull[acc]), acc_phase, abortf)) break;
+      tc_fence_after();
+      const uint32_t m = q * 32 + lane;
+      const uint32_t oy = ty * p.TH + m / p.TW, ox = tx * p.TW + m % p.TW;
+      const bool valid = oy < p.OP && ox < p.OQ;
+      __nv_bfloat16* orow = p.out + (long long)n * p.out_plane + (long long)oy * p.out_pitch + (long long)ox * p.OC;
+#pragma unroll 1
+      for (uint32_t ch = 0; ch < BN / 32; ++ch) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + ((q * 32u) << 16) + acc * BN + ch * 32, v);
+        tmem_ld_wait();
+        const uint32_t c0 = tn * BN + ch * 32;
+        if (valid && c0 < p.OC) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const uint32_t cg = c0 + g * 8;
+            float f[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              f[j] = __uint_as_float(v[g * 8 + j]);
+              if (p.bias && cg + j < p.OC) f[j] += p.bias[cg + j];
+            }
+            if (cg + 8 <= p.OC && (p.OC & 7u) == 0) {
+              if (p.accumulate) {
+                uint4 old = *(const uint4*)(orow + cg);
+                const __nv_bfloat162* o2 = (const __nv_bfloat162*)&old;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  float2 t = __bfloat1622float2(o2[j]);
+                  f[2 * j] += t.x; f[2 * j + 1] += t.y;
+                }
+              }
+              if (p.relu) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = fmaxf(f[j], 0.f);
+              }
+              uint4 pk;
+              __nv_bfloat162* p2 = (__nv_bfloat162*)&pk;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) p2[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+              *(uint4*)(orow + cg) = pk;
+            } else {
+              for (int j = 0; j < 8; ++j)
+                if (cg + j < p.OC) {
+                  float t = f[j];
+                  if (p.accumulate) t += __bfloat162float(orow[cg + j]);
+                  if (p.relu) t = fmaxf(t, 0.f);
+                  orow[cg + j] = __float2bfloat16_rn(t);
+                }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctl->tempty[acc]));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abortf) {
+    // Let any tile copy that is still in flight land before shared memory is released.
+    for (int i = 0; i < 2000; ++i) __nanosleep(500);
+    if (threadIdx.x == 0 && p.status) *p.status = AD_ERR_TIMEOUT;
+  }
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------- filter gradient
+struct WgParams {
+  uint32_t NI, OP, OQ;  // dy: images, rows, cols
+  uint32_t KO, CI;      // dy channels (GEMM M), x channels (GEMM N)
+  uint32_t kh, kw, sh, sw, dh, dw;
+  int32_t offy, offx;
+  uint32_t TH, TW, tiles_y, tiles_x;
+  uint32_t ktiles, ctiles, splits;
+  float* partial;       // [splits][KO][kh*kw][CI]
+  int32_t* status;
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+conv_tc_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_constant__ CUtensorMap map_x,
+                     const WgParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  constexpr uint32_t kABytes = 2 * kSlabBytes, kBBytes = (BN / 64) * kSlabBytes, kStageBytes = kABytes + kBBytes;
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  SmemCtl* ctl = (SmemCtl*)(smem + (size_t)STAGES * kStageBytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
+
+  // blockIdx.y -> (tap, k tile, c tile); blockIdx.x -> split of the pixel tiles
+  const uint32_t split = blockIdx.x;
+  uint32_t rem = blockIdx.y;
+  const uint32_t ct = rem % p.ctiles; rem /= p.ctiles;
+  const uint32_t kt = rem % p.ktiles; rem /= p.ktiles;
+  const uint32_t tap = rem, r = tap / p.kw, s = tap % p.kw;
+  const uint32_t sp_tiles = p.NI * p.tiles_y * p.tiles_x;
+  const uint32_t my_tiles = split < sp_tiles ? (sp_tiles - split + p.splits - 1) / p.splits : 0;
+
+  if (threadIdx.x == 0) {
+    for (int st = 0; st < STAGES; ++st) {
+      mbar_init(smem_u32(&ctl->full[st]), 1);
+      mbar_init(smem_u32(&ctl->empty[st]), 1);
+    }
+    mbar_init(smem_u32(&ctl->tfull[0]), 1);
+    ctl->abort_flag = 0;
+    mbar_init_fence();
+    tma_prefetch_desc(&map_dy);
+    tma_prefetch_desc(&map_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  volatile int* abortf = &ctl->abort_flag;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      for (uint32_t j = 0; j < my_tiles; ++j) {
+        const uint32_t tm = split + j * p.splits;
+        const uint32_t tx = tm % p.tiles_x, ty = (tm / p.tiles_x) % p.tiles_y, n = tm / (p.tiles_x * p.tiles_y);
+        if (!mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1u, abortf)) break;
+        const uint32_t full = smem_u32(&ctl->full[stage]);
+        uint8_t* st = smem + (size_t)stage * kStageBytes;
+        mbar_expect_tx(full, kStageBytes);
+        const int qx = (int)(tx * p.TW), qy = (int)(ty * p.TH);
+        tma_load_4d(smem_u32(st), &map_dy, full, (int)(kt * 128), qx, qy, (int)n);
+        tma_load_4d(smem_u32(st + kSlabBytes), &map_dy, full, (int)(kt * 128 + 64), qx, qy, (int)n);
+        const int ix = qx * (int)p.sw + (int)(s * p.dw) + p.offx, iy = qy * (int)p.sh + (int)(r * p.dh) + p.offy;
+#pragma unroll
+        for (int b = 0; b < BN / 64; ++b)
+          tma_load_4d(smem_u32(st + kABytes + b * kSlabBytes), &map_x, full, (int)(ct * BN + b * 64), ix, iy, (int)n);
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_bf16(BN, 1, 1);
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (uint32_t j = 0; j < my_tiles; ++j) {
+        if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abortf)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + (size_t)stage * kStageBytes);
+#pragma unroll
+        for (uint32_t ks = 0; ks < 8; ++ks) {  // 8 x (K = 16 pixels = 16 rows of 128 B)
+          const uint64_t da = smem_desc_sw128(sa + ks * 2048, kSlabBytes, 1024);
+          const uint64_t db = smem_desc_sw128(sa + kABytes + ks * 2048, kSlabBytes, 1024);
+          umma_bf16(tmem_base, da, db, idesc, (j | ks) != 0u);
+        }
+        umma_commit(smem_u32(&ctl->empty[stage]));
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      }
+      if (ok) umma_commit(smem_u32(&ctl->tfull[0]));
+    }
+  } else {
+    const uint32_t q = (uint32_t)warp & 3u;
+    const uint32_t taps = p.kh * p.kw;
+    const uint32_t k = kt * 128 + q * 32 + lane;
+    float* orow = p.partial + (((size_t)split * p.KO + k) * taps + tap) * p.CI + (size_t)ct * BN;
+    if (my_tiles == 0) {
+      if (k < p.KO)
+        for (uint32_t c = 0; c < BN && ct * BN + c < p.CI; ++c) orow[c] = 0.f;
+    } else if (mbar_wait(smem_u32(&ctl->tfull[0]), 0, abortf)) {
+      tc_fence_after();
+#pragma unroll 1
+      for (uint32_t ch = 0; ch < BN / 32; ++ch) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + ((q * 32u) << 16) + ch * 32, v);
+        tmem_ld_wait();
+        if (k < p.KO) {
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const uint32_t c = ct * BN + ch * 32 + g * 4;
+            if (c + 4 <= p.CI)
+              *(float4*)(orow + ch * 32 + g * 4) = make_float4(__uint_as_float(v[g * 4]), __uint_as_float(v[g * 4 + 1]),
+                                                               __uint_as_float(v[g * 4 + 2]), __uint_as_float(v[g * 4 + 3]));
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abortf) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(500);
+    if (threadIdx.x == 0 && p.status) *p.status = AD_ERR_TIMEOUT;
+  }
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// dw[i] (+)= sum over splits of partial[s][i], fixed order.
+__global__ void __launch_bounds__(256) wgrad_reduce_kernel(size_t n, uint32_t splits, const float* __restrict__ partial,
+                                                           float* dw, int accumulate) {
+  const size_t nt = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += nt) {
+    float t = 0.f;
+    for (uint32_t s = 0; s < splits; ++s) t += partial[(size_t)s * n + i];
+    dw[i] = accumulate ? dw[i] + t : t;
+  }
+}
+
+// Filter for the data gradient: wt[c][kh-1-r][kw-1-s][k] = w[k][r][s][c]  (bf16).
+__global__ void __launch_bounds__(256) filter_transpose_flip_kernel(uint32_t K, uint32_t kh, uint32_t kw, uint32_t C,
+                                                                    const __nv_bfloat16* __restrict__ w,
+                                                                    __nv_bfloat16* wt) {
+  const size_t total = (size_t)K * kh * kw * C, nt = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nt) {
+    uint32_t k = (uint32_t)(i % K);
+    size_t rr = i / K;
+    uint32_t s = (uint32_t)(rr % kw); rr /= kw;
+    uint32_t r = (uint32_t)(rr % kh);
+    uint32_t c = (uint32_t)(rr / kh);
+    wt[i] = w[(((size_t)k * kh + (kh - 1 - r)) * kw + (kw - 1 - s)) * C + c];
+  }
+}
+
+// db[k] (+)= sum over pixels of dy[pixel][k]   (NHWC bf16 view with row / image pitches).
+__global__ void __launch_bounds__(256) bias_grad_nhwc_kernel(uint32_t NI, uint32_t OP, uint32_t OQ, uint32_t K,
+                                                             long long pitch, long long plane,
+                                                             const __nv_bfloat16* __restrict__ dy, float* db,
+                                                             int accumulate) {
+  // block = 32 channels x 8 pixel lanes; one block per channel group (bias gradients are tiny).
+  const uint32_t k = blockIdx.x * 32 + threadIdx.x;
+  float acc = 0.f;
+  const size_t per = (size_t)NI * OP * OQ;
+  if (k < K)
+    for (size_t i = threadIdx.y; i < per; i += 8) {
+      uint32_t x = (uint32_t)(i % OQ);
+      size_t rr = i / OQ;
+      uint32_t y = (uint32_t)(rr % OP), n = (uint32_t)(rr / OP);
+      acc += __bfloat162float(dy[(long long)n * plane + (long long)y * pitch + (long long)x * K + k]);
+    }
+  __shared__ float red[8][33];
+  red[threadIdx.y][threadIdx.x] = acc;
+  __syncthreads();
+  if (threadIdx.y == 0 && k < K) {
+    float t = 0.f;
+    for (int w = 0; w < 8; ++w) t += red[w][threadIdx.x];
+    db[k] = accumulate ? db[k] + t : t;
+  }
+}
+
+// ---------------------------------------------------------------- host side
+struct Geo {
+  uint32_t P, Q;
+};
+static int conv_geo(const ad_conv2d_args* a, Geo& g) {
+  if (!a) return AD_ERR_BAD_ARG;
+  if (a->N == 0 || a->C == 0 || a->H == 0 || a->W == 0 || a->K == 0 || a->kh == 0 || a->kw == 0) return AD_ERR_BAD_ARG;
+  if (a->stride_h == 0 || a->stride_w == 0 || a->dil_h == 0 || a->dil_w == 0) return AD_ERR_BAD_ARG;
+  const long long eh = (long long)a->H + 2ll * a->pad_h - (long long)a->dil_h * (a->kh - 1) - 1;
+  const long long ew = (long long)a->W + 2ll * a->pad_w - (long long)a->dil_w * (a->kw - 1) - 1;
+  if (eh < 0 || ew < 0) return AD_ERR_BAD_ARG;
+  g.P = (uint32_t)(eh / a->stride_h + 1);
+  g.Q = (uint32_t)(ew / a->stride_w + 1);
+  return AD_OK;
+}
+
+// Spatial patch of 128 output pixels wasting the fewest lanes on partial tiles.
+static void pick_tile(uint32_t OP, uint32_t OQ, uint32_t sh, uint32_t sw, uint32_t& TH, uint32_t& TW) {
+  unsigned long long best = ~0ull;
+  TH = 1; TW = 128;
+  for (uint32_t tw = 128; tw >= 8; tw >>= 1) {
+    const uint32_t th = 128 / tw;
+    if (tw * sw > 256 || th * sh > 256) continue;
+    const unsigned long long cost = (unsigned long long)((OQ + tw - 1) / tw * tw) * ((OP + th - 1) / th * th);
+    if (cost < best) { best = cost; TH = th; TW = tw; }
+  }
+}
+
+template <int BN>
+static int launch_fwd(const CUtensorMap& ma, const CUtensorMap& mb, const FwdParams& p, cudaStream_t s) {
+  constexpr int kStageBytes = kSlabBytes + BN * 128;
+  constexpr int STAGES = (200 * 1024) / kStageBytes > 8 ? 8 : (200 * 1024) / kStageBytes;
+  constexpr int smem = STAGES * kStageBytes + 1024 + (int)sizeof(SmemCtl);
+  static unsigned attr_done = 0;  // one bit per device: the attribute is per device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!(attr_done & (1u << (dev & 31)))) {
+    if (cudaFuncSetAttribute(conv_tc_fwd_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+        cudaSuccess) {
+      cudaGetLastError();
+      return AD_ERR_CUDA;
+    }
+    attr_done |= 1u << (dev & 31);
+  }
+  const uint32_t total = p.NI * p.tiles_y * p.tiles_x * p.tiles_n;
+  const unsigned grid = total < (uint32_t)kNumSMs ? total : kNumSMs;
+  conv_tc_fwd_kernel<BN, STAGES><<<grid, kThreads, smem, s>>>(ma, mb, p);
+  count_launch();
+  return launch_status();
+}
+
+// Generic forward-style implicit GEMM launch (fprop, or dgrad expressed as fprop).
+static int run_fwd_gemm(const void* act, uint32_t NI, uint32_t IH, uint32_t IW, uint32_t CK, const void* filt,
+                        uint32_t OC, uint32_t kh, uint32_t kw, uint32_t sh, uint32_t sw, uint32_t dh, uint32_t dw,
+                        int offy, int offx, uint32_t OP, uint32_t OQ, void* out, long long out_pitch,
+                        long long out_plane, const float* bias, int relu, int accumulate, int32_t* status,
+                        cudaStream_t s) {
+  if (CK % 64 != 0) return AD_ERR_UNSUPPORTED;
+  FwdParams p{};
+  p.NI = NI; p.OP = OP; p.OQ = OQ; p.OC = OC; p.CK = CK;
+  p.kh = kh; p.kw = kw; p.sh = sh; p.sw = sw; p.dh = dh; p.dw = dw; p.offy = offy; p.offx = offx;
+  pick_tile(OP, OQ, sh, sw, p.TH, p.TW);
+  p.tiles_y = (OP + p.TH - 1) / p.TH;
+  p.tiles_x = (OQ + p.TW - 1) / p.TW;
+  const int BN = OC > 128 ? 256 : (OC > 64 ? 128 : (OC > 32 ? 64 : 32));
+  p.tiles_n = (OC + BN - 1) / BN;
+  p.out_pitch = out_pitch ? out_pitch : (long long)OQ * OC;
+  p.out_plane = out_plane ? out_plane : (long long)OP * OQ * OC;
+  if (((uintptr_t)out & 15u) || (p.out_pitch % 8) || (p.out_plane % 8)) {
+    if ((OC & 7u) == 0) return AD_ERR_ALIGN;
+  }
+  p.out = (__nv_bfloat16*)out;
+  p.bias = bias; p.relu = relu; p.accumulate = accumulate; p.status = status;
+
+  CUtensorMap ma, mb;
+  {
+    uint64_t dims[4] = {CK, IW, IH, NI};
+    uint64_t str[4] = {0, (uint64_t)CK * 2, (uint64_t)IW * CK * 2, (uint64_t)IH * IW * CK * 2};
+    uint32_t box[4] = {64, p.TW * sw, p.TH * sh, 1};
+    uint32_t es[4] = {1, sw, sh, 1};
+    int st = make_tmap_bf16(&ma, act, 4, dims, str, box, es);
+    if (st != AD_OK) return st;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)kh * kw * CK, OC};
+    uint64_t str[2] = {0, (uint64_t)kh * kw * CK * 2};
+    uint32_t box[2] = {64, (uint32_t)BN};
+    uint32_t es[2] = {1, 1};
+    int st = make_tmap_bf16(&mb, filt, 2, dims, str, box, es);
+    if (st != AD_OK) return st;
+  }
+  switch (BN) {
+    case 256: return launch_fwd<256>(ma, mb, p, s);
+    case 128: return launch_fwd<128>(ma, mb, p, s);
+    case 64: return launch_fwd<64>(ma, mb, p, s);
+    default: return launch_fwd<32>(ma, mb, p, s);
+  }
+}
+
+template <int BN>
+static int launch_wgrad(const CUtensorMap& mdy, const CUtensorMap& mx, const WgParams& p, cudaStream_t s) {
+  constexpr int kStageBytes = 2 * kSlabBytes + (BN / 64) * kSlabBytes;
+  constexpr int STAGES = (200 * 1024) / kStageBytes;
+  constexpr int smem = STAGES * kStageBytes + 1024 + (int)sizeof(SmemCtl);
+  static unsigned attr_done = 0;  // one bit per device: the attribute is per device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!(attr_done & (1u << (dev & 31)))) {
+    if (cudaFuncSetAttribute(conv_tc_wgrad_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+        cudaSuccess) {
+      cudaGetLastError();
+      return AD_ERR_CUDA;
+    }
+    attr_done |= 1u << (dev & 31);
+  }
+  dim3 grid(p.splits, p.kh * p.kw * p.ktiles * p.ctiles);
+  conv_tc_wgrad_kernel<BN, STAGES><<<grid, kThreads, smem, s>>>(mdy, mx, p);
+  count_launch();
+  return launch_status();
+}
+
+static uint32_t wgrad_splits(uint32_t sp_tiles, uint32_t outer) {
+  uint32_t want = (2 * kNumSMs + outer - 1) / outer;
+  if (want > sp_tiles) want = sp_tiles;
+  if (want > 64) want = 64;
+  if (want < 1) want = 1;
+  return want;
+}
+
+size_t conv_tc_scratch_bytes(const ad_conv2d_args* a, int pass) {
+  Geo g;
+  if (conv_geo(a, g) != AD_OK) return 0;
+  const size_t wcount = (size_t)a->K * a->kh * a->kw * a->C;
+  if (pass == 1) return wcount * 2 + 16;  // transposed, mirrored filter (bf16) + status word
+  if (pass == 2) {
+    uint32_t TH, TW;
+    pick_tile(g.P, g.Q, 1, 1, TH, TW);
+    const uint32_t sp = a->N * ((g.P + TH - 1) / TH) * ((g.Q + TW - 1) / TW);
+    const uint32_t BN = a->C > 64 ? 128 : 64;
+    const uint32_t outer = a->kh * a->kw * ((a->K + 127) / 128) * ((a->C + BN - 1) / BN);
+    return (size_t)wgrad_splits(sp, outer) * wcount * 4 + 16;
+  }
+  return 16;
+}
+
+int conv_tc_fprop(const ad_conv2d_args* a, cudaStream_t s) {
+  Geo g;
+  int st = conv_geo(a, g);
+  if (st != AD_OK) return st;
+  if (!a->x || !a->w || !a->y) return AD_ERR_BAD_ARG;
+  if (a->pad_h || a->pad_w) {
+    // Implicit padding is served by TMA's out-of-bounds zero fill (negative start coordinates).
+  }
+  int32_t* status = (a->scratch && a->scratch_bytes >= 16) ? (int32_t*)a->scratch : nullptr;
+  return run_fwd_gemm(a->x, a->N, a->H, a->W, a->C, a->w, a->K, a->kh, a->kw, a->stride_h, a->stride_w, a->dil_h,
+                      a->dil_w, -(int)a->pad_h, -(int)a->pad_w, g.P, g.Q, a->y, a->y_pitch, a->y_plane, a->bias, a->relu,
+                      0, status, s);
+}
+
+int conv_tc_dgrad(const ad_conv2d_args* a, cudaStream_t s) {
+  Geo g;
+  int st = conv_geo(a, g);
+  if (st != AD_OK) return st;
+  if (!a->y || !a->w || !a->dx || !a->scratch) return AD_ERR_BAD_ARG;
+  if (a->stride_h != 1 || a->stride_w != 1) return AD_ERR_UNSUPPORTED;
+  if (a->y_pitch || a->y_plane) return AD_ERR_UNSUPPORTED;  // dy must be dense for the TMA view
+  if (a->K % 64 != 0) return AD_ERR_UNSUPPORTED;
+  if (a->scratch_bytes < conv_tc_scratch_bytes(a, 1)) return AD_ERR_SCRATCH;
+  int32_t* status = (int32_t*)a->scratch;
+  __nv_bfloat16* wt = (__nv_bfloat16*)((char*)a->scratch + 16);
+  const size_t wcount = (size_t)a->K * a->kh * a->kw * a->C;
+  filter_transpose_flip_kernel<<<grid_for(wcount, 256), 256, 0, s>>>(a->K, a->kh, a->kw, a->C,
+                                                                     (const __nv_bfloat16*)a->w, wt);
+  count_launch();
+  // dx[n,yy,xx,c] = sum_{r',s',k} dy[n, yy + ph - (kh-1)*dh + r'*dh, xx + ..., k] * wt[c][r'][s'][k]
+  const int offy = (int)a->pad_h - (int)((a->kh - 1) * a->dil_h), offx = (int)a->pad_w - (int)((a->kw - 1) * a->dil_w);
+  return run_fwd_gemm(a->y, a->N, g.P, g.Q, a->K, wt, a->C, a->kh, a->kw, 1, 1, a->dil_h, a->dil_w, offy, offx, a->H,
+                      a->W, a->dx, 0, 0, nullptr, 0, a->accumulate, status, s);
+}
+
+int conv_tc_wgrad(const ad_conv2d_args* a, cudaStream_t s) {
+  Geo g;
+  int st = conv_geo(a, g);
+  if (st != AD_OK) return st;
+  if (!a->x || !a->y || !a->dw || !a->scratch) return AD_ERR_BAD_ARG;
+  if (a->y_pitch || a->y_plane) return AD_ERR_UNSUPPORTED;
+  if (a->C % 64 != 0 || a->K % 8 != 0) return AD_ERR_UNSUPPORTED;
+  if (a->scratch_bytes < conv_tc_scratch_bytes(a, 2)) return AD_ERR_SCRATCH;
+  WgParams p{};
+  p.NI = a->N; p.OP = g.P; p.OQ = g.Q; p.KO = a->K; p.CI = a->C;
+  p.kh = a->kh; p.kw = a->kw; p.sh = a->stride_h; p.sw = a->stride_w; p.dh = a->dil_h; p.dw = a->dil_w;
+  p.offy = -(int)a->pad_h; p.offx = -(int)a->pad_w;
+  // The tile is chosen for the dy grid; the x box is the same patch scaled by the stride.
+  pick_tile(g.P, g.Q, a->stride_h, a->stride_w, p.TH, p.TW);
+  {
+    uint32_t th, tw;
+    pick_tile(g.P, g.Q, 1, 1, th, tw);
+    if (th * a->stride_h <= 256 && tw * a->stride_w <= 256) { p.TH = th; p.TW = tw; }
+  }
+  p.tiles_y = (g.P + p.TH - 1) / p.TH;
+  p.tiles_x = (g.Q + p.TW - 1) / p.TW;
+  const int BN = a->C > 64 ? 128 : 64;
+  p.ktiles = (a->K + 127) / 128;
+  p.ctiles = (a->C + BN - 1) / BN;
+  const uint32_t sp_tiles = p.NI * p.tiles_y * p.tiles_x;
+  p.splits = wgrad_splits(sp_tiles, p.kh * p.kw * p.ktiles * p.ctiles);
+  p.status = (int32_t*)a->scratch;
+  p.partial = (float*)((char*)a->scratch + 16);
+  const size_t wcount = (size_t)a->K * a->kh * a->kw * a->C;
+  if (a->scratch_bytes < (size_t)p.splits * wcount * 4 + 16) return AD_ERR_SCRATCH;
+
+  CUtensorMap mdy, mx;
+  {
+    uint64_t dims[4] = {a->K, g.Q, g.P, a->N};
+    uint64_t str[4] = {0, (uint64_t)a->K * 2, (uint64_t)g.Q * a->K * 2, (uint64_t)g.P * g.Q * a->K * 2};
+    uint32_t box[4] = {64, p.TW, p.TH, 1};
+    uint32_t es[4] = {1, 1, 1, 1};
+    st = make_tmap_bf16(&mdy, a->y, 4, dims, str, box, es);
+    if (st != AD_OK) return st;
+  }
+  {
+    uint64_t dims[4] = {a->C, a->W, a->H, a->N};
+    uint64_t str[4] = {0, (uint64_t)a->C * 2, (uint64_t)a->W * a->C * 2, (uint64_t)a->H * a->W * a->C * 2};
+    uint32_t box[4] = {64, p.TW * a->stride_w, p.TH * a->stride_h, 1};
+    uint32_t es[4] = {1, a->stride_w, a->stride_h, 1};
+    st = make_tmap_bf16(&mx, a->x, 4, dims, str, box, es);
+    if (st != AD_OK) return st;
+  }
+  st = BN == 128 ? launch_wgrad<128>(mdy, mx, p, s) : launch_wgrad<64>(mdy, mx, p, s);
+  if (st != AD_OK) return st;
+  wgrad_reduce_kernel<<<grid_for(wcount, 256), 256, 0, s>>>(wcount, p.splits, p.partial, (float*)a->dw, a->accumulate);
+  count_launch();
+  if (a->db) {
+    dim3 block(32, 8);
+    bias_grad_nhwc_kernel<<<(a->K + 31) / 32, block, 0, s>>>(a->N, g.P, g.Q, a->K, (long long)g.Q * a->K,
+                                                             (long long)g.P * g.Q * a->K, (const __nv_bfloat16*)a->y,
+                                                             a->db, a->accumulate);
+    count_launch();
+  }
+  return launch_status();
+}
+
+}  // namespace tc
+
+// fp32 direct path (conv_direct.cu)
+int conv_direct_fprop(const ad_conv2d_args* a, cudaStream_t s);
+int conv_direct_dgrad(const ad_conv2d_args* a, cudaStream_t s);
+int conv_direct_wgrad(const ad_conv2d_args* a, cudaStream_t s);
+
+}  // namespace adk
+
+using namespace adk;
+
+static int path_of(const ad_conv2d_args* a) {
+  if (!a) return -1;
+  if (a->dtype == AD_F32 && a->layout == AD_NCHW) return 0;
+  if (a->dtype == AD_BF16 && a->layout == AD_NHWC) return 1;
+  return -1;
+}
+
+extern "C" size_t ad_conv2d_scratch_bytes(const ad_conv2d_args* a, int32_t pass) {
+  if (path_of(a) != 1) return 0;
+  return tc::conv_tc_scratch_bytes(a, pass);
+}
+
+extern "C" int ad_conv2d_fprop(const ad_conv2d_args* a, void* stream) {
+  switch (path_of(a)) {
+    case 0: return conv_direct_fprop(a, as_stream(stream));
+    case 1: return tc::conv_tc_fprop(a, as_stream(stream));
+    default: return a ? AD_ERR_UNSUPPORTED : AD_ERR_BAD_ARG;
+  }
+}
+extern "C" int ad_conv2d_dgrad(const ad_conv2d_args* a, void* stream) {
+  switch (path_of(a)) {
+    case 0: return conv_direct_dgrad(a, as_stream(stream));
+    case 1: return tc::conv_tc_dgrad(a, as_stream(stream));
+    default: return a ? AD_ERR_UNSUPPORTED : AD_ERR_BAD_ARG;
+  }
+}
+extern "C" int ad_conv2d_wgrad(const ad_conv2d_args* a, void* stream) {
+  switch (path_of(a)) {
+    case 0: return conv_direct_wgrad(a, as_stream(stream));
+    case 1: return tc::conv_tc_wgrad(a, as_stream(stream));
+    default: return a ? AD_ERR_UNSUPPORTED : AD_ERR_BAD_ARG;
+  }
+}

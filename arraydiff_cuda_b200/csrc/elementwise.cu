@@ -1,0 +1,221 @@
+// Packed fp32 array arithmetic, the fused SGD update, and strided ReLU / add / convert.
+// All HBM-bound: one read of each input and one write of each output, 16-byte vectors
+// where the pointers allow, grid-stride loops sized from the SM count.
+#include "common.cuh"
+
+namespace adk {
+
+unsigned long long g_launch_count = 0;
+
+// ---------------------------------------------------------------- packed fp32 arrays
+// The rounding of each expression is written out (explicit fmaf / __fmul_rn) so that the
+// result does not depend on compiler contraction and matches the reference kernels, which
+// nvcc compiles with fused multiply-add (src/kernels/array.cu:58-150).
+enum ArrOp { kSet, kAdd, kAddScaled, kAddOnline, kScale, kScaleAdd };
+
+template <int OP>
+__device__ __forceinline__ float arr_apply(float a, float b, float x, float y) {
+  switch (OP) {
+    case kSet: return a;
+    case kAdd: return __fadd_rn(x, y);
+    case kAddScaled: return fmaf(a, x, __fmul_rn(b, y));
+    case kAddOnline: return fmaf(a, __fsub_rn(x, y), y);
+    case kScale: return __fmul_rn(a, x);
+    default: return fmaf(a, x, y);
+  }
+}
+
+template <int OP>
+__global__ void __launch_bounds__(256) arr_kernel(size_t n, float a, float b, const float* __restrict__ x, float* y) {
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nt = (size_t)gridDim.x * blockDim.x;
+  const bool vec = (((uintptr_t)y | (uintptr_t)(OP == kSet ? (const float*)y : x)) & 15u) == 0;
+  if (vec) {
+    const size_t n4 = n / 4;
+    for (size_t i = tid; i < n4; i += nt) {
+      float4 xv = OP == kSet ? make_float4(0, 0, 0, 0) : reinterpret_cast<const float4*>(x)[i];
+      float4 yv = (OP == kSet || OP == kScale) ? make_float4(0, 0, 0, 0) : reinterpret_cast<float4*>(y)[i];
+      yv.x = arr_apply<OP>(a, b, xv.x, yv.x); yv.y = arr_apply<OP>(a, b, xv.y, yv.y);
+      yv.z = arr_apply<OP>(a, b, xv.z, yv.z); yv.w = arr_apply<OP>(a, b, xv.w, yv.w);
+      reinterpret_cast<float4*>(y)[i] = yv;
+    }
+    for (size_t i = n4 * 4 + tid; i < n; i += nt)
+      y[i] = arr_apply<OP>(a, b, OP == kSet ? 0.f : x[i], (OP == kSet || OP == kScale) ? 0.f : y[i]);
+  } else {
+    for (size_t i = tid; i < n; i += nt)
+      y[i] = arr_apply<OP>(a, b, OP == kSet ? 0.f : x[i], (OP == kSet || OP == kScale) ? 0.f : y[i]);
+  }
+}
+
+template <int OP>
+static int arr_launch(size_t n, float a, float b, const float* x, float* y, void* stream) {
+  if (n == 0) return AD_OK;
+  if (!y || (OP != kSet && !x)) return AD_ERR_BAD_ARG;
+  arr_kernel<OP><<<grid_for((n + 3) / 4, 256), 256, 0, as_stream(stream)>>>(n, a, b, x, y);
+  count_launch();
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- fused SGD
+__global__ void __launch_bounds__(256) sgd_kernel(size_t n, float* theta, float* g, float* m, float l2, float mu,
+                                                  float alpha, float alpha_next, int nesterov,
+                                                  __nv_bfloat16* shadow) {
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nt = (size_t)gridDim.x * blockDim.x;
+  const float nmu = __fmul_rn(-alpha_next, mu);
+  for (size_t i = tid; i < n; i += nt) {
+    float gi = g[i], th = theta[i], mi = m[i];
+    if (l2 != 0.f) gi = fmaf(l2, th, __fmul_rn(1.0f, gi));
+    mi = fmaf(1.0f, gi, __fmul_rn(mu, mi));
+    if (nesterov) {
+      th = fmaf(-alpha, gi, __fmul_rn(1.0f, th));
+      th = fmaf(nmu, mi, __fmul_rn(1.0f, th));
+    } else {
+      th = fmaf(-alpha, mi, __fmul_rn(1.0f, th));
+    }
+    g[i] = gi; m[i] = mi; theta[i] = th;
+    if (shadow) shadow[i] = __float2bfloat16_rn(th);
+  }
+}
+
+// ---------------------------------------------------------------- strided views
+struct View {
+  char* base;
+  long long sn, sc, sy, sx;
+};
+static View view_of(const ad_tensor4* t) { return View{(char*)t->base, t->sn, t->sc, t->sy, t->sx}; }
+
+// Linear index -> (n,c,y,x) in the order that makes the OUTPUT view's fastest axis the
+// fastest thread index (channel-fastest if sc == 1, else x-fastest).
+struct Dims { uint32_t N, C, H, W; int c_fastest; };
+__device__ __forceinline__ void unpack(const Dims& d, size_t i, uint32_t& n, uint32_t& c, uint32_t& y, uint32_t& x) {
+  if (d.c_fastest) {
+    c = (uint32_t)(i % d.C); i /= d.C;
+    x = (uint32_t)(i % d.W); i /= d.W;
+    y = (uint32_t)(i % d.H); n = (uint32_t)(i / d.H);
+  } else {
+    x = (uint32_t)(i % d.W); i /= d.W;
+    y = (uint32_t)(i % d.H); i /= d.H;
+    c = (uint32_t)(i % d.C); n = (uint32_t)(i / d.C);
+  }
+}
+__device__ __forceinline__ long long voff(const View& v, uint32_t n, uint32_t c, uint32_t y, uint32_t x) {
+  return n * v.sn + c * v.sc + y * v.sy + x * v.sx;
+}
+
+enum EwOp { kRelu, kReluBwd, kAdd2, kConvert };
+
+template <int OP, typename TA, typename TB, typename TY>
+__global__ void __launch_bounds__(256) ew_kernel(Dims d, View a, View b, View yv, int accumulate) {
+  const size_t total = (size_t)d.N * d.C * d.H * d.W;
+  const size_t nt = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nt) {
+    uint32_t n, c, y, x;
+    unpack(d, i, n, c, y, x);
+    TY* yp = (TY*)yv.base + voff(yv, n, c, y, x);
+    float av = ld_f((const TA*)a.base + voff(a, n, c, y, x));
+    float r;
+    if (OP == kRelu) r = fmaxf(av, 0.f);
+    else if (OP == kConvert) r = av;
+    else {
+      float bv = ld_f((const TB*)b.base + voff(b, n, c, y, x));
+      r = OP == kAdd2 ? av + bv : (av > 0.f ? bv : 0.f);
+    }
+    if (accumulate) r += ld_f(yp);
+    st_f(yp, r);
+  }
+}
+
+static int same_dims(const ad_tensor4* a, const ad_tensor4* b) {
+  return a->N == b->N && a->C == b->C && a->H == b->H && a->W == b->W;
+}
+
+template <int OP>
+static int ew_launch(const ad_tensor4* a, const ad_tensor4* b, const ad_tensor4* y, int accumulate, void* stream) {
+  if (!a || !y || !a->base || !y->base || (OP != kRelu && OP != kConvert && (!b || !b->base))) return AD_ERR_BAD_ARG;
+  if (!same_dims(a, y) || (b && !same_dims(b, y))) return AD_ERR_BAD_ARG;
+  const size_t total = (size_t)y->N * y->C * y->H * y->W;
+  if (total == 0) return AD_OK;
+  Dims d{y->N, y->C, y->H, y->W, y->sc == 1 && y->C > 1};
+  View va = view_of(a), vb = b ? view_of(b) : View{nullptr, 0, 0, 0, 0}, vy = view_of(y);
+  const unsigned grid = grid_for(total, 256, 16);
+  cudaStream_t s = as_stream(stream);
+  const int da = a->dtype, db = b ? b->dtype : a->dtype, dy = y->dtype;
+#define EW_CASE(TA_, TB_, TY_) ew_kernel<OP, TA_, TB_, TY_><<<grid, 256, 0, s>>>(d, va, vb, vy, accumulate)
+  using bf = __nv_bfloat16;
+  if (da == AD_F32 && db == AD_F32 && dy == AD_F32) EW_CASE(float, float, float);
+  else if (da == AD_BF16 && db == AD_BF16 && dy == AD_BF16) EW_CASE(bf, bf, bf);
+  else if (da == AD_F32 && db == AD_F32 && dy == AD_BF16) EW_CASE(float, float, bf);
+  else if (da == AD_BF16 && db == AD_BF16 && dy == AD_F32) EW_CASE(bf, bf, float);
+  else return AD_ERR_UNSUPPORTED;
+#undef EW_CASE
+  count_launch();
+  return launch_status();
+}
+
+}  // namespace adk
+
+using namespace adk;
+
+extern "C" const char* ad_status_string(int status) {
+  switch (status) {
+    case AD_OK: return "ok";
+    case AD_ERR_BAD_ARG: return "bad argument";
+    case AD_ERR_UNSUPPORTED: return "unsupported dtype/layout/shape";
+    case AD_ERR_CUDA: return "CUDA launch error";
+    case AD_ERR_TIMEOUT: return "bounded device wait timed out";
+    case AD_ERR_ALIGN: return "misaligned pointer or pitch";
+    case AD_ERR_SCRATCH: return "scratch buffer too small";
+    default: return "unknown status";
+  }
+}
+
+extern "C" uint64_t ad_launch_count(void) { return __atomic_load_n(&g_launch_count, __ATOMIC_RELAXED); }
+
+extern "C" int ad_array_set_constant(size_t n, float c, float* x, void* stream) {
+  return arr_launch<kSet>(n, c, 0.f, nullptr, x, stream);
+}
+extern "C" int ad_array_add(size_t n, const float* x, float* y, void* stream) {
+  return arr_launch<kAdd>(n, 0.f, 0.f, x, y, stream);
+}
+extern "C" int ad_array_add_scaled(size_t n, float alpha, float beta, const float* x, float* y, void* stream) {
+  return arr_launch<kAddScaled>(n, alpha, beta, x, y, stream);
+}
+extern "C" int ad_array_add_online(size_t n, float alpha, const float* x, float* y, void* stream) {
+  return arr_launch<kAddOnline>(n, alpha, 0.f, x, y, stream);
+}
+extern "C" int ad_array_scale(size_t n, float scale, const float* x, float* y, void* stream) {
+  return arr_launch<kScale>(n, scale, 0.f, x, y, stream);
+}
+extern "C" int ad_array_scale_add(size_t n, float scale, const float* x, float* y, void* stream) {
+  return arr_launch<kScaleAdd>(n, scale, 0.f, x, y, stream);
+}
+
+extern "C" int ad_fill_zero(void* x, size_t bytes, void* stream) {
+  if (bytes == 0) return AD_OK;
+  if (!x) return AD_ERR_BAD_ARG;
+  // A memset node: runs on the copy/fill path at full HBM write bandwidth, no kernel needed.
+  return cudaMemsetAsync(x, 0, bytes, as_stream(stream)) == cudaSuccess ? AD_OK : AD_ERR_CUDA;
+}
+
+extern "C" int ad_sgd_step(size_t n, float* theta, float* g, float* m, float l2, float mu, float alpha,
+                           float alpha_next, int32_t nesterov, void* bf16_shadow, void* stream) {
+  if (n == 0) return AD_OK;
+  if (!theta || !g || !m) return AD_ERR_BAD_ARG;
+  sgd_kernel<<<grid_for(n, 256), 256, 0, as_stream(stream)>>>(n, theta, g, m, l2, mu, alpha, alpha_next, nesterov,
+                                                               (__nv_bfloat16*)bf16_shadow);
+  count_launch();
+  return launch_status();
+}
+
+extern "C" int ad_relu_fwd(const ad_tensor4* x, const ad_tensor4* y, void* stream) {
+  return ew_launch<kRelu>(x, nullptr, y, 0, stream);
+}
+extern "C" int ad_relu_bwd(const ad_tensor4* x, const ad_tensor4* dy, const ad_tensor4* dx, int32_t accumulate,
+                           void* stream) {
+  return ew_launch<kReluBwd>(x, dy, dx, accumulate, stream);
+}
+extern "C" int ad_add(const ad_tensor4* a, const ad_tensor4* b, const ad_tensor4* y, void* stream) {
+  return ew_launch<kAdd2>(a, b, y, 0, stream);
+}
+extern "C" int ad_convert(const ad_tensor4* src, const ad_tensor4* dst, int32_t accumulate, void* stream) {
+  return ew_launch<kConvert>(src, nullptr, dst, accumulate, stream);
+}

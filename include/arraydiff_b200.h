@@ -1,0 +1,297 @@
+/*
+ * arraydiff_b200 -- C ABI of the B200 (sm_100a) kernels behind arraydiff's spatially
+ * parallel convolution path.
+ *
+ * Every entry point
+ *   - takes plain pointers and sizes (device pointers unless a parameter says "host"),
+ *   - is asynchronous on the CUDA stream passed as `stream` (a cudaStream_t cast to void*),
+ *   - validates its arguments BEFORE launching and returns 0 (AD_OK) or a negative ad_status,
+ *   - never allocates, frees or synchronises; the caller owns all memory, scratch included.
+ * The device that owns the buffers must be current on the calling thread.
+ *
+ * Each declaration cites the reference interface it replaces as
+ * <file in peterhj/arraydiff_cuda>:<lines>.
+ *
+ * Axis and layout conventions follow the reference: NCHW means x (width) fastest,
+ * then y, then channel, then batch.  A "padded strip" holds (h + 2p) x (W + 2p)
+ * positions per plane with the interior at offset (p, p).
+ */
+#ifndef ARRAYDIFF_B200_H
+#define ARRAYDIFF_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AD_MAX_PEERS 8 /* include/arraydiff/spatial.hh:11 (ARRAYDIFF_MAX_PEERS) */
+
+typedef enum {
+  AD_OK = 0,
+  AD_ERR_BAD_ARG = -1,     /* null pointer, zero extent, h < 2p, R out of range ...        */
+  AD_ERR_UNSUPPORTED = -2, /* a dtype / layout / shape combination with no kernel          */
+  AD_ERR_CUDA = -3,        /* the launch itself reported a CUDA error                      */
+  AD_ERR_TIMEOUT = -4,     /* a bounded device-side wait ran out (reported via status word) */
+  AD_ERR_ALIGN = -5,       /* a pointer or pitch violates the alignment the kernel needs   */
+  AD_ERR_SCRATCH = -6      /* caller-provided scratch is too small                         */
+} ad_status;
+
+/* include/arraydiff/spatial.hh:25-29 (Spatial2DDataType) -- bf16 added. */
+typedef enum { AD_F32 = 0, AD_BF16 = 3 } ad_dtype;
+/* include/arraydiff/spatial.hh:20-23 (Spatial2DTensorFormat). */
+typedef enum { AD_NCHW = 0, AD_NHWC = 1 } ad_layout;
+
+const char* ad_status_string(int status);
+/* Number of kernels this library has launched in the calling process (all entry points). */
+uint64_t ad_launch_count(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Halo exchange and halo-gradient accumulate-back over a 1 x R grid of H-strips.
+ * Replaces  Spatial2DComm::halo_exchange / halo_reduce / group_end   src/spatial.cc:58-245
+ * and the kernels behind them                                        src/kernels/spatial.cu:401-652
+ * (launchers spatial2d_1x2_halo_{exch,reduce}_nchw, spatial2d_1x4_..., include/arraydiff/kernels.hh:116-166).
+ *
+ * Field names follow Spatial2DArg (include/arraydiff/spatial.hh:31-43): dims are INTERIOR dims,
+ * buffers are PADDED base pointers.  bufs[r] is rank r's padded strip, addressable from the
+ * launching device (same device, peer-enabled, or an opened IPC mapping).
+ *
+ * One call serves the ranks [rank_first, rank_first + rank_count): one rank per process/GPU, or
+ * all R ranks in one launch when the strips share a device.
+ *
+ * ad_halo_exchange:  rank r WRITES its edge interior rows into its neighbours' halo rows
+ *     P_{r+1}[.., j,       p+x] = P_r[.., h+j, p+x]     j < p   (r < R-1)
+ *     P_{r-1}[.., p+h+j,   p+x] = P_r[.., p+j, p+x]     j < p   (r > 0)
+ *   which is the reference's exchange seen from the sender.  With push = 0 the same rows move
+ *   the reference's way (rank r READS from its neighbours into its own halo rows).
+ * ad_halo_reduce:    rank r adds its neighbours' halo rows into its own edge interior rows
+ *     G_r[.., h+j, p+x] += G_{r+1}[.., j,     p+x]      (r < R-1)
+ *     G_r[.., p+j, p+x] += G_{r-1}[.., p+h+j, p+x]      (r > 0)
+ *   fp32: plain add (one addend per element, so the reference's atomicAdd gives the same bits);
+ *   bf16: add in fp32, round to nearest even.
+ * Requires h >= 2p, R in [1, 8].  Interior columns only: W-pad columns are never touched.
+ *
+ * Signalling (optional).  If signal_flags != NULL, once all rows of this launch are written the
+ * kernel stores `epoch` with system-scope release semantics to signal_flags[q] for each peer
+ * rank q it wrote to (exchange) -- q's consumer then waits on it with ad_flag_wait.
+ */
+typedef struct {
+  int32_t dtype;          /* ad_dtype   */
+  int32_t layout;         /* ad_layout  */
+  uint32_t halo_pad;      /* p          */
+  uint32_t base_width;    /* W          */
+  uint32_t base_height;   /* h = H / R  */
+  uint32_t num_channels;  /* C          */
+  uint32_t batch_size;    /* N          */
+  uint32_t num_ranks;     /* R          */
+  uint32_t rank_first;
+  uint32_t rank_count;
+  int32_t push;           /* exchange only: 1 = write into neighbours, 0 = read from neighbours */
+  uint32_t reserved;
+  void* bufs[AD_MAX_PEERS];
+  uint64_t* signal_flags[AD_MAX_PEERS]; /* may be all NULL */
+  uint64_t epoch;
+  uint32_t* block_counter;  /* one zero-initialised uint32 in local memory; needed iff signalling */
+} ad_halo_args;
+
+int ad_halo_exchange(const ad_halo_args* args, void* stream);
+int ad_halo_reduce(const ad_halo_args* args, void* stream);
+
+/*
+ * Bounded wait for *flag >= epoch (system-scope acquire).  Gives up after timeout_ns nanoseconds
+ * of device time and then stores AD_ERR_TIMEOUT to *status_word (device memory, caller zeroes it)
+ * instead of spinning on; the host reads the status word at its next synchronisation point.
+ * Replaces the unbounded host spin of Spatial2DComm::group_end, src/spatial.cc:59-70.
+ */
+int ad_flag_wait(const uint64_t* flag, uint64_t epoch, uint64_t timeout_ns, int32_t* status_word, void* stream);
+/* Stores `epoch` to *flag with system-scope release semantics after all prior work on `stream`. */
+int ad_flag_signal(uint64_t* flag, uint64_t epoch, void* stream);
+
+/* CUDA IPC plumbing for one-process-per-GPU launches: the reference is single-process and gets
+ * peer pointers for free (src/spatial.cc:13-50); separate processes exchange these handles. */
+int ad_ipc_get_handle(void* dev_ptr, uint8_t handle_out[64]);   /* host out */
+int ad_ipc_open_handle(const uint8_t handle[64], void** dev_ptr_out);
+int ad_ipc_close_handle(void* dev_ptr);
+int ad_enable_peer_access(int device, int peer_device); /* src/spatial.cc:13-29 */
+
+/* ------------------------------------------------------------------------------------------
+ * 2-D window copy / add between packed NCHW tensors.
+ * Replaces slice2d_copy_hw_nchw_packed / slice2d_add_hw_nchw_packed,
+ * include/arraydiff/kernels.hh:222-256, src/kernels/slice.cu:12-105; same argument order.
+ *   dst[n,c,dst_h_off+y,dst_w_off+x] (=|+=) src[n,c,src_h_off+y,src_w_off+x],  y<count_h, x<count_w
+ * dtype AD_F32 or AD_BF16 (bf16 add: fp32 add, round to nearest even).
+ * Halo pad / unpad (HaloPad2DOp, HaloUnpad2DOp: src/op.cc:2634-2639, :2705-2710, :2788-2793,
+ * :2863-2868) are this call with the padded geometry as src or dst.
+ */
+int ad_slice2d_copy_hw_nchw_packed(int32_t dtype, uint32_t count_w, uint32_t count_h,
+                                   uint32_t src_width, uint32_t src_height,
+                                   uint32_t dst_width, uint32_t dst_height,
+                                   uint32_t channels, uint32_t batch_size,
+                                   const void* src, uint32_t src_w_off, uint32_t src_h_off,
+                                   void* dst, uint32_t dst_w_off, uint32_t dst_h_off, void* stream);
+int ad_slice2d_add_hw_nchw_packed(int32_t dtype, uint32_t count_w, uint32_t count_h,
+                                  uint32_t src_width, uint32_t src_height,
+                                  uint32_t dst_width, uint32_t dst_height,
+                                  uint32_t channels, uint32_t batch_size,
+                                  const void* src, uint32_t src_w_off, uint32_t src_h_off,
+                                  void* dst, uint32_t dst_w_off, uint32_t dst_h_off, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Packed array arithmetic on fp32, rounding exactly as the reference kernels do.
+ * Replaces include/arraydiff/kernels.hh:72-93, src/kernels/array.cu:58-257.
+ */
+int ad_array_set_constant(size_t n, float c, float* x, void* stream);                          /* x = c            */
+int ad_array_add(size_t n, const float* x, float* y, void* stream);                            /* y = x + y        */
+int ad_array_add_scaled(size_t n, float alpha, float beta, const float* x, float* y, void* stream); /* y = a*x + b*y */
+int ad_array_add_online(size_t n, float alpha, const float* x, float* y, void* stream);        /* y += a*(x-y)     */
+int ad_array_scale(size_t n, float scale, const float* x, float* y, void* stream);             /* y = s*x          */
+int ad_array_scale_add(size_t n, float scale, const float* x, float* y, void* stream);         /* y = s*x + y      */
+int ad_fill_zero(void* x, size_t bytes, void* stream);
+
+/*
+ * One fused pass of the reference's SGD update on a flat fp32 parameter buffer, the same
+ * add_scaled sequence as ParallelSGDOptimizer::step, include/arraydiff/optimize.hh:479-499:
+ *   g = l2*theta + g (if l2 != 0);  m = g + mu*m;
+ *   nesterov: theta -= alpha*g; theta -= alpha_next*mu*m      else: theta -= alpha*m
+ * bf16_shadow (optional) receives round-to-nearest-even(theta) for the tensor-core kernels.
+ */
+int ad_sgd_step(size_t n, float* theta, float* g, float* m, float l2, float mu, float alpha,
+                float alpha_next, int32_t nesterov, void* bf16_shadow, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Softmax / loss.
+ * ad_softmax_nll_loss_{fwd,bwd} replace include/arraydiff/kernels.hh:98-102,
+ * src/kernels/softmax.cu:36-96  ([batch][channels] probabilities, uint32 labels):
+ *   loss[b] = -logf(y[label[b] + C*b]);   dx[b,c] += dloss[b] * (y[b,c] - [c == label[b]])
+ */
+int ad_softmax_nll_loss_fwd(uint32_t num_channels, uint32_t batch_size, const float* y,
+                            const uint32_t* label, float* loss, void* stream);
+int ad_softmax_nll_loss_bwd(uint32_t num_channels, uint32_t batch_size, const float* y,
+                            const uint32_t* label, const float* dloss, float* dx, void* stream);
+/*
+ * Fused per-pixel softmax + cross-entropy over the channel axis (the 3-D case the reference leaves
+ * unimplemented, CudnnSoftmaxNLLLossOp src/op.cc:4190-4236; softmax mode CHANNEL :4216-4223).
+ * logits [N][C][HW] (NCHW) or [N][HW][C] (NHWC), fp32 or bf16; labels uint32 [N][HW].
+ *   fwd: loss[n,t] = logsumexp_c(logits) - logits[label]   (fp32 [N][HW]); picked (optional) gets
+ *        the flat element index of the selected logit, for exact label-index checks.
+ *   bwd: dlogits[n,c,t] (+)= dloss[n,t] * (softmax_c - [c == label]);  accumulate != 0 adds.
+ * C <= 1024.
+ */
+int ad_softmax_ce_pixel_fwd(int32_t dtype, int32_t layout, uint32_t N, uint32_t C, uint32_t HW,
+                            const void* logits, const uint32_t* label, float* loss, uint64_t* picked,
+                            void* stream);
+int ad_softmax_ce_pixel_bwd(int32_t dtype, int32_t layout, uint32_t N, uint32_t C, uint32_t HW,
+                            const void* logits, const uint32_t* label, const float* dloss, void* dlogits,
+                            int32_t accumulate, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Strided 4-D tensor view used by the normalisation / pooling / conversion kernels.
+ * Element (n, c, y, x) lives at base + n*sn + c*sc + y*sy + x*sx (strides in ELEMENTS), so one
+ * descriptor covers packed NCHW, packed NHWC and the interior of a halo-padded strip alike.
+ */
+typedef struct {
+  void* base;
+  int32_t dtype; /* ad_dtype */
+  uint32_t N, C, H, W;
+  int64_t sn, sc, sy, sx;
+} ad_tensor4;
+
+/*
+ * Spatial batch normalisation with batch statistics, optional fused ReLU.
+ * Replaces CudnnBatchNorm2DOp (cudnnBatchNormalizationForwardTraining / Backward,
+ * src/op.cc:3969-4003, :4083-4097; eps 1e-5) and the CudnnActivationOp that follows it in every
+ * zoo block (src/op.cc:3104-3110, :3177-3185; src/zoo.cc:596-637).
+ *   fwd: stats over (N,H,W) of x -> save_mean[C], save_invstd[C], batch_var[C] (biased);
+ *        y = relu?(gamma*(x-mean)*invstd + beta).
+ *   bwd: dy masked by (y > 0) if relu; dgamma += , dbeta += ; dx (+)= ...
+ * part_sums: caller scratch of at least ad_bn_scratch_bytes(C) bytes.
+ * Statistics are this call's tensor only (the reference's per-strip behaviour); for statistics
+ * across ranks use the two-phase calls: ad_bn_partial_stats -> (allreduce of 2*C floats) ->
+ * ad_bn_finalize_apply.
+ */
+size_t ad_bn_scratch_bytes(uint32_t C);
+int ad_bn_fwd_train(const ad_tensor4* x, const ad_tensor4* y, const float* gamma, const float* beta,
+                    float* save_mean, float* save_invstd, float* batch_var, float eps, int32_t relu,
+                    void* scratch, size_t scratch_bytes, void* stream);
+int ad_bn_bwd(const ad_tensor4* x, const ad_tensor4* dy, const ad_tensor4* dx, const float* gamma,
+              const float* beta, const float* save_mean, const float* save_invstd, float* dgamma,
+              float* dbeta, int32_t relu, int32_t accumulate_dx, void* scratch, size_t scratch_bytes,
+              void* stream);
+/* sums[0..C) = sum x, sums[C..2C) = sum x^2 over this tensor (fp32, overwritten). */
+int ad_bn_partial_stats(const ad_tensor4* x, float* sums, void* scratch, size_t scratch_bytes, void* stream);
+/* count = total elements per channel behind `sums` (all ranks). */
+int ad_bn_finalize_apply(const ad_tensor4* x, const ad_tensor4* y, const float* sums, double count,
+                         const float* gamma, const float* beta, float* save_mean, float* save_invstd,
+                         float* batch_var, float eps, int32_t relu, void* stream);
+
+/*
+ * Max pooling over an explicitly padded input (window kh x kw, stride sh x sw, no implicit pad):
+ * the pad cells take part in the max with the value the buffer holds, which is how the reference
+ * drives cuDNN for halo-padded inputs (CudnnPool2DOp, src/op.cc:3440-3446, :3496-3513, :3610-3631).
+ * y dims must be ((H-kh)/sh+1, (W-kw)/sw+1).  bwd recomputes each window's argmax (first maximum
+ * in row-major window order) and gathers dx[i] (+)= sum of dy over the windows whose argmax is i
+ * -- no atomics, so the result is reproducible.
+ */
+int ad_maxpool2d_fwd(const ad_tensor4* x, const ad_tensor4* y, uint32_t kh, uint32_t kw, uint32_t sh,
+                     uint32_t sw, void* stream);
+int ad_maxpool2d_bwd(const ad_tensor4* x, const ad_tensor4* dy, const ad_tensor4* dx, uint32_t kh,
+                     uint32_t kw, uint32_t sh, uint32_t sw, int32_t accumulate, void* stream);
+
+/* ReLU and residual sum on strided views (CudnnActivationOp src/op.cc:3054-3344,
+ * JoinOp<SumJoin> src/op.cc:745-802, :859-864).  Any of the views may alias.
+ *   ad_relu_fwd: y = max(x,0);  ad_relu_bwd: dx (+)= dy*[x>0];  ad_add: y = a + b. */
+int ad_relu_fwd(const ad_tensor4* x, const ad_tensor4* y, void* stream);
+int ad_relu_bwd(const ad_tensor4* x, const ad_tensor4* dy, const ad_tensor4* dx, int32_t accumulate, void* stream);
+int ad_add(const ad_tensor4* a, const ad_tensor4* b, const ad_tensor4* y, void* stream);
+/* Copy with dtype/layout conversion between two views of equal dims (fp32 <-> bf16 RNE);
+ * accumulate != 0 gives dst += src (in fp32).  Covers TransposeNHWCToNCHWOp / CastOp at the
+ * graph edges (src/op.cc:428-628) and pad/unpad copies between layouts. */
+int ad_convert(const ad_tensor4* src, const ad_tensor4* dst, int32_t accumulate, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Convolution (cross-correlation), forward / data gradient / filter+bias gradient.
+ * Replaces CudnnConv2DOp: cudnnConvolutionForward src/op.cc:1577-1610, BackwardBias :1642-1647,
+ * BackwardFilter :1661-1683, BackwardData :1702-1724; geometry Conv2DShape
+ * include/arraydiff/op.hh:1799-1810 and CudnnConv2DSize src/op.cc:1343-1422.
+ *
+ * x is the tensor the kernel actually reads: for halo_padded_input pass the padded strip dims
+ * (H = h+2p, W = W+2p) and pad_h = pad_w = 0, as the reference does.  Output dims
+ *   P = (H + 2*pad_h - dil_h*(kh-1) - 1)/stride_h + 1, Q likewise.
+ *
+ * Two arithmetic paths:
+ *   AD_F32 / AD_NCHW : fp32 operands, fp32 accumulate (SIMT FMA).  Filter KCRS fp32.
+ *   AD_BF16 / AD_NHWC: bf16 operands, fp32 accumulate in tensor memory (tcgen05.mma), operands
+ *                      staged by TMA.  Filter KRSC bf16 (K, kh, kw, C), C and K multiples of 8 ...
+ * y / dy / dx may be views into larger (e.g. halo-padded) buffers: *_pitch give the row pitch
+ * (elements between consecutive y) and *_plane the pitch between images (NHWC) or planes (NCHW);
+ * 0 means packed.
+ */
+typedef struct {
+  int32_t dtype, layout;
+  uint32_t N, C, H, W;     /* input as read (padded dims if halo-padded) */
+  uint32_t K, kh, kw;
+  uint32_t stride_h, stride_w, dil_h, dil_w, pad_h, pad_w;
+  int32_t relu;            /* fprop epilogue: y = max(y, 0) */
+  int32_t accumulate;      /* dgrad: dx += ; wgrad: dw += , db +=   (else overwrite) */
+  const void* x;           /* [N][C][H][W] or [N][H][W][C]; dense */
+  const void* w;           /* KCRS fp32  |  KRSC bf16 */
+  const float* bias;       /* [K] fp32 or NULL */
+  void* y;                 /* fprop out / dgrad+wgrad in (dy) */
+  int64_t y_pitch, y_plane;
+  void* dx;                /* dgrad out, same geometry as x */
+  void* dw;                /* wgrad out: KCRS fp32 | KRSC fp32 */
+  float* db;               /* [K] or NULL */
+  void* scratch;           /* see ad_conv2d_scratch_bytes */
+  size_t scratch_bytes;
+} ad_conv2d_args;
+
+size_t ad_conv2d_scratch_bytes(const ad_conv2d_args* a, int32_t pass /* 0 fprop, 1 dgrad, 2 wgrad */);
+int ad_conv2d_fprop(const ad_conv2d_args* a, void* stream);
+int ad_conv2d_dgrad(const ad_conv2d_args* a, void* stream);
+int ad_conv2d_wgrad(const ad_conv2d_args* a, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ARRAYDIFF_B200_H */

@@ -1,0 +1,191 @@
+"""Convolution forward / data gradient / filter gradient against the oracle.
+fp32 NCHW path: max-relative 1e-5.  bf16 NHWC tensor-core path: max-relative 2e-2 against the
+oracle evaluated on the bf16-rounded operands (fp32 accumulate on both sides)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from arraydiff_cuda_b200 import abi
+from oracle import orc
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+TOL_F32 = 1e-5
+TOL_BF16 = 2e-2
+
+
+def conv_args(dtype, layout, x_shape_nchw, K, k, stride, dil, pad):
+    N, Cc, Hh, W = x_shape_nchw
+    a = abi.Conv2dArgs()
+    a.dtype, a.layout = dtype, layout
+    a.N, a.C, a.H, a.W, a.K, a.kh, a.kw = N, Cc, Hh, W, K, k, k
+    a.stride_h = a.stride_w = stride
+    a.dil_h = a.dil_w = dil
+    a.pad_h = a.pad_w = pad
+    return a
+
+
+F32_CASES = [
+    # N, C, H, W, K, k, stride, dil, pad
+    (1, 3, 9, 10, 4, 3, 1, 1, 1),
+    (2, 4, 11, 9, 5, 3, 2, 1, 1),
+    (1, 2, 12, 12, 3, 3, 1, 2, 2),
+    (1, 3, 37, 41, 8, 7, 2, 1, 3),
+    (2, 5, 6, 7, 6, 1, 1, 1, 0),
+    (1, 64, 34, 66, 64, 3, 1, 1, 0),   # one halo-padded strip of BASELINE config 1 (h=32, p=1)
+]
+
+
+@pytest.mark.parametrize("case", F32_CASES)
+def test_conv_fp32_direct(case):
+    import torch
+    N, Cc, Hh, W, K, k, s, d, pd = case
+    x, w, b = H.uniform(1, (N, Cc, Hh, W)), H.normal(2, (K, Cc, k, k), float(np.sqrt(2.0 / (k * k * Cc)))), H.normal(3, (K,))
+    y_w = orc.conv2d_fprop(x, w, b, (s, s), (d, d), (pd, pd), omp=True)
+    dy = H.uniform(4, y_w.shape)
+    dx_w = orc.conv2d_dgrad(dy, w, x.shape, (s, s), (d, d), (pd, pd), omp=True)
+    db_w = np.zeros(K, np.float32)
+    dw_w = orc.conv2d_wgrad(x, dy, w.shape, (s, s), (d, d), (pd, pd), db=db_w, omp=True)
+    L = abi.lib()
+    a = conv_args(abi.AD_F32, abi.AD_NCHW, x.shape, K, k, s, d, pd)
+    dx_, dw_, db_ = H.dev(x), H.dev(w), H.dev(b)
+    y = torch.empty(y_w.shape, device="cuda")
+    a.x, a.w, a.bias, a.y = dx_.data_ptr(), dw_.data_ptr(), db_.data_ptr(), y.data_ptr()
+    abi.check(L.ad_conv2d_fprop(C.byref(a), H.stream()))
+    H.sync()
+    assert H.max_rel(H.host(y), y_w) < TOL_F32
+    ddy = H.dev(dy)
+    gdx, gdw, gdb = torch.ones(x.shape, device="cuda"), torch.ones(w.shape, device="cuda"), torch.ones(K, device="cuda")
+    a.y, a.dx, a.dw, a.db, a.accumulate = ddy.data_ptr(), gdx.data_ptr(), gdw.data_ptr(), gdb.data_ptr(), 1
+    abi.check(L.ad_conv2d_dgrad(C.byref(a), H.stream()))
+    abi.check(L.ad_conv2d_wgrad(C.byref(a), H.stream()))
+    H.sync()
+    assert H.max_rel(H.host(gdx) - 1, dx_w) < TOL_F32      # accumulate: += on top of the ones
+    assert H.max_rel(H.host(gdw) - 1, dw_w) < 2 * TOL_F32
+    assert H.max_rel(H.host(gdb) - 1, db_w) < 2 * TOL_F32
+
+
+TC_CASES = [
+    # N, C, H, W, K, k, stride, dil, pad           (H, W are the dims the kernel reads)
+    (1, 64, 16, 16, 64, 1, 1, 1, 0),     # 1x1, single tile row block
+    (2, 64, 13, 21, 256, 1, 1, 1, 0),    # 1x1 64->256, ragged tiles
+    (1, 256, 9, 40, 64, 1, 1, 1, 0),     # 1x1 256->64, 4 channel slabs
+    (1, 64, 18, 34, 64, 3, 1, 1, 0),     # 3x3 on a halo-padded strip (h=16, W=32, p=1)
+    (2, 64, 20, 20, 128, 3, 1, 2, 0),    # dilated 3x3 (d=2) on a halo-2 strip
+    (1, 128, 24, 24, 64, 3, 1, 4, 0),    # dilated 3x3 (d=4)
+    (1, 64, 17, 19, 64, 3, 1, 1, 1),     # implicit zero padding through out-of-bounds fill
+    (1, 64, 34, 34, 128, 3, 2, 1, 0),    # 3x3 stride 2 on a padded strip
+    (1, 64, 32, 32, 256, 1, 2, 1, 0),    # 1x1 stride 2 projection
+    (1, 192, 12, 140, 64, 1, 1, 1, 0),   # the 7x7 stem after im2col: K = 147 padded to 192
+    (1, 64, 8, 8, 19, 1, 1, 1, 0),       # 19-class head (ragged output channels)
+]
+
+
+def _tc_setup(case, seed=10):
+    N, Cc, Hh, W, K, k, s, d, pd = case
+    x = orc.round_bf16(H.uniform(seed, (N, Cc, Hh, W)))
+    w = orc.round_bf16(H.normal(seed + 1, (K, Cc, k, k), float(np.sqrt(2.0 / (k * k * Cc)))))
+    return x, w
+
+
+@pytest.mark.parametrize("case", TC_CASES)
+def test_conv_tc_fprop(case):
+    import torch
+    N, Cc, Hh, W, K, k, s, d, pd = case
+    x, w = _tc_setup(case)
+    b = H.normal(12, (K,))
+    y_w = orc.conv2d_fprop(x, w, b, (s, s), (d, d), (pd, pd), omp=True)
+    L = abi.lib()
+    a = conv_args(abi.AD_BF16, abi.AD_NHWC, x.shape, K, k, s, d, pd)
+    dx_ = H.dev_bf16(orc.nchw_to_nhwc(x))
+    dw_ = H.dev_bf16(np.ascontiguousarray(np.transpose(w, (0, 2, 3, 1))))  # KRSC
+    db_ = H.dev(b)
+    P, Q = y_w.shape[2:]
+    y = torch.full((N, P, Q, K), 7.0, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    a.x, a.w, a.bias, a.y = dx_.data_ptr(), dw_.data_ptr(), db_.data_ptr(), y.data_ptr()
+    a.scratch, a.scratch_bytes = status.data_ptr(), 16
+    abi.check(L.ad_conv2d_fprop(C.byref(a), H.stream()))
+    H.sync()
+    assert status[0].item() == 0
+    got = orc.nhwc_to_nchw(H.host(y))
+    err = H.max_rel(got, y_w)
+    assert err < TOL_BF16, err
+    a.relu = 1
+    abi.check(L.ad_conv2d_fprop(C.byref(a), H.stream()))
+    H.sync()
+    assert H.max_rel(orc.nhwc_to_nchw(H.host(y)), np.maximum(y_w, 0)) < TOL_BF16
+
+
+@pytest.mark.parametrize("case", [c for c in TC_CASES if c[6] == 1 and c[4] % 64 == 0])
+def test_conv_tc_dgrad(case):
+    import torch
+    N, Cc, Hh, W, K, k, s, d, pd = case
+    x, w = _tc_setup(case)
+    P = (Hh + 2 * pd - d * (k - 1) - 1) // s + 1
+    Q = (W + 2 * pd - d * (k - 1) - 1) // s + 1
+    dy = orc.round_bf16(H.uniform(13, (N, K, P, Q)))
+    dx_w = orc.conv2d_dgrad(dy, w, x.shape, (s, s), (d, d), (pd, pd), omp=True)
+    L = abi.lib()
+    a = conv_args(abi.AD_BF16, abi.AD_NHWC, x.shape, K, k, s, d, pd)
+    dw_ = H.dev_bf16(np.ascontiguousarray(np.transpose(w, (0, 2, 3, 1))))
+    ddy = H.dev_bf16(orc.nchw_to_nhwc(dy))
+    dx = torch.full((N, Hh, W, Cc), 3.0, dtype=torch.bfloat16, device="cuda")
+    nscr = L.ad_conv2d_scratch_bytes(C.byref(a), 1)
+    scratch = torch.zeros(nscr, dtype=torch.uint8, device="cuda")
+    a.w, a.y, a.dx, a.scratch, a.scratch_bytes = dw_.data_ptr(), ddy.data_ptr(), dx.data_ptr(), scratch.data_ptr(), nscr
+    abi.check(L.ad_conv2d_dgrad(C.byref(a), H.stream()))
+    H.sync()
+    assert scratch[:4].view(torch.int32).item() == 0
+    err = H.max_rel(orc.nhwc_to_nchw(H.host(dx)), dx_w)
+    assert err < TOL_BF16, err
+    a.accumulate = 1
+    abi.check(L.ad_conv2d_dgrad(C.byref(a), H.stream()))
+    H.sync()
+    assert H.max_rel(orc.nhwc_to_nchw(H.host(dx)), 2 * dx_w) < 2 * TOL_BF16
+
+
+@pytest.mark.parametrize("case", [c for c in TC_CASES if c[4] % 8 == 0])
+def test_conv_tc_wgrad(case):
+    import torch
+    N, Cc, Hh, W, K, k, s, d, pd = case
+    x, w = _tc_setup(case)
+    P = (Hh + 2 * pd - d * (k - 1) - 1) // s + 1
+    Q = (W + 2 * pd - d * (k - 1) - 1) // s + 1
+    dy = orc.round_bf16(H.uniform(14, (N, K, P, Q)))
+    db_w = np.zeros(K, np.float32)
+    dw_w = orc.conv2d_wgrad(x, dy, w.shape, (s, s), (d, d), (pd, pd), db=db_w, omp=True)
+    L = abi.lib()
+    a = conv_args(abi.AD_BF16, abi.AD_NHWC, x.shape, K, k, s, d, pd)
+    dx_ = H.dev_bf16(orc.nchw_to_nhwc(x))
+    ddy = H.dev_bf16(orc.nchw_to_nhwc(dy))
+    dw = torch.full((K, k, k, Cc), 5.0, device="cuda")
+    db = torch.full((K,), 5.0, device="cuda")
+    nscr = L.ad_conv2d_scratch_bytes(C.byref(a), 2)
+    scratch = torch.zeros(nscr, dtype=torch.uint8, device="cuda")
+    a.x, a.y, a.dw, a.db, a.scratch, a.scratch_bytes = dx_.data_ptr(), ddy.data_ptr(), dw.data_ptr(), db.data_ptr(), scratch.data_ptr(), nscr
+    abi.check(L.ad_conv2d_wgrad(C.byref(a), H.stream()))
+    H.sync()
+    assert scratch[:4].view(torch.int32).item() == 0
+    got = np.transpose(H.host(dw), (0, 3, 1, 2))  # KRSC -> KCRS
+    err = H.max_rel(got, dw_w)
+    assert err < 1e-3, err       # operands are exact in bf16 and the sum is fp32: far inside 2e-2
+    assert H.max_rel(H.host(db), db_w) < 1e-4
+    first = H.host(dw).copy()
+    abi.check(L.ad_conv2d_wgrad(C.byref(a), H.stream()))
+    H.sync()
+    assert np.array_equal(H.host(dw), first)  # fixed-order split reduction: bit-reproducible
+
+
+def test_conv_rejects_bad_arguments():
+    L = abi.lib()
+    a = conv_args(abi.AD_BF16, abi.AD_NCHW, (1, 64, 8, 8), 64, 3, 1, 1, 0)
+    assert L.ad_conv2d_fprop(C.byref(a), H.stream()) == abi.AD_ERR_UNSUPPORTED   # no bf16 NCHW kernel
+    a = conv_args(abi.AD_BF16, abi.AD_NHWC, (1, 48, 8, 8), 64, 3, 1, 1, 0)
+    x = H.dev_bf16(np.zeros((1, 8, 8, 48), np.float32))
+    a.x = a.w = a.y = x.data_ptr()
+    assert L.ad_conv2d_fprop(C.byref(a), H.stream()) == abi.AD_ERR_UNSUPPORTED   # C not a multiple of 64
+    a = conv_args(abi.AD_F32, abi.AD_NCHW, (1, 4, 2, 2), 4, 3, 1, 1, 0)
+    assert L.ad_conv2d_fprop(C.byref(a), H.stream()) == abi.AD_ERR_BAD_ARG       # kernel larger than input
+    assert L.ad_conv2d_fprop(None, H.stream()) == abi.AD_ERR_BAD_ARG

@@ -1,0 +1,270 @@
+"""Packed array arithmetic, SGD, softmax / NLL, batch norm, pooling, ReLU / add / convert
+kernels against the oracle."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from arraydiff_cuda_b200 import abi
+from oracle import orc
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+f32 = C.c_float
+
+
+@pytest.mark.parametrize("n", [1, 5, 1031, 1 << 20])
+@pytest.mark.parametrize("misalign", [0, 1])
+def test_array_ops_bit_exact(n, misalign):
+    L = abi.lib()
+    x, y = H.normal(1, (n + 1,), 3.0), H.normal(2, (n + 1,), 3.0)
+    a, b = 0.37, -1.21
+    calls = {
+        "add": lambda dx, dy: L.ad_array_add(n, dx, dy, H.stream()),
+        "add_scaled": lambda dx, dy: L.ad_array_add_scaled(n, f32(a), f32(b), dx, dy, H.stream()),
+        "add_online": lambda dx, dy: L.ad_array_add_online(n, f32(a), dx, dy, H.stream()),
+        "scale": lambda dx, dy: L.ad_array_scale(n, f32(a), dx, dy, H.stream()),
+        "scale_add": lambda dx, dy: L.ad_array_scale_add(n, f32(a), dx, dy, H.stream()),
+    }
+    for name, call in calls.items():
+        dx, dy = H.dev(x), H.dev(y)
+        off = 4 * misalign
+        abi.check(call(C.c_void_p(dx.data_ptr() + off), C.c_void_p(dy.data_ptr() + off)))
+        H.sync()
+        want = y[misalign:misalign + n].copy()
+        orc.array_op(name, np.ascontiguousarray(x[misalign:misalign + n]), want, a, b)
+        got = H.host(dy)
+        assert np.array_equal(got[misalign:misalign + n], want), name
+        assert got[misalign + n:].tolist() == y[misalign + n:].tolist()
+    d = H.dev(y)
+    abi.check(L.ad_array_set_constant(n, f32(2.5), H.ptr(d), H.stream()))
+    H.sync()
+    assert np.all(H.host(d)[:n] == 2.5)
+
+
+@pytest.mark.parametrize("nesterov", [0, 1])
+@pytest.mark.parametrize("l2", [0.0, 1e-4])
+def test_sgd_step_bit_exact_with_bf16_shadow(nesterov, l2):
+    import torch
+    n = 100003
+    th, g, m = H.normal(3, (n,)), H.normal(4, (n,)), H.normal(5, (n,))
+    dth, dg, dm = H.dev(th), H.dev(g), H.dev(m)
+    shadow = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+    abi.check(abi.lib().ad_sgd_step(n, H.ptr(dth), H.ptr(dg), H.ptr(dm), f32(l2), f32(0.9), f32(0.1), f32(0.05), nesterov,
+                                    H.ptr(shadow), H.stream()))
+    H.sync()
+    orc.sgd_step(th, g, m, l2, 0.9, 0.1, 0.05, nesterov)
+    assert np.array_equal(H.host(dth), th) and np.array_equal(H.host(dg), g) and np.array_equal(H.host(dm), m)
+    assert np.array_equal(H.bits_bf16(shadow), orc.f32_to_bf16(th))
+
+
+def test_nll_loss_kernels():
+    import torch
+    B, Cc = 1000, 1000
+    y = H.uniform(6, (B, Cc), 1e-3, 1.0)
+    label = H.rng(7).integers(0, Cc, (B,)).astype(np.uint32)
+    label[:2] = [0, Cc - 1]
+    dloss, dx0 = H.uniform(8, (B,)), H.uniform(9, (B, Cc))
+    dy_, dl, ddl, ddx = H.dev(y), torch.from_numpy(label.view(np.int32)).cuda(), H.dev(dloss), H.dev(dx0)
+    loss = torch.empty(B, device="cuda")
+    L = abi.lib()
+    abi.check(L.ad_softmax_nll_loss_fwd(Cc, B, H.ptr(dy_), H.ptr(dl), H.ptr(loss), H.stream()))
+    abi.check(L.ad_softmax_nll_loss_bwd(Cc, B, H.ptr(dy_), H.ptr(dl), H.ptr(ddl), H.ptr(ddx), H.stream()))
+    H.sync()
+    np.testing.assert_allclose(H.host(loss), orc.softmax_nll_loss_fwd(y, label), rtol=1e-6)
+    want = dx0.copy()
+    orc.softmax_nll_loss_bwd(y, label, dloss, want)
+    assert np.array_equal(H.host(ddx), want)  # label indexing and rounding both exact
+
+
+@pytest.mark.parametrize("Cc", [2, 19, 1000])
+@pytest.mark.parametrize("layout", [abi.AD_NCHW, abi.AD_NHWC])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_softmax_ce_pixel(Cc, layout, dtype):
+    import torch
+    N, HW = 2, 77
+    logits = H.normal(10, (N, Cc, HW), 2.0)
+    if dtype == "bf16":
+        logits = orc.round_bf16(logits)
+    label = H.rng(11).integers(0, Cc, (N, HW)).astype(np.uint32)
+    label[0, :2] = [0, Cc - 1]
+    dloss = H.uniform(12, (N, HW))
+    loss_w, _, picked_w = orc.softmax_ce_pixel_fwd(logits, label)
+    dlog_w = orc.softmax_ce_pixel_bwd(logits, label, dloss)
+    arr = logits if layout == abi.AD_NCHW else np.ascontiguousarray(np.transpose(logits, (0, 2, 1)))
+    d = H.dev(arr) if dtype == "f32" else H.dev_bf16(arr)
+    dl = torch.from_numpy(label.view(np.int32)).cuda()
+    loss = torch.empty((N, HW), device="cuda")
+    picked = torch.empty((N, HW), dtype=torch.int64, device="cuda")
+    dlog = torch.zeros_like(d)
+    L = abi.lib()
+    dt = abi.AD_F32 if dtype == "f32" else abi.AD_BF16
+    abi.check(L.ad_softmax_ce_pixel_fwd(dt, layout, N, Cc, HW, H.ptr(d), H.ptr(dl), H.ptr(loss), H.ptr(picked), H.stream()))
+    abi.check(L.ad_softmax_ce_pixel_bwd(dt, layout, N, Cc, HW, H.ptr(d), H.ptr(dl), H.ptr(H.dev(dloss)), H.ptr(dlog), 0, H.stream()))
+    H.sync()
+    # label index: bit-exact
+    pk = picked.cpu().numpy().astype(np.uint64)
+    if layout == abi.AD_NCHW:
+        assert np.array_equal(pk, picked_w)
+    else:
+        n_idx, t_idx = np.meshgrid(np.arange(N), np.arange(HW), indexing="ij")
+        assert np.array_equal(pk, ((n_idx * HW + t_idx) * Cc + label).astype(np.uint64))
+    assert H.max_rel(H.host(loss), loss_w) < 1e-5
+    got = H.host(dlog)
+    if layout == abi.AD_NHWC:
+        got = np.transpose(got, (0, 2, 1))
+    assert H.max_rel(got, dlog_w) < (1e-5 if dtype == "f32" else 2e-2)
+
+
+def _views(arr_nchw, layout, dtype, pad=0):
+    """Device tensor (optionally inside a zero halo-padded buffer) + Tensor4 view of the interior."""
+    import torch
+    N, Cc, Hh, W = arr_nchw.shape
+    buf = np.zeros((N, Cc, Hh + 2 * pad, W + 2 * pad), np.float32)
+    buf[:, :, pad:pad + Hh, pad:pad + W] = arr_nchw
+    if layout == abi.AD_NHWC:
+        buf = orc.nchw_to_nhwc(buf)
+    t = H.dev(buf) if dtype == "f32" else H.dev_bf16(buf)
+    mk = H.view_nchw if layout == abi.AD_NCHW else H.view_nhwc
+    return t, mk(t, (pad, Hh, W) if pad else None)
+
+
+def _back(t, layout, pad, Hh, W):
+    a = H.host(t)
+    if layout == abi.AD_NHWC:
+        a = orc.nhwc_to_nchw(a)
+    return a[:, :, pad:pad + Hh, pad:pad + W]
+
+
+@pytest.mark.parametrize("layout", [abi.AD_NCHW, abi.AD_NHWC])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("relu", [0, 1])
+def test_batch_norm_fwd_bwd(layout, dtype, relu):
+    import torch
+    N, Cc, Hh, W = 2, 37, 19, 23
+    x = H.normal(20, (N, Cc, Hh, W)) * H.uniform(21, (1, Cc, 1, 1), 0.5, 2.0) + H.uniform(22, (1, Cc, 1, 1))
+    dy = H.uniform(23, (N, Cc, Hh, W))
+    if dtype == "bf16":
+        x, dy = orc.round_bf16(x), orc.round_bf16(dy)
+    gamma, beta = H.uniform(24, (Cc,), 0.5, 1.5), H.uniform(25, (Cc,), -0.5, 0.5)
+    y_w, mean_w, invstd_w, var_w = orc.bn_fwd_train(x, gamma, beta, relu=relu)
+    dx_w, dg_w, db_w = orc.bn_bwd(x, dy, gamma, beta, mean_w, invstd_w, relu=relu)
+    L = abi.lib()
+    tx, vx = _views(x, layout, dtype)
+    ty, vy = _views(np.zeros_like(x), layout, dtype, pad=1)   # output lands inside a halo-padded buffer
+    tdy, vdy = _views(dy, layout, dtype)
+    tdx, vdx = _views(np.zeros_like(x), layout, dtype)
+    dgm, dbt = H.dev(gamma), H.dev(beta)
+    mean, invstd, var = (torch.empty(Cc, device="cuda") for _ in range(3))
+    dgam, dbet = torch.zeros(Cc, device="cuda"), torch.zeros(Cc, device="cuda")
+    nscr = L.ad_bn_scratch_bytes(Cc)
+    scratch = torch.empty(nscr, dtype=torch.uint8, device="cuda")
+    abi.check(L.ad_bn_fwd_train(C.byref(vx), C.byref(vy), H.ptr(dgm), H.ptr(dbt), H.ptr(mean), H.ptr(invstd), H.ptr(var),
+                                f32(1e-5), relu, H.ptr(scratch), nscr, H.stream()))
+    abi.check(L.ad_bn_bwd(C.byref(vx), C.byref(vdy), C.byref(vdx), H.ptr(dgm), H.ptr(dbt), H.ptr(mean), H.ptr(invstd),
+                          H.ptr(dgam), H.ptr(dbet), relu, 0, H.ptr(scratch), nscr, H.stream()))
+    H.sync()
+    tol = 1e-5 if dtype == "f32" else 2e-2
+    assert H.max_rel(H.host(mean), mean_w) < 1e-5 and H.max_rel(H.host(invstd), invstd_w) < 1e-5
+    assert H.max_rel(H.host(var), var_w) < 1e-5
+    assert H.max_rel(_back(ty, layout, 1, Hh, W), y_w) < tol
+    ypad = H.host(ty) if layout == abi.AD_NCHW else orc.nhwc_to_nchw(H.host(ty))
+    assert np.all(ypad[:, :, 0, :] == 0) and np.all(ypad[:, :, :, 0] == 0)  # halo cells untouched
+    # backward is checked with the device's own saved statistics (what the op consumes)
+    assert H.max_rel(_back(tdx, layout, 0, Hh, W), dx_w) < (5e-5 if dtype == "f32" else 2e-2)
+    assert H.max_rel(H.host(dgam), dg_w) < 5e-5 and H.max_rel(H.host(dbet), db_w) < 5e-5
+    assert L.ad_bn_fwd_train(C.byref(vx), C.byref(vy), H.ptr(dgm), H.ptr(dbt), H.ptr(mean), H.ptr(invstd), H.ptr(var),
+                             f32(1e-5), relu, H.ptr(scratch), 8, H.stream()) == abi.AD_ERR_SCRATCH
+
+
+def test_batch_norm_two_phase_matches_single_call_across_strips():
+    """Statistics over R strips via partial sums + host-side sum == statistics over the whole tensor."""
+    import torch
+    N, Cc, Hh, W, R = 1, 8, 16, 12, 4
+    x = H.normal(26, (N, Cc, Hh, W))
+    gamma, beta = np.ones(Cc, np.float32), np.zeros(Cc, np.float32)
+    y_w, mean_w, invstd_w, _ = orc.bn_fwd_train(x, gamma, beta, relu=True)
+    L = abi.lib()
+    nscr = L.ad_bn_scratch_bytes(Cc)
+    scratch = torch.empty(nscr, dtype=torch.uint8, device="cuda")
+    h = Hh // R
+    sums = torch.zeros((R, 2 * Cc), device="cuda")
+    strips = []
+    for r in range(R):
+        t, v = _views(np.ascontiguousarray(x[:, :, r * h:(r + 1) * h]), abi.AD_NCHW, "f32")
+        strips.append((t, v))
+        abi.check(L.ad_bn_partial_stats(C.byref(v), C.c_void_p(sums.data_ptr() + r * 8 * Cc), H.ptr(scratch), nscr, H.stream()))
+    total = sums.sum(dim=0).contiguous()   # stands in for the 2C-float allreduce
+    mean, invstd = torch.empty(Cc, device="cuda"), torch.empty(Cc, device="cuda")
+    for r in range(R):
+        t, v = strips[r]
+        out = torch.empty_like(t)
+        vo = H.view_nchw(out)
+        abi.check(L.ad_bn_finalize_apply(C.byref(v), C.byref(vo), H.ptr(total), C.c_double(N * Hh * W), H.ptr(H.dev(gamma)),
+                                         H.ptr(H.dev(beta)), H.ptr(mean), H.ptr(invstd), None, f32(1e-5), 1, H.stream()))
+        H.sync()
+        assert H.max_rel(H.host(out), y_w[:, :, r * h:(r + 1) * h]) < 1e-5
+    assert H.max_rel(H.host(mean), mean_w) < 1e-5
+
+
+@pytest.mark.parametrize("layout", [abi.AD_NCHW, abi.AD_NHWC])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_maxpool_3x3_s2_on_padded_input(layout, dtype):
+    """The reference's pool sees the explicit zero pad cells (pad value 0, not -inf)."""
+    N, Cc, Hh, W, p = 2, 5, 12, 14, 1
+    x = H.normal(30, (N, Cc, Hh, W)) - 0.5      # mostly negative at some borders: pad zeros win there
+    if dtype == "bf16":
+        x = orc.round_bf16(x)
+    xp = np.zeros((N, Cc, Hh + 2, W + 2), np.float32)
+    xp[:, :, 1:-1, 1:-1] = x
+    y_w = orc.maxpool2d_fwd(xp, (3, 3), (2, 2))
+    dy = H.uniform(31, y_w.shape)
+    if dtype == "bf16":
+        dy = orc.round_bf16(dy)
+    dx_w = orc.maxpool2d_bwd(xp, dy, (3, 3), (2, 2))
+    tx, vx = _views(xp, layout, dtype)
+    ty, vy = _views(np.zeros_like(y_w), layout, dtype)
+    tdy, vdy = _views(dy, layout, dtype)
+    tdx, vdx = _views(np.zeros_like(xp), layout, dtype)
+    L = abi.lib()
+    abi.check(L.ad_maxpool2d_fwd(C.byref(vx), C.byref(vy), 3, 3, 2, 2, H.stream()))
+    abi.check(L.ad_maxpool2d_bwd(C.byref(vx), C.byref(vdy), C.byref(vdx), 3, 3, 2, 2, 0, H.stream()))
+    H.sync()
+    assert np.array_equal(_back(ty, layout, 0, *y_w.shape[2:]), y_w)
+    got = _back(tdx, layout, 0, Hh + 2, W + 2)
+    if dtype == "f32":
+        np.testing.assert_allclose(got, dx_w, rtol=0, atol=1e-6)
+    else:
+        assert H.max_rel(got, dx_w) < 2e-2
+
+
+@pytest.mark.parametrize("layout", [abi.AD_NCHW, abi.AD_NHWC])
+def test_relu_add_convert(layout):
+    N, Cc, Hh, W = 2, 6, 5, 7
+    a, b = H.normal(40, (N, Cc, Hh, W)), H.normal(41, (N, Cc, Hh, W))
+    L = abi.lib()
+    ta, va = _views(a, layout, "f32")
+    tb, vb = _views(b, layout, "f32")
+    ty, vy = _views(np.zeros_like(a), layout, "f32", pad=2)
+    abi.check(L.ad_relu_fwd(C.byref(va), C.byref(vy), H.stream()))
+    H.sync()
+    assert np.array_equal(_back(ty, layout, 2, Hh, W), np.maximum(a, 0))
+    abi.check(L.ad_add(C.byref(va), C.byref(vb), C.byref(vy), H.stream()))
+    H.sync()
+    assert np.array_equal(_back(ty, layout, 2, Hh, W), a + b)
+    tdx, vdx = _views(np.ones_like(a), layout, "f32")
+    abi.check(L.ad_relu_bwd(C.byref(va), C.byref(vb), C.byref(vdx), 1, H.stream()))
+    H.sync()
+    want = np.ones_like(a)
+    orc.relu_bwd(a, b, want)
+    assert np.array_equal(_back(tdx, layout, 0, Hh, W), want)
+    # NCHW fp32 -> NHWC bf16 (graph edge conversion) and back
+    tn, vn = _views(a, abi.AD_NCHW, "f32")
+    th, vh = _views(np.zeros_like(a), abi.AD_NHWC, "bf16")
+    abi.check(L.ad_convert(C.byref(vn), C.byref(vh), 0, H.stream()))
+    H.sync()
+    assert np.array_equal(H.bits_bf16(th), orc.f32_to_bf16(orc.nchw_to_nhwc(a)))
+    tback, vback = _views(np.zeros_like(a), abi.AD_NCHW, "f32")
+    abi.check(L.ad_convert(C.byref(vh), C.byref(vback), 0, H.stream()))
+    H.sync()
+    assert np.array_equal(H.host(tback), orc.round_bf16(a))
