@@ -18,7 +18,7 @@ __device__ __forceinline__ float arr_apply(float a, float b, float x, float y) {
   switch (OP) {
     case kSet: return a;
     case kAdd: return __fadd_rn(x, y);
-    case kAddScaled: return fmaf(a, x, __fmul_rn(b, y));
+    case kAddScaled: return fmaf(b, y, __fmul_rn(a, x));
     case kAddOnline: return fmaf(a, __fsub_rn(x, y), y);
     case kScale: return __fmul_rn(a, x);
     default: return fmaf(a, x, y);
@@ -63,13 +63,14 @@ __global__ void __launch_bounds__(256) sgd_kernel(size_t n, float* theta, float*
   const float nmu = __fmul_rn(-alpha_next, mu);
   for (size_t i = tid; i < n; i += nt) {
     float gi = g[i], th = theta[i], mi = m[i];
-    if (l2 != 0.f) gi = fmaf(l2, th, __fmul_rn(1.0f, gi));
-    mi = fmaf(1.0f, gi, __fmul_rn(mu, mi));
+    // each line is add_scaled(alpha, x, beta): y = fma(beta, y, round(alpha * x))
+    if (l2 != 0.f) gi = fmaf(1.0f, gi, __fmul_rn(l2, th));
+    mi = fmaf(mu, mi, __fmul_rn(1.0f, gi));
     if (nesterov) {
-      th = fmaf(-alpha, gi, __fmul_rn(1.0f, th));
-      th = fmaf(nmu, mi, __fmul_rn(1.0f, th));
+      th = fmaf(1.0f, th, __fmul_rn(-alpha, gi));
+      th = fmaf(1.0f, th, __fmul_rn(nmu, mi));
     } else {
-      th = fmaf(-alpha, mi, __fmul_rn(1.0f, th));
+      th = fmaf(1.0f, th, __fmul_rn(-alpha, mi));
     }
     g[i] = gi; m[i] = mi; theta[i] = th;
     if (shadow) shadow[i] = __float2bfloat16_rn(th);

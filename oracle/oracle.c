@@ -468,9 +468,10 @@ void orc_relu_bwd(size_t n, const float* x, const float* dy, float* dx) {
  * nvcc contracts a*b + c into one fused multiply-add when it compiles the reference
  * (its default -fmad=true), so the rounding of those kernels is that of fmaf below;
  * this file is compiled with -ffp-contract=off so that nothing else is fused. */
-/* alpha*x + beta*y as the reference's add_scaled kernel rounds it. */
+/* alpha*x + beta*y as the reference's add_scaled kernel rounds it: the golden vectors
+ * recorded from that kernel show round(alpha*x) first, then one fused beta*y + that. */
 static inline float orc_add_scaled1(float alpha, float x, float beta, float y) {
-  return fmaf(alpha, x, beta * y);
+  return fmaf(beta, y, alpha * x);
 }
 
 void orc_array_add(size_t n, const float* x, float* y) {              /* y += x        :82-93   */

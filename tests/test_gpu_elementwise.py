@@ -100,7 +100,8 @@ def test_softmax_ce_pixel(Cc, layout, dtype):
     L = abi.lib()
     dt = abi.AD_F32 if dtype == "f32" else abi.AD_BF16
     abi.check(L.ad_softmax_ce_pixel_fwd(dt, layout, N, Cc, HW, H.ptr(d), H.ptr(dl), H.ptr(loss), H.ptr(picked), H.stream()))
-    abi.check(L.ad_softmax_ce_pixel_bwd(dt, layout, N, Cc, HW, H.ptr(d), H.ptr(dl), H.ptr(H.dev(dloss)), H.ptr(dlog), 0, H.stream()))
+    ddl = H.dev(dloss)
+    abi.check(L.ad_softmax_ce_pixel_bwd(dt, layout, N, Cc, HW, H.ptr(d), H.ptr(dl), H.ptr(ddl), H.ptr(dlog), 0, H.stream()))
     H.sync()
     # label index: bit-exact
     pk = picked.cpu().numpy().astype(np.uint64)
@@ -196,12 +197,13 @@ def test_batch_norm_two_phase_matches_single_call_across_strips():
         abi.check(L.ad_bn_partial_stats(C.byref(v), C.c_void_p(sums.data_ptr() + r * 8 * Cc), H.ptr(scratch), nscr, H.stream()))
     total = sums.sum(dim=0).contiguous()   # stands in for the 2C-float allreduce
     mean, invstd = torch.empty(Cc, device="cuda"), torch.empty(Cc, device="cuda")
+    dgm, dbt = H.dev(gamma), H.dev(beta)
     for r in range(R):
         t, v = strips[r]
         out = torch.empty_like(t)
         vo = H.view_nchw(out)
-        abi.check(L.ad_bn_finalize_apply(C.byref(v), C.byref(vo), H.ptr(total), C.c_double(N * Hh * W), H.ptr(H.dev(gamma)),
-                                         H.ptr(H.dev(beta)), H.ptr(mean), H.ptr(invstd), None, f32(1e-5), 1, H.stream()))
+        abi.check(L.ad_bn_finalize_apply(C.byref(v), C.byref(vo), H.ptr(total), C.c_double(N * Hh * W), H.ptr(dgm),
+                                         H.ptr(dbt), H.ptr(mean), H.ptr(invstd), None, f32(1e-5), 1, H.stream()))
         H.sync()
         assert H.max_rel(H.host(out), y_w[:, :, r * h:(r + 1) * h]) < 1e-5
     assert H.max_rel(H.host(mean), mean_w) < 1e-5

@@ -188,7 +188,7 @@ def test_sgd_step_nesterov_and_plain():
         m1 = g1 + 0.9 * m0
         want = th0 - 0.1 * g1 - 0.05 * 0.9 * m1 if nesterov else th0 - 0.1 * m1
         np.testing.assert_allclose(th, want, rtol=1e-5, atol=1e-6)
-        np.testing.assert_allclose(m, m1, rtol=1e-6)
+        np.testing.assert_allclose(m, m1, rtol=1e-5, atol=1e-7)
 
 
 @pytest.mark.parametrize("R", [2, 4])
