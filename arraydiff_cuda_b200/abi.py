@@ -57,6 +57,8 @@ SIGNATURES = {
     "ad_ipc_open_handle": (C.c_int, [C.c_char_p, C.POINTER(vp)]),
     "ad_ipc_close_handle": (C.c_int, [vp]),
     "ad_enable_peer_access": (C.c_int, [C.c_int, C.c_int]),
+    "ad_device_malloc": (C.c_int, [sz, C.POINTER(vp)]),
+    "ad_device_free": (C.c_int, [vp]),
     "ad_slice2d_copy_hw_nchw_packed": (C.c_int, [i32] + [u32] * 8 + [vp, u32, u32, vp, u32, u32, vp]),
     "ad_slice2d_add_hw_nchw_packed": (C.c_int, [i32] + [u32] * 8 + [vp, u32, u32, vp, u32, u32, vp]),
     "ad_array_set_constant": (C.c_int, [sz, f32, vp, vp]),

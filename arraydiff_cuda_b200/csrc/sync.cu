@@ -94,3 +94,15 @@ extern "C" int ad_enable_peer_access(int device, int peer_device) {
   cudaGetLastError();
   return AD_OK;
 }
+
+extern "C" int ad_device_malloc(size_t bytes, void** dev_ptr_out) {
+  if (!dev_ptr_out || bytes == 0) return AD_ERR_BAD_ARG;
+  if (cudaMalloc(dev_ptr_out, bytes) != cudaSuccess) { cudaGetLastError(); return AD_ERR_CUDA; }
+  return AD_OK;
+}
+
+extern "C" int ad_device_free(void* dev_ptr) {
+  if (!dev_ptr) return AD_ERR_BAD_ARG;
+  if (cudaFree(dev_ptr) != cudaSuccess) { cudaGetLastError(); return AD_ERR_CUDA; }
+  return AD_OK;
+}

@@ -1,0 +1,397 @@
+"""Benchmark of the spatially parallel convolution path.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5                  # this library
+    python bench.py --impl reference --gpus 1 --steps 3 --warmup 1  # the CPU path on the host cores
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W      # one rank per GPU
+
+Workload (`config.workload` = "microbench_spatial_conv"): the shape the reference fixes for its
+own measurement of this path -- 3x3 convolution, dilation 3, halo 3, batch 32, 64 -> 64 channels,
+512 x 512 pixels, the H axis cut into one strip per GPU (tools/microbench_spatial_conv.cc:25-41,
+:101-107).  One step = halo exchange + forward conv + data gradient + filter gradient +
+halo-gradient accumulate-back + filter-gradient allreduce.  The total work is fixed as GPUs are
+added ("strong" scaling).  bf16 operands, fp32 accumulate; synthetic seeded inputs.
+
+metric  = spatial conv fwd+bwd TFLOP/s, FLOPs = 3 x 2*N*K*C*9*P*Q counted on the unpartitioned
+          output (halo recompute and padding are not credited).
+value   = with inputs resident in HBM;  e2e = same step fed from pinned host buffers through the
+          C ABI, with the host->device copies of x and dy and the device->host read of dw timed.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BATCH, CH, SIZE, KS, DIL, PAD = 32, 64, 512, 3, 3, 3
+METRIC, UNIT = "spatial_conv_fwd_bwd_tflops", "TFLOP/s"
+
+
+def flops_per_pass(n=BATCH, rows=SIZE, cols=SIZE):
+    return 2.0 * n * CH * CH * KS * KS * rows * cols
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"hbm_gbs": d["hbm_gbs"], "tf_burst": d["bf16_tflops"], "tf_sustained": d["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tf_burst": 1590.0, "tf_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def cpu_conv_sample(target_seconds, threads_omp=True):
+    """Times the oracle's conv fwd + dgrad + wgrad on a strip sample of the workload (one image,
+    `rows` output rows, full width, dilation 3, halo-padded input) sized for ~target_seconds."""
+    from oracle import orc
+    from tests import helpers as H
+
+    def run(rows):
+        x = H.uniform(1, (1, CH, rows + 2 * PAD, SIZE + 2 * PAD))
+        w = H.normal(2, (CH, CH, KS, KS), float(np.sqrt(2.0 / (KS * KS * CH))))
+        dy = H.uniform(3, (1, CH, rows, SIZE))
+        t0 = time.perf_counter()
+        y = orc.conv2d_fprop(x, w, None, dil=(DIL, DIL), omp=threads_omp)
+        orc.conv2d_dgrad(dy, w, x.shape, dil=(DIL, DIL), omp=threads_omp)
+        orc.conv2d_wgrad(x, dy, w.shape, dil=(DIL, DIL), omp=threads_omp)
+        dt = time.perf_counter() - t0
+        assert y.shape == (1, CH, rows, SIZE)
+        return dt, 3 * flops_per_pass(1, rows, SIZE)
+
+    dt, fl = run(2)                       # calibration
+    rows = int(max(2, min(SIZE, 2 * target_seconds / max(dt, 1e-6))))
+    dt, fl = run(rows)
+    return fl / dt / 1e12, dt, rows, orc.num_threads(threads_omp)
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    budget = 120.0 / max(1, args.steps + args.warmup)
+    vals, rows, cores, secs = [], 0, 1, 0.0
+    for i in range(args.warmup + args.steps):
+        v, dt, rows, cores = cpu_conv_sample(min(20.0, budget))
+        if i >= args.warmup:
+            vals.append(v); secs += dt
+    value = float(np.mean(vals))
+    sample = f"oracle conv fwd+dgrad+wgrad on a {rows}-row x {SIZE}-col strip of one image per step (of 32 x 512 rows)"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * secs / max(1, args.steps), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "microbench_spatial_conv", "batch": BATCH, "channels": CH, "image": [SIZE, SIZE],
+                   "kernel": KS, "dilation": DIL, "halo": PAD, "bounded_sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+# ----------------------------------------------------------------------------- GPU arm
+class Step:
+    """Buffers and the per-step call sequence of one rank (one H-strip)."""
+
+    def __init__(self, rank, world):
+        import torch
+        from arraydiff_cuda_b200 import abi, dist as addist
+        self.torch, self.abi = torch, abi
+        self.L = abi.load()
+        self.rank, self.world = rank, world
+        self.h = SIZE // world
+        h, Wp, Hp = self.h, SIZE + 2 * PAD, SIZE // world + 2 * PAD
+        bf = torch.bfloat16
+        xbytes = BATCH * Hp * Wp * CH * 2
+        self.arena = addist.SymmetricArena(2 * xbytes + (1 << 20), rank, world)
+        self.x, self.x_off = self.arena.alloc((BATCH, Hp, Wp, CH), bf)       # halo-padded input strip
+        self.gx, self.gx_off = self.arena.alloc((BATCH, Hp, Wp, CH), bf)     # halo-padded input gradient
+        self.flags, self.flags_off = self.arena.alloc((8,), torch.int64)      # 0 from_prev 1 from_next 2 gprev 3 gnext
+        self.counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self.status = torch.zeros(4, dtype=torch.int32, device="cuda")
+        g = torch.Generator(device="cuda").manual_seed(1234 + rank)
+        self.x.zero_()
+        self.x[:, PAD:PAD + h, PAD:PAD + SIZE] = (torch.rand((BATCH, h, SIZE, CH), device="cuda", generator=g) * 2 - 1).to(bf)
+        gw = torch.Generator(device="cuda").manual_seed(99)
+        self.w = (torch.randn((CH, KS, KS, CH), device="cuda", generator=gw) * float(np.sqrt(2.0 / (KS * KS * CH)))).to(bf)
+        self.y = torch.empty((BATCH, h, SIZE, CH), dtype=bf, device="cuda")
+        self.dy = (torch.rand((BATCH, h, SIZE, CH), device="cuda", generator=g) * 2 - 1).to(bf)
+        self.dw = torch.zeros((CH, KS, KS, CH), device="cuda")
+        a = abi.Conv2dArgs()
+        a.dtype, a.layout = abi.AD_BF16, abi.AD_NHWC
+        a.N, a.C, a.H, a.W, a.K, a.kh, a.kw = BATCH, CH, Hp, Wp, CH, KS, KS
+        a.stride_h = a.stride_w = 1
+        a.dil_h = a.dil_w = DIL
+        nscr = max(self.L.ad_conv2d_scratch_bytes(C.byref(a), 1), self.L.ad_conv2d_scratch_bytes(C.byref(a), 2), 16)
+        self.scratch = torch.zeros(nscr, dtype=torch.uint8, device="cuda")
+        a.x, a.w, a.scratch, a.scratch_bytes = self.x.data_ptr(), self.w.data_ptr(), self.scratch.data_ptr(), nscr
+        self.conv = a
+        self.epoch = 0
+        ha = abi.HaloArgs()
+        ha.dtype, ha.layout = abi.AD_BF16, abi.AD_NHWC
+        ha.halo_pad, ha.base_width, ha.base_height, ha.num_channels, ha.batch_size = PAD, SIZE, h, CH, BATCH
+        ha.num_ranks, ha.rank_first, ha.rank_count, ha.push = world, rank, 1, 1
+        self.hx, self.hg = ha, abi.HaloArgs.from_buffer_copy(ha)
+        xp, gp, fp = self.arena.peers(self.x_off), self.arena.peers(self.gx_off), self.arena.peers(self.flags_off)
+        for r in range(world):
+            self.hx.bufs[r], self.hg.bufs[r] = xp[r], gp[r]
+        if rank + 1 < world:
+            self.hx.signal_flags[rank + 1] = fp[rank + 1] + 0      # its "from_prev"
+        if rank > 0:
+            self.hx.signal_flags[rank - 1] = fp[rank - 1] + 8      # its "from_next"
+        self.hx.block_counter = self.counter.data_ptr()
+        self.fp = fp
+        # pinned host copies for the end-to-end variant
+        self.hx_host = torch.empty(self.x.shape, dtype=bf).pin_memory()
+        self.hx_host.copy_(self.x.cpu())
+        self.dy_host = torch.empty(self.dy.shape, dtype=bf).pin_memory()
+        self.dy_host.copy_(self.dy.cpu())
+        self.dw_host = torch.empty(self.dw.shape, dtype=torch.float32).pin_memory()
+
+    def _s(self):
+        return C.c_void_p(self.torch.cuda.current_stream().cuda_stream)
+
+    def _wait(self, slot, epoch):
+        self.abi.check(self.L.ad_flag_wait(C.c_void_p(self.flags.data_ptr() + 8 * slot), epoch, 2_000_000_000,
+                                           C.c_void_p(self.status.data_ptr()), self._s()), "flag wait")
+
+    def _signal(self, rank, slot, epoch):
+        self.abi.check(self.L.ad_flag_signal(C.c_void_p(self.fp[rank] + 8 * slot), epoch, self._s()), "flag signal")
+
+    def run(self, e2e=False):
+        L, abi, a, s = self.L, self.abi, self.conv, self._s()
+        r, R = self.rank, self.world
+        self.epoch += 1
+        ep = self.epoch
+        if e2e:
+            self.x.copy_(self.hx_host, non_blocking=True)
+            self.dy.copy_(self.dy_host, non_blocking=True)
+        # forward: push my edge rows into the neighbours' halo rows, wait for theirs, convolve
+        if R > 1:
+            self.hx.epoch = ep
+            abi.check(L.ad_halo_exchange(C.byref(self.hx), s), "halo exchange")
+            if r > 0:
+                self._wait(0, ep)
+            if r + 1 < R:
+                self._wait(1, ep)
+        a.y, a.accumulate = self.y.data_ptr(), 0
+        abi.check(L.ad_conv2d_fprop(C.byref(a), s), "fprop")
+        # backward: data gradient over the whole padded strip, filter gradient, halo-gradient accumulate-back
+        a.y, a.dx, a.dw = self.dy.data_ptr(), self.gx.data_ptr(), self.dw.data_ptr()
+        abi.check(L.ad_conv2d_dgrad(C.byref(a), s), "dgrad")
+        if R > 1:
+            if r + 1 < R:
+                self._signal(r + 1, 2, ep)
+            if r > 0:
+                self._signal(r - 1, 3, ep)
+        abi.check(L.ad_conv2d_wgrad(C.byref(a), s), "wgrad")
+        if R > 1:
+            if r > 0:
+                self._wait(2, ep)
+            if r + 1 < R:
+                self._wait(3, ep)
+            abi.check(L.ad_halo_reduce(C.byref(self.hg), s), "halo reduce")
+            import torch.distributed as dist
+            dist.all_reduce(self.dw)       # filter-gradient allreduce over NCCL / NVLink
+        if e2e:
+            self.dw_host.copy_(self.dw, non_blocking=True)
+
+    def check_status(self):
+        st = self.status.cpu().tolist() + self.scratch[:4].view(self.torch.int32).cpu().tolist()
+        if any(v != 0 for v in st):
+            raise RuntimeError(f"device-side bounded wait reported {st}")
+
+
+def timed_loop(torch, dist, step, steps, e2e, world):
+    """Barrier + synchronize on both sides, device time by CUDA events, max over ranks."""
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step.run(e2e=e2e)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.barrier()
+    return ms
+
+
+def kernel_times(torch, step, iters=10):
+    """Per-kernel device time (CUDA events on the launching stream), each launch after an L2 flush."""
+    L, abi, a = step.L, step.abi, step.conv
+    s = step._s()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def t(fn):
+        fn(); torch.cuda.synchronize()
+        out = []
+        for _ in range(iters):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record(); torch.cuda.synchronize()
+            out.append(e0.elapsed_time(e1))
+        return float(np.mean(out)) * 1e-3
+
+    def fprop():
+        a.y = step.y.data_ptr(); abi.check(L.ad_conv2d_fprop(C.byref(a), s))
+
+    def dgrad():
+        a.y, a.dx = step.dy.data_ptr(), step.gx.data_ptr(); abi.check(L.ad_conv2d_dgrad(C.byref(a), s))
+
+    def wgrad():
+        a.y, a.dw = step.dy.data_ptr(), step.dw.data_ptr(); abi.check(L.ad_conv2d_wgrad(C.byref(a), s))
+
+    return {"fprop": t(fprop), "dgrad": t(dgrad), "wgrad": t(wgrad)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    if SIZE % world:
+        raise SystemExit("image height must divide by the number of GPUs")
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    from arraydiff_cuda_b200 import abi
+    L = abi.load()   # raises if the CUDA library is missing: no fallback
+    step = Step(rank, world)
+    for _ in range(args.warmup):
+        step.run()
+    torch.cuda.synchronize()
+    step.check_status()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = L.ad_launch_count()
+    ms = timed_loop(torch, dist, step, args.steps, False, world)
+    launches = L.ad_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    step.check_status()
+    for _ in range(2):
+        step.run(e2e=True)
+    e2e_steps = max(3, args.steps // 4)
+    ms_e2e = timed_loop(torch, dist, step, e2e_steps, True, world)
+    step.check_status()
+
+    total_flops = 3 * flops_per_pass()
+    value = total_flops / (ms / args.steps * 1e-3) / 1e12
+    e2e_value = total_flops / (ms_e2e / e2e_steps * 1e-3) / 1e12
+    if rank == 0:
+        peaks = measured_peaks()
+        kt = kernel_times(torch, step)
+        top = max(kt, key=kt.get)
+        per_launch_flops = flops_per_pass(BATCH, step.h, SIZE)
+        achieved = per_launch_flops / kt[top] / 1e12
+        cpu = None
+        if world == 1:
+            v, dt, rows, cores = cpu_conv_sample(args.cpu_seconds)
+            cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
+                   "sample": f"oracle conv fwd+dgrad+wgrad on a {rows}-row x {SIZE}-col strip of one image ({dt:.1f} s)"}
+        hbytes = step.hx_host.numel() * 2 + step.dy_host.numel() * 2
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "microbench_spatial_conv", "batch": BATCH, "channels": CH, "image": [SIZE, SIZE],
+                       "kernel": KS, "dilation": DIL, "halo": PAD, "strips": world, "layout": "NHWC",
+                       "l2": "inputs larger than L2 (1.07 GB activations per pass)", "parallelism": f"spatial-h{world}"},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": hbytes,
+                    "d2h_bytes_per_step": step.dw_host.numel() * 4, "steps": e2e_steps},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "tensor", "kernel": f"conv_tc_{top}", "achieved": achieved, "peak": peaks["tf_burst"],
+                         "unit": "TFLOP/s", "frac": achieved / peaks["tf_burst"], "traffic": None,
+                         "peak_source": peaks["source"] + " (burst, kernel timed alone)",
+                         "kernels_us": {k: v * 1e6 for k, v in kt.items()}},
+            "clocks": clocks,
+        }
+        if cpu:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

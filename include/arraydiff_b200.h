@@ -114,6 +114,11 @@ int ad_ipc_get_handle(void* dev_ptr, uint8_t handle_out[64]);   /* host out */
 int ad_ipc_open_handle(const uint8_t handle[64], void** dev_ptr_out);
 int ad_ipc_close_handle(void* dev_ptr);
 int ad_enable_peer_access(int device, int peer_device); /* src/spatial.cc:13-29 */
+/* Set-up helpers, NOT for the hot path: one cudaMalloc'd arena per rank keeps halo buffers and
+ * flag words at the same offset on every rank, so that one IPC handle per rank is enough
+ * (GPUMemory<T>, include/arraydiff/array_gpu.hh:82-109, is the reference's allocator). */
+int ad_device_malloc(size_t bytes, void** dev_ptr_out);
+int ad_device_free(void* dev_ptr);
 
 /* ------------------------------------------------------------------------------------------
  * 2-D window copy / add between packed NCHW tensors.
