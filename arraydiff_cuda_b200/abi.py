@@ -7,6 +7,7 @@ LIB_PATH = os.path.join(HERE, "libarraydiff_b200.so")
 
 AD_MAX_PEERS = 8
 AD_OK, AD_ERR_BAD_ARG, AD_ERR_UNSUPPORTED, AD_ERR_CUDA, AD_ERR_TIMEOUT, AD_ERR_ALIGN, AD_ERR_SCRATCH = 0, -1, -2, -3, -4, -5, -6
+AD_ERR_LIMIT = -7
 AD_F32, AD_BF16 = 0, 3
 AD_NCHW, AD_NHWC = 0, 1
 
@@ -75,6 +76,7 @@ SIGNATURES = {
     "ad_softmax_ce_pixel_bwd": (C.c_int, [i32, i32, u32, u32, u32, vp, vp, vp, vp, i32, vp]),
     "ad_bn_scratch_bytes": (sz, [u32]),
     "ad_bn_fwd_train": (C.c_int, [C.POINTER(Tensor4), C.POINTER(Tensor4), vp, vp, vp, vp, vp, f32, i32, vp, sz, vp]),
+    "ad_bn_fwd_train_noalloc": (C.c_int, [C.POINTER(Tensor4), C.POINTER(Tensor4), vp, vp, vp, vp, vp, f32, i32, vp]),
     "ad_bn_bwd": (C.c_int, [C.POINTER(Tensor4)] * 3 + [vp, vp, vp, vp, vp, vp, i32, i32, vp, sz, vp]),
     "ad_bn_partial_stats": (C.c_int, [C.POINTER(Tensor4), vp, vp, sz, vp]),
     "ad_bn_finalize_apply": (C.c_int, [C.POINTER(Tensor4), C.POINTER(Tensor4), vp, C.c_double, vp, vp, vp, vp, vp, f32, i32, vp]),

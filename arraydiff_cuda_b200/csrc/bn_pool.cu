@@ -393,3 +393,43 @@ extern "C" int ad_maxpool2d_bwd(const ad_tensor4* x, const ad_tensor4* dy, const
   count_launch();
   return launch_status();
 }
+
+// ------------------------------------------------------------------ allocation-free variant
+// Some callers of this library are not in a position to allocate device memory for the
+// statistics scratch: an op body running inside a host framework that has handed the whole
+// device to its own memory pool, or a latency-critical loop in which cudaMalloc (which may
+// synchronise the device) must not appear.  For them the scratch of the batch-norm forward
+// lives in this file-scope device array, sized for at most kBnStaticMaxC channels.  The array
+// exists once per GPU that loads the library and is held until the process exits.
+constexpr uint32_t kBnStaticMaxC = 2048;
+constexpr size_t kBnStaticBytes = (size_t)(adk::kBnMaxSplits + 1) * 2 * kBnStaticMaxC * sizeof(float);
+static __device__ __align__(256) unsigned char g_bn_static_scratch[kBnStaticBytes];
+
+// In host code the array's name is only a handle for the runtime, never a device address:
+// the address has to be asked for, once per device, with that device current.
+static int bn_static_scratch_address(void** out) {
+  constexpr int kMaxDevices = 64;
+  static void* addr[kMaxDevices] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return AD_ERR_CUDA; }
+  if (!addr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_bn_static_scratch) != cudaSuccess || !p) { cudaGetLastError(); return AD_ERR_CUDA; }
+    addr[dev] = p;
+  }
+  *out = addr[dev];
+  return AD_OK;
+}
+
+extern "C" int ad_bn_fwd_train_noalloc(const ad_tensor4* x, const ad_tensor4* y, const float* gamma, const float* beta,
+                                       float* save_mean, float* save_invstd, float* batch_var, float eps, int32_t relu,
+                                       void* stream) {
+  if (!x) return AD_ERR_BAD_ARG;
+  if (x->C > kBnStaticMaxC) return AD_ERR_LIMIT;  // more channels than the built-in scratch holds
+  void* scratch = nullptr;
+  int st = bn_static_scratch_address(&scratch);
+  if (st != AD_OK) return st;
+  // Every word of the scratch that the kernels read is written earlier in the same call, so
+  // nothing has to be cleared even though the array keeps the previous call's contents.
+  return ad_bn_fwd_train(x, y, gamma, beta, save_mean, save_invstd, batch_var, eps, relu, scratch, kBnStaticBytes, stream);
+}

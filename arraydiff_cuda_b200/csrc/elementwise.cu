@@ -165,6 +165,7 @@ extern "C" const char* ad_status_string(int status) {
     case AD_ERR_TIMEOUT: return "bounded device wait timed out";
     case AD_ERR_ALIGN: return "misaligned pointer or pitch";
     case AD_ERR_SCRATCH: return "scratch buffer too small";
+    case AD_ERR_LIMIT: return "size exceeds a limit built into the entry point";
     default: return "unknown status";
   }
 }

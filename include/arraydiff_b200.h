@@ -35,7 +35,8 @@ typedef enum {
   AD_ERR_CUDA = -3,        /* the launch itself reported a CUDA error                      */
   AD_ERR_TIMEOUT = -4,     /* a bounded device-side wait ran out (reported via status word) */
   AD_ERR_ALIGN = -5,       /* a pointer or pitch violates the alignment the kernel needs   */
-  AD_ERR_SCRATCH = -6      /* caller-provided scratch is too small                         */
+  AD_ERR_SCRATCH = -6,     /* caller-provided scratch is too small                         */
+  AD_ERR_LIMIT = -7        /* a size exceeds a limit built into the entry point             */
 } ad_status;
 
 /* include/arraydiff/spatial.hh:25-29 (Spatial2DDataType) -- bf16 added. */
@@ -223,6 +224,22 @@ int ad_bn_bwd(const ad_tensor4* x, const ad_tensor4* dy, const ad_tensor4* dx, c
               const float* beta, const float* save_mean, const float* save_invstd, float* dgamma,
               float* dbeta, int32_t relu, int32_t accumulate_dx, void* scratch, size_t scratch_bytes,
               void* stream);
+/*
+ * ad_bn_fwd_train without any scratch argument, for callers that cannot allocate device memory
+ * (an op running under a framework that owns the whole device through its own pool, or a loop
+ * that must not meet cudaMalloc's device synchronisation).  This entry point has no counterpart
+ * in the reference.  The scratch is a fixed array inside the library, enough for C <= 2048
+ * channels (about 2 MiB, present once on every GPU that loads the library until the process
+ * ends); more channels are refused with AD_ERR_LIMIT.  Inputs and outputs are still the
+ * caller's.  Nothing is allocated or freed, here or in anything this calls.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
+ * that device current); make that first call before any stream capture starts.
+ * All calls share the one array: two calls that can overlap on the GPU (different streams
+ * without an ordering between them) race on it and give wrong statistics -- order them.
+ */
+int ad_bn_fwd_train_noalloc(const ad_tensor4* x, const ad_tensor4* y, const float* gamma, const float* beta,
+                            float* save_mean, float* save_invstd, float* batch_var, float eps, int32_t relu,
+                            void* stream);
 /* sums[0..C) = sum x, sums[C..2C) = sum x^2 over this tensor (fp32, overwritten). */
 int ad_bn_partial_stats(const ad_tensor4* x, float* sums, void* scratch, size_t scratch_bytes, void* stream);
 /* count = total elements per channel behind `sums` (all ranks). */
