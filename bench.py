@@ -35,8 +35,8 @@ BATCH, CH, SIZE, KS, DIL, PAD = 32, 64, 512, 3, 3, 3
 METRIC, UNIT = "spatial_conv_fwd_bwd_tflops", "TFLOP/s"
 
 
-def flops_per_pass(n=BATCH, rows=SIZE, cols=SIZE):
-    return 2.0 * n * CH * CH * KS * KS * rows * cols
+def flops_per_pass(n=None, rows=SIZE, cols=SIZE):
+    return 2.0 * (BATCH if n is None else n) * CH * CH * KS * KS * rows * cols
 
 
 def measured_peaks():
@@ -307,13 +307,17 @@ def kernel_times(torch, step, iters=10):
 
 
 def main():
+    global BATCH
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--batch", type=int, default=BATCH,
+                    help="images per step; the default is the workload's, smaller values are for profiler captures")
     args = ap.parse_args()
+    BATCH = args.batch
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference_arm(args)
@@ -375,7 +379,7 @@ def main():
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "microbench_spatial_conv", "batch": BATCH, "channels": CH, "image": [SIZE, SIZE],
                        "kernel": KS, "dilation": DIL, "halo": PAD, "strips": world, "layout": "NHWC",
-                       "l2": "inputs larger than L2 (1.07 GB activations per pass)", "parallelism": f"spatial-h{world}"},
+                       "l2": "inputs larger than L2 (%.2f GB activations per pass)" % (BATCH * SIZE * SIZE * CH * 2 / 1e9), "parallelism": f"spatial-h{world}"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": hbytes,
                     "d2h_bytes_per_step": step.dw_host.numel() * 4, "steps": e2e_steps},
             "gpu_launches": int(launches),
