@@ -221,3 +221,39 @@ extern "C" int ad_add(const ad_tensor4* a, const ad_tensor4* b, const ad_tensor4
 extern "C" int ad_convert(const ad_tensor4* src, const ad_tensor4* dst, int32_t accumulate, void* stream) {
   return ew_launch<kConvert>(src, nullptr, dst, accumulate, stream);
 }
+
+// ---------------------------------------------------------------- patch matrix for C_in < 8 layers
+namespace adk {
+template <typename T>
+__global__ void __launch_bounds__(256) im2col_kernel(View x, uint32_t N, uint32_t C, uint32_t H, uint32_t W, uint32_t kh,
+                                                     uint32_t kw, uint32_t sh, uint32_t sw, uint32_t dh, uint32_t dw,
+                                                     uint32_t P, uint32_t Q, __nv_bfloat16* out, uint32_t ldo) {
+  const uint32_t cols = kh * kw * C;
+  const size_t total = (size_t)N * P * Q * cols, nt = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nt) {
+    const uint32_t col = (uint32_t)(i % cols);
+    const size_t pix = i / cols;
+    const uint32_t c = col % C, tap = col / C, s = tap % kw, r = tap / kw;
+    const uint32_t q = (uint32_t)(pix % Q);
+    const size_t rest = pix / Q;
+    const uint32_t p = (uint32_t)(rest % P), n = (uint32_t)(rest / P);
+    const uint32_t yy = p * sh + r * dh, xx = q * sw + s * dw;
+    float v = 0.f;
+    if (yy < H && xx < W) v = ld_f((const T*)x.base + voff(x, n, c, yy, xx));
+    out[pix * ldo + col] = __float2bfloat16_rn(v);
+  }
+}
+}  // namespace adk
+
+extern "C" int ad_im2col(const ad_tensor4* x, uint32_t kh, uint32_t kw, uint32_t sh, uint32_t sw, uint32_t dh, uint32_t dw,
+                         uint32_t P, uint32_t Q, void* out_bf16, uint32_t ldo, void* stream) {
+  if (!x || !x->base || !out_bf16 || kh == 0 || kw == 0 || sh == 0 || sw == 0 || dh == 0 || dw == 0) return AD_ERR_BAD_ARG;
+  if (ldo < kh * kw * x->C) return AD_ERR_BAD_ARG;
+  const size_t total = (size_t)x->N * P * Q * kh * kw * x->C;
+  if (total == 0) return AD_OK;
+  adk::View v = adk::view_of(x);
+  AD_DISPATCH_DTYPE(x->dtype, (adk::im2col_kernel<T><<<adk::grid_for(total, 256, 16), 256, 0, adk::as_stream(stream)>>>(
+                                  v, x->N, x->C, x->H, x->W, kh, kw, sh, sw, dh, dw, P, Q, (__nv_bfloat16*)out_bf16, ldo)));
+  adk::count_launch();
+  return adk::launch_status();
+}

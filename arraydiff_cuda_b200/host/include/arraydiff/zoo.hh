@@ -1,0 +1,66 @@
+// Model builders of the spatially parallel path.  Same entry points as the reference's
+// include/arraydiff/zoo.hh:61-190 for this path (conv2d / parallel_conv2d, the spatial_parallel_*
+// residual blocks); bodies compose the operators of op.hh per rank, in the same order on every rank
+// so that flat parameter buffers line up (reference include/arraydiff/optimize.hh:323-333).
+#ifndef ARRAYDIFF_ZOO_HH
+#define ARRAYDIFF_ZOO_HH
+
+#include "arraydiff/op.hh"
+
+namespace arraydiff {
+
+template <typename V> struct ParamOp { shared_ptr<Var<V>> op; VarIdSet params, grads; };
+template <typename V> struct ParallelParamOp { vector<shared_ptr<Var<V>>> ops; vector<VarIdSet> params, grads; };
+template <typename V> struct BatchNormParamOp { shared_ptr<Var<V>> op; VarIdSet params, grads, batch_stats, fixed_stats; };
+template <typename V> struct ParallelBatchNormParamOp {
+  vector<shared_ptr<Var<V>>> ops;
+  vector<VarIdSet> params, grads, batch_stats, fixed_stats;
+};
+
+typedef IOOp<GPUArray4D<float>>::InitFn KernelInitFn;
+// normal(0, sqrt(2 / fan_in)), drawn on the host from the shared generator (reference src/op.cc:362-408)
+template <typename A> typename IOOp<A>::InitFn kaiming_init_gen(size_t fan_in, size_t fan_out);
+template <typename A> typename IOOp<A>::InitFn zeros_init_gen();
+
+template <typename V> ParamOp<V> conv2d(Conv2DShape shape, shared_ptr<Var<V>> input, KernelInitFn kernel_init, bool enable_bias, shared_ptr<Context> ctx);
+template <typename V> ParallelParamOp<V> parallel_conv2d(Conv2DShape shape, vector<shared_ptr<Var<V>>> inputs, KernelInitFn kernel_init, bool enable_bias, shared_ptr<Context> ctx);
+template <typename V> vector<shared_ptr<Var<V>>> parallel_relu(vector<shared_ptr<Var<V>>> inputs, shared_ptr<Context> ctx);
+template <typename V> vector<shared_ptr<Var<V>>> parallel_sum(vector<vector<shared_ptr<Var<V>>>> inputs, shared_ptr<Context> ctx);
+// batch norm per rank, optionally with the following ReLU folded in
+template <typename V> ParallelBatchNormParamOp<V> parallel_batch_norm(size_t channels, shared_ptr<bool> switch_var, vector<shared_ptr<Var<V>>> inputs, bool fuse_relu, shared_ptr<Context> ctx);
+
+template <typename V> ParallelBatchNormParamOp<V> spatial_parallel_residual_v2_conv2d(Conv2DShape shape, shared_ptr<bool> switch_var, vector<shared_ptr<Var<V>>> inputs, shared_ptr<Context> ctx);
+template <typename V> ParallelBatchNormParamOp<V> spatial_parallel_proj_residual_v2_conv2d(Conv2DShape shape, size_t stride, shared_ptr<bool> switch_var, vector<shared_ptr<Var<V>>> inputs, shared_ptr<Context> ctx);
+template <typename V> ParallelBatchNormParamOp<V> spatial_parallel_bottleneck_residual_v2_conv2d(Conv2DShape shape, size_t bottleneck, shared_ptr<bool> switch_var, vector<shared_ptr<Var<V>>> inputs, shared_ptr<Context> ctx);
+template <typename V> ParallelBatchNormParamOp<V> spatial_parallel_proj_bottleneck_residual_v2_conv2d(Conv2DShape shape, size_t bottleneck, size_t stride, shared_ptr<bool> switch_var, vector<shared_ptr<Var<V>>> inputs, shared_ptr<Context> ctx);
+
+class ConvNetConfig {
+public:
+  size_t input_c = 3, input_w = 0, input_h = 0, batch_size = 1, minibatch_size = 1;
+};
+
+// A spatially partitioned feature extractor: per-rank inputs (the full image, scattered into
+// H-strips inside the graph), per-rank outputs (strips), and the per-rank variable sets.
+struct SpatialParallelNet {
+  shared_ptr<bool> batch_norm_use_fixed;
+  vector<shared_ptr<IOOp<Act>>> inputs;
+  vector<ActVar> outputs;
+  shared_ptr<Op> sink;          // GroupSinkOp over all outputs: walk from here
+  VarIdSet input_vars;
+  vector<VarIdSet> output_grad_vars;
+  vector<VarIdSet> dev_params, dev_grads, dev_batch_stats, dev_fixed_stats;
+};
+
+template <typename T>
+class SpatialParallelResNet {
+public:
+  // One 3x3 convolution (stride 1, pad 1, bias) over H-strips: scatter -> halo pad -> halo exchange ->
+  // conv.  The plumbing case of the partitioned path.
+  static SpatialParallelNet MakeConv3x3(const ConvNetConfig& config, size_t filters, shared_ptr<Context> ctx);
+  // ResNet-50 stem + stage 1: 7x7/2 conv to 64 channels, BN, ReLU, 3x3/2 max pool, then three
+  // pre-activation bottleneck blocks (64-64-256), the first with a 1x1 projection.
+  static SpatialParallelNet MakeStemStage1(const ConvNetConfig& config, shared_ptr<Context> ctx);
+};
+
+}  // namespace arraydiff
+#endif

@@ -1,0 +1,181 @@
+// C entry points over the C++ host layer, for drivers that are not C++ (the Python tests and the
+// benchmark): build a context and a net, feed host tensors, run forward / backward / update, read
+// results back.  Handles are opaque pointers; functions return 0 or a negative ad_status.
+#include <cstring>
+#include <memory>
+
+#include "arraydiff/optimize.hh"
+#include "arraydiff/zoo.hh"
+
+using namespace arraydiff;
+
+namespace {
+struct Net {
+  shared_ptr<MultiGPUContext> ctx;
+  SpatialParallelNet net;
+  ConvNetConfig cfg;
+  std::unique_ptr<ParallelSGDOptimizer<float>> opt;
+  std::unique_ptr<TxnId> txn;
+  std::mt19937_64 rng;
+};
+struct Ctx { shared_ptr<MultiGPUContext> ctx; };
+}  // namespace
+
+extern "C" {
+
+void* adh_context_create(const int* devices, int n, int mode, size_t arena_mb) {
+  vector<int> devs(devices, devices + n);
+  auto* c = new Ctx{MultiGPUContext::Make(devs, (ComputeMode)mode, arena_mb << 20)};
+  return c;
+}
+void* adh_context_create_distributed(int rank, int world, int device, int mode, size_t arena_mb) {
+  return new Ctx{MultiGPUContext::MakeDistributed((size_t)rank, (size_t)world, device, (ComputeMode)mode, arena_mb << 20)};
+}
+void adh_context_destroy(void* c) { delete (Ctx*)c; }
+int adh_context_arena_handle(void* c, uint8_t out[64]) {
+  auto& m = ((Ctx*)c)->ctx;
+  return ad_ipc_get_handle(m->arena_base(m->my_rank()), out);
+}
+int adh_context_set_peer_handle(void* c, int rank, const uint8_t handle[64]) {
+  auto& m = ((Ctx*)c)->ctx;
+  void* p = nullptr;
+  GPUConn conn = m->device_context(m->my_rank())->conn();
+  int st = ad_ipc_open_handle(handle, &p);
+  if (st != AD_OK) return st;
+  m->set_peer_arena((size_t)rank, p);
+  return AD_OK;
+}
+void adh_context_set_allreduce_hook(void* c, void (*fn)(float*, size_t, cudaStream_t, void*), void* user) {
+  ((Ctx*)c)->ctx->set_allreduce_hook(fn, user);
+}
+void* adh_context_stream(void* c, int rank) { return (void*)((Ctx*)c)->ctx->device_context((size_t)rank)->stream(); }
+
+// kind: "conv3x3" (filters = output channels) or "stem_stage1"
+void* adh_net_create(void* c, const char* kind, int H, int W, int C, int batch, int filters, uint64_t seed) {
+  auto* n = new Net();
+  n->ctx = ((Ctx*)c)->ctx;
+  n->cfg.input_h = (size_t)H; n->cfg.input_w = (size_t)W; n->cfg.input_c = (size_t)C; n->cfg.batch_size = (size_t)batch;
+  n->rng.seed(seed);
+  if (!std::strcmp(kind, "conv3x3")) n->net = SpatialParallelResNet<float>::MakeConv3x3(n->cfg, (size_t)filters, n->ctx);
+  else if (!std::strcmp(kind, "stem_stage1")) n->net = SpatialParallelResNet<float>::MakeStemStage1(n->cfg, n->ctx);
+  else { delete n; return nullptr; }
+  SGDConfig sc;
+  sc.step_size = make_shared<ConstantSchedule<double>>(0.1);
+  sc.momentum = make_shared<ConstantSchedule<double>>(0.9);
+  n->opt.reset(new ParallelSGDOptimizer<float>(sc, n->net.sink, n->net.dev_params, n->net.dev_grads));
+  n->opt->reset(n->ctx, &n->rng);
+  return n;
+}
+void adh_net_destroy(void* h) { delete (Net*)h; }
+int adh_net_configure_sgd(void* h, double step_size, double momentum, double l2, int nesterov) {
+  auto* n = (Net*)h;
+  SGDConfig sc;
+  sc.step_size = make_shared<ConstantSchedule<double>>(step_size);
+  sc.momentum = make_shared<ConstantSchedule<double>>(momentum);
+  sc.l2_reg = l2; sc.nesterov = nesterov != 0;
+  vector<float> keep(n->opt->param_dim());
+  size_t first = n->ctx->distributed() ? n->ctx->my_rank() : 0;
+  n->opt->store_params(first, keep.data());
+  n->opt.reset(new ParallelSGDOptimizer<float>(sc, n->net.sink, n->net.dev_params, n->net.dev_grads));
+  std::mt19937_64 rng(1);
+  n->opt->reset(n->ctx, &rng);
+  n->opt->load_params(keep.data());
+  return AD_OK;
+}
+// "name offset size\n" per parameter of the flat buffer (rank 0's order; every rank's is the same)
+size_t adh_net_param_manifest(void* h, char* buf, size_t cap) {
+  auto* n = (Net*)h;
+  size_t first = n->ctx->distributed() ? n->ctx->my_rank() : 0;
+  ParamManifest m;
+  any w = &m;
+  TxnId t;
+  n->net.sink->store_val(t, n->net.dev_params[first], 0, &w);
+  string out;
+  for (auto& e : m) out += e.name + " " + std::to_string(e.offset) + " " + std::to_string(e.size) + "\n";
+  if (buf && cap) { std::strncpy(buf, out.c_str(), cap - 1); buf[cap - 1] = 0; }
+  return out.size();
+}
+size_t adh_net_param_count(void* h) { return ((Net*)h)->opt->param_dim(); }
+int adh_net_get_params(void* h, int rank, float* host) { ((Net*)h)->opt->store_params((size_t)rank, host); return AD_OK; }
+int adh_net_set_params(void* h, const float* host) { ((Net*)h)->opt->load_params(host); return AD_OK; }
+// dims of one rank's output strip: N, C, h, W
+void adh_net_output_dims(void* h, int dims[4]) {
+  auto* n = (Net*)h;
+  ActVar o;
+  for (auto& x : n->net.outputs) if (x) { o = x; break; }
+  Shape3D d = o->shape();
+  dims[0] = (int)o->batch_shape(); dims[1] = (int)d.shape[2]; dims[2] = (int)d.shape[1]; dims[3] = (int)d.shape[0];
+}
+// full image, packed NCHW fp32 on the host; starts a new transaction and runs the forward pass
+int adh_net_forward(void* h, const float* image_nchw) {
+  auto* n = (Net*)h;
+  n->txn.reset(new TxnId());
+  n->opt->persist(*n->txn);
+  any rd = const_cast<float*>(image_nchw);
+  for (auto& in : n->net.inputs) {
+    if (!in) continue;
+    VarIdSet v = VarIdSet::Singleton(in->data().val.var());
+    n->net.sink->load_val(*n->txn, v, 0, &rd);   // every rank receives the image (offset 0 each time)
+  }
+  n->net.sink->eval(*n->txn);
+  return AD_OK;
+}
+int adh_net_get_output(void* h, int rank, float* host_strip) {
+  auto* n = (Net*)h;
+  for (auto& o : n->net.outputs) {
+    if ((int)o->rank() != rank) continue;
+    VarIdSet v = VarIdSet::Singleton(o->data().val.var());
+    any w = host_strip;
+    n->net.sink->store_val(*n->txn, v, 0, &w);
+    return AD_OK;
+  }
+  return AD_ERR_BAD_ARG;
+}
+int adh_net_set_output_grad(void* h, int rank, const float* host_strip) {
+  auto* n = (Net*)h;
+  for (auto& o : n->net.outputs) {
+    if ((int)o->rank() != rank) continue;
+    any rd = const_cast<float*>(host_strip);
+    n->net.sink->load_grad(*n->txn, n->net.output_grad_vars[(size_t)rank], 0, &rd);
+    return AD_OK;
+  }
+  return AD_ERR_BAD_ARG;
+}
+int adh_net_backward(void* h) {
+  auto* n = (Net*)h;
+  n->net.sink->backward(*n->txn);
+  return AD_OK;
+}
+// flat gradient of rank's parameters (this rank's strip only, before the allreduce)
+int adh_net_get_param_grads(void* h, int rank, float* host) {
+  auto* n = (Net*)h;
+  GPUContext* g = n->ctx->device_context((size_t)rank).get();
+  GPUMemory<float> tmp(n->opt->param_dim(), g);
+  any w = tmp;
+  n->net.sink->store_grad(*n->txn, n->net.dev_grads[(size_t)rank], 0, &w);
+  GPUConn conn = g->conn();
+  tmp.store_sync(host, n->opt->param_dim(), 0, conn);
+  return AD_OK;
+}
+// gradient w.r.t. the full image as seen by `rank` (non-zero only on its rows)
+int adh_net_get_input_grad(void* h, int rank, float* host_full) {
+  auto* n = (Net*)h;
+  auto& in = n->net.inputs[(size_t)rank];
+  if (!in) return AD_ERR_BAD_ARG;
+  VarIdSet v = VarIdSet::Singleton(in->data().grad.var());
+  any w = host_full;
+  n->net.sink->store_grad(*n->txn, v, 0, &w);
+  return AD_OK;
+}
+// allreduce of the gradients + SGD update on every rank
+int adh_net_sgd_step(void* h) { auto* n = (Net*)h; n->opt->step(*n->txn); return AD_OK; }
+int adh_net_sync(void* h) { ((Net*)h)->ctx->sync(); return AD_OK; }
+int adh_net_status(void* h) {
+  auto* n = (Net*)h;
+  int st = 0;
+  for (size_t r = 0; r < n->ctx->num_ranks(); ++r) if (n->ctx->is_local(r)) { int s = n->ctx->device_context(r)->read_status(); if (s) st = s; }
+  return st;
+}
+size_t adh_net_arena_used(void* h, int rank) { return ((Net*)h)->ctx->device_context((size_t)rank)->arena().used(); }
+
+}  // extern "C"

@@ -1,0 +1,291 @@
+// Builders: every function creates the same operators in the same order on every rank.
+#include <cmath>
+
+#include "arraydiff/zoo.hh"
+
+namespace arraydiff {
+
+static size_t ranks_of(const shared_ptr<Context>& ctx) {
+  auto m = dynamic_cast<MultiGPUContext*>(ctx.get());
+  return m ? m->num_ranks() : 1;
+}
+static GPUContext* gpu_at(const shared_ptr<Context>& ctx, size_t rank) {
+  if (auto m = dynamic_cast<MultiGPUContext*>(ctx.get())) return m->device_context(rank).get();
+  return dynamic_cast<GPUContext*>(ctx.get());
+}
+static bool local_rank(const shared_ptr<Context>& ctx, size_t rank) {
+  auto m = dynamic_cast<MultiGPUContext*>(ctx.get());
+  return m ? m->is_local(rank) : true;
+}
+
+template <typename A>
+typename IOOp<A>::InitFn kaiming_init_gen(size_t fan_in, size_t) {
+  return [fan_in](A* a, std::mt19937_64* rng, shared_ptr<Context>) {
+    std::normal_distribution<float> dist(0.0f, std::sqrt(2.0f / (float)fan_in));
+    vector<float> h(a->flat_size());
+    for (auto& v : h) v = dist(*rng);
+    CUDA_CHECK(cudaMemcpy(a->dptr(), h.data(), h.size() * 4, cudaMemcpyHostToDevice));
+  };
+}
+template <typename A>
+typename IOOp<A>::InitFn zeros_init_gen() {
+  return [](A* a, std::mt19937_64*, shared_ptr<Context>) { CUDA_CHECK(cudaMemset(a->dptr(), 0, a->flat_size() * 4)); };
+}
+template IOOp<GPUArray4D<float>>::InitFn kaiming_init_gen<GPUArray4D<float>>(size_t, size_t);
+template IOOp<GPUArray1D<float>>::InitFn zeros_init_gen<GPUArray1D<float>>();
+
+template <>
+ParamOp<Act> conv2d(Conv2DShape shape, ActVar input, KernelInitFn kernel_init, bool enable_bias, shared_ptr<Context> ctx) {
+  const size_t r = input->rank();
+  const size_t cin = input->shape().shape[2];
+  // Shape4D(kw, kh, c_in, c_out): KCRS in memory (reference src/zoo.cc:102)
+  auto kernel = IOOp<GPUArray4D<float>>::Make(Shape4D(shape.kernel[0], shape.kernel[1], cin, shape.filters), 1, kernel_init, r, ctx);
+  shared_ptr<IOOp<GPUArray1D<float>>> bias;
+  if (enable_bias) bias = IOOp<GPUArray1D<float>>::Make(Shape1D(shape.filters), 1, zeros_init_gen<GPUArray1D<float>>(), r, ctx);
+  kernel->set_name(NameScope::current() + ".kernel");
+  if (bias) bias->set_name(NameScope::current() + ".bias");
+  ParamOp<Act> p;
+  p.op = CudnnConv2DOpF::Make(shape, input, kernel, bias, ctx);
+  p.params.insert(kernel->data().val.var());
+  p.grads.insert(kernel->data().grad.var());
+  if (bias) { p.params.insert(bias->data().val.var()); p.grads.insert(bias->data().grad.var()); }
+  return p;
+}
+
+template <>
+ParallelParamOp<Act> parallel_conv2d(Conv2DShape shape, vector<ActVar> inputs, KernelInitFn kernel_init, bool enable_bias,
+                                     shared_ptr<Context> ctx) {
+  ParallelParamOp<Act> out;
+  for (auto& x : inputs) {   // one op per rank, each with its own parameter variable (reference src/zoo.cc:140-153)
+    auto p = conv2d<Act>(shape, x, kernel_init, enable_bias, ctx);
+    out.ops.push_back(p.op);
+    out.params.push_back(p.params);
+    out.grads.push_back(p.grads);
+  }
+  return out;
+}
+
+template <>
+vector<ActVar> parallel_relu(vector<ActVar> inputs, shared_ptr<Context> ctx) {
+  vector<ActVar> out;
+  for (auto& x : inputs) out.push_back(CudnnActivationOpF::Make(kReluAct, x, ctx));
+  return out;
+}
+template <>
+vector<ActVar> parallel_sum(vector<vector<ActVar>> inputs, shared_ptr<Context> ctx) {
+  vector<ActVar> out;
+  for (size_t r = 0; r < inputs.at(0).size(); ++r) {
+    vector<ActVar> xs;
+    for (auto& branch : inputs) xs.push_back(branch.at(r));
+    out.push_back(SumJoinOpF::Make(xs, ctx));
+  }
+  return out;
+}
+template <>
+ParallelBatchNormParamOp<Act> parallel_batch_norm(size_t channels, shared_ptr<bool> switch_var, vector<ActVar> inputs, bool fuse_relu,
+                                                  shared_ptr<Context> ctx) {
+  ParallelBatchNormParamOp<Act> out;
+  for (auto& x : inputs) {
+    auto parts = CudnnBatchNorm2DOpF::Make(channels, switch_var, x, ctx);
+    if (fuse_relu) parts.op->fuse_relu();
+    out.ops.push_back(parts.op);
+    VarIdSet p, g, bs, fs;
+    p.insert(parts.scale->data().val.var()); p.insert(parts.shift->data().val.var());
+    g.insert(parts.scale->data().grad.var()); g.insert(parts.shift->data().grad.var());
+    bs.insert(parts.batch_mean->data().val.var()); bs.insert(parts.batch_variance->data().val.var());
+    fs.insert(parts.fixed_mean->data().val.var()); fs.insert(parts.fixed_variance->data().val.var());
+    out.params.push_back(p); out.grads.push_back(g); out.batch_stats.push_back(bs); out.fixed_stats.push_back(fs);
+  }
+  return out;
+}
+
+// Collects the per-rank variable sets while a block is assembled.
+struct BlockVars {
+  explicit BlockVars(size_t R) : params(R), grads(R), batch_stats(R), fixed_stats(R) {}
+  void add(const ParallelParamOp<Act>& p) {
+    for (size_t r = 0; r < params.size(); ++r) { params[r].insert_all(p.params[r]); grads[r].insert_all(p.grads[r]); }
+  }
+  void add(const ParallelBatchNormParamOp<Act>& p) {
+    for (size_t r = 0; r < params.size(); ++r) {
+      params[r].insert_all(p.params[r]); grads[r].insert_all(p.grads[r]);
+      batch_stats[r].insert_all(p.batch_stats[r]); fixed_stats[r].insert_all(p.fixed_stats[r]);
+    }
+  }
+  ParallelBatchNormParamOp<Act> finish(vector<ActVar> ops) { return {ops, params, grads, batch_stats, fixed_stats}; }
+  vector<VarIdSet> params, grads, batch_stats, fixed_stats;
+};
+
+// BN -> ReLU, fused into one kernel
+static vector<ActVar> bn_relu(const char* name, size_t channels, shared_ptr<bool> sw, vector<ActVar> in, BlockVars& vars, shared_ptr<Context> ctx) {
+  NameScope scope(name);
+  auto bn = parallel_batch_norm<Act>(channels, sw, in, true, ctx);
+  vars.add(bn);
+  return bn.ops;
+}
+// halo pad -> halo exchange -> conv on the halo-padded strip
+static vector<ActVar> halo_conv(const char* name, Conv2DShape shape, vector<ActVar> in, BlockVars& vars, shared_ptr<Context> ctx) {
+  NameScope scope(name);
+  assert(shape.pad[0] == shape.pad[1]);
+  shape.halo_padded_input = true;
+  auto pad = HaloPad2DOpF::MakeParallel(shape.pad[0], in, ctx);
+  auto exch = HaloExch2DOpF::MakeParallel(shape.pad[0], pad, ctx);
+  const size_t cin = in.at(0)->shape().shape[2];
+  auto conv = parallel_conv2d<Act>(shape, exch, kaiming_init_gen<GPUArray4D<float>>(cin * shape.kernel[0] * shape.kernel[1], shape.filters), false, ctx);
+  vars.add(conv);
+  return conv.ops;
+}
+static vector<ActVar> conv1x1(const char* name, size_t filters, size_t stride, vector<ActVar> in, BlockVars& vars, shared_ptr<Context> ctx) {
+  NameScope scope(name);
+  Conv2DShape s;
+  s.filters = filters; s.kernel = {1, 1}; s.stride = {stride, stride}; s.pad = {0, 0};
+  auto conv = parallel_conv2d<Act>(s, in, kaiming_init_gen<GPUArray4D<float>>(in.at(0)->shape().shape[2], filters), false, ctx);
+  vars.add(conv);
+  return conv.ops;
+}
+
+// BN-ReLU-[pad-exch-conv3x3] x2, identity shortcut   (reference src/zoo.cc:577-652)
+template <>
+ParallelBatchNormParamOp<Act> spatial_parallel_residual_v2_conv2d(Conv2DShape shape, shared_ptr<bool> sw, vector<ActVar> inputs, shared_ptr<Context> ctx) {
+  BlockVars vars(inputs.size());
+  shape.stride = {1, 1};
+  auto a0 = bn_relu("bn0", inputs.at(0)->shape().shape[2], sw, inputs, vars, ctx);
+  auto c1 = halo_conv("conv1", shape, a0, vars, ctx);
+  auto a1 = bn_relu("bn1", shape.filters, sw, c1, vars, ctx);
+  auto c2 = halo_conv("conv2", shape, a1, vars, ctx);
+  return vars.finish(parallel_sum<Act>({inputs, c2}, ctx));
+}
+// same with a strided 1x1 projection shortcut taken after the first BN-ReLU   (reference src/zoo.cc:654-738)
+template <>
+ParallelBatchNormParamOp<Act> spatial_parallel_proj_residual_v2_conv2d(Conv2DShape shape, size_t stride, shared_ptr<bool> sw, vector<ActVar> inputs, shared_ptr<Context> ctx) {
+  BlockVars vars(inputs.size());
+  auto a0 = bn_relu("bn0", inputs.at(0)->shape().shape[2], sw, inputs, vars, ctx);
+  auto proj = conv1x1("proj", shape.filters, stride, a0, vars, ctx);
+  Conv2DShape s1 = shape;
+  s1.stride = {stride, stride};
+  auto c1 = halo_conv("conv1", s1, a0, vars, ctx);
+  auto a1 = bn_relu("bn1", shape.filters, sw, c1, vars, ctx);
+  Conv2DShape s2 = shape;
+  s2.stride = {1, 1};
+  auto c2 = halo_conv("conv2", s2, a1, vars, ctx);
+  return vars.finish(parallel_sum<Act>({proj, c2}, ctx));
+}
+// BN-ReLU-1x1, BN-ReLU-[pad-exch-3x3], BN-ReLU-1x1 (x bottleneck), identity shortcut   (reference src/zoo.cc:740-837)
+template <>
+ParallelBatchNormParamOp<Act> spatial_parallel_bottleneck_residual_v2_conv2d(Conv2DShape shape, size_t bottleneck, shared_ptr<bool> sw, vector<ActVar> inputs, shared_ptr<Context> ctx) {
+  BlockVars vars(inputs.size());
+  assert(inputs.at(0)->shape().shape[2] == bottleneck * shape.filters);   // channels are axis 2
+  shape.stride = {1, 1};
+  auto a0 = bn_relu("bn0", inputs.at(0)->shape().shape[2], sw, inputs, vars, ctx);
+  auto c1 = conv1x1("conv1", shape.filters, 1, a0, vars, ctx);
+  auto a1 = bn_relu("bn1", shape.filters, sw, c1, vars, ctx);
+  auto c2 = halo_conv("conv2", shape, a1, vars, ctx);
+  auto a2 = bn_relu("bn2", shape.filters, sw, c2, vars, ctx);
+  auto c3 = conv1x1("conv3", bottleneck * shape.filters, 1, a2, vars, ctx);
+  return vars.finish(parallel_sum<Act>({inputs, c3}, ctx));
+}
+// bottleneck with a strided 1x1 projection shortcut; the 3x3 carries the stride   (reference src/zoo.cc:839-946,
+// which strides only the projection: the single-GPU twin at :541-542 strides the 3x3 as done here)
+template <>
+ParallelBatchNormParamOp<Act> spatial_parallel_proj_bottleneck_residual_v2_conv2d(Conv2DShape shape, size_t bottleneck, size_t stride, shared_ptr<bool> sw, vector<ActVar> inputs, shared_ptr<Context> ctx) {
+  BlockVars vars(inputs.size());
+  auto a0 = bn_relu("bn0", inputs.at(0)->shape().shape[2], sw, inputs, vars, ctx);
+  auto proj = conv1x1("proj", bottleneck * shape.filters, stride, a0, vars, ctx);
+  auto c1 = conv1x1("conv1", shape.filters, 1, a0, vars, ctx);
+  auto a1 = bn_relu("bn1", shape.filters, sw, c1, vars, ctx);
+  Conv2DShape s2 = shape;
+  s2.stride = {stride, stride};
+  auto c2 = halo_conv("conv2", s2, a1, vars, ctx);
+  auto a2 = bn_relu("bn2", shape.filters, sw, c2, vars, ctx);
+  auto c3 = conv1x1("conv3", bottleneck * shape.filters, 1, a2, vars, ctx);
+  return vars.finish(parallel_sum<Act>({proj, c3}, ctx));
+}
+
+static SpatialParallelNet begin_net(const ConvNetConfig& cfg, shared_ptr<Context> ctx, vector<ActVar>& strips) {
+  SpatialParallelNet net;
+  const size_t R = ranks_of(ctx);
+  net.batch_norm_use_fixed = make_shared<bool>(false);
+  net.dev_params.resize(R); net.dev_grads.resize(R); net.dev_batch_stats.resize(R); net.dev_fixed_stats.resize(R);
+  net.output_grad_vars.resize(R);
+  vector<ActVar> full;
+  for (size_t r = 0; r < R; ++r) {
+    if (!local_rank(ctx, r)) { net.inputs.push_back(nullptr); continue; }
+    auto in = IOOp<Act>::Make(Shape3D(cfg.input_w, cfg.input_h, cfg.input_c), cfg.batch_size, nullptr, r, ctx);
+    net.inputs.push_back(in);
+    net.input_vars.insert(in->data().val.var());
+    full.push_back(in);
+  }
+  // every rank holds the image and cuts out its own rows (reference src/zoo.cc:1522-1523)
+  for (auto& x : full) strips.push_back(make_shared<SpatialScatter2DOpF>(x->rank(), R, x, ctx));
+  (void)gpu_at;
+  return net;
+}
+static void absorb(SpatialParallelNet& net, const vector<ActVar>& ops, const vector<VarIdSet>& p, const vector<VarIdSet>& g,
+                   const vector<VarIdSet>* bs = nullptr, const vector<VarIdSet>* fs = nullptr) {
+  for (size_t i = 0; i < ops.size(); ++i) {
+    const size_t r = ops[i]->rank();
+    net.dev_params[r].insert_all(p[i]); net.dev_grads[r].insert_all(g[i]);
+    if (bs) net.dev_batch_stats[r].insert_all((*bs)[i]);
+    if (fs) net.dev_fixed_stats[r].insert_all((*fs)[i]);
+  }
+}
+static void finish_net(SpatialParallelNet& net, const vector<ActVar>& outs) {
+  net.outputs = outs;
+  vector<shared_ptr<Op>> members(outs.begin(), outs.end());
+  net.sink = make_shared<GroupSinkOp>(members);
+  for (auto& o : outs) net.output_grad_vars[o->rank()].insert(o->data().grad.var());
+}
+
+template <>
+SpatialParallelNet SpatialParallelResNet<float>::MakeConv3x3(const ConvNetConfig& cfg, size_t filters, shared_ptr<Context> ctx) {
+  vector<ActVar> strips;
+  SpatialParallelNet net = begin_net(cfg, ctx, strips);
+  Conv2DShape s;
+  s.filters = filters; s.kernel = {3, 3}; s.pad = {1, 1}; s.halo_padded_input = true;
+  auto pad = HaloPad2DOpF::MakeParallel(1, strips, ctx);
+  auto exch = HaloExch2DOpF::MakeParallel(1, pad, ctx);
+  NameScope scope("conv");
+  auto conv = parallel_conv2d<Act>(s, exch, kaiming_init_gen<GPUArray4D<float>>(cfg.input_c * 9, filters), false, ctx);
+  absorb(net, conv.ops, conv.params, conv.grads);
+  // grads of the input are wanted too in this plumbing case: an IOOp keeps them
+  finish_net(net, conv.ops);
+  return net;
+}
+
+template <>
+SpatialParallelNet SpatialParallelResNet<float>::MakeStemStage1(const ConvNetConfig& cfg, shared_ptr<Context> ctx) {
+  vector<ActVar> strips;
+  SpatialParallelNet net = begin_net(cfg, ctx, strips);
+  auto sw = net.batch_norm_use_fixed;
+  // stem: halo 3, 7x7/2 -> 64
+  Conv2DShape c1;
+  c1.filters = 64; c1.kernel = {7, 7}; c1.stride = {2, 2}; c1.pad = {3, 3}; c1.halo_padded_input = true;
+  auto pad1 = HaloPad2DOpF::MakeParallel(3, strips, ctx);
+  auto exch1 = HaloExch2DOpF::MakeParallel(3, pad1, ctx);
+  ParallelParamOp<Act> conv1;
+  { NameScope scope("stem.conv"); conv1 = parallel_conv2d<Act>(c1, exch1, kaiming_init_gen<GPUArray4D<float>>(cfg.input_c * 49, 64), false, ctx); }
+  absorb(net, conv1.ops, conv1.params, conv1.grads);
+  ParallelBatchNormParamOp<Act> bn1;
+  { NameScope scope("stem.bn"); bn1 = parallel_batch_norm<Act>(64, sw, conv1.ops, true, ctx); }
+  absorb(net, bn1.ops, bn1.params, bn1.grads, &bn1.batch_stats, &bn1.fixed_stats);
+  // 3x3/2 max pool on a halo-1 strip
+  Pool2DShape pool;
+  pool.window = {3, 3}; pool.stride = {2, 2}; pool.pad = {1, 1}; pool.halo_padded_input = true;
+  auto pad2 = HaloPad2DOpF::MakeParallel(1, bn1.ops, ctx);
+  auto exch2 = HaloExch2DOpF::MakeParallel(1, pad2, ctx);
+  auto pooled = CudnnPool2DOpF::MakeParallel(pool, exch2, ctx);
+  // stage 1: bottlenecks 64-64-256
+  Conv2DShape b;
+  b.filters = 64; b.kernel = {3, 3}; b.pad = {1, 1};
+  ParallelBatchNormParamOp<Act> blk;
+  { NameScope scope("block1"); blk = spatial_parallel_proj_bottleneck_residual_v2_conv2d<Act>(b, 4, 1, sw, pooled, ctx); }
+  absorb(net, blk.ops, blk.params, blk.grads, &blk.batch_stats, &blk.fixed_stats);
+  for (int i = 0; i < 2; ++i) {
+    NameScope scope(i == 0 ? "block2" : "block3");
+    blk = spatial_parallel_bottleneck_residual_v2_conv2d<Act>(b, 4, sw, blk.ops, ctx);
+    absorb(net, blk.ops, blk.params, blk.grads, &blk.batch_stats, &blk.fixed_stats);
+  }
+  finish_net(net, blk.ops);
+  return net;
+}
+
+}  // namespace arraydiff

@@ -1,0 +1,151 @@
+"""ctypes view of the C entry points of the C++ host layer (host/src/capi.cc): contexts, nets,
+forward / backward / update with host tensors.  Plumbing for tests and the benchmark."""
+import ctypes as C
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libarraydiff_host.so")
+F32_NCHW, BF16_NHWC = 0, 1
+_lib = None
+
+
+def load():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing -- build it with `python -m arraydiff_cuda_b200.host.build`")
+        from . import abi
+        abi.load()  # the kernel library must be resident first
+        L = C.CDLL(LIB_PATH)
+        vp = C.c_void_p
+        L.adh_context_create.restype = vp
+        L.adh_context_create.argtypes = [C.POINTER(C.c_int), C.c_int, C.c_int, C.c_size_t]
+        L.adh_context_create_distributed.restype = vp
+        L.adh_context_create_distributed.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_size_t]
+        L.adh_context_destroy.argtypes = [vp]
+        L.adh_context_arena_handle.argtypes = [vp, C.c_char_p]
+        L.adh_context_set_peer_handle.argtypes = [vp, C.c_int, C.c_char_p]
+        L.adh_context_set_allreduce_hook.argtypes = [vp, vp, vp]
+        L.adh_context_stream.restype = vp
+        L.adh_context_stream.argtypes = [vp, C.c_int]
+        L.adh_net_create.restype = vp
+        L.adh_net_create.argtypes = [vp, C.c_char_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint64]
+        L.adh_net_destroy.argtypes = [vp]
+        L.adh_net_configure_sgd.argtypes = [vp, C.c_double, C.c_double, C.c_double, C.c_int]
+        L.adh_net_param_manifest.restype = C.c_size_t
+        L.adh_net_param_manifest.argtypes = [vp, C.c_char_p, C.c_size_t]
+        L.adh_net_param_count.restype = C.c_size_t
+        L.adh_net_param_count.argtypes = [vp]
+        for name in ("adh_net_get_params", "adh_net_get_output", "adh_net_set_output_grad", "adh_net_get_param_grads",
+                     "adh_net_get_input_grad"):
+            getattr(L, name).argtypes = [vp, C.c_int, vp]
+        L.adh_net_set_params.argtypes = [vp, vp]
+        L.adh_net_output_dims.argtypes = [vp, C.POINTER(C.c_int)]
+        L.adh_net_forward.argtypes = [vp, vp]
+        for name in ("adh_net_backward", "adh_net_sgd_step", "adh_net_sync", "adh_net_status"):
+            getattr(L, name).argtypes = [vp]
+        L.adh_net_arena_used.restype = C.c_size_t
+        L.adh_net_arena_used.argtypes = [vp, C.c_int]
+        _lib = L
+    return _lib
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+class Context:
+    def __init__(self, devices, mode=F32_NCHW, arena_mb=1024):
+        self.L = load()
+        arr = (C.c_int * len(devices))(*devices)
+        self.h = self.L.adh_context_create(arr, len(devices), mode, arena_mb)
+        self.num_ranks = len(devices)
+
+    def close(self):
+        if self.h:
+            self.L.adh_context_destroy(self.h)
+            self.h = None
+
+
+class Net:
+    """kind: 'conv3x3' or 'stem_stage1'."""
+
+    def __init__(self, ctx, kind, H, W, Cin, batch=1, filters=64, seed=1):
+        self.L, self.ctx = ctx.L, ctx
+        self.h = self.L.adh_net_create(ctx.h, kind.encode(), H, W, Cin, batch, filters, seed)
+        if not self.h:
+            raise ValueError(kind)
+        self.in_shape = (batch, Cin, H, W)
+        d = (C.c_int * 4)()
+        self.L.adh_net_output_dims(self.h, d)
+        self.strip_shape = tuple(d)
+        self.nparam = self.L.adh_net_param_count(self.h)
+
+    def manifest(self):
+        n = self.L.adh_net_param_manifest(self.h, None, 0)
+        buf = C.create_string_buffer(n + 1)
+        self.L.adh_net_param_manifest(self.h, buf, n + 1)
+        out = {}
+        for line in buf.value.decode().splitlines():
+            name, off, size = line.split()
+            out[name] = (int(off), int(size))
+        return out
+
+    def params(self, rank=0):
+        a = np.empty(self.nparam, np.float32)
+        self.L.adh_net_get_params(self.h, rank, _p(a))
+        return a
+
+    def set_params(self, flat):
+        flat = np.ascontiguousarray(flat, np.float32)
+        self.L.adh_net_set_params(self.h, _p(flat))
+
+    def forward(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        assert x.shape == self.in_shape
+        self.L.adh_net_forward(self.h, _p(x))
+
+    def output(self, rank):
+        a = np.empty(self.strip_shape, np.float32)
+        assert self.L.adh_net_get_output(self.h, rank, _p(a)) == 0
+        return a
+
+    def full_output(self):
+        return np.concatenate([self.output(r) for r in range(self.ctx.num_ranks)], axis=2)
+
+    def set_output_grad(self, rank, dy):
+        dy = np.ascontiguousarray(dy, np.float32)
+        assert dy.shape == self.strip_shape
+        assert self.L.adh_net_set_output_grad(self.h, rank, _p(dy)) == 0
+
+    def backward(self):
+        self.L.adh_net_backward(self.h)
+
+    def param_grads(self, rank):
+        a = np.empty(self.nparam, np.float32)
+        self.L.adh_net_get_param_grads(self.h, rank, _p(a))
+        return a
+
+    def input_grad(self, rank):
+        a = np.empty(self.in_shape, np.float32)
+        assert self.L.adh_net_get_input_grad(self.h, rank, _p(a)) == 0
+        return a
+
+    def configure_sgd(self, step_size, momentum, l2=0.0, nesterov=False):
+        self.L.adh_net_configure_sgd(self.h, step_size, momentum, l2, int(nesterov))
+
+    def sgd_step(self):
+        self.L.adh_net_sgd_step(self.h)
+
+    def sync(self):
+        self.L.adh_net_sync(self.h)
+
+    def status(self):
+        return self.L.adh_net_status(self.h)
+
+    def close(self):
+        if self.h:
+            self.L.adh_net_destroy(self.h)
+            self.h = None

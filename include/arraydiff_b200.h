@@ -271,6 +271,17 @@ int ad_add(const ad_tensor4* a, const ad_tensor4* b, const ad_tensor4* y, void* 
  * graph edges (src/op.cc:428-628) and pad/unpad copies between layouts. */
 int ad_convert(const ad_tensor4* src, const ad_tensor4* dst, int32_t accumulate, void* stream);
 
+/*
+ * Patch matrix for first layers whose channel count is too small for the tensor-core path
+ * (the 7x7/2 stem, C_in = 3):  out[(n*P + p)*Q + q][(r*kw + s)*C + c] = x[n, c, p*sh + r*dh, q*sw + s*dw]
+ * as bf16, row pitch ldo >= kh*kw*C; columns beyond kh*kw*C are not written (zero them once).
+ * The convolution then runs as a 1x1 convolution over ldo channels through ad_conv2d_* (the
+ * reference leaves this layer to cuDNN like any other: CudnnConv2DOp, src/op.cc:1577-1599).
+ * x is the tensor as read (halo-padded dims, no implicit padding).
+ */
+int ad_im2col(const ad_tensor4* x, uint32_t kh, uint32_t kw, uint32_t sh, uint32_t sw, uint32_t dh, uint32_t dw,
+              uint32_t P, uint32_t Q, void* out_bf16, uint32_t ldo, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Convolution (cross-correlation), forward / data gradient / filter+bias gradient.
  * Replaces CudnnConv2DOp: cudnnConvolutionForward src/op.cc:1577-1610, BackwardBias :1642-1647,

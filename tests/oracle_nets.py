@@ -1,0 +1,126 @@
+"""CPU reference of the partitioned nets, composed from the oracle's operators (test infrastructure).
+
+Batch norm uses per-strip statistics -- each of the R H-strips normalises with its own mean and
+variance, which is what the reference's spatially parallel graph does (one cudnnBatchNormalization
+call per device, src/op.cc:3988-4003) and what the C++ host layer reproduces."""
+import numpy as np
+
+from oracle import orc
+
+
+def _ident(a):
+    return a
+
+
+def _strips(a, R):
+    h = a.shape[2] // R
+    return [np.ascontiguousarray(a[:, :, r * h:(r + 1) * h]) for r in range(R)]
+
+
+class BnRelu:
+    def __init__(self, gamma, beta, R, q=_ident):
+        self.gamma, self.beta, self.R, self.q = gamma, beta, R, q
+
+    def fwd(self, x):
+        self.x = x
+        outs, self.stats = [], []
+        for s in _strips(x, self.R):
+            y, mean, invstd, _ = orc.bn_fwd_train(s, self.gamma, self.beta, relu=True, omp=True)
+            outs.append(y)
+            self.stats.append((mean, invstd))
+        return self.q(np.concatenate(outs, axis=2))
+
+    def bwd(self, dy):
+        dxs, dg, db = [], 0, 0
+        for s, g, (mean, invstd) in zip(_strips(self.x, self.R), _strips(dy, self.R), self.stats):
+            dx, a, b = orc.bn_bwd(s, g, self.gamma, self.beta, mean, invstd, relu=True, omp=True)
+            dxs.append(dx); dg = dg + a; db = db + b
+        return self.q(np.concatenate(dxs, axis=2)), dg, db
+
+
+class Conv:
+    def __init__(self, w, stride=1, pad=0, q=_ident):
+        self.w, self.s, self.p, self.q = w, (stride, stride), (pad, pad), q
+
+    def fwd(self, x):
+        self.x = x
+        return self.q(orc.conv2d_fprop(x, self.w, None, self.s, (1, 1), self.p, omp=True))
+
+    def bwd(self, dy, need_dx=True):
+        dw = orc.conv2d_wgrad(self.x, dy, self.w.shape, self.s, (1, 1), self.p, omp=True)
+        dx = self.q(orc.conv2d_dgrad(dy, self.w, self.x.shape, self.s, (1, 1), self.p, omp=True)) if need_dx else None
+        return dx, dw
+
+
+class StemStage1:
+    """7x7/2 conv -> BN+ReLU -> 3x3/2 max pool (zero pad) -> proj bottleneck -> 2 bottlenecks (64-64-256)."""
+
+    def __init__(self, P, R, bf16=False):
+        """P: dict name -> array (kernels KCRS, scale/shift vectors) keyed like the host layer's manifest.
+        bf16=True rounds every stored activation and activation gradient to bfloat16, as the
+        tensor-core graph does (arithmetic inside each op stays at oracle precision)."""
+        self.P, self.R = P, R
+        self.q = orc.round_bf16 if bf16 else _ident
+
+    def _bn(self, name):
+        return BnRelu(self.P[name + ".scale"], self.P[name + ".shift"], self.R, self.q)
+
+    def _conv(self, name, stride=1, pad=0):
+        return Conv(self.P[name + ".kernel"], stride, pad, self.q)
+
+    def forward(self, x):
+        L = self.L = {}
+        L["stem.conv"] = self._conv("stem.conv", 2, 3)
+        L["stem.bn"] = self._bn("stem.bn")
+        a = L["stem.bn"].fwd(L["stem.conv"].fwd(x))
+        self.pool_in = np.zeros((a.shape[0], a.shape[1], a.shape[2] + 2, a.shape[3] + 2), np.float32)
+        self.pool_in[:, :, 1:-1, 1:-1] = a
+        t = orc.maxpool2d_fwd(self.pool_in, (3, 3), (2, 2), omp=True)
+        for b in ("block1", "block2", "block3"):
+            L[b + ".bn0"] = self._bn(b + ".bn0")
+            a0 = L[b + ".bn0"].fwd(t)
+            L[b + ".conv1"] = self._conv(b + ".conv1")
+            L[b + ".bn1"] = self._bn(b + ".bn1")
+            a1 = L[b + ".bn1"].fwd(L[b + ".conv1"].fwd(a0))
+            L[b + ".conv2"] = self._conv(b + ".conv2", 1, 1)
+            L[b + ".bn2"] = self._bn(b + ".bn2")
+            a2 = L[b + ".bn2"].fwd(L[b + ".conv2"].fwd(a1))
+            L[b + ".conv3"] = self._conv(b + ".conv3")
+            c3 = L[b + ".conv3"].fwd(a2)
+            if b == "block1":
+                L[b + ".proj"] = self._conv(b + ".proj")
+                t = self.q(L[b + ".proj"].fwd(a0) + c3)
+            else:
+                t = self.q(t + c3)
+        return t
+
+    def backward(self, dy):
+        """Returns dict name -> gradient (same keys as P)."""
+        L, G = self.L, {}
+
+        def bn_b(name, g):
+            dx, dg, db = L[name].bwd(g)
+            G[name + ".scale"], G[name + ".shift"] = dg, db
+            return dx
+
+        def conv_b(name, g, need_dx=True):
+            dx, dw = L[name].bwd(g, need_dx)
+            G[name + ".kernel"] = dw
+            return dx
+
+        g = dy
+        for b in ("block3", "block2", "block1"):
+            d = conv_b(b + ".conv3", g)
+            d = bn_b(b + ".bn2", d)
+            d = conv_b(b + ".conv2", d)
+            d = bn_b(b + ".bn1", d)
+            d = conv_b(b + ".conv1", d)
+            if b == "block1":
+                d = self.q(d + conv_b(b + ".proj", g))      # both branches accumulate into the same bf16 buffer
+                g = bn_b(b + ".bn0", d)
+            else:
+                g = self.q(g + bn_b(b + ".bn0", d))
+        dpool = self.q(orc.maxpool2d_bwd(self.pool_in, g, (3, 3), (2, 2), omp=True)[:, :, 1:-1, 1:-1])
+        d = bn_b("stem.bn", np.ascontiguousarray(dpool))
+        conv_b("stem.conv", d, need_dx=False)
+        return G
