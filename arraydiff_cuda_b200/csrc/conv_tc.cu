@@ -25,6 +25,7 @@
 #include "common.cuh"
 #include "tc_common.cuh"
 
+#include <cstdlib>
 #include <mutex>
 
 namespace adk {
@@ -502,6 +503,18 @@ static int launch_fwd(const CUtensorMap& ma, const CUtensorMap& mb, const FwdPar
   return launch_status();
 }
 
+int conv_tc_row_fwd(const void* act, uint32_t NI, uint32_t IH, uint32_t IW, uint32_t CK, const void* filt, uint32_t OC,
+                    uint32_t kh, uint32_t kw, uint32_t sh, uint32_t sw, uint32_t dh, uint32_t dw, int offy, int offx,
+                    uint32_t OP, uint32_t OQ, void* out, long long out_pitch, long long out_plane, const float* bias,
+                    int relu, int accumulate, int32_t* status, cudaStream_t s);
+
+size_t conv_tc_row_wgrad_scratch(uint32_t NI, uint32_t CI, uint32_t KO, uint32_t kh, uint32_t kw, uint32_t sh, uint32_t sw,
+                                 uint32_t dh, uint32_t dw, uint32_t OP, uint32_t OQ);
+int conv_tc_row_wgrad(const void* x, uint32_t NI, uint32_t IH, uint32_t IW, uint32_t CI, const void* dy, uint32_t KO,
+                      uint32_t kh, uint32_t kw, uint32_t sh, uint32_t sw, uint32_t dh, uint32_t dw, int offy, int offx,
+                      uint32_t OP, uint32_t OQ, float* dwt, int accumulate, void* partial, size_t partial_bytes,
+                      int32_t* status, cudaStream_t s);
+
 // Generic forward-style implicit GEMM launch (fprop, or dgrad expressed as fprop).
 static int run_fwd_gemm(const void* act, uint32_t NI, uint32_t IH, uint32_t IW, uint32_t CK, const void* filt,
                         uint32_t OC, uint32_t kh, uint32_t kw, uint32_t sh, uint32_t sw, uint32_t dh, uint32_t dw,
@@ -509,6 +522,12 @@ static int run_fwd_gemm(const void* act, uint32_t NI, uint32_t IH, uint32_t IW, 
                         long long out_plane, const float* bias, int relu, int accumulate, int32_t* status,
                         cudaStream_t s) {
   if (CK % 64 != 0) return AD_ERR_UNSUPPORTED;
+  if (!getenv("ARRAYDIFF_B200_NO_ROW_KERNEL")) {
+    // 64-channel layers: the row-tile kernel fetches each activation patch once (conv_tc_row.cu)
+    int st = conv_tc_row_fwd(act, NI, IH, IW, CK, filt, OC, kh, kw, sh, sw, dh, dw, offy, offx, OP, OQ, out, out_pitch,
+                             out_plane, bias, relu, accumulate, status, s);
+    if (st != AD_ERR_UNSUPPORTED) return st;
+  }
   FwdParams p{};
   p.NI = NI; p.OP = OP; p.OQ = OQ; p.OC = OC; p.CK = CK;
   p.kh = kh; p.kw = kw; p.sh = sh; p.sw = sw; p.dh = dh; p.dw = dw; p.offy = offy; p.offx = offx;
@@ -591,7 +610,9 @@ size_t conv_tc_scratch_bytes(const ad_conv2d_args* a, int pass) {
     const uint32_t sp = a->N * ((g.P + TH - 1) / TH) * ((g.Q + TW - 1) / TW);
     const uint32_t BN = a->C > 64 ? 128 : 64;
     const uint32_t outer = a->kh * a->kw * ((a->K + 127) / 128) * ((a->C + BN - 1) / BN);
-    return (size_t)wgrad_splits(sp, outer) * wcount * 4 + 16;
+    size_t general = (size_t)wgrad_splits(sp, outer) * wcount * 4 + 16;
+    size_t row = conv_tc_row_wgrad_scratch(a->N, a->C, a->K, a->kh, a->kw, a->stride_h, a->stride_w, a->dil_h, a->dil_w, g.P, g.Q) + 16;
+    return general > row ? general : row;
   }
   return 16;
 }
@@ -639,6 +660,20 @@ int conv_tc_wgrad(const ad_conv2d_args* a, cudaStream_t s) {
   if (a->y_pitch || a->y_plane) return AD_ERR_UNSUPPORTED;
   if (a->C % 64 != 0 || a->K % 8 != 0) return AD_ERR_UNSUPPORTED;
   if (a->scratch_bytes < conv_tc_scratch_bytes(a, 2)) return AD_ERR_SCRATCH;
+  if (!getenv("ARRAYDIFF_B200_NO_ROW_KERNEL")) {
+    // 64-channel layers: one CTA serves all taps from one fetch of x and dy (conv_tc_row.cu)
+    st = conv_tc_row_wgrad(a->x, a->N, a->H, a->W, a->C, a->y, a->K, a->kh, a->kw, a->stride_h, a->stride_w, a->dil_h,
+                           a->dil_w, -(int)a->pad_h, -(int)a->pad_w, g.P, g.Q, (float*)a->dw, a->accumulate,
+                           (char*)a->scratch + 16, a->scratch_bytes - 16, (int32_t*)a->scratch, s);
+    if (st == AD_OK && a->db) {
+      dim3 block(32, 8);
+      bias_grad_nhwc_kernel<<<(a->K + 31) / 32, block, 0, s>>>(a->N, g.P, g.Q, a->K, (long long)g.Q * a->K,
+                                                               (long long)g.P * g.Q * a->K, (const __nv_bfloat16*)a->y,
+                                                               a->db, a->accumulate);
+      count_launch();
+    }
+    if (st != AD_ERR_UNSUPPORTED) return st;
+  }
   WgParams p{};
   p.NI = a->N; p.OP = g.P; p.OQ = g.Q; p.KO = a->K; p.CI = a->C;
   p.kh = a->kh; p.kw = a->kw; p.sh = a->stride_h; p.sw = a->stride_w; p.dh = a->dil_h; p.dw = a->dil_w;

@@ -1,0 +1,600 @@
+// Row-tile variants of the tensor-core convolution kernels for 64-channel layers.
+//
+// With 64 input channels a 3x3 convolution moves 9 shifted copies of every activation patch (and
+// 9 filter tiles) from L2 into shared memory per output tile, and the L2 -> SM fabric, not the
+// tensor pipe or HBM, sets the speed.  Here an output tile is 128 consecutive pixels of ONE output
+// row, so the activation patch it needs is kh rows of 128 + (kw-1)*dil pixels: it is fetched ONCE
+// (one TMA box, the dilated rows picked by the box's element stride) and every filter tap is an
+// MMA whose A descriptor simply starts (r * row_pitch + s * dil) pixel rows further into the same
+// swizzled patch.  The whole filter (taps x 8 KiB) stays resident in shared memory for the
+// lifetime of the CTA.  L2 -> SM traffic per tile drops from taps x 24 KiB to one ~51 KiB patch.
+//
+//   conv_tc_row_fwd_kernel    forward / stride-1 data gradient, CK = 64, OC <= 64
+//   conv_tc_row_wgrad_kernel  filter gradient for C = K = 64... (see below)
+//
+// Same bounded-wait, abort-flag and tensor-memory discipline as conv_tc.cu; no multicast loads.
+#include "common.cuh"
+#include "tc_common.cuh"
+
+#include <cstdlib>
+
+namespace adk {
+namespace tc {
+
+constexpr int kRowThreads = 192;
+constexpr uint32_t kTapBytes = 8192;  // one [64 out ch][64 in ch] filter tap, K-major SW128
+
+struct RowCtl {
+  unsigned long long full[4], empty[4], tfull[2], tempty[2], wbar, stg_full[2], stg_free[2];
+  uint32_t tmem_base;
+  volatile int abort_flag;
+};
+
+struct RowFwdParams {
+  uint32_t NI, OP, OQ, OC;
+  uint32_t kh, kw, dh, dw;
+  int32_t offy, offx;
+  uint32_t tiles_x, pw;        // pw: patch row pitch in pixels (multiple of 8)
+  uint32_t patch_bytes, stages;
+  long long out_pitch, out_plane;
+  __nv_bfloat16* out;
+  const float* bias;
+  int32_t relu, accumulate;
+  int32_t* status;
+  int32_t tma_store;     // epilogue stages the tile in shared memory and stores it with one TMA tile store
+};
+
+constexpr int kMaxDynSmem = 227 * 1024;
+
+// An operand may start any whole number of 128-byte rows into a 1024-byte aligned SWIZZLE_128B
+// region: the tensor core applies the swizzle to absolute shared-memory address bits (bits 4-6 ^=
+// bits 7-9), exactly as TMA did when it wrote the region, so the plain descriptor with the shifted
+// start address (base-offset field left 0) reads the right bytes.  Measured on B200: setting the
+// base-offset field to the start row's phase gives wrong results, leaving it 0 matches the oracle.
+__device__ __forceinline__ uint64_t smem_desc_sw128_at(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return smem_desc_sw128(saddr, lbo_bytes, sbo_bytes);
+}
+
+// KH, KW > 0: filter extent known at compile time, the per-tile MMA sequence is fully unrolled so
+// that the single issuing thread spends a handful of instructions per MMA (with N = 64 an MMA
+// lasts only ~32 cycles, so issue overhead, not the tensor pipe, would otherwise set the pace).
+template <int KH, int KW>
+__global__ void __launch_bounds__(kRowThreads, 1)
+conv_tc_row_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                       const __grid_constant__ CUtensorMap map_o, const RowFwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t taps = p.kh * p.kw;
+  uint8_t* wsm = smem;
+  uint8_t* psm = smem + (size_t)taps * kTapBytes;
+  uint8_t* osm = psm + (size_t)p.stages * p.patch_bytes;          // 2 x 16 KiB output staging (TMA store path)
+  RowCtl* ctl = (RowCtl*)(osm + (p.tma_store ? 2 * 16384 : 0));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t total_tiles = p.NI * p.OP * p.tiles_x;
+  constexpr uint32_t BN = 64, kTmemCols = 128;
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&ctl->full[s]), 1);
+      mbar_init(smem_u32(&ctl->empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&ctl->tfull[a]), 1);
+      mbar_init(smem_u32(&ctl->tempty[a]), 4);
+    }
+    mbar_init(smem_u32(&ctl->wbar), 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&ctl->stg_full[b]), 4);
+      mbar_init(smem_u32(&ctl->stg_free[b]), 1);
+    }
+    ctl->abort_flag = 0;
+    mbar_init_fence();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+    if (p.tma_store) tma_prefetch_desc(&map_o);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  volatile int* abortf = &ctl->abort_flag;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // the filter, once
+      const uint32_t wbar = smem_u32(&ctl->wbar);
+      mbar_expect_tx(wbar, taps * kTapBytes);
+      for (uint32_t t = 0; t < taps; ++t) tma_load_2d(smem_u32(wsm + (size_t)t * kTapBytes), &map_b, wbar, (int)(t * 64), 0);
+      uint32_t stage = 0, phase = 0;
+      for (uint32_t tile = blockIdx.x; tile < total_tiles && !*abortf; tile += gridDim.x) {
+        const uint32_t tx = tile % p.tiles_x, oy = (tile / p.tiles_x) % p.OP, n = tile / (p.tiles_x * p.OP);
+        if (!mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1u, abortf)) break;
+        const uint32_t full = smem_u32(&ctl->full[stage]);
+        mbar_expect_tx(full, p.kh * p.pw * 128u);
+        tma_load_4d(smem_u32(psm + (size_t)stage * p.patch_bytes), &map_a, full, 0, (int)(tx * 128) + p.offx, (int)oy + p.offy, (int)n);
+        if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_bf16(BN, 0, 0);
+      uint32_t stage = 0, phase = 0, it = 0;
+      bool ok = mbar_wait(smem_u32(&ctl->wbar), 0, abortf);
+      for (uint32_t tile = blockIdx.x; ok && tile < total_tiles && !*abortf; tile += gridDim.x, ++it) {
+        const uint32_t acc = it & 1u, acc_phase = (it >> 1) & 1u;
+        if (!mbar_wait(smem_u32(&ctl->tempty[acc]), acc_phase ^ 1u, abortf)) break;
+        if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abortf)) break;
+        tc_fence_after();
+        const uint32_t d = tmem_base + acc * BN;
+        const uint32_t pa = smem_u32(psm + (size_t)stage * p.patch_bytes), wa = smem_u32(wsm);
+        const uint64_t da0 = smem_desc_sw128(pa, 16, 1024), db0 = smem_desc_sw128(wa, 16, 1024);
+        if (KH > 0) {
+#pragma unroll
+          for (int t = 0; t < KH * KW; ++t) {
+            // descriptor address fields count 16-byte units: one pixel row = 8, one filter tap = 512
+            const uint32_t aoff = ((uint32_t)(t / KW) * p.pw + (uint32_t)(t % KW) * p.dw) * 8u;
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+              umma_bf16(d, da0 + aoff + 2 * kk, db0 + (uint32_t)t * 512u + 2 * kk, idesc, (t | kk) ? 1u : 0u);
+          }
+        } else {
+          uint32_t first = 1;
+          for (uint32_t r = 0; r < p.kh; ++r)
+            for (uint32_t s = 0; s < p.kw; ++s) {
+              const uint64_t da = da0 + (r * p.pw + s * p.dw) * 8u, db = db0 + (r * p.kw + s) * 512u;
+#pragma unroll
+              for (uint32_t kk = 0; kk < 4; ++kk) {
+                umma_bf16(d, da + 2 * kk, db + 2 * kk, idesc, first ? 0u : 1u);
+                first = 0;
+              }
+            }
+        }
+        umma_commit(smem_u32(&ctl->empty[stage]));
+        umma_commit(smem_u32(&ctl->tfull[acc]));
+        if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else {
+    const uint32_t q = (uint32_t)warp & 3u;
+    uint32_t it = 0;
+    for (uint32_t tile = blockIdx.x; tile < total_tiles && !*abortf; tile += gridDim.x, ++it) {
+      const uint32_t acc = it & 1u, acc_phase = (it >> 1) & 1u;
+      const uint32_t tx = tile % p.tiles_x, oy = (tile / p.tiles_x) % p.OP, n = tile / (p.tiles_x * p.OP);
+      if (!mbar_wait(smem_u32(&ctl->tfull[acc]), acc_phase, abortf)) break;
+      tc_fence_after();
+      if (p.tma_store) {
+        // Stage the tile as [128 px][64 ch] bf16 in the 128-byte-swizzled layout, then ONE TMA tile store
+        // writes it (coalesced, clipped to the tensor) -- instead of 32 scattered 16-byte stores per
+        // instruction from registers.
+        const uint32_t b = it & 1u;
+        const uint32_t m = q * 32 + lane;
+        uint8_t* stg = osm + (size_t)b * 16384;
+        bool ok = true;
+        if (it >= 2) ok = mbar_wait(smem_u32(&ctl->stg_free[b]), ((it >> 1) - 1u) & 1u, abortf);
+        if (!__all_sync(0xffffffffu, ok)) break;   // leave together: the tensor-memory loads below are warp-wide
+#pragma unroll 1
+        for (uint32_t ch = 0; ch < BN / 32; ++ch) {
+          uint32_t v[32];
+          tmem_ld32(tmem_base + ((q * 32u) << 16) + acc * BN + ch * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const uint32_t cg = ch * 32 + g * 8;
+            float f[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              f[j] = __uint_as_float(v[g * 8 + j]);
+              if (p.bias && cg + j < p.OC) f[j] += p.bias[cg + j];
+              if (p.relu) f[j] = fmaxf(f[j], 0.f);
+            }
+            uint4 pk;
+            __nv_bfloat162* p2 = (__nv_bfloat162*)&pk;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) p2[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+            const uint32_t chunk = (cg >> 3) ^ (m & 7u);
+            *(uint4*)(stg + m * 128u + chunk * 16u) = pk;
+          }
+        }
+        // accumulator drained: hand it back to the MMA warp
+        tc_fence_before();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(smem_u32(&ctl->tempty[acc]));
+          mbar_arrive(smem_u32(&ctl->stg_full[b]));
+        }
+        if (q == 0 && lane == 0) {
+          // on a failed wait the abort flag is up and every warp leaves at the top of its next iteration
+          if (mbar_wait(smem_u32(&ctl->stg_full[b]), (it >> 1) & 1u, abortf)) {
+            asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(&map_o),
+                         "r"(smem_u32(stg)), "r"(0), "r"((int)(tx * 128)), "r"((int)oy), "r"((int)n)
+                         : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            // every store but the newest has finished reading its staging buffer: free the other one
+            asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            if (it >= 1) mbar_arrive(smem_u32(&ctl->stg_free[b ^ 1u]));
+          }
+        }
+        __syncwarp();
+        continue;
+      }
+      const uint32_t ox = tx * 128 + q * 32 + lane;
+      const bool valid = ox < p.OQ;
+      __nv_bfloat16* orow = p.out + (long long)n * p.out_plane + (long long)oy * p.out_pitch + (long long)ox * p.OC;
+#pragma unroll 1
+      for (uint32_t ch = 0; ch < BN / 32; ++ch) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + ((q * 32u) << 16) + acc * BN + ch * 32, v);
+        tmem_ld_wait();
+        const uint32_t c0 = ch * 32;
+        if (valid && c0 < p.OC) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const uint32_t cg = c0 + g * 8;
+            float f[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              f[j] = __uint_as_float(v[g * 8 + j]);
+              if (p.bias && cg + j < p.OC) f[j] += p.bias[cg + j];
+            }
+            if (cg + 8 <= p.OC && (p.OC & 7u) == 0) {
+              if (p.accumulate) {
+                uint4 old = *(const uint4*)(orow + cg);
+                const __nv_bfloat162* o2 = (const __nv_bfloat162*)&old;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  float2 t = __bfloat1622float2(o2[j]);
+                  f[2 * j] += t.x; f[2 * j + 1] += t.y;
+                }
+              }
+              if (p.relu) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = fmaxf(f[j], 0.f);
+              }
+              uint4 pk;
+              __nv_bfloat162* p2 = (__nv_bfloat162*)&pk;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) p2[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+              *(uint4*)(orow + cg) = pk;
+            } else {
+              for (int j = 0; j < 8; ++j)
+                if (cg + j < p.OC) {
+                  float t = f[j];
+                  if (p.accumulate) t += __bfloat162float(orow[cg + j]);
+                  if (p.relu) t = fmaxf(t, 0.f);
+                  orow[cg + j] = __float2bfloat16_rn(t);
+                }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctl->tempty[acc]));
+    }
+    // all tile stores of this thread complete before shared memory is given up
+    if (p.tma_store && q == 0 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abortf) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(500);
+    if (threadIdx.x == 0 && p.status) *p.status = AD_ERR_TIMEOUT;
+  }
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+
+// Returns AD_ERR_UNSUPPORTED when the shape is outside what this variant serves, so that the
+// caller falls back to the general kernel.
+int conv_tc_row_fwd(const void* act, uint32_t NI, uint32_t IH, uint32_t IW, uint32_t CK, const void* filt, uint32_t OC,
+                    uint32_t kh, uint32_t kw, uint32_t sh, uint32_t sw, uint32_t dh, uint32_t dw, int offy, int offx,
+                    uint32_t OP, uint32_t OQ, void* out, long long out_pitch, long long out_plane, const float* bias,
+                    int relu, int accumulate, int32_t* status, cudaStream_t s) {
+  if (sh != 1 || sw != 1 || CK != 64 || OC > 64 || OQ < 96) return AD_ERR_UNSUPPORTED;
+  const uint32_t taps = kh * kw;
+  const uint32_t pw = (128 + (kw - 1) * dw + 7) / 8 * 8;
+  if (pw > 256 || (kh - 1) * dh + 1 > 256 || taps > 16) return AD_ERR_UNSUPPORTED;
+  const uint32_t patch_bytes = kh * pw * 128;
+  const long long op_ = out_pitch ? out_pitch : (long long)OQ * OC, opl_ = out_plane ? out_plane : (long long)OP * OQ * OC;
+  const bool tma_store = !accumulate && (OC & 7u) == 0 && !((uintptr_t)out & 15u) && (op_ % 8) == 0 && (opl_ % 8) == 0;
+  const long long avail = (long long)kMaxDynSmem - 1024 - (long long)sizeof(RowCtl) - (long long)taps * kTapBytes -
+                          (tma_store ? 2 * 16384 : 0);
+  long long stages = avail / patch_bytes;
+  if (stages < 2) return AD_ERR_UNSUPPORTED;
+  if (stages > 4) stages = 4;
+  RowFwdParams p{};
+  p.NI = NI; p.OP = OP; p.OQ = OQ; p.OC = OC;
+  p.kh = kh; p.kw = kw; p.dh = dh; p.dw = dw; p.offy = offy; p.offx = offx;
+  p.tiles_x = (OQ + 127) / 128; p.pw = pw; p.patch_bytes = patch_bytes; p.stages = (uint32_t)stages;
+  p.out_pitch = out_pitch ? out_pitch : (long long)OQ * OC;
+  p.out_plane = out_plane ? out_plane : (long long)OP * OQ * OC;
+  if ((OC & 7u) == 0 && (((uintptr_t)out & 15u) || (p.out_pitch % 8) || (p.out_plane % 8))) return AD_ERR_ALIGN;
+  p.out = (__nv_bfloat16*)out; p.bias = bias; p.relu = relu; p.accumulate = accumulate; p.status = status;
+  p.tma_store = tma_store ? 1 : 0;
+  CUtensorMap ma, mb, mo;
+  {
+    uint64_t dims[4] = {CK, IW, IH, NI};
+    uint64_t str[4] = {0, (uint64_t)CK * 2, (uint64_t)IW * CK * 2, (uint64_t)IH * IW * CK * 2};
+    uint32_t box[4] = {64, pw, (kh - 1) * dh + 1, 1};
+    uint32_t es[4] = {1, 1, dh, 1};
+    int st = make_tmap_bf16(&ma, act, 4, dims, str, box, es);
+    if (st != AD_OK) return st;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)taps * CK, OC};
+    uint64_t str[2] = {0, (uint64_t)taps * CK * 2};
+    uint32_t box[2] = {64, 64};
+    uint32_t es[2] = {1, 1};
+    int st = make_tmap_bf16(&mb, filt, 2, dims, str, box, es);
+    if (st != AD_OK) return st;
+  }
+  mo = ma;
+  if (tma_store) {
+    uint64_t dims[4] = {OC, OQ, OP, NI};
+    uint64_t str[4] = {0, (uint64_t)OC * 2, (uint64_t)p.out_pitch * 2, (uint64_t)p.out_plane * 2};
+    uint32_t box[4] = {64, 128, 1, 1};
+    uint32_t es[4] = {1, 1, 1, 1};
+    int st = make_tmap_bf16(&mo, out, 4, dims, str, box, es);
+    if (st != AD_OK) return st;
+  }
+  const int smem = (int)(taps * kTapBytes + stages * patch_bytes + (tma_store ? 2 * 16384 : 0) + 1024 + sizeof(RowCtl));
+  const uint32_t total = NI * OP * p.tiles_x;
+  const unsigned grid = total < (uint32_t)kNumSMs ? total : kNumSMs;
+  void (*kern)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const RowFwdParams) =
+      (kh == 3 && kw == 3) ? conv_tc_row_fwd_kernel<3, 3> : (kh == 1 && kw == 1) ? conv_tc_row_fwd_kernel<1, 1>
+                                                                                 : conv_tc_row_fwd_kernel<0, 0>;
+  // the attribute is per function and per device; setting it is cheap enough to do per launch
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem) != cudaSuccess) {
+    cudaGetLastError();
+    return AD_ERR_CUDA;
+  }
+  kern<<<grid, kRowThreads, smem, s>>>(ma, mb, mo, p);
+  count_launch();
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- filter gradient, C = 64, K <= 64
+// Per tile (128 consecutive dy pixels of one row): ONE load of the dy tile [128 px][64 k] and ONE
+// load of the x patch [kh rows][pw px][64 c].  Every tap is an MMA over the same two buffers:
+//   D[(tap, c)][k] += sum_px x[px + shift(tap)][c] * dy[px][k]
+// A = x (MN-major, M = 128 = two taps (r, s) and (r+1, s) stacked: the second 64-channel block is
+// one patch row, pw*128 bytes, further on, a multiple of 1024 so both blocks share a swizzle phase),
+// B = dy (MN-major, N = 64).  ceil(kh/2)*kw accumulators of 64 columns live in tensor memory for the
+// whole kernel; each CTA walks its share of the tiles and writes ONE fp32 partial at the end, which
+// wgrad_row_reduce_kernel sums over CTAs in a fixed order.  x and dy are read from DRAM once.
+struct RowWgParams {
+  uint32_t NI, OP, OQ, KO;
+  uint32_t kh, kw, dh, dw;
+  int32_t offy, offx;
+  uint32_t tiles_x, pw, patch_bytes, stage_bytes, stages, naccs;
+  float* partial;   // [grid][naccs][128][64]
+  int32_t* status;
+};
+
+template <int KH, int KW>
+__global__ void __launch_bounds__(kRowThreads, 1)
+conv_tc_row_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_constant__ CUtensorMap map_x,
+                         const RowWgParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  RowCtl* ctl = (RowCtl*)(smem + (size_t)p.stages * p.stage_bytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t total_tiles = p.NI * p.OP * p.tiles_x;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kDyBytes = 16384;
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&ctl->full[s]), 1);
+      mbar_init(smem_u32(&ctl->empty[s]), 1);
+    }
+    mbar_init(smem_u32(&ctl->tfull[0]), 1);
+    ctl->abort_flag = 0;
+    mbar_init_fence();
+    tma_prefetch_desc(&map_dy);
+    tma_prefetch_desc(&map_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  volatile int* abortf = &ctl->abort_flag;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      for (uint32_t tile = blockIdx.x; tile < total_tiles && !*abortf; tile += gridDim.x) {
+        const uint32_t tx = tile % p.tiles_x, oy = (tile / p.tiles_x) % p.OP, n = tile / (p.tiles_x * p.OP);
+        if (!mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1u, abortf)) break;
+        const uint32_t full = smem_u32(&ctl->full[stage]);
+        uint8_t* st = smem + (size_t)stage * p.stage_bytes;
+        mbar_expect_tx(full, kDyBytes + p.kh * p.pw * 128u);
+        tma_load_4d(smem_u32(st), &map_dy, full, 0, (int)(tx * 128), (int)oy, (int)n);
+        tma_load_4d(smem_u32(st + kDyBytes), &map_x, full, 0, (int)(tx * 128) + p.offx, (int)oy + p.offy, (int)n);
+        if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_bf16(64, 1, 1);
+      uint32_t stage = 0, phase = 0, first = 1;
+      bool ok = true;
+      for (uint32_t tile = blockIdx.x; tile < total_tiles && !*abortf; tile += gridDim.x) {
+        if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abortf)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sdy = smem_u32(smem + (size_t)stage * p.stage_bytes), sx = sdy + kDyBytes;
+        const uint64_t db0 = smem_desc_sw128(sdy, 0, 1024);
+        if (KH > 0) {
+#pragma unroll
+          for (int r = 0; r < KH; r += 2)
+#pragma unroll
+            for (int sx_ = 0; sx_ < KW; ++sx_) {
+              const uint32_t acc = (uint32_t)((r / 2) * KW + sx_);
+              const uint32_t a0 = sx + ((uint32_t)r * p.pw + (uint32_t)sx_ * p.dw) * 128u;
+              const uint64_t da0 = smem_desc_sw128(a0, (r + 1 < KH) ? p.pw * 128u : 0u, 1024);
+#pragma unroll
+              for (int ks = 0; ks < 8; ++ks)   // 8 x 16 pixels; 16 rows of 128 B = 128 units of 16 B
+                umma_bf16(tmem_base + acc * 64, da0 + 128u * ks, db0 + 128u * ks, idesc, (first && ks == 0) ? 0u : 1u);
+            }
+        } else {
+          uint32_t acc = 0;
+          for (uint32_t r = 0; r < p.kh; r += 2)
+            for (uint32_t s = 0; s < p.kw; ++s, ++acc) {
+              const uint32_t a0 = sx + (r * p.pw + s * p.dw) * 128u;
+              const uint32_t lbo = (r + 1 < p.kh) ? p.pw * 128u : 0u;   // unpaired tap: both halves read the same rows
+              const uint64_t da0 = smem_desc_sw128(a0, lbo, 1024);
+#pragma unroll
+              for (uint32_t ks = 0; ks < 8; ++ks)
+                umma_bf16(tmem_base + acc * 64, da0 + 128u * ks, db0 + 128u * ks, idesc, (first && ks == 0) ? 0u : 1u);
+            }
+        }
+        first = 0;
+        umma_commit(smem_u32(&ctl->empty[stage]));
+        if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+      }
+      if (ok) umma_commit(smem_u32(&ctl->tfull[0]));
+    }
+  } else {
+    const uint32_t q = (uint32_t)warp & 3u;
+    const uint32_t row = q * 32 + lane;
+    float* out = p.partial + ((size_t)blockIdx.x * p.naccs * 128 + row) * 64;
+    const bool have = blockIdx.x < total_tiles;
+    if (!have) {
+      for (uint32_t a = 0; a < p.naccs; ++a)
+        for (uint32_t c = 0; c < 64; c += 4) *(float4*)(out + (size_t)a * 128 * 64 + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+    } else if (mbar_wait(smem_u32(&ctl->tfull[0]), 0, abortf)) {
+      tc_fence_after();
+#pragma unroll 1
+      for (uint32_t a = 0; a < p.naccs; ++a)
+#pragma unroll 1
+        for (uint32_t ch = 0; ch < 2; ++ch) {
+          uint32_t v[32];
+          tmem_ld32(tmem_base + ((q * 32u) << 16) + a * 64 + ch * 32, v);
+          tmem_ld_wait();
+          float* o = out + (size_t)a * 128 * 64 + ch * 32;
+#pragma unroll
+          for (int g = 0; g < 8; ++g)
+            *(float4*)(o + g * 4) = make_float4(__uint_as_float(v[g * 4]), __uint_as_float(v[g * 4 + 1]),
+                                                __uint_as_float(v[g * 4 + 2]), __uint_as_float(v[g * 4 + 3]));
+        }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abortf) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(500);
+    if (threadIdx.x == 0 && p.status) *p.status = AD_ERR_TIMEOUT;
+  }
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// dw[k][tap][c] (+)= sum over CTAs of partial[cta][acc(tap)][half(tap)*64 + c][k], fixed order.
+__global__ void __launch_bounds__(256) wgrad_row_reduce_kernel(uint32_t nparts, uint32_t naccs, uint32_t KO, uint32_t kh,
+                                                               uint32_t kw, const float* __restrict__ partial, float* dw,
+                                                               int accumulate) {
+  const uint32_t taps = kh * kw;
+  const size_t total = (size_t)KO * taps * 64, nt = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nt) {
+    const uint32_t c = (uint32_t)(i % 64), tap = (uint32_t)((i / 64) % taps), k = (uint32_t)(i / (64 * taps));
+    const uint32_t r = tap / kw, s = tap % kw;
+    const uint32_t acc = (r / 2) * kw + s, row = (r & 1u) * 64 + c;
+    float t = 0.f;
+    for (uint32_t pi = 0; pi < nparts; ++pi) t += partial[(((size_t)pi * naccs + acc) * 128 + row) * 64 + k];
+    dw[i] = accumulate ? dw[i] + t : t;
+  }
+}
+
+static uint32_t row_wgrad_grid(uint32_t NI, uint32_t OP, uint32_t OQ) {
+  const uint32_t total = NI * OP * ((OQ + 127) / 128);
+  return total < (uint32_t)kNumSMs ? total : (uint32_t)kNumSMs;
+}
+static bool row_wgrad_ok(uint32_t CI, uint32_t KO, uint32_t kh, uint32_t kw, uint32_t sh, uint32_t sw, uint32_t dh,
+                         uint32_t dw, uint32_t OQ) {
+  if (sh != 1 || sw != 1 || CI != 64 || KO > 64 || (KO & 7u) || OQ < 96) return false;
+  if (((kh + 1) / 2) * kw > 8) return false;
+  const uint32_t pw = (128 + (kw - 1) * dw + 7) / 8 * 8;
+  return pw <= 256 && (kh - 1) * dh + 1 <= 256;
+}
+size_t conv_tc_row_wgrad_scratch(uint32_t NI, uint32_t CI, uint32_t KO, uint32_t kh, uint32_t kw, uint32_t sh, uint32_t sw,
+                                 uint32_t dh, uint32_t dw, uint32_t OP, uint32_t OQ) {
+  if (!row_wgrad_ok(CI, KO, kh, kw, sh, sw, dh, dw, OQ)) return 0;
+  return (size_t)row_wgrad_grid(NI, OP, OQ) * (((kh + 1) / 2) * kw) * 128 * 64 * 4;
+}
+
+int conv_tc_row_wgrad(const void* x, uint32_t NI, uint32_t IH, uint32_t IW, uint32_t CI, const void* dy, uint32_t KO,
+                      uint32_t kh, uint32_t kw, uint32_t sh, uint32_t sw, uint32_t dh, uint32_t dw, int offy, int offx,
+                      uint32_t OP, uint32_t OQ, float* dwt, int accumulate, void* partial, size_t partial_bytes,
+                      int32_t* status, cudaStream_t s) {
+  if (!row_wgrad_ok(CI, KO, kh, kw, sh, sw, dh, dw, OQ)) return AD_ERR_UNSUPPORTED;
+  RowWgParams p{};
+  p.NI = NI; p.OP = OP; p.OQ = OQ; p.KO = KO;
+  p.kh = kh; p.kw = kw; p.dh = dh; p.dw = dw; p.offy = offy; p.offx = offx;
+  p.tiles_x = (OQ + 127) / 128;
+  p.pw = (128 + (kw - 1) * dw + 7) / 8 * 8;
+  p.patch_bytes = kh * p.pw * 128;
+  p.stage_bytes = 16384 + p.patch_bytes;
+  p.naccs = ((kh + 1) / 2) * kw;
+  long long stages = ((long long)kMaxDynSmem - 1024 - (long long)sizeof(RowCtl)) / p.stage_bytes;
+  if (stages < 2) return AD_ERR_UNSUPPORTED;
+  if (stages > 4) stages = 4;
+  p.stages = (uint32_t)stages;
+  const uint32_t grid = row_wgrad_grid(NI, OP, OQ);
+  if (partial_bytes < (size_t)grid * p.naccs * 128 * 64 * 4) return AD_ERR_SCRATCH;
+  p.partial = (float*)partial;
+  p.status = status;
+  CUtensorMap mdy, mx;
+  {
+    uint64_t dims[4] = {KO, OQ, OP, NI};
+    uint64_t str[4] = {0, (uint64_t)KO * 2, (uint64_t)OQ * KO * 2, (uint64_t)OP * OQ * KO * 2};
+    uint32_t box[4] = {64, 128, 1, 1};
+    uint32_t es[4] = {1, 1, 1, 1};
+    int st = make_tmap_bf16(&mdy, dy, 4, dims, str, box, es);
+    if (st != AD_OK) return st;
+  }
+  {
+    uint64_t dims[4] = {CI, IW, IH, NI};
+    uint64_t str[4] = {0, (uint64_t)CI * 2, (uint64_t)IW * CI * 2, (uint64_t)IH * IW * CI * 2};
+    uint32_t box[4] = {64, p.pw, (kh - 1) * dh + 1, 1};
+    uint32_t es[4] = {1, 1, dh, 1};
+    int st = make_tmap_bf16(&mx, x, 4, dims, str, box, es);
+    if (st != AD_OK) return st;
+  }
+  const int smem = (int)(stages * p.stage_bytes + 1024 + sizeof(RowCtl));
+  void (*kern)(const CUtensorMap, const CUtensorMap, const RowWgParams) =
+      (kh == 3 && kw == 3) ? conv_tc_row_wgrad_kernel<3, 3> : (kh == 1 && kw == 1) ? conv_tc_row_wgrad_kernel<1, 1>
+                                                                                 : conv_tc_row_wgrad_kernel<0, 0>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem) != cudaSuccess) {
+    cudaGetLastError();
+    return AD_ERR_CUDA;
+  }
+  kern<<<grid, kRowThreads, smem, s>>>(mdy, mx, p);
+  count_launch();
+  const size_t wcount = (size_t)KO * kh * kw * 64;
+  wgrad_row_reduce_kernel<<<grid_for(wcount, 256), 256, 0, s>>>(grid, p.naccs, KO, kh, kw, p.partial, dwt, accumulate);
+  count_launch();
+  return launch_status();
+}
+
+}  // namespace tc
+}  // namespace adk
