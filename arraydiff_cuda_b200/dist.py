@@ -73,3 +73,66 @@ class SymmetricArena:
         self._opened = []
         self.bytes = None
         L.ad_device_free(C.c_void_p(self.base))
+
+
+class HaloPlan:
+    """Who talks to whom for one rank of a 1 x R strip grid, and over which flag words.
+
+    Every rank owns four 64-bit flag words at the same arena offset:
+        0 from_prev   set by rank-1 when its rows have landed in my top halo
+        1 from_next   set by rank+1 when its rows have landed in my bottom halo
+        2 grad_prev   set by rank-1 when its halo-gradient rows are final (I may pull them)
+        3 grad_next   set by rank+1 likewise
+    Epochs only grow; nothing is ever reset.  This is the host logic that replaces the epoch
+    rendez-vous of Spatial2DComm::group_end (reference src/spatial.cc:58-70)."""
+    FROM_PREV, FROM_NEXT, GRAD_PREV, GRAD_NEXT = 0, 1, 2, 3
+
+    def __init__(self, rank, world):
+        if not (1 <= world <= 8) or not (0 <= rank < world):
+            raise ValueError("rank/world out of range (1 x R grid, R <= 8)")
+        self.rank, self.world = rank, world
+        self.prev = rank - 1 if rank > 0 else None
+        self.next = rank + 1 if rank + 1 < world else None
+
+    def exchange_signals(self):
+        """(peer rank, flag slot on that peer) pairs this rank sets after pushing its edge rows."""
+        out = []
+        if self.next is not None:
+            out.append((self.next, self.FROM_PREV))
+        if self.prev is not None:
+            out.append((self.prev, self.FROM_NEXT))
+        return out
+
+    def exchange_waits(self):
+        """Own flag slots this rank waits on before reading its halo rows."""
+        return ([self.FROM_PREV] if self.prev is not None else []) + ([self.FROM_NEXT] if self.next is not None else [])
+
+    def reduce_signals(self):
+        out = []
+        if self.next is not None:
+            out.append((self.next, self.GRAD_PREV))
+        if self.prev is not None:
+            out.append((self.prev, self.GRAD_NEXT))
+        return out
+
+    def reduce_waits(self):
+        return ([self.GRAD_PREV] if self.prev is not None else []) + ([self.GRAD_NEXT] if self.next is not None else [])
+
+    def push_rows(self, p, h):
+        """(peer, my first source row, peer's first destination row) for the forward push; rows are
+        indices into the padded strip (height h + 2p)."""
+        out = []
+        if self.next is not None:
+            out.append((self.next, h, 0))
+        if self.prev is not None:
+            out.append((self.prev, p, p + h))
+        return out
+
+    def pull_rows(self, p, h):
+        """(peer, peer's first halo row, my first interior row) for the backward accumulate."""
+        out = []
+        if self.next is not None:
+            out.append((self.next, 0, h))
+        if self.prev is not None:
+            out.append((self.prev, p + h, p))
+        return out

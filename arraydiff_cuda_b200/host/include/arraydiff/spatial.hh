@@ -65,7 +65,8 @@ private:
               Spatial2DTensorFormat f, Spatial2DDataType t);
   MultiGPUContext* ctx_;
   cudaEvent_t ready_;     // in-process: "my buffer is ready for my neighbours" (recorded by halo_*)
-  uint64_t* flags_;       // between processes: 4 flag words in my arena (from_prev, from_next, grad_prev, grad_next)
+  uint64_t* flags_;       // between processes: flag words in my arena: 0 from_prev, 1 from_next, 2 grad_prev,
+                          // 3 grad_next, 4 next_ready, 5 prev_ready
   uint32_t* counter_;     // block ticket counter for the publishing kernel
   bool in_group_;
 };

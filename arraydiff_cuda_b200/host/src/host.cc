@@ -203,6 +203,11 @@ void Spatial2DComm::record(Spatial2DOperation op, void* buf, uint32_t p, uint32_
   if (!ctx_->distributed()) {
     // "my buffer is as my neighbours may now read it"
     CUDA_CHECK(cudaEventRecord(ready_, conn.stream()));
+  } else if (op == SPATIAL2D_OP_HXEXCH) {
+    // my padded buffer exists, its pad cells are zeroed and its interior is written: the neighbours
+    // may now push into my halo rows (words 4 / 5: "next is ready" / "prev is ready")
+    if (rank > 0) AD_CHECK(ad_flag_signal((uint64_t*)ctx_->peer_ptr(flags_ + 4, rank, rank - 1), epoch, conn.stream()));
+    if (rank + 1 < num_ranks) AD_CHECK(ad_flag_signal((uint64_t*)ctx_->peer_ptr(flags_ + 5, rank, rank + 1), epoch, conn.stream()));
   } else if (op == SPATIAL2D_OP_HXREDUCE) {
     // my halo-gradient rows are final: tell the neighbours that will pull them
     if (rank + 1 < num_ranks) AD_CHECK(ad_flag_signal((uint64_t*)ctx_->peer_ptr(flags_ + 2, rank, rank + 1), epoch, conn.stream()));
@@ -260,6 +265,8 @@ void Spatial2DComm::group_end(GPUConn& conn) {
     if (rank > 0) a.signal_flags[rank - 1] = (uint64_t*)ctx_->peer_ptr(flags_ + 1, rank, rank - 1);
     a.epoch = arg.epoch;
     a.block_counter = counter_;
+    if (rank + 1 < num_ranks) AD_CHECK(ad_flag_wait(flags_ + 4, arg.epoch, kTimeoutNs, g->status_word(), s));
+    if (rank > 0) AD_CHECK(ad_flag_wait(flags_ + 5, arg.epoch, kTimeoutNs, g->status_word(), s));
     AD_CHECK(ad_halo_exchange(&a, s));
     if (rank > 0) AD_CHECK(ad_flag_wait(flags_ + 0, arg.epoch, kTimeoutNs, g->status_word(), s));
     if (rank + 1 < num_ranks) AD_CHECK(ad_flag_wait(flags_ + 1, arg.epoch, kTimeoutNs, g->status_word(), s));

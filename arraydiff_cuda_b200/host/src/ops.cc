@@ -15,6 +15,12 @@ static GPUContext* gpu_of(const shared_ptr<Context>& ctx, size_t rank) {
   assert(g);
   return g;
 }
+// In a one-process-per-GPU run the per-rank lists hold only the local rank, so the grid size comes
+// from the context, not from the list length.
+static size_t num_ranks_of(const shared_ptr<Context>& ctx, size_t fallback) {
+  if (auto m = dynamic_cast<MultiGPUContext*>(ctx.get())) return m->num_ranks();
+  return fallback;
+}
 GPUContext* ActOp::gpu() { return gpu_of(ctx_, rank_); }
 MultiGPUContext* ActOp::mgpu() { return dynamic_cast<MultiGPUContext*>(ctx_.get()); }
 
@@ -200,7 +206,7 @@ template class IOOp<Act>;
 // ------------------------------------------------------------------ scatter / gather
 vector<ActVar> SpatialScatter2DOpF::MakeParallel(vector<ActVar> inputs, shared_ptr<Context> ctx) {
   vector<ActVar> out;
-  for (size_t r = 0; r < inputs.size(); ++r) out.push_back(make_shared<SpatialScatter2DOpF>(r, inputs.size(), inputs[r], ctx));
+  for (size_t r = 0; r < inputs.size(); ++r) out.push_back(make_shared<SpatialScatter2DOpF>(inputs[r]->rank(), num_ranks_of(ctx, inputs.size()), inputs[r], ctx));
   return out;
 }
 SpatialScatter2DOpF::SpatialScatter2DOpF(size_t rank, size_t num_ranks, ActVar x, shared_ptr<Context> ctx)
@@ -230,7 +236,7 @@ void SpatialScatter2DOpF::_backward(TxnId txn) {
 
 vector<ActVar> SpatialGather2DOpF::MakeParallel(vector<ActVar> inputs, shared_ptr<Context> ctx) {
   vector<ActVar> out;
-  for (size_t r = 0; r < inputs.size(); ++r) out.push_back(make_shared<SpatialGather2DOpF>(r, inputs.size(), inputs[r], ctx));
+  for (size_t r = 0; r < inputs.size(); ++r) out.push_back(make_shared<SpatialGather2DOpF>(inputs[r]->rank(), num_ranks_of(ctx, inputs.size()), inputs[r], ctx));
   return out;
 }
 SpatialGather2DOpF::SpatialGather2DOpF(size_t rank, size_t num_ranks, ActVar x, shared_ptr<Context> ctx)
@@ -261,7 +267,7 @@ void SpatialGather2DOpF::_backward(TxnId txn) {
 // ------------------------------------------------------------------ halo pad / unpad / repad
 vector<ActVar> HaloPad2DOpF::MakeParallel(size_t halo_pad, vector<ActVar> inputs, shared_ptr<Context> ctx) {
   vector<ActVar> out;
-  for (size_t r = 0; r < inputs.size(); ++r) out.push_back(make_shared<HaloPad2DOpF>(halo_pad, r, inputs[r], ctx));
+  for (size_t r = 0; r < inputs.size(); ++r) out.push_back(make_shared<HaloPad2DOpF>(halo_pad, inputs[r]->rank(), inputs[r], ctx));
   return out;
 }
 HaloPad2DOpF::HaloPad2DOpF(size_t halo_pad, size_t rank, ActVar x, shared_ptr<Context> ctx) : ActOp(rank, ctx), x_(x), pad_(halo_pad) {
@@ -288,7 +294,7 @@ void HaloPad2DOpF::_backward(TxnId txn) {
 
 vector<ActVar> HaloUnpad2DOpF::MakeParallel(size_t halo_pad, vector<ActVar> inputs, shared_ptr<Context> ctx) {
   vector<ActVar> out;
-  for (size_t r = 0; r < inputs.size(); ++r) out.push_back(make_shared<HaloUnpad2DOpF>(halo_pad, r, inputs[r], ctx));
+  for (size_t r = 0; r < inputs.size(); ++r) out.push_back(make_shared<HaloUnpad2DOpF>(halo_pad, inputs[r]->rank(), inputs[r], ctx));
   return out;
 }
 HaloUnpad2DOpF::HaloUnpad2DOpF(size_t halo_pad, size_t rank, ActVar x, shared_ptr<Context> ctx) : ActOp(rank, ctx), x_(x), pad_(halo_pad) {
@@ -311,7 +317,7 @@ void HaloUnpad2DOpF::_backward(TxnId txn) {
 
 vector<ActVar> HaloRepad2DOpF::MakeParallel(size_t src_pad, size_t dst_pad, vector<ActVar> inputs, shared_ptr<Context> ctx) {
   vector<ActVar> out;
-  for (size_t r = 0; r < inputs.size(); ++r) out.push_back(make_shared<HaloRepad2DOpF>(src_pad, dst_pad, r, inputs[r], ctx));
+  for (size_t r = 0; r < inputs.size(); ++r) out.push_back(make_shared<HaloRepad2DOpF>(src_pad, dst_pad, inputs[r]->rank(), inputs[r], ctx));
   return out;
 }
 HaloRepad2DOpF::HaloRepad2DOpF(size_t src_pad, size_t dst_pad, size_t rank, ActVar x, shared_ptr<Context> ctx)

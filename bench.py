@@ -191,10 +191,9 @@ class Step:
         xp, gp, fp = self.arena.peers(self.x_off), self.arena.peers(self.gx_off), self.arena.peers(self.flags_off)
         for r in range(world):
             self.hx.bufs[r], self.hg.bufs[r] = xp[r], gp[r]
-        if rank + 1 < world:
-            self.hx.signal_flags[rank + 1] = fp[rank + 1] + 0      # its "from_prev"
-        if rank > 0:
-            self.hx.signal_flags[rank - 1] = fp[rank - 1] + 8      # its "from_next"
+        self.plan = addist.HaloPlan(rank, world)
+        for peer, slot in self.plan.exchange_signals():
+            self.hx.signal_flags[peer] = fp[peer] + 8 * slot
         self.hx.block_counter = self.counter.data_ptr()
         self.fp = fp
         # pinned host copies for the end-to-end variant
@@ -226,26 +225,20 @@ class Step:
         if R > 1:
             self.hx.epoch = ep
             abi.check(L.ad_halo_exchange(C.byref(self.hx), s), "halo exchange")
-            if r > 0:
-                self._wait(0, ep)
-            if r + 1 < R:
-                self._wait(1, ep)
+            for slot in self.plan.exchange_waits():
+                self._wait(slot, ep)
         a.y, a.accumulate = self.y.data_ptr(), 0
         abi.check(L.ad_conv2d_fprop(C.byref(a), s), "fprop")
         # backward: data gradient over the whole padded strip, filter gradient, halo-gradient accumulate-back
         a.y, a.dx, a.dw = self.dy.data_ptr(), self.gx.data_ptr(), self.dw.data_ptr()
         abi.check(L.ad_conv2d_dgrad(C.byref(a), s), "dgrad")
         if R > 1:
-            if r + 1 < R:
-                self._signal(r + 1, 2, ep)
-            if r > 0:
-                self._signal(r - 1, 3, ep)
+            for peer, slot in self.plan.reduce_signals():
+                self._signal(peer, slot, ep)
         abi.check(L.ad_conv2d_wgrad(C.byref(a), s), "wgrad")
         if R > 1:
-            if r > 0:
-                self._wait(2, ep)
-            if r + 1 < R:
-                self._wait(3, ep)
+            for slot in self.plan.reduce_waits():
+                self._wait(slot, ep)
             abi.check(L.ad_halo_reduce(C.byref(self.hg), s), "halo reduce")
             import torch.distributed as dist
             dist.all_reduce(self.dw)       # filter-gradient allreduce over NCCL / NVLink

@@ -1,0 +1,139 @@
+"""One rank of the multi-GPU tests (launched by tests/test_gpu_multi.py through torch.distributed.run).
+Checks, with one process per GPU and peers mapped through CUDA IPC:
+  1. halo push with release flags + bounded waits, and the pull-accumulate, bit-exact vs the oracle;
+  2. the C++ host layer in distributed mode: partitioned 3x3 conv forward / backward / SGD step with
+     the filter-gradient allreduce over NCCL, vs the unpartitioned oracle."""
+import ctypes as C
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+from arraydiff_cuda_b200 import abi, hostlib  # noqa: E402
+from arraydiff_cuda_b200.dist import HaloPlan, SymmetricArena, _Raw  # noqa: E402
+from oracle import orc  # noqa: E402
+from tests import helpers as H  # noqa: E402
+
+
+def halo_part(rank, world):
+    L = abi.load()
+    p, W, h, Cc, N = 3, 50, 8, 5, 2
+    full = H.uniform(500, (N, Cc, h * world, W))
+    strips = H.split_strips(full, world, p)
+    want = H.expected_strips_after_exchange(full, world, p)[rank]
+    arena = SymmetricArena(8 << 20, rank, world)
+    buf, off = arena.alloc(strips[rank].shape, torch.float32)
+    gbuf, goff = arena.alloc(strips[rank].shape, torch.float32)
+    flags, foff = arena.alloc((8,), torch.int64)
+    buf.copy_(torch.from_numpy(strips[rank]))
+    allg = [H.uniform(600 + r, strips[r].shape) for r in range(world)]
+    gbuf.copy_(torch.from_numpy(allg[rank]))
+    counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    dist.barrier()
+    plan = HaloPlan(rank, world)
+    s = H.stream()
+    a = H.halo_args(arena.peers(off), abi.AD_F32, abi.AD_NCHW, p, W, h, Cc, N, rank_first=rank, rank_count=1, push=1)
+    fp = arena.peers(foff)
+    for peer, slot in plan.exchange_signals():
+        a.signal_flags[peer] = fp[peer] + 8 * slot
+    a.epoch, a.block_counter = 1, counter.data_ptr()
+    abi.check(L.ad_halo_exchange(C.byref(a), s))
+    for slot in plan.exchange_waits():
+        abi.check(L.ad_flag_wait(C.c_void_p(flags.data_ptr() + 8 * slot), 1, 2_000_000_000, H.ptr(status), s))
+    torch.cuda.synchronize()
+    assert status.item() == 0, "flag wait timed out"
+    assert np.array_equal(buf.cpu().numpy(), want), "halo exchange mismatch"
+    # backward: signal, wait, pull-accumulate
+    for peer, slot in plan.reduce_signals():
+        abi.check(L.ad_flag_signal(C.c_void_p(fp[peer] + 8 * slot), 1, s))
+    for slot in plan.reduce_waits():
+        abi.check(L.ad_flag_wait(C.c_void_p(flags.data_ptr() + 8 * slot), 1, 2_000_000_000, H.ptr(status), s))
+    g = H.halo_args(arena.peers(goff), abi.AD_F32, abi.AD_NCHW, p, W, h, Cc, N, rank_first=rank, rank_count=1)
+    abi.check(L.ad_halo_reduce(C.byref(g), s))
+    torch.cuda.synchronize()
+    wantg = [x.copy() for x in allg]
+    orc.halo_reduce(wantg, orc.NCHW, p, W, h, Cc, N)
+    assert status.item() == 0
+    assert np.array_equal(gbuf.cpu().numpy(), wantg[rank]), "halo reduce mismatch"
+    dist.barrier()
+    arena.close()
+
+
+_keep = []
+
+
+def host_part(rank, world, local):
+    Lh = hostlib.load()
+    ctxh = Lh.adh_context_create_distributed(rank, world, local, hostlib.F32_NCHW, 256)
+    # exchange arena handles
+    hb = C.create_string_buffer(64)
+    assert Lh.adh_context_arena_handle(ctxh, hb) == 0
+    mine = torch.from_numpy(np.frombuffer(hb.raw, dtype=np.uint8).copy()).cuda()
+    allh = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(allh, mine)
+    for r in range(world):
+        if r != rank:
+            assert Lh.adh_context_set_peer_handle(ctxh, r, bytes(allh[r].cpu().numpy().tobytes())) == 0
+    # filter-gradient allreduce over NCCL on the host layer's own stream
+    HOOK = C.CFUNCTYPE(None, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p)
+
+    def allreduce(buf, count, stream, user):
+        t = torch.as_tensor(_Raw(buf, count * 4), device="cuda").view(torch.float32)
+        with torch.cuda.stream(torch.cuda.ExternalStream(stream)):
+            dist.all_reduce(t)
+
+    hook = HOOK(allreduce)
+    _keep.append(hook)
+    Lh.adh_context_set_allreduce_hook(ctxh, C.cast(hook, C.c_void_p), None)
+
+    class Ctx:  # minimal stand-in for hostlib.Context around the distributed handle
+        pass
+    ctx = Ctx()
+    ctx.L, ctx.h, ctx.num_ranks = Lh, ctxh, world
+    N, Cc, K, Hh, W = 1, 64, 64, 64, 64
+    net = hostlib.Net(ctx, "conv3x3", Hh, W, Cc, N, K, seed=3)
+    x = H.uniform(100, (N, Cc, Hh, W))
+    w = H.normal(101, (K, Cc, 3, 3), float(np.sqrt(2.0 / (9 * 64))))
+    dy = H.uniform(102, (N, K, Hh, W))
+    net.set_params(w.reshape(-1))
+    net.configure_sgd(0.1, 0.9, l2=0.0, nesterov=False)
+    h = Hh // world
+    net.forward(x)
+    y = net.output(rank)
+    y_w = orc.conv2d_fprop(x, w, None, pad=(1, 1), omp=True)
+    assert H.max_rel(y, y_w[:, :, rank * h:(rank + 1) * h]) < 1e-5, "partitioned forward mismatch"
+    net.set_output_grad(rank, dy[:, :, rank * h:(rank + 1) * h])
+    net.backward()
+    dx = net.input_grad(rank)
+    dx_w = orc.conv2d_dgrad(dy, w, x.shape, pad=(1, 1), omp=True)
+    assert H.max_rel(dx[:, :, rank * h:(rank + 1) * h], dx_w[:, :, rank * h:(rank + 1) * h]) < 1e-5, "dgrad mismatch"
+    net.sgd_step()
+    net.sync()
+    assert net.status() == 0
+    dw_w = orc.conv2d_wgrad(x, dy, w.shape, pad=(1, 1), omp=True)
+    theta, g, m = w.reshape(-1).copy(), dw_w.reshape(-1).copy(), np.zeros(w.size, np.float32)
+    orc.sgd_step(theta, g, m, 0.0, 0.9, 0.1, 0.1, 0)
+    assert H.max_rel(net.params(rank), theta) < 1e-5, "update after allreduce mismatch"
+    dist.barrier()
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    halo_part(rank, world)
+    host_part(rank, world, local)
+    if rank == 0:
+        print("MULTI_OK", world)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
