@@ -43,6 +43,7 @@ class Conv2dArgs(C.Structure):
         ("y_pitch", i64), ("y_plane", i64),
         ("dx", vp), ("dw", vp), ("db", vp),
         ("scratch", vp), ("scratch_bytes", sz),
+        ("out_row_begin", u32), ("out_row_count", u32),
     ]
 
 

@@ -155,6 +155,7 @@ int conv_direct_fprop(const ad_conv2d_args* a, cudaStream_t s) {
   int st = geometry(a, g);
   if (st != AD_OK) return st;
   if (!a->x || !a->w || !a->y) return AD_ERR_BAD_ARG;
+  if (a->out_row_count) return AD_ERR_UNSUPPORTED;   // row ranges: tensor-core path only
   const size_t total = (size_t)g.N * g.K * g.P * g.Q;
   conv_fprop_f32<<<grid_for(total, 256, 16), 256, 0, s>>>(g, (const float*)a->x, (const float*)a->w, a->bias, (float*)a->y);
   count_launch();

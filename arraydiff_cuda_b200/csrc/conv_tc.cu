@@ -626,9 +626,19 @@ int conv_tc_fprop(const ad_conv2d_args* a, cudaStream_t s) {
     // Implicit padding is served by TMA's out-of-bounds zero fill (negative start coordinates).
   }
   int32_t* status = (a->scratch && a->scratch_bytes >= 16) ? (int32_t*)a->scratch : nullptr;
+  // A row range is the same problem with fewer output rows: shift the input row offset and the
+  // output pointer, keep the pitches of the full tensor.
+  uint32_t q0 = 0, nq = g.P;
+  if (a->out_row_count) {
+    if ((unsigned long long)a->out_row_begin + a->out_row_count > g.P) return AD_ERR_BAD_ARG;
+    q0 = a->out_row_begin; nq = a->out_row_count;
+  }
+  const long long pitch = a->y_pitch ? a->y_pitch : (long long)g.Q * a->K;
+  const long long plane = a->y_plane ? a->y_plane : (long long)g.P * g.Q * a->K;
+  __nv_bfloat16* out = (__nv_bfloat16*)a->y + (long long)q0 * pitch;
   return run_fwd_gemm(a->x, a->N, a->H, a->W, a->C, a->w, a->K, a->kh, a->kw, a->stride_h, a->stride_w, a->dil_h,
-                      a->dil_w, -(int)a->pad_h, -(int)a->pad_w, g.P, g.Q, a->y, a->y_pitch, a->y_plane, a->bias, a->relu,
-                      0, status, s);
+                      a->dil_w, -(int)a->pad_h + (int)(q0 * a->stride_h), -(int)a->pad_w, nq, g.Q, out, pitch, plane, a->bias,
+                      a->relu, 0, status, s);
 }
 
 int conv_tc_dgrad(const ad_conv2d_args* a, cudaStream_t s) {

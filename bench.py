@@ -191,6 +191,7 @@ class Step:
         xp, gp, fp = self.arena.peers(self.x_off), self.arena.peers(self.gx_off), self.arena.peers(self.flags_off)
         for r in range(world):
             self.hx.bufs[r], self.hg.bufs[r] = xp[r], gp[r]
+        self.side = torch.cuda.Stream()
         self.plan = addist.HaloPlan(rank, world)
         for peer, slot in self.plan.exchange_signals():
             self.hx.signal_flags[peer] = fp[peer] + 8 * slot
@@ -221,27 +222,49 @@ class Step:
         if e2e:
             self.x.copy_(self.hx_host, non_blocking=True)
             self.dy.copy_(self.dy_host, non_blocking=True)
-        # forward: push my edge rows into the neighbours' halo rows, wait for theirs, convolve
-        if R > 1:
-            self.hx.epoch = ep
-            abi.check(L.ad_halo_exchange(C.byref(self.hx), s), "halo exchange")
-            for slot in self.plan.exchange_waits():
-                self._wait(slot, ep)
+        # forward: push my edge rows into the neighbours' halo rows on a side stream and wait there for
+        # theirs, while the main stream already convolves the interior rows; the PAD boundary rows at
+        # either end follow once the halo has landed
         a.y, a.accumulate = self.y.data_ptr(), 0
-        abi.check(L.ad_conv2d_fprop(C.byref(a), s), "fprop")
+        if R > 1:
+            main = self.torch.cuda.current_stream()
+            self.side.wait_stream(main)
+            with self.torch.cuda.stream(self.side):
+                s2 = self._s()
+                self.hx.epoch = ep
+                abi.check(L.ad_halo_exchange(C.byref(self.hx), s2), "halo exchange")
+                for slot in self.plan.exchange_waits():
+                    self._wait(slot, ep)
+                landed = self.side.record_event()
+            a.out_row_begin, a.out_row_count = PAD, self.h - 2 * PAD
+            abi.check(L.ad_conv2d_fprop(C.byref(a), s), "fprop interior")
+            main.wait_event(landed)
+            for q0 in (0, self.h - PAD):
+                a.out_row_begin, a.out_row_count = q0, PAD
+                abi.check(L.ad_conv2d_fprop(C.byref(a), s), "fprop boundary")
+            a.out_row_begin, a.out_row_count = 0, 0
+        else:
+            abi.check(L.ad_conv2d_fprop(C.byref(a), s), "fprop")
         # backward: data gradient over the whole padded strip, filter gradient, halo-gradient accumulate-back
         a.y, a.dx, a.dw = self.dy.data_ptr(), self.gx.data_ptr(), self.dw.data_ptr()
         abi.check(L.ad_conv2d_dgrad(C.byref(a), s), "dgrad")
         if R > 1:
-            for peer, slot in self.plan.reduce_signals():
-                self._signal(peer, slot, ep)
+            # the halo-gradient accumulate-back (signal, wait for the neighbours, pull + add) runs on the
+            # side stream underneath the filter gradient
+            main = self.torch.cuda.current_stream()
+            self.side.wait_stream(main)
+            with self.torch.cuda.stream(self.side):
+                s2 = self._s()
+                for peer, slot in self.plan.reduce_signals():
+                    self._signal(peer, slot, ep)
+                for slot in self.plan.reduce_waits():
+                    self._wait(slot, ep)
+                abi.check(L.ad_halo_reduce(C.byref(self.hg), s2), "halo reduce")
         abi.check(L.ad_conv2d_wgrad(C.byref(a), s), "wgrad")
         if R > 1:
-            for slot in self.plan.reduce_waits():
-                self._wait(slot, ep)
-            abi.check(L.ad_halo_reduce(C.byref(self.hg), s), "halo reduce")
             import torch.distributed as dist
             dist.all_reduce(self.dw)       # filter-gradient allreduce over NCCL / NVLink
+            self.torch.cuda.current_stream().wait_stream(self.side)
         if e2e:
             self.dw_host.copy_(self.dw, non_blocking=True)
 

@@ -317,6 +317,11 @@ typedef struct {
   float* db;               /* [K] or NULL */
   void* scratch;           /* see ad_conv2d_scratch_bytes */
   size_t scratch_bytes;
+  /* fprop on the tensor-core path only: compute output rows [out_row_begin, out_row_begin + out_row_count)
+   * and leave the others untouched (0, 0 = all rows).  Lets a caller convolve the interior rows of a
+   * strip while its halo rows are still in flight, and the p boundary rows afterwards -- the overlap
+   * the reference forgoes by synchronising every device around each exchange (src/op.cc:2976, :3001). */
+  uint32_t out_row_begin, out_row_count;
 } ad_conv2d_args;
 
 size_t ad_conv2d_scratch_bytes(const ad_conv2d_args* a, int32_t pass /* 0 fprop, 1 dgrad, 2 wgrad */);

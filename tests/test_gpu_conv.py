@@ -189,3 +189,38 @@ def test_conv_rejects_bad_arguments():
     a = conv_args(abi.AD_F32, abi.AD_NCHW, (1, 4, 2, 2), 4, 3, 1, 1, 0)
     assert L.ad_conv2d_fprop(C.byref(a), H.stream()) == abi.AD_ERR_BAD_ARG       # kernel larger than input
     assert L.ad_conv2d_fprop(None, H.stream()) == abi.AD_ERR_BAD_ARG
+
+
+@pytest.mark.parametrize("case", [(2, 64, 22, 140, 64, 3, 1, 3, 0), (1, 128, 20, 24, 128, 3, 1, 1, 0), (1, 64, 34, 34, 128, 3, 2, 1, 0)])
+def test_conv_tc_fprop_row_ranges_compose(case):
+    """Interior rows first, boundary rows later (what the halo overlap does) == one full call, bit for bit,
+    and rows outside a range are not touched."""
+    import torch
+    N, Cc, Hh, W, K, k, s, d, pd = case
+    x, w = _tc_setup(case)
+    L = abi.lib()
+    a = conv_args(abi.AD_BF16, abi.AD_NHWC, x.shape, K, k, s, d, pd)
+    dx_ = H.dev_bf16(orc.nchw_to_nhwc(x))
+    dw_ = H.dev_bf16(np.ascontiguousarray(np.transpose(w, (0, 2, 3, 1))))
+    P = (Hh + 2 * pd - d * (k - 1) - 1) // s + 1
+    Q = (W + 2 * pd - d * (k - 1) - 1) // s + 1
+    full = torch.zeros((N, P, Q, K), dtype=torch.bfloat16, device="cuda")
+    parts = torch.full((N, P, Q, K), 9.0, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    a.x, a.w, a.scratch, a.scratch_bytes = dx_.data_ptr(), dw_.data_ptr(), status.data_ptr(), 16
+    a.y = full.data_ptr()
+    abi.check(L.ad_conv2d_fprop(C.byref(a), H.stream()))
+    a.y = parts.data_ptr()
+    b = 3
+    a.out_row_begin, a.out_row_count = b, P - 2 * b
+    abi.check(L.ad_conv2d_fprop(C.byref(a), H.stream()))
+    H.sync()
+    assert torch.all(parts[:, :b] == 9.0) and torch.all(parts[:, P - b:] == 9.0)
+    a.out_row_begin, a.out_row_count = 0, b
+    abi.check(L.ad_conv2d_fprop(C.byref(a), H.stream()))
+    a.out_row_begin, a.out_row_count = P - b, b
+    abi.check(L.ad_conv2d_fprop(C.byref(a), H.stream()))
+    H.sync()
+    assert torch.equal(parts, full) and status[0].item() == 0
+    a.out_row_begin, a.out_row_count = P - 1, 2
+    assert L.ad_conv2d_fprop(C.byref(a), H.stream()) == abi.AD_ERR_BAD_ARG
