@@ -322,6 +322,143 @@ def kernel_times(torch, step, iters=10):
     return {"fprop": t(fprop), "dgrad": t(dgrad), "wgrad": t(wgrad)}
 
 
+# ----------------------------------------------------------------------------- halo microbenchmark
+def run_halo_workload(args):
+    """`--workload halo`: BASELINE config 2 -- NCHW tensors N=8, C=256, 224x224 cut into H-strips, halo
+    1 and 3, fp32 and bf16; forward exchange and backward accumulate.  On one GPU the R strips share the
+    device and move in ONE launch (HBM-bound: payload read + written); on N GPUs each rank pushes to /
+    pulls from its neighbours over NVLink, with NCCL send/recv of packed faces timed beside it."""
+    import torch
+    import torch.distributed as dist
+    from arraydiff_cuda_b200 import abi, dist as addist
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    L = abi.load()
+    N, Cc, Hh, W = 8, 256, 224, 224
+    cases = []
+    s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def timed(fn, iters):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        if world > 1:
+            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms * 1e-3
+
+    launches0 = L.ad_launch_count()
+    for R in ([world] if world > 1 else [2, 4, 8]):
+        h = Hh // R
+        for dt, tdt, es in ((abi.AD_F32, torch.float32, 4), (abi.AD_BF16, torch.bfloat16, 2)):
+            for p in (1, 3):
+                shape = (N, Cc, h + 2 * p, W + 2 * p)
+                payload = 2 * (R - 1) * N * Cc * p * W * es
+                a = abi.HaloArgs()
+                a.dtype, a.layout = dt, abi.AD_NCHW
+                a.halo_pad, a.base_width, a.base_height, a.num_channels, a.batch_size = p, W, h, Cc, N
+                a.num_ranks = R
+                rec = {"strips": R, "halo": p, "dtype": "f32" if es == 4 else "bf16", "payload_bytes": payload}
+                if world == 1:
+                    bufs = [torch.randn(shape, device="cuda").to(tdt) for _ in range(R)]
+                    a.rank_first, a.rank_count, a.push = 0, R, 1
+                    for r in range(R):
+                        a.bufs[r] = bufs[r].data_ptr()
+                    te = timed(lambda: abi.check(L.ad_halo_exchange(C.byref(a), s)), args.steps)
+                    tr = timed(lambda: abi.check(L.ad_halo_reduce(C.byref(a), s)), args.steps)
+                else:
+                    arena = addist.SymmetricArena(int(np.prod(shape)) * es + (1 << 20), rank, world)
+                    buf, off = arena.alloc(shape, tdt)
+                    flags, foff = arena.alloc((8,), torch.int64)
+                    buf.copy_(torch.randn(shape, device="cuda").to(tdt))
+                    counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+                    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+                    plan = addist.HaloPlan(rank, world)
+                    a.rank_first, a.rank_count, a.push = rank, 1, 1
+                    peers, fp = arena.peers(off), arena.peers(foff)
+                    for r in range(R):
+                        a.bufs[r] = peers[r]
+                    for peer, slot in plan.exchange_signals():
+                        a.signal_flags[peer] = fp[peer] + 8 * slot
+                    a.block_counter = counter.data_ptr()
+                    ep = [0]
+
+                    def exch():
+                        ep[0] += 1
+                        a.epoch = ep[0]
+                        abi.check(L.ad_halo_exchange(C.byref(a), s))
+                        for slot in plan.exchange_waits():
+                            abi.check(L.ad_flag_wait(C.c_void_p(flags.data_ptr() + 8 * slot), ep[0], 2_000_000_000,
+                                                     C.c_void_p(status.data_ptr()), s))
+
+                    def red():
+                        ep[0] += 1
+                        for peer, slot in plan.reduce_signals():
+                            abi.check(L.ad_flag_signal(C.c_void_p(fp[peer] + 8 * slot), ep[0], s))
+                        for slot in plan.reduce_waits():
+                            abi.check(L.ad_flag_wait(C.c_void_p(flags.data_ptr() + 8 * slot), ep[0], 2_000_000_000,
+                                                     C.c_void_p(status.data_ptr()), s))
+                        abi.check(L.ad_halo_reduce(C.byref(a), s))
+
+                    def nccl():
+                        ops, recvs = [], []
+                        for peer, src, dst in plan.push_rows(p, h):
+                            send = buf[:, :, src:src + p, p:p + W].contiguous()
+                            recv = torch.empty_like(send)
+                            mine = [d for (q, _, d) in addist.HaloPlan(peer, world).push_rows(p, h) if q == rank][0]
+                            ops += [dist.P2POp(dist.isend, send, peer), dist.P2POp(dist.irecv, recv, peer)]
+                            recvs.append((recv, mine))
+                        for w_ in dist.batch_isend_irecv(ops):
+                            w_.wait()
+                        for recv, dst in recvs:
+                            buf[:, :, dst:dst + p, p:p + W] = recv
+
+                    te, tr, tn = timed(exch, args.steps), timed(red, args.steps), timed(nccl, args.steps)
+                    if int(status.item()) != 0:
+                        raise RuntimeError("bounded flag wait timed out")
+                    rec["nccl_sendrecv_us"] = tn * 1e6
+                    rec["nccl_sendrecv_gbs"] = payload / tn / 1e9
+                    dist.barrier()
+                    arena.close()
+                rec.update(exchange_us=te * 1e6, exchange_gbs=payload / te / 1e9, reduce_us=tr * 1e6, reduce_gbs=payload / tr / 1e9)
+                cases.append(rec)
+    if rank == 0:
+        peaks = measured_peaks()
+        top = max(cases, key=lambda c: c["payload_bytes"])
+        # one GPU: every payload byte is read and written locally; N GPUs: bytes into the busiest GPU over NVLink
+        if world == 1:
+            achieved, peak, bound = 2 * top["payload_bytes"] / (top["exchange_us"] * 1e-6) / 1e9, peaks["hbm_gbs"], "hbm"
+        else:
+            per_gpu = top["payload_bytes"] / (world - 1)      # two faces land in an interior rank
+            achieved, peak, bound = per_gpu / (top["exchange_us"] * 1e-6) / 1e9, 770.0, "nvlink"
+        print(json.dumps({
+            "metric": "halo_exchange_gbs", "value": top["exchange_gbs"], "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": top["exchange_us"] / 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "halo_microbench", "tensor": [N, Cc, Hh, W], "layout": "NCHW",
+                       "l2": "same buffers every iteration (payload smaller than L2; launch-latency dominated below ~10 MiB)"},
+            "gpu_launches": int(L.ad_launch_count() - launches0),
+            "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None},
+            "cases": cases,
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     global BATCH
     ap = argparse.ArgumentParser()
@@ -330,6 +467,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--workload", default="conv", choices=["conv", "halo"],
+                    help="conv: the headline spatial conv step; halo: the halo-exchange microbenchmark (config 2)")
     ap.add_argument("--batch", type=int, default=BATCH,
                     help="images per step; the default is the workload's, smaller values are for profiler captures")
     args = ap.parse_args()
@@ -337,6 +476,9 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.workload == "halo":
+        run_halo_workload(args)
         return
 
     import torch

@@ -37,3 +37,45 @@ def test_reference_halo_kernels_match_oracle(ref, R, geom):
         (orc.halo_reduce if reduce else orc.halo_exchange)(want, orc.NCHW, p, W, h, Cc, N)
         for r in range(R):
             assert np.array_equal(d[r].cpu().numpy(), want[r]), (reduce, r)
+
+
+@pytest.mark.parametrize("R,p", [(2, 1), (4, 3)])
+def test_speed_against_reference_halo_kernels(ref, R, p):
+    """Same GPU, same tensors (BASELINE config 2, fp32): this library's exchange against the reference's
+    own kernel, one launch per rank as the reference does.  Prints both; ours must be at least 2x faster."""
+    import torch
+    from arraydiff_cuda_b200 import abi
+    N, Cc, Hh, W = 8, 256, 224, 224
+    h = Hh // R
+    u = C.c_uint32
+    bufs = [torch.randn((N, Cc, h + 2 * p, W + 2 * p), device="cuda") for _ in range(R)]
+    ptrs = [C.c_void_p(t.data_ptr()) for t in bufs]
+    fn = ref.ref_halo_1x2 if R == 2 else ref.ref_halo_1x4
+
+    def run_ref():
+        for r in range(R):
+            fn(0, u(r), u(p), u(W), u(h), u(Cc), u(N), *ptrs, None)
+
+    a = H.halo_args(bufs, abi.AD_F32, abi.AD_NCHW, p, W, h, Cc, N)
+    L = abi.lib()
+
+    def run_ours():
+        abi.check(L.ad_halo_exchange(C.byref(a), H.stream()))
+
+    def timed(f):
+        for _ in range(5):
+            f()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(50):
+            f()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / 50 * 1e3
+
+    t_ref, t_ours = timed(run_ref), timed(run_ours)
+    payload = 2 * (R - 1) * N * Cc * p * W * 4
+    print(f"\nhalo exchange R={R} p={p} fp32: reference {t_ref:.1f} us ({payload / t_ref / 1e3:.0f} GB/s), "
+          f"this library {t_ours:.1f} us ({payload / t_ours / 1e3:.0f} GB/s)")
+    assert t_ours * 2 < t_ref
