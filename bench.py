@@ -39,6 +39,12 @@ def flops_per_pass(n=None, rows=SIZE, cols=SIZE):
     return 2.0 * (BATCH if n is None else n) * CH * CH * KS * KS * rows * cols
 
 
+# DRAM traffic per launch (dram__bytes_read + dram__bytes_write) of the three conv kernels, from the ncu
+# capture summarised in profiles/conv_tc_microbench_spatial_conv.md: measured at batch 4 on one GPU; traffic
+# grows in proportion to the pixels a launch processes, so it is scaled by batch / 4 / strips.
+NCU_TRAFFIC_BATCH4 = {"fprop": 233.7e6, "dgrad": 232.9e6, "wgrad": 276.1e6}
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -542,7 +548,8 @@ def main():
                     "d2h_bytes_per_step": step.dw_host.numel() * 4, "steps": e2e_steps},
             "gpu_launches": int(launches),
             "roofline": {"bound": "tensor", "kernel": f"conv_tc_{top}", "achieved": achieved, "peak": peaks["tf_burst"],
-                         "unit": "TFLOP/s", "frac": achieved / peaks["tf_burst"], "traffic": None,
+                         "unit": "TFLOP/s", "frac": achieved / peaks["tf_burst"],
+                         "traffic": NCU_TRAFFIC_BATCH4[top] * BATCH / 4 / world,
                          "peak_source": peaks["source"] + " (burst, kernel timed alone)",
                          "kernels_us": {k: v * 1e6 for k, v in kt.items()}},
             "clocks": clocks,
