@@ -167,6 +167,22 @@ int adh_net_get_input_grad(void* h, int rank, float* host_full) {
   n->net.sink->store_grad(*n->txn, v, 0, &w);
   return AD_OK;
 }
+// One full step on data that is already resident on the device: the image loaded by the last
+// adh_net_forward and the output gradients loaded by the last adh_net_set_output_grad are carried into a
+// new transaction; forward, backward and (optionally) gradient allreduce + SGD update run without any
+// host transfer or synchronisation.
+int adh_net_step_resident(void* h, int with_update) {
+  auto* n = (Net*)h;
+  n->txn.reset(new TxnId());
+  n->opt->persist(*n->txn);
+  n->net.sink->persist(*n->txn, n->net.input_vars);
+  n->net.sink->eval(*n->txn);
+  for (size_t r = 0; r < n->ctx->num_ranks(); ++r)
+    if (n->ctx->is_local(r)) n->net.sink->load_grad(*n->txn, n->net.output_grad_vars[r], 0, nullptr);
+  n->net.sink->backward(*n->txn);
+  if (with_update) n->opt->step(*n->txn);
+  return AD_OK;
+}
 // allreduce of the gradients + SGD update on every rank
 int adh_net_sgd_step(void* h) { auto* n = (Net*)h; n->opt->step(*n->txn); return AD_OK; }
 int adh_net_sync(void* h) { ((Net*)h)->ctx->sync(); return AD_OK; }

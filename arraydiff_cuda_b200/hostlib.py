@@ -44,6 +44,7 @@ def load():
         L.adh_net_set_params.argtypes = [vp, vp]
         L.adh_net_output_dims.argtypes = [vp, C.POINTER(C.c_int)]
         L.adh_net_forward.argtypes = [vp, vp]
+        L.adh_net_step_resident.argtypes = [vp, C.c_int]
         for name in ("adh_net_backward", "adh_net_sgd_step", "adh_net_sync", "adh_net_status"):
             getattr(L, name).argtypes = [vp]
         L.adh_net_arena_used.restype = C.c_size_t
@@ -135,6 +136,10 @@ class Net:
 
     def configure_sgd(self, step_size, momentum, l2=0.0, nesterov=False):
         self.L.adh_net_configure_sgd(self.h, step_size, momentum, l2, int(nesterov))
+
+    def step_resident(self, with_update=True):
+        """forward + backward (+ allreduce and SGD) on the image and output gradients already on the device"""
+        self.L.adh_net_step_resident(self.h, int(with_update))
 
     def sgd_step(self):
         self.L.adh_net_sgd_step(self.h)
