@@ -165,6 +165,126 @@ __global__ void bn_param_grads(uint32_t C, const float* __restrict__ sums, float
   if (dgamma) dgamma[c] += sums[C + c];
 }
 
+
+// ------------------------------------------------------------------ NHWC bf16 fast paths
+// Channel-fastest bf16 views whose strides are multiples of 8 elements: a thread owns 8 adjacent
+// channels (one 16-byte load / store per pixel) of a fixed channel group, so the per-channel
+// constants sit in registers and every warp access is a run of whole 128-byte lines.
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { float2 t = __bfloat1622float2(h[j]); f[2 * j] = t.x; f[2 * j + 1] = t.y; }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 v;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+  return v;
+}
+__device__ __forceinline__ long long pix_off(const BView& v, size_t i, uint32_t H, uint32_t W) {
+  const uint32_t x = (uint32_t)(i % W);
+  const size_t r = i / W;
+  const uint32_t y = (uint32_t)(r % H), n = (uint32_t)(r / H);
+  return n * v.sn + y * v.sy + x * v.sx;
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(256) bn_reduce_vec(BnRed p, float* partial) {
+  const uint32_t G = p.C / 8, cg = threadIdx.x % G, pl = threadIdx.x / G, PL = 256 / G;
+  const size_t per = (size_t)p.N * p.H * p.W;
+  float a[8], b[8], mean[8], invstd[8], gam[8], bet[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    a[j] = b[j] = 0.f;
+    if (MODE == 1) { mean[j] = p.mean[cg * 8 + j]; invstd[j] = p.invstd[cg * 8 + j]; gam[j] = p.gamma[cg * 8 + j]; bet[j] = p.beta[cg * 8 + j]; }
+  }
+  for (size_t i = (size_t)blockIdx.x * PL + pl; i < per; i += (size_t)gridDim.x * PL) {
+    float xv[8];
+    unpack8(*(const uint4*)((const __nv_bfloat16*)p.x.base + pix_off(p.x, i, p.H, p.W) + cg * 8), xv);
+    if (MODE == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { a[j] += xv[j]; b[j] = fmaf(xv[j], xv[j], b[j]); }
+    } else {
+      float g[8];
+      unpack8(*(const uint4*)((const __nv_bfloat16*)p.dy.base + pix_off(p.dy, i, p.H, p.W) + cg * 8), g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xhat = (xv[j] - mean[j]) * invstd[j];
+        float gj = g[j];
+        if (p.relu && fmaf(gam[j], xhat, bet[j]) <= 0.f) gj = 0.f;
+        a[j] += gj;
+        b[j] = fmaf(gj, xhat, b[j]);
+      }
+    }
+  }
+  __shared__ float sa[256][9], sb[256][9];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { sa[threadIdx.x][j] = a[j]; sb[threadIdx.x][j] = b[j]; }
+  __syncthreads();
+  if (pl == 0) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float ta = 0.f, tb = 0.f;
+      for (uint32_t q = 0; q < PL; ++q) { ta += sa[q * G + cg][j]; tb += sb[q * G + cg][j]; }
+      partial[(size_t)blockIdx.x * 2 * p.C + cg * 8 + j] = ta;
+      partial[(size_t)blockIdx.x * 2 * p.C + p.C + cg * 8 + j] = tb;
+    }
+  }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(256) bn_apply_vec(BnApply p) {
+  const uint32_t G = p.C / 8, cg = threadIdx.x % G, pl = threadIdx.x / G, PL = 256 / G;
+  const size_t per = (size_t)p.N * p.H * p.W;
+  float sc[8], sh[8], mean[8], invstd[8], m1[8], m2[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t c = cg * 8 + j;
+    mean[j] = p.mean[c]; invstd[j] = p.invstd[c];
+    sc[j] = p.gamma[c]; sh[j] = p.beta[c];
+    if (MODE == 1) { m1[j] = (float)((double)p.partial[c] / p.count); m2[j] = (float)((double)p.partial[p.C + c] / p.count); }
+  }
+  for (size_t i = (size_t)blockIdx.x * PL + pl; i < per; i += (size_t)gridDim.x * PL) {
+    float xv[8], o[8];
+    unpack8(*(const uint4*)((const __nv_bfloat16*)p.x.base + pix_off(p.x, i, p.H, p.W) + cg * 8), xv);
+    uint4* op = (uint4*)((__nv_bfloat16*)p.out.base + pix_off(p.out, i, p.H, p.W) + cg * 8);
+    if (MODE == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xhat = (xv[j] - mean[j]) * invstd[j];
+        float v = fmaf(sc[j], xhat, sh[j]);
+        o[j] = p.relu ? fmaxf(v, 0.f) : v;
+      }
+    } else {
+      float g[8], old[8];
+      unpack8(*(const uint4*)((const __nv_bfloat16*)p.dy.base + pix_off(p.dy, i, p.H, p.W) + cg * 8), g);
+      if (p.accumulate) unpack8(*op, old);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xhat = (xv[j] - mean[j]) * invstd[j];
+        float gj = g[j];
+        if (p.relu && fmaf(sc[j], xhat, sh[j]) <= 0.f) gj = 0.f;
+        float v = sc[j] * invstd[j] * (gj - m1[j] - xhat * m2[j]);
+        o[j] = p.accumulate ? v + old[j] : v;
+      }
+    }
+    *op = pack8(o);
+  }
+}
+
+static bool vec_view_ok(const ad_tensor4* t) {
+  if (t->dtype != AD_BF16 || t->sc != 1 || (t->C & 7u) || t->C < 8 || t->C > 2048) return false;
+  if (256 % (t->C / 8)) return false;
+  return !((uintptr_t)t->base & 15u) && !(t->sn & 7) && !(t->sy & 7) && !(t->sx & 7);
+}
+static unsigned vec_grid(const ad_tensor4* t) {
+  const size_t per = (size_t)t->N * t->H * t->W, PL = 256 / (t->C / 8);
+  size_t g = (per + PL * 4 - 1) / (PL * 4);
+  if (g > (size_t)kBnMaxSplits) g = kBnMaxSplits;
+  return (unsigned)(g < 1 ? 1 : g);
+}
+
 static int pick_splits(const ad_tensor4* x, bool cfast) {
   const size_t per = (size_t)x->N * x->H * x->W;
   const size_t groups = cfast ? (x->C + 31) / 32 : x->C;
@@ -179,6 +299,12 @@ static int pick_splits(const ad_tensor4* x, bool cfast) {
 template <int MODE>
 static int launch_reduce(const BnRed& p, const ad_tensor4* x, float* partial, int& nsplit, cudaStream_t s) {
   const bool cfast = x->sc == 1 && x->C > 1;
+  if (vec_view_ok(x) && (MODE == 0 || (p.dy.sc == 1 && !((uintptr_t)p.dy.base & 15u) && !(p.dy.sn & 7) && !(p.dy.sy & 7) && !(p.dy.sx & 7)))) {
+    nsplit = (int)vec_grid(x);
+    bn_reduce_vec<MODE><<<nsplit, 256, 0, s>>>(p, partial);
+    count_launch();
+    return launch_status();
+  }
   nsplit = pick_splits(x, cfast);
   if (cfast) {
     dim3 grid((x->C + 31) / 32, nsplit), block(32, 8);
@@ -261,6 +387,82 @@ __global__ void __launch_bounds__(256) maxpool_bwd_kernel(PoolP p) {
   }
 }
 
+
+// NHWC bf16 pooling, 8 channels per thread.  Same first-maximum rule as the scalar kernels.
+__global__ void __launch_bounds__(256) maxpool_fwd_vec(PoolP p) {
+  const uint32_t G = p.C / 8;
+  const size_t total = (size_t)p.N * p.P * p.Q * G, nt = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nt) {
+    const uint32_t cg = (uint32_t)(i % G);
+    size_t r = i / G;
+    const uint32_t s = (uint32_t)(r % p.Q); r /= p.Q;
+    const uint32_t q = (uint32_t)(r % p.P), n = (uint32_t)(r / p.P);
+    float best[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) best[j] = -INFINITY;
+    for (uint32_t a = 0; a < p.kh; ++a)
+      for (uint32_t b = 0; b < p.kw; ++b) {
+        float v[8];
+        unpack8(*(const uint4*)((const __nv_bfloat16*)p.x.base + n * p.x.sn + (q * p.sh + a) * p.x.sy + (s * p.sw + b) * p.x.sx + cg * 8), v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) if (v[j] > best[j] || (a == 0 && b == 0)) best[j] = v[j];
+      }
+    *(uint4*)((__nv_bfloat16*)p.y.base + n * p.y.sn + q * p.y.sy + s * p.y.sx + cg * 8) = pack8(best);
+  }
+}
+// one thread per input pixel x 8 channels; gathers from the (at most ceil(kh/sh) x ceil(kw/sw)) windows over it
+__global__ void __launch_bounds__(256) maxpool_bwd_vec(PoolP p) {
+  const uint32_t G = p.C / 8;
+  const size_t total = (size_t)p.N * p.H * p.W * G, nt = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nt) {
+    const uint32_t cg = (uint32_t)(i % G);
+    size_t r = i / G;
+    const uint32_t x = (uint32_t)(r % p.W); r /= p.W;
+    const uint32_t y = (uint32_t)(r % p.H), n = (uint32_t)(r / p.H);
+    const __nv_bfloat16* xb = (const __nv_bfloat16*)p.x.base + n * p.x.sn + cg * 8;
+    float acc[8], me[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    unpack8(*(const uint4*)(xb + y * p.x.sy + x * p.x.sx), me);
+    const uint32_t q_lo = y + 1 > p.kh ? (y + 1 - p.kh + p.sh - 1) / p.sh : 0;
+    const uint32_t s_lo = x + 1 > p.kw ? (x + 1 - p.kw + p.sw - 1) / p.sw : 0;
+    for (uint32_t q = q_lo; q < p.P && q * p.sh <= y; ++q)
+      for (uint32_t s = s_lo; s < p.Q && s * p.sw <= x; ++s) {
+        // this element is the window's first maximum iff no earlier element (scan order) is >= it
+        // and no later element is > it
+        bool win[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) win[j] = true;
+        for (uint32_t a = 0; a < p.kh; ++a)
+          for (uint32_t b = 0; b < p.kw; ++b) {
+            const uint32_t yy = q * p.sh + a, xx = s * p.sw + b;
+            if (yy == y && xx == x) continue;
+            float v[8];
+            unpack8(*(const uint4*)(xb + yy * p.x.sy + xx * p.x.sx), v);
+            const bool earlier = yy < y || (yy == y && xx < x);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) win[j] = win[j] && (earlier ? v[j] < me[j] : v[j] <= me[j]);
+          }
+        float g[8];
+        unpack8(*(const uint4*)((const __nv_bfloat16*)p.dy.base + n * p.dy.sn + q * p.dy.sy + s * p.dy.sx + cg * 8), g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) if (win[j]) acc[j] += g[j];
+      }
+    uint4* op = (uint4*)((__nv_bfloat16*)p.dx.base + n * p.dx.sn + y * p.dx.sy + x * p.dx.sx + cg * 8);
+    if (p.accumulate) {
+      float old[8];
+      unpack8(*op, old);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += old[j];
+    }
+    *op = pack8(acc);
+  }
+}
+static bool pool_vec_ok(const ad_tensor4* t) {
+  return t->dtype == AD_BF16 && t->sc == 1 && (t->C & 7u) == 0 && !((uintptr_t)t->base & 15u) && !(t->sn & 7) &&
+         !(t->sy & 7) && !(t->sx & 7);
+}
+
 }  // namespace adk
 
 using namespace adk;
@@ -291,7 +493,8 @@ extern "C" int ad_bn_finalize_apply(const ad_tensor4* x, const ad_tensor4* y, co
   BnApply a{bview(x), bview(x), bview(y), x->N, x->C, x->H, x->W, y->sc == 1 && y->C > 1, relu, 0,
             gamma, beta, save_mean, save_invstd, nullptr, 1, count};
   const size_t total = (size_t)x->N * x->C * x->H * x->W;
-  AD_DISPATCH_DTYPE(x->dtype, (bn_apply<T, 0><<<grid_for(total, 256, 16), 256, 0, s>>>(a)));
+  if (vec_view_ok(x) && vec_view_ok(y)) bn_apply_vec<0><<<kNumSMs * 4, 256, 0, s>>>(a);
+  else AD_DISPATCH_DTYPE(x->dtype, (bn_apply<T, 0><<<grid_for(total, 256, 16), 256, 0, s>>>(a)));
   count_launch();
   return launch_status();
 }
@@ -315,7 +518,8 @@ extern "C" int ad_bn_fwd_train(const ad_tensor4* x, const ad_tensor4* y, const f
   count_launch();
   BnApply a{bview(x), bview(x), bview(y), x->N, x->C, x->H, x->W, y->sc == 1 && y->C > 1, relu, 0,
             gamma, beta, save_mean, save_invstd, nullptr, 1, count};
-  AD_DISPATCH_DTYPE(x->dtype, (bn_apply<T, 0><<<grid_for(total, 256, 16), 256, 0, s>>>(a)));
+  if (vec_view_ok(x) && vec_view_ok(y)) bn_apply_vec<0><<<kNumSMs * 4, 256, 0, s>>>(a);
+  else AD_DISPATCH_DTYPE(x->dtype, (bn_apply<T, 0><<<grid_for(total, 256, 16), 256, 0, s>>>(a)));
   count_launch();
   return launch_status();
 }
@@ -345,7 +549,8 @@ extern "C" int ad_bn_bwd(const ad_tensor4* x, const ad_tensor4* dy, const ad_ten
   }
   BnApply a{bview(x), bview(dy), bview(dx), x->N, x->C, x->H, x->W, dx->sc == 1 && dx->C > 1, relu, accumulate_dx,
             gamma, beta, save_mean, save_invstd, sums, 1, (double)x->N * x->H * x->W};
-  AD_DISPATCH_DTYPE(x->dtype, (bn_apply<T, 1><<<grid_for(total, 256, 16), 256, 0, s>>>(a)));
+  if (vec_view_ok(x) && vec_view_ok(dy) && vec_view_ok(dx)) bn_apply_vec<1><<<kNumSMs * 4, 256, 0, s>>>(a);
+  else AD_DISPATCH_DTYPE(x->dtype, (bn_apply<T, 1><<<grid_for(total, 256, 16), 256, 0, s>>>(a)));
   count_launch();
   return launch_status();
 }
@@ -371,7 +576,8 @@ extern "C" int ad_maxpool2d_fwd(const ad_tensor4* x, const ad_tensor4* y, uint32
   p.c_fastest = y->sc == 1 && y->C > 1;
   const size_t total = (size_t)p.N * p.C * p.P * p.Q;
   if (total == 0) return AD_OK;
-  AD_DISPATCH_DTYPE(x->dtype, (maxpool_fwd_kernel<T><<<grid_for(total, 256, 16), 256, 0, as_stream(stream)>>>(p)));
+  if (pool_vec_ok(x) && pool_vec_ok(y)) maxpool_fwd_vec<<<grid_for(total / 8, 256, 16), 256, 0, as_stream(stream)>>>(p);
+  else AD_DISPATCH_DTYPE(x->dtype, (maxpool_fwd_kernel<T><<<grid_for(total, 256, 16), 256, 0, as_stream(stream)>>>(p)));
   count_launch();
   return launch_status();
 }
@@ -389,7 +595,8 @@ extern "C" int ad_maxpool2d_bwd(const ad_tensor4* x, const ad_tensor4* dy, const
   p.accumulate = accumulate;
   const size_t total = (size_t)p.N * p.C * p.H * p.W;
   if (total == 0) return AD_OK;
-  AD_DISPATCH_DTYPE(x->dtype, (maxpool_bwd_kernel<T><<<grid_for(total, 256, 16), 256, 0, as_stream(stream)>>>(p)));
+  if (pool_vec_ok(x) && pool_vec_ok(dy) && pool_vec_ok(dx)) maxpool_bwd_vec<<<grid_for(total / 8, 256, 16), 256, 0, as_stream(stream)>>>(p);
+  else AD_DISPATCH_DTYPE(x->dtype, (maxpool_bwd_kernel<T><<<grid_for(total, 256, 16), 256, 0, as_stream(stream)>>>(p)));
   count_launch();
   return launch_status();
 }

@@ -125,6 +125,48 @@ __global__ void __launch_bounds__(256) ew_kernel(Dims d, View a, View b, View yv
   }
 }
 
+
+// bf16 channel-fastest views with 8-element-aligned strides: 8 channels (16 bytes) per thread.
+__device__ __forceinline__ void ew_unpack8(const uint4& v, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { float2 t = __bfloat1622float2(h[j]); f[2 * j] = t.x; f[2 * j + 1] = t.y; }
+}
+template <int OP>
+__global__ void __launch_bounds__(256) ew_vec_kernel(Dims d, View a, View b, View yv, int accumulate) {
+  const uint32_t G = d.C / 8;
+  const size_t total = (size_t)d.N * d.H * d.W * G, nt = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nt) {
+    const uint32_t cg = (uint32_t)(i % G);
+    size_t r = i / G;
+    const uint32_t x = (uint32_t)(r % d.W); r /= d.W;
+    const uint32_t y = (uint32_t)(r % d.H), n = (uint32_t)(r / d.H);
+    float av[8], bv[8], o[8], old[8];
+    ew_unpack8(*(const uint4*)((const __nv_bfloat16*)a.base + voff(a, n, cg * 8, y, x)), av);
+    if (OP == kAdd2 || OP == kReluBwd) ew_unpack8(*(const uint4*)((const __nv_bfloat16*)b.base + voff(b, n, cg * 8, y, x)), bv);
+    uint4* op = (uint4*)((__nv_bfloat16*)yv.base + voff(yv, n, cg * 8, y, x));
+    if (accumulate) ew_unpack8(*op, old);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float v;
+      if (OP == kRelu) v = fmaxf(av[j], 0.f);
+      else if (OP == kConvert) v = av[j];
+      else if (OP == kAdd2) v = av[j] + bv[j];
+      else v = av[j] > 0.f ? bv[j] : 0.f;
+      o[j] = accumulate ? v + old[j] : v;
+    }
+    uint4 pk;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(o[2 * j], o[2 * j + 1]);
+    *op = pk;
+  }
+}
+static bool ew_vec_ok(const ad_tensor4* t) {
+  return t->dtype == AD_BF16 && t->sc == 1 && (t->C & 7u) == 0 && !((uintptr_t)t->base & 15u) && !(t->sn & 7) &&
+         !(t->sy & 7) && !(t->sx & 7);
+}
+
 static int same_dims(const ad_tensor4* a, const ad_tensor4* b) {
   return a->N == b->N && a->C == b->C && a->H == b->H && a->W == b->W;
 }
@@ -137,8 +179,13 @@ static int ew_launch(const ad_tensor4* a, const ad_tensor4* b, const ad_tensor4*
   if (total == 0) return AD_OK;
   Dims d{y->N, y->C, y->H, y->W, y->sc == 1 && y->C > 1};
   View va = view_of(a), vb = b ? view_of(b) : View{nullptr, 0, 0, 0, 0}, vy = view_of(y);
-  const unsigned grid = grid_for(total, 256, 16);
   cudaStream_t s = as_stream(stream);
+  if (ew_vec_ok(a) && ew_vec_ok(y) && (!b || ew_vec_ok(b))) {
+    ew_vec_kernel<OP><<<grid_for(total / 8, 256, 16), 256, 0, s>>>(d, va, vb, vy, accumulate);
+    count_launch();
+    return launch_status();
+  }
+  const unsigned grid = grid_for(total, 256, 16);
   const int da = a->dtype, db = b ? b->dtype : a->dtype, dy = y->dtype;
 #define EW_CASE(TA_, TB_, TY_) ew_kernel<OP, TA_, TB_, TY_><<<grid, 256, 0, s>>>(d, va, vb, vy, accumulate)
   using bf = __nv_bfloat16;

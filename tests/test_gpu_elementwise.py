@@ -140,9 +140,10 @@ def _back(t, layout, pad, Hh, W):
 @pytest.mark.parametrize("layout", [abi.AD_NCHW, abi.AD_NHWC])
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
 @pytest.mark.parametrize("relu", [0, 1])
-def test_batch_norm_fwd_bwd(layout, dtype, relu):
+@pytest.mark.parametrize("Cc", [37, 64])        # 64: the 8-channels-per-thread NHWC bf16 kernels
+def test_batch_norm_fwd_bwd(layout, dtype, relu, Cc):
     import torch
-    N, Cc, Hh, W = 2, 37, 19, 23
+    N, Hh, W = 2, 19, 23
     x = H.normal(20, (N, Cc, Hh, W)) * H.uniform(21, (1, Cc, 1, 1), 0.5, 2.0) + H.uniform(22, (1, Cc, 1, 1))
     dy = H.uniform(23, (N, Cc, Hh, W))
     if dtype == "bf16":
@@ -211,9 +212,10 @@ def test_batch_norm_two_phase_matches_single_call_across_strips():
 
 @pytest.mark.parametrize("layout", [abi.AD_NCHW, abi.AD_NHWC])
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
-def test_maxpool_3x3_s2_on_padded_input(layout, dtype):
+@pytest.mark.parametrize("Cc", [5, 16])
+def test_maxpool_3x3_s2_on_padded_input(layout, dtype, Cc):
     """The reference's pool sees the explicit zero pad cells (pad value 0, not -inf)."""
-    N, Cc, Hh, W, p = 2, 5, 12, 14, 1
+    N, Hh, W, p = 2, 12, 14, 1
     x = H.normal(30, (N, Cc, Hh, W)) - 0.5      # mostly negative at some borders: pad zeros win there
     if dtype == "bf16":
         x = orc.round_bf16(x)
@@ -241,8 +243,9 @@ def test_maxpool_3x3_s2_on_padded_input(layout, dtype):
 
 
 @pytest.mark.parametrize("layout", [abi.AD_NCHW, abi.AD_NHWC])
-def test_relu_add_convert(layout):
-    N, Cc, Hh, W = 2, 6, 5, 7
+@pytest.mark.parametrize("Cc", [6, 16])
+def test_relu_add_convert(layout, Cc):
+    N, Hh, W = 2, 5, 7
     a, b = H.normal(40, (N, Cc, Hh, W)), H.normal(41, (N, Cc, Hh, W))
     L = abi.lib()
     ta, va = _views(a, layout, "f32")
@@ -270,3 +273,27 @@ def test_relu_add_convert(layout):
     abi.check(L.ad_convert(C.byref(vh), C.byref(vback), 0, H.stream()))
     H.sync()
     assert np.array_equal(H.host(tback), orc.round_bf16(a))
+
+
+def test_nhwc_bf16_vector_paths_match_scalar_semantics():
+    """relu / add / relu-bwd / accumulate-convert on aligned NHWC bf16 views (8 channels per thread), with the
+    output inside a halo-padded buffer."""
+    N, Cc, Hh, W = 2, 64, 9, 11
+    a, b = orc.round_bf16(H.normal(50, (N, Cc, Hh, W))), orc.round_bf16(H.normal(51, (N, Cc, Hh, W)))
+    L = abi.lib()
+    ta, va = _views(a, abi.AD_NHWC, "bf16")
+    tb, vb = _views(b, abi.AD_NHWC, "bf16")
+    ty, vy = _views(np.zeros_like(a), abi.AD_NHWC, "bf16", pad=1)
+    abi.check(L.ad_add(C.byref(va), C.byref(vb), C.byref(vy), H.stream()))
+    H.sync()
+    assert np.array_equal(_back(ty, abi.AD_NHWC, 1, Hh, W), orc.round_bf16(a + b))
+    abi.check(L.ad_relu_fwd(C.byref(va), C.byref(vy), H.stream()))
+    H.sync()
+    assert np.array_equal(_back(ty, abi.AD_NHWC, 1, Hh, W), np.maximum(a, 0))
+    tdx, vdx = _views(b, abi.AD_NHWC, "bf16")
+    abi.check(L.ad_relu_bwd(C.byref(va), C.byref(vb), C.byref(vdx), 1, H.stream()))
+    H.sync()
+    assert np.array_equal(_back(tdx, abi.AD_NHWC, 0, Hh, W), orc.round_bf16(b + np.where(a > 0, b, 0)))
+    abi.check(L.ad_convert(C.byref(va), C.byref(vdx), 1, H.stream()))
+    H.sync()
+    assert np.array_equal(_back(tdx, abi.AD_NHWC, 0, Hh, W), orc.round_bf16(orc.round_bf16(b + np.where(a > 0, b, 0)) + a))
