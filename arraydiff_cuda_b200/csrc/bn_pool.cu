@@ -10,6 +10,12 @@
 namespace adk {
 
 constexpr int kBnMaxSplits = 128;
+// Partial-sum rows a reduction may use for C channels: as many as fit the scratch of the widest layer
+// ((128 + 1) rows of 2 * 2048 floats), at most 1024 -- narrow layers get more blocks in flight.
+__host__ __device__ inline int bn_max_splits(uint32_t C) {
+  long long s = (long long)(kBnMaxSplits + 1) * 2 * 2048 / (2ll * (C ? C : 1)) - 1;
+  return (int)(s > 1024 ? 1024 : (s < 1 ? 1 : s));
+}
 
 struct BView { const char* base; long long sn, sc, sy, sx; };
 static BView bview(const ad_tensor4* t) { return BView{(const char*)t->base, t->sn, t->sc, t->sy, t->sx}; }
@@ -91,25 +97,34 @@ __global__ void __launch_bounds__(256) bn_reduce_cfast(BnRed p, float* partial) 
   }
 }
 
-// sums[0..2C) = sum over splits (double accumulate).
-__global__ void bn_combine(uint32_t C2, int nsplit, const float* __restrict__ partial, float* sums) {
-  uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= C2) return;
-  double t = 0.0;
-  for (int s = 0; s < nsplit; ++s) t += (double)partial[(size_t)s * C2 + i];
-  sums[i] = (float)t;
+__device__ __forceinline__ double warp_sum_f64(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
 }
 
-// mean / invstd / var from sums; double arithmetic for the cancellation in E[x^2]-E[x]^2.
-__global__ void bn_finalize(uint32_t C, int nsplit, const float* __restrict__ partial_or_sums, double count, float eps,
-                            float* mean, float* invstd, float* var) {
-  uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+// sums[0..2C) = sum over splits (double accumulate); one warp per entry, lanes stride over the splits.
+__global__ void __launch_bounds__(256) bn_combine(uint32_t C2, int nsplit, const float* __restrict__ partial, float* sums) {
+  const uint32_t i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (i >= C2) return;
+  double t = 0.0;
+  for (int s = lane; s < nsplit; s += 32) t += (double)partial[(size_t)s * C2 + i];
+  t = warp_sum_f64(t);
+  if (lane == 0) sums[i] = (float)t;
+}
+
+// mean / invstd / var from sums; double arithmetic for the cancellation in E[x^2]-E[x]^2.  One warp per channel.
+__global__ void __launch_bounds__(256) bn_finalize(uint32_t C, int nsplit, const float* __restrict__ partial_or_sums, double count,
+                                                   float eps, float* mean, float* invstd, float* var) {
+  const uint32_t c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (c >= C) return;
   double s = 0.0, ss = 0.0;
-  for (int k = 0; k < nsplit; ++k) {
+  for (int k = lane; k < nsplit; k += 32) {
     s += (double)partial_or_sums[(size_t)k * 2 * C + c];
     ss += (double)partial_or_sums[(size_t)k * 2 * C + C + c];
   }
+  s = warp_sum_f64(s); ss = warp_sum_f64(ss);
+  if (lane != 0) return;
   double m = s / count, v = ss / count - m * m;
   if (v < 0.0) v = 0.0;
   if (mean) mean[c] = (float)m;
@@ -280,8 +295,8 @@ static bool vec_view_ok(const ad_tensor4* t) {
 }
 static unsigned vec_grid(const ad_tensor4* t) {
   const size_t per = (size_t)t->N * t->H * t->W, PL = 256 / (t->C / 8);
-  size_t g = (per + PL * 4 - 1) / (PL * 4);
-  if (g > (size_t)kBnMaxSplits) g = kBnMaxSplits;
+  size_t g = (per + PL * 2 - 1) / (PL * 2);
+  if (g > (size_t)bn_max_splits(t->C)) g = bn_max_splits(t->C);
   return (unsigned)(g < 1 ? 1 : g);
 }
 
@@ -292,6 +307,7 @@ static int pick_splits(const ad_tensor4* x, bool cfast) {
   size_t maxs = (per + (cfast ? 8 : 256) * 4 - 1) / ((cfast ? 8 : 256) * 4);
   if (want > maxs) want = maxs;
   if (want > (size_t)kBnMaxSplits) want = kBnMaxSplits;
+  if (want > (size_t)bn_max_splits(x->C)) want = bn_max_splits(x->C);
   if (want < 1) want = 1;
   return (int)want;
 }
@@ -430,9 +446,7 @@ __global__ void __launch_bounds__(256) maxpool_bwd_vec(PoolP p) {
       for (uint32_t s = s_lo; s < p.Q && s * p.sw <= x; ++s) {
         // this element is the window's first maximum iff no earlier element (scan order) is >= it
         // and no later element is > it
-        bool win[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) win[j] = true;
+        uint32_t win = 0xffu;   // bit j: channel j of this element is still the window's first maximum
         for (uint32_t a = 0; a < p.kh; ++a)
           for (uint32_t b = 0; b < p.kw; ++b) {
             const uint32_t yy = q * p.sh + a, xx = s * p.sw + b;
@@ -441,12 +455,13 @@ __global__ void __launch_bounds__(256) maxpool_bwd_vec(PoolP p) {
             unpack8(*(const uint4*)(xb + yy * p.x.sy + xx * p.x.sx), v);
             const bool earlier = yy < y || (yy == y && xx < x);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) win[j] = win[j] && (earlier ? v[j] < me[j] : v[j] <= me[j]);
+            for (int j = 0; j < 8; ++j)
+              if (!(earlier ? v[j] < me[j] : v[j] <= me[j])) win &= ~(1u << j);
           }
         float g[8];
         unpack8(*(const uint4*)((const __nv_bfloat16*)p.dy.base + n * p.dy.sn + q * p.dy.sy + s * p.dy.sx + cg * 8), g);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) if (win[j]) acc[j] += g[j];
+        for (int j = 0; j < 8; ++j) if (win & (1u << j)) acc[j] += g[j];
       }
     uint4* op = (uint4*)((__nv_bfloat16*)p.dx.base + n * p.dx.sn + y * p.dx.sy + x * p.dx.sx + cg * 8);
     if (p.accumulate) {
@@ -467,7 +482,7 @@ static bool pool_vec_ok(const ad_tensor4* t) {
 
 using namespace adk;
 
-extern "C" size_t ad_bn_scratch_bytes(uint32_t C) { return (size_t)(kBnMaxSplits + 1) * 2 * C * sizeof(float); }
+extern "C" size_t ad_bn_scratch_bytes(uint32_t C) { return (size_t)(bn_max_splits(C) + 1) * 2 * C * sizeof(float); }
 
 extern "C" int ad_bn_partial_stats(const ad_tensor4* x, float* sums, void* scratch, size_t scratch_bytes, void* stream) {
   if (!x || !x->base || !sums || !scratch) return AD_ERR_BAD_ARG;
@@ -477,7 +492,7 @@ extern "C" int ad_bn_partial_stats(const ad_tensor4* x, float* sums, void* scrat
   int nsplit = 1;
   int st = launch_reduce<0>(p, x, (float*)scratch, nsplit, s);
   if (st != AD_OK) return st;
-  bn_combine<<<(2 * x->C + 255) / 256, 256, 0, s>>>(2 * x->C, nsplit, (const float*)scratch, sums);
+  bn_combine<<<(2 * x->C + 7) / 8, 256, 0, s>>>(2 * x->C, nsplit, (const float*)scratch, sums);
   count_launch();
   return launch_status();
 }
@@ -488,7 +503,7 @@ extern "C" int ad_bn_finalize_apply(const ad_tensor4* x, const ad_tensor4* y, co
   if (!x || !y || !x->base || !y->base || !sums || !gamma || !beta || !save_mean || !save_invstd) return AD_ERR_BAD_ARG;
   if (!dims_eq(x, y) || count <= 0.0) return AD_ERR_BAD_ARG;
   cudaStream_t s = as_stream(stream);
-  bn_finalize<<<(x->C + 127) / 128, 128, 0, s>>>(x->C, 1, sums, count, eps, save_mean, save_invstd, batch_var);
+  bn_finalize<<<(x->C + 7) / 8, 256, 0, s>>>(x->C, 1, sums, count, eps, save_mean, save_invstd, batch_var);
   count_launch();
   BnApply a{bview(x), bview(x), bview(y), x->N, x->C, x->H, x->W, y->sc == 1 && y->C > 1, relu, 0,
             gamma, beta, save_mean, save_invstd, nullptr, 1, count};
@@ -513,7 +528,7 @@ extern "C" int ad_bn_fwd_train(const ad_tensor4* x, const ad_tensor4* y, const f
   int st = launch_reduce<0>(p, x, (float*)scratch, nsplit, s);
   if (st != AD_OK) return st;
   const double count = (double)x->N * x->H * x->W;
-  bn_finalize<<<(x->C + 127) / 128, 128, 0, s>>>(x->C, nsplit, (const float*)scratch, count, eps, save_mean,
+  bn_finalize<<<(x->C + 7) / 8, 256, 0, s>>>(x->C, nsplit, (const float*)scratch, count, eps, save_mean,
                                                  save_invstd, batch_var);
   count_launch();
   BnApply a{bview(x), bview(x), bview(y), x->N, x->C, x->H, x->W, y->sc == 1 && y->C > 1, relu, 0,
@@ -540,8 +555,8 @@ extern "C" int ad_bn_bwd(const ad_tensor4* x, const ad_tensor4* dy, const ad_ten
   float* partial = (float*)scratch;
   int st = launch_reduce<1>(p, x, partial, nsplit, s);
   if (st != AD_OK) return st;
-  float* sums = partial + (size_t)kBnMaxSplits * 2 * x->C;
-  bn_combine<<<(2 * x->C + 255) / 256, 256, 0, s>>>(2 * x->C, nsplit, partial, sums);
+  float* sums = partial + (size_t)bn_max_splits(x->C) * 2 * x->C;
+  bn_combine<<<(2 * x->C + 7) / 8, 256, 0, s>>>(2 * x->C, nsplit, partial, sums);
   count_launch();
   if (dgamma || dbeta) {
     bn_param_grads<<<(x->C + 127) / 128, 128, 0, s>>>(x->C, sums, dgamma, dbeta);

@@ -84,10 +84,13 @@ struct FwdParams {
   const float* bias;
   int32_t relu, accumulate;
   int32_t* status;
+  int32_t tma_store;   // epilogue: stage 64-channel chunks in shared memory, one TMA tile store each
 };
 
+constexpr int kStagingBytes = 2 * 16384;
+
 struct SmemCtl {
-  unsigned long long full[8], empty[8], tfull[2], tempty[2];
+  unsigned long long full[8], empty[8], tfull[2], tempty[2], stg_full[2], stg_free[2];
   uint32_t tmem_base;
   volatile int abort_flag;
 };
@@ -101,11 +104,12 @@ __device__ __forceinline__ uint32_t pow2_cols(uint32_t c) {
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                   const FwdParams p) {
+                   const __grid_constant__ CUtensorMap map_o, const FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   constexpr uint32_t kStageBytes = kSlabBytes + BN * 128;
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  SmemCtl* ctl = (SmemCtl*)(smem + (size_t)STAGES * kStageBytes);
+  uint8_t* osm = smem + (size_t)STAGES * kStageBytes;
+  SmemCtl* ctl = (SmemCtl*)(osm + kStagingBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t tiles_m = p.NI * p.tiles_y * p.tiles_x;
   const uint32_t total_tiles = tiles_m * p.tiles_n;
@@ -121,11 +125,14 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&ctl->tfull[a]), 1);
       mbar_init(smem_u32(&ctl->tempty[a]), 4);
+      mbar_init(smem_u32(&ctl->stg_full[a]), 4);
+      mbar_init(smem_u32(&ctl->stg_free[a]), 1);
     }
     ctl->abort_flag = 0;
     mbar_init_fence();
     tma_prefetch_desc(&map_a);
     tma_prefetch_desc(&map_b);
+    if (p.tma_store) tma_prefetch_desc(&map_o);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
@@ -194,6 +201,63 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       if (!mbar_wait(smem_u32(&ctl->tfull[acc]), acc_phase, abortf)) break;
       tc_fence_after();
       const uint32_t m = q * 32 + lane;
+      if (BN >= 64 && p.tma_store) {
+        // 64-channel chunks of the tile go through a swizzled [128 px][64 ch] staging buffer and one TMA
+        // tile store each: coalesced, clipped to the tensor, no per-thread scattered 16-byte stores.
+        bool live = true;
+#pragma unroll 1
+        for (uint32_t c64 = 0; c64 < BN / 64 && live; ++c64) {
+          const uint32_t cc = it * (BN / 64) + c64, b = cc & 1u;
+          uint8_t* stg = osm + (size_t)b * 16384;
+          bool ok = true;
+          if (cc >= 2) ok = mbar_wait(smem_u32(&ctl->stg_free[b]), ((cc >> 1) - 1u) & 1u, abortf);
+          if (!__all_sync(0xffffffffu, ok)) { live = false; break; }
+#pragma unroll
+          for (uint32_t half = 0; half < 2; ++half) {
+            uint32_t v[32];
+            tmem_ld32(tmem_base + ((q * 32u) << 16) + acc * BN + c64 * 64 + half * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const uint32_t cl = half * 32 + g * 8, cg = tn * BN + c64 * 64 + cl;
+              float f[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                f[j] = __uint_as_float(v[g * 8 + j]);
+                if (p.bias && cg + j < p.OC) f[j] += p.bias[cg + j];
+                if (p.relu) f[j] = fmaxf(f[j], 0.f);
+              }
+              uint4 pk;
+              __nv_bfloat162* p2 = (__nv_bfloat162*)&pk;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) p2[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+              *(uint4*)(stg + m * 128u + (((cl >> 3) ^ (m & 7u)) * 16u)) = pk;
+            }
+          }
+          if (c64 == BN / 64 - 1) tc_fence_before();
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            if (c64 == BN / 64 - 1) mbar_arrive(smem_u32(&ctl->tempty[acc]));   // accumulator drained
+            mbar_arrive(smem_u32(&ctl->stg_full[b]));
+          }
+          if (q == 0 && lane == 0) {
+            if (mbar_wait(smem_u32(&ctl->stg_full[b]), (cc >> 1) & 1u, abortf)) {
+              if (tn * BN + c64 * 64 < p.OC)
+                asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(&map_o),
+                             "r"(smem_u32(stg)), "r"((int)(tn * BN + c64 * 64)), "r"((int)(tx * p.TW)), "r"((int)(ty * p.TH)),
+                             "r"((int)n)
+                             : "memory");
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+              asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+              if (cc >= 1) mbar_arrive(smem_u32(&ctl->stg_free[b ^ 1u]));
+            }
+          }
+          __syncwarp();
+        }
+        if (!live) break;
+        continue;
+      }
       const uint32_t oy = ty * p.TH + m / p.TW, ox = tx * p.TW + m % p.TW;
       const bool valid = oy < p.OP && ox < p.OQ;
       __nv_bfloat16* orow = p.out + (long long)n * p.out_plane + (long long)oy * p.out_pitch + (long long)ox * p.OC;
@@ -248,6 +312,7 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&ctl->tempty[acc]));
     }
+    if (p.tma_store && q == 0 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   tc_fence_before();
@@ -481,10 +546,10 @@ static void pick_tile(uint32_t OP, uint32_t OQ, uint32_t sh, uint32_t sw, uint32
 }
 
 template <int BN>
-static int launch_fwd(const CUtensorMap& ma, const CUtensorMap& mb, const FwdParams& p, cudaStream_t s) {
+static int launch_fwd(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const FwdParams& p, cudaStream_t s) {
   constexpr int kStageBytes = kSlabBytes + BN * 128;
-  constexpr int STAGES = (200 * 1024) / kStageBytes > 8 ? 8 : (200 * 1024) / kStageBytes;
-  constexpr int smem = STAGES * kStageBytes + 1024 + (int)sizeof(SmemCtl);
+  constexpr int STAGES = (192 * 1024) / kStageBytes > 8 ? 8 : (192 * 1024) / kStageBytes;
+  constexpr int smem = STAGES * kStageBytes + kStagingBytes + 1024 + (int)sizeof(SmemCtl);
   static unsigned attr_done = 0;  // one bit per device: the attribute is per device
   int dev = 0;
   cudaGetDevice(&dev);
@@ -498,7 +563,7 @@ static int launch_fwd(const CUtensorMap& ma, const CUtensorMap& mb, const FwdPar
   }
   const uint32_t total = p.NI * p.tiles_y * p.tiles_x * p.tiles_n;
   const unsigned grid = total < (uint32_t)kNumSMs ? total : kNumSMs;
-  conv_tc_fwd_kernel<BN, STAGES><<<grid, kThreads, smem, s>>>(ma, mb, p);
+  conv_tc_fwd_kernel<BN, STAGES><<<grid, kThreads, smem, s>>>(ma, mb, mo, p);
   count_launch();
   return launch_status();
 }
@@ -561,11 +626,22 @@ static int run_fwd_gemm(const void* act, uint32_t NI, uint32_t IH, uint32_t IW, 
     int st = make_tmap_bf16(&mb, filt, 2, dims, str, box, es);
     if (st != AD_OK) return st;
   }
+  CUtensorMap mo = ma;
+  p.tma_store = (!accumulate && BN >= 64 && (OC & 7u) == 0 && !((uintptr_t)out & 15u) && (p.out_pitch % 8) == 0 &&
+                 (p.out_plane % 8) == 0) ? 1 : 0;
+  if (p.tma_store) {
+    uint64_t dims[4] = {OC, OQ, OP, NI};
+    uint64_t str[4] = {0, (uint64_t)OC * 2, (uint64_t)p.out_pitch * 2, (uint64_t)p.out_plane * 2};
+    uint32_t box[4] = {64, p.TW, p.TH, 1};
+    uint32_t es[4] = {1, 1, 1, 1};
+    int st = make_tmap_bf16(&mo, out, 4, dims, str, box, es);
+    if (st != AD_OK) return st;
+  }
   switch (BN) {
-    case 256: return launch_fwd<256>(ma, mb, p, s);
-    case 128: return launch_fwd<128>(ma, mb, p, s);
-    case 64: return launch_fwd<64>(ma, mb, p, s);
-    default: return launch_fwd<32>(ma, mb, p, s);
+    case 256: return launch_fwd<256>(ma, mb, mo, p, s);
+    case 128: return launch_fwd<128>(ma, mb, mo, p, s);
+    case 64: return launch_fwd<64>(ma, mb, mo, p, s);
+    default: return launch_fwd<32>(ma, mb, mo, p, s);
   }
 }
 

@@ -290,6 +290,38 @@ __global__ void __launch_bounds__(256) im2col_kernel(View x, uint32_t N, uint32_
     out[pix * ldo + col] = __float2bfloat16_rn(v);
   }
 }
+// Same matrix, 8 output columns (one 16-byte store) per thread; columns past kh*kw*C are written as zeros.
+template <typename T>
+__global__ void __launch_bounds__(256) im2col_vec_kernel(View x, uint32_t N, uint32_t C, uint32_t H, uint32_t W, uint32_t kh,
+                                                         uint32_t kw, uint32_t sh, uint32_t sw, uint32_t dh, uint32_t dw,
+                                                         uint32_t P, uint32_t Q, __nv_bfloat16* out, uint32_t ldo) {
+  const uint32_t cols = kh * kw * C, groups = ldo / 8;
+  const size_t total = (size_t)N * P * Q * groups, nt = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nt) {
+    const uint32_t gcol = (uint32_t)(i % groups) * 8;
+    const size_t pix = i / groups;
+    const uint32_t q = (uint32_t)(pix % Q);
+    const size_t rest = pix / Q;
+    const uint32_t p = (uint32_t)(rest % P), n = (uint32_t)(rest / P);
+    uint32_t c = gcol % C, tap = gcol / C;
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      v[j] = 0.f;
+      if (gcol + j < cols) {
+        const uint32_t s = tap % kw, r = tap / kw;
+        const uint32_t yy = p * sh + r * dh, xx = q * sw + s * dw;
+        if (yy < H && xx < W) v[j] = ld_f((const T*)x.base + voff(x, n, c, yy, xx));
+      }
+      if (++c == C) { c = 0; ++tap; }
+    }
+    uint4 pk;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+    *(uint4*)(out + pix * ldo + gcol) = pk;
+  }
+}
 }  // namespace adk
 
 extern "C" int ad_im2col(const ad_tensor4* x, uint32_t kh, uint32_t kw, uint32_t sh, uint32_t sw, uint32_t dh, uint32_t dw,
@@ -299,6 +331,13 @@ extern "C" int ad_im2col(const ad_tensor4* x, uint32_t kh, uint32_t kw, uint32_t
   const size_t total = (size_t)x->N * P * Q * kh * kw * x->C;
   if (total == 0) return AD_OK;
   adk::View v = adk::view_of(x);
+  if ((ldo & 7u) == 0 && ((uintptr_t)out_bf16 & 15u) == 0) {
+    const size_t tv = (size_t)x->N * P * Q * (ldo / 8);
+    AD_DISPATCH_DTYPE(x->dtype, (adk::im2col_vec_kernel<T><<<adk::grid_for(tv, 256, 16), 256, 0, adk::as_stream(stream)>>>(
+                                    v, x->N, x->C, x->H, x->W, kh, kw, sh, sw, dh, dw, P, Q, (__nv_bfloat16*)out_bf16, ldo)));
+    adk::count_launch();
+    return adk::launch_status();
+  }
   AD_DISPATCH_DTYPE(x->dtype, (adk::im2col_kernel<T><<<adk::grid_for(total, 256, 16), 256, 0, adk::as_stream(stream)>>>(
                                   v, x->N, x->C, x->H, x->W, kh, kw, sh, sw, dh, dw, P, Q, (__nv_bfloat16*)out_bf16, ldo)));
   adk::count_launch();

@@ -115,6 +115,20 @@ public:
     }
     return buf_->writers.insert(node.raw_id()).second;
   }
+  // accumulate() for a contributor that may write the WHOLE buffer: returns 0 if `node` has already
+  // contributed in this transaction, 2 if it is the first contributor and covers(buffer) holds -- it
+  // then OVERWRITES (no zero fill, no read of the old value) -- and 1 (add; init has run if needed) otherwise.
+  int accumulate_full(TxnId txn, NodeId node, function<bool(V&)> covers, function<void(V*)> init) {
+    ensure();
+    if (!buf_->curr_txn || *buf_->curr_txn != txn.raw_id()) {
+      buf_->curr_txn = txn.raw_id(); buf_->rollover = false; buf_->writers.clear();
+      buf_->writers.insert(node.raw_id());
+      if (covers && covers(*buf_->buffer)) return 2;
+      if (init) init(&*buf_->buffer);
+      return 1;
+    }
+    return buf_->writers.insert(node.raw_id()).second ? 1 : 0;
+  }
   V& get(TxnId txn, NodeId) { assert(buf_->buffer && buf_->curr_txn && *buf_->curr_txn == txn.raw_id()); return *buf_->buffer; }
   V& get_excl(TxnId txn, NodeId n) { return get(txn, n); }
   V& get_mut(TxnId txn, NodeId n) { return get(txn, n); }

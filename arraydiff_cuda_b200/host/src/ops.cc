@@ -75,6 +75,10 @@ static void copy_window(const Act& src, size_t sx, size_t sy, const Act& dst, si
   }
 }
 
+// a writer of the interior covers the whole buffer exactly when there is no padding
+static bool unpadded(Act& a) { return a.offset().shape[0] == 0 && a.offset().shape[1] == 0; }
+static bool always(Act&) { return true; }
+
 static function<void(Act*)> zero_init(GPUContext* g) {
   return [g](Act* a) { GPUConn c = g->conn(); a->zero(c); };
 }
@@ -256,12 +260,13 @@ void SpatialGather2DOpF::_forward(TxnId txn) {
 }
 void SpatialGather2DOpF::_backward(TxnId txn) {
   auto xd = x_->data();
-  if (!xd.grad.accumulate(txn, id(), zero_init(gpu()))) return;
+  const int mode = xd.grad.accumulate_full(txn, id(), unpadded, zero_init(gpu()));
+  if (!mode) return;
   GPUConn conn = gpu()->conn();
   Act& dx = xd.grad.get_mut(txn, id());
   Act& dy = y_.grad.get(txn, id());
   const size_t h = dx.dim().shape[1];
-  copy_window(dy, 0, rank_ * h, dx, dx.offset().shape[0], dx.offset().shape[1], dim_.shape[0], h, true, conn.stream());
+  copy_window(dy, 0, rank_ * h, dx, dx.offset().shape[0], dx.offset().shape[1], dim_.shape[0], h, mode == 1, conn.stream());
 }
 
 // ------------------------------------------------------------------ halo pad / unpad / repad
@@ -285,11 +290,12 @@ void HaloPad2DOpF::_forward(TxnId txn) {
 }
 void HaloPad2DOpF::_backward(TxnId txn) {
   auto xd = x_->data();
-  if (!xd.grad.accumulate(txn, id(), zero_init(gpu()))) return;
+  const int mode = xd.grad.accumulate_full(txn, id(), unpadded, zero_init(gpu()));
+  if (!mode) return;
   GPUConn conn = gpu()->conn();
   Act& dx = xd.grad.get_mut(txn, id());
   Act& dy = y_.grad.get(txn, id());
-  copy_window(dy, pad_, pad_, dx, dx.offset().shape[0], dx.offset().shape[1], dim_.shape[0], dim_.shape[1], true, conn.stream());
+  copy_window(dy, pad_, pad_, dx, dx.offset().shape[0], dx.offset().shape[1], dim_.shape[0], dim_.shape[1], mode == 1, conn.stream());
 }
 
 vector<ActVar> HaloUnpad2DOpF::MakeParallel(size_t halo_pad, vector<ActVar> inputs, shared_ptr<Context> ctx) {
@@ -538,10 +544,11 @@ void CudnnConv2DOpF::_backward(TxnId txn) {
   // data gradient over the whole padded extent, halo rows included (reference src/op.cc:1687-1724)
   if (use_im2col_) return;   // first layer: its input is data and takes no gradient
   auto xd = x_->data();
-  if (xd.grad.accumulate(txn, id(), zero_init(g))) {
+  // halo-padded input: the gradient covers the whole padded extent; packed input: the whole packed extent
+  if (const int mode = xd.grad.accumulate_full(txn, id(), shape_.halo_padded_input ? always : unpadded, zero_init(g))) {
     Act& dx = xd.grad.get_mut(txn, id());
     a.dx = dx.base_dptr();
-    a.accumulate = 1;
+    a.accumulate = mode == 1 ? 1 : 0;
     if (f32) {
       a.w = kd.val.get(txn, id()).dptr();
       AD_CHECK(ad_conv2d_dgrad(&a, s));
@@ -582,7 +589,8 @@ void CudnnPool2DOpF::_forward(TxnId txn) {
 }
 void CudnnPool2DOpF::_backward(TxnId txn) {
   auto xd = x_->data();
-  if (!xd.grad.accumulate(txn, id(), zero_init(gpu()))) return;
+  const int mode = xd.grad.accumulate_full(txn, id(), shape_.halo_padded_input ? always : unpadded, zero_init(gpu()));
+  if (!mode) return;
   GPUConn conn = gpu()->conn();
   Act& x = xd.val.get(txn, id());
   Act& dx = xd.grad.get_mut(txn, id());
@@ -590,7 +598,7 @@ void CudnnPool2DOpF::_backward(TxnId txn) {
   ad_tensor4 dxv = shape_.halo_padded_input ? dx.view_base() : dx.view_interior();
   ad_tensor4 dyv = y_.grad.get(txn, id()).view_interior();
   AD_CHECK(ad_maxpool2d_bwd(&xv, &dyv, &dxv, (uint32_t)shape_.window[1], (uint32_t)shape_.window[0], (uint32_t)shape_.stride[1],
-                            (uint32_t)shape_.stride[0], 1, conn.stream()));
+                            (uint32_t)shape_.stride[0], mode == 1 ? 1 : 0, conn.stream()));
 }
 
 // ------------------------------------------------------------------ batch norm (+ fused ReLU)
@@ -651,8 +659,8 @@ void CudnnBatchNorm2DOpF::_backward(TxnId txn) {
   auto xd = x_->data();
   auto zero1 = [g](Stat* a) { GPUConn c = g->conn(); AD_CHECK(ad_fill_zero(a->dptr(), a->flat_size() * 4, c.stream())); };
   auto sd = scale_->data(), hd = shift_->data();
-  const bool first = xd.grad.accumulate(txn, id(), zero_init(g));
-  if (!first) return;
+  const int mode = xd.grad.accumulate_full(txn, id(), unpadded, zero_init(g));
+  if (!mode) return;
   sd.grad.accumulate(txn, id(), zero1);
   hd.grad.accumulate(txn, id(), zero1);
   GPUConn conn = g->conn();
@@ -661,7 +669,7 @@ void CudnnBatchNorm2DOpF::_backward(TxnId txn) {
   ad_tensor4 xv = xd.val.get(txn, id()).view_interior(), dyv = y_.grad.get(txn, id()).view_interior(),
              dxv = xd.grad.get_mut(txn, id()).view_interior();
   AD_CHECK(ad_bn_bwd(&xv, &dyv, &dxv, sd.val.get(txn, id()).dptr(), hd.val.get(txn, id()).dptr(), save_mean_, save_invstd_,
-                     sd.grad.get_mut(txn, id()).dptr(), hd.grad.get_mut(txn, id()).dptr(), relu_ ? 1 : 0, 1, g->get_scratch(),
+                     sd.grad.get_mut(txn, id()).dptr(), hd.grad.get_mut(txn, id()).dptr(), relu_ ? 1 : 0, mode == 1 ? 1 : 0, g->get_scratch(),
                      g->scratch_size(), conn.stream()));
 }
 
@@ -681,11 +689,12 @@ void CudnnActivationOpF::_forward(TxnId txn) {
 }
 void CudnnActivationOpF::_backward(TxnId txn) {
   auto xd = x_->data();
-  if (!xd.grad.accumulate(txn, id(), zero_init(gpu()))) return;
+  const int mode = xd.grad.accumulate_full(txn, id(), unpadded, zero_init(gpu()));
+  if (!mode) return;
   GPUConn conn = gpu()->conn();
   ad_tensor4 xv = xd.val.get(txn, id()).view_interior(), dyv = y_.grad.get(txn, id()).view_interior(),
              dxv = xd.grad.get_mut(txn, id()).view_interior();
-  AD_CHECK(ad_relu_bwd(&xv, &dyv, &dxv, 1, conn.stream()));
+  AD_CHECK(ad_relu_bwd(&xv, &dyv, &dxv, mode == 1 ? 1 : 0, conn.stream()));
 }
 
 ActVar SumJoinOpF::Make(vector<ActVar> xs, shared_ptr<Context> ctx) { return make_shared<SumJoinOpF>(xs, ctx); }
@@ -710,9 +719,10 @@ void SumJoinOpF::_backward(TxnId txn) {
   ad_tensor4 dyv = y_.grad.get(txn, id()).view_interior();
   for (auto& x : xs_) {
     auto xd = x->data();
-    if (!xd.grad.accumulate(txn, id(), zero_init(gpu()))) continue;
+    const int mode = xd.grad.accumulate_full(txn, id(), unpadded, zero_init(gpu()));
+    if (!mode) continue;
     ad_tensor4 dxv = xd.grad.get_mut(txn, id()).view_interior();
-    AD_CHECK(ad_convert(&dyv, &dxv, 1, conn.stream()));
+    AD_CHECK(ad_convert(&dyv, &dxv, mode == 1 ? 1 : 0, conn.stream()));
   }
 }
 
