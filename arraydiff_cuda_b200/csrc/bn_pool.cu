@@ -11,9 +11,10 @@ namespace adk {
 
 constexpr int kBnMaxSplits = 128;
 // Partial-sum rows a reduction may use for C channels: as many as fit the scratch of the widest layer
-// ((128 + 1) rows of 2 * 2048 floats), at most 1024 -- narrow layers get more blocks in flight.
+// ((128 + 1) rows of 2 * 2048 floats) beside the two trailing rows (combined sums, their means), at
+// most 1024 -- narrow layers get more blocks in flight.
 __host__ __device__ inline int bn_max_splits(uint32_t C) {
-  long long s = (long long)(kBnMaxSplits + 1) * 2 * 2048 / (2ll * (C ? C : 1)) - 1;
+  long long s = (long long)(kBnMaxSplits + 1) * 2 * 2048 / (2ll * (C ? C : 1)) - 2;
   return (int)(s > 1024 ? 1024 : (s < 1 ? 1 : s));
 }
 
@@ -97,39 +98,58 @@ __global__ void __launch_bounds__(256) bn_reduce_cfast(BnRed p, float* partial) 
   }
 }
 
-__device__ __forceinline__ double warp_sum_f64(double v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
-}
-
-// sums[0..2C) = sum over splits (double accumulate); one warp per entry, lanes stride over the splits.
-__global__ void __launch_bounds__(256) bn_combine(uint32_t C2, int nsplit, const float* __restrict__ partial, float* sums) {
-  const uint32_t i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (i >= C2) return;
-  double t = 0.0;
-  for (int s = lane; s < nsplit; s += 32) t += (double)partial[(size_t)s * C2 + i];
-  t = warp_sum_f64(t);
-  if (lane == 0) sums[i] = (float)t;
-}
-
-// mean / invstd / var from sums; double arithmetic for the cancellation in E[x^2]-E[x]^2.  One warp per channel.
-__global__ void __launch_bounds__(256) bn_finalize(uint32_t C, int nsplit, const float* __restrict__ partial_or_sums, double count,
-                                                   float eps, float* mean, float* invstd, float* var) {
-  const uint32_t c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (c >= C) return;
+// Stage 2 of the statistics, 32 channels per block: 8 row lanes walk the partial rows (each warp
+// access is one 128-byte line), sum in double, and are combined in a fixed order.
+//   kind 0: mean / invstd / var from (sum x, sum x^2); double arithmetic for the cancellation in E[x^2]-E[x]^2
+//   kind 1: sums[0..2C) = (sum g, sum g*xhat), sums[2C..4C) = those over count; dbeta += sum g, dgamma += sum g*xhat
+//   kind 2: sums[0..2C) only
+__global__ void __launch_bounds__(256) bn_finish(int kind, uint32_t C, int nsplit, const float* __restrict__ partial,
+                                                 double count, float eps, float* mean, float* invstd, float* var,
+                                                 float* sums, float* dgamma, float* dbeta) {
+  const uint32_t lane = threadIdx.x & 31, rl = threadIdx.x >> 5, c = blockIdx.x * 32 + lane;
   double s = 0.0, ss = 0.0;
-  for (int k = lane; k < nsplit; k += 32) {
-    s += (double)partial_or_sums[(size_t)k * 2 * C + c];
-    ss += (double)partial_or_sums[(size_t)k * 2 * C + C + c];
+  if (c < C) {
+    int k = rl;
+    for (; k + 24 < nsplit; k += 32) {
+      float v[4], w[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        v[u] = partial[(size_t)(k + 8 * u) * 2 * C + c];
+        w[u] = partial[(size_t)(k + 8 * u) * 2 * C + C + c];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) { s += (double)v[u]; ss += (double)w[u]; }
+    }
+    for (; k < nsplit; k += 8) {
+      s += (double)partial[(size_t)k * 2 * C + c];
+      ss += (double)partial[(size_t)k * 2 * C + C + c];
+    }
   }
-  s = warp_sum_f64(s); ss = warp_sum_f64(ss);
-  if (lane != 0) return;
-  double m = s / count, v = ss / count - m * m;
-  if (v < 0.0) v = 0.0;
-  if (mean) mean[c] = (float)m;
-  if (invstd) invstd[c] = (float)(1.0 / sqrt(v + (double)eps));
-  if (var) var[c] = (float)v;
+  __shared__ double sh[2][8][32];
+  sh[0][rl][lane] = s;
+  sh[1][rl][lane] = ss;
+  __syncthreads();
+  if (rl != 0 || c >= C) return;
+  s = 0.0; ss = 0.0;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) { s += sh[0][w][lane]; ss += sh[1][w][lane]; }
+  if (kind == 0) {
+    double m = s / count, v = ss / count - m * m;
+    if (v < 0.0) v = 0.0;
+    if (mean) mean[c] = (float)m;
+    if (invstd) invstd[c] = (float)(1.0 / sqrt(v + (double)eps));
+    if (var) var[c] = (float)v;
+    return;
+  }
+  const float fs = (float)s, fss = (float)ss;
+  sums[c] = fs;
+  sums[C + c] = fss;
+  if (kind == 1) {
+    sums[2 * C + c] = (float)((double)fs / count);
+    sums[3 * C + c] = (float)((double)fss / count);
+    if (dbeta) dbeta[c] += fs;
+    if (dgamma) dgamma[c] += fss;
+  }
 }
 
 struct BnApply {
@@ -137,7 +157,7 @@ struct BnApply {
   uint32_t N, C, H, W;
   int c_fastest, relu, accumulate;
   const float *gamma, *beta, *mean, *invstd;
-  const float* partial;  // backward: combined sums [2C]
+  const float* partial;  // backward: combined sums [2C], then (vector path) those over count [2C]
   int nsplit;
   double count;
 };
@@ -173,13 +193,6 @@ __global__ void __launch_bounds__(256) bn_apply(BnApply p) {
   }
 }
 
-__global__ void bn_param_grads(uint32_t C, const float* __restrict__ sums, float* dgamma, float* dbeta) {
-  uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
-  if (dbeta) dbeta[c] += sums[c];
-  if (dgamma) dgamma[c] += sums[C + c];
-}
-
 
 // ------------------------------------------------------------------ NHWC bf16 fast paths
 // Channel-fastest bf16 views whose strides are multiples of 8 elements: a thread owns 8 adjacent
@@ -197,39 +210,58 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
   return v;
 }
-__device__ __forceinline__ long long pix_off(const BView& v, size_t i, uint32_t H, uint32_t W) {
-  const uint32_t x = (uint32_t)(i % W);
-  const size_t r = i / W;
-  const uint32_t y = (uint32_t)(r % H), n = (uint32_t)(r / H);
+// Element offset of pixel i (n, y, x flattened).  Views whose pixels are evenly spaced need no division;
+// others decode with 32-bit arithmetic (the launchers require N*H*W < 2^31).
+__device__ __forceinline__ long long pix_off(const BView& v, uint32_t i, uint32_t H, uint32_t W) {
+  if (v.sy == (long long)W * v.sx && v.sn == (long long)H * v.sy) return (long long)i * v.sx;
+  const uint32_t r = i / W, x = i - r * W, n = r / H, y = r - n * H;
   return n * v.sn + y * v.sy + x * v.sx;
 }
+__device__ __forceinline__ uint4 ld16(const BView& v, long long off) {
+  return *(const uint4*)((const __nv_bfloat16*)v.base + off);
+}
+
+constexpr int kBnUnroll = 4;  // pixels in flight per thread: all loads of a batch are issued before any use
 
 template <int MODE>
-__global__ void __launch_bounds__(256) bn_reduce_vec(BnRed p, float* partial) {
+__global__ void __launch_bounds__(256, 2) bn_reduce_vec(BnRed p, float* partial) {
   const uint32_t G = p.C / 8, cg = threadIdx.x % G, pl = threadIdx.x / G, PL = 256 / G;
-  const size_t per = (size_t)p.N * p.H * p.W;
+  const uint32_t per = p.N * p.H * p.W, stride = gridDim.x * PL;
   float a[8], b[8], mean[8], invstd[8], gam[8], bet[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     a[j] = b[j] = 0.f;
     if (MODE == 1) { mean[j] = p.mean[cg * 8 + j]; invstd[j] = p.invstd[cg * 8 + j]; gam[j] = p.gamma[cg * 8 + j]; bet[j] = p.beta[cg * 8 + j]; }
   }
-  for (size_t i = (size_t)blockIdx.x * PL + pl; i < per; i += (size_t)gridDim.x * PL) {
-    float xv[8];
-    unpack8(*(const uint4*)((const __nv_bfloat16*)p.x.base + pix_off(p.x, i, p.H, p.W) + cg * 8), xv);
-    if (MODE == 0) {
+  for (uint32_t i0 = blockIdx.x * PL + pl; i0 < per; i0 += kBnUnroll * stride) {
+    uint4 xr[kBnUnroll], gr[kBnUnroll];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { a[j] += xv[j]; b[j] = fmaf(xv[j], xv[j], b[j]); }
-    } else {
-      float g[8];
-      unpack8(*(const uint4*)((const __nv_bfloat16*)p.dy.base + pix_off(p.dy, i, p.H, p.W) + cg * 8), g);
+    for (int u = 0; u < kBnUnroll; ++u) {
+      const uint32_t i = i0 + u * stride;
+      if (i < per) {
+        xr[u] = ld16(p.x, pix_off(p.x, i, p.H, p.W) + cg * 8);
+        if (MODE == 1) gr[u] = ld16(p.dy, pix_off(p.dy, i, p.H, p.W) + cg * 8);
+      }
+    }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float xhat = (xv[j] - mean[j]) * invstd[j];
-        float gj = g[j];
-        if (p.relu && fmaf(gam[j], xhat, bet[j]) <= 0.f) gj = 0.f;
-        a[j] += gj;
-        b[j] = fmaf(gj, xhat, b[j]);
+    for (int u = 0; u < kBnUnroll; ++u) {
+      if (i0 + u * stride >= per) break;
+      float xv[8];
+      unpack8(xr[u], xv);
+      if (MODE == 0) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { a[j] += xv[j]; b[j] = fmaf(xv[j], xv[j], b[j]); }
+      } else {
+        float g[8];
+        unpack8(gr[u], g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xhat = (xv[j] - mean[j]) * invstd[j];
+          float gj = g[j];
+          if (p.relu && fmaf(gam[j], xhat, bet[j]) <= 0.f) gj = 0.f;
+          a[j] += gj;
+          b[j] = fmaf(gj, xhat, b[j]);
+        }
       }
     }
   }
@@ -237,65 +269,85 @@ __global__ void __launch_bounds__(256) bn_reduce_vec(BnRed p, float* partial) {
 #pragma unroll
   for (int j = 0; j < 8; ++j) { sa[threadIdx.x][j] = a[j]; sb[threadIdx.x][j] = b[j]; }
   __syncthreads();
-  if (pl == 0) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float ta = 0.f, tb = 0.f;
-      for (uint32_t q = 0; q < PL; ++q) { ta += sa[q * G + cg][j]; tb += sb[q * G + cg][j]; }
-      partial[(size_t)blockIdx.x * 2 * p.C + cg * 8 + j] = ta;
-      partial[(size_t)blockIdx.x * 2 * p.C + p.C + cg * 8 + j] = tb;
-    }
+  // thread t < 2C sums one of the block's 2C outputs over the pixel lanes, in lane order
+  for (uint32_t t = threadIdx.x; t < 2 * p.C; t += 256) {
+    const uint32_t which = t / p.C, c = t - which * p.C, g = c >> 3, j = c & 7;
+    float acc = 0.f;
+    for (uint32_t q = 0; q < PL; ++q) acc += which ? sb[q * G + g][j] : sa[q * G + g][j];
+    partial[(size_t)blockIdx.x * 2 * p.C + t] = acc;
   }
 }
 
-template <int MODE>
-__global__ void __launch_bounds__(256) bn_apply_vec(BnApply p) {
+// U pixels in flight per thread (the backward form holds three 16-byte values per pixel, so fewer)
+template <int MODE, int U = (MODE == 0 ? kBnUnroll : 2)>
+__global__ void __launch_bounds__(256, 2) bn_apply_vec(BnApply p) {
   const uint32_t G = p.C / 8, cg = threadIdx.x % G, pl = threadIdx.x / G, PL = 256 / G;
-  const size_t per = (size_t)p.N * p.H * p.W;
+  const uint32_t per = p.N * p.H * p.W, stride = gridDim.x * PL;
   float sc[8], sh[8], mean[8], invstd[8], m1[8], m2[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const uint32_t c = cg * 8 + j;
     mean[j] = p.mean[c]; invstd[j] = p.invstd[c];
     sc[j] = p.gamma[c]; sh[j] = p.beta[c];
-    if (MODE == 1) { m1[j] = (float)((double)p.partial[c] / p.count); m2[j] = (float)((double)p.partial[p.C + c] / p.count); }
+    if (MODE == 1) { m1[j] = p.partial[2 * p.C + c]; m2[j] = p.partial[3 * p.C + c]; }
   }
-  for (size_t i = (size_t)blockIdx.x * PL + pl; i < per; i += (size_t)gridDim.x * PL) {
-    float xv[8], o[8];
-    unpack8(*(const uint4*)((const __nv_bfloat16*)p.x.base + pix_off(p.x, i, p.H, p.W) + cg * 8), xv);
-    uint4* op = (uint4*)((__nv_bfloat16*)p.out.base + pix_off(p.out, i, p.H, p.W) + cg * 8);
-    if (MODE == 0) {
+  for (uint32_t i0 = blockIdx.x * PL + pl; i0 < per; i0 += U * stride) {
+    uint4 xr[U], gr[U], oldr[U];
+    uint4* op[U];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float xhat = (xv[j] - mean[j]) * invstd[j];
-        float v = fmaf(sc[j], xhat, sh[j]);
-        o[j] = p.relu ? fmaxf(v, 0.f) : v;
-      }
-    } else {
-      float g[8], old[8];
-      unpack8(*(const uint4*)((const __nv_bfloat16*)p.dy.base + pix_off(p.dy, i, p.H, p.W) + cg * 8), g);
-      if (p.accumulate) unpack8(*op, old);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float xhat = (xv[j] - mean[j]) * invstd[j];
-        float gj = g[j];
-        if (p.relu && fmaf(sc[j], xhat, sh[j]) <= 0.f) gj = 0.f;
-        float v = sc[j] * invstd[j] * (gj - m1[j] - xhat * m2[j]);
-        o[j] = p.accumulate ? v + old[j] : v;
+    for (int u = 0; u < U; ++u) {
+      const uint32_t i = i0 + u * stride;
+      if (i < per) {
+        xr[u] = ld16(p.x, pix_off(p.x, i, p.H, p.W) + cg * 8);
+        op[u] = (uint4*)((__nv_bfloat16*)p.out.base + pix_off(p.out, i, p.H, p.W) + cg * 8);
+        if (MODE == 1) {
+          gr[u] = ld16(p.dy, pix_off(p.dy, i, p.H, p.W) + cg * 8);
+          if (p.accumulate) oldr[u] = *op[u];
+        }
       }
     }
-    *op = pack8(o);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (i0 + u * stride >= per) break;
+      float xv[8], o[8];
+      unpack8(xr[u], xv);
+      if (MODE == 0) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xhat = (xv[j] - mean[j]) * invstd[j];
+          float v = fmaf(sc[j], xhat, sh[j]);
+          o[j] = p.relu ? fmaxf(v, 0.f) : v;
+        }
+      } else {
+        float g[8], old[8];
+        unpack8(gr[u], g);
+        if (p.accumulate) unpack8(oldr[u], old);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xhat = (xv[j] - mean[j]) * invstd[j];
+          float gj = g[j];
+          if (p.relu && fmaf(sc[j], xhat, sh[j]) <= 0.f) gj = 0.f;
+          float v = sc[j] * invstd[j] * (gj - m1[j] - xhat * m2[j]);
+          o[j] = p.accumulate ? v + old[j] : v;
+        }
+      }
+      *op[u] = pack8(o);
+    }
   }
 }
 
 static bool vec_view_ok(const ad_tensor4* t) {
   if (t->dtype != AD_BF16 || t->sc != 1 || (t->C & 7u) || t->C < 8 || t->C > 2048) return false;
   if (256 % (t->C / 8)) return false;
+  if ((size_t)t->N * t->H * t->W >= (1ull << 31)) return false;
   return !((uintptr_t)t->base & 15u) && !(t->sn & 7) && !(t->sy & 7) && !(t->sx & 7);
 }
+// blocks of the vector reduction = partial rows: enough to fill the machine, each thread with
+// at least one batch of pixels, within the rows the scratch holds
 static unsigned vec_grid(const ad_tensor4* t) {
   const size_t per = (size_t)t->N * t->H * t->W, PL = 256 / (t->C / 8);
-  size_t g = (per + PL * 2 - 1) / (PL * 2);
+  size_t g = (per + PL * kBnUnroll - 1) / (PL * kBnUnroll);
+  if (g > (size_t)kNumSMs * 4) g = (size_t)kNumSMs * 4;
   if (g > (size_t)bn_max_splits(t->C)) g = bn_max_splits(t->C);
   return (unsigned)(g < 1 ? 1 : g);
 }
@@ -473,6 +525,75 @@ __global__ void __launch_bounds__(256) maxpool_bwd_vec(PoolP p) {
     *op = pack8(acc);
   }
 }
+// Tiled backward for NHWC bf16: a block owns a 16 x 16 patch of input pixels for up to 8 channel groups.
+// Phase 1 finds, once per window that touches the patch, the position (4 bits per channel) of the window's
+// first maximum; phase 2 lets every input pixel pick its gradient from the windows over it.  Same
+// first-maximum rule and the same summation order (q, then s, ascending) as the kernels above, with a
+// ninth of their loads when windows overlap.
+constexpr uint32_t kPoolTile = 16, kPoolMaxWin = 400;
+__global__ void __launch_bounds__(256) maxpool_bwd_tile(PoolP p, uint32_t gchunks) {
+  __shared__ uint32_t widx[kPoolMaxWin][8];
+  const uint32_t G = p.C / 8, gc = blockIdx.x % gchunks, tx = blockIdx.x / gchunks, ty = blockIdx.y, n = blockIdx.z;
+  const uint32_t g0 = gc * 8, gcnt = G - g0 < 8 ? G - g0 : 8;
+  const uint32_t y0 = ty * kPoolTile, x0 = tx * kPoolTile;
+  const uint32_t y1 = y0 + kPoolTile < p.H ? y0 + kPoolTile : p.H, x1 = x0 + kPoolTile < p.W ? x0 + kPoolTile : p.W;
+  const uint32_t q_lo = y0 + 1 > p.kh ? (y0 + 1 - p.kh + p.sh - 1) / p.sh : 0;
+  const uint32_t s_lo = x0 + 1 > p.kw ? (x0 + 1 - p.kw + p.sw - 1) / p.sw : 0;
+  const uint32_t q_hi = (y1 - 1) / p.sh < p.P - 1 ? (y1 - 1) / p.sh : p.P - 1;   // inclusive
+  const uint32_t s_hi = (x1 - 1) / p.sw < p.Q - 1 ? (x1 - 1) / p.sw : p.Q - 1;
+  const uint32_t nq = q_hi >= q_lo ? q_hi - q_lo + 1 : 0, ns = s_hi >= s_lo ? s_hi - s_lo + 1 : 0;
+  const __nv_bfloat16* xb = (const __nv_bfloat16*)p.x.base + n * p.x.sn;
+  for (uint32_t it = threadIdx.x; it < nq * ns * gcnt; it += 256) {
+    const uint32_t cgl = it % gcnt, w = it / gcnt, s = s_lo + w % ns, q = q_lo + w / ns;
+    float best[8];
+    uint32_t word = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) best[j] = -INFINITY;
+    for (uint32_t a = 0; a < p.kh; ++a)
+      for (uint32_t b = 0; b < p.kw; ++b) {
+        float v[8];
+        unpack8(*(const uint4*)(xb + (q * p.sh + a) * p.x.sy + (s * p.sw + b) * p.x.sx + (g0 + cgl) * 8), v);
+        const uint32_t pos = a * p.kw + b;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (v[j] > best[j] || pos == 0) { best[j] = v[j]; word = (word & ~(15u << (4 * j))) | (pos << (4 * j)); }
+      }
+    widx[w][cgl] = word;
+  }
+  __syncthreads();
+  const __nv_bfloat16* gb = (const __nv_bfloat16*)p.dy.base + n * p.dy.sn;
+  for (uint32_t it = threadIdx.x; it < kPoolTile * kPoolTile * gcnt; it += 256) {
+    const uint32_t cgl = it % gcnt, pix = it / gcnt, x = x0 + pix % kPoolTile, y = y0 + pix / kPoolTile;
+    if (y >= p.H || x >= p.W) continue;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    const uint32_t qa = y + 1 > p.kh ? (y + 1 - p.kh + p.sh - 1) / p.sh : 0;
+    const uint32_t sa = x + 1 > p.kw ? (x + 1 - p.kw + p.sw - 1) / p.sw : 0;
+    for (uint32_t q = qa; q < p.P && q * p.sh <= y; ++q)
+      for (uint32_t s = sa; s < p.Q && s * p.sw <= x; ++s) {
+        const uint32_t word = widx[(q - q_lo) * ns + (s - s_lo)][cgl], pos = (y - q * p.sh) * p.kw + (x - s * p.sw);
+        float g[8];
+        unpack8(*(const uint4*)(gb + q * p.dy.sy + s * p.dy.sx + (g0 + cgl) * 8), g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) if (((word >> (4 * j)) & 15u) == pos) acc[j] += g[j];
+      }
+    uint4* op = (uint4*)((__nv_bfloat16*)p.dx.base + n * p.dx.sn + y * p.dx.sy + x * p.dx.sx + (g0 + cgl) * 8);
+    if (p.accumulate) {
+      float old[8];
+      unpack8(*op, old);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += old[j];
+    }
+    *op = pack8(acc);
+  }
+}
+// the tile kernel's limits: positions fit 4 bits, the windows over a patch fit its table
+static bool pool_tile_ok(const PoolP& p) {
+  if (p.kh * p.kw > 16 || p.N > 65535) return false;
+  const uint32_t mq = (kPoolTile + p.kh - 2) / p.sh + 1, ms = (kPoolTile + p.kw - 2) / p.sw + 1;
+  return mq * ms <= kPoolMaxWin && (p.H + kPoolTile - 1) / kPoolTile <= 65535;
+}
 static bool pool_vec_ok(const ad_tensor4* t) {
   return t->dtype == AD_BF16 && t->sc == 1 && (t->C & 7u) == 0 && !((uintptr_t)t->base & 15u) && !(t->sn & 7) &&
          !(t->sy & 7) && !(t->sx & 7);
@@ -482,7 +603,7 @@ static bool pool_vec_ok(const ad_tensor4* t) {
 
 using namespace adk;
 
-extern "C" size_t ad_bn_scratch_bytes(uint32_t C) { return (size_t)(bn_max_splits(C) + 1) * 2 * C * sizeof(float); }
+extern "C" size_t ad_bn_scratch_bytes(uint32_t C) { return (size_t)(bn_max_splits(C) + 2) * 2 * C * sizeof(float); }
 
 extern "C" int ad_bn_partial_stats(const ad_tensor4* x, float* sums, void* scratch, size_t scratch_bytes, void* stream) {
   if (!x || !x->base || !sums || !scratch) return AD_ERR_BAD_ARG;
@@ -492,7 +613,8 @@ extern "C" int ad_bn_partial_stats(const ad_tensor4* x, float* sums, void* scrat
   int nsplit = 1;
   int st = launch_reduce<0>(p, x, (float*)scratch, nsplit, s);
   if (st != AD_OK) return st;
-  bn_combine<<<(2 * x->C + 7) / 8, 256, 0, s>>>(2 * x->C, nsplit, (const float*)scratch, sums);
+  bn_finish<<<(x->C + 31) / 32, 256, 0, s>>>(2, x->C, nsplit, (const float*)scratch, 1.0, 0.f, nullptr, nullptr, nullptr, sums,
+                                             nullptr, nullptr);
   count_launch();
   return launch_status();
 }
@@ -503,7 +625,8 @@ extern "C" int ad_bn_finalize_apply(const ad_tensor4* x, const ad_tensor4* y, co
   if (!x || !y || !x->base || !y->base || !sums || !gamma || !beta || !save_mean || !save_invstd) return AD_ERR_BAD_ARG;
   if (!dims_eq(x, y) || count <= 0.0) return AD_ERR_BAD_ARG;
   cudaStream_t s = as_stream(stream);
-  bn_finalize<<<(x->C + 7) / 8, 256, 0, s>>>(x->C, 1, sums, count, eps, save_mean, save_invstd, batch_var);
+  bn_finish<<<(x->C + 31) / 32, 256, 0, s>>>(0, x->C, 1, sums, count, eps, save_mean, save_invstd, batch_var, nullptr, nullptr,
+                                             nullptr);
   count_launch();
   BnApply a{bview(x), bview(x), bview(y), x->N, x->C, x->H, x->W, y->sc == 1 && y->C > 1, relu, 0,
             gamma, beta, save_mean, save_invstd, nullptr, 1, count};
@@ -528,8 +651,8 @@ extern "C" int ad_bn_fwd_train(const ad_tensor4* x, const ad_tensor4* y, const f
   int st = launch_reduce<0>(p, x, (float*)scratch, nsplit, s);
   if (st != AD_OK) return st;
   const double count = (double)x->N * x->H * x->W;
-  bn_finalize<<<(x->C + 7) / 8, 256, 0, s>>>(x->C, nsplit, (const float*)scratch, count, eps, save_mean,
-                                                 save_invstd, batch_var);
+  bn_finish<<<(x->C + 31) / 32, 256, 0, s>>>(0, x->C, nsplit, (const float*)scratch, count, eps, save_mean, save_invstd,
+                                             batch_var, nullptr, nullptr, nullptr);
   count_launch();
   BnApply a{bview(x), bview(x), bview(y), x->N, x->C, x->H, x->W, y->sc == 1 && y->C > 1, relu, 0,
             gamma, beta, save_mean, save_invstd, nullptr, 1, count};
@@ -556,14 +679,11 @@ extern "C" int ad_bn_bwd(const ad_tensor4* x, const ad_tensor4* dy, const ad_ten
   int st = launch_reduce<1>(p, x, partial, nsplit, s);
   if (st != AD_OK) return st;
   float* sums = partial + (size_t)bn_max_splits(x->C) * 2 * x->C;
-  bn_combine<<<(2 * x->C + 7) / 8, 256, 0, s>>>(2 * x->C, nsplit, partial, sums);
+  const double count = (double)x->N * x->H * x->W;
+  bn_finish<<<(x->C + 31) / 32, 256, 0, s>>>(1, x->C, nsplit, partial, count, 0.f, nullptr, nullptr, nullptr, sums, dgamma, dbeta);
   count_launch();
-  if (dgamma || dbeta) {
-    bn_param_grads<<<(x->C + 127) / 128, 128, 0, s>>>(x->C, sums, dgamma, dbeta);
-    count_launch();
-  }
   BnApply a{bview(x), bview(dy), bview(dx), x->N, x->C, x->H, x->W, dx->sc == 1 && dx->C > 1, relu, accumulate_dx,
-            gamma, beta, save_mean, save_invstd, sums, 1, (double)x->N * x->H * x->W};
+            gamma, beta, save_mean, save_invstd, sums, 1, count};
   if (vec_view_ok(x) && vec_view_ok(dy) && vec_view_ok(dx)) bn_apply_vec<1><<<kNumSMs * 4, 256, 0, s>>>(a);
   else AD_DISPATCH_DTYPE(x->dtype, (bn_apply<T, 1><<<grid_for(total, 256, 16), 256, 0, s>>>(a)));
   count_launch();
@@ -610,7 +730,11 @@ extern "C" int ad_maxpool2d_bwd(const ad_tensor4* x, const ad_tensor4* dy, const
   p.accumulate = accumulate;
   const size_t total = (size_t)p.N * p.C * p.H * p.W;
   if (total == 0) return AD_OK;
-  if (pool_vec_ok(x) && pool_vec_ok(dy) && pool_vec_ok(dx)) maxpool_bwd_vec<<<grid_for(total / 8, 256, 16), 256, 0, as_stream(stream)>>>(p);
+  if (pool_vec_ok(x) && pool_vec_ok(dy) && pool_vec_ok(dx) && pool_tile_ok(p)) {
+    const uint32_t gchunks = (p.C / 8 + 7) / 8;
+    dim3 grid((p.W + kPoolTile - 1) / kPoolTile * gchunks, (p.H + kPoolTile - 1) / kPoolTile, p.N);
+    maxpool_bwd_tile<<<grid, 256, 0, as_stream(stream)>>>(p, gchunks);
+  } else if (pool_vec_ok(x) && pool_vec_ok(dy) && pool_vec_ok(dx)) maxpool_bwd_vec<<<grid_for(total / 8, 256, 16), 256, 0, as_stream(stream)>>>(p);
   else AD_DISPATCH_DTYPE(x->dtype, (maxpool_bwd_kernel<T><<<grid_for(total, 256, 16), 256, 0, as_stream(stream)>>>(p)));
   count_launch();
   return launch_status();

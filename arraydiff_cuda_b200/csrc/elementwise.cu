@@ -132,34 +132,54 @@ __device__ __forceinline__ void ew_unpack8(const uint4& v, float (&f)[8]) {
 #pragma unroll
   for (int j = 0; j < 4; ++j) { float2 t = __bfloat1622float2(h[j]); f[2 * j] = t.x; f[2 * j + 1] = t.y; }
 }
+// Element offset of channel group cg of pixel i; evenly spaced pixels need no division.
+__device__ __forceinline__ long long ew_pix_off(const View& v, uint32_t i, uint32_t H, uint32_t W) {
+  if (v.sy == (long long)W * v.sx && v.sn == (long long)H * v.sy) return (long long)i * v.sx;
+  const uint32_t r = i / W, x = i - r * W, n = r / H, y = r - n * H;
+  return n * v.sn + y * v.sy + x * v.sx;
+}
+// G = C/8 channel groups; the launcher guarantees N*H*W*G < 2^31.  Two items per thread and pass.
 template <int OP>
 __global__ void __launch_bounds__(256) ew_vec_kernel(Dims d, View a, View b, View yv, int accumulate) {
   const uint32_t G = d.C / 8;
-  const size_t total = (size_t)d.N * d.H * d.W * G, nt = (size_t)gridDim.x * blockDim.x;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nt) {
-    const uint32_t cg = (uint32_t)(i % G);
-    size_t r = i / G;
-    const uint32_t x = (uint32_t)(r % d.W); r /= d.W;
-    const uint32_t y = (uint32_t)(r % d.H), n = (uint32_t)(r / d.H);
-    float av[8], bv[8], o[8], old[8];
-    ew_unpack8(*(const uint4*)((const __nv_bfloat16*)a.base + voff(a, n, cg * 8, y, x)), av);
-    if (OP == kAdd2 || OP == kReluBwd) ew_unpack8(*(const uint4*)((const __nv_bfloat16*)b.base + voff(b, n, cg * 8, y, x)), bv);
-    uint4* op = (uint4*)((__nv_bfloat16*)yv.base + voff(yv, n, cg * 8, y, x));
-    if (accumulate) ew_unpack8(*op, old);
+  const uint32_t total = d.N * d.H * d.W * G, nt = gridDim.x * blockDim.x;
+  constexpr int U = 2;
+  for (uint32_t i0 = blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += U * nt) {
+    uint4 ar[U], br[U], oldr[U];
+    uint4* op[U];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float v;
-      if (OP == kRelu) v = fmaxf(av[j], 0.f);
-      else if (OP == kConvert) v = av[j];
-      else if (OP == kAdd2) v = av[j] + bv[j];
-      else v = av[j] > 0.f ? bv[j] : 0.f;
-      o[j] = accumulate ? v + old[j] : v;
+    for (int u = 0; u < U; ++u) {
+      const uint32_t i = i0 + u * nt;
+      if (i < total) {
+        const uint32_t pix = i / G, cg = i - pix * G;
+        ar[u] = *(const uint4*)((const __nv_bfloat16*)a.base + ew_pix_off(a, pix, d.H, d.W) + cg * 8);
+        if (OP == kAdd2 || OP == kReluBwd) br[u] = *(const uint4*)((const __nv_bfloat16*)b.base + ew_pix_off(b, pix, d.H, d.W) + cg * 8);
+        op[u] = (uint4*)((__nv_bfloat16*)yv.base + ew_pix_off(yv, pix, d.H, d.W) + cg * 8);
+        if (accumulate) oldr[u] = *op[u];
+      }
     }
-    uint4 pk;
-    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(o[2 * j], o[2 * j + 1]);
-    *op = pk;
+    for (int u = 0; u < U; ++u) {
+      if (i0 + u * nt >= total) break;
+      float av[8], bv[8], o[8], old[8];
+      ew_unpack8(ar[u], av);
+      if (OP == kAdd2 || OP == kReluBwd) ew_unpack8(br[u], bv);
+      if (accumulate) ew_unpack8(oldr[u], old);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float v;
+        if (OP == kRelu) v = fmaxf(av[j], 0.f);
+        else if (OP == kConvert) v = av[j];
+        else if (OP == kAdd2) v = av[j] + bv[j];
+        else v = av[j] > 0.f ? bv[j] : 0.f;
+        o[j] = accumulate ? v + old[j] : v;
+      }
+      uint4 pk;
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(o[2 * j], o[2 * j + 1]);
+      *op[u] = pk;
+    }
   }
 }
 static bool ew_vec_ok(const ad_tensor4* t) {
@@ -180,8 +200,8 @@ static int ew_launch(const ad_tensor4* a, const ad_tensor4* b, const ad_tensor4*
   Dims d{y->N, y->C, y->H, y->W, y->sc == 1 && y->C > 1};
   View va = view_of(a), vb = b ? view_of(b) : View{nullptr, 0, 0, 0, 0}, vy = view_of(y);
   cudaStream_t s = as_stream(stream);
-  if (ew_vec_ok(a) && ew_vec_ok(y) && (!b || ew_vec_ok(b))) {
-    ew_vec_kernel<OP><<<grid_for(total / 8, 256, 16), 256, 0, s>>>(d, va, vb, vy, accumulate);
+  if (total / 8 < (1ull << 31) && ew_vec_ok(a) && ew_vec_ok(y) && (!b || ew_vec_ok(b))) {
+    ew_vec_kernel<OP><<<grid_for(total / 16, 256, 16), 256, 0, s>>>(d, va, vb, vy, accumulate);
     count_launch();
     return launch_status();
   }
@@ -322,6 +342,64 @@ __global__ void __launch_bounds__(256) im2col_vec_kernel(View x, uint32_t N, uin
     *(uint4*)(out + pix * ldo + gcol) = pk;
   }
 }
+// Same matrix built one output row per block: the kh input rows the row's patches touch are staged in
+// shared memory as bf16 (zeros past the tensor's edge), a table maps each column to its offset inside the
+// staged rows, and every thread then assembles 16-byte pieces of the output from shared memory.  Each input
+// element is fetched from global memory once per output row instead of once per patch that holds it.
+template <typename T>
+__global__ void __launch_bounds__(256) im2col_row_kernel(View x, uint32_t C, uint32_t H, uint32_t W, uint32_t kh, uint32_t kw,
+                                                         uint32_t sh, uint32_t sw, uint32_t dh, uint32_t dw, uint32_t P,
+                                                         uint32_t Q, __nv_bfloat16* out, uint32_t ldo, uint32_t rowlen) {
+  extern __shared__ __align__(16) unsigned char im2col_smem[];
+  __nv_bfloat16* rows = (__nv_bfloat16*)im2col_smem;                                    // [kh][rowlen]
+  uint32_t* tab = (uint32_t*)(im2col_smem + (((size_t)kh * rowlen * 2 + 15) & ~(size_t)15));  // [ldo]
+  const uint32_t p = blockIdx.x % P, n = blockIdx.x / P, cols = kh * kw * C;
+  for (uint32_t t = threadIdx.x; t < ldo; t += 256) {
+    uint32_t e = 0xffffffffu;
+    if (t < cols) { const uint32_t c = t % C, tap = t / C, s = tap % kw, r = tap / kw; e = r * rowlen + s * dw * C + c; }
+    tab[t] = e;
+  }
+  const bool packed = x.sc == 1 && x.sx == (long long)C;
+  for (uint32_t r = 0; r < kh; ++r) {
+    const uint32_t yy = p * sh + r * dh;
+    const T* src = (const T*)x.base + n * x.sn + yy * x.sy;
+    for (uint32_t e = threadIdx.x; e < rowlen; e += 256) {
+      float v = 0.f;
+      if (yy < H) {
+        if (packed) { if (e < W * C) v = ld_f(src + e); }
+        else { const uint32_t xx = e / C, c = e - xx * C; if (xx < W) v = ld_f(src + xx * x.sx + c * x.sc); }
+      }
+      rows[r * rowlen + e] = __float2bfloat16_rn(v);
+    }
+  }
+  __syncthreads();
+  const uint32_t groups = ldo / 8;
+  __nv_bfloat16* orow = out + ((size_t)n * P + p) * Q * ldo;
+  const unsigned short* rs = (const unsigned short*)rows;
+  for (uint32_t it = threadIdx.x; it < Q * groups; it += 256) {
+    const uint32_t q = it / groups, g = it - q * groups, base = q * sw * C;
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t e0 = tab[g * 8 + 2 * j], e1 = tab[g * 8 + 2 * j + 1];
+      const uint32_t lo = e0 == 0xffffffffu ? 0u : rs[e0 + base], hi = e1 == 0xffffffffu ? 0u : rs[e1 + base];
+      w[j] = lo | (hi << 16);
+    }
+    *(uint4*)(orow + (size_t)q * ldo + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+template <typename T>
+static int launch_im2col_row(const View& v, const ad_tensor4* x, uint32_t kh, uint32_t kw, uint32_t sh, uint32_t sw, uint32_t dh,
+                             uint32_t dw, uint32_t P, uint32_t Q, __nv_bfloat16* out, uint32_t ldo, uint32_t rowlen, size_t smem,
+                             cudaStream_t s) {
+  auto kern = im2col_row_kernel<T>;
+  if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    cudaGetLastError();
+    return AD_ERR_CUDA;
+  }
+  kern<<<x->N * P, 256, smem, s>>>(v, x->C, x->H, x->W, kh, kw, sh, sw, dh, dw, P, Q, out, ldo, rowlen);
+  return AD_OK;
+}
 }  // namespace adk
 
 extern "C" int ad_im2col(const ad_tensor4* x, uint32_t kh, uint32_t kw, uint32_t sh, uint32_t sw, uint32_t dh, uint32_t dw,
@@ -332,6 +410,17 @@ extern "C" int ad_im2col(const ad_tensor4* x, uint32_t kh, uint32_t kw, uint32_t
   if (total == 0) return AD_OK;
   adk::View v = adk::view_of(x);
   if ((ldo & 7u) == 0 && ((uintptr_t)out_bf16 & 15u) == 0) {
+    // staged-row form when the rows of one output row fit shared memory
+    const uint32_t rowlen = ((Q - 1) * sw + (kw - 1) * dw + 1) * x->C;
+    const size_t smem = (((size_t)kh * rowlen * 2 + 15) & ~(size_t)15) + (size_t)ldo * 4;
+    if (smem <= 100 * 1024 && (size_t)x->N * P < (1ull << 31) && (size_t)Q * (ldo / 8) < (1ull << 31)) {
+      int st = AD_OK;
+      AD_DISPATCH_DTYPE(x->dtype, (st = adk::launch_im2col_row<T>(v, x, kh, kw, sh, sw, dh, dw, P, Q, (__nv_bfloat16*)out_bf16, ldo,
+                                                                  rowlen, smem, adk::as_stream(stream))));
+      if (st != AD_OK) return st;
+      adk::count_launch();
+      return adk::launch_status();
+    }
     const size_t tv = (size_t)x->N * P * Q * (ldo / 8);
     AD_DISPATCH_DTYPE(x->dtype, (adk::im2col_vec_kernel<T><<<adk::grid_for(tv, 256, 16), 256, 0, adk::as_stream(stream)>>>(
                                     v, x->N, x->C, x->H, x->W, kh, kw, sh, sw, dh, dw, P, Q, (__nv_bfloat16*)out_bf16, ldo)));
