@@ -98,41 +98,47 @@ __global__ void __launch_bounds__(256) bn_reduce_cfast(BnRed p, float* partial) 
   }
 }
 
-// Stage 2 of the statistics, 32 channels per block: 8 row lanes walk the partial rows (each warp
-// access is one 128-byte line), sum in double, and are combined in a fixed order.
+// Stage 2 of the statistics, 32 channels per block of 1024 threads: 32 row lanes walk the partial rows
+// (each warp access is one 128-byte line, up to 8 rows in flight per thread), sum in double, and are
+// combined in a fixed order.
 //   kind 0: mean / invstd / var from (sum x, sum x^2); double arithmetic for the cancellation in E[x^2]-E[x]^2
 //   kind 1: sums[0..2C) = (sum g, sum g*xhat), sums[2C..4C) = those over count; dbeta += sum g, dgamma += sum g*xhat
 //   kind 2: sums[0..2C) only
-__global__ void __launch_bounds__(256) bn_finish(int kind, uint32_t C, int nsplit, const float* __restrict__ partial,
-                                                 double count, float eps, float* mean, float* invstd, float* var,
-                                                 float* sums, float* dgamma, float* dbeta) {
+constexpr int kFinishLanes = 32;
+__global__ void __launch_bounds__(32 * kFinishLanes) bn_finish(int kind, uint32_t C, int nsplit, const float* __restrict__ partial,
+                                                               double count, float eps, float* mean, float* invstd,
+                                                               float* var, float* sums, float* dgamma, float* dbeta) {
   const uint32_t lane = threadIdx.x & 31, rl = threadIdx.x >> 5, c = blockIdx.x * 32 + lane;
   double s = 0.0, ss = 0.0;
   if (c < C) {
-    int k = rl;
-    for (; k + 24 < nsplit; k += 32) {
-      float v[4], w[4];
+    for (int k0 = rl; k0 < nsplit; k0 += 8 * kFinishLanes) {
+      float v[8], w[8];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        v[u] = partial[(size_t)(k + 8 * u) * 2 * C + c];
-        w[u] = partial[(size_t)(k + 8 * u) * 2 * C + C + c];
+      for (int u = 0; u < 8; ++u) {
+        const int k = k0 + u * kFinishLanes;
+        v[u] = w[u] = 0.f;
+        if (k < nsplit) { v[u] = partial[(size_t)k * 2 * C + c]; w[u] = partial[(size_t)k * 2 * C + C + c]; }
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) { s += (double)v[u]; ss += (double)w[u]; }
-    }
-    for (; k < nsplit; k += 8) {
-      s += (double)partial[(size_t)k * 2 * C + c];
-      ss += (double)partial[(size_t)k * 2 * C + C + c];
+      for (int u = 0; u < 8; ++u) { s += (double)v[u]; ss += (double)w[u]; }
     }
   }
-  __shared__ double sh[2][8][32];
+  __shared__ double sh[2][kFinishLanes][33];
   sh[0][rl][lane] = s;
   sh[1][rl][lane] = ss;
   __syncthreads();
+  // warp w < 2 sums statistic w: lane = channel, row lanes in order
+  if (rl >= 2) return;
+  double t = 0.0;
+#pragma unroll 8
+  for (int w = 0; w < kFinishLanes; ++w) t += sh[rl][w][lane];
+  __shared__ double tot[2][32];
+  tot[rl][lane] = t;
+  __syncwarp();
+  // the two warps meet through shared memory: named barrier over these 64 threads
+  asm volatile("bar.sync 1, 64;" ::: "memory");
   if (rl != 0 || c >= C) return;
-  s = 0.0; ss = 0.0;
-#pragma unroll
-  for (int w = 0; w < 8; ++w) { s += sh[0][w][lane]; ss += sh[1][w][lane]; }
+  s = tot[0][lane]; ss = tot[1][lane];
   if (kind == 0) {
     double m = s / count, v = ss / count - m * m;
     if (v < 0.0) v = 0.0;
@@ -613,7 +619,7 @@ extern "C" int ad_bn_partial_stats(const ad_tensor4* x, float* sums, void* scrat
   int nsplit = 1;
   int st = launch_reduce<0>(p, x, (float*)scratch, nsplit, s);
   if (st != AD_OK) return st;
-  bn_finish<<<(x->C + 31) / 32, 256, 0, s>>>(2, x->C, nsplit, (const float*)scratch, 1.0, 0.f, nullptr, nullptr, nullptr, sums,
+  bn_finish<<<(x->C + 31) / 32, 32 * kFinishLanes, 0, s>>>(2, x->C, nsplit, (const float*)scratch, 1.0, 0.f, nullptr, nullptr, nullptr, sums,
                                              nullptr, nullptr);
   count_launch();
   return launch_status();
@@ -625,7 +631,7 @@ extern "C" int ad_bn_finalize_apply(const ad_tensor4* x, const ad_tensor4* y, co
   if (!x || !y || !x->base || !y->base || !sums || !gamma || !beta || !save_mean || !save_invstd) return AD_ERR_BAD_ARG;
   if (!dims_eq(x, y) || count <= 0.0) return AD_ERR_BAD_ARG;
   cudaStream_t s = as_stream(stream);
-  bn_finish<<<(x->C + 31) / 32, 256, 0, s>>>(0, x->C, 1, sums, count, eps, save_mean, save_invstd, batch_var, nullptr, nullptr,
+  bn_finish<<<(x->C + 31) / 32, 32 * kFinishLanes, 0, s>>>(0, x->C, 1, sums, count, eps, save_mean, save_invstd, batch_var, nullptr, nullptr,
                                              nullptr);
   count_launch();
   BnApply a{bview(x), bview(x), bview(y), x->N, x->C, x->H, x->W, y->sc == 1 && y->C > 1, relu, 0,
@@ -651,7 +657,7 @@ extern "C" int ad_bn_fwd_train(const ad_tensor4* x, const ad_tensor4* y, const f
   int st = launch_reduce<0>(p, x, (float*)scratch, nsplit, s);
   if (st != AD_OK) return st;
   const double count = (double)x->N * x->H * x->W;
-  bn_finish<<<(x->C + 31) / 32, 256, 0, s>>>(0, x->C, nsplit, (const float*)scratch, count, eps, save_mean, save_invstd,
+  bn_finish<<<(x->C + 31) / 32, 32 * kFinishLanes, 0, s>>>(0, x->C, nsplit, (const float*)scratch, count, eps, save_mean, save_invstd,
                                              batch_var, nullptr, nullptr, nullptr);
   count_launch();
   BnApply a{bview(x), bview(x), bview(y), x->N, x->C, x->H, x->W, y->sc == 1 && y->C > 1, relu, 0,
@@ -680,7 +686,7 @@ extern "C" int ad_bn_bwd(const ad_tensor4* x, const ad_tensor4* dy, const ad_ten
   if (st != AD_OK) return st;
   float* sums = partial + (size_t)bn_max_splits(x->C) * 2 * x->C;
   const double count = (double)x->N * x->H * x->W;
-  bn_finish<<<(x->C + 31) / 32, 256, 0, s>>>(1, x->C, nsplit, partial, count, 0.f, nullptr, nullptr, nullptr, sums, dgamma, dbeta);
+  bn_finish<<<(x->C + 31) / 32, 32 * kFinishLanes, 0, s>>>(1, x->C, nsplit, partial, count, 0.f, nullptr, nullptr, nullptr, sums, dgamma, dbeta);
   count_launch();
   BnApply a{bview(x), bview(dy), bview(dx), x->N, x->C, x->H, x->W, dx->sc == 1 && dx->C > 1, relu, accumulate_dx,
             gamma, beta, save_mean, save_invstd, sums, 1, count};

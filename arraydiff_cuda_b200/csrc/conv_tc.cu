@@ -468,12 +468,24 @@ conv_tc_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_co
 // dw[i] (+)= sum over splits of partial[s][i], fixed order.
 __global__ void __launch_bounds__(256) wgrad_reduce_kernel(size_t n, uint32_t splits, const float* __restrict__ partial,
                                                            float* dw, int accumulate) {
-  const size_t nt = (size_t)gridDim.x * blockDim.x;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += nt) {
-    float t = 0.f;
-    for (uint32_t s = 0; s < splits; ++s) t += partial[(size_t)s * n + i];
-    dw[i] = accumulate ? dw[i] + t : t;
-  }
+  // 64 outputs x 4 split lanes per block: lane l sums splits l, l+4, ... (8 loads in flight), lanes combine in order
+  const uint32_t tx = threadIdx.x & 63, pl = threadIdx.x >> 6;
+  const size_t i = (size_t)blockIdx.x * 64 + tx;
+  float t = 0.f;
+  if (i < n)
+    for (uint32_t s0 = pl; s0 < splits; s0 += 32) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) { const uint32_t si = s0 + 4 * u; v[u] = si < splits ? partial[(size_t)si * n + i] : 0.f; }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) t += v[u];
+    }
+  __shared__ float sh[4][64];
+  sh[pl][tx] = t;
+  __syncthreads();
+  if (pl != 0 || i >= n) return;
+  t = ((sh[0][tx] + sh[1][tx]) + sh[2][tx]) + sh[3][tx];
+  dw[i] = accumulate ? dw[i] + t : t;
 }
 
 // Filter for the data gradient: wt[c][kh-1-r][kw-1-s][k] = w[k][r][s][c]  (bf16).
@@ -802,7 +814,7 @@ int conv_tc_wgrad(const ad_conv2d_args* a, cudaStream_t s) {
   }
   st = BN == 128 ? launch_wgrad<128>(mdy, mx, p, s) : launch_wgrad<64>(mdy, mx, p, s);
   if (st != AD_OK) return st;
-  wgrad_reduce_kernel<<<grid_for(wcount, 256), 256, 0, s>>>(wcount, p.splits, p.partial, (float*)a->dw, a->accumulate);
+  wgrad_reduce_kernel<<<(unsigned)((wcount + 63) / 64), 256, 0, s>>>(wcount, p.splits, p.partial, (float*)a->dw, a->accumulate);
   count_launch();
   if (a->db) {
     dim3 block(32, 8);

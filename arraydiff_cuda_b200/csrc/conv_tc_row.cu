@@ -510,19 +510,45 @@ conv_tc_row_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __gri
 }
 
 // dw[k][tap][c] (+)= sum over CTAs of partial[cta][acc(tap)][half(tap)*64 + c][k], fixed order.
+// A block is 64 float4 items (4 adjacent k of one accumulator row: coalesced reads) x 4 part lanes; every
+// lane sums parts lane, lane+4, ... with 8 loads in flight, the lanes are combined in order.
 __global__ void __launch_bounds__(256) wgrad_row_reduce_kernel(uint32_t nparts, uint32_t naccs, uint32_t KO, uint32_t kh,
                                                                uint32_t kw, const float* __restrict__ partial, float* dw,
                                                                int accumulate) {
-  const uint32_t taps = kh * kw;
-  const size_t total = (size_t)KO * taps * 64, nt = (size_t)gridDim.x * blockDim.x;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nt) {
-    const uint32_t c = (uint32_t)(i % 64), tap = (uint32_t)((i / 64) % taps), k = (uint32_t)(i / (64 * taps));
-    const uint32_t r = tap / kw, s = tap % kw;
-    const uint32_t acc = (r / 2) * kw + s, row = (r & 1u) * 64 + c;
-    float t = 0.f;
-    for (uint32_t pi = 0; pi < nparts; ++pi) t += partial[(((size_t)pi * naccs + acc) * 128 + row) * 64 + k];
-    dw[i] = accumulate ? dw[i] + t : t;
+  const uint32_t tx = threadIdx.x & 63, pl = threadIdx.x >> 6;
+  const uint32_t item = blockIdx.x * 64 + tx, nitems = naccs * 128 * 16;
+  float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (item < nitems) {
+    const size_t part_stride = (size_t)naccs * 128 * 64;
+    const float* src = partial + (size_t)item * 4;
+    for (uint32_t p0 = pl; p0 < nparts; p0 += 32) {
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const uint32_t pi = p0 + 4 * u;
+        v[u] = pi < nparts ? *(const float4*)(src + pi * part_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) { t.x += v[u].x; t.y += v[u].y; t.z += v[u].z; t.w += v[u].w; }
+    }
   }
+  __shared__ float4 sh[4][64];
+  sh[pl][tx] = t;
+  __syncthreads();
+  if (pl != 0 || item >= nitems) return;
+#pragma unroll
+  for (int w = 1; w < 4; ++w) { const float4 o = sh[w][tx]; t.x += o.x; t.y += o.y; t.z += o.z; t.w += o.w; }
+  const uint32_t k0 = (item & 15u) * 4, row = (item >> 4) & 127u, acc = item >> 11;
+  const uint32_t c = row & 63u, r = (acc / kw) * 2 + (row >> 6), sx = acc % kw;
+  if (r >= kh) return;   // the unused half of an odd last row pair
+  const uint32_t taps = kh * kw, tap = r * kw + sx;
+  const float o[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    if (k0 + j < KO) {
+      float* d = dw + ((size_t)(k0 + j) * taps + tap) * 64 + c;
+      *d = accumulate ? *d + o[j] : o[j];
+    }
 }
 
 static uint32_t row_wgrad_grid(uint32_t NI, uint32_t OP, uint32_t OQ) {
@@ -591,7 +617,7 @@ int conv_tc_row_wgrad(const void* x, uint32_t NI, uint32_t IH, uint32_t IW, uint
   kern<<<grid, kRowThreads, smem, s>>>(mdy, mx, p);
   count_launch();
   const size_t wcount = (size_t)KO * kh * kw * 64;
-  wgrad_row_reduce_kernel<<<grid_for(wcount, 256), 256, 0, s>>>(grid, p.naccs, KO, kh, kw, p.partial, dwt, accumulate);
+  wgrad_row_reduce_kernel<<<(p.naccs * 128 * 16 + 63) / 64, 256, 0, s>>>(grid, p.naccs, KO, kh, kw, p.partial, dwt, accumulate);
   count_launch();
   return launch_status();
 }

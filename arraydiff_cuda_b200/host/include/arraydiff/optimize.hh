@@ -62,6 +62,15 @@ public:
 
   size_t param_dim() const { return param_dim_; }
   size_t iteration() const { return iter_count_; }
+  // A replayed (graph-captured) step does its update on the device only: the host-side iteration
+  // counter, which indexes the schedules, is advanced here.
+  void skip_iterations(size_t n) { iter_count_ += n; }
+  // the three schedule values the next step() bakes into its update kernel
+  void schedule_now(float out[3]) const {
+    out[0] = (float)cfg_.momentum->at(iter_count_);
+    out[1] = (float)cfg_.step_size->at(iter_count_);
+    out[2] = (float)cfg_.step_size->at(iter_count_ + 1);
+  }
 
   // Draws the initial parameters, makes every rank's replica equal to rank 0's and sets up the flat
   // parameter / gradient / momentum buffers (reference :314-386).

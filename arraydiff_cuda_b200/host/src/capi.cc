@@ -17,6 +17,11 @@ struct Net {
   std::unique_ptr<ParallelSGDOptimizer<float>> opt;
   std::unique_ptr<TxnId> txn;
   std::mt19937_64 rng;
+  // the resident step captured as one CUDA graph (adh_net_step_graph)
+  cudaGraphExec_t gexec = nullptr;
+  int g_update = 0;
+  float g_key[3] = {0.f, 0.f, 0.f};
+  uint64_t g_launches = 0;
 };
 struct Ctx { shared_ptr<MultiGPUContext> ctx; };
 }  // namespace
@@ -183,6 +188,60 @@ int adh_net_step_resident(void* h, int with_update) {
   if (with_update) n->opt->step(*n->txn);
   return AD_OK;
 }
+// The same step replayed from a CUDA graph.  The first call (and any call after the schedule values or
+// `with_update` changed) records adh_net_step_resident on the ranks' streams -- rank 0's stream is the
+// origin, the other local ranks' streams are forked from it and joined back -- and instantiates the
+// graph; every call launches it once.  Buffers are arena-resident, so addresses are stable between
+// steps.  One process per GPU keeps the eager path: its flag epochs change every step.
+int adh_net_step_graph(void* h, int with_update) {
+  auto* n = (Net*)h;
+  if (n->ctx->distributed()) return adh_net_step_resident(h, with_update);
+  float key[3];
+  n->opt->schedule_now(key);
+  if (n->gexec && (n->g_update != with_update || std::memcmp(key, n->g_key, sizeof key))) {
+    cudaGraphExecDestroy(n->gexec);
+    n->gexec = nullptr;
+  }
+  const size_t R = n->ctx->num_ranks();
+  cudaStream_t origin = n->ctx->device_context(0)->stream();
+  if (!n->gexec) {
+    GPUConn c0 = n->ctx->device_context(0)->conn();
+    CUDA_CHECK(cudaStreamBeginCapture(origin, cudaStreamCaptureModeRelaxed));
+    vector<cudaEvent_t> evs;
+    cudaEvent_t fork;
+    CUDA_CHECK(cudaEventCreateWithFlags(&fork, cudaEventDisableTiming));
+    CUDA_CHECK(cudaEventRecord(fork, origin));
+    evs.push_back(fork);
+    for (size_t r = 1; r < R; ++r) CUDA_CHECK(cudaStreamWaitEvent(n->ctx->device_context(r)->stream(), fork, 0));
+    const uint64_t l0 = ad_launch_count();
+    adh_net_step_resident(h, with_update);
+    n->g_launches = ad_launch_count() - l0;
+    for (size_t r = 1; r < R; ++r) {
+      GPUConn cr = n->ctx->device_context(r)->conn();
+      cudaEvent_t e;
+      CUDA_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+      CUDA_CHECK(cudaEventRecord(e, n->ctx->device_context(r)->stream()));
+      CUDA_CHECK(cudaStreamWaitEvent(origin, e, 0));
+      evs.push_back(e);
+    }
+    cudaGraph_t graph = nullptr;
+    GPUConn c1 = n->ctx->device_context(0)->conn();
+    CUDA_CHECK(cudaStreamEndCapture(origin, &graph));
+    CUDA_CHECK(cudaGraphInstantiate(&n->gexec, graph, 0));
+    cudaGraphDestroy(graph);
+    for (auto e : evs) cudaEventDestroy(e);
+    n->g_update = with_update;
+    std::memcpy(n->g_key, key, sizeof key);
+    CUDA_CHECK(cudaGraphLaunch(n->gexec, origin));   // the recording itself executed nothing
+    return AD_OK;
+  }
+  GPUConn c0 = n->ctx->device_context(0)->conn();
+  CUDA_CHECK(cudaGraphLaunch(n->gexec, origin));
+  if (with_update) n->opt->skip_iterations(1);
+  return AD_OK;
+}
+// kernels one replay of the graph launches (0 before the first adh_net_step_graph)
+uint64_t adh_net_graph_launches(void* h) { return ((Net*)h)->g_launches; }
 // allreduce of the gradients + SGD update on every rank
 int adh_net_sgd_step(void* h) { auto* n = (Net*)h; n->opt->step(*n->txn); return AD_OK; }
 int adh_net_sync(void* h) { ((Net*)h)->ctx->sync(); return AD_OK; }

@@ -155,6 +155,13 @@ void MultiGPUContext::allreduce_sum(float* buf, size_t count) {
     GPUConn c = dev_ctxs_[r]->conn();
     CUDA_CHECK(cudaStreamWaitEvent(c.stream(), done, 0));
     CUDA_CHECK(cudaMemcpyAsync(peer_ptr(buf, 0, r), buf, count * sizeof(float), cudaMemcpyDeviceToDevice, c.stream()));
+    // rank 0 goes on to update its buffer in place (the SGD kernel adds the L2 term into the gradient):
+    // not before every peer has taken its copy
+    CUDA_CHECK(cudaEventRecord(ev[r], c.stream()));
+  }
+  {
+    GPUConn c = dev_ctxs_[0]->conn();
+    for (size_t r = 1; r < num_ranks_; ++r) CUDA_CHECK(cudaStreamWaitEvent(c.stream(), ev[r], 0));
   }
   for (auto e : ev) cudaEventDestroy(e);
   cudaEventDestroy(done);

@@ -606,6 +606,7 @@ static IOOp<GPUArray1D<float>>::InitFn const_init(float v) {
   return [v](GPUArray1D<float>* a, std::mt19937_64*, shared_ptr<Context>) {
     int dev = 0;
     cudaGetDevice(&dev);
+    cudaDeviceSynchronize();   // the context streams do not synchronise with the default stream
     AD_CHECK(ad_array_set_constant(a->flat_size(), v, a->dptr(), nullptr));
     cudaDeviceSynchronize();
   };

@@ -24,12 +24,20 @@ typename IOOp<A>::InitFn kaiming_init_gen(size_t fan_in, size_t) {
     std::normal_distribution<float> dist(0.0f, std::sqrt(2.0f / (float)fan_in));
     vector<float> h(a->flat_size());
     for (auto& v : h) v = dist(*rng);
+    // the context streams do not synchronise with the default stream: drain what is queued on this
+    // array (its allocation-time zero fill) before the copy, and the copy before anything reads it
+    CUDA_CHECK(cudaDeviceSynchronize());
     CUDA_CHECK(cudaMemcpy(a->dptr(), h.data(), h.size() * 4, cudaMemcpyHostToDevice));
+    CUDA_CHECK(cudaDeviceSynchronize());
   };
 }
 template <typename A>
 typename IOOp<A>::InitFn zeros_init_gen() {
-  return [](A* a, std::mt19937_64*, shared_ptr<Context>) { CUDA_CHECK(cudaMemset(a->dptr(), 0, a->flat_size() * 4)); };
+  return [](A* a, std::mt19937_64*, shared_ptr<Context>) {
+    CUDA_CHECK(cudaDeviceSynchronize());
+    CUDA_CHECK(cudaMemset(a->dptr(), 0, a->flat_size() * 4));
+    CUDA_CHECK(cudaDeviceSynchronize());
+  };
 }
 template IOOp<GPUArray4D<float>>::InitFn kaiming_init_gen<GPUArray4D<float>>(size_t, size_t);
 template IOOp<GPUArray1D<float>>::InitFn zeros_init_gen<GPUArray1D<float>>();

@@ -45,6 +45,9 @@ def load():
         L.adh_net_output_dims.argtypes = [vp, C.POINTER(C.c_int)]
         L.adh_net_forward.argtypes = [vp, vp]
         L.adh_net_step_resident.argtypes = [vp, C.c_int]
+        L.adh_net_step_graph.argtypes = [vp, C.c_int]
+        L.adh_net_graph_launches.restype = C.c_uint64
+        L.adh_net_graph_launches.argtypes = [vp]
         for name in ("adh_net_backward", "adh_net_sgd_step", "adh_net_sync", "adh_net_status"):
             getattr(L, name).argtypes = [vp]
         L.adh_net_arena_used.restype = C.c_size_t
@@ -140,6 +143,14 @@ class Net:
     def step_resident(self, with_update=True):
         """forward + backward (+ allreduce and SGD) on the image and output gradients already on the device"""
         self.L.adh_net_step_resident(self.h, int(with_update))
+
+    def step_graph(self, with_update=True):
+        """the resident step replayed from a CUDA graph (recorded on the first call)"""
+        assert self.L.adh_net_step_graph(self.h, int(with_update)) == 0
+
+    def graph_launches(self):
+        """kernels one graph replay launches"""
+        return int(self.L.adh_net_graph_launches(self.h))
 
     def sgd_step(self):
         self.L.adh_net_sgd_step(self.h)

@@ -512,7 +512,8 @@ def run_stem_workload(args):
         ranks, strips = [rank], world
     else:
         strips = max(1, args.strips)
-        ctx = hostlib.Context([local] * strips, hostlib.BF16_NHWC, arena_mb=8192 // strips)
+        ctx = hostlib.Context([local] * strips, hostlib.BF16_NHWC,
+                              arena_mb=max(512, int(4096 * (S / 1024.0) ** 2) // strips + 256))
         ranks = list(range(strips))
     net = hostlib.Net(ctx, "stem_stage1", S, S, 3, 1, seed=1)
     net.configure_sgd(0.01, 0.9, l2=1e-4, nesterov=True)
@@ -528,9 +529,14 @@ def run_stem_workload(args):
         net.sgd_step()
         return net.output(ranks[0])          # D2H read of a result
 
+    # steady-state step: the resident step replayed from a CUDA graph (one process per GPU keeps the
+    # eager path: its flag epochs change every step)
+    use_graph = world == 1 and not args.no_graph
+    step = (lambda: net.step_graph(True)) if use_graph else (lambda: net.step_resident(True))
     e2e_step()
+    net.step_resident(True)
     for _ in range(max(3, args.warmup)):
-        net.step_resident(True)
+        step()
     net.sync()
     assert net.status() == 0, "a bounded device wait timed out"
     streams = [torch.cuda.ExternalStream(Lh.adh_context_stream(ctx.h, r)) for r in ranks]
@@ -544,7 +550,7 @@ def run_stem_workload(args):
     e0 = torch.cuda.Event(enable_timing=True)
     e0.record(streams[0])
     for _ in range(args.steps):
-        net.step_resident(True)
+        step()
     ends = []
     for st in streams:
         e = torch.cuda.Event(enable_timing=True)
@@ -552,7 +558,7 @@ def run_stem_workload(args):
         ends.append(e)
     torch.cuda.synchronize()
     ms = max(e0.elapsed_time(e) for e in ends)
-    launches = L.ad_launch_count() - launches0
+    launches = net.graph_launches() * args.steps if use_graph else L.ad_launch_count() - launches0
     clocks = sampler.stop() if rank == 0 else None
     if world > 1:
         t = torch.tensor([ms], device="cuda", dtype=torch.float64)
@@ -581,7 +587,7 @@ def run_stem_workload(args):
             "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "images_per_s": 1.0 / step_s,
             "config": {"workload": "resnet50_stem_stage1", "image": [1, 3, S, S], "strips": strips, "layout": "NHWC",
-                       "bn_statistics": "per strip (as the reference)", "update": "allreduce + Nesterov SGD",
+                       "bn_statistics": "per strip (as the reference)", "update": "allreduce + Nesterov SGD", "launch": "cuda graph" if use_graph else "eager",
                        "l2": "activations of one step total ~1.2 GB, larger than L2", "parallelism": f"spatial-h{strips}"},
             "e2e": {"value": flops / t_e2e / 1e12, "unit": UNIT, "h2d_bytes_per_step": int(x.nbytes + sum(d.nbytes for d in dy) // max(1, world if world > 1 else 1)),
                     "d2h_bytes_per_step": int(np.prod(net.strip_shape) * 4), "steps": k_e2e, "timing": "host clock between synchronisations"},
@@ -605,6 +611,7 @@ def main():
                          "stem_stage1: ResNet-50 stem + stage 1 through the C++ op graph (config 3)")
     ap.add_argument("--strips", type=int, default=1, help="stem_stage1 on one GPU: ranks sharing the device")
     ap.add_argument("--image", type=int, default=1024, help="stem_stage1: image height = width")
+    ap.add_argument("--no-graph", action="store_true", help="stem_stage1: launch every kernel eagerly instead of replaying a CUDA graph")
     ap.add_argument("--batch", type=int, default=BATCH,
                     help="images per step; the default is the workload's, smaller values are for profiler captures")
     args = ap.parse_args()
@@ -646,7 +653,7 @@ def main():
         sampler.start()
     launches0 = L.ad_launch_count()
     ms = timed_loop(torch, dist, step, args.steps, False, world)
-    launches = L.ad_launch_count() - launches0
+    launches = net.graph_launches() * args.steps if use_graph else L.ad_launch_count() - launches0
     clocks = sampler.stop() if rank == 0 else None
     step.check_status()
     for _ in range(2):
