@@ -71,7 +71,8 @@ int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t*
 
 constexpr int kTileM = 128;         // pixels (fwd) / dy channels (wgrad) per tile = TMEM lanes
 constexpr int kSlabBytes = 16384;   // one [128 rows][64 bf16] swizzled operand slab
-constexpr int kThreads = 192;       // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
+constexpr int kThreads = 192;       // filter-gradient kernel: warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
+constexpr int kFwdThreads = 320;    // forward kernel: warp 0 TMA, warp 1 MMA, two groups of 4 epilogue warps
 
 struct FwdParams {
   uint32_t NI, OP, OQ, OC;  // output: images, rows, cols, channels
@@ -102,7 +103,7 @@ __device__ __forceinline__ uint32_t pow2_cols(uint32_t c) {
 }
 
 template <int BN, int STAGES>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kFwdThreads, 1)
 conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                    const __grid_constant__ CUtensorMap map_o, const FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -124,7 +125,8 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&ctl->tfull[a]), 1);
-      mbar_init(smem_u32(&ctl->tempty[a]), 4);
+      // an accumulator is drained by both epilogue groups when a tile has several 64-channel chunks
+      mbar_init(smem_u32(&ctl->tempty[a]), (p.tma_store && BN >= 128) ? 8 : 4);
       mbar_init(smem_u32(&ctl->stg_full[a]), 4);
       mbar_init(smem_u32(&ctl->stg_free[a]), 1);
     }
@@ -193,64 +195,73 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     }
   } else {
     const uint32_t q = (uint32_t)warp & 3u;  // TMEM lane quarter this warp may read
-    uint32_t it = 0;
+    const uint32_t grp = ((uint32_t)warp - 2u) >> 2;   // epilogue warps 2..5 = group 0, 6..9 = group 1
+    const bool leader = (((uint32_t)warp - 2u) & 3u) == 0u;
+    uint32_t it = 0, gk = 0;   // gk: chunks this group has staged so far
     for (uint32_t tile = blockIdx.x; tile < total_tiles && !*abortf; tile += gridDim.x, ++it) {
       const uint32_t acc = it & 1u, acc_phase = (it >> 1) & 1u;
       const uint32_t tn = tile / tiles_m, tm = tile % tiles_m;
       const uint32_t tx = tm % p.tiles_x, ty = (tm / p.tiles_x) % p.tiles_y, n = tm / (p.tiles_x * p.tiles_y);
-      if (!mbar_wait(smem_u32(&ctl->tfull[acc]), acc_phase, abortf)) break;
-      tc_fence_after();
       const uint32_t m = q * 32 + lane;
       if (BN >= 64 && p.tma_store) {
         // 64-channel chunks of the tile go through a swizzled [128 px][64 ch] staging buffer and one TMA
-        // tile store each: coalesced, clipped to the tensor, no per-thread scattered 16-byte stores.
+        // tile store each: coalesced, clipped to the tensor, no per-thread scattered 16-byte stores.  The
+        // two warp groups take alternate chunks (alternate tiles when a tile is one chunk), each with its
+        // own staging buffer, so one group converts while the other group's store drains.
+        constexpr uint32_t kChunks = BN / 64;
+        if (kChunks == 1 && (it & 1u) != grp) continue;
+        if (!mbar_wait(smem_u32(&ctl->tfull[acc]), acc_phase, abortf)) break;
+        tc_fence_after();
+        uint8_t* stg = osm + (size_t)grp * 16384;
+        uint8_t* srow = stg + m * 128u;
+        const uint32_t m7 = m & 7u;
         bool live = true;
 #pragma unroll 1
-        for (uint32_t c64 = 0; c64 < BN / 64 && live; ++c64) {
-          const uint32_t cc = it * (BN / 64) + c64, b = cc & 1u;
-          uint8_t* stg = osm + (size_t)b * 16384;
-          bool ok = true;
-          if (cc >= 2) ok = mbar_wait(smem_u32(&ctl->stg_free[b]), ((cc >> 1) - 1u) & 1u, abortf);
-          if (!__all_sync(0xffffffffu, ok)) { live = false; break; }
-#pragma unroll
-          for (uint32_t half = 0; half < 2; ++half) {
-            uint32_t v[32];
-            tmem_ld32(tmem_base + ((q * 32u) << 16) + acc * BN + c64 * 64 + half * 32, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              const uint32_t cl = half * 32 + g * 8, cg = tn * BN + c64 * 64 + cl;
-              float f[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                f[j] = __uint_as_float(v[g * 8 + j]);
-                if (p.bias && cg + j < p.OC) f[j] += p.bias[cg + j];
-                if (p.relu) f[j] = fmaxf(f[j], 0.f);
-              }
-              uint4 pk;
-              __nv_bfloat162* p2 = (__nv_bfloat162*)&pk;
-#pragma unroll
-              for (int j = 0; j < 4; ++j) p2[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
-              *(uint4*)(stg + m * 128u + (((cl >> 3) ^ (m & 7u)) * 16u)) = pk;
-            }
+        for (uint32_t c64 = (kChunks == 1 ? 0u : grp); c64 < kChunks && live; c64 += 2, ++gk) {
+          uint32_t v[64];
+          const uint32_t taddr = tmem_base + ((q * 32u) << 16) + acc * BN + c64 * 64;
+          tmem_ld32(taddr, *(uint32_t(*)[32])&v[0]);
+          tmem_ld32(taddr + 32, *(uint32_t(*)[32])&v[32]);
+          tmem_ld_wait();
+          if (c64 + 2 >= kChunks) {   // this warp's last read of the accumulator
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&ctl->tempty[acc]));
           }
-          if (c64 == BN / 64 - 1) tc_fence_before();
+          bool ok = true;
+          if (gk >= 1) ok = mbar_wait(smem_u32(&ctl->stg_free[grp]), (gk - 1u) & 1u, abortf);
+          if (!__all_sync(0xffffffffu, ok)) { live = false; break; }
+          const uint32_t cbase = tn * BN + c64 * 64;
+          if (p.bias) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j)
+              if (cbase + j < p.OC) v[j] = __float_as_uint(__uint_as_float(v[j]) + p.bias[cbase + j]);
+          }
+          if (p.relu) {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) v[j] = __float_as_uint(fmaxf(__uint_as_float(v[j]), 0.f));
+          }
+#pragma unroll
+          for (uint32_t g8 = 0; g8 < 8; ++g8) {
+            uint4 pk;
+            __nv_bfloat162* p2 = (__nv_bfloat162*)&pk;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              p2[j] = __floats2bfloat162_rn(__uint_as_float(v[g8 * 8 + 2 * j]), __uint_as_float(v[g8 * 8 + 2 * j + 1]));
+            *(uint4*)(srow + ((g8 ^ m7) * 16u)) = pk;
+          }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           __syncwarp();
-          if (lane == 0) {
-            if (c64 == BN / 64 - 1) mbar_arrive(smem_u32(&ctl->tempty[acc]));   // accumulator drained
-            mbar_arrive(smem_u32(&ctl->stg_full[b]));
-          }
-          if (q == 0 && lane == 0) {
-            if (mbar_wait(smem_u32(&ctl->stg_full[b]), (cc >> 1) & 1u, abortf)) {
-              if (tn * BN + c64 * 64 < p.OC)
+          if (lane == 0) mbar_arrive(smem_u32(&ctl->stg_full[grp]));
+          if (leader && lane == 0) {
+            if (mbar_wait(smem_u32(&ctl->stg_full[grp]), gk & 1u, abortf)) {
+              if (cbase < p.OC)
                 asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(&map_o),
-                             "r"(smem_u32(stg)), "r"((int)(tn * BN + c64 * 64)), "r"((int)(tx * p.TW)), "r"((int)(ty * p.TH)),
-                             "r"((int)n)
+                             "r"(smem_u32(stg)), "r"((int)cbase), "r"((int)(tx * p.TW)), "r"((int)(ty * p.TH)), "r"((int)n)
                              : "memory");
               asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-              asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-              if (cc >= 1) mbar_arrive(smem_u32(&ctl->stg_free[b ^ 1u]));
+              asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+              mbar_arrive(smem_u32(&ctl->stg_free[grp]));
             }
           }
           __syncwarp();
@@ -258,6 +269,9 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         if (!live) break;
         continue;
       }
+      if (grp != 0) continue;   // the scattered-store form is served by the first group alone
+      if (!mbar_wait(smem_u32(&ctl->tfull[acc]), acc_phase, abortf)) break;
+      tc_fence_after();
       const uint32_t oy = ty * p.TH + m / p.TW, ox = tx * p.TW + m % p.TW;
       const bool valid = oy < p.OP && ox < p.OQ;
       __nv_bfloat16* orow = p.out + (long long)n * p.out_plane + (long long)oy * p.out_pitch + (long long)ox * p.OC;
@@ -312,7 +326,7 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&ctl->tempty[acc]));
     }
-    if (p.tma_store && q == 0 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    if (p.tma_store && leader && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   tc_fence_before();
@@ -575,7 +589,7 @@ static int launch_fwd(const CUtensorMap& ma, const CUtensorMap& mb, const CUtens
   }
   const uint32_t total = p.NI * p.tiles_y * p.tiles_x * p.tiles_n;
   const unsigned grid = total < (uint32_t)kNumSMs ? total : kNumSMs;
-  conv_tc_fwd_kernel<BN, STAGES><<<grid, kThreads, smem, s>>>(ma, mb, mo, p);
+  conv_tc_fwd_kernel<BN, STAGES><<<grid, kFwdThreads, smem, s>>>(ma, mb, mo, p);
   count_launch();
   return launch_status();
 }

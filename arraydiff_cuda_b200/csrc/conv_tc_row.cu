@@ -176,27 +176,33 @@ conv_tc_row_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         bool ok = true;
         if (it >= 2) ok = mbar_wait(smem_u32(&ctl->stg_free[b]), ((it >> 1) - 1u) & 1u, abortf);
         if (!__all_sync(0xffffffffu, ok)) break;   // leave together: the tensor-memory loads below are warp-wide
-#pragma unroll 1
-        for (uint32_t ch = 0; ch < BN / 32; ++ch) {
-          uint32_t v[32];
-          tmem_ld32(tmem_base + ((q * 32u) << 16) + acc * BN + ch * 32, v);
+        {
+          // both halves of the 64 columns are requested before the wait; bias / ReLU are uniform branches
+          static_assert(BN == 64, "one 64-channel chunk per tile");
+          uint32_t v[64];
+          const uint32_t taddr = tmem_base + ((q * 32u) << 16) + acc * BN;
+          tmem_ld32(taddr, *(uint32_t(*)[32])&v[0]);
+          tmem_ld32(taddr + 32, *(uint32_t(*)[32])&v[32]);
           tmem_ld_wait();
+          if (p.bias) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const uint32_t cg = ch * 32 + g * 8;
-            float f[8];
+            for (int j = 0; j < 64; ++j)
+              if ((uint32_t)j < p.OC) v[j] = __float_as_uint(__uint_as_float(v[j]) + p.bias[j]);
+          }
+          if (p.relu) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              f[j] = __uint_as_float(v[g * 8 + j]);
-              if (p.bias && cg + j < p.OC) f[j] += p.bias[cg + j];
-              if (p.relu) f[j] = fmaxf(f[j], 0.f);
-            }
+            for (int j = 0; j < 64; ++j) v[j] = __float_as_uint(fmaxf(__uint_as_float(v[j]), 0.f));
+          }
+          uint8_t* srow = stg + m * 128u;
+          const uint32_t m7 = m & 7u;
+#pragma unroll
+          for (uint32_t g8 = 0; g8 < 8; ++g8) {
             uint4 pk;
             __nv_bfloat162* p2 = (__nv_bfloat162*)&pk;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) p2[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
-            const uint32_t chunk = (cg >> 3) ^ (m & 7u);
-            *(uint4*)(stg + m * 128u + chunk * 16u) = pk;
+            for (int j = 0; j < 4; ++j)
+              p2[j] = __floats2bfloat162_rn(__uint_as_float(v[g8 * 8 + 2 * j]), __uint_as_float(v[g8 * 8 + 2 * j + 1]));
+            *(uint4*)(srow + ((g8 ^ m7) * 16u)) = pk;
           }
         }
         // accumulator drained: hand it back to the MMA warp

@@ -653,7 +653,7 @@ def main():
         sampler.start()
     launches0 = L.ad_launch_count()
     ms = timed_loop(torch, dist, step, args.steps, False, world)
-    launches = net.graph_launches() * args.steps if use_graph else L.ad_launch_count() - launches0
+    launches = L.ad_launch_count() - launches0
     clocks = sampler.stop() if rank == 0 else None
     step.check_status()
     for _ in range(2):
