@@ -87,6 +87,8 @@ SIGNATURES = {
     "ad_relu_bwd": (C.c_int, [C.POINTER(Tensor4)] * 3 + [i32, vp]),
     "ad_add": (C.c_int, [C.POINTER(Tensor4)] * 3 + [vp]),
     "ad_convert": (C.c_int, [C.POINTER(Tensor4), C.POINTER(Tensor4), i32, vp]),
+    "ad_upsample_bilinear_fwd": (C.c_int, [C.POINTER(Tensor4), C.POINTER(Tensor4), u32, i32, u32, u32, vp]),
+    "ad_upsample_bilinear_bwd": (C.c_int, [C.POINTER(Tensor4), C.POINTER(Tensor4), u32, i32, u32, u32, i32, vp]),
     "ad_im2col": (C.c_int, [C.POINTER(Tensor4)] + [u32] * 8 + [vp, u32, vp]),
     "ad_conv2d_scratch_bytes": (sz, [C.POINTER(Conv2dArgs), i32]),
     "ad_conv2d_fprop": (C.c_int, [C.POINTER(Conv2dArgs), vp]),

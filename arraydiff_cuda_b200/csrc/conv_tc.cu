@@ -502,6 +502,22 @@ __global__ void __launch_bounds__(256) wgrad_reduce_kernel(size_t n, uint32_t sp
   dw[i] = accumulate ? dw[i] + t : t;
 }
 
+// up[n][y][x][:] = dy[n][y/sh][x/sw][:] where both divisions are exact, else 0  (16-byte groups of channels)
+__global__ void __launch_bounds__(256) zero_insert_kernel(const uint4* __restrict__ dy, uint4* up, uint32_t N, uint32_t P,
+                                                          uint32_t Q, uint32_t DP, uint32_t DQ, uint32_t G, uint32_t sh,
+                                                          uint32_t sw) {
+  const size_t total = (size_t)N * DP * DQ * G, nt = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nt) {
+    const uint32_t g = (uint32_t)(i % G);
+    size_t r = i / G;
+    const uint32_t x = (uint32_t)(r % DQ); r /= DQ;
+    const uint32_t y = (uint32_t)(r % DP), n = (uint32_t)(r / DP);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (y % sh == 0 && x % sw == 0) v = dy[(((size_t)n * P + y / sh) * Q + x / sw) * G + g];
+    up[i] = v;
+  }
+}
+
 // Filter for the data gradient: wt[c][kh-1-r][kw-1-s][k] = w[k][r][s][c]  (bf16).
 __global__ void __launch_bounds__(256) filter_transpose_flip_kernel(uint32_t K, uint32_t kh, uint32_t kw, uint32_t C,
                                                                     const __nv_bfloat16* __restrict__ w,
@@ -705,7 +721,13 @@ size_t conv_tc_scratch_bytes(const ad_conv2d_args* a, int pass) {
   Geo g;
   if (conv_geo(a, g) != AD_OK) return 0;
   const size_t wcount = (size_t)a->K * a->kh * a->kw * a->C;
-  if (pass == 1) return wcount * 2 + 16;  // transposed, mirrored filter (bf16) + status word
+  if (pass == 1) {
+    // status word + transposed, mirrored filter (bf16) [+ the zero-inserted copy of dy for a strided layer]
+    size_t b = ((wcount * 2 + 16 + 1023) / 1024) * 1024;
+    if (a->stride_h != 1 || a->stride_w != 1)
+      b += (size_t)a->N * ((g.P - 1) * a->stride_h + 1) * ((g.Q - 1) * a->stride_w + 1) * a->K * 2;
+    return b;
+  }
   if (pass == 2) {
     uint32_t TH, TW;
     pick_tile(g.P, g.Q, 1, 1, TH, TW);
@@ -748,7 +770,6 @@ int conv_tc_dgrad(const ad_conv2d_args* a, cudaStream_t s) {
   int st = conv_geo(a, g);
   if (st != AD_OK) return st;
   if (!a->y || !a->w || !a->dx || !a->scratch) return AD_ERR_BAD_ARG;
-  if (a->stride_h != 1 || a->stride_w != 1) return AD_ERR_UNSUPPORTED;
   if (a->y_pitch || a->y_plane) return AD_ERR_UNSUPPORTED;  // dy must be dense for the TMA view
   if (a->K % 64 != 0) return AD_ERR_UNSUPPORTED;
   if (a->scratch_bytes < conv_tc_scratch_bytes(a, 1)) return AD_ERR_SCRATCH;
@@ -760,7 +781,21 @@ int conv_tc_dgrad(const ad_conv2d_args* a, cudaStream_t s) {
   count_launch();
   // dx[n,yy,xx,c] = sum_{r',s',k} dy[n, yy + ph - (kh-1)*dh + r'*dh, xx + ..., k] * wt[c][r'][s'][k]
   const int offy = (int)a->pad_h - (int)((a->kh - 1) * a->dil_h), offx = (int)a->pad_w - (int)((a->kw - 1) * a->dil_w);
-  return run_fwd_gemm(a->y, a->N, g.P, g.Q, a->K, wt, a->C, a->kh, a->kw, 1, 1, a->dil_h, a->dil_w, offy, offx, a->H,
+  const void* dy = a->y;
+  uint32_t DP = g.P, DQ = g.Q;
+  if (a->stride_h != 1 || a->stride_w != 1) {
+    // Strided layer: the data gradient is the stride-1 gradient of dy with (stride - 1) zeros inserted
+    // between its pixels.  The zero-inserted copy lives in scratch; the tensor-core kernel then runs
+    // unchanged (and multiplies the zeros -- strided layers are few).
+    DP = (g.P - 1) * a->stride_h + 1; DQ = (g.Q - 1) * a->stride_w + 1;
+    __nv_bfloat16* up = (__nv_bfloat16*)((char*)a->scratch + ((wcount * 2 + 16 + 1023) / 1024) * 1024);
+    const size_t total8 = (size_t)a->N * DP * DQ * (a->K / 8);
+    zero_insert_kernel<<<grid_for(total8, 256, 16), 256, 0, s>>>((const uint4*)a->y, (uint4*)up, a->N, g.P, g.Q, DP, DQ,
+                                                                   a->K / 8, a->stride_h, a->stride_w);
+    count_launch();
+    dy = up;
+  }
+  return run_fwd_gemm(dy, a->N, DP, DQ, a->K, wt, a->C, a->kh, a->kw, 1, 1, a->dil_h, a->dil_w, offy, offx, a->H,
                       a->W, a->dx, 0, 0, nullptr, 0, a->accumulate, status, s);
 }
 

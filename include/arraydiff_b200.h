@@ -260,6 +260,23 @@ int ad_maxpool2d_fwd(const ad_tensor4* x, const ad_tensor4* y, uint32_t kh, uint
 int ad_maxpool2d_bwd(const ad_tensor4* x, const ad_tensor4* dy, const ad_tensor4* dx, uint32_t kh,
                      uint32_t kw, uint32_t sh, uint32_t sw, int32_t accumulate, void* stream);
 
+/*
+ * Bilinear x`scale` upsample (half-pixel centres, edges clamped: the align_corners = false rule) of a
+ * strip, and its gradient.  No counterpart in the reference, whose segmentation head was never written;
+ * this is the step between the 1/8-resolution logits and the per-pixel loss
+ * (CudnnSoftmaxNLLLossOp, src/op.cc:4190-4236) in the 1024x2048 configuration.
+ *   x: rows [x_row0, x_row0 + x.H) of a low-resolution tensor of in_rows_total rows (x_row0 may be -1:
+ *      a halo row above the first row); y: rows [y_row0, y_row0 + y.H) of the scale-times larger result,
+ *      y.W == x.W * scale.  Every source row the y rows refer to must lie inside x, else AD_ERR_BAD_ARG.
+ *   fwd: y = interp(x).   bwd: dx (+)= interp^T(dy) over the dy rows given -- rows of dx that belong to a
+ *      neighbouring strip (halo rows) receive this strip's share, to be summed by ad_halo_reduce.
+ *      The gradient is a gather in a fixed order: no atomics, reproducible.
+ */
+int ad_upsample_bilinear_fwd(const ad_tensor4* x, const ad_tensor4* y, uint32_t scale, int32_t x_row0,
+                             uint32_t in_rows_total, uint32_t y_row0, void* stream);
+int ad_upsample_bilinear_bwd(const ad_tensor4* dy, const ad_tensor4* dx, uint32_t scale, int32_t x_row0,
+                             uint32_t in_rows_total, uint32_t y_row0, int32_t accumulate, void* stream);
+
 /* ReLU and residual sum on strided views (CudnnActivationOp src/op.cc:3054-3344,
  * JoinOp<SumJoin> src/op.cc:745-802, :859-864).  Any of the views may alias.
  *   ad_relu_fwd: y = max(x,0);  ad_relu_bwd: dx (+)= dy*[x>0];  ad_add: y = a + b. */

@@ -297,3 +297,46 @@ def test_nhwc_bf16_vector_paths_match_scalar_semantics():
     abi.check(L.ad_convert(C.byref(va), C.byref(vdx), 1, H.stream()))
     H.sync()
     assert np.array_equal(_back(tdx, abi.AD_NHWC, 0, Hh, W), orc.round_bf16(orc.round_bf16(b + np.where(a > 0, b, 0)) + a))
+
+
+@pytest.mark.parametrize("layout", [abi.AD_NCHW, abi.AD_NHWC])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("R,scale", [(1, 8), (2, 8), (4, 2), (2, 3)])
+def test_upsample_bilinear_strips_equal_unpartitioned(layout, dtype, R, scale):
+    """Each strip (with one halo row on its inner edges) upsamples to exactly its rows of the oracle's
+    unpartitioned result; the strip gradients, overlap-added over the halo rows, give the oracle's gradient."""
+    N, Cc, Hh, W = 2, 5, 8, 6
+    x = H.normal(50, (N, Cc, Hh, W))
+    dy = H.uniform(51, (N, Cc, Hh * scale, W * scale))
+    if dtype == "bf16":
+        x, dy = orc.round_bf16(x), orc.round_bf16(dy)
+    y_w = orc.upsample_bilinear_fwd(x, scale)
+    dx_w = orc.upsample_bilinear_bwd(dy, scale)
+    L = abi.lib()
+    h = Hh // R
+    dx_sum = np.zeros((N, Cc, Hh + 2, W), np.float64)     # row i holds global row i - 1
+    for r in range(R):
+        xs = np.zeros((N, Cc, h + 2, W), np.float32)
+        lo, hi = max(0, r * h - 1), min(Hh, (r + 1) * h + 1)
+        xs[:, :, lo - (r * h - 1):hi - (r * h - 1)] = x[:, :, lo:hi]
+        tx, vx = _views(xs, layout, dtype)
+        ty, vy = _views(np.zeros((N, Cc, h * scale, W * scale), np.float32), layout, dtype)
+        tdy, vdy = _views(dy[:, :, r * h * scale:(r + 1) * h * scale], layout, dtype)
+        tdx, vdx = _views(np.full((N, Cc, h + 2, W), 7.0, np.float32), layout, dtype)
+        abi.check(L.ad_upsample_bilinear_fwd(C.byref(vx), C.byref(vy), scale, r * h - 1, Hh, r * h * scale, H.stream()))
+        abi.check(L.ad_upsample_bilinear_bwd(C.byref(vdy), C.byref(vdx), scale, r * h - 1, Hh, r * h * scale, 0, H.stream()))
+        H.sync()
+        got = _back(ty, layout, 0, h * scale, W * scale)
+        want = y_w[:, :, r * h * scale:(r + 1) * h * scale]
+        assert H.max_rel(got, want) < (1e-6 if dtype == "f32" else 8e-3)
+        g = _back(tdx, layout, 0, h + 2, W).astype(np.float64)
+        if r == 0:
+            assert np.all(g[:, :, 0] == 0)                # the row above the tensor receives nothing
+        if r == R - 1:
+            assert np.all(g[:, :, -1] == 0)
+        dx_sum[:, :, r * h:r * h + h + 2] += g
+    assert H.max_rel(dx_sum[:, :, 1:-1], dx_w) < (1e-5 if dtype == "f32" else 8e-3)
+    # a view that lacks a needed source row is refused before any launch
+    tx, vx = _views(np.zeros((N, Cc, Hh - 1, W), np.float32), layout, dtype)
+    ty, vy = _views(np.zeros((N, Cc, Hh * scale, W * scale), np.float32), layout, dtype)
+    assert L.ad_upsample_bilinear_fwd(C.byref(vx), C.byref(vy), scale, 0, Hh, 0, H.stream()) == abi.AD_ERR_BAD_ARG
