@@ -480,8 +480,8 @@ conv_tc_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_co
 }
 
 // dw[i] (+)= sum over splits of partial[s][i], fixed order.
-__global__ void __launch_bounds__(256) wgrad_reduce_kernel(size_t n, uint32_t splits, const float* __restrict__ partial,
-                                                           float* dw, int accumulate) {
+__global__ void __launch_bounds__(256) wgrad_reduce_kernel(size_t n, size_t part_stride, uint32_t splits,
+                                                           const float* __restrict__ partial, float* dw, int accumulate) {
   // 64 outputs x 4 split lanes per block: lane l sums splits l, l+4, ... (8 loads in flight), lanes combine in order
   const uint32_t tx = threadIdx.x & 63, pl = threadIdx.x >> 6;
   const size_t i = (size_t)blockIdx.x * 64 + tx;
@@ -490,7 +490,7 @@ __global__ void __launch_bounds__(256) wgrad_reduce_kernel(size_t n, uint32_t sp
     for (uint32_t s0 = pl; s0 < splits; s0 += 32) {
       float v[8];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) { const uint32_t si = s0 + 4 * u; v[u] = si < splits ? partial[(size_t)si * n + i] : 0.f; }
+      for (int u = 0; u < 8; ++u) { const uint32_t si = s0 + 4 * u; v[u] = si < splits ? partial[(size_t)si * part_stride + i] : 0.f; }
 #pragma unroll
       for (int u = 0; u < 8; ++u) t += v[u];
     }
@@ -518,18 +518,29 @@ __global__ void __launch_bounds__(256) zero_insert_kernel(const uint4* __restric
   }
 }
 
-// Filter for the data gradient: wt[c][kh-1-r][kw-1-s][k] = w[k][r][s][c]  (bf16).
-__global__ void __launch_bounds__(256) filter_transpose_flip_kernel(uint32_t K, uint32_t kh, uint32_t kw, uint32_t C,
-                                                                    const __nv_bfloat16* __restrict__ w,
+// Filter for the data gradient: wt[c][kh-1-r][kw-1-s][k] = w[k][r][s][c]  (bf16); rows of Kp >= K
+// entries, zero past K.
+__global__ void __launch_bounds__(256) filter_transpose_flip_kernel(uint32_t K, uint32_t Kp, uint32_t kh, uint32_t kw,
+                                                                    uint32_t C, const __nv_bfloat16* __restrict__ w,
                                                                     __nv_bfloat16* wt) {
-  const size_t total = (size_t)K * kh * kw * C, nt = (size_t)gridDim.x * blockDim.x;
+  const size_t total = (size_t)Kp * kh * kw * C, nt = (size_t)gridDim.x * blockDim.x;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nt) {
-    uint32_t k = (uint32_t)(i % K);
-    size_t rr = i / K;
+    uint32_t k = (uint32_t)(i % Kp);
+    size_t rr = i / Kp;
     uint32_t s = (uint32_t)(rr % kw); rr /= kw;
     uint32_t r = (uint32_t)(rr % kh);
     uint32_t c = (uint32_t)(rr / kh);
-    wt[i] = w[(((size_t)k * kh + (kh - 1 - r)) * kw + (kw - 1 - s)) * C + c];
+    wt[i] = k < K ? w[(((size_t)k * kh + (kh - 1 - r)) * kw + (kw - 1 - s)) * C + c] : __float2bfloat16_rn(0.f);
+  }
+}
+// dst[pixel][0..Kp) = src[pixel][0..K), zero past K
+__global__ void __launch_bounds__(256) pad_channels_kernel(size_t pixels, uint32_t K, uint32_t Kp,
+                                                           const __nv_bfloat16* __restrict__ src, __nv_bfloat16* dst) {
+  const size_t total = pixels * Kp, nt = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nt) {
+    const uint32_t k = (uint32_t)(i % Kp);
+    const size_t px = i / Kp;
+    dst[i] = k < K ? src[px * K + k] : __float2bfloat16_rn(0.f);
   }
 }
 
@@ -717,26 +728,42 @@ static uint32_t wgrad_splits(uint32_t sp_tiles, uint32_t outer) {
   return want;
 }
 
+static size_t round_1k(size_t b) { return (b + 1023) / 1024 * 1024; }
+// Gradient channel counts the tensor-core kernels take as they are: the data gradient reduces over K in
+// 64-channel slabs, the filter gradient needs 16-byte pixel pitches of dy.  Other counts (a 19-class head)
+// run on a zero-padded copy of dy kept in scratch.
+static uint32_t dgrad_kp(uint32_t K) { return (K + 63) / 64 * 64; }
+static uint32_t wgrad_kp(uint32_t K) { return (K + 7) / 8 * 8; }
+
+// Scratch layouts:
+//   pass 1 (data gradient):   [status 16 B | transposed filter C,R,S,Kp bf16] [dy padded to Kp channels, if Kp != K]
+//                             [dy with zeros inserted, if strided]
+//   pass 2 (filter gradient): [status 16 B] [dy padded, if Kp != K] [fp32 partials]
 size_t conv_tc_scratch_bytes(const ad_conv2d_args* a, int pass) {
   Geo g;
   if (conv_geo(a, g) != AD_OK) return 0;
-  const size_t wcount = (size_t)a->K * a->kh * a->kw * a->C;
+  const size_t pixels = (size_t)a->N * g.P * g.Q;
   if (pass == 1) {
-    // status word + transposed, mirrored filter (bf16) [+ the zero-inserted copy of dy for a strided layer]
-    size_t b = ((wcount * 2 + 16 + 1023) / 1024) * 1024;
+    const uint32_t Kp = dgrad_kp(a->K);
+    size_t b = round_1k((size_t)Kp * a->kh * a->kw * a->C * 2 + 16);
+    if (Kp != a->K) b += round_1k(pixels * Kp * 2);
     if (a->stride_h != 1 || a->stride_w != 1)
-      b += (size_t)a->N * ((g.P - 1) * a->stride_h + 1) * ((g.Q - 1) * a->stride_w + 1) * a->K * 2;
+      b += round_1k((size_t)a->N * ((g.P - 1) * a->stride_h + 1) * ((g.Q - 1) * a->stride_w + 1) * Kp * 2);
     return b;
   }
   if (pass == 2) {
+    const uint32_t Kp = wgrad_kp(a->K);
+    const size_t wcount = (size_t)Kp * a->kh * a->kw * a->C;
     uint32_t TH, TW;
     pick_tile(g.P, g.Q, 1, 1, TH, TW);
     const uint32_t sp = a->N * ((g.P + TH - 1) / TH) * ((g.Q + TW - 1) / TW);
     const uint32_t BN = a->C > 64 ? 128 : 64;
-    const uint32_t outer = a->kh * a->kw * ((a->K + 127) / 128) * ((a->C + BN - 1) / BN);
-    size_t general = (size_t)wgrad_splits(sp, outer) * wcount * 4 + 16;
-    size_t row = conv_tc_row_wgrad_scratch(a->N, a->C, a->K, a->kh, a->kw, a->stride_h, a->stride_w, a->dil_h, a->dil_w, g.P, g.Q) + 16;
-    return general > row ? general : row;
+    const uint32_t outer = a->kh * a->kw * ((Kp + 127) / 128) * ((a->C + BN - 1) / BN);
+    size_t general = (size_t)wgrad_splits(sp, outer) * wcount * 4;
+    size_t row = conv_tc_row_wgrad_scratch(a->N, a->C, a->K, a->kh, a->kw, a->stride_h, a->stride_w, a->dil_h, a->dil_w, g.P, g.Q);
+    size_t b = 1024 + (general > row ? general : row);
+    if (Kp != a->K) b += round_1k(pixels * Kp * 2);
+    return b;
   }
   return 16;
 }
@@ -771,31 +798,39 @@ int conv_tc_dgrad(const ad_conv2d_args* a, cudaStream_t s) {
   if (st != AD_OK) return st;
   if (!a->y || !a->w || !a->dx || !a->scratch) return AD_ERR_BAD_ARG;
   if (a->y_pitch || a->y_plane) return AD_ERR_UNSUPPORTED;  // dy must be dense for the TMA view
-  if (a->K % 64 != 0) return AD_ERR_UNSUPPORTED;
   if (a->scratch_bytes < conv_tc_scratch_bytes(a, 1)) return AD_ERR_SCRATCH;
+  const uint32_t Kp = dgrad_kp(a->K);
   int32_t* status = (int32_t*)a->scratch;
   __nv_bfloat16* wt = (__nv_bfloat16*)((char*)a->scratch + 16);
-  const size_t wcount = (size_t)a->K * a->kh * a->kw * a->C;
-  filter_transpose_flip_kernel<<<grid_for(wcount, 256), 256, 0, s>>>(a->K, a->kh, a->kw, a->C,
+  char* next = (char*)a->scratch + round_1k((size_t)Kp * a->kh * a->kw * a->C * 2 + 16);
+  const size_t wcount = (size_t)Kp * a->kh * a->kw * a->C;
+  filter_transpose_flip_kernel<<<grid_for(wcount, 256), 256, 0, s>>>(a->K, Kp, a->kh, a->kw, a->C,
                                                                      (const __nv_bfloat16*)a->w, wt);
   count_launch();
+  const void* dy = a->y;
+  if (Kp != a->K) {
+    const size_t pixels = (size_t)a->N * g.P * g.Q;
+    pad_channels_kernel<<<grid_for(pixels * Kp, 256, 16), 256, 0, s>>>(pixels, a->K, Kp, (const __nv_bfloat16*)a->y,
+                                                                        (__nv_bfloat16*)next);
+    count_launch();
+    dy = next;
+    next += round_1k(pixels * Kp * 2);
+  }
   // dx[n,yy,xx,c] = sum_{r',s',k} dy[n, yy + ph - (kh-1)*dh + r'*dh, xx + ..., k] * wt[c][r'][s'][k]
   const int offy = (int)a->pad_h - (int)((a->kh - 1) * a->dil_h), offx = (int)a->pad_w - (int)((a->kw - 1) * a->dil_w);
-  const void* dy = a->y;
   uint32_t DP = g.P, DQ = g.Q;
   if (a->stride_h != 1 || a->stride_w != 1) {
     // Strided layer: the data gradient is the stride-1 gradient of dy with (stride - 1) zeros inserted
     // between its pixels.  The zero-inserted copy lives in scratch; the tensor-core kernel then runs
     // unchanged (and multiplies the zeros -- strided layers are few).
     DP = (g.P - 1) * a->stride_h + 1; DQ = (g.Q - 1) * a->stride_w + 1;
-    __nv_bfloat16* up = (__nv_bfloat16*)((char*)a->scratch + ((wcount * 2 + 16 + 1023) / 1024) * 1024);
-    const size_t total8 = (size_t)a->N * DP * DQ * (a->K / 8);
-    zero_insert_kernel<<<grid_for(total8, 256, 16), 256, 0, s>>>((const uint4*)a->y, (uint4*)up, a->N, g.P, g.Q, DP, DQ,
-                                                                   a->K / 8, a->stride_h, a->stride_w);
+    const size_t total8 = (size_t)a->N * DP * DQ * (Kp / 8);
+    zero_insert_kernel<<<grid_for(total8, 256, 16), 256, 0, s>>>((const uint4*)dy, (uint4*)next, a->N, g.P, g.Q, DP, DQ,
+                                                                   Kp / 8, a->stride_h, a->stride_w);
     count_launch();
-    dy = up;
+    dy = next;
   }
-  return run_fwd_gemm(dy, a->N, DP, DQ, a->K, wt, a->C, a->kh, a->kw, 1, 1, a->dil_h, a->dil_w, offy, offx, a->H,
+  return run_fwd_gemm(dy, a->N, DP, DQ, Kp, wt, a->C, a->kh, a->kw, 1, 1, a->dil_h, a->dil_w, offy, offx, a->H,
                       a->W, a->dx, 0, 0, nullptr, 0, a->accumulate, status, s);
 }
 
@@ -805,13 +840,25 @@ int conv_tc_wgrad(const ad_conv2d_args* a, cudaStream_t s) {
   if (st != AD_OK) return st;
   if (!a->x || !a->y || !a->dw || !a->scratch) return AD_ERR_BAD_ARG;
   if (a->y_pitch || a->y_plane) return AD_ERR_UNSUPPORTED;
-  if (a->C % 64 != 0 || a->K % 8 != 0) return AD_ERR_UNSUPPORTED;
+  if (a->C % 64 != 0) return AD_ERR_UNSUPPORTED;
   if (a->scratch_bytes < conv_tc_scratch_bytes(a, 2)) return AD_ERR_SCRATCH;
-  if (!getenv("ARRAYDIFF_B200_NO_ROW_KERNEL")) {
+  const uint32_t Kp = wgrad_kp(a->K);
+  const void* dy = a->y;
+  char* part_base = (char*)a->scratch + 1024;
+  if (Kp != a->K) {
+    const size_t pixels = (size_t)a->N * g.P * g.Q;
+    pad_channels_kernel<<<grid_for(pixels * Kp, 256, 16), 256, 0, s>>>(pixels, a->K, Kp, (const __nv_bfloat16*)a->y,
+                                                                        (__nv_bfloat16*)part_base);
+    count_launch();
+    dy = part_base;
+    part_base += round_1k(pixels * Kp * 2);
+  }
+  const size_t part_bytes = a->scratch_bytes - (size_t)(part_base - (char*)a->scratch);
+  if (Kp == a->K && !getenv("ARRAYDIFF_B200_NO_ROW_KERNEL")) {
     // 64-channel layers: one CTA serves all taps from one fetch of x and dy (conv_tc_row.cu)
     st = conv_tc_row_wgrad(a->x, a->N, a->H, a->W, a->C, a->y, a->K, a->kh, a->kw, a->stride_h, a->stride_w, a->dil_h,
                            a->dil_w, -(int)a->pad_h, -(int)a->pad_w, g.P, g.Q, (float*)a->dw, a->accumulate,
-                           (char*)a->scratch + 16, a->scratch_bytes - 16, (int32_t*)a->scratch, s);
+                           part_base, part_bytes, (int32_t*)a->scratch, s);
     if (st == AD_OK && a->db) {
       dim3 block(32, 8);
       bias_grad_nhwc_kernel<<<(a->K + 31) / 32, block, 0, s>>>(a->N, g.P, g.Q, a->K, (long long)g.Q * a->K,
@@ -822,7 +869,7 @@ int conv_tc_wgrad(const ad_conv2d_args* a, cudaStream_t s) {
     if (st != AD_ERR_UNSUPPORTED) return st;
   }
   WgParams p{};
-  p.NI = a->N; p.OP = g.P; p.OQ = g.Q; p.KO = a->K; p.CI = a->C;
+  p.NI = a->N; p.OP = g.P; p.OQ = g.Q; p.KO = Kp; p.CI = a->C;
   p.kh = a->kh; p.kw = a->kw; p.sh = a->stride_h; p.sw = a->stride_w; p.dh = a->dil_h; p.dw = a->dil_w;
   p.offy = -(int)a->pad_h; p.offx = -(int)a->pad_w;
   // The tile is chosen for the dy grid; the x box is the same patch scaled by the stride.
@@ -835,22 +882,22 @@ int conv_tc_wgrad(const ad_conv2d_args* a, cudaStream_t s) {
   p.tiles_y = (g.P + p.TH - 1) / p.TH;
   p.tiles_x = (g.Q + p.TW - 1) / p.TW;
   const int BN = a->C > 64 ? 128 : 64;
-  p.ktiles = (a->K + 127) / 128;
+  p.ktiles = (Kp + 127) / 128;
   p.ctiles = (a->C + BN - 1) / BN;
   const uint32_t sp_tiles = p.NI * p.tiles_y * p.tiles_x;
   p.splits = wgrad_splits(sp_tiles, p.kh * p.kw * p.ktiles * p.ctiles);
   p.status = (int32_t*)a->scratch;
-  p.partial = (float*)((char*)a->scratch + 16);
-  const size_t wcount = (size_t)a->K * a->kh * a->kw * a->C;
-  if (a->scratch_bytes < (size_t)p.splits * wcount * 4 + 16) return AD_ERR_SCRATCH;
+  p.partial = (float*)part_base;
+  const size_t wcount = (size_t)a->K * a->kh * a->kw * a->C, wcount_p = (size_t)Kp * a->kh * a->kw * a->C;
+  if (part_bytes < (size_t)p.splits * wcount_p * 4) return AD_ERR_SCRATCH;
 
   CUtensorMap mdy, mx;
   {
-    uint64_t dims[4] = {a->K, g.Q, g.P, a->N};
-    uint64_t str[4] = {0, (uint64_t)a->K * 2, (uint64_t)g.Q * a->K * 2, (uint64_t)g.P * g.Q * a->K * 2};
+    uint64_t dims[4] = {Kp, g.Q, g.P, a->N};
+    uint64_t str[4] = {0, (uint64_t)Kp * 2, (uint64_t)g.Q * Kp * 2, (uint64_t)g.P * g.Q * Kp * 2};
     uint32_t box[4] = {64, p.TW, p.TH, 1};
     uint32_t es[4] = {1, 1, 1, 1};
-    st = make_tmap_bf16(&mdy, a->y, 4, dims, str, box, es);
+    st = make_tmap_bf16(&mdy, dy, 4, dims, str, box, es);
     if (st != AD_OK) return st;
   }
   {
@@ -863,7 +910,7 @@ int conv_tc_wgrad(const ad_conv2d_args* a, cudaStream_t s) {
   }
   st = BN == 128 ? launch_wgrad<128>(mdy, mx, p, s) : launch_wgrad<64>(mdy, mx, p, s);
   if (st != AD_OK) return st;
-  wgrad_reduce_kernel<<<(unsigned)((wcount + 63) / 64), 256, 0, s>>>(wcount, p.splits, p.partial, (float*)a->dw, a->accumulate);
+  wgrad_reduce_kernel<<<(unsigned)((wcount + 63) / 64), 256, 0, s>>>(wcount, wcount_p, p.splits, p.partial, (float*)a->dw, a->accumulate);
   count_launch();
   if (a->db) {
     dim3 block(32, 8);
