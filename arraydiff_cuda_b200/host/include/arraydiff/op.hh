@@ -481,6 +481,49 @@ private:
   vector<ActVar> xs_;
 };
 
+// Bilinear x`scale` upsample of an H-strip (half-pixel centres, edges clamped).  The input is the strip
+// halo-padded by one row and exchanged, so that each strip produces exactly its rows of the
+// unpartitioned result; the gradient leaves the neighbours' shares in the halo rows, where the halo
+// exchange's backward pass sums them.  Not in the reference: the segmentation head it never wrote.
+class UpsampleBilinear2DOpF : public ActOp {
+public:
+  static vector<ActVar> MakeParallel(size_t scale, vector<ActVar> inputs, shared_ptr<Context> ctx);
+  UpsampleBilinear2DOpF(size_t scale, size_t num_ranks, ActVar x, shared_ptr<Context> ctx);
+  void _forward(TxnId txn) override;
+  void _backward(TxnId txn) override;
+private:
+  ad_tensor4 low_view(Act& a) const;
+  ActVar x_;
+  size_t scale_, num_ranks_;
+};
+
+// Per-pixel softmax + negative log likelihood over the channel axis: the 3-D case of
+// CudnnSoftmaxNLLLossOp that the reference asserts as unimplemented (src/op.cc:4190-4236).  A sink:
+// forward fills loss[n][y][x] = logsumexp_c(x) - x[label], backward writes
+// dx (+)= dloss * (softmax - onehot) with the per-pixel weight set by set_loss_weight (1 / pixels of
+// the whole batch for a mean loss).  Labels are uint32 [N][h][W] of this rank's strip.
+class CudnnSoftmaxNLLLoss2DOpF : public virtual Op {
+public:
+  static vector<shared_ptr<CudnnSoftmaxNLLLoss2DOpF>> MakeParallel(vector<ActVar> logits, shared_ptr<Context> ctx);
+  CudnnSoftmaxNLLLoss2DOpF(ActVar x, shared_ptr<Context> ctx);
+  void _forward(TxnId txn) override;
+  void _backward(TxnId txn) override;
+  void _set_grad_sink(TxnId) override {}
+  string _debug_op_label() override { return "CudnnSoftmaxNLLLossOp"; }
+  size_t rank() const { return x_->rank(); }
+  size_t pixels() const { return n_ * hw_; }
+  void load_labels(const uint32_t* host);      // synchronous host -> device copy
+  void set_loss_weight(float w);
+  double loss_sum();                           // synchronous: sum of the per-pixel losses of the last forward
+  void store_loss(float* host);                // synchronous: the per-pixel losses
+private:
+  ActVar x_;
+  shared_ptr<Context> ctx_;
+  size_t n_, hw_, classes_;
+  uint32_t* labels_ = nullptr;
+  float *loss_ = nullptr, *dloss_ = nullptr;
+};
+
 // Joins the per-rank sub-graphs under one root so that a single walk orders every rank's operators
 // (the reference's graphs end in one scalar loss; a feature extractor has one output per rank).
 class GroupSinkOp : public virtual Op {
@@ -503,6 +546,8 @@ template <typename V> using CudnnPool2DOp = CudnnPool2DOpF;
 template <typename S, typename V = Act, typename A = GPUArray1D<float>> using CudnnBatchNorm2DOp = CudnnBatchNorm2DOpF;
 template <typename V> using CudnnActivationOp = CudnnActivationOpF;
 template <typename V, typename J = SumJoin> using JoinOp = SumJoinOpF;
+template <typename V> using UpsampleBilinear2DOp = UpsampleBilinear2DOpF;
+template <typename V> using CudnnSoftmaxNLLLossOp = CudnnSoftmaxNLLLoss2DOpF;
 
 }  // namespace arraydiff
 #endif

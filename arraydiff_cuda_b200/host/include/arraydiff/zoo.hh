@@ -41,11 +41,20 @@ public:
 
 // A spatially partitioned feature extractor: per-rank inputs (the full image, scattered into
 // H-strips inside the graph), per-rank outputs (strips), and the per-rank variable sets.
+// Depth / width of the dilated segmentation net: channels of stage s are base << s (x4 at the block
+// outputs); blocks {3,4,6,3} with base 64 is ResNet-50.
+struct SegNetConfig {
+  size_t base = 64;
+  size_t blocks[4] = {3, 4, 6, 3};
+  size_t classes = 19;
+};
+
 struct SpatialParallelNet {
   shared_ptr<bool> batch_norm_use_fixed;
   vector<shared_ptr<IOOp<Act>>> inputs;
   vector<ActVar> outputs;
-  shared_ptr<Op> sink;          // GroupSinkOp over all outputs: walk from here
+  vector<shared_ptr<CudnnSoftmaxNLLLoss2DOpF>> losses;   // per-rank loss sinks (nets that end in a loss)
+  shared_ptr<Op> sink;          // GroupSinkOp over all outputs (or losses): walk from here
   VarIdSet input_vars;
   vector<VarIdSet> output_grad_vars;
   vector<VarIdSet> dev_params, dev_grads, dev_batch_stats, dev_fixed_stats;
@@ -60,6 +69,9 @@ public:
   // ResNet-50 stem + stage 1: 7x7/2 conv to 64 channels, BN, ReLU, 3x3/2 max pool, then three
   // pre-activation bottleneck blocks (64-64-256), the first with a 1x1 projection.
   static SpatialParallelNet MakeStemStage1(const ConvNetConfig& config, shared_ptr<Context> ctx);
+  // Dilated ResNet-50 segmentation net at output stride 8 with a bilinear x8 head and per-pixel loss
+  // (the 1024x2048, 19-class configuration); labels go to net.losses[r]->load_labels.
+  static SpatialParallelNet MakeSegNet50(const ConvNetConfig& config, const SegNetConfig& seg, shared_ptr<Context> ctx);
 };
 
 }  // namespace arraydiff

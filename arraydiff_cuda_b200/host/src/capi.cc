@@ -63,6 +63,14 @@ void* adh_net_create(void* c, const char* kind, int H, int W, int C, int batch, 
   n->rng.seed(seed);
   if (!std::strcmp(kind, "conv3x3")) n->net = SpatialParallelResNet<float>::MakeConv3x3(n->cfg, (size_t)filters, n->ctx);
   else if (!std::strcmp(kind, "stem_stage1")) n->net = SpatialParallelResNet<float>::MakeStemStage1(n->cfg, n->ctx);
+  else if (!std::strncmp(kind, "segnet", 6)) {
+    // "segnet50": ResNet-50 depth; "segnet_small": one block per stage; `filters` (if > 0) = stem width
+    SegNetConfig seg;
+    if (filters > 0) seg.base = (size_t)filters;
+    if (!std::strcmp(kind, "segnet_small")) for (auto& b : seg.blocks) b = 1;
+    else if (std::strcmp(kind, "segnet50")) { delete n; return nullptr; }
+    n->net = SpatialParallelResNet<float>::MakeSegNet50(n->cfg, seg, n->ctx);
+  }
   else { delete n; return nullptr; }
   SGDConfig sc;
   sc.step_size = make_shared<ConstantSchedule<double>>(0.1);
@@ -182,11 +190,41 @@ int adh_net_step_resident(void* h, int with_update) {
   n->opt->persist(*n->txn);
   n->net.sink->persist(*n->txn, n->net.input_vars);
   n->net.sink->eval(*n->txn);
-  for (size_t r = 0; r < n->ctx->num_ranks(); ++r)
-    if (n->ctx->is_local(r)) n->net.sink->load_grad(*n->txn, n->net.output_grad_vars[r], 0, nullptr);
+  if (n->net.losses.empty())   // a net that ends in a loss makes its own output gradient
+    for (size_t r = 0; r < n->ctx->num_ranks(); ++r)
+      if (n->ctx->is_local(r)) n->net.sink->load_grad(*n->txn, n->net.output_grad_vars[r], 0, nullptr);
   n->net.sink->backward(*n->txn);
   if (with_update) n->opt->step(*n->txn);
   return AD_OK;
+}
+// labels of `rank`'s strip, uint32 [N][h][W] (nets that end in the per-pixel loss)
+int adh_net_set_labels(void* h, int rank, const uint32_t* host) {
+  auto* n = (Net*)h;
+  for (auto& l : n->net.losses)
+    if ((int)l->rank() == rank) { l->load_labels(host); return AD_OK; }
+  return AD_ERR_BAD_ARG;
+}
+// sum of the per-pixel losses of the local ranks' strips and the number of pixels behind it (synchronous)
+int adh_net_loss(void* h, double* sum, uint64_t* pixels) {
+  auto* n = (Net*)h;
+  if (n->net.losses.empty()) return AD_ERR_BAD_ARG;
+  double s = 0.0;
+  uint64_t px = 0;
+  for (auto& l : n->net.losses) { s += l->loss_sum(); px += l->pixels(); }
+  *sum = s; *pixels = px;
+  return AD_OK;
+}
+// gradient of an output strip (packed NCHW fp32): what the loss wrote, or what set_output_grad loaded
+int adh_net_get_output_grad(void* h, int rank, float* host_strip) {
+  auto* n = (Net*)h;
+  for (auto& o : n->net.outputs) {
+    if ((int)o->rank() != rank) continue;
+    VarIdSet v = VarIdSet::Singleton(o->data().grad.var());
+    any w = host_strip;
+    n->net.sink->store_grad(*n->txn, v, 0, &w);
+    return AD_OK;
+  }
+  return AD_ERR_BAD_ARG;
 }
 // The same step replayed from a CUDA graph.  The first call (and any call after the schedule values or
 // `with_update` changed) records adh_net_step_resident on the ranks' streams -- rank 0's stream is the

@@ -727,4 +727,110 @@ void SumJoinOpF::_backward(TxnId txn) {
   }
 }
 
+// ------------------------------------------------------------------ bilinear upsample of a strip
+vector<ActVar> UpsampleBilinear2DOpF::MakeParallel(size_t scale, vector<ActVar> inputs, shared_ptr<Context> ctx) {
+  vector<ActVar> out;
+  for (auto& x : inputs) out.push_back(make_shared<UpsampleBilinear2DOpF>(scale, num_ranks_of(ctx, inputs.size()), x, ctx));
+  return out;
+}
+UpsampleBilinear2DOpF::UpsampleBilinear2DOpF(size_t scale, size_t num_ranks, ActVar x, shared_ptr<Context> ctx)
+    : ActOp(x->rank(), ctx), x_(x), scale_(scale), num_ranks_(num_ranks) {
+  inputs_.push_back(x);
+  Shape3D d = x->shape();
+  alloc_output(Shape3D(d.shape[0] * scale, d.shape[1] * scale, d.shape[2]), 0, 0, x->batch_shape());
+}
+// all rows of the (halo-padded) buffer, interior columns only
+ad_tensor4 UpsampleBilinear2DOpF::low_view(Act& a) const {
+  ad_tensor4 v = a.view_base();
+  v.base = (char*)v.base + (long long)a.offset().shape[0] * v.sx * (long long)a.elem_size();
+  v.W = (uint32_t)a.dim().shape[0];
+  return v;
+}
+void UpsampleBilinear2DOpF::_forward(TxnId txn) {
+  if (!y_.val.overwrite(txn, id())) return;
+  GPUConn conn = gpu()->conn();
+  Act& x = x_->data().val.get(txn, id());
+  const size_t p = x.offset().shape[1], h = x.dim().shape[1];
+  assert((p >= 1 || num_ranks_ == 1) && "a partitioned upsample reads one halo row of each neighbour");
+  ad_tensor4 xv = low_view(x), yv = y_.val.get_excl(txn, id()).view_interior();
+  AD_CHECK(ad_upsample_bilinear_fwd(&xv, &yv, (uint32_t)scale_, (int32_t)(rank_ * h) - (int32_t)p, (uint32_t)(h * num_ranks_),
+                                    (uint32_t)(rank_ * h * scale_), conn.stream()));
+}
+void UpsampleBilinear2DOpF::_backward(TxnId txn) {
+  auto xd = x_->data();
+  // every interior column of every row (halo rows included) is written; the zero pad columns of a
+  // gradient buffer are never read
+  const int mode = xd.grad.accumulate_full(txn, id(), always, zero_init(gpu()));
+  if (!mode) return;
+  GPUConn conn = gpu()->conn();
+  Act& dx = xd.grad.get_mut(txn, id());
+  const size_t p = dx.offset().shape[1], h = dx.dim().shape[1];
+  ad_tensor4 dxv = low_view(dx), dyv = y_.grad.get(txn, id()).view_interior();
+  AD_CHECK(ad_upsample_bilinear_bwd(&dyv, &dxv, (uint32_t)scale_, (int32_t)(rank_ * h) - (int32_t)p, (uint32_t)(h * num_ranks_),
+                                    (uint32_t)(rank_ * h * scale_), mode == 1 ? 1 : 0, conn.stream()));
+}
+
+// ------------------------------------------------------------------ per-pixel softmax + NLL (sink)
+vector<shared_ptr<CudnnSoftmaxNLLLoss2DOpF>> CudnnSoftmaxNLLLoss2DOpF::MakeParallel(vector<ActVar> logits, shared_ptr<Context> ctx) {
+  vector<shared_ptr<CudnnSoftmaxNLLLoss2DOpF>> out;
+  for (auto& x : logits) out.push_back(make_shared<CudnnSoftmaxNLLLoss2DOpF>(x, ctx));
+  return out;
+}
+CudnnSoftmaxNLLLoss2DOpF::CudnnSoftmaxNLLLoss2DOpF(ActVar x, shared_ptr<Context> ctx) : x_(x), ctx_(ctx) {
+  inputs_.push_back(x);
+  Shape3D d = x->shape();
+  n_ = x->batch_shape(); hw_ = d.shape[0] * d.shape[1]; classes_ = d.shape[2];
+  GPUContext* g = gpu_of(ctx_, x_->rank());
+  GPUConn conn = g->conn();
+  labels_ = (uint32_t*)g->arena().alloc(n_ * hw_ * sizeof(uint32_t));
+  loss_ = (float*)g->arena().alloc(n_ * hw_ * sizeof(float));
+  dloss_ = (float*)g->arena().alloc(n_ * hw_ * sizeof(float));
+  AD_CHECK(ad_fill_zero(labels_, n_ * hw_ * sizeof(uint32_t), conn.stream()));
+  AD_CHECK(ad_fill_zero(loss_, n_ * hw_ * sizeof(float), conn.stream()));
+  AD_CHECK(ad_array_set_constant(n_ * hw_, 1.0f, dloss_, conn.stream()));
+  conn.sync();
+}
+void CudnnSoftmaxNLLLoss2DOpF::load_labels(const uint32_t* host) {
+  GPUConn conn = gpu_of(ctx_, x_->rank())->conn();
+  CUDA_CHECK(cudaMemcpyAsync(labels_, host, n_ * hw_ * sizeof(uint32_t), cudaMemcpyHostToDevice, conn.stream()));
+  conn.sync();
+}
+void CudnnSoftmaxNLLLoss2DOpF::set_loss_weight(float w) {
+  GPUConn conn = gpu_of(ctx_, x_->rank())->conn();
+  AD_CHECK(ad_array_set_constant(n_ * hw_, w, dloss_, conn.stream()));
+  conn.sync();
+}
+void CudnnSoftmaxNLLLoss2DOpF::store_loss(float* host) {
+  GPUConn conn = gpu_of(ctx_, x_->rank())->conn();
+  CUDA_CHECK(cudaMemcpyAsync(host, loss_, n_ * hw_ * sizeof(float), cudaMemcpyDeviceToHost, conn.stream()));
+  conn.sync();
+}
+double CudnnSoftmaxNLLLoss2DOpF::loss_sum() {
+  vector<float> h(n_ * hw_);
+  store_loss(h.data());
+  double s = 0.0;
+  for (float v : h) s += (double)v;
+  return s;
+}
+void CudnnSoftmaxNLLLoss2DOpF::_forward(TxnId txn) {
+  GPUConn conn = gpu_of(ctx_, x_->rank())->conn();
+  Act& x = x_->data().val.get(txn, id());
+  assert(x.offset().shape[0] == 0 && x.offset().shape[1] == 0 && "the loss reads dense logits");
+  const bool f32 = x.storage() == COMPUTE_F32_NCHW;
+  AD_CHECK(ad_softmax_ce_pixel_fwd(f32 ? AD_F32 : AD_BF16, f32 ? AD_NCHW : AD_NHWC, (uint32_t)n_, (uint32_t)classes_, (uint32_t)hw_,
+                                   x.base_dptr(), labels_, loss_, nullptr, conn.stream()));
+}
+void CudnnSoftmaxNLLLoss2DOpF::_backward(TxnId txn) {
+  auto xd = x_->data();
+  GPUContext* g = gpu_of(ctx_, x_->rank());
+  const int mode = xd.grad.accumulate_full(txn, id(), unpadded, zero_init(g));
+  if (!mode) return;
+  GPUConn conn = g->conn();
+  Act& x = xd.val.get(txn, id());
+  Act& dx = xd.grad.get_mut(txn, id());
+  const bool f32 = x.storage() == COMPUTE_F32_NCHW;
+  AD_CHECK(ad_softmax_ce_pixel_bwd(f32 ? AD_F32 : AD_BF16, f32 ? AD_NCHW : AD_NHWC, (uint32_t)n_, (uint32_t)classes_, (uint32_t)hw_,
+                                   x.base_dptr(), labels_, dloss_, dx.base_dptr(), mode == 1 ? 1 : 0, conn.stream()));
+}
+
 }  // namespace arraydiff

@@ -259,28 +259,32 @@ SpatialParallelNet SpatialParallelResNet<float>::MakeConv3x3(const ConvNetConfig
   return net;
 }
 
+// ResNet stem on H-strips: halo 3, 7x7/2 -> `width` channels, BN + ReLU, then a 3x3/2 max pool on a halo-1 strip
+static vector<ActVar> stem(SpatialParallelNet& net, const ConvNetConfig& cfg, size_t width, vector<ActVar> strips, shared_ptr<Context> ctx) {
+  auto sw = net.batch_norm_use_fixed;
+  Conv2DShape c1;
+  c1.filters = width; c1.kernel = {7, 7}; c1.stride = {2, 2}; c1.pad = {3, 3}; c1.halo_padded_input = true;
+  auto pad1 = HaloPad2DOpF::MakeParallel(3, strips, ctx);
+  auto exch1 = HaloExch2DOpF::MakeParallel(3, pad1, ctx);
+  ParallelParamOp<Act> conv1;
+  { NameScope scope("stem.conv"); conv1 = parallel_conv2d<Act>(c1, exch1, kaiming_init_gen<GPUArray4D<float>>(cfg.input_c * 49, width), false, ctx); }
+  absorb(net, conv1.ops, conv1.params, conv1.grads);
+  ParallelBatchNormParamOp<Act> bn1;
+  { NameScope scope("stem.bn"); bn1 = parallel_batch_norm<Act>(width, sw, conv1.ops, true, ctx); }
+  absorb(net, bn1.ops, bn1.params, bn1.grads, &bn1.batch_stats, &bn1.fixed_stats);
+  Pool2DShape pool;
+  pool.window = {3, 3}; pool.stride = {2, 2}; pool.pad = {1, 1}; pool.halo_padded_input = true;
+  auto pad2 = HaloPad2DOpF::MakeParallel(1, bn1.ops, ctx);
+  auto exch2 = HaloExch2DOpF::MakeParallel(1, pad2, ctx);
+  return CudnnPool2DOpF::MakeParallel(pool, exch2, ctx);
+}
+
 template <>
 SpatialParallelNet SpatialParallelResNet<float>::MakeStemStage1(const ConvNetConfig& cfg, shared_ptr<Context> ctx) {
   vector<ActVar> strips;
   SpatialParallelNet net = begin_net(cfg, ctx, strips);
   auto sw = net.batch_norm_use_fixed;
-  // stem: halo 3, 7x7/2 -> 64
-  Conv2DShape c1;
-  c1.filters = 64; c1.kernel = {7, 7}; c1.stride = {2, 2}; c1.pad = {3, 3}; c1.halo_padded_input = true;
-  auto pad1 = HaloPad2DOpF::MakeParallel(3, strips, ctx);
-  auto exch1 = HaloExch2DOpF::MakeParallel(3, pad1, ctx);
-  ParallelParamOp<Act> conv1;
-  { NameScope scope("stem.conv"); conv1 = parallel_conv2d<Act>(c1, exch1, kaiming_init_gen<GPUArray4D<float>>(cfg.input_c * 49, 64), false, ctx); }
-  absorb(net, conv1.ops, conv1.params, conv1.grads);
-  ParallelBatchNormParamOp<Act> bn1;
-  { NameScope scope("stem.bn"); bn1 = parallel_batch_norm<Act>(64, sw, conv1.ops, true, ctx); }
-  absorb(net, bn1.ops, bn1.params, bn1.grads, &bn1.batch_stats, &bn1.fixed_stats);
-  // 3x3/2 max pool on a halo-1 strip
-  Pool2DShape pool;
-  pool.window = {3, 3}; pool.stride = {2, 2}; pool.pad = {1, 1}; pool.halo_padded_input = true;
-  auto pad2 = HaloPad2DOpF::MakeParallel(1, bn1.ops, ctx);
-  auto exch2 = HaloExch2DOpF::MakeParallel(1, pad2, ctx);
-  auto pooled = CudnnPool2DOpF::MakeParallel(pool, exch2, ctx);
+  auto pooled = stem(net, cfg, 64, strips, ctx);
   // stage 1: bottlenecks 64-64-256
   Conv2DShape b;
   b.filters = 64; b.kernel = {3, 3}; b.pad = {1, 1};
@@ -293,6 +297,53 @@ SpatialParallelNet SpatialParallelResNet<float>::MakeStemStage1(const ConvNetCon
     absorb(net, blk.ops, blk.params, blk.grads, &blk.batch_stats, &blk.fixed_stats);
   }
   finish_net(net, blk.ops);
+  return net;
+}
+
+// Dilated ResNet-50 for per-pixel classification at output stride 8: stem, stages of pre-activation
+// bottlenecks (stage 2 strided, stages 3 and 4 dilated by 2 and 4 with halos of 2 and 4 rows), BN + ReLU,
+// 1x1 classifier with bias, x8 bilinear upsample of the halo-1 logits, per-pixel softmax NLL.
+// Built from the same spatial_parallel_* blocks as the reference's nets (src/zoo.cc:740-946); the head is
+// the one its CudnnSoftmaxNLLLossOp stops short of (src/op.cc:4225).
+template <>
+SpatialParallelNet SpatialParallelResNet<float>::MakeSegNet50(const ConvNetConfig& cfg, const SegNetConfig& seg, shared_ptr<Context> ctx) {
+  vector<ActVar> strips;
+  SpatialParallelNet net = begin_net(cfg, ctx, strips);
+  auto sw = net.batch_norm_use_fixed;
+  vector<ActVar> cur = stem(net, cfg, seg.base, strips, ctx);
+  const size_t strides[4] = {1, 2, 1, 1}, dils[4] = {1, 1, 2, 4};
+  for (int st = 0; st < 4; ++st) {
+    Conv2DShape b;
+    b.filters = seg.base << st; b.kernel = {3, 3}; b.dilate = {dils[st], dils[st]}; b.pad = {dils[st], dils[st]};
+    for (size_t i = 0; i < seg.blocks[st]; ++i) {
+      NameScope scope("stage" + std::to_string(st + 1) + ".block" + std::to_string(i + 1));
+      ParallelBatchNormParamOp<Act> blk =
+          i == 0 ? spatial_parallel_proj_bottleneck_residual_v2_conv2d<Act>(b, 4, strides[st], sw, cur, ctx)
+                 : spatial_parallel_bottleneck_residual_v2_conv2d<Act>(b, 4, sw, cur, ctx);
+      absorb(net, blk.ops, blk.params, blk.grads, &blk.batch_stats, &blk.fixed_stats);
+      cur = blk.ops;
+    }
+  }
+  ParallelBatchNormParamOp<Act> bnf;
+  { NameScope scope("head.bn"); bnf = parallel_batch_norm<Act>((seg.base << 3) * 4, sw, cur, true, ctx); }
+  absorb(net, bnf.ops, bnf.params, bnf.grads, &bnf.batch_stats, &bnf.fixed_stats);
+  Conv2DShape hc;
+  hc.filters = seg.classes; hc.kernel = {1, 1};
+  ParallelParamOp<Act> head;
+  { NameScope scope("head.conv"); head = parallel_conv2d<Act>(hc, bnf.ops, kaiming_init_gen<GPUArray4D<float>>((seg.base << 3) * 4, seg.classes), true, ctx); }
+  absorb(net, head.ops, head.params, head.grads);
+  auto padl = HaloPad2DOpF::MakeParallel(1, head.ops, ctx);
+  auto exchl = HaloExch2DOpF::MakeParallel(1, padl, ctx);
+  auto up = UpsampleBilinear2DOpF::MakeParallel(8, exchl, ctx);
+  net.losses = CudnnSoftmaxNLLLoss2DOpF::MakeParallel(up, ctx);
+  size_t pixels = 0;
+  const size_t R = ranks_of(ctx);
+  for (auto& l : net.losses) pixels = l->pixels() * R;   // equal strips
+  for (auto& l : net.losses) l->set_loss_weight(1.0f / (float)pixels);   // gradient of the mean loss over the whole batch
+  net.outputs = up;
+  vector<shared_ptr<Op>> members(net.losses.begin(), net.losses.end());
+  net.sink = make_shared<GroupSinkOp>(members);
+  for (auto& o : up) net.output_grad_vars[o->rank()].insert(o->data().grad.var());
   return net;
 }
 

@@ -45,6 +45,9 @@ def load():
         L.adh_net_output_dims.argtypes = [vp, C.POINTER(C.c_int)]
         L.adh_net_forward.argtypes = [vp, vp]
         L.adh_net_step_resident.argtypes = [vp, C.c_int]
+        L.adh_net_set_labels.argtypes = [vp, C.c_int, vp]
+        L.adh_net_loss.argtypes = [vp, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]
+        L.adh_net_get_output_grad.argtypes = [vp, C.c_int, vp]
         L.adh_net_step_graph.argtypes = [vp, C.c_int]
         L.adh_net_graph_launches.restype = C.c_uint64
         L.adh_net_graph_launches.argtypes = [vp]
@@ -74,7 +77,7 @@ class Context:
 
 
 class Net:
-    """kind: 'conv3x3' or 'stem_stage1'."""
+    """kind: 'conv3x3', 'stem_stage1', 'segnet50' or 'segnet_small' (one block per stage; `filters` = stem width)."""
 
     def __init__(self, ctx, kind, H, W, Cin, batch=1, filters=64, seed=1):
         self.L, self.ctx = ctx.L, ctx
@@ -126,6 +129,23 @@ class Net:
 
     def backward(self):
         self.L.adh_net_backward(self.h)
+
+    def set_labels(self, rank, labels):
+        """uint32 [N][h][W] labels of `rank`'s strip (nets that end in the per-pixel loss)"""
+        labels = np.ascontiguousarray(labels, np.uint32)
+        assert labels.shape == (self.strip_shape[0],) + self.strip_shape[2:]
+        assert self.L.adh_net_set_labels(self.h, rank, _p(labels)) == 0
+
+    def loss(self):
+        """(sum of the per-pixel losses over the local strips, pixels behind it) of the last forward"""
+        s, n = C.c_double(), C.c_uint64()
+        assert self.L.adh_net_loss(self.h, C.byref(s), C.byref(n)) == 0
+        return s.value, n.value
+
+    def output_grad(self, rank):
+        a = np.empty(self.strip_shape, np.float32)
+        assert self.L.adh_net_get_output_grad(self.h, rank, _p(a)) == 0
+        return a
 
     def param_grads(self, rank):
         a = np.empty(self.nparam, np.float32)

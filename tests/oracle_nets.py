@@ -39,16 +39,17 @@ class BnRelu:
 
 
 class Conv:
-    def __init__(self, w, stride=1, pad=0, q=_ident):
-        self.w, self.s, self.p, self.q = w, (stride, stride), (pad, pad), q
+    def __init__(self, w, stride=1, pad=0, q=_ident, dil=1, bias=None):
+        self.w, self.s, self.p, self.q, self.d, self.b = w, (stride, stride), (pad, pad), q, (dil, dil), bias
 
     def fwd(self, x):
         self.x = x
-        return self.q(orc.conv2d_fprop(x, self.w, None, self.s, (1, 1), self.p, omp=True))
+        return self.q(orc.conv2d_fprop(x, self.w, self.b, self.s, self.d, self.p, omp=True))
 
     def bwd(self, dy, need_dx=True):
-        dw = orc.conv2d_wgrad(self.x, dy, self.w.shape, self.s, (1, 1), self.p, omp=True)
-        dx = self.q(orc.conv2d_dgrad(dy, self.w, self.x.shape, self.s, (1, 1), self.p, omp=True)) if need_dx else None
+        self.db = np.zeros(self.w.shape[0], np.float32) if self.b is not None else None
+        dw = orc.conv2d_wgrad(self.x, dy, self.w.shape, self.s, self.d, self.p, db=self.db, omp=True)
+        dx = self.q(orc.conv2d_dgrad(dy, self.w, self.x.shape, self.s, self.d, self.p, omp=True)) if need_dx else None
         return dx, dw
 
 
@@ -120,6 +121,98 @@ class StemStage1:
                 g = bn_b(b + ".bn0", d)
             else:
                 g = self.q(g + bn_b(b + ".bn0", d))
+        dpool = self.q(orc.maxpool2d_bwd(self.pool_in, g, (3, 3), (2, 2), omp=True)[:, :, 1:-1, 1:-1])
+        d = bn_b("stem.bn", np.ascontiguousarray(dpool))
+        conv_b("stem.conv", d, need_dx=False)
+        return G
+
+
+class SegNet:
+    """Dilated bottleneck ResNet at output stride 8 -> BN+ReLU -> 1x1 classifier (bias) -> x8 bilinear ->
+    per-pixel softmax NLL (mean over all pixels).  Stage s: width base << s, blocks[s] pre-activation
+    bottlenecks, the first with a projection; stage 2 strided by 2, stages 3 / 4 dilated by 2 / 4."""
+
+    def __init__(self, P, R, blocks, bf16=False):
+        self.P, self.R, self.blocks = P, R, blocks
+        self.q = orc.round_bf16 if bf16 else _ident
+
+    def _bn(self, name):
+        return BnRelu(self.P[name + ".scale"], self.P[name + ".shift"], self.R, self.q)
+
+    def _conv(self, name, stride=1, pad=0, dil=1):
+        return Conv(self.P[name + ".kernel"], stride, pad, self.q, dil, self.P.get(name + ".bias"))
+
+    def forward(self, x, labels):
+        L = self.L = {}
+        L["stem.conv"] = self._conv("stem.conv", 2, 3)
+        L["stem.bn"] = self._bn("stem.bn")
+        a = L["stem.bn"].fwd(L["stem.conv"].fwd(x))
+        self.pool_in = np.zeros((a.shape[0], a.shape[1], a.shape[2] + 2, a.shape[3] + 2), np.float32)
+        self.pool_in[:, :, 1:-1, 1:-1] = a
+        t = orc.maxpool2d_fwd(self.pool_in, (3, 3), (2, 2), omp=True)
+        strides, dils = (1, 2, 1, 1), (1, 1, 2, 4)
+        for st in range(4):
+            for i in range(self.blocks[st]):
+                b = f"stage{st + 1}.block{i + 1}"
+                stride = strides[st] if i == 0 else 1
+                L[b + ".bn0"] = self._bn(b + ".bn0")
+                a0 = L[b + ".bn0"].fwd(t)
+                L[b + ".conv1"] = self._conv(b + ".conv1")
+                L[b + ".bn1"] = self._bn(b + ".bn1")
+                a1 = L[b + ".bn1"].fwd(L[b + ".conv1"].fwd(a0))
+                L[b + ".conv2"] = self._conv(b + ".conv2", stride, dils[st], dils[st])
+                L[b + ".bn2"] = self._bn(b + ".bn2")
+                a2 = L[b + ".bn2"].fwd(L[b + ".conv2"].fwd(a1))
+                L[b + ".conv3"] = self._conv(b + ".conv3")
+                c3 = L[b + ".conv3"].fwd(a2)
+                if i == 0:
+                    L[b + ".proj"] = self._conv(b + ".proj", stride)
+                    t = self.q(L[b + ".proj"].fwd(a0) + c3)
+                else:
+                    t = self.q(t + c3)
+        L["head.bn"] = self._bn("head.bn")
+        L["head.conv"] = self._conv("head.conv")
+        logits = L["head.conv"].fwd(L["head.bn"].fwd(t))
+        self.up = self.q(orc.upsample_bilinear_fwd(logits, 8))
+        N, Cc, Hh, W = self.up.shape
+        self.labels = np.ascontiguousarray(labels.reshape(N, Hh * W), np.uint32)
+        loss, _, _ = orc.softmax_ce_pixel_fwd(self.up.reshape(N, Cc, Hh * W), self.labels, omp=True)
+        self.loss = loss.reshape(N, Hh, W)
+        return self.up, float(loss.astype(np.float64).mean())
+
+    def backward(self):
+        L, G = self.L, {}
+
+        def bn_b(name, g):
+            dx, dg, db = L[name].bwd(g)
+            G[name + ".scale"], G[name + ".shift"] = dg, db
+            return dx
+
+        def conv_b(name, g, need_dx=True):
+            dx, dw = L[name].bwd(g, need_dx)
+            G[name + ".kernel"] = dw
+            if L[name].b is not None:
+                G[name + ".bias"] = L[name].db
+            return dx
+
+        N, Cc, Hh, W = self.up.shape
+        dloss = np.full((N, Hh * W), 1.0 / (N * Hh * W), np.float32)
+        self.dup = self.q(orc.softmax_ce_pixel_bwd(self.up.reshape(N, Cc, Hh * W), self.labels, dloss, omp=True).reshape(N, Cc, Hh, W))
+        g = self.q(orc.upsample_bilinear_bwd(self.dup, 8))
+        g = bn_b("head.bn", conv_b("head.conv", g))
+        for st in (3, 2, 1, 0):
+            for i in reversed(range(self.blocks[st])):
+                b = f"stage{st + 1}.block{i + 1}"
+                d = conv_b(b + ".conv3", g)
+                d = bn_b(b + ".bn2", d)
+                d = conv_b(b + ".conv2", d)
+                d = bn_b(b + ".bn1", d)
+                d = conv_b(b + ".conv1", d)
+                if i == 0:
+                    d = self.q(d + conv_b(b + ".proj", g))
+                    g = bn_b(b + ".bn0", d)
+                else:
+                    g = self.q(g + bn_b(b + ".bn0", d))
         dpool = self.q(orc.maxpool2d_bwd(self.pool_in, g, (3, 3), (2, 2), omp=True)[:, :, 1:-1, 1:-1])
         d = bn_b("stem.bn", np.ascontiguousarray(dpool))
         conv_b("stem.conv", d, need_dx=False)
