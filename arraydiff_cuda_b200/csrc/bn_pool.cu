@@ -353,7 +353,7 @@ static bool vec_view_ok(const ad_tensor4* t) {
 static unsigned vec_grid(const ad_tensor4* t) {
   const size_t per = (size_t)t->N * t->H * t->W, PL = 256 / (t->C / 8);
   size_t g = (per + PL * kBnUnroll - 1) / (PL * kBnUnroll);
-  if (g > (size_t)kNumSMs * 4) g = (size_t)kNumSMs * 4;
+  if (g > (size_t)kNumSMs * 2) g = (size_t)kNumSMs * 2;   // two resident blocks per SM keep ~5 MB of loads in flight
   if (g > (size_t)bn_max_splits(t->C)) g = bn_max_splits(t->C);
   return (unsigned)(g < 1 ? 1 : g);
 }

@@ -466,11 +466,33 @@ def run_halo_workload(args):
 
 
 # ----------------------------------------------------------------------------- config 3 through the C++ op graph
-def run_stem_workload(args):
+def segnet_flops(N, Hh, W, classes=19, blocks=(3, 4, 6, 3), base=64):
+    """fwd + dgrad + wgrad FLOPs of the dilated ResNet-50 segmentation net (2*N*K*C*kh*kw*P*Q per pass on the
+    unpartitioned output, stem data gradient excluded)."""
+    total = 2.0 * N * base * 3 * 49 * (Hh // 2) * (W // 2) * 2          # stem: fprop + wgrad
+    px, cin = N * (Hh // 4) * (W // 4), base
+    for st in range(4):
+        mid, out = base << st, (base << st) * 4
+        for i in range(blocks[st]):
+            px_out = px // 4 if (st == 1 and i == 0) else px
+            f = 2.0 * px * mid * cin                                     # conv1 1x1
+            f += 2.0 * px_out * mid * mid * 9                            # conv2 3x3 (carries the stride)
+            f += 2.0 * px_out * out * mid                                # conv3 1x1
+            if i == 0:
+                f += 2.0 * px_out * out * cin                            # projection
+            total += 3.0 * f
+            px, cin = px_out, out
+    total += 3.0 * 2.0 * px * classes * cin
+    return total
+
+
+def run_net_workload(args, kind):
     """`--workload stem_stage1`: BASELINE config 3 -- ResNet-50 stem + stage 1 on one 3x1024x1024 image,
     H-partitioned over the GPUs (or over `--strips` ranks sharing one GPU), bf16 operands, forward +
     backward against an upstream gradient N(0,1), filter-gradient allreduce and SGD update, all through
-    the C++ host layer (zoo builder -> op graph -> C ABI kernels).  93.6 GFLOP per step (stem dgrad excluded)."""
+    the C++ host layer (zoo builder -> op graph -> C ABI kernels).  93.6 GFLOP per step (stem dgrad excluded).
+    `--workload segnet`: BASELINE config 4 -- dilated ResNet-50 at output stride 8 on 2x3x1024x2048 with a
+    19-class head, x8 bilinear upsample and per-pixel softmax NLL against uniform random labels."""
     import torch
     import torch.distributed as dist
     from arraydiff_cuda_b200 import abi, hostlib
@@ -478,14 +500,17 @@ def run_stem_workload(args):
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
+    seg = kind == "segnet"
     S = args.image
+    Hh, Ww, NB = (S, 2 * S, 2) if seg else (S, S, 1)
     L = abi.load()
     Lh = hostlib.load()
     keep = []
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-        h = Lh.adh_context_create_distributed(rank, world, local, hostlib.BF16_NHWC, 4096)
+        h = Lh.adh_context_create_distributed(rank, world, local, hostlib.BF16_NHWC,
+                                              (40960 // world + 2048) if seg else 4096)
         hb = C.create_string_buffer(64)
         assert Lh.adh_context_arena_handle(h, hb) == 0
         mine = torch.from_numpy(np.frombuffer(hb.raw, dtype=np.uint8).copy()).cuda()
@@ -513,21 +538,29 @@ def run_stem_workload(args):
     else:
         strips = max(1, args.strips)
         ctx = hostlib.Context([local] * strips, hostlib.BF16_NHWC,
-                              arena_mb=max(512, int(4096 * (S / 1024.0) ** 2) // strips + 256))
+                              arena_mb=max(512, int((40960 if seg else 4096) * (S / 1024.0) ** 2) // strips + 256))
         ranks = list(range(strips))
-    net = hostlib.Net(ctx, "stem_stage1", S, S, 3, 1, seed=1)
+    net = hostlib.Net(ctx, "segnet50" if seg else "stem_stage1", Hh, Ww, 3, NB, seed=1)
     net.configure_sgd(0.01, 0.9, l2=1e-4, nesterov=True)
     rng = np.random.default_rng(7)
-    x = rng.uniform(0, 1, (1, 3, S, S)).astype(np.float32)
-    dy = [rng.standard_normal(net.strip_shape).astype(np.float32) for _ in range(strips)]
+    x = rng.uniform(0, 1, (NB, 3, Hh, Ww)).astype(np.float32)
+    if seg:
+        labels = rng.integers(0, 19, (NB, Hh, Ww)).astype(np.uint32)
+        hs = Hh // strips
+        dy = []
+    else:
+        dy = [rng.standard_normal(net.strip_shape).astype(np.float32) for _ in range(strips)]
 
     def e2e_step():
         net.forward(x)                       # host image -> every local rank (H2D inside)
         for r in ranks:
-            net.set_output_grad(r, dy[r])    # host upstream gradient -> device
+            if seg:
+                net.set_labels(r, labels[:, r * hs:(r + 1) * hs])   # host labels -> device
+            else:
+                net.set_output_grad(r, dy[r])    # host upstream gradient -> device
         net.backward()
         net.sgd_step()
-        return net.output(ranks[0])          # D2H read of a result
+        return net.loss() if seg else net.output(ranks[0])          # D2H read of a result
 
     # steady-state step: the resident step replayed from a CUDA graph (one process per GPU keeps the
     # eager path: its flag epochs change every step)
@@ -579,18 +612,18 @@ def run_stem_workload(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         t_e2e = float(t.item())
     scale = (S / 1024.0) ** 2
-    flops = 93.6e9 * scale
+    flops = segnet_flops(NB, Hh, Ww) if seg else 93.6e9 * scale
     if rank == 0:
         step_s = ms / args.steps * 1e-3
         print(json.dumps({
             "metric": METRIC, "value": flops / step_s / 1e12, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "images_per_s": 1.0 / step_s,
-            "config": {"workload": "resnet50_stem_stage1", "image": [1, 3, S, S], "strips": strips, "layout": "NHWC",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "images_per_s": NB / step_s,
+            "config": {"workload": "resnet50_dilated_segnet" if seg else "resnet50_stem_stage1", "image": [NB, 3, Hh, Ww], "strips": strips, "layout": "NHWC",
                        "bn_statistics": "per strip (as the reference)", "update": "allreduce + Nesterov SGD", "launch": "cuda graph" if use_graph else "eager",
-                       "l2": "activations of one step total ~1.2 GB, larger than L2", "parallelism": f"spatial-h{strips}"},
-            "e2e": {"value": flops / t_e2e / 1e12, "unit": UNIT, "h2d_bytes_per_step": int(x.nbytes + sum(d.nbytes for d in dy) // max(1, world if world > 1 else 1)),
-                    "d2h_bytes_per_step": int(np.prod(net.strip_shape) * 4), "steps": k_e2e, "timing": "host clock between synchronisations"},
+                       "l2": "activations of one step total more than 1 GB, larger than L2", "parallelism": f"spatial-h{strips}"},
+            "e2e": {"value": flops / t_e2e / 1e12, "unit": UNIT, "h2d_bytes_per_step": int(x.nbytes + (labels.nbytes // world if seg else sum(d.nbytes for d in dy))),
+                    "d2h_bytes_per_step": int(np.prod(net.strip_shape[2:]) * NB * 4 if seg else np.prod(net.strip_shape) * 4), "steps": k_e2e, "timing": "host clock between synchronisations"},
             "gpu_launches": int(launches), "clocks": clocks,
         }))
     if world > 1:
@@ -606,9 +639,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
-    ap.add_argument("--workload", default="conv", choices=["conv", "halo", "stem_stage1"],
+    ap.add_argument("--workload", default="conv", choices=["conv", "halo", "stem_stage1", "segnet"],
                     help="conv: the headline spatial conv step; halo: the halo-exchange microbenchmark (config 2); "
-                         "stem_stage1: ResNet-50 stem + stage 1 through the C++ op graph (config 3)")
+                         "stem_stage1: ResNet-50 stem + stage 1 through the C++ op graph (config 3); "
+                         "segnet: dilated ResNet-50 segmentation net, 2x3x1024x2048 (config 4; --image = height)")
     ap.add_argument("--strips", type=int, default=1, help="stem_stage1 on one GPU: ranks sharing the device")
     ap.add_argument("--image", type=int, default=1024, help="stem_stage1: image height = width")
     ap.add_argument("--no-graph", action="store_true", help="stem_stage1: launch every kernel eagerly instead of replaying a CUDA graph")
@@ -623,8 +657,8 @@ def main():
     if args.workload == "halo":
         run_halo_workload(args)
         return
-    if args.workload == "stem_stage1":
-        run_stem_workload(args)
+    if args.workload in ("stem_stage1", "segnet"):
+        run_net_workload(args, args.workload)
         return
 
     import torch
