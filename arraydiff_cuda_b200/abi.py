@@ -44,6 +44,7 @@ class Conv2dArgs(C.Structure):
         ("dx", vp), ("dw", vp), ("db", vp),
         ("scratch", vp), ("scratch_bytes", sz),
         ("out_row_begin", u32), ("out_row_count", u32),
+        ("dx_col_begin", u32), ("dx_col_count", u32),
     ]
 
 

@@ -167,6 +167,7 @@ int conv_direct_dgrad(const ad_conv2d_args* a, cudaStream_t s) {
   int st = geometry(a, g);
   if (st != AD_OK) return st;
   if (!a->y || !a->w || !a->dx) return AD_ERR_BAD_ARG;
+  if (a->dx_col_count) return AD_ERR_UNSUPPORTED;   // column ranges: tensor-core path only
   const size_t total = (size_t)g.N * g.C * g.H * g.W;
   conv_dgrad_f32<<<grid_for(total, 256, 16), 256, 0, s>>>(g, (const float*)a->y, (const float*)a->w, (float*)a->dx);
   count_launch();

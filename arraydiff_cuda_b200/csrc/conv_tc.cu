@@ -830,8 +830,16 @@ int conv_tc_dgrad(const ad_conv2d_args* a, cudaStream_t s) {
     count_launch();
     dy = next;
   }
-  return run_fwd_gemm(dy, a->N, DP, DQ, Kp, wt, a->C, a->kh, a->kw, 1, 1, a->dil_h, a->dil_w, offy, offx, a->H,
-                      a->W, a->dx, 0, 0, nullptr, 0, a->accumulate, status, s);
+  // A column range is the same problem with fewer output columns: shift the input column offset and the
+  // output pointer, keep the pitches of the full tensor.
+  uint32_t c0 = 0, nc = a->W;
+  if (a->dx_col_count) {
+    if ((unsigned long long)a->dx_col_begin + a->dx_col_count > a->W) return AD_ERR_BAD_ARG;
+    c0 = a->dx_col_begin; nc = a->dx_col_count;
+  }
+  return run_fwd_gemm(dy, a->N, DP, DQ, Kp, wt, a->C, a->kh, a->kw, 1, 1, a->dil_h, a->dil_w, offy, offx + (int)c0, a->H,
+                      nc, (__nv_bfloat16*)a->dx + (size_t)c0 * a->C, (long long)a->W * a->C, (long long)a->H * a->W * a->C,
+                      nullptr, 0, a->accumulate, status, s);
 }
 
 int conv_tc_wgrad(const ad_conv2d_args* a, cudaStream_t s) {

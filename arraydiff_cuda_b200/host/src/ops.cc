@@ -554,6 +554,11 @@ void CudnnConv2DOpF::_backward(TxnId txn) {
       AD_CHECK(ad_conv2d_dgrad(&a, s));
     } else {
       a.w = w_bf16_;
+      if (shape_.halo_padded_input && dx.offset().shape[0] > 0) {
+        // the W-pad columns of a gradient buffer are never read (pad / exchange backward take interior columns)
+        a.dx_col_begin = (uint32_t)dx.offset().shape[0];
+        a.dx_col_count = (uint32_t)dx.dim().shape[0];
+      }
       const size_t need = ad_conv2d_scratch_bytes(&a, 1);
       g->reserve_scratch(need);
       a.scratch = g->get_scratch(); a.scratch_bytes = g->scratch_size();

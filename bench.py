@@ -253,6 +253,7 @@ class Step:
             abi.check(L.ad_conv2d_fprop(C.byref(a), s), "fprop")
         # backward: data gradient over the whole padded strip, filter gradient, halo-gradient accumulate-back
         a.y, a.dx, a.dw = self.dy.data_ptr(), self.gx.data_ptr(), self.dw.data_ptr()
+        a.dx_col_begin, a.dx_col_count = PAD, SIZE     # the W-pad columns of the gradient buffer are never read
         abi.check(L.ad_conv2d_dgrad(C.byref(a), s), "dgrad")
         if R > 1:
             # the halo-gradient accumulate-back (signal, wait for the neighbours, pull + add) runs on the
@@ -320,7 +321,9 @@ def kernel_times(torch, step, iters=10):
         a.y = step.y.data_ptr(); abi.check(L.ad_conv2d_fprop(C.byref(a), s))
 
     def dgrad():
-        a.y, a.dx = step.dy.data_ptr(), step.gx.data_ptr(); abi.check(L.ad_conv2d_dgrad(C.byref(a), s))
+        a.y, a.dx = step.dy.data_ptr(), step.gx.data_ptr()
+        a.dx_col_begin, a.dx_col_count = PAD, SIZE
+        abi.check(L.ad_conv2d_dgrad(C.byref(a), s))
 
     def wgrad():
         a.y, a.dw = step.dy.data_ptr(), step.dw.data_ptr(); abi.check(L.ad_conv2d_wgrad(C.byref(a), s))

@@ -339,6 +339,12 @@ typedef struct {
    * strip while its halo rows are still in flight, and the p boundary rows afterwards -- the overlap
    * the reference forgoes by synchronising every device around each exchange (src/op.cc:2976, :3001). */
   uint32_t out_row_begin, out_row_count;
+  /* dgrad on the tensor-core path only: write columns [dx_col_begin, dx_col_begin + dx_col_count) of every
+   * row of dx and leave the others untouched (0, 0 = all columns).  The W-pad columns of a halo-padded
+   * gradient buffer stand for zero-padding cells of x: nothing ever reads them (HaloPad2DOp's backward takes
+   * the interior, src/op.cc:2705-2710; the halo reduce takes interior columns, src/kernels/spatial.cu:191-205),
+   * and leaving them out keeps rows of W = k * 128 pixels free of a nearly empty trailing tile. */
+  uint32_t dx_col_begin, dx_col_count;
 } ad_conv2d_args;
 
 size_t ad_conv2d_scratch_bytes(const ad_conv2d_args* a, int32_t pass /* 0 fprop, 1 dgrad, 2 wgrad */);

@@ -226,3 +226,41 @@ def test_conv_tc_fprop_row_ranges_compose(case):
     assert torch.equal(parts, full) and status[0].item() == 0
     a.out_row_begin, a.out_row_count = P - 1, 2
     assert L.ad_conv2d_fprop(C.byref(a), H.stream()) == abi.AD_ERR_BAD_ARG
+
+
+@pytest.mark.parametrize("case", [(2, 64, 22, 140, 64, 3, 1, 3, 0), (1, 128, 20, 40, 128, 3, 1, 1, 0), (1, 64, 34, 34, 128, 3, 2, 1, 0)])
+def test_conv_tc_dgrad_column_range(case):
+    """The data gradient restricted to the interior columns of a halo-padded buffer == those columns of the
+    full gradient, bit for bit, and the pad columns are not touched."""
+    import torch
+    N, Cc, Hh, W, K, k, s, d, pd = case
+    x, w = _tc_setup(case)
+    P = (Hh + 2 * pd - d * (k - 1) - 1) // s + 1
+    Q = (W + 2 * pd - d * (k - 1) - 1) // s + 1
+    dy = orc.round_bf16(H.uniform(14, (N, K, P, Q)))
+    L = abi.lib()
+    a = conv_args(abi.AD_BF16, abi.AD_NHWC, x.shape, K, k, s, d, pd)
+    dw_ = H.dev_bf16(np.ascontiguousarray(np.transpose(w, (0, 2, 3, 1))))
+    ddy = H.dev_bf16(orc.nchw_to_nhwc(dy))
+    full = torch.zeros((N, Hh, W, Cc), dtype=torch.bfloat16, device="cuda")
+    part = torch.full((N, Hh, W, Cc), 5.0, dtype=torch.bfloat16, device="cuda")
+    nscr = L.ad_conv2d_scratch_bytes(C.byref(a), 1)
+    scratch = torch.zeros(nscr, dtype=torch.uint8, device="cuda")
+    a.w, a.y, a.scratch, a.scratch_bytes = dw_.data_ptr(), ddy.data_ptr(), scratch.data_ptr(), nscr
+    a.dx = full.data_ptr()
+    abi.check(L.ad_conv2d_dgrad(C.byref(a), H.stream()))
+    p = d * (k - 1) // 2
+    a.dx = part.data_ptr()
+    a.dx_col_begin, a.dx_col_count = p, W - 2 * p
+    abi.check(L.ad_conv2d_dgrad(C.byref(a), H.stream()))
+    H.sync()
+    assert scratch[:4].view(torch.int32).item() == 0
+    assert torch.equal(part[:, :, p:W - p], full[:, :, p:W - p])
+    assert torch.all(part[:, :, :p] == 5.0) and torch.all(part[:, :, W - p:] == 5.0)
+    a.dx_col_begin, a.dx_col_count = W - 1, 2
+    assert L.ad_conv2d_dgrad(C.byref(a), H.stream()) == abi.AD_ERR_BAD_ARG
+    a32 = conv_args(abi.AD_F32, abi.AD_NCHW, (1, 4, 8, 8), 4, 3, 1, 1, 0)
+    a32.dx_col_begin, a32.dx_col_count = 1, 6
+    z = torch.zeros(1024, device="cuda")
+    a32.y = a32.w = a32.dx = z.data_ptr()
+    assert L.ad_conv2d_dgrad(C.byref(a32), H.stream()) == abi.AD_ERR_UNSUPPORTED
