@@ -189,6 +189,7 @@ class Step:
         a.x, a.w, a.scratch, a.scratch_bytes = self.x.data_ptr(), self.w.data_ptr(), self.scratch.data_ptr(), nscr
         self.conv = a
         self.epoch = 0
+        self.halo = True       # False: the same step without halo transfers (measures what they cost exposed)
         ha = abi.HaloArgs()
         ha.dtype, ha.layout = abi.AD_BF16, abi.AD_NHWC
         ha.halo_pad, ha.base_width, ha.base_height, ha.num_channels, ha.batch_size = PAD, SIZE, h, CH, BATCH
@@ -232,7 +233,7 @@ class Step:
         # theirs, while the main stream already convolves the interior rows; the PAD boundary rows at
         # either end follow once the halo has landed
         a.y, a.accumulate = self.y.data_ptr(), 0
-        if R > 1:
+        if R > 1 and self.halo:
             main = self.torch.cuda.current_stream()
             self.side.wait_stream(main)
             with self.torch.cuda.stream(self.side):
@@ -255,7 +256,7 @@ class Step:
         a.y, a.dx, a.dw = self.dy.data_ptr(), self.gx.data_ptr(), self.dw.data_ptr()
         a.dx_col_begin, a.dx_col_count = PAD, SIZE     # the W-pad columns of the gradient buffer are never read
         abi.check(L.ad_conv2d_dgrad(C.byref(a), s), "dgrad")
-        if R > 1:
+        if R > 1 and self.halo:
             # the halo-gradient accumulate-back (signal, wait for the neighbours, pull + add) runs on the
             # side stream underneath the filter gradient
             main = self.torch.cuda.current_stream()
@@ -299,6 +300,25 @@ def timed_loop(torch, dist, step, steps, e2e, world):
         ms = float(t.item())
         dist.barrier()
     return ms
+
+
+def step_distribution(torch, dist, step, n, world):
+    """n individually timed steps (CUDA events around each, no host synchronisation in between); per step
+    the max over ranks; returns (median, p10, p90) in ms."""
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(n + 1)]
+    ev[0].record()
+    for i in range(n):
+        step.run()
+        ev[i + 1].record()
+    torch.cuda.synchronize()
+    t = torch.tensor([ev[i].elapsed_time(ev[i + 1]) for i in range(n)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    v = np.sort(t.cpu().numpy())
+    return float(np.median(v)), float(v[int(0.1 * (n - 1))]), float(v[int(round(0.9 * (n - 1)))])
 
 
 def kernel_times(torch, step, iters=10):
@@ -699,6 +719,16 @@ def main():
     ms_e2e = timed_loop(torch, dist, step, e2e_steps, True, world)
     step.check_status()
 
+    med, p10, p90 = step_distribution(torch, dist, step, max(100, args.steps), world)
+    ms_nohalo = None
+    if world > 1:
+        step.halo = False
+        for _ in range(3):
+            step.run()
+        ms_nohalo = timed_loop(torch, dist, step, args.steps, False, world)
+        step.halo = True
+    step.check_status()
+
     total_flops = 3 * flops_per_pass()
     value = total_flops / (ms / args.steps * 1e-3) / 1e12
     e2e_value = total_flops / (ms_e2e / e2e_steps * 1e-3) / 1e12
@@ -724,6 +754,8 @@ def main():
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": hbytes,
                     "d2h_bytes_per_step": step.dw_host.numel() * 4, "steps": e2e_steps},
             "gpu_launches": int(launches),
+            "step_ms": {"median": med, "p10": p10, "p90": p90, "samples": max(100, args.steps)},
+            "halo_exposed_ms": None if ms_nohalo is None else ms / args.steps - ms_nohalo / args.steps,
             "roofline": {"bound": "tensor", "kernel": f"conv_tc_{top}", "achieved": achieved, "peak": peaks["tf_burst"],
                          "unit": "TFLOP/s", "frac": achieved / peaks["tf_burst"],
                          "traffic": NCU_TRAFFIC_BATCH4[top] * BATCH / 4 / world,
