@@ -88,6 +88,10 @@ SIGNATURES = {
     "ad_relu_bwd": (C.c_int, [C.POINTER(Tensor4)] * 3 + [i32, vp]),
     "ad_add": (C.c_int, [C.POINTER(Tensor4)] * 3 + [vp]),
     "ad_convert": (C.c_int, [C.POINTER(Tensor4), C.POINTER(Tensor4), i32, vp]),
+    "ad_avgpool2d_fwd": (C.c_int, [C.POINTER(Tensor4), C.POINTER(Tensor4), u32, u32, u32, u32, vp]),
+    "ad_avgpool2d_bwd": (C.c_int, [C.POINTER(Tensor4), C.POINTER(Tensor4), u32, u32, u32, u32, i32, vp]),
+    "ad_linear_fwd": (C.c_int, [i32, u32, u32, u32, vp, vp, vp, vp, vp]),
+    "ad_linear_bwd": (C.c_int, [i32, u32, u32, u32, vp, vp, vp, vp, vp, vp, i32, i32, vp]),
     "ad_upsample_bilinear_fwd": (C.c_int, [C.POINTER(Tensor4), C.POINTER(Tensor4), u32, i32, u32, u32, vp]),
     "ad_upsample_bilinear_bwd": (C.c_int, [C.POINTER(Tensor4), C.POINTER(Tensor4), u32, i32, u32, u32, i32, vp]),
     "ad_im2col": (C.c_int, [C.POINTER(Tensor4)] + [u32] * 8 + [vp, u32, vp]),

@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libarraydiff_b200.so")
-SOURCES = ["elementwise.cu", "segcopy.cu", "softmax.cu", "bn_pool.cu", "sync.cu", "conv_direct.cu", "conv_tc.cu", "conv_tc_row.cu", "upsample.cu"]
+SOURCES = ["elementwise.cu", "segcopy.cu", "softmax.cu", "bn_pool.cu", "sync.cu", "conv_direct.cu", "conv_tc.cu", "conv_tc_row.cu", "upsample.cu", "head.cu"]
 HEADERS = ["common.cuh", "tc_common.cuh"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

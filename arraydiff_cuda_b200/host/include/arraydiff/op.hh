@@ -481,6 +481,56 @@ private:
   vector<ActVar> xs_;
 };
 
+// Re-assembly of the strips on every rank: y_r = concat_q x_q along H.  The reference builds it from
+// SpatialGather2DOp (strip into a zeroed full tensor) followed by AllreduceOp (src/zoo.cc:1841-1842), which
+// moves R times the bytes; here every rank pulls its peers' strips (peer loads inside one process, peer
+// loads ordered by flag words between processes).  Backward is the matching reduce-scatter:
+// dx_r (+)= sum_q dy_q[rows of strip r], peers in rank order.
+class SpatialAllGather2DOpF;
+// one rank's gathered tensor: owns the buffers, the shared operator fills them
+class AllGatherOutF : public ActOp {
+public:
+  AllGatherOutF(shared_ptr<SpatialAllGather2DOpF> shared, ActVar strip, size_t num_ranks, shared_ptr<Context> ctx);
+  void _forward(TxnId) override {}
+  void _backward(TxnId) override {}
+};
+// One operator over all ranks, like HaloExch2DOp: its backward runs once every rank's consumer has
+// delivered the gradient of its gathered tensor.
+class SpatialAllGather2DOpF : public virtual Op {
+public:
+  static vector<ActVar> MakeParallel(vector<ActVar> inputs, shared_ptr<Context> ctx);
+  SpatialAllGather2DOpF(vector<ActVar> inputs, shared_ptr<Context> ctx);
+  void _forward(TxnId txn) override;
+  void _backward(TxnId txn) override;
+  string _debug_op_label() override { return "SpatialAllGather2DOp"; }
+private:
+  void wait_peers(size_t rank, cudaStream_t s);
+  std::optional<uint64_t> done_fwd_, done_bwd_;
+  vector<ActVar> xs_;
+  vector<AllGatherOutF*> outs_;      // same order as xs_; owned by the graph (they hold this operator as their input)
+  shared_ptr<Context> ctx_;
+  size_t num_ranks_;
+};
+
+// y = x w^T + b on [batch][features] activations (1 x 1 spatial extent), w Shape4D(1,1,in,out) = [out][in] in
+// memory.  The reference's CublasLinearOp (src/op.cc:1199-1340) on GPUBatchArray1D.
+class CublasLinearOpF : public ActOp {
+public:
+  typedef GPUArray4D<float> Kernel;
+  typedef GPUArray1D<float> Bias;
+  static shared_ptr<CublasLinearOpF> Make(size_t filters, ActVar x, shared_ptr<Var<Kernel>> kernel, shared_ptr<Var<Bias>> bias,
+                                          shared_ptr<Context> ctx);
+  CublasLinearOpF(size_t filters, ActVar x, shared_ptr<Var<Kernel>> kernel, shared_ptr<Var<Bias>> bias, shared_ptr<Context> ctx);
+  void _forward(TxnId txn) override;
+  void _backward(TxnId txn) override;
+  string _debug_op_label() override { return "CublasLinearOp"; }
+private:
+  ActVar x_;
+  shared_ptr<Var<Kernel>> kernel_;
+  shared_ptr<Var<Bias>> bias_;
+  size_t in_, out_;
+};
+
 // Bilinear x`scale` upsample of an H-strip (half-pixel centres, edges clamped).  The input is the strip
 // halo-padded by one row and exchanged, so that each strip produces exactly its rows of the
 // unpartitioned result; the gradient leaves the neighbours' shares in the halo rows, where the halo
@@ -547,6 +597,8 @@ template <typename S, typename V = Act, typename A = GPUArray1D<float>> using Cu
 template <typename V> using CudnnActivationOp = CudnnActivationOpF;
 template <typename V, typename J = SumJoin> using JoinOp = SumJoinOpF;
 template <typename V> using UpsampleBilinear2DOp = UpsampleBilinear2DOpF;
+template <typename V> using SpatialAllGather2DOp = SpatialAllGather2DOpF;
+template <typename V, typename K = GPUArray4D<float>, typename B = GPUArray1D<float>> using CublasLinearOp = CublasLinearOpF;
 template <typename V> using CudnnSoftmaxNLLLossOp = CudnnSoftmaxNLLLoss2DOpF;
 
 }  // namespace arraydiff

@@ -55,6 +55,11 @@ public:
   void halo_reduce(void* buf, uint32_t halo_pad, uint32_t base_width, uint32_t base_height, uint32_t num_channels,
                    uint32_t batch_size, Spatial2DTensorFormat tensor_format, Spatial2DDataType data_type);
 
+  // all-gather of strips between processes: flag word q of this rank's block says "rank q's strip of the
+  // gather_epoch-th gather (or gather gradient) may be read"
+  uint64_t* gather_flags() const { return gflags_; }
+  uint64_t gather_epoch = 0;
+
   uint32_t rank, rank_w, rank_h, num_ranks, num_w_ranks, num_h_ranks;
   uint64_t epoch;
   Spatial2DArg arg;
@@ -68,6 +73,7 @@ private:
   uint64_t* flags_;       // between processes: flag words in my arena: 0 from_prev, 1 from_next, 2 grad_prev,
                           // 3 grad_next, 4 next_ready, 5 prev_ready
   uint32_t* counter_;     // block ticket counter for the publishing kernel
+  uint64_t* gflags_ = nullptr;   // 8 words, see gather_flags()
   bool in_group_;
 };
 

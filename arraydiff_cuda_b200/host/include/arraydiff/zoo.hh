@@ -20,10 +20,15 @@ template <typename V> struct ParallelBatchNormParamOp {
 typedef IOOp<GPUArray4D<float>>::InitFn KernelInitFn;
 // normal(0, sqrt(2 / fan_in)), drawn on the host from the shared generator (reference src/op.cc:362-408)
 template <typename A> typename IOOp<A>::InitFn kaiming_init_gen(size_t fan_in, size_t fan_out);
+// uniform(+-sqrt(6 / (fan_in + fan_out)))   (reference src/op.cc:362-408)
+template <typename A> typename IOOp<A>::InitFn xavier_init_gen(size_t fan_in, size_t fan_out);
 template <typename A> typename IOOp<A>::InitFn zeros_init_gen();
 
 template <typename V> ParamOp<V> conv2d(Conv2DShape shape, shared_ptr<Var<V>> input, KernelInitFn kernel_init, bool enable_bias, shared_ptr<Context> ctx);
 template <typename V> ParallelParamOp<V> parallel_conv2d(Conv2DShape shape, vector<shared_ptr<Var<V>>> inputs, KernelInitFn kernel_init, bool enable_bias, shared_ptr<Context> ctx);
+// fully connected layer with bias on [batch][features] activations, one replica per rank (reference src/zoo.cc:62-90)
+template <typename V> ParamOp<V> linear(size_t filters, shared_ptr<Var<V>> input, KernelInitFn kernel_init, shared_ptr<Context> ctx);
+template <typename V> ParallelParamOp<V> parallel_linear(size_t filters, vector<shared_ptr<Var<V>>> inputs, KernelInitFn kernel_init, shared_ptr<Context> ctx);
 template <typename V> vector<shared_ptr<Var<V>>> parallel_relu(vector<shared_ptr<Var<V>>> inputs, shared_ptr<Context> ctx);
 template <typename V> vector<shared_ptr<Var<V>>> parallel_sum(vector<vector<shared_ptr<Var<V>>>> inputs, shared_ptr<Context> ctx);
 // batch norm per rank, optionally with the following ReLU folded in
@@ -69,6 +74,12 @@ public:
   // ResNet-50 stem + stage 1: 7x7/2 conv to 64 channels, BN, ReLU, 3x3/2 max pool, then three
   // pre-activation bottleneck blocks (64-64-256), the first with a 1x1 projection.
   static SpatialParallelNet MakeStemStage1(const ConvNetConfig& config, shared_ptr<Context> ctx);
+  // The reference's spatially parallel classifier (ResNet<float>::MakeParallelResNet18, src/zoo.cc:1475-1909): 7x7
+  // conv with bias at stride 1, 3x3/2 max pool, basic pre-activation residual blocks 64,64 / 128,128 / 256,256 /
+  // 512 / 512 (each first block of a width strided by 2 with a projection), BN + ReLU, re-assembly of the strips
+  // on every rank, global average pool, linear classifier, softmax NLL.  Every rank computes the (tiny) head
+  // on the whole batch; labels go to every net.losses[r]->load_labels.
+  static SpatialParallelNet MakeParallelResNet18(const ConvNetConfig& config, size_t classes, shared_ptr<Context> ctx);
   // Dilated ResNet-50 segmentation net at output stride 8 with a bilinear x8 head and per-pixel loss
   // (the 1024x2048, 19-class configuration); labels go to net.losses[r]->load_labels.
   static SpatialParallelNet MakeSegNet50(const ConvNetConfig& config, const SegNetConfig& seg, shared_ptr<Context> ctx);

@@ -63,6 +63,7 @@ void* adh_net_create(void* c, const char* kind, int H, int W, int C, int batch, 
   n->rng.seed(seed);
   if (!std::strcmp(kind, "conv3x3")) n->net = SpatialParallelResNet<float>::MakeConv3x3(n->cfg, (size_t)filters, n->ctx);
   else if (!std::strcmp(kind, "stem_stage1")) n->net = SpatialParallelResNet<float>::MakeStemStage1(n->cfg, n->ctx);
+  else if (!std::strcmp(kind, "parallel_resnet18")) n->net = SpatialParallelResNet<float>::MakeParallelResNet18(n->cfg, filters > 0 ? (size_t)filters : 1000, n->ctx);
   else if (!std::strncmp(kind, "segnet", 6)) {
     // "segnet50": ResNet-50 depth; "segnet_small": one block per stage; `filters` (if > 0) = stem width
     SegNetConfig seg;

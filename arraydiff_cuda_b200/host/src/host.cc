@@ -188,6 +188,8 @@ void Spatial2DComm::InitAll(Spatial2DComm* comms, uint32_t num_w_ranks, uint32_t
       CUDA_CHECK(cudaEventCreateWithFlags(&c.ready_, cudaEventDisableTiming));
       c.flags_ = (uint64_t*)g->arena().alloc(64);      // same offset on every rank: first allocation after the status word
       c.counter_ = (uint32_t*)g->arena().alloc(64);
+      c.gflags_ = (uint64_t*)g->arena().alloc(64);
+      CUDA_CHECK(cudaMemsetAsync(c.gflags_, 0, 64, conn.stream()));
       CUDA_CHECK(cudaMemsetAsync(c.flags_, 0, 64, conn.stream()));
       CUDA_CHECK(cudaMemsetAsync(c.counter_, 0, 64, conn.stream()));
       conn.sync();

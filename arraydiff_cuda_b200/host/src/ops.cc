@@ -58,19 +58,20 @@ size_t ActOp::_store_grad(TxnId, VarIdSet& vars, size_t offset, any* writer) {
 // Coordinates are relative to each array's PADDED origin.  NCHW fp32 goes through the slice kernel
 // as is; NHWC bf16 is the same kernel seen as one plane per image with rows of W*C elements.
 static void copy_window(const Act& src, size_t sx, size_t sy, const Act& dst, size_t dx, size_t dy, size_t w, size_t h,
-                        bool add, cudaStream_t s) {
+                        bool add, cudaStream_t s, const void* src_base = nullptr) {
   assert(src.storage() == dst.storage());
+  if (!src_base) src_base = src.base_dptr();   // else: the same geometry at another address (a peer's copy)
   const Shape3D sp = src.padded_dim(), dp = dst.padded_dim();
   const uint32_t C = (uint32_t)sp.shape[2], N = (uint32_t)src.batch_size();
   assert(dp.shape[2] == C && dst.batch_size() == N);
   auto fn = add ? ad_slice2d_add_hw_nchw_packed : ad_slice2d_copy_hw_nchw_packed;
   if (src.storage() == COMPUTE_F32_NCHW) {
     AD_CHECK(fn(AD_F32, (uint32_t)w, (uint32_t)h, (uint32_t)sp.shape[0], (uint32_t)sp.shape[1], (uint32_t)dp.shape[0],
-                (uint32_t)dp.shape[1], C, N, src.base_dptr(), (uint32_t)sx, (uint32_t)sy, dst.base_dptr(), (uint32_t)dx,
+                (uint32_t)dp.shape[1], C, N, src_base, (uint32_t)sx, (uint32_t)sy, dst.base_dptr(), (uint32_t)dx,
                 (uint32_t)dy, s));
   } else {
     AD_CHECK(fn(AD_BF16, (uint32_t)(w * C), (uint32_t)h, (uint32_t)(sp.shape[0] * C), (uint32_t)sp.shape[1],
-                (uint32_t)(dp.shape[0] * C), (uint32_t)dp.shape[1], 1, N, src.base_dptr(), (uint32_t)(sx * C), (uint32_t)sy,
+                (uint32_t)(dp.shape[0] * C), (uint32_t)dp.shape[1], 1, N, src_base, (uint32_t)(sx * C), (uint32_t)sy,
                 dst.base_dptr(), (uint32_t)(dx * C), (uint32_t)dy, s));
   }
 }
@@ -579,7 +580,7 @@ vector<ActVar> CudnnPool2DOpF::MakeParallel(Pool2DShape shape, vector<ActVar> in
 }
 CudnnPool2DOpF::CudnnPool2DOpF(Pool2DShape shape, ActVar x, shared_ptr<Context> ctx) : ActOp(x->rank(), ctx), shape_(shape), x_(x) {
   inputs_.push_back(x);
-  assert(shape.pooling == kMaxPool && "average pooling belongs to the classifier head, which is not built");
+  assert((shape.pooling == kMaxPool || !shape.halo_padded_input) && "average pooling takes an unpadded input");
   alloc_output(shape.calculate_output_shape(x->shape()), 0, 0, x->batch_shape());
 }
 void CudnnPool2DOpF::_forward(TxnId txn) {
@@ -589,6 +590,11 @@ void CudnnPool2DOpF::_forward(TxnId txn) {
   if (shape_.halo_padded_input) assert(x.offset().shape[0] == shape_.pad[0] && x.offset().shape[1] == shape_.pad[1]);   // reference src/op.cc:3427-3428
   ad_tensor4 xv = shape_.halo_padded_input ? x.view_base() : x.view_interior();
   ad_tensor4 yv = y_.val.get_excl(txn, id()).view_interior();
+  if (shape_.pooling == kAveragePool) {
+    AD_CHECK(ad_avgpool2d_fwd(&xv, &yv, (uint32_t)shape_.window[1], (uint32_t)shape_.window[0], (uint32_t)shape_.stride[1],
+                              (uint32_t)shape_.stride[0], conn.stream()));
+    return;
+  }
   AD_CHECK(ad_maxpool2d_fwd(&xv, &yv, (uint32_t)shape_.window[1], (uint32_t)shape_.window[0], (uint32_t)shape_.stride[1],
                             (uint32_t)shape_.stride[0], conn.stream()));
 }
@@ -602,6 +608,11 @@ void CudnnPool2DOpF::_backward(TxnId txn) {
   ad_tensor4 xv = shape_.halo_padded_input ? x.view_base() : x.view_interior();
   ad_tensor4 dxv = shape_.halo_padded_input ? dx.view_base() : dx.view_interior();
   ad_tensor4 dyv = y_.grad.get(txn, id()).view_interior();
+  if (shape_.pooling == kAveragePool) {
+    AD_CHECK(ad_avgpool2d_bwd(&dyv, &dxv, (uint32_t)shape_.window[1], (uint32_t)shape_.window[0], (uint32_t)shape_.stride[1],
+                              (uint32_t)shape_.stride[0], mode == 1 ? 1 : 0, conn.stream()));
+    return;
+  }
   AD_CHECK(ad_maxpool2d_bwd(&xv, &dyv, &dxv, (uint32_t)shape_.window[1], (uint32_t)shape_.window[0], (uint32_t)shape_.stride[1],
                             (uint32_t)shape_.stride[0], mode == 1 ? 1 : 0, conn.stream()));
 }
@@ -730,6 +741,161 @@ void SumJoinOpF::_backward(TxnId txn) {
     ad_tensor4 dxv = xd.grad.get_mut(txn, id()).view_interior();
     AD_CHECK(ad_convert(&dyv, &dxv, mode == 1 ? 1 : 0, conn.stream()));
   }
+}
+
+// ------------------------------------------------------------------ all-gather of strips / reduce-scatter of gradients
+AllGatherOutF::AllGatherOutF(shared_ptr<SpatialAllGather2DOpF> shared, ActVar strip, size_t num_ranks, shared_ptr<Context> ctx)
+    : ActOp(strip->rank(), ctx) {
+  inputs_.push_back(shared);
+  Shape3D d = strip->shape();
+  alloc_output(Shape3D(d.shape[0], d.shape[1] * num_ranks, d.shape[2]), 0, 0, strip->batch_shape());
+}
+vector<ActVar> SpatialAllGather2DOpF::MakeParallel(vector<ActVar> inputs, shared_ptr<Context> ctx) {
+  auto shared = make_shared<SpatialAllGather2DOpF>(inputs, ctx);
+  vector<ActVar> out;
+  for (auto& x : inputs) {
+    auto o = make_shared<AllGatherOutF>(shared, x, shared->num_ranks_, ctx);
+    shared->outs_.push_back(o.get());
+    out.push_back(o);
+  }
+  return out;
+}
+SpatialAllGather2DOpF::SpatialAllGather2DOpF(vector<ActVar> inputs, shared_ptr<Context> ctx)
+    : xs_(inputs), ctx_(ctx), num_ranks_(num_ranks_of(ctx, inputs.size())) {
+  for (auto& x : inputs) inputs_.push_back(x);
+}
+// Between processes: tell every peer that my strip (or my gradient) of this round may be read, then wait
+// (bounded) for theirs.  Every rank calls the gathers in the same order, so the round number agrees.
+void SpatialAllGather2DOpF::wait_peers(size_t rank, cudaStream_t s) {
+  auto* m = dynamic_cast<MultiGPUContext*>(ctx_.get());
+  Spatial2DComm* comm = m->spatial_comm(rank);
+  const uint64_t ep = ++comm->gather_epoch;
+  GPUContext* g = m->device_context(rank).get();
+  for (size_t q = 0; q < num_ranks_; ++q)
+    if (q != rank) AD_CHECK(ad_flag_signal((uint64_t*)m->peer_ptr(comm->gather_flags() + rank, rank, q), ep, s));
+  for (size_t q = 0; q < num_ranks_; ++q)
+    if (q != rank) AD_CHECK(ad_flag_wait(comm->gather_flags() + q, ep, 2000000000ull, g->status_word(), s));
+}
+// stream `to` waits for everything issued so far on stream `from`
+static void order_after(cudaStream_t to, cudaStream_t from) {
+  cudaEvent_t e;
+  CUDA_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  CUDA_CHECK(cudaEventRecord(e, from));
+  CUDA_CHECK(cudaStreamWaitEvent(to, e, 0));
+  CUDA_CHECK(cudaEventDestroy(e));
+}
+void SpatialAllGather2DOpF::_forward(TxnId txn) {
+  if (done_fwd_ && *done_fwd_ == txn.raw_id()) return;
+  done_fwd_ = txn.raw_id();
+  auto* m = dynamic_cast<MultiGPUContext*>(ctx_.get());
+  assert(m);
+  for (size_t i = 0; i < xs_.size(); ++i) {
+    const size_t r = xs_[i]->rank();
+    if (!m->is_local(r)) continue;
+    auto yd = outs_[i]->data();
+    if (!yd.val.overwrite(txn, id())) continue;
+    GPUContext* g = m->device_context(r).get();
+    GPUConn conn = g->conn();
+    Act& x = xs_[i]->data().val.get(txn, id());
+    Act& y = yd.val.get_excl(txn, id());
+    const size_t w = x.dim().shape[0], h = x.dim().shape[1], ox = x.offset().shape[0], oy = x.offset().shape[1];
+    copy_window(x, ox, oy, y, 0, r * h, w, h, false, conn.stream());
+    if (num_ranks_ == 1) continue;
+    if (m->distributed()) {
+      wait_peers(r, conn.stream());
+      for (size_t q = 0; q < num_ranks_; ++q)
+        if (q != r) copy_window(x, ox, oy, y, 0, q * h, w, h, false, conn.stream(), m->peer_ptr(x.base_dptr(), r, q));
+      continue;
+    }
+    for (size_t j = 0; j < xs_.size(); ++j) {
+      const size_t q = xs_[j]->rank();
+      if (q == r) continue;
+      // what has been issued on rank q's stream so far includes the producer of its strip
+      order_after(conn.stream(), m->device_context(q)->stream());
+      Act& xs = xs_[j]->data().val.get(txn, id());
+      copy_window(xs, xs.offset().shape[0], xs.offset().shape[1], y, 0, q * h, w, h, false, conn.stream());
+    }
+  }
+}
+void SpatialAllGather2DOpF::_backward(TxnId txn) {
+  if (done_bwd_ && *done_bwd_ == txn.raw_id()) return;
+  done_bwd_ = txn.raw_id();
+  auto* m = dynamic_cast<MultiGPUContext*>(ctx_.get());
+  for (size_t i = 0; i < xs_.size(); ++i) {
+    const size_t r = xs_[i]->rank();
+    if (!m->is_local(r)) continue;
+    GPUContext* g = m->device_context(r).get();
+    auto xd = xs_[i]->data();
+    const int mode = xd.grad.accumulate_full(txn, id(), unpadded, zero_init(g));
+    if (!mode) continue;
+    GPUConn conn = g->conn();
+    Act& dx = xd.grad.get_mut(txn, id());
+    Act& dy = outs_[i]->data().grad.get(txn, id());
+    const size_t w = dx.dim().shape[0], h = dx.dim().shape[1], ox = dx.offset().shape[0], oy = dx.offset().shape[1];
+    // peers in rank order, the own share in its place: the sum does not depend on which rank computes it
+    bool first = mode != 1;
+    auto add_from = [&](const Act& src, const void* base) {
+      copy_window(src, 0, r * h, dx, ox, oy, w, h, !first, conn.stream(), base);
+      first = false;
+    };
+    if (num_ranks_ > 1 && m->distributed()) wait_peers(r, conn.stream());
+    for (size_t q = 0; q < num_ranks_; ++q) {
+      if (q == r) { add_from(dy, nullptr); continue; }
+      if (m->distributed()) { add_from(dy, m->peer_ptr(dy.base_dptr(), r, q)); continue; }
+      for (size_t j = 0; j < xs_.size(); ++j) {
+        if (xs_[j]->rank() != q) continue;
+        order_after(conn.stream(), m->device_context(q)->stream());
+        add_from(outs_[j]->data().grad.get(txn, id()), nullptr);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ fully connected
+shared_ptr<CublasLinearOpF> CublasLinearOpF::Make(size_t filters, ActVar x, shared_ptr<Var<Kernel>> kernel, shared_ptr<Var<Bias>> bias,
+                                                  shared_ptr<Context> ctx) {
+  return make_shared<CublasLinearOpF>(filters, x, kernel, bias, ctx);
+}
+CublasLinearOpF::CublasLinearOpF(size_t filters, ActVar x, shared_ptr<Var<Kernel>> kernel, shared_ptr<Var<Bias>> bias, shared_ptr<Context> ctx)
+    : ActOp(x->rank(), ctx), x_(x), kernel_(kernel), bias_(bias), out_(filters) {
+  inputs_.push_back(x);
+  inputs_.push_back(kernel);
+  if (bias) inputs_.push_back(bias);
+  Shape3D d = x->shape();
+  assert(d.shape[0] == 1 && d.shape[1] == 1 && "the linear layer takes [batch][features] (flatten after a global pool)");
+  in_ = d.shape[2];
+  alloc_output(Shape3D(1, 1, filters), 0, 0, x->batch_shape());
+}
+void CublasLinearOpF::_forward(TxnId txn) {
+  if (!y_.val.overwrite(txn, id())) return;
+  GPUConn conn = gpu()->conn();
+  Act& x = x_->data().val.get(txn, id());
+  Act& y = y_.val.get_excl(txn, id());
+  assert(x.offset().shape[0] == 0 && x.offset().shape[1] == 0);
+  const int dt = x.storage() == COMPUTE_F32_NCHW ? AD_F32 : AD_BF16;
+  AD_CHECK(ad_linear_fwd(dt, (uint32_t)x.batch_size(), (uint32_t)in_, (uint32_t)out_, x.base_dptr(),
+                         kernel_->data().val.get(txn, id()).dptr(), bias_ ? bias_->data().val.get(txn, id()).dptr() : nullptr,
+                         y.base_dptr(), conn.stream()));
+}
+void CublasLinearOpF::_backward(TxnId txn) {
+  GPUContext* g = gpu();
+  GPUConn conn = g->conn();
+  Act& x = x_->data().val.get(txn, id());
+  Act& dy = y_.grad.get(txn, id());
+  const int dt = x.storage() == COMPUTE_F32_NCHW ? AD_F32 : AD_BF16;
+  auto kd = kernel_->data();
+  float* dw = nullptr;
+  float* db = nullptr;
+  auto zero_k = [g](Kernel* a) { GPUConn c = g->conn(); AD_CHECK(ad_fill_zero(a->dptr(), a->flat_size() * 4, c.stream())); };
+  auto zero_b = [g](Bias* a) { GPUConn c = g->conn(); AD_CHECK(ad_fill_zero(a->dptr(), a->flat_size() * 4, c.stream())); };
+  if (kd.grad.accumulate(txn, id(), zero_k)) dw = kd.grad.get_mut(txn, id()).dptr();
+  if (bias_ && dw) { auto bd = bias_->data(); bd.grad.accumulate(txn, id(), zero_b); db = bd.grad.get_mut(txn, id()).dptr(); }
+  auto xd = x_->data();
+  const int mode = xd.grad.accumulate_full(txn, id(), unpadded, zero_init(g));
+  void* dxp = mode ? xd.grad.get_mut(txn, id()).base_dptr() : nullptr;
+  if (!dw && !dxp) return;
+  AD_CHECK(ad_linear_bwd(dt, (uint32_t)x.batch_size(), (uint32_t)in_, (uint32_t)out_, x.base_dptr(), kd.val.get(txn, id()).dptr(),
+                         dy.base_dptr(), dxp, dw, db, mode == 1 ? 1 : 0, 1, conn.stream()));
 }
 
 // ------------------------------------------------------------------ bilinear upsample of a strip

@@ -32,6 +32,18 @@ typename IOOp<A>::InitFn kaiming_init_gen(size_t fan_in, size_t) {
   };
 }
 template <typename A>
+typename IOOp<A>::InitFn xavier_init_gen(size_t fan_in, size_t fan_out) {
+  return [fan_in, fan_out](A* a, std::mt19937_64* rng, shared_ptr<Context>) {
+    const float half = std::sqrt(6.0f / (float)(fan_in + fan_out));
+    std::uniform_real_distribution<float> dist(-half, half);
+    vector<float> h(a->flat_size());
+    for (auto& v : h) v = dist(*rng);
+    CUDA_CHECK(cudaDeviceSynchronize());
+    CUDA_CHECK(cudaMemcpy(a->dptr(), h.data(), h.size() * 4, cudaMemcpyHostToDevice));
+    CUDA_CHECK(cudaDeviceSynchronize());
+  };
+}
+template <typename A>
 typename IOOp<A>::InitFn zeros_init_gen() {
   return [](A* a, std::mt19937_64*, shared_ptr<Context>) {
     CUDA_CHECK(cudaDeviceSynchronize());
@@ -41,6 +53,7 @@ typename IOOp<A>::InitFn zeros_init_gen() {
 }
 template IOOp<GPUArray4D<float>>::InitFn kaiming_init_gen<GPUArray4D<float>>(size_t, size_t);
 template IOOp<GPUArray1D<float>>::InitFn zeros_init_gen<GPUArray1D<float>>();
+template IOOp<GPUArray4D<float>>::InitFn xavier_init_gen<GPUArray4D<float>>(size_t, size_t);
 
 template <>
 ParamOp<Act> conv2d(Conv2DShape shape, ActVar input, KernelInitFn kernel_init, bool enable_bias, shared_ptr<Context> ctx) {
@@ -66,6 +79,33 @@ ParallelParamOp<Act> parallel_conv2d(Conv2DShape shape, vector<ActVar> inputs, K
   ParallelParamOp<Act> out;
   for (auto& x : inputs) {   // one op per rank, each with its own parameter variable (reference src/zoo.cc:140-153)
     auto p = conv2d<Act>(shape, x, kernel_init, enable_bias, ctx);
+    out.ops.push_back(p.op);
+    out.params.push_back(p.params);
+    out.grads.push_back(p.grads);
+  }
+  return out;
+}
+
+template <>
+ParamOp<Act> linear(size_t filters, ActVar input, KernelInitFn kernel_init, shared_ptr<Context> ctx) {
+  const size_t r = input->rank();
+  const size_t in = input->shape().shape[2];
+  // Shape4D(1, 1, in, out): [out][in] in memory, the reference's Shape2D(in, out)
+  auto kernel = IOOp<GPUArray4D<float>>::Make(Shape4D(1, 1, in, filters), 1, kernel_init, r, ctx);
+  auto bias = IOOp<GPUArray1D<float>>::Make(Shape1D(filters), 1, zeros_init_gen<GPUArray1D<float>>(), r, ctx);
+  kernel->set_name(NameScope::current() + ".kernel");
+  bias->set_name(NameScope::current() + ".bias");
+  ParamOp<Act> p;
+  p.op = CublasLinearOpF::Make(filters, input, kernel, bias, ctx);
+  p.params.insert(kernel->data().val.var()); p.params.insert(bias->data().val.var());
+  p.grads.insert(kernel->data().grad.var()); p.grads.insert(bias->data().grad.var());
+  return p;
+}
+template <>
+ParallelParamOp<Act> parallel_linear(size_t filters, vector<ActVar> inputs, KernelInitFn kernel_init, shared_ptr<Context> ctx) {
+  ParallelParamOp<Act> out;
+  for (auto& x : inputs) {
+    auto p = linear<Act>(filters, x, kernel_init, ctx);
     out.ops.push_back(p.op);
     out.params.push_back(p.params);
     out.grads.push_back(p.grads);
@@ -344,6 +384,62 @@ SpatialParallelNet SpatialParallelResNet<float>::MakeSegNet50(const ConvNetConfi
   vector<shared_ptr<Op>> members(net.losses.begin(), net.losses.end());
   net.sink = make_shared<GroupSinkOp>(members);
   for (auto& o : up) net.output_grad_vars[o->rank()].insert(o->data().grad.var());
+  return net;
+}
+
+template <>
+SpatialParallelNet SpatialParallelResNet<float>::MakeParallelResNet18(const ConvNetConfig& cfg, size_t classes, shared_ptr<Context> ctx) {
+  vector<ActVar> strips;
+  SpatialParallelNet net = begin_net(cfg, ctx, strips);
+  auto sw = net.batch_norm_use_fixed;
+  const size_t R = ranks_of(ctx);
+  // conv1: 7x7, stride 1, bias, Xavier (reference src/zoo.cc:1527-1556); no BN / ReLU before the pool
+  Conv2DShape c1;
+  c1.filters = 64; c1.kernel = {7, 7}; c1.pad = {3, 3}; c1.halo_padded_input = true;
+  auto pad1 = HaloPad2DOpF::MakeParallel(3, strips, ctx);
+  auto exch1 = HaloExch2DOpF::MakeParallel(3, pad1, ctx);
+  ParallelParamOp<Act> conv1;
+  { NameScope scope("conv1"); conv1 = parallel_conv2d<Act>(c1, exch1, xavier_init_gen<GPUArray4D<float>>(cfg.input_c * 49, 64), true, ctx); }
+  absorb(net, conv1.ops, conv1.params, conv1.grads);
+  Pool2DShape pool;
+  pool.window = {3, 3}; pool.stride = {2, 2}; pool.pad = {1, 1}; pool.halo_padded_input = true;
+  auto pad2 = HaloPad2DOpF::MakeParallel(1, conv1.ops, ctx);
+  auto exch2 = HaloExch2DOpF::MakeParallel(1, pad2, ctx);
+  vector<ActVar> cur = CudnnPool2DOpF::MakeParallel(pool, exch2, ctx);
+  // res2_1, res2_2 (64) | res3_1 (128, /2), res3_2 | res4_1 (256, /2), res4_2 | res5_1 (512, /2) | res6_1 (512, /2)
+  struct Blk { const char* name; size_t filters; bool proj; };
+  const Blk blocks[] = {{"res2_1", 64, false}, {"res2_2", 64, false}, {"res3_1", 128, true}, {"res3_2", 128, false},
+                        {"res4_1", 256, true}, {"res4_2", 256, false}, {"res5_1", 512, true}, {"res6_1", 512, true}};
+  for (const Blk& b : blocks) {
+    Conv2DShape s;
+    s.filters = b.filters; s.kernel = {3, 3}; s.pad = {1, 1};
+    NameScope scope(b.name);
+    ParallelBatchNormParamOp<Act> blk = b.proj ? spatial_parallel_proj_residual_v2_conv2d<Act>(s, 2, sw, cur, ctx)
+                                               : spatial_parallel_residual_v2_conv2d<Act>(s, sw, cur, ctx);
+    absorb(net, blk.ops, blk.params, blk.grads, &blk.batch_stats, &blk.fixed_stats);
+    cur = blk.ops;
+  }
+  ParallelBatchNormParamOp<Act> bnf;
+  { NameScope scope("bn_final"); bnf = parallel_batch_norm<Act>(512, sw, cur, true, ctx); }
+  absorb(net, bnf.ops, bnf.params, bnf.grads, &bnf.batch_stats, &bnf.fixed_stats);
+  // strips -> the whole feature map on every rank, global average pool, classifier
+  auto full = SpatialAllGather2DOpF::MakeParallel(bnf.ops, ctx);
+  Pool2DShape gp;
+  gp.pooling = kAveragePool;
+  gp.window = {full.at(0)->shape().shape[0], full.at(0)->shape().shape[1]};
+  gp.stride = gp.window;
+  auto pooled = CudnnPool2DOpF::MakeParallel(gp, full, ctx);
+  ParallelParamOp<Act> fc;
+  { NameScope scope("fc1"); fc = parallel_linear<Act>(classes, pooled, xavier_init_gen<GPUArray4D<float>>(512, classes), ctx); }
+  absorb(net, fc.ops, fc.params, fc.grads);
+  net.losses = CudnnSoftmaxNLLLoss2DOpF::MakeParallel(fc.ops, ctx);
+  // every rank holds the whole batch: the mean loss, shared out over the R replicas of the head so that the
+  // sum over ranks (reduce-scatter of the feature gradient, allreduce of the parameter gradients) is the gradient
+  for (auto& l : net.losses) l->set_loss_weight(1.0f / (float)(cfg.batch_size * R));
+  net.outputs = fc.ops;
+  vector<shared_ptr<Op>> members(net.losses.begin(), net.losses.end());
+  net.sink = make_shared<GroupSinkOp>(members);
+  for (auto& o : fc.ops) net.output_grad_vars[o->rank()].insert(o->data().grad.var());
   return net;
 }
 

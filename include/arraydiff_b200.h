@@ -261,6 +261,29 @@ int ad_maxpool2d_bwd(const ad_tensor4* x, const ad_tensor4* dy, const ad_tensor4
                      uint32_t kw, uint32_t sh, uint32_t sw, int32_t accumulate, void* stream);
 
 /*
+ * Average pooling (window kh x kw, stride sh x sw, no implicit pad; a window the size of the input is the
+ * global pool of the classifier head).  Replaces CudnnPool2DOp with kAveragePool
+ * (cudnnPoolingForward / Backward, src/op.cc:3496-3513, :3610-3631; src/zoo.cc:1843-1852).
+ * y dims must be ((H-kh)/sh+1, (W-kw)/sw+1); bwd: dx (+)= mean-weights^T dy, a gather in a fixed order.
+ */
+int ad_avgpool2d_fwd(const ad_tensor4* x, const ad_tensor4* y, uint32_t kh, uint32_t kw, uint32_t sh,
+                     uint32_t sw, void* stream);
+int ad_avgpool2d_bwd(const ad_tensor4* dy, const ad_tensor4* dx, uint32_t kh, uint32_t kw, uint32_t sh,
+                     uint32_t sw, int32_t accumulate, void* stream);
+/*
+ * Fully connected layer on [batch][features] rows: y = x w^T + bias with w [out][in] fp32 (in fastest: the
+ * reference's Shape2D(in, out), minor axis first) and x / y / dy / dx of `dtype` (fp32 or bf16).
+ * Replaces CublasLinearOp (cublasSgemm + bias add, src/op.cc:1199-1340).
+ *   bwd: dx (+)= dy w (skipped if dx is NULL); dw (+)= dy^T x, db (+)= sum_b dy (skipped if dw is NULL).
+ * Batch sums run in index order: reproducible.
+ */
+int ad_linear_fwd(int32_t dtype, uint32_t batch, uint32_t in_features, uint32_t out_features, const void* x,
+                  const float* w, const float* bias, void* y, void* stream);
+int ad_linear_bwd(int32_t dtype, uint32_t batch, uint32_t in_features, uint32_t out_features, const void* x,
+                  const float* w, const void* dy, void* dx, float* dw, float* db, int32_t accumulate_dx,
+                  int32_t accumulate_dw, void* stream);
+
+/*
  * Bilinear x`scale` upsample (half-pixel centres, edges clamped: the align_corners = false rule) of a
  * strip, and its gradient.  No counterpart in the reference, whose segmentation head was never written;
  * this is the step between the 1/8-resolution logits and the per-pixel loss

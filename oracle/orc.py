@@ -261,6 +261,42 @@ def upsample_bilinear_bwd(dy, scale, dx=None):
     return dx
 
 
+def avgpool2d_fwd(x, k, s):
+    """Mean over kh x kw windows, no implicit pad (cudnnPoolingForward, AVERAGE; reference src/op.cc:3496-3513)."""
+    x = np.asarray(x, np.float64)
+    N, Cc, H, W = x.shape
+    P, Q = (H - k[0]) // s[0] + 1, (W - k[1]) // s[1] + 1
+    y = np.zeros((N, Cc, P, Q), np.float64)
+    for a in range(k[0]):
+        for b in range(k[1]):
+            y += x[:, :, a:a + (P - 1) * s[0] + 1:s[0], b:b + (Q - 1) * s[1] + 1:s[1]]
+    return (y / (k[0] * k[1])).astype(np.float32)
+
+
+def avgpool2d_bwd(dy, x_shape, k, s):
+    dy = np.asarray(dy, np.float64)
+    N, Cc, P, Q = dy.shape
+    dx = np.zeros(x_shape, np.float64)
+    for a in range(k[0]):
+        for b in range(k[1]):
+            dx[:, :, a:a + (P - 1) * s[0] + 1:s[0], b:b + (Q - 1) * s[1] + 1:s[1]] += dy
+    return (dx / (k[0] * k[1])).astype(np.float32)
+
+
+def linear_fwd(x, w, bias=None):
+    """y = x w^T + bias, w [out][in] (cublasSgemm + bias add, reference src/op.cc:1199-1247)."""
+    y = np.asarray(x, np.float64) @ np.asarray(w, np.float64).T
+    if bias is not None:
+        y = y + np.asarray(bias, np.float64)
+    return y.astype(np.float32)
+
+
+def linear_bwd(x, w, dy):
+    """(dx, dw, db) of linear_fwd (reference src/op.cc:1249-1340)."""
+    x, w, dy = np.asarray(x, np.float64), np.asarray(w, np.float64), np.asarray(dy, np.float64)
+    return (dy @ w).astype(np.float32), (dy.T @ x).astype(np.float32), dy.sum(axis=0).astype(np.float32)
+
+
 def sgd_step(theta, g, m, l2, mu, alpha, alpha_next, nesterov):
     f = C.c_float
     _load().orc_sgd_step(C.c_size_t(theta.size), _p(theta), _p(g), _p(m), f(l2), f(mu), f(alpha), f(alpha_next),

@@ -217,3 +217,88 @@ class SegNet:
         d = bn_b("stem.bn", np.ascontiguousarray(dpool))
         conv_b("stem.conv", d, need_dx=False)
         return G
+
+
+class ParallelResNet18:
+    """The reference's spatially parallel classifier (src/zoo.cc:1475-1909): 7x7 conv (bias, stride 1) -> 3x3/2 max
+    pool (zero pad) -> basic pre-activation blocks 64,64 | 128 (/2),128 | 256 (/2),256 | 512 (/2) | 512 (/2) ->
+    BN+ReLU -> global average pool -> linear -> softmax NLL, mean over the batch."""
+    BLOCKS = (("res2_1", False), ("res2_2", False), ("res3_1", True), ("res3_2", False), ("res4_1", True),
+              ("res4_2", False), ("res5_1", True), ("res6_1", True))
+
+    def __init__(self, P, R, bf16=False):
+        self.P, self.R = P, R
+        self.q = orc.round_bf16 if bf16 else _ident
+
+    def _bn(self, name):
+        return BnRelu(self.P[name + ".scale"], self.P[name + ".shift"], self.R, self.q)
+
+    def _conv(self, name, stride=1, pad=0):
+        return Conv(self.P[name + ".kernel"], stride, pad, self.q, 1, self.P.get(name + ".bias"))
+
+    def forward(self, x, labels):
+        L = self.L = {}
+        L["conv1"] = self._conv("conv1", 1, 3)
+        a = L["conv1"].fwd(x)
+        self.pool_in = np.zeros((a.shape[0], a.shape[1], a.shape[2] + 2, a.shape[3] + 2), np.float32)
+        self.pool_in[:, :, 1:-1, 1:-1] = a
+        t = orc.maxpool2d_fwd(self.pool_in, (3, 3), (2, 2), omp=True)
+        for b, proj in self.BLOCKS:
+            stride = 2 if proj else 1
+            L[b + ".bn0"] = self._bn(b + ".bn0")
+            a0 = L[b + ".bn0"].fwd(t)
+            L[b + ".conv1"] = self._conv(b + ".conv1", stride, 1)
+            L[b + ".bn1"] = self._bn(b + ".bn1")
+            a1 = L[b + ".bn1"].fwd(L[b + ".conv1"].fwd(a0))
+            L[b + ".conv2"] = self._conv(b + ".conv2", 1, 1)
+            c2 = L[b + ".conv2"].fwd(a1)
+            if proj:
+                L[b + ".proj"] = self._conv(b + ".proj", stride)
+                t = self.q(L[b + ".proj"].fwd(a0) + c2)
+            else:
+                t = self.q(t + c2)
+        L["bn_final"] = self._bn("bn_final")
+        self.feat = L["bn_final"].fwd(t)
+        k = self.feat.shape[2:]
+        self.pooled = self.q(orc.avgpool2d_fwd(self.feat, k, k))
+        N = x.shape[0]
+        self.w, self.b = self.P["fc1.kernel"].reshape(-1, self.pooled.shape[1]), self.P["fc1.bias"]
+        self.logits = self.q(orc.linear_fwd(self.pooled.reshape(N, -1), self.w, self.b))
+        self.labels = np.ascontiguousarray(labels.reshape(N, 1), np.uint32)
+        loss, _, _ = orc.softmax_ce_pixel_fwd(self.logits.reshape(N, -1, 1), self.labels, omp=True)
+        return self.logits, float(loss.astype(np.float64).mean())
+
+    def backward(self):
+        L, G = self.L, {}
+
+        def bn_b(name, g):
+            dx, dg, db = L[name].bwd(g)
+            G[name + ".scale"], G[name + ".shift"] = dg, db
+            return dx
+
+        def conv_b(name, g, need_dx=True):
+            dx, dw = L[name].bwd(g, need_dx)
+            G[name + ".kernel"] = dw
+            if L[name].b is not None:
+                G[name + ".bias"] = L[name].db
+            return dx
+
+        N, K = self.logits.shape
+        dloss = np.full((N, 1), 1.0 / N, np.float32)
+        self.dlogits = self.q(orc.softmax_ce_pixel_bwd(self.logits.reshape(N, K, 1), self.labels, dloss, omp=True).reshape(N, K))
+        dpooled, G["fc1.kernel"], G["fc1.bias"] = orc.linear_bwd(self.pooled.reshape(N, -1), self.w, self.dlogits)
+        k = self.feat.shape[2:]
+        g = self.q(orc.avgpool2d_bwd(self.q(dpooled).reshape(self.pooled.shape), self.feat.shape, k, k))
+        g = bn_b("bn_final", g)
+        for b, proj in reversed(self.BLOCKS):
+            d = conv_b(b + ".conv2", g)
+            d = bn_b(b + ".bn1", d)
+            d = conv_b(b + ".conv1", d)
+            if proj:
+                d = self.q(d + conv_b(b + ".proj", g))
+                g = bn_b(b + ".bn0", d)
+            else:
+                g = self.q(g + bn_b(b + ".bn0", d))
+        dpool = np.ascontiguousarray(orc.maxpool2d_bwd(self.pool_in, g, (3, 3), (2, 2), omp=True)[:, :, 1:-1, 1:-1])
+        conv_b("conv1", self.q(dpool), need_dx=False)
+        return G

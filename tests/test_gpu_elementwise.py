@@ -340,3 +340,57 @@ def test_upsample_bilinear_strips_equal_unpartitioned(layout, dtype, R, scale):
     tx, vx = _views(np.zeros((N, Cc, Hh - 1, W), np.float32), layout, dtype)
     ty, vy = _views(np.zeros((N, Cc, Hh * scale, W * scale), np.float32), layout, dtype)
     assert L.ad_upsample_bilinear_fwd(C.byref(vx), C.byref(vy), scale, 0, Hh, 0, H.stream()) == abi.AD_ERR_BAD_ARG
+
+
+@pytest.mark.parametrize("layout", [abi.AD_NCHW, abi.AD_NHWC])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("k,s", [((8, 8), (8, 8)), ((2, 3), (2, 1))])
+def test_average_pool(layout, dtype, k, s):
+    """Global (window = input) and windowed mean pooling against the numpy restatement."""
+    N, Cc, Hh, W = 2, 12, 8, 8
+    x = H.normal(60, (N, Cc, Hh, W))
+    if dtype == "bf16":
+        x = orc.round_bf16(x)
+    y_w = orc.avgpool2d_fwd(x, k, s)
+    dy = H.uniform(61, y_w.shape)
+    if dtype == "bf16":
+        dy = orc.round_bf16(dy)
+    dx_w = orc.avgpool2d_bwd(dy, x.shape, k, s)
+    tx, vx = _views(x, layout, dtype)
+    ty, vy = _views(np.zeros_like(y_w), layout, dtype)
+    tdy, vdy = _views(dy, layout, dtype)
+    tdx, vdx = _views(np.ones_like(x), layout, dtype)
+    L = abi.lib()
+    abi.check(L.ad_avgpool2d_fwd(C.byref(vx), C.byref(vy), k[0], k[1], s[0], s[1], H.stream()))
+    abi.check(L.ad_avgpool2d_bwd(C.byref(vdy), C.byref(vdx), k[0], k[1], s[0], s[1], 1, H.stream()))
+    H.sync()
+    tol = 1e-6 if dtype == "f32" else 8e-3
+    assert H.max_rel(_back(ty, layout, 0, *y_w.shape[2:]), y_w) < tol
+    assert H.max_rel(_back(tdx, layout, 0, Hh, W), dx_w + 1.0) < tol
+    assert L.ad_avgpool2d_fwd(C.byref(vx), C.byref(vdx), k[0], k[1], s[0], s[1], H.stream()) == abi.AD_ERR_BAD_ARG
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("B,I,O", [(4, 512, 1000), (3, 70, 19)])
+def test_linear_layer(dtype, B, I, O):
+    """y = x w^T + b and its three gradients against the numpy restatement."""
+    x, w, b = H.normal(70, (B, I)), H.normal(71, (O, I), 0.05), H.normal(72, (O,))
+    dy = H.uniform(73, (B, O))
+    if dtype == "bf16":
+        x, dy = orc.round_bf16(x), orc.round_bf16(dy)
+    y_w = orc.linear_fwd(x, w, b)
+    dx_w, dw_w, db_w = orc.linear_bwd(x, w, dy)
+    mk = H.dev if dtype == "f32" else H.dev_bf16
+    tx, tdy = mk(x), mk(dy)
+    ty, tdx = mk(np.zeros_like(y_w)), mk(np.full_like(x, 2.0))
+    tw, tb = H.dev(w), H.dev(b)
+    tdw, tdb = H.dev(np.zeros_like(w)), H.dev(np.zeros_like(b))
+    L = abi.lib()
+    dt = abi.AD_F32 if dtype == "f32" else abi.AD_BF16
+    abi.check(L.ad_linear_fwd(dt, B, I, O, H.ptr(tx), H.ptr(tw), H.ptr(tb), H.ptr(ty), H.stream()))
+    abi.check(L.ad_linear_bwd(dt, B, I, O, H.ptr(tx), H.ptr(tw), H.ptr(tdy), H.ptr(tdx), H.ptr(tdw), H.ptr(tdb), 1, 0, H.stream()))
+    H.sync()
+    tol = 2e-6 if dtype == "f32" else 8e-3
+    assert H.max_rel(H.host(ty), y_w) < tol
+    assert H.max_rel(H.host(tdx), dx_w + 2.0) < tol
+    assert H.max_rel(H.host(tdw), dw_w) < 2e-6 and H.max_rel(H.host(tdb), db_w) < 2e-6
