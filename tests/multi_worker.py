@@ -70,7 +70,7 @@ _keep = []
 
 def host_part(rank, world, local):
     Lh = hostlib.load()
-    ctxh = Lh.adh_context_create_distributed(rank, world, local, hostlib.F32_NCHW, 256)
+    ctxh = Lh.adh_context_create_distributed(rank, world, local, hostlib.F32_NCHW, 1536)
     # exchange arena handles
     hb = C.create_string_buffer(64)
     assert Lh.adh_context_arena_handle(ctxh, hb) == 0
@@ -120,6 +120,55 @@ def host_part(rank, world, local):
     theta, g, m = w.reshape(-1).copy(), dw_w.reshape(-1).copy(), np.zeros(w.size, np.float32)
     orc.sgd_step(theta, g, m, 0.0, 0.9, 0.1, 0.1, 0)
     assert H.max_rel(net.params(rank), theta) < 1e-5, "update after allreduce mismatch"
+    dist.barrier()
+    classifier_part(ctx, rank, world)
+
+
+def classifier_part(ctx, rank, world):
+    """The spatially parallel classifier between processes: strips all-gathered with peer loads ordered by flag
+    words, the head replicated per rank, the feature gradient reduce-scattered the same way."""
+    from tests.oracle_nets import ParallelResNet18
+    N, Cc, Hh, W, classes = 2, 3, 64 * world, 64, 10
+    net = hostlib.Net(ctx, "parallel_resnet18", Hh, W, Cc, N, filters=classes, seed=23)
+    man = net.manifest()
+    flat = net.params(rank)
+    rng = np.random.default_rng(9)
+    for name, (off, size) in man.items():      # wide-margin BN affine: every ReLU passes everything
+        if name.endswith(".scale"):
+            flat[off:off + size] = rng.uniform(0.05, 0.15, size)
+        if name.endswith(".shift"):
+            flat[off:off + size] = rng.uniform(1.0, 1.4, size)
+        if name.endswith(".bias"):
+            flat[off:off + size] = rng.uniform(-0.5, 0.5, size)
+    net.set_params(flat)
+    shapes = {"conv1.kernel": (64, 3, 7, 7), "fc1.kernel": (classes, 512, 1, 1)}
+    cin = 64
+    for b, proj in ParallelResNet18.BLOCKS:
+        f = {"2": 64, "3": 128, "4": 256, "5": 512, "6": 512}[b[3]]
+        shapes[b + ".conv1.kernel"], shapes[b + ".conv2.kernel"] = (f, cin, 3, 3), (f, f, 3, 3)
+        if proj:
+            shapes[b + ".proj.kernel"] = (f, cin, 1, 1)
+        cin = f
+    P = {k: flat[o:o + n].reshape(shapes[k]) if k in shapes else flat[o:o + n] for k, (o, n) in man.items()}
+    x = H.uniform(600, (N, Cc, Hh, W), 0.0, 1.0)
+    labels = np.array([1, classes - 1], np.uint32)
+    net.set_labels(rank, labels.reshape(N, 1, 1))
+    ref = ParallelResNet18(P, world)
+    logits_w, loss_w = ref.forward(x, labels)
+    net.forward(x)
+    assert H.max_rel(net.output(rank).reshape(N, classes), logits_w) < 5e-5, "gathered logits mismatch"
+    s, px = net.loss()
+    assert abs(s / px - loss_w) < 1e-5 * max(1.0, abs(loss_w))
+    G = ref.backward()
+    net.backward()
+    net.sync()
+    assert net.status() == 0
+    g = torch.from_numpy(net.param_grads(rank)).cuda()
+    dist.all_reduce(g)
+    g = g.cpu().numpy()
+    for name, (off, size) in man.items():
+        a, b = g[off:off + size], G[name].reshape(-1)
+        assert float(np.abs(a - b).max()) <= 2e-3 * float(np.abs(b).max()) + 1e-6, (name, H.max_rel(a, b))
     dist.barrier()
 
 
