@@ -107,6 +107,9 @@ public:
   void zero(GPUConn& conn) const { AD_CHECK(ad_fill_zero(dptr_, padded_elems() * elem_size(), conn.stream())); }
   // Host transfers in the reference's layout: packed NCHW fp32 of the INTERIOR.
   void load_host_nchw(const float* src, GPUContext* ctx) const;
+  // rows [row0, row0 + h) of a packed NCHW fp32 host tensor of full_h rows: one pitched copy, so that a rank
+  // receives its strip and nothing else
+  void load_host_nchw_rows(const float* src_full, size_t full_h, size_t row0, GPUContext* ctx) const;
   void store_host_nchw(float* dst, GPUContext* ctx) const;
 private:
   Shape3D dim_, offset_, stride_;

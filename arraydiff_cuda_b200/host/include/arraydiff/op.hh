@@ -278,6 +278,8 @@ private:
   VarData<A> data_;
 };
 template <typename A> using SrcOp = IOOp<A>;
+// A reader for activations that lets every rank take only its rows of a full host image (packed NCHW fp32).
+struct HostRows { const float* base; size_t full_h, row0; };
 
 // Common base of activation operators of one rank.
 class ActOp : public Var<Act> {

@@ -125,11 +125,14 @@ int adh_net_forward(void* h, const float* image_nchw) {
   auto* n = (Net*)h;
   n->txn.reset(new TxnId());
   n->opt->persist(*n->txn);
-  any rd = const_cast<float*>(image_nchw);
   for (auto& in : n->net.inputs) {
     if (!in) continue;
     VarIdSet v = VarIdSet::Singleton(in->data().val.var());
-    n->net.sink->load_val(*n->txn, v, 0, &rd);   // every rank receives the image (offset 0 each time)
+    const size_t h = in->shape().shape[1];
+    any rd;
+    if (h != n->cfg.input_h) rd = HostRows{image_nchw, n->cfg.input_h, in->rank() * h};   // the rank's strip, straight from the host image
+    else rd = const_cast<float*>(image_nchw);                                             // the whole image on every rank
+    n->net.sink->load_val(*n->txn, v, 0, &rd);
   }
   n->net.sink->eval(*n->txn);
   return AD_OK;

@@ -339,6 +339,21 @@ void GPUBatchArray3D<float>::load_host_nchw(const float* src, GPUContext* ctx) c
   conn.sync();
 }
 template <>
+void GPUBatchArray3D<float>::load_host_nchw_rows(const float* src_full, size_t full_h, size_t row0, GPUContext* ctx) const {
+  const size_t n = dim_.flat_size() * batch_;
+  GPUConn conn = ctx->conn();
+  ctx->reserve_scratch(n * sizeof(float));
+  float* tmp = (float*)ctx->get_scratch();
+  const long long W = dim_.shape[0], H = dim_.shape[1], C = dim_.shape[2];
+  assert(row0 + (size_t)H <= full_h);
+  CUDA_CHECK(cudaMemcpy2DAsync(tmp, (size_t)(H * W) * sizeof(float), src_full + row0 * (size_t)W, full_h * (size_t)W * sizeof(float),
+                               (size_t)(H * W) * sizeof(float), (size_t)C * batch_, cudaMemcpyHostToDevice, conn.stream()));
+  ad_tensor4 s = {tmp, AD_F32, (uint32_t)batch_, (uint32_t)C, (uint32_t)H, (uint32_t)W, C * H * W, H * W, W, 1};
+  ad_tensor4 d = view_interior();
+  AD_CHECK(ad_convert(&s, &d, 0, conn.stream()));
+  conn.sync();
+}
+template <>
 void GPUBatchArray3D<float>::store_host_nchw(float* dst, GPUContext* ctx) const {
   const size_t n = dim_.flat_size() * batch_;
   GPUConn conn = ctx->conn();

@@ -145,6 +145,13 @@ template <typename A>
 static void io_move(A& a, any* flat, size_t offset, bool to_device, GPUContext* g) {
   const size_t n = IOTraits<A>::size(a);
   GPUConn conn = g->conn();
+  if constexpr (std::is_same<A, Act>::value) {
+    if (auto hr = std::any_cast<HostRows>(flat)) {
+      assert(to_device);
+      a.load_host_nchw_rows(hr->base, hr->full_h, hr->row0, g);
+      return;
+    }
+  }
   if (auto hp = std::any_cast<float*>(flat)) {
     float* host = *hp + offset;
     if constexpr (std::is_same<A, Act>::value) {

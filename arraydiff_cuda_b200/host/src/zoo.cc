@@ -248,20 +248,25 @@ ParallelBatchNormParamOp<Act> spatial_parallel_proj_bottleneck_residual_v2_conv2
   return vars.finish(parallel_sum<Act>({proj, c3}, ctx));
 }
 
-static SpatialParallelNet begin_net(const ConvNetConfig& cfg, shared_ptr<Context> ctx, vector<ActVar>& strips) {
+// scatter_on_load: every rank's input variable is its strip, filled straight from the host image (HostRows);
+// otherwise every rank holds the whole image and a SpatialScatter2DOp cuts out its rows inside the graph
+// (the reference's BroadcastOp + SpatialScatter2DOp, src/zoo.cc:1522-1523).
+static SpatialParallelNet begin_net(const ConvNetConfig& cfg, shared_ptr<Context> ctx, vector<ActVar>& strips, bool scatter_on_load = false) {
   SpatialParallelNet net;
   const size_t R = ranks_of(ctx);
   net.batch_norm_use_fixed = make_shared<bool>(false);
   net.dev_params.resize(R); net.dev_grads.resize(R); net.dev_batch_stats.resize(R); net.dev_fixed_stats.resize(R);
   net.output_grad_vars.resize(R);
+  assert(cfg.input_h % R == 0);
   vector<ActVar> full;
   for (size_t r = 0; r < R; ++r) {
     if (!local_rank(ctx, r)) { net.inputs.push_back(nullptr); continue; }
-    auto in = IOOp<Act>::Make(Shape3D(cfg.input_w, cfg.input_h, cfg.input_c), cfg.batch_size, nullptr, r, ctx);
+    auto in = IOOp<Act>::Make(Shape3D(cfg.input_w, scatter_on_load ? cfg.input_h / R : cfg.input_h, cfg.input_c), cfg.batch_size, nullptr, r, ctx);
     net.inputs.push_back(in);
     net.input_vars.insert(in->data().val.var());
     full.push_back(in);
   }
+  if (scatter_on_load) { strips = full; return net; }
   // every rank holds the image and cuts out its own rows (reference src/zoo.cc:1522-1523)
   for (auto& x : full) strips.push_back(make_shared<SpatialScatter2DOpF>(x->rank(), R, x, ctx));
   (void)gpu_at;
@@ -322,7 +327,7 @@ static vector<ActVar> stem(SpatialParallelNet& net, const ConvNetConfig& cfg, si
 template <>
 SpatialParallelNet SpatialParallelResNet<float>::MakeStemStage1(const ConvNetConfig& cfg, shared_ptr<Context> ctx) {
   vector<ActVar> strips;
-  SpatialParallelNet net = begin_net(cfg, ctx, strips);
+  SpatialParallelNet net = begin_net(cfg, ctx, strips, true);
   auto sw = net.batch_norm_use_fixed;
   auto pooled = stem(net, cfg, 64, strips, ctx);
   // stage 1: bottlenecks 64-64-256
@@ -348,7 +353,7 @@ SpatialParallelNet SpatialParallelResNet<float>::MakeStemStage1(const ConvNetCon
 template <>
 SpatialParallelNet SpatialParallelResNet<float>::MakeSegNet50(const ConvNetConfig& cfg, const SegNetConfig& seg, shared_ptr<Context> ctx) {
   vector<ActVar> strips;
-  SpatialParallelNet net = begin_net(cfg, ctx, strips);
+  SpatialParallelNet net = begin_net(cfg, ctx, strips, true);
   auto sw = net.batch_norm_use_fixed;
   vector<ActVar> cur = stem(net, cfg, seg.base, strips, ctx);
   const size_t strides[4] = {1, 2, 1, 1}, dils[4] = {1, 1, 2, 4};
@@ -390,7 +395,7 @@ SpatialParallelNet SpatialParallelResNet<float>::MakeSegNet50(const ConvNetConfi
 template <>
 SpatialParallelNet SpatialParallelResNet<float>::MakeParallelResNet18(const ConvNetConfig& cfg, size_t classes, shared_ptr<Context> ctx) {
   vector<ActVar> strips;
-  SpatialParallelNet net = begin_net(cfg, ctx, strips);
+  SpatialParallelNet net = begin_net(cfg, ctx, strips, true);
   auto sw = net.batch_norm_use_fixed;
   const size_t R = ranks_of(ctx);
   // conv1: 7x7, stride 1, bias, Xavier (reference src/zoo.cc:1527-1556); no BN / ReLU before the pool

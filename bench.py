@@ -645,7 +645,7 @@ def run_net_workload(args, kind):
             "config": {"workload": "resnet50_dilated_segnet" if seg else "resnet50_stem_stage1", "image": [NB, 3, Hh, Ww], "strips": strips, "layout": "NHWC",
                        "bn_statistics": "per strip (as the reference)", "update": "allreduce + Nesterov SGD", "launch": "cuda graph" if use_graph else "eager",
                        "l2": "activations of one step total more than 1 GB, larger than L2", "parallelism": f"spatial-h{strips}"},
-            "e2e": {"value": flops / t_e2e / 1e12, "unit": UNIT, "h2d_bytes_per_step": int(x.nbytes + (labels.nbytes // world if seg else sum(d.nbytes for d in dy))),
+            "e2e": {"value": flops / t_e2e / 1e12, "unit": UNIT, "h2d_bytes_per_step": int(x.nbytes // world + (labels.nbytes // world if seg else sum(d.nbytes for d in dy))),
                     "d2h_bytes_per_step": int(np.prod(net.strip_shape[2:]) * NB * 4 if seg else np.prod(net.strip_shape) * 4), "steps": k_e2e, "timing": "host clock between synchronisations"},
             "gpu_launches": int(launches), "clocks": clocks,
         }))
