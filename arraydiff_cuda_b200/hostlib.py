@@ -114,8 +114,10 @@ class Net:
         assert x.shape == self.in_shape
         self.L.adh_net_forward(self.h, _p(x))
 
-    def output(self, rank):
-        a = np.empty(self.strip_shape, np.float32)
+    def output(self, rank, out=None):
+        """`out`: a float32 array of strip_shape to fill (e.g. in pinned memory) instead of a fresh one"""
+        a = np.empty(self.strip_shape, np.float32) if out is None else out
+        assert a.shape == self.strip_shape and a.dtype == np.float32 and a.flags.c_contiguous
         assert self.L.adh_net_get_output(self.h, rank, _p(a)) == 0
         return a
 

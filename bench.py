@@ -574,6 +574,15 @@ def run_net_workload(args, kind):
     else:
         dy = [rng.standard_normal(net.strip_shape).astype(np.float32) for _ in range(strips)]
 
+    # the end-to-end step moves its tensors between PINNED host buffers and the device
+    def pinned(a):
+        return torch.from_numpy(a).pin_memory().numpy()
+    x = pinned(x)
+    dy = [pinned(d) for d in dy]
+    if seg:
+        labels = pinned(labels)
+    out_host = pinned(np.empty(net.strip_shape, np.float32))
+
     def e2e_step():
         net.forward(x)                       # host image -> every local rank (H2D inside)
         for r in ranks:
@@ -583,7 +592,7 @@ def run_net_workload(args, kind):
                 net.set_output_grad(r, dy[r])    # host upstream gradient -> device
         net.backward()
         net.sgd_step()
-        return net.loss() if seg else net.output(ranks[0])          # D2H read of a result
+        return net.loss() if seg else net.output(ranks[0], out=out_host)          # D2H read of a result
 
     # steady-state step: the resident step replayed from a CUDA graph (one process per GPU keeps the
     # eager path: its flag epochs change every step)
