@@ -24,6 +24,7 @@ class HaloArgs(C.Structure):
         ("signal_flags", vp * AD_MAX_PEERS),
         ("epoch", u64),
         ("block_counter", vp),
+        ("epoch_base", vp),
     ]
 
 
@@ -58,6 +59,10 @@ SIGNATURES = {
     "ad_flag_signal": (C.c_int, [vp, u64, vp]),
     "ad_ipc_get_handle": (C.c_int, [vp, C.c_char_p]),
     "ad_ipc_open_handle": (C.c_int, [C.c_char_p, C.POINTER(vp)]),
+    "ad_flag_wait_rel": (C.c_int, [vp, vp, u64, u64, vp, vp]),
+    "ad_flag_signal_rel": (C.c_int, [vp, vp, u64, vp]),
+    "ad_flag_advance": (C.c_int, [vp, u64, vp]),
+    "ad_peer_sum": (C.c_int, [u32, vp, vp, sz, sz, vp]),
     "ad_ipc_close_handle": (C.c_int, [vp]),
     "ad_enable_peer_access": (C.c_int, [C.c_int, C.c_int]),
     "ad_device_malloc": (C.c_int, [sz, C.POINTER(vp)]),

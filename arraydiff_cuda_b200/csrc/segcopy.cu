@@ -41,6 +41,7 @@ struct SegParams {
   uint64_t* signal_flags[AD_MAX_PEERS];
   uint32_t signal_mask;
   uint64_t epoch;
+  const unsigned long long* epoch_base;
   uint32_t* block_counter;
 };
 
@@ -185,10 +186,11 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) seg_move_kernel(const Seg
       if (ticket == gridDim.x - 1) {
         __threadfence_system();
         *prm.block_counter = 0u;
+        const unsigned long long value = (unsigned long long)prm.epoch + (prm.epoch_base ? *prm.epoch_base : 0ull);
         for (int q = 0; q < AD_MAX_PEERS; ++q)
           if (prm.signal_mask & (1u << q)) {
             unsigned long long* f = (unsigned long long*)prm.signal_flags[q];
-            asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(f), "l"((unsigned long long)prm.epoch) : "memory");
+            asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(f), "l"(value) : "memory");
           }
       }
     }
@@ -290,6 +292,7 @@ extern "C" int ad_halo_exchange(const ad_halo_args* a, void* stream) {
       }
     }
     prm.epoch = a->epoch;
+    prm.epoch_base = (const unsigned long long*)a->epoch_base;
     prm.block_counter = a->block_counter;
   }
   return launch_seg(prm, as_stream(stream));

@@ -137,7 +137,11 @@ public:
   // the caller-installed hook (NCCL) is used.
   typedef void (*AllreduceHook)(float* buf, size_t count, cudaStream_t stream, void* user);
   void set_allreduce_hook(AllreduceHook fn, void* user) { ar_hook_ = fn; ar_user_ = user; }
+  bool has_allreduce_hook() const { return ar_hook_ != nullptr; }
   void allreduce_sum(float* local_buf_rank0_offset_base, size_t count);
+  // Between processes: advances every local rank's flag base by the signalling operations issued since the
+  // last call (Spatial2DComm::end_phase).  Call it where a unit of work that may be replayed as a CUDA graph ends.
+  void end_phase();
 
 private:
   size_t num_ranks_, my_rank_;
@@ -148,6 +152,8 @@ private:
   Spatial2DComm* spatial_comms_;
   AllreduceHook ar_hook_;
   void* ar_user_;
+  float* ar_stage_ = nullptr;    // between processes without a hook: this rank's gradient as its peers read it
+  size_t ar_stage_count_ = 0;
 };
 
 }  // namespace arraydiff

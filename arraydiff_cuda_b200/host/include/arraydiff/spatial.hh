@@ -58,7 +58,15 @@ public:
   // all-gather of strips between processes: flag word q of this rank's block says "rank q's strip of the
   // gather_epoch-th gather (or gather gradient) may be read"
   uint64_t* gather_flags() const { return gflags_; }
-  uint64_t gather_epoch = 0;
+  // Between processes every flag value is *epoch_base() + k, k the number of the signalling operation inside
+  // the current phase (next_phase_epoch()); end_phase() advances the base on the device by the k used.  A
+  // phase recorded into a CUDA graph therefore replays with fresh values, and all ranks -- which run the
+  // same operations in the same order -- agree on them.
+  uint64_t* epoch_base() const { return ebase_; }
+  uint64_t next_phase_epoch() { return ++phase_; }
+  void end_phase(cudaStream_t s);
+  // flag words of the gradient allreduce between processes: word q = progress of rank q
+  uint64_t* allreduce_flags() const { return arflags_; }
 
   uint32_t rank, rank_w, rank_h, num_ranks, num_w_ranks, num_h_ranks;
   uint64_t epoch;
@@ -74,6 +82,9 @@ private:
                           // 3 grad_next, 4 next_ready, 5 prev_ready
   uint32_t* counter_;     // block ticket counter for the publishing kernel
   uint64_t* gflags_ = nullptr;   // 8 words, see gather_flags()
+  uint64_t* arflags_ = nullptr;  // 8 words, see allreduce_flags()
+  uint64_t* ebase_ = nullptr;    // device word, see epoch_base()
+  uint64_t phase_ = 0;
   bool in_group_;
 };
 

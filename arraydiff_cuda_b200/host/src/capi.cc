@@ -135,6 +135,7 @@ int adh_net_forward(void* h, const float* image_nchw) {
     n->net.sink->load_val(*n->txn, v, 0, &rd);
   }
   n->net.sink->eval(*n->txn);
+  n->ctx->end_phase();
   return AD_OK;
 }
 int adh_net_get_output(void* h, int rank, float* host_strip) {
@@ -161,6 +162,7 @@ int adh_net_set_output_grad(void* h, int rank, const float* host_strip) {
 int adh_net_backward(void* h) {
   auto* n = (Net*)h;
   n->net.sink->backward(*n->txn);
+  n->ctx->end_phase();
   return AD_OK;
 }
 // flat gradient of rank's parameters (this rank's strip only, before the allreduce)
@@ -199,6 +201,7 @@ int adh_net_step_resident(void* h, int with_update) {
       if (n->ctx->is_local(r)) n->net.sink->load_grad(*n->txn, n->net.output_grad_vars[r], 0, nullptr);
   n->net.sink->backward(*n->txn);
   if (with_update) n->opt->step(*n->txn);
+  n->ctx->end_phase();
   return AD_OK;
 }
 // labels of `rank`'s strip, uint32 [N][h][W] (nets that end in the per-pixel loss)
@@ -237,17 +240,20 @@ int adh_net_get_output_grad(void* h, int rank, float* host_strip) {
 // steps.  One process per GPU keeps the eager path: its flag epochs change every step.
 int adh_net_step_graph(void* h, int with_update) {
   auto* n = (Net*)h;
-  if (n->ctx->distributed()) return adh_net_step_resident(h, with_update);
+  // one process per GPU: replayable when the gradient allreduce is the built-in peer exchange (a hook may
+  // call into a library that cannot be captured)
+  if (n->ctx->distributed() && n->ctx->has_allreduce_hook()) return adh_net_step_resident(h, with_update);
   float key[3];
   n->opt->schedule_now(key);
   if (n->gexec && (n->g_update != with_update || std::memcmp(key, n->g_key, sizeof key))) {
     cudaGraphExecDestroy(n->gexec);
     n->gexec = nullptr;
   }
-  const size_t R = n->ctx->num_ranks();
-  cudaStream_t origin = n->ctx->device_context(0)->stream();
+  const bool dist = n->ctx->distributed();
+  const size_t R = dist ? 1 : n->ctx->num_ranks(), first = dist ? n->ctx->my_rank() : 0;
+  cudaStream_t origin = n->ctx->device_context(first)->stream();
   if (!n->gexec) {
-    GPUConn c0 = n->ctx->device_context(0)->conn();
+    GPUConn c0 = n->ctx->device_context(first)->conn();
     CUDA_CHECK(cudaStreamBeginCapture(origin, cudaStreamCaptureModeRelaxed));
     vector<cudaEvent_t> evs;
     cudaEvent_t fork;
@@ -267,7 +273,7 @@ int adh_net_step_graph(void* h, int with_update) {
       evs.push_back(e);
     }
     cudaGraph_t graph = nullptr;
-    GPUConn c1 = n->ctx->device_context(0)->conn();
+    GPUConn c1 = n->ctx->device_context(first)->conn();
     CUDA_CHECK(cudaStreamEndCapture(origin, &graph));
     CUDA_CHECK(cudaGraphInstantiate(&n->gexec, graph, 0));
     cudaGraphDestroy(graph);
@@ -277,7 +283,7 @@ int adh_net_step_graph(void* h, int with_update) {
     CUDA_CHECK(cudaGraphLaunch(n->gexec, origin));   // the recording itself executed nothing
     return AD_OK;
   }
-  GPUConn c0 = n->ctx->device_context(0)->conn();
+  GPUConn c0 = n->ctx->device_context(first)->conn();
   CUDA_CHECK(cudaGraphLaunch(n->gexec, origin));
   if (with_update) n->opt->skip_iterations(1);
   return AD_OK;
@@ -285,7 +291,7 @@ int adh_net_step_graph(void* h, int with_update) {
 // kernels one replay of the graph launches (0 before the first adh_net_step_graph)
 uint64_t adh_net_graph_launches(void* h) { return ((Net*)h)->g_launches; }
 // allreduce of the gradients + SGD update on every rank
-int adh_net_sgd_step(void* h) { auto* n = (Net*)h; n->opt->step(*n->txn); return AD_OK; }
+int adh_net_sgd_step(void* h) { auto* n = (Net*)h; n->opt->step(*n->txn); n->ctx->end_phase(); return AD_OK; }
 int adh_net_sync(void* h) { ((Net*)h)->ctx->sync(); return AD_OK; }
 int adh_net_status(void* h) {
   auto* n = (Net*)h;

@@ -123,15 +123,56 @@ MultiGPUContext::MultiGPUContext(const vector<int>& devices, ComputeMode mode, s
 void MultiGPUContext::sync() {
   for (size_t r = 0; r < num_ranks_; ++r) if (dev_ctxs_[r]) dev_ctxs_[r]->sync();
 }
+void MultiGPUContext::end_phase() {
+  if (!distributed_) return;
+  for (size_t r = 0; r < num_ranks_; ++r)
+    if (is_local(r)) spatial_comms_[r].end_phase(dev_ctxs_[r]->stream());
+}
 void MultiGPUContext::sync_rank(size_t rank) { dev_ctxs_.at(rank)->sync(); }
 shared_ptr<GPUContext> MultiGPUContext::device_context(size_t rank) { assert(dev_ctxs_.at(rank)); return dev_ctxs_.at(rank); }
 Spatial2DComm* MultiGPUContext::spatial_comm(size_t rank) { return &spatial_comms_[rank]; }
 
 void MultiGPUContext::allreduce_sum(float* buf, size_t count) {
   if (num_ranks_ == 1) return;
+  if (distributed_ && ar_hook_) {
+    ar_hook_(buf, count, dev_ctxs_[my_rank_]->stream(), ar_user_);   // e.g. ncclAllReduce
+    return;
+  }
   if (distributed_) {
-    assert(ar_hook_ && "install an allreduce hook (NCCL) for one-process-per-GPU runs");
-    ar_hook_(buf, count, dev_ctxs_[my_rank_]->stream(), ar_user_);
+    // No hook: reduce-scatter + all-gather with peer loads, ordered by flag words with bounded waits.  Every
+    // kernel and copy is on this rank's stream and every flag value is relative, so the whole exchange can be
+    // captured in a CUDA graph; each slice is summed once, in rank order, so all ranks end with the same bits.
+    const size_t r = my_rank_, R = num_ranks_;
+    GPUContext* g = dev_ctxs_[r].get();
+    GPUConn conn = g->conn();
+    cudaStream_t s = conn.stream();
+    Spatial2DComm* comm = &spatial_comms_[r];
+    if (ar_stage_count_ < count) {
+      ar_stage_ = (float*)g->arena().alloc(count * sizeof(float));   // same offset on every rank: all ranks get here alike
+      ar_stage_count_ = count;
+    }
+    const uint64_t kTimeoutNs = 2000000000ull;
+    auto round = [&]() {
+      const uint64_t k = comm->next_phase_epoch();
+      for (size_t q = 0; q < R; ++q)
+        if (q != r) AD_CHECK(ad_flag_signal_rel((uint64_t*)peer_ptr(comm->allreduce_flags() + r, r, q), comm->epoch_base(), k, s));
+      for (size_t q = 0; q < R; ++q)
+        if (q != r) AD_CHECK(ad_flag_wait_rel(comm->allreduce_flags() + q, comm->epoch_base(), k, kTimeoutNs, g->status_word(), s));
+    };
+    CUDA_CHECK(cudaMemcpyAsync(ar_stage_, buf, count * sizeof(float), cudaMemcpyDeviceToDevice, s));
+    round();                                                       // every rank's staged gradient is readable
+    const size_t per = ((count + R - 1) / R + 3) / 4 * 4;
+    auto lo = [&](size_t q) { return std::min(count, q * per); };
+    const float* srcs[ARRAYDIFF_MAX_PEERS];
+    for (size_t q = 0; q < R; ++q) srcs[q] = (const float*)peer_ptr(ar_stage_, r, q);
+    AD_CHECK(ad_peer_sum((uint32_t)R, srcs, buf, lo(r), lo(r + 1), s));   // my slice of the sum
+    round();                                                       // every rank's slice is final
+    for (size_t q = 0; q < R; ++q) {
+      if (q == r || lo(q) == lo(q + 1)) continue;
+      CUDA_CHECK(cudaMemcpyAsync(buf + lo(q), (const float*)peer_ptr(buf, r, q) + lo(q), (lo(q + 1) - lo(q)) * sizeof(float),
+                                 cudaMemcpyDeviceToDevice, s));
+    }
+    round();                                                       // nobody still reads my slice or my staged copy
     return;
   }
   // In-process ranks: rank 0 adds every peer's buffer (peer loads), then every peer copies the sum back.
@@ -189,7 +230,11 @@ void Spatial2DComm::InitAll(Spatial2DComm* comms, uint32_t num_w_ranks, uint32_t
       c.flags_ = (uint64_t*)g->arena().alloc(64);      // same offset on every rank: first allocation after the status word
       c.counter_ = (uint32_t*)g->arena().alloc(64);
       c.gflags_ = (uint64_t*)g->arena().alloc(64);
+      c.arflags_ = (uint64_t*)g->arena().alloc(64);
+      c.ebase_ = (uint64_t*)g->arena().alloc(64);
       CUDA_CHECK(cudaMemsetAsync(c.gflags_, 0, 64, conn.stream()));
+      CUDA_CHECK(cudaMemsetAsync(c.arflags_, 0, 64, conn.stream()));
+      CUDA_CHECK(cudaMemsetAsync(c.ebase_, 0, 64, conn.stream()));
       CUDA_CHECK(cudaMemsetAsync(c.flags_, 0, 64, conn.stream()));
       CUDA_CHECK(cudaMemsetAsync(c.counter_, 0, 64, conn.stream()));
       conn.sync();
@@ -198,6 +243,11 @@ void Spatial2DComm::InitAll(Spatial2DComm* comms, uint32_t num_w_ranks, uint32_t
 }
 
 void Spatial2DComm::group_start() { in_group_ = true; }
+void Spatial2DComm::end_phase(cudaStream_t s) {
+  if (!ebase_ || phase_ == 0) return;
+  AD_CHECK(ad_flag_advance(ebase_, phase_, s));
+  phase_ = 0;
+}
 
 void Spatial2DComm::record(Spatial2DOperation op, void* buf, uint32_t p, uint32_t w, uint32_t h, uint32_t c, uint32_t n,
                            Spatial2DTensorFormat f, Spatial2DDataType t) {
@@ -205,22 +255,27 @@ void Spatial2DComm::record(Spatial2DOperation op, void* buf, uint32_t p, uint32_
   arg.operation = op; arg.tensor_format = f; arg.data_type = t;
   arg.halo_pad = p; arg.base_width = w; arg.base_height = h; arg.num_channels = c; arg.batch_size = n;
   arg.buffer = buf;
-  arg.epoch = ++epoch;
+  ++epoch;
+  arg.epoch = epoch;
   if (!ctx_) return;
   auto g = ctx_->device_context(rank);
   GPUConn conn = g->conn();
   if (!ctx_->distributed()) {
     // "my buffer is as my neighbours may now read it"
     CUDA_CHECK(cudaEventRecord(ready_, conn.stream()));
-  } else if (op == SPATIAL2D_OP_HXEXCH) {
+    return;
+  }
+  const uint64_t k = next_phase_epoch();   // between processes: the value is *epoch_base() + k
+  arg.epoch = k;
+  if (op == SPATIAL2D_OP_HXEXCH) {
     // my padded buffer exists, its pad cells are zeroed and its interior is written: the neighbours
     // may now push into my halo rows (words 4 / 5: "next is ready" / "prev is ready")
-    if (rank > 0) AD_CHECK(ad_flag_signal((uint64_t*)ctx_->peer_ptr(flags_ + 4, rank, rank - 1), epoch, conn.stream()));
-    if (rank + 1 < num_ranks) AD_CHECK(ad_flag_signal((uint64_t*)ctx_->peer_ptr(flags_ + 5, rank, rank + 1), epoch, conn.stream()));
+    if (rank > 0) AD_CHECK(ad_flag_signal_rel((uint64_t*)ctx_->peer_ptr(flags_ + 4, rank, rank - 1), ebase_, k, conn.stream()));
+    if (rank + 1 < num_ranks) AD_CHECK(ad_flag_signal_rel((uint64_t*)ctx_->peer_ptr(flags_ + 5, rank, rank + 1), ebase_, k, conn.stream()));
   } else if (op == SPATIAL2D_OP_HXREDUCE) {
     // my halo-gradient rows are final: tell the neighbours that will pull them
-    if (rank + 1 < num_ranks) AD_CHECK(ad_flag_signal((uint64_t*)ctx_->peer_ptr(flags_ + 2, rank, rank + 1), epoch, conn.stream()));
-    if (rank > 0) AD_CHECK(ad_flag_signal((uint64_t*)ctx_->peer_ptr(flags_ + 3, rank, rank - 1), epoch, conn.stream()));
+    if (rank + 1 < num_ranks) AD_CHECK(ad_flag_signal_rel((uint64_t*)ctx_->peer_ptr(flags_ + 2, rank, rank + 1), ebase_, k, conn.stream()));
+    if (rank > 0) AD_CHECK(ad_flag_signal_rel((uint64_t*)ctx_->peer_ptr(flags_ + 3, rank, rank - 1), ebase_, k, conn.stream()));
   }
 }
 void Spatial2DComm::halo_exchange(void* buf, uint32_t halo_pad, uint32_t base_width, uint32_t base_height,
@@ -273,15 +328,16 @@ void Spatial2DComm::group_end(GPUConn& conn) {
     if (rank + 1 < num_ranks) a.signal_flags[rank + 1] = (uint64_t*)ctx_->peer_ptr(flags_ + 0, rank, rank + 1);
     if (rank > 0) a.signal_flags[rank - 1] = (uint64_t*)ctx_->peer_ptr(flags_ + 1, rank, rank - 1);
     a.epoch = arg.epoch;
+    a.epoch_base = ebase_;
     a.block_counter = counter_;
-    if (rank + 1 < num_ranks) AD_CHECK(ad_flag_wait(flags_ + 4, arg.epoch, kTimeoutNs, g->status_word(), s));
-    if (rank > 0) AD_CHECK(ad_flag_wait(flags_ + 5, arg.epoch, kTimeoutNs, g->status_word(), s));
+    if (rank + 1 < num_ranks) AD_CHECK(ad_flag_wait_rel(flags_ + 4, ebase_, arg.epoch, kTimeoutNs, g->status_word(), s));
+    if (rank > 0) AD_CHECK(ad_flag_wait_rel(flags_ + 5, ebase_, arg.epoch, kTimeoutNs, g->status_word(), s));
     AD_CHECK(ad_halo_exchange(&a, s));
-    if (rank > 0) AD_CHECK(ad_flag_wait(flags_ + 0, arg.epoch, kTimeoutNs, g->status_word(), s));
-    if (rank + 1 < num_ranks) AD_CHECK(ad_flag_wait(flags_ + 1, arg.epoch, kTimeoutNs, g->status_word(), s));
+    if (rank > 0) AD_CHECK(ad_flag_wait_rel(flags_ + 0, ebase_, arg.epoch, kTimeoutNs, g->status_word(), s));
+    if (rank + 1 < num_ranks) AD_CHECK(ad_flag_wait_rel(flags_ + 1, ebase_, arg.epoch, kTimeoutNs, g->status_word(), s));
   } else {
-    if (rank > 0) AD_CHECK(ad_flag_wait(flags_ + 2, arg.epoch, kTimeoutNs, g->status_word(), s));
-    if (rank + 1 < num_ranks) AD_CHECK(ad_flag_wait(flags_ + 3, arg.epoch, kTimeoutNs, g->status_word(), s));
+    if (rank > 0) AD_CHECK(ad_flag_wait_rel(flags_ + 2, ebase_, arg.epoch, kTimeoutNs, g->status_word(), s));
+    if (rank + 1 < num_ranks) AD_CHECK(ad_flag_wait_rel(flags_ + 3, ebase_, arg.epoch, kTimeoutNs, g->status_word(), s));
     AD_CHECK(ad_halo_reduce(&a, s));
   }
 }

@@ -776,12 +776,12 @@ SpatialAllGather2DOpF::SpatialAllGather2DOpF(vector<ActVar> inputs, shared_ptr<C
 void SpatialAllGather2DOpF::wait_peers(size_t rank, cudaStream_t s) {
   auto* m = dynamic_cast<MultiGPUContext*>(ctx_.get());
   Spatial2DComm* comm = m->spatial_comm(rank);
-  const uint64_t ep = ++comm->gather_epoch;
+  const uint64_t k = comm->next_phase_epoch();
   GPUContext* g = m->device_context(rank).get();
   for (size_t q = 0; q < num_ranks_; ++q)
-    if (q != rank) AD_CHECK(ad_flag_signal((uint64_t*)m->peer_ptr(comm->gather_flags() + rank, rank, q), ep, s));
+    if (q != rank) AD_CHECK(ad_flag_signal_rel((uint64_t*)m->peer_ptr(comm->gather_flags() + rank, rank, q), comm->epoch_base(), k, s));
   for (size_t q = 0; q < num_ranks_; ++q)
-    if (q != rank) AD_CHECK(ad_flag_wait(comm->gather_flags() + q, ep, 2000000000ull, g->status_word(), s));
+    if (q != rank) AD_CHECK(ad_flag_wait_rel(comm->gather_flags() + q, comm->epoch_base(), k, 2000000000ull, g->status_word(), s));
 }
 // stream `to` waits for everything issued so far on stream `from`
 static void order_after(cudaStream_t to, cudaStream_t from) {

@@ -549,9 +549,12 @@ def run_net_workload(args, kind):
             with torch.cuda.stream(torch.cuda.ExternalStream(stream)):
                 dist.all_reduce(t)
 
-        hook = HOOK(allreduce)
-        keep.append(hook)
-        Lh.adh_context_set_allreduce_hook(h, C.cast(hook, C.c_void_p), None)
+        if args.nccl_allreduce:
+            # filter gradients over NCCL (torch.distributed) instead of the built-in peer exchange; such a
+            # step is launched eagerly
+            hook = HOOK(allreduce)
+            keep.append(hook)
+            Lh.adh_context_set_allreduce_hook(h, C.cast(hook, C.c_void_p), None)
 
         class Ctx:
             pass
@@ -594,9 +597,9 @@ def run_net_workload(args, kind):
         net.sgd_step()
         return net.loss() if seg else net.output(ranks[0], out=out_host)          # D2H read of a result
 
-    # steady-state step: the resident step replayed from a CUDA graph (one process per GPU keeps the
-    # eager path: its flag epochs change every step)
-    use_graph = world == 1 and not args.no_graph
+    # steady-state step: the resident step replayed from a CUDA graph (flag values between processes are
+    # relative to a device-resident base, the gradient allreduce is the built-in peer exchange)
+    use_graph = not args.no_graph and not (world > 1 and args.nccl_allreduce)
     step = (lambda: net.step_graph(True)) if use_graph else (lambda: net.step_resident(True))
     e2e_step()
     net.step_resident(True)
@@ -652,7 +655,7 @@ def run_net_workload(args, kind):
             "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "images_per_s": NB / step_s,
             "config": {"workload": "resnet50_dilated_segnet" if seg else "resnet50_stem_stage1", "image": [NB, 3, Hh, Ww], "strips": strips, "layout": "NHWC",
-                       "bn_statistics": "per strip (as the reference)", "update": "allreduce + Nesterov SGD", "launch": "cuda graph" if use_graph else "eager",
+                       "bn_statistics": "per strip (as the reference)", "update": "allreduce (%s) + Nesterov SGD" % ("nccl" if world > 1 and args.nccl_allreduce else "peer loads" if strips > 1 else "single rank"), "launch": "cuda graph" if use_graph else "eager",
                        "l2": "activations of one step total more than 1 GB, larger than L2", "parallelism": f"spatial-h{strips}"},
             "e2e": {"value": flops / t_e2e / 1e12, "unit": UNIT, "h2d_bytes_per_step": int(x.nbytes // world + (labels.nbytes // world if seg else sum(d.nbytes for d in dy))),
                     "d2h_bytes_per_step": int(np.prod(net.strip_shape[2:]) * NB * 4 if seg else np.prod(net.strip_shape) * 4), "steps": k_e2e, "timing": "host clock between synchronisations"},
@@ -677,6 +680,8 @@ def main():
                          "segnet: dilated ResNet-50 segmentation net, 2x3x1024x2048 (config 4; --image = height)")
     ap.add_argument("--strips", type=int, default=1, help="stem_stage1 on one GPU: ranks sharing the device")
     ap.add_argument("--image", type=int, default=1024, help="stem_stage1: image height = width")
+    ap.add_argument("--nccl-allreduce", action="store_true",
+                    help="stem_stage1 / segnet on several GPUs: sum the filter gradients with NCCL instead of the built-in peer exchange")
     ap.add_argument("--no-graph", action="store_true", help="stem_stage1: launch every kernel eagerly instead of replaying a CUDA graph")
     ap.add_argument("--batch", type=int, default=BATCH,
                     help="images per step; the default is the workload's, smaller values are for profiler captures")

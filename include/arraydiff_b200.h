@@ -94,6 +94,7 @@ typedef struct {
   uint64_t* signal_flags[AD_MAX_PEERS]; /* may be all NULL */
   uint64_t epoch;
   uint32_t* block_counter;  /* one zero-initialised uint32 in local memory; needed iff signalling */
+  const uint64_t* epoch_base; /* NULL, or a device word of this rank: the value signalled is *epoch_base + epoch */
 } ad_halo_args;
 
 int ad_halo_exchange(const ad_halo_args* args, void* stream);
@@ -108,6 +109,25 @@ int ad_halo_reduce(const ad_halo_args* args, void* stream);
 int ad_flag_wait(const uint64_t* flag, uint64_t epoch, uint64_t timeout_ns, int32_t* status_word, void* stream);
 /* Stores `epoch` to *flag with system-scope release semantics after all prior work on `stream`. */
 int ad_flag_signal(uint64_t* flag, uint64_t epoch, void* stream);
+/*
+ * The same two with the value *base + offset, `base` a device word of the calling rank: a sequence of
+ * waits and signals recorded once (a CUDA graph of a training step) serves every step, the base being
+ * advanced on the device by ad_flag_advance when a step's offsets are used up.  All ranks advance their
+ * bases alike, so the values agree across ranks.
+ */
+int ad_flag_wait_rel(const uint64_t* flag, const uint64_t* base, uint64_t offset, uint64_t timeout_ns,
+                     int32_t* status_word, void* stream);
+int ad_flag_signal_rel(uint64_t* flag, const uint64_t* base, uint64_t offset, void* stream);
+int ad_flag_advance(uint64_t* base, uint64_t delta, void* stream);
+/*
+ * out[i] = sum over q < num_ranks of bufs[q][i] for i in [begin, end), peers in rank order (so every rank
+ * that sums the same range gets the same bits).  bufs may be peer memory (plain loads over NVLink); all
+ * pointers 16-byte aligned.  The building block of the filter-gradient allreduce between processes
+ * (replaces ncclAllReduce in ParallelSGDOptimizer::step, include/arraydiff/optimize.hh:407-470, when the
+ * step is to be captured in a CUDA graph): reduce-scatter = every rank sums its slice, all-gather = every
+ * rank copies the other slices, with ad_flag_* in between.
+ */
+int ad_peer_sum(uint32_t num_ranks, const float* const* bufs, float* out, size_t begin, size_t end, void* stream);
 
 /* CUDA IPC plumbing for one-process-per-GPU launches: the reference is single-process and gets
  * peer pointers for free (src/spatial.cc:13-50); separate processes exchange these handles. */

@@ -122,6 +122,49 @@ def host_part(rank, world, local):
     assert H.max_rel(net.params(rank), theta) < 1e-5, "update after allreduce mismatch"
     dist.barrier()
     classifier_part(ctx, rank, world)
+    graph_part(ctx, rank, world, local)
+
+
+def graph_part(ctx, rank, world, local):
+    """Without an allreduce hook the filter gradients are summed by the built-in peer exchange and the whole
+    training step replays from a CUDA graph in every process; after the same steps the parameters equal, bit
+    for bit, those of the same net run as `world` strips inside one process (eagerly, on rank 0's GPU)."""
+    ctx.L.adh_context_set_allreduce_hook(ctx.h, None, None)
+    N, Cc, Hh, W = 1, 3, 64 * world, 64
+    x = H.uniform(700, (N, Cc, Hh, W), 0.0, 1.0)
+    dy = H.normal(701, (N, 256, Hh // 4, W // 4))
+    h = dy.shape[2] // world
+
+    def train(net, ranks, graph, init=None):
+        net.configure_sgd(1e-3, 0.9, l2=1e-4, nesterov=True)
+        if init is not None:      # the draw order of the shared generator differs between the two set-ups
+            net.set_params(init)
+        net.forward(x)
+        for r in ranks:
+            net.set_output_grad(r, dy[:, :, r * h:(r + 1) * h])
+        net.backward()
+        net.sgd_step()
+        net.step_resident(True)
+        for _ in range(3):
+            net.step_graph(True) if graph else net.step_resident(True)
+        net.step_resident(True)
+        net.sync()
+        assert net.status() == 0
+        return net.params(ranks[0])
+
+    net = hostlib.Net(ctx, "stem_stage1", Hh, W, Cc, N, seed=29)
+    start = net.params(rank).copy()
+    mine = train(net, [rank], True)
+    assert net.graph_launches() > 100, "the step was not captured"
+    got = torch.from_numpy(mine).cuda()
+    ref = got.clone()
+    dist.broadcast(ref, 0)
+    assert torch.equal(got, ref), "replicas diverged"
+    if rank == 0:
+        local_ctx = hostlib.Context([local] * world, hostlib.F32_NCHW, arena_mb=512)
+        want = train(hostlib.Net(local_ctx, "stem_stage1", Hh, W, Cc, N, seed=29), list(range(world)), False, init=start)
+        assert np.array_equal(mine, want), float(np.abs(mine - want).max())
+    dist.barrier()
 
 
 def classifier_part(ctx, rank, world):
