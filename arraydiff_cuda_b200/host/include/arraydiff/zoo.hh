@@ -80,6 +80,12 @@ public:
   // on every rank, global average pool, linear classifier, softmax NLL.  Every rank computes the (tiny) head
   // on the whole batch; labels go to every net.losses[r]->load_labels.
   static SpatialParallelNet MakeParallelResNet18(const ConvNetConfig& config, size_t classes, shared_ptr<Context> ctx);
+  // ResNet-50 classifier over H-strips (the reference's MakeParallelResNet50 entry, src/zoo.cc:2200-2484, there an
+  // 18-layer body; here the bottleneck stages {3,4,6,3} built from spatial_parallel_*bottleneck* blocks): stem,
+  // max pool, stages strided 1,2,2,2, BN + ReLU, all-gather, global average pool, linear, softmax NLL.  A strided
+  // stage needs an even strip height; when a stage would meet an odd one (224 rows over 2 strips reach 7 rows per
+  // strip in front of stage 4) the strips are re-assembled in front of it and the rest runs replicated per rank.
+  static SpatialParallelNet MakeParallelResNet50(const ConvNetConfig& config, size_t classes, shared_ptr<Context> ctx);
   // Dilated ResNet-50 segmentation net at output stride 8 with a bilinear x8 head and per-pixel loss
   // (the 1024x2048, 19-class configuration); labels go to net.losses[r]->load_labels.
   static SpatialParallelNet MakeSegNet50(const ConvNetConfig& config, const SegNetConfig& seg, shared_ptr<Context> ctx);

@@ -64,6 +64,7 @@ void* adh_net_create(void* c, const char* kind, int H, int W, int C, int batch, 
   if (!std::strcmp(kind, "conv3x3")) n->net = SpatialParallelResNet<float>::MakeConv3x3(n->cfg, (size_t)filters, n->ctx);
   else if (!std::strcmp(kind, "stem_stage1")) n->net = SpatialParallelResNet<float>::MakeStemStage1(n->cfg, n->ctx);
   else if (!std::strcmp(kind, "parallel_resnet18")) n->net = SpatialParallelResNet<float>::MakeParallelResNet18(n->cfg, filters > 0 ? (size_t)filters : 1000, n->ctx);
+  else if (!std::strcmp(kind, "parallel_resnet50")) n->net = SpatialParallelResNet<float>::MakeParallelResNet50(n->cfg, filters > 0 ? (size_t)filters : 1000, n->ctx);
   else if (!std::strncmp(kind, "segnet", 6)) {
     // "segnet50": ResNet-50 depth; "segnet_small": one block per stage; `filters` (if > 0) = stem width
     SegNetConfig seg;
@@ -210,6 +211,14 @@ int adh_net_set_labels(void* h, int rank, const uint32_t* host) {
   for (auto& l : n->net.losses)
     if ((int)l->rank() == rank) { l->load_labels(host); return AD_OK; }
   return AD_ERR_BAD_ARG;
+}
+// weight of every per-pixel (per-image) loss term in the gradient, e.g. 1 / (global batch x ranks per replica group)
+// when several data-parallel groups sum their gradients
+int adh_net_set_loss_weight(void* h, float w) {
+  auto* n = (Net*)h;
+  if (n->net.losses.empty()) return AD_ERR_BAD_ARG;
+  for (auto& l : n->net.losses) l->set_loss_weight(w);
+  return AD_OK;
 }
 // sum of the per-pixel losses of the local ranks' strips and the number of pixels behind it (synchronous)
 int adh_net_loss(void* h, double* sum, uint64_t* pixels) {

@@ -448,4 +448,77 @@ SpatialParallelNet SpatialParallelResNet<float>::MakeParallelResNet18(const Conv
   return net;
 }
 
+// single-rank twins of the halo_conv / bottleneck helpers for the replicated tail of a net: ordinary zero padding
+static vector<ActVar> plain_conv3x3(const char* name, Conv2DShape shape, vector<ActVar> in, BlockVars& vars, shared_ptr<Context> ctx) {
+  NameScope scope(name);
+  shape.halo_padded_input = true;   // pad -> conv on the padded buffer, without an exchange: every rank holds all rows
+  auto pad = HaloPad2DOpF::MakeParallel(shape.pad[0], in, ctx);
+  const size_t cin = in.at(0)->shape().shape[2];
+  auto conv = parallel_conv2d<Act>(shape, pad, kaiming_init_gen<GPUArray4D<float>>(cin * shape.kernel[0] * shape.kernel[1], shape.filters), false, ctx);
+  vars.add(conv);
+  return conv.ops;
+}
+static ParallelBatchNormParamOp<Act> replicated_bottleneck(Conv2DShape shape, size_t bottleneck, size_t stride, bool proj, shared_ptr<bool> sw,
+                                                           vector<ActVar> inputs, shared_ptr<Context> ctx) {
+  BlockVars vars(inputs.size());
+  auto a0 = bn_relu("bn0", inputs.at(0)->shape().shape[2], sw, inputs, vars, ctx);
+  vector<ActVar> shortcut = inputs;
+  if (proj) shortcut = conv1x1("proj", bottleneck * shape.filters, stride, a0, vars, ctx);
+  auto c1 = conv1x1("conv1", shape.filters, 1, a0, vars, ctx);
+  auto a1 = bn_relu("bn1", shape.filters, sw, c1, vars, ctx);
+  Conv2DShape s2 = shape;
+  s2.stride = {stride, stride};
+  auto c2 = plain_conv3x3("conv2", s2, a1, vars, ctx);
+  auto a2 = bn_relu("bn2", shape.filters, sw, c2, vars, ctx);
+  auto c3 = conv1x1("conv3", bottleneck * shape.filters, 1, a2, vars, ctx);
+  return vars.finish(parallel_sum<Act>({shortcut, c3}, ctx));
+}
+
+template <>
+SpatialParallelNet SpatialParallelResNet<float>::MakeParallelResNet50(const ConvNetConfig& cfg, size_t classes, shared_ptr<Context> ctx) {
+  vector<ActVar> strips;
+  SpatialParallelNet net = begin_net(cfg, ctx, strips, true);
+  auto sw = net.batch_norm_use_fixed;
+  const size_t R = ranks_of(ctx);
+  vector<ActVar> cur = stem(net, cfg, 64, strips, ctx);
+  const size_t blocks[4] = {3, 4, 6, 3}, strides[4] = {1, 2, 2, 2};
+  bool gathered = R == 1;
+  for (int st = 0; st < 4; ++st) {
+    Conv2DShape b;
+    b.filters = (size_t)64 << st; b.kernel = {3, 3}; b.pad = {1, 1};
+    if (!gathered && strides[st] == 2 && (cur.at(0)->shape().shape[1] % 2)) {
+      cur = SpatialAllGather2DOpF::MakeParallel(cur, ctx);   // an odd strip cannot be strided: go on replicated
+      gathered = true;
+    }
+    for (size_t i = 0; i < blocks[st]; ++i) {
+      NameScope scope("stage" + std::to_string(st + 1) + ".block" + std::to_string(i + 1));
+      ParallelBatchNormParamOp<Act> blk;
+      if (gathered && R > 1) blk = replicated_bottleneck(b, 4, i == 0 ? strides[st] : 1, i == 0, sw, cur, ctx);
+      else blk = i == 0 ? spatial_parallel_proj_bottleneck_residual_v2_conv2d<Act>(b, 4, strides[st], sw, cur, ctx)
+                        : spatial_parallel_bottleneck_residual_v2_conv2d<Act>(b, 4, sw, cur, ctx);
+      absorb(net, blk.ops, blk.params, blk.grads, &blk.batch_stats, &blk.fixed_stats);
+      cur = blk.ops;
+    }
+  }
+  ParallelBatchNormParamOp<Act> bnf;
+  { NameScope scope("bn_final"); bnf = parallel_batch_norm<Act>(2048, sw, cur, true, ctx); }
+  absorb(net, bnf.ops, bnf.params, bnf.grads, &bnf.batch_stats, &bnf.fixed_stats);
+  auto full = (gathered && R > 1) ? bnf.ops : SpatialAllGather2DOpF::MakeParallel(bnf.ops, ctx);
+  Pool2DShape gp;
+  gp.pooling = kAveragePool;
+  gp.window = {full.at(0)->shape().shape[0], full.at(0)->shape().shape[1]};
+  gp.stride = gp.window;
+  auto pooled = CudnnPool2DOpF::MakeParallel(gp, full, ctx);
+  ParallelParamOp<Act> fc;
+  { NameScope scope("fc1"); fc = parallel_linear<Act>(classes, pooled, xavier_init_gen<GPUArray4D<float>>(2048, classes), ctx); }
+  absorb(net, fc.ops, fc.params, fc.grads);
+  net.losses = CudnnSoftmaxNLLLoss2DOpF::MakeParallel(fc.ops, ctx);
+  for (auto& l : net.losses) l->set_loss_weight(1.0f / (float)(cfg.batch_size * R));
+  net.outputs = fc.ops;
+  vector<shared_ptr<Op>> members(net.losses.begin(), net.losses.end());
+  net.sink = make_shared<GroupSinkOp>(members);
+  for (auto& o : fc.ops) net.output_grad_vars[o->rank()].insert(o->data().grad.var());
+  return net;
+}
+
 }  // namespace arraydiff

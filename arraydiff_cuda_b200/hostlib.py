@@ -46,6 +46,7 @@ def load():
         L.adh_net_forward.argtypes = [vp, vp]
         L.adh_net_step_resident.argtypes = [vp, C.c_int]
         L.adh_net_set_labels.argtypes = [vp, C.c_int, vp]
+        L.adh_net_set_loss_weight.argtypes = [vp, C.c_float]
         L.adh_net_loss.argtypes = [vp, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]
         L.adh_net_get_output_grad.argtypes = [vp, C.c_int, vp]
         L.adh_net_step_graph.argtypes = [vp, C.c_int]
@@ -77,7 +78,7 @@ class Context:
 
 
 class Net:
-    """kind: 'conv3x3', 'stem_stage1', 'segnet50' or 'segnet_small' (one block per stage; `filters` = stem width)."""
+    """kind: 'conv3x3', 'stem_stage1', 'parallel_resnet18', 'parallel_resnet50', 'segnet50' or 'segnet_small' (one block per stage; `filters` = stem width)."""
 
     def __init__(self, ctx, kind, H, W, Cin, batch=1, filters=64, seed=1):
         self.L, self.ctx = ctx.L, ctx
@@ -137,6 +138,9 @@ class Net:
         labels = np.ascontiguousarray(labels, np.uint32)
         assert labels.shape == (self.strip_shape[0],) + self.strip_shape[2:]
         assert self.L.adh_net_set_labels(self.h, rank, _p(labels)) == 0
+
+    def set_loss_weight(self, w):
+        assert self.L.adh_net_set_loss_weight(self.h, w) == 0
 
     def loss(self):
         """(sum of the per-pixel losses over the local strips, pixels behind it) of the last forward"""

@@ -302,3 +302,100 @@ class ParallelResNet18:
         dpool = np.ascontiguousarray(orc.maxpool2d_bwd(self.pool_in, g, (3, 3), (2, 2), omp=True)[:, :, 1:-1, 1:-1])
         conv_b("conv1", self.q(dpool), need_dx=False)
         return G
+
+
+class ParallelResNet50:
+    """Bottleneck ResNet classifier over R strips: stem, stages of pre-activation bottlenecks strided 1,2,2,2 (the
+    3x3 carries the stride), BN+ReLU, global average pool, linear, softmax NLL.  Batch norm normalises per strip
+    until a strided stage would meet an odd strip height; from there on the tensor is whole on every rank and
+    statistics are over all rows."""
+
+    def __init__(self, P, R, blocks=(3, 4, 6, 3), bf16=False):
+        self.P, self.R, self.blocks = P, R, blocks
+        self.q = orc.round_bf16 if bf16 else _ident
+
+    def _bn(self, name, R):
+        return BnRelu(self.P[name + ".scale"], self.P[name + ".shift"], R, self.q)
+
+    def _conv(self, name, stride=1, pad=0):
+        return Conv(self.P[name + ".kernel"], stride, pad, self.q, 1, self.P.get(name + ".bias"))
+
+    def forward(self, x, labels):
+        L = self.L = {}
+        R = self.R
+        L["stem.conv"] = self._conv("stem.conv", 2, 3)
+        L["stem.bn"] = self._bn("stem.bn", R)
+        a = L["stem.bn"].fwd(L["stem.conv"].fwd(x))
+        self.pool_in = np.zeros((a.shape[0], a.shape[1], a.shape[2] + 2, a.shape[3] + 2), np.float32)
+        self.pool_in[:, :, 1:-1, 1:-1] = a
+        t = orc.maxpool2d_fwd(self.pool_in, (3, 3), (2, 2), omp=True)
+        self.names = []
+        for st in range(4):
+            stride_st = (1, 2, 2, 2)[st]
+            if R > 1 and stride_st == 2 and (t.shape[2] // R) % 2:
+                R = 1                                   # re-assembled: the rest runs on whole tensors
+            for i in range(self.blocks[st]):
+                b = f"stage{st + 1}.block{i + 1}"
+                stride = stride_st if i == 0 else 1
+                self.names.append((b, i == 0))
+                L[b + ".bn0"] = self._bn(b + ".bn0", R)
+                a0 = L[b + ".bn0"].fwd(t)
+                L[b + ".conv1"] = self._conv(b + ".conv1")
+                L[b + ".bn1"] = self._bn(b + ".bn1", R)
+                a1 = L[b + ".bn1"].fwd(L[b + ".conv1"].fwd(a0))
+                L[b + ".conv2"] = self._conv(b + ".conv2", stride, 1)
+                L[b + ".bn2"] = self._bn(b + ".bn2", R)
+                a2 = L[b + ".bn2"].fwd(L[b + ".conv2"].fwd(a1))
+                L[b + ".conv3"] = self._conv(b + ".conv3")
+                c3 = L[b + ".conv3"].fwd(a2)
+                if i == 0:
+                    L[b + ".proj"] = self._conv(b + ".proj", stride)
+                    t = self.q(L[b + ".proj"].fwd(a0) + c3)
+                else:
+                    t = self.q(t + c3)
+        L["bn_final"] = self._bn("bn_final", R)
+        self.feat = L["bn_final"].fwd(t)
+        k = self.feat.shape[2:]
+        self.pooled = self.q(orc.avgpool2d_fwd(self.feat, k, k))
+        N = x.shape[0]
+        self.w, self.b = self.P["fc1.kernel"].reshape(-1, self.pooled.shape[1]), self.P["fc1.bias"]
+        self.logits = self.q(orc.linear_fwd(self.pooled.reshape(N, -1), self.w, self.b))
+        self.labels = np.ascontiguousarray(labels.reshape(N, 1), np.uint32)
+        loss, _, _ = orc.softmax_ce_pixel_fwd(self.logits.reshape(N, -1, 1), self.labels, omp=True)
+        return self.logits, float(loss.astype(np.float64).mean())
+
+    def backward(self):
+        L, G = self.L, {}
+
+        def bn_b(name, g):
+            dx, dg, db = L[name].bwd(g)
+            G[name + ".scale"], G[name + ".shift"] = dg, db
+            return dx
+
+        def conv_b(name, g, need_dx=True):
+            dx, dw = L[name].bwd(g, need_dx)
+            G[name + ".kernel"] = dw
+            return dx
+
+        N, K = self.logits.shape
+        dloss = np.full((N, 1), 1.0 / N, np.float32)
+        dlogits = self.q(orc.softmax_ce_pixel_bwd(self.logits.reshape(N, K, 1), self.labels, dloss, omp=True).reshape(N, K))
+        dpooled, G["fc1.kernel"], G["fc1.bias"] = orc.linear_bwd(self.pooled.reshape(N, -1), self.w, dlogits)
+        k = self.feat.shape[2:]
+        g = self.q(orc.avgpool2d_bwd(self.q(dpooled).reshape(self.pooled.shape), self.feat.shape, k, k))
+        g = bn_b("bn_final", g)
+        for b, first in reversed(self.names):
+            d = conv_b(b + ".conv3", g)
+            d = bn_b(b + ".bn2", d)
+            d = conv_b(b + ".conv2", d)
+            d = bn_b(b + ".bn1", d)
+            d = conv_b(b + ".conv1", d)
+            if first:
+                d = self.q(d + conv_b(b + ".proj", g))
+                g = bn_b(b + ".bn0", d)
+            else:
+                g = self.q(g + bn_b(b + ".bn0", d))
+        dpool = self.q(orc.maxpool2d_bwd(self.pool_in, g, (3, 3), (2, 2), omp=True)[:, :, 1:-1, 1:-1])
+        d = bn_b("stem.bn", np.ascontiguousarray(dpool))
+        conv_b("stem.conv", d, need_dx=False)
+        return G
