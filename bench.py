@@ -509,13 +509,33 @@ def segnet_flops(N, Hh, W, classes=19, blocks=(3, 4, 6, 3), base=64):
     return total
 
 
+def resnet50_flops(N, Hh, W, classes=1000):
+    """fwd + dgrad + wgrad FLOPs of the ResNet-50 classifier (stem data gradient excluded)."""
+    total = 2.0 * N * 64 * 3 * 49 * (Hh // 2) * (W // 2) * 2
+    px, cin = N * (Hh // 4) * (W // 4), 64
+    for st, nb in enumerate((3, 4, 6, 3)):
+        mid, out = 64 << st, (64 << st) * 4
+        for i in range(nb):
+            px_out = px // 4 if (st > 0 and i == 0) else px
+            f = 2.0 * px * mid * cin + 2.0 * px_out * mid * mid * 9 + 2.0 * px_out * out * mid
+            if i == 0:
+                f += 2.0 * px_out * out * cin
+            total += 3.0 * f
+            px, cin = px_out, out
+    return total + 3.0 * 2.0 * N * classes * cin
+
+
 def run_net_workload(args, kind):
     """`--workload stem_stage1`: BASELINE config 3 -- ResNet-50 stem + stage 1 on one 3x1024x1024 image,
     H-partitioned over the GPUs (or over `--strips` ranks sharing one GPU), bf16 operands, forward +
     backward against an upstream gradient N(0,1), filter-gradient allreduce and SGD update, all through
     the C++ host layer (zoo builder -> op graph -> C ABI kernels).  93.6 GFLOP per step (stem dgrad excluded).
     `--workload segnet`: BASELINE config 4 -- dilated ResNet-50 at output stride 8 on 2x3x1024x2048 with a
-    19-class head, x8 bilinear upsample and per-pixel softmax NLL against uniform random labels."""
+    19-class head, x8 bilinear upsample and per-pixel softmax NLL against uniform random labels.
+    `--workload resnet50_hybrid`: BASELINE config 5 -- ResNet-50 classifier on 224 x 224, global batch 256, the
+    GPUs in data-parallel groups of 2 H-strips each (8 GPUs: 4 data x 2 spatial; halos and the all-gather by peer
+    loads inside a group, filter gradients summed over all GPUs with NCCL).  On one GPU: one group (batch 64) as
+    2 strips sharing the device."""
     import torch
     import torch.distributed as dist
     from arraydiff_cuda_b200 import abi, hostlib
@@ -523,25 +543,33 @@ def run_net_workload(args, kind):
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
-    seg = kind == "segnet"
-    S = args.image
+    seg, hyb = kind == "segnet", kind == "resnet50_hybrid"
+    S = 224 if hyb and args.image == 1024 else args.image
     Hh, Ww, NB = (S, 2 * S, 2) if seg else (S, S, 1)
+    Sg = 2 if hyb else world                 # ranks per spatial group
+    if hyb and world > 1 and world % Sg:
+        raise SystemExit("resnet50_hybrid needs an even number of GPUs")
+    D = max(1, world // Sg) if hyb else 1    # data-parallel groups
+    srank, group = (rank % Sg, rank // Sg) if hyb else (rank, 0)
+    if hyb:
+        NB = 256 // (D if world > 1 else 4)
     L = abi.load()
     Lh = hostlib.load()
     keep = []
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-        h = Lh.adh_context_create_distributed(rank, world, local, hostlib.BF16_NHWC,
-                                              (40960 // world + 2048) if seg else 4096)
+        h = Lh.adh_context_create_distributed(srank, Sg, local, hostlib.BF16_NHWC,
+                                              24576 if hyb else (40960 // world + 2048) if seg else 4096)
         hb = C.create_string_buffer(64)
         assert Lh.adh_context_arena_handle(h, hb) == 0
         mine = torch.from_numpy(np.frombuffer(hb.raw, dtype=np.uint8).copy()).cuda()
         allh = [torch.empty_like(mine) for _ in range(world)]
         dist.all_gather(allh, mine)
-        for r in range(world):
-            if r != rank:
-                assert Lh.adh_context_set_peer_handle(h, r, bytes(allh[r].cpu().numpy().tobytes())) == 0
+        for q in range(Sg):                   # the peers of my spatial group
+            wr = group * Sg + q
+            if q != srank:
+                assert Lh.adh_context_set_peer_handle(h, q, bytes(allh[wr].cpu().numpy().tobytes())) == 0
         HOOK = C.CFUNCTYPE(None, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p)
 
         def allreduce(buf, count, stream, user):
@@ -549,7 +577,8 @@ def run_net_workload(args, kind):
             with torch.cuda.stream(torch.cuda.ExternalStream(stream)):
                 dist.all_reduce(t)
 
-        if args.nccl_allreduce:
+        if args.nccl_allreduce or D > 1:      # several data groups: the sum spans all GPUs
+            args.nccl_allreduce = True
             # filter gradients over NCCL (torch.distributed) instead of the built-in peer exchange; such a
             # step is launched eagerly
             hook = HOOK(allreduce)
@@ -559,20 +588,26 @@ def run_net_workload(args, kind):
         class Ctx:
             pass
         ctx = Ctx()
-        ctx.L, ctx.h, ctx.num_ranks = Lh, h, world
-        ranks, strips = [rank], world
+        ctx.L, ctx.h, ctx.num_ranks = Lh, h, Sg
+        ranks, strips = [srank], Sg
     else:
-        strips = max(1, args.strips)
+        strips = max(2 if hyb else 1, args.strips)
         ctx = hostlib.Context([local] * strips, hostlib.BF16_NHWC,
-                              arena_mb=max(512, int((40960 if seg else 4096) * (S / 1024.0) ** 2) // strips + 256))
+                              arena_mb=24576 if hyb else max(512, int((40960 if seg else 4096) * (S / 1024.0) ** 2) // strips + 256))
         ranks = list(range(strips))
-    net = hostlib.Net(ctx, "segnet50" if seg else "stem_stage1", Hh, Ww, 3, NB, seed=1)
+    net = hostlib.Net(ctx, "segnet50" if seg else "parallel_resnet50" if hyb else "stem_stage1", Hh, Ww, 3, NB,
+                      filters=1000 if hyb else 64, seed=1)
     net.configure_sgd(0.01, 0.9, l2=1e-4, nesterov=True)
-    rng = np.random.default_rng(7)
+    if hyb:
+        net.set_loss_weight(1.0 / (NB * D * strips))     # mean over the global batch, shared out over a group's replicas of the head
+    rng = np.random.default_rng(7 + group)
     x = rng.uniform(0, 1, (NB, 3, Hh, Ww)).astype(np.float32)
     if seg:
         labels = rng.integers(0, 19, (NB, Hh, Ww)).astype(np.uint32)
         hs = Hh // strips
+        dy = []
+    elif hyb:
+        labels = rng.integers(0, 1000, (NB, 1, 1)).astype(np.uint32)
         dy = []
     else:
         dy = [rng.standard_normal(net.strip_shape).astype(np.float32) for _ in range(strips)]
@@ -582,7 +617,7 @@ def run_net_workload(args, kind):
         return torch.from_numpy(a).pin_memory().numpy()
     x = pinned(x)
     dy = [pinned(d) for d in dy]
-    if seg:
+    if seg or hyb:
         labels = pinned(labels)
     out_host = pinned(np.empty(net.strip_shape, np.float32))
 
@@ -591,11 +626,13 @@ def run_net_workload(args, kind):
         for r in ranks:
             if seg:
                 net.set_labels(r, labels[:, r * hs:(r + 1) * hs])   # host labels -> device
+            elif hyb:
+                net.set_labels(r, labels)
             else:
                 net.set_output_grad(r, dy[r])    # host upstream gradient -> device
         net.backward()
         net.sgd_step()
-        return net.loss() if seg else net.output(ranks[0], out=out_host)          # D2H read of a result
+        return net.loss() if (seg or hyb) else net.output(ranks[0], out=out_host)          # D2H read of a result
 
     # steady-state step: the resident step replayed from a CUDA graph (flag values between processes are
     # relative to a device-resident base, the gradient allreduce is the built-in peer exchange)
@@ -647,18 +684,19 @@ def run_net_workload(args, kind):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         t_e2e = float(t.item())
     scale = (S / 1024.0) ** 2
-    flops = segnet_flops(NB, Hh, Ww) if seg else 93.6e9 * scale
+    flops = segnet_flops(NB, Hh, Ww) if seg else resnet50_flops(NB * D, Hh, Ww) if hyb else 93.6e9 * scale
     if rank == 0:
         step_s = ms / args.steps * 1e-3
         print(json.dumps({
             "metric": METRIC, "value": flops / step_s / 1e12, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "images_per_s": NB / step_s,
-            "config": {"workload": "resnet50_dilated_segnet" if seg else "resnet50_stem_stage1", "image": [NB, 3, Hh, Ww], "strips": strips, "layout": "NHWC",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "images_per_s": NB * D / step_s,
+            "config": {"workload": "resnet50_dilated_segnet" if seg else f"resnet50_hybrid_{D}x{strips}" if hyb else "resnet50_stem_stage1",
+                       "image": [NB * D, 3, Hh, Ww], "strips": strips, "data_groups": D, "layout": "NHWC",
                        "bn_statistics": "per strip (as the reference)", "update": "allreduce (%s) + Nesterov SGD" % ("nccl" if world > 1 and args.nccl_allreduce else "peer loads" if strips > 1 else "single rank"), "launch": "cuda graph" if use_graph else "eager",
-                       "l2": "activations of one step total more than 1 GB, larger than L2", "parallelism": f"spatial-h{strips}"},
-            "e2e": {"value": flops / t_e2e / 1e12, "unit": UNIT, "h2d_bytes_per_step": int(x.nbytes // world + (labels.nbytes // world if seg else sum(d.nbytes for d in dy))),
-                    "d2h_bytes_per_step": int(np.prod(net.strip_shape[2:]) * NB * 4 if seg else np.prod(net.strip_shape) * 4), "steps": k_e2e, "timing": "host clock between synchronisations"},
+                       "l2": "activations of one step total more than 1 GB, larger than L2", "parallelism": f"data{D}-spatial-h{strips}" if hyb else f"spatial-h{strips}"},
+            "e2e": {"value": flops / t_e2e / 1e12, "unit": UNIT, "h2d_bytes_per_step": int(x.nbytes // (Sg if world > 1 else 1) + (labels.nbytes if hyb else labels.nbytes // world if seg else sum(d.nbytes for d in dy))),
+                    "d2h_bytes_per_step": int(NB * 4 if hyb else np.prod(net.strip_shape[2:]) * NB * 4 if seg else np.prod(net.strip_shape) * 4), "steps": k_e2e, "timing": "host clock between synchronisations"},
             "gpu_launches": int(launches), "clocks": clocks,
         }))
     if world > 1:
@@ -674,10 +712,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
-    ap.add_argument("--workload", default="conv", choices=["conv", "halo", "stem_stage1", "segnet"],
+    ap.add_argument("--workload", default="conv", choices=["conv", "halo", "stem_stage1", "segnet", "resnet50_hybrid"],
                     help="conv: the headline spatial conv step; halo: the halo-exchange microbenchmark (config 2); "
                          "stem_stage1: ResNet-50 stem + stage 1 through the C++ op graph (config 3); "
-                         "segnet: dilated ResNet-50 segmentation net, 2x3x1024x2048 (config 4; --image = height)")
+                         "segnet: dilated ResNet-50 segmentation net, 2x3x1024x2048 (config 4; --image = height); "
+                         "resnet50_hybrid: ResNet-50 classifier, 224 x 224, batch 256, data-parallel groups of 2 strips (config 5)")
     ap.add_argument("--strips", type=int, default=1, help="stem_stage1 on one GPU: ranks sharing the device")
     ap.add_argument("--image", type=int, default=1024, help="stem_stage1: image height = width")
     ap.add_argument("--nccl-allreduce", action="store_true",
@@ -694,7 +733,7 @@ def main():
     if args.workload == "halo":
         run_halo_workload(args)
         return
-    if args.workload in ("stem_stage1", "segnet"):
+    if args.workload in ("stem_stage1", "segnet", "resnet50_hybrid"):
         run_net_workload(args, args.workload)
         return
 
