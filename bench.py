@@ -353,7 +353,7 @@ def kernel_times(torch, step, iters=10):
 
 # ----------------------------------------------------------------------------- halo microbenchmark
 def run_halo_workload(args):
-    """`--workload halo`: BASELINE config 2 -- NCHW tensors N=8, C=256, 224x224 cut into H-strips, halo
+    """`--workload halo`: benchmark config 2 -- NCHW tensors N=8, C=256, 224x224 cut into H-strips, halo
     1 and 3, fp32 and bf16; forward exchange and backward accumulate.  On one GPU the R strips share the
     device and move in ONE launch (HBM-bound: payload read + written); on N GPUs each rank pushes to /
     pulls from its neighbours over NVLink, with NCCL send/recv of packed faces timed beside it."""
@@ -526,13 +526,13 @@ def resnet50_flops(N, Hh, W, classes=1000):
 
 
 def run_net_workload(args, kind):
-    """`--workload stem_stage1`: BASELINE config 3 -- ResNet-50 stem + stage 1 on one 3x1024x1024 image,
+    """`--workload stem_stage1`: benchmark config 3 -- ResNet-50 stem + stage 1 on one 3x1024x1024 image,
     H-partitioned over the GPUs (or over `--strips` ranks sharing one GPU), bf16 operands, forward +
     backward against an upstream gradient N(0,1), filter-gradient allreduce and SGD update, all through
     the C++ host layer (zoo builder -> op graph -> C ABI kernels).  93.6 GFLOP per step (stem dgrad excluded).
-    `--workload segnet`: BASELINE config 4 -- dilated ResNet-50 at output stride 8 on 2x3x1024x2048 with a
+    `--workload segnet`: benchmark config 4 -- dilated ResNet-50 at output stride 8 on 2x3x1024x2048 with a
     19-class head, x8 bilinear upsample and per-pixel softmax NLL against uniform random labels.
-    `--workload resnet50_hybrid`: BASELINE config 5 -- ResNet-50 classifier on 224 x 224, global batch 256, the
+    `--workload resnet50_hybrid`: benchmark config 5 -- ResNet-50 classifier on 224 x 224, global batch 256, the
     GPUs in data-parallel groups of 2 H-strips each (8 GPUs: 4 data x 2 spatial; halos and the all-gather by peer
     loads inside a group, filter gradients summed over all GPUs with NCCL).  On one GPU: one group (batch 64) as
     2 strips sharing the device."""

@@ -586,7 +586,7 @@ static void bilin_src(int o, int scale, int in_size, int* i0, int* i1, double* f
 }
 
 /* Bilinear x`scale` upsample of [planes][H][W] (not present in the reference; used by
- * the segmentation head that BASELINE's 1024x2048 configuration names). */
+ * the segmentation head of the 1024x2048 benchmark configuration). */
 void orc_upsample_bilinear_fwd(const float* x, float* y, int planes, int H, int W, int scale) {
   int OH = H * scale, OW = W * scale;
   ORC_PAR

@@ -33,7 +33,7 @@ F32_CASES = [
     (1, 2, 12, 12, 3, 3, 1, 2, 2),
     (1, 3, 37, 41, 8, 7, 2, 1, 3),
     (2, 5, 6, 7, 6, 1, 1, 1, 0),
-    (1, 64, 34, 66, 64, 3, 1, 1, 0),   # one halo-padded strip of BASELINE config 1 (h=32, p=1)
+    (1, 64, 34, 66, 64, 3, 1, 1, 0),   # one halo-padded strip of benchmark config 1 (h=32, p=1)
 ]
 
 

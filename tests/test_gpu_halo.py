@@ -184,7 +184,7 @@ def test_slice_rejects_windows_outside_the_tensors():
 
 
 def test_config2_full_size_exchange_and_reduce():
-    """BASELINE config 2 at full size: N=8, C=256, 224x224, R in {2,4,8}, p in {1,3}, fp32 and bf16.
+    """benchmark config 2 at full size: N=8, C=256, 224x224, R in {2,4,8}, p in {1,3}, fp32 and bf16.
     Checked through a size-independent property: after the exchange each strip equals the window of
     the zero-padded full tensor (compared on the device), and reduce is the overlap-add."""
     import torch

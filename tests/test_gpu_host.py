@@ -22,7 +22,7 @@ def _unflatten(net, flat):
 @pytest.mark.parametrize("R", [1, 2, 4])
 @pytest.mark.parametrize("mode", ["f32", "bf16"])
 def test_config1_partitioned_conv3x3_forward_backward_update(R, mode):
-    """BASELINE config 1: 3x3 conv, stride 1, pad 1, N=1, C=K=64, 64x64, H-strips with 1-row halos:
+    """benchmark config 1: 3x3 conv, stride 1, pad 1, N=1, C=K=64, 64x64, H-strips with 1-row halos:
     fwd + data-grad + weight-grad against the unsplit conv, then one SGD step on the summed gradient."""
     from arraydiff_cuda_b200 import hostlib
     N, Cc, K, Hh, W = 1, 64, 64, 64, 64
@@ -76,7 +76,7 @@ def test_config1_partitioned_conv3x3_forward_backward_update(R, mode):
 
 @pytest.mark.parametrize("R,mode", [(1, "f32"), (2, "f32"), (4, "f32"), (2, "bf16")])
 def test_stem_stage1_matches_oracle(R, mode):
-    """ResNet-50 stem + stage 1 (BASELINE config 3 at a reduced image size) through the op graph:
+    """ResNet-50 stem + stage 1 (benchmark config 3 at a reduced image size) through the op graph:
     output, every parameter gradient (summed over ranks) vs the CPU composition of oracle ops."""
     from arraydiff_cuda_b200 import hostlib
     N, Cc, Hh, W = 1, 3, 64, 64

@@ -41,7 +41,7 @@ def test_reference_halo_kernels_match_oracle(ref, R, geom):
 
 @pytest.mark.parametrize("R,p", [(2, 1), (4, 3)])
 def test_speed_against_reference_halo_kernels(ref, R, p):
-    """Same GPU, same tensors (BASELINE config 2, fp32): this library's exchange against the reference's
+    """Same GPU, same tensors (benchmark config 2, fp32): this library's exchange against the reference's
     own kernel, one launch per rank as the reference does.  Prints both.  The small case (3.5 MiB) sits on
     the launch floor of both; on the larger one ours must be at least 2x faster."""
     import torch

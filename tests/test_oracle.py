@@ -193,7 +193,7 @@ def test_sgd_step_nesterov_and_plain():
 
 @pytest.mark.parametrize("R", [2, 4])
 def test_config1_partitioned_conv_equals_unpartitioned(R):
-    """BASELINE config 1: 3x3 conv, stride 1, pad 1, fp32, N=1, C=K=64, 64x64, split into H-strips
+    """benchmark config 1: 3x3 conv, stride 1, pad 1, fp32, N=1, C=K=64, 64x64, split into H-strips
     with 1-row halos exchanged in host memory; fwd + dgrad + wgrad vs the unsplit conv."""
     N, Cc, K, Hh, W, p = 1, 64, 64, 64, 64, 1
     x = H.uniform(100, (N, Cc, Hh, W))
