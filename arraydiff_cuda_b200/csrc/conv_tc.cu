@@ -23,6 +23,8 @@
 // their loops, tensor memory is freed and AD_ERR_TIMEOUT is written to a status word.
 // No TMA load here uses cluster multicast.
 #include "common.cuh"
+#include <algorithm>
+
 #include "tc_common.cuh"
 
 #include <cstdlib>
@@ -544,30 +546,38 @@ __global__ void __launch_bounds__(256) pad_channels_kernel(size_t pixels, uint32
   }
 }
 
-// db[k] (+)= sum over pixels of dy[pixel][k]   (NHWC bf16 view with row / image pitches).
-__global__ void __launch_bounds__(256) bias_grad_nhwc_kernel(uint32_t NI, uint32_t OP, uint32_t OQ, uint32_t K,
-                                                             long long pitch, long long plane,
-                                                             const __nv_bfloat16* __restrict__ dy, float* db,
-                                                             int accumulate) {
-  // block = 32 channels x 8 pixel lanes; one block per channel group (bias gradients are tiny).
-  const uint32_t k = blockIdx.x * 32 + threadIdx.x;
+// db[k] (+)= sum over pixels of dy[pixel][k] (dense NHWC bf16), in two fixed-order stages: block (channel group,
+// split) sums its share of the pixels into part[split][k], bias_grad_finish adds the splits in order.
+__global__ void __launch_bounds__(256) bias_grad_nhwc_kernel(size_t pixels, uint32_t K, const __nv_bfloat16* __restrict__ dy,
+                                                             float* part) {
+  const uint32_t k = blockIdx.x * 32 + threadIdx.x, split = blockIdx.y, nsplit = gridDim.y;
+  const size_t chunk = (pixels + nsplit - 1) / nsplit, lo = (size_t)split * chunk, hi = lo + chunk < pixels ? lo + chunk : pixels;
   float acc = 0.f;
-  const size_t per = (size_t)NI * OP * OQ;
   if (k < K)
-    for (size_t i = threadIdx.y; i < per; i += 8) {
-      uint32_t x = (uint32_t)(i % OQ);
-      size_t rr = i / OQ;
-      uint32_t y = (uint32_t)(rr % OP), n = (uint32_t)(rr / OP);
-      acc += __bfloat162float(dy[(long long)n * plane + (long long)y * pitch + (long long)x * K + k]);
-    }
+    for (size_t i = lo + threadIdx.y; i < hi; i += 8) acc += __bfloat162float(dy[i * K + k]);
   __shared__ float red[8][33];
   red[threadIdx.y][threadIdx.x] = acc;
   __syncthreads();
   if (threadIdx.y == 0 && k < K) {
     float t = 0.f;
     for (int w = 0; w < 8; ++w) t += red[w][threadIdx.x];
-    db[k] = accumulate ? db[k] + t : t;
+    part[(size_t)split * K + k] = t;
   }
+}
+__global__ void bias_grad_finish(uint32_t K, uint32_t nsplit, const float* __restrict__ part, float* db, int accumulate) {
+  const uint32_t k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= K) return;
+  float t = 0.f;
+  for (uint32_t s = 0; s < nsplit; ++s) t += part[(size_t)s * K + k];
+  db[k] = accumulate ? db[k] + t : t;
+}
+// `part`: scratch of at least 64 * K floats (the filter-gradient partials, free again once they are reduced)
+static void launch_bias_grad(size_t pixels, uint32_t K, const void* dy, float* db, int accumulate, float* part, cudaStream_t s) {
+  const uint32_t nsplit = (uint32_t)std::min<size_t>(64, std::max<size_t>(1, pixels / 512));
+  dim3 grid((K + 31) / 32, nsplit), block(32, 8);
+  bias_grad_nhwc_kernel<<<grid, block, 0, s>>>(pixels, K, (const __nv_bfloat16*)dy, part);
+  bias_grad_finish<<<(K + 127) / 128, 128, 0, s>>>(K, nsplit, part, db, accumulate);
+  count_launch(2);
 }
 
 // ---------------------------------------------------------------- host side
@@ -867,13 +877,7 @@ int conv_tc_wgrad(const ad_conv2d_args* a, cudaStream_t s) {
     st = conv_tc_row_wgrad(a->x, a->N, a->H, a->W, a->C, a->y, a->K, a->kh, a->kw, a->stride_h, a->stride_w, a->dil_h,
                            a->dil_w, -(int)a->pad_h, -(int)a->pad_w, g.P, g.Q, (float*)a->dw, a->accumulate,
                            part_base, part_bytes, (int32_t*)a->scratch, s);
-    if (st == AD_OK && a->db) {
-      dim3 block(32, 8);
-      bias_grad_nhwc_kernel<<<(a->K + 31) / 32, block, 0, s>>>(a->N, g.P, g.Q, a->K, (long long)g.Q * a->K,
-                                                               (long long)g.P * g.Q * a->K, (const __nv_bfloat16*)a->y,
-                                                               a->db, a->accumulate);
-      count_launch();
-    }
+    if (st == AD_OK && a->db) launch_bias_grad((size_t)a->N * g.P * g.Q, a->K, a->y, a->db, a->accumulate, (float*)part_base, s);
     if (st != AD_ERR_UNSUPPORTED) return st;
   }
   WgParams p{};
@@ -920,13 +924,7 @@ int conv_tc_wgrad(const ad_conv2d_args* a, cudaStream_t s) {
   if (st != AD_OK) return st;
   wgrad_reduce_kernel<<<(unsigned)((wcount + 63) / 64), 256, 0, s>>>(wcount, wcount_p, p.splits, p.partial, (float*)a->dw, a->accumulate);
   count_launch();
-  if (a->db) {
-    dim3 block(32, 8);
-    bias_grad_nhwc_kernel<<<(a->K + 31) / 32, block, 0, s>>>(a->N, g.P, g.Q, a->K, (long long)g.Q * a->K,
-                                                             (long long)g.P * g.Q * a->K, (const __nv_bfloat16*)a->y,
-                                                             a->db, a->accumulate);
-    count_launch();
-  }
+  if (a->db) launch_bias_grad((size_t)a->N * g.P * g.Q, a->K, a->y, a->db, a->accumulate, p.partial, s);
   return launch_status();
 }
 

@@ -99,6 +99,44 @@ __global__ void __launch_bounds__(256) ce_nhwc(uint32_t C, size_t pixels, const 
   }
 }
 
+// Few classes (C <= 32, e.g. 19): a block stages 256 consecutive pixels in shared memory with coalesced loads,
+// a thread then owns one pixel (class stride C floats: conflict-free for odd C), results leave coalesced again.
+template <typename T, bool BWD>
+__global__ void __launch_bounds__(256) ce_nhwc_small(uint32_t C, size_t pixels, const T* __restrict__ x,
+                                                      const uint32_t* __restrict__ label, float* loss,
+                                                      unsigned long long* picked, const float* __restrict__ dloss, T* dx,
+                                                      int accumulate) {
+  extern __shared__ float ce_sm[];   // [256][C]
+  for (size_t p0 = (size_t)blockIdx.x * 256; p0 < pixels; p0 += (size_t)gridDim.x * 256) {
+    const uint32_t np = pixels - p0 < 256 ? (uint32_t)(pixels - p0) : 256u, ne = np * C;
+    const T* xb = x + p0 * C;
+    for (uint32_t e = threadIdx.x; e < ne; e += 256) ce_sm[e] = ld_f(xb + e);
+    __syncthreads();
+    if (threadIdx.x < np) {
+      float* px = ce_sm + threadIdx.x * C;
+      const size_t i = p0 + threadIdx.x;
+      float m = -INFINITY;
+      for (uint32_t c = 0; c < C; ++c) m = fmaxf(m, px[c]);
+      float z = 0.f;
+      for (uint32_t c = 0; c < C; ++c) z += expf(px[c] - m);
+      const uint32_t l = label[i];
+      if (!BWD) {
+        loss[i] = (logf(z) + m) - px[l];
+        if (picked) picked[i] = i * C + l;
+      } else {
+        const float rz = 1.f / z, d = dloss[i];
+        for (uint32_t c = 0; c < C; ++c) px[c] = d * (expf(px[c] - m) * rz - (c == l ? 1.f : 0.f));
+      }
+    }
+    if (BWD) {
+      __syncthreads();
+      T* db = dx + p0 * C;
+      for (uint32_t e = threadIdx.x; e < ne; e += 256) st_f(db + e, accumulate ? ce_sm[e] + ld_f(db + e) : ce_sm[e]);
+    }
+    __syncthreads();
+  }
+}
+
 }  // namespace adk
 
 using namespace adk;
@@ -132,6 +170,10 @@ extern "C" int ad_softmax_ce_pixel_fwd(int32_t dtype, int32_t layout, uint32_t N
   if (layout == AD_NCHW) {
     AD_DISPATCH_DTYPE(dtype, (ce_fwd_nchw<T><<<grid_for(pixels, 256), 256, 0, s>>>(
                                  N, C, HW, (const T*)logits, label, loss, (unsigned long long*)picked)));
+  } else if (layout == AD_NHWC && C <= 32) {
+    AD_DISPATCH_DTYPE(dtype, (ce_nhwc_small<T, false><<<grid_for(pixels, 256, 16), 256, 256 * C * sizeof(float), s>>>(
+                                 C, pixels, (const T*)logits, label, loss, (unsigned long long*)picked, nullptr,
+                                 nullptr, 0)));
   } else if (layout == AD_NHWC) {
     AD_DISPATCH_DTYPE(dtype, (ce_nhwc<T, false><<<grid_for(pixels, 8), 256, 0, s>>>(
                                  C, pixels, (const T*)logits, label, loss, (unsigned long long*)picked, nullptr,
@@ -153,6 +195,10 @@ extern "C" int ad_softmax_ce_pixel_bwd(int32_t dtype, int32_t layout, uint32_t N
   if (layout == AD_NCHW) {
     AD_DISPATCH_DTYPE(dtype, (ce_bwd_nchw<T><<<grid_for(pixels, 256), 256, 0, s>>>(
                                  N, C, HW, (const T*)logits, label, dloss, (T*)dlogits, accumulate)));
+  } else if (layout == AD_NHWC && C <= 32) {
+    AD_DISPATCH_DTYPE(dtype, (ce_nhwc_small<T, true><<<grid_for(pixels, 256, 16), 256, 256 * C * sizeof(float), s>>>(
+                                 C, pixels, (const T*)logits, label, nullptr, nullptr, dloss, (T*)dlogits,
+                                 accumulate)));
   } else if (layout == AD_NHWC) {
     AD_DISPATCH_DTYPE(dtype, (ce_nhwc<T, true><<<grid_for(pixels, 8), 256, 0, s>>>(
                                  C, pixels, (const T*)logits, label, nullptr, nullptr, dloss, (T*)dlogits,

@@ -95,6 +95,81 @@ __global__ void __launch_bounds__(256) upsample_bwd_kernel(UpP p) {
   }
 }
 
+// Channel-fastest views: one thread per PIXEL computes the source cells and weights once and walks the channels
+// (adjacent threads own adjacent pixels, so a warp's accesses cover runs of whole pixels).
+template <typename T>
+__global__ void __launch_bounds__(256) upsample_fwd_px_kernel(UpP p) {
+  const uint32_t total = p.N * p.YH * p.YW, nt = gridDim.x * blockDim.x;
+  const float inv = 1.0f / (float)p.scale;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nt) {
+    const uint32_t ox = i % p.YW, r = i / p.YW, oy = r % p.YH, n = r / p.YH;
+    int y0, y1, x0, x1;
+    float fy, fx;
+    bilin_src(p.y_row0 + oy, inv, p.in_rows_total, y0, y1, fy);
+    bilin_src(ox, inv, p.XW, x0, x1, fx);
+    y0 -= p.x_row0; y1 -= p.x_row0;
+    const T* X = (const T*)p.x.base + n * p.x.sn;
+    const T *pa = X + y0 * p.x.sy + x0 * p.x.sx, *pb = X + y0 * p.x.sy + x1 * p.x.sx;
+    const T *pd = X + y1 * p.x.sy + x0 * p.x.sx, *pe = X + y1 * p.x.sy + x1 * p.x.sx;
+    T* o = (T*)p.y.base + n * p.y.sn + oy * p.y.sy + ox * p.y.sx;
+    for (uint32_t c = 0; c < p.C; ++c) {
+      const float v = (1.f - fy) * ((1.f - fx) * ld_f(pa + c) + fx * ld_f(pb + c)) + fy * ((1.f - fx) * ld_f(pd + c) + fx * ld_f(pe + c));
+      st_f(o + c, v);
+    }
+  }
+}
+// Gradient, channel-fastest: one thread per low-resolution pixel and group of up to 8 channels; the weights
+// of a candidate are computed once for the group.  Same candidates and order as the element form.
+template <typename T>
+__global__ void __launch_bounds__(256) upsample_bwd_px_kernel(UpP p) {
+  const uint32_t G = (p.C + 7) / 8, total = p.N * p.XH * p.XW * G, nt = gridDim.x * blockDim.x;
+  const float inv = 1.0f / (float)p.scale;
+  const int s = (int)p.scale;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += nt) {
+    const uint32_t cg = i % G;
+    uint32_t r = i / G;
+    const uint32_t xl = r % p.XW; r /= p.XW;
+    const uint32_t yl = r % p.XH, n = r / p.XH;
+    const uint32_t c0 = cg * 8, nc = p.C - c0 < 8 ? p.C - c0 : 8;
+    const int yg = (int)yl + p.x_row0, xg = (int)xl;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    if (yg >= 0 && yg < (int)p.in_rows_total) {
+      int oy_lo = yg == 0 ? 0 : (yg - 1) * s, oy_hi = yg == (int)p.in_rows_total - 1 ? (int)p.in_rows_total * s - 1 : (yg + 2) * s - 1;
+      int ox_lo = xg == 0 ? 0 : (xg - 1) * s, ox_hi = xg == (int)p.XW - 1 ? (int)p.XW * s - 1 : (xg + 2) * s - 1;
+      if (oy_lo < (int)p.y_row0) oy_lo = (int)p.y_row0;
+      if (oy_hi > (int)(p.y_row0 + p.YH) - 1) oy_hi = (int)(p.y_row0 + p.YH) - 1;
+      const T* Gp = (const T*)p.y.base + n * p.y.sn + c0;
+      for (int oy = oy_lo; oy <= oy_hi; ++oy) {
+        int y0, y1;
+        float fy;
+        bilin_src((uint32_t)oy, inv, p.in_rows_total, y0, y1, fy);
+        const float wy = (y0 == yg ? 1.f - fy : 0.f) + (y1 == yg ? fy : 0.f);
+        if (wy == 0.f) continue;
+        float row[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) row[j] = 0.f;
+        for (int ox = ox_lo; ox <= ox_hi; ++ox) {
+          int x0, x1;
+          float fx;
+          bilin_src((uint32_t)ox, inv, p.XW, x0, x1, fx);
+          const float wx = (x0 == xg ? 1.f - fx : 0.f) + (x1 == xg ? fx : 0.f);
+          if (wx == 0.f) continue;
+          const T* gp = Gp + (oy - (int)p.y_row0) * p.y.sy + ox * p.y.sx;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if ((uint32_t)j < nc) row[j] = fmaf(wx, ld_f(gp + j), row[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = fmaf(wy, row[j], acc[j]);
+      }
+    }
+    T* o = (T*)p.x.base + n * p.x.sn + yl * p.x.sy + xl * p.x.sx + c0;
+    for (uint32_t j = 0; j < nc; ++j) st_f(o + j, p.accumulate ? ld_f(o + j) + acc[j] : acc[j]);
+  }
+}
+
 static int up_params(const ad_tensor4* lo, const ad_tensor4* hi, uint32_t scale, int32_t x_row0, uint32_t in_rows_total,
                      uint32_t y_row0, UpP& p) {
   if (!lo || !hi || !lo->base || !hi->base || scale == 0 || in_rows_total == 0) return AD_ERR_BAD_ARG;
@@ -134,7 +209,10 @@ extern "C" int ad_upsample_bilinear_fwd(const ad_tensor4* x, const ad_tensor4* y
   const size_t total = (size_t)p.N * p.C * p.YH * p.YW;
   if (total == 0) return AD_OK;
   p.c_fastest = y->sc == 1 && y->C > 1;
-  AD_DISPATCH_DTYPE(x->dtype, (upsample_fwd_kernel<T><<<grid_for(total, 256, 16), 256, 0, as_stream(stream)>>>(p)));
+  if (p.c_fastest && x->sc == 1)
+    AD_DISPATCH_DTYPE(x->dtype, (upsample_fwd_px_kernel<T><<<grid_for(total / p.C, 256, 16), 256, 0, as_stream(stream)>>>(p)));
+  else
+    AD_DISPATCH_DTYPE(x->dtype, (upsample_fwd_kernel<T><<<grid_for(total, 256, 16), 256, 0, as_stream(stream)>>>(p)));
   count_launch();
   return launch_status();
 }
@@ -148,7 +226,10 @@ extern "C" int ad_upsample_bilinear_bwd(const ad_tensor4* dy, const ad_tensor4* 
   if (total == 0) return AD_OK;
   p.c_fastest = dx->sc == 1 && dx->C > 1;
   p.accumulate = accumulate;
-  AD_DISPATCH_DTYPE(dx->dtype, (upsample_bwd_kernel<T><<<grid_for(total, 256, 16), 256, 0, as_stream(stream)>>>(p)));
+  if (p.c_fastest && dy->sc == 1)
+    AD_DISPATCH_DTYPE(dx->dtype, (upsample_bwd_px_kernel<T><<<grid_for(total / p.C * ((p.C + 7) / 8), 256, 16), 256, 0, as_stream(stream)>>>(p)));
+  else
+    AD_DISPATCH_DTYPE(dx->dtype, (upsample_bwd_kernel<T><<<grid_for(total, 256, 16), 256, 0, as_stream(stream)>>>(p)));
   count_launch();
   return launch_status();
 }
