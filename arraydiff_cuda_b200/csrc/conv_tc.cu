@@ -82,6 +82,7 @@ struct FwdParams {
   uint32_t kh, kw, sh, sw, dh, dw;
   int32_t offy, offx;       // input row = oy*sh + r*dh + offy
   uint32_t TH, TW, tiles_y, tiles_x, tiles_n;
+  uint32_t TN, tiles_b;     // a tile spans TN images of TH x TW pixels (small maps); tiles_b = ceil(NI / TN)
   long long out_pitch, out_plane;  // elements between output rows / images
   __nv_bfloat16* out;
   const float* bias;
@@ -114,7 +115,7 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   uint8_t* osm = smem + (size_t)STAGES * kStageBytes;
   SmemCtl* ctl = (SmemCtl*)(osm + kStagingBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t tiles_m = p.NI * p.tiles_y * p.tiles_x;
+  const uint32_t tiles_m = p.tiles_b * p.tiles_y * p.tiles_x;
   const uint32_t total_tiles = tiles_m * p.tiles_n;
   const uint32_t slabs = p.CK / 64;
   const uint32_t kiters = p.kh * p.kw * slabs;
@@ -153,7 +154,7 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       uint32_t stage = 0, phase = 0;
       for (uint32_t tile = blockIdx.x; tile < total_tiles && !*abortf; tile += gridDim.x) {
         const uint32_t tn = tile / tiles_m, tm = tile % tiles_m;
-        const uint32_t tx = tm % p.tiles_x, ty = (tm / p.tiles_x) % p.tiles_y, n = tm / (p.tiles_x * p.tiles_y);
+        const uint32_t tx = tm % p.tiles_x, ty = (tm / p.tiles_x) % p.tiles_y, n = tm / (p.tiles_x * p.tiles_y) * p.TN;
         const int x0 = (int)(tx * p.TW * p.sw) + p.offx, y0 = (int)(ty * p.TH * p.sh) + p.offy;
         bool ok = true;
         for (uint32_t r = 0; r < p.kh && ok; ++r)
@@ -203,7 +204,7 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     for (uint32_t tile = blockIdx.x; tile < total_tiles && !*abortf; tile += gridDim.x, ++it) {
       const uint32_t acc = it & 1u, acc_phase = (it >> 1) & 1u;
       const uint32_t tn = tile / tiles_m, tm = tile % tiles_m;
-      const uint32_t tx = tm % p.tiles_x, ty = (tm / p.tiles_x) % p.tiles_y, n = tm / (p.tiles_x * p.tiles_y);
+      const uint32_t tx = tm % p.tiles_x, ty = (tm / p.tiles_x) % p.tiles_y, n = tm / (p.tiles_x * p.tiles_y) * p.TN;
       const uint32_t m = q * 32 + lane;
       if (BN >= 64 && p.tma_store) {
         // 64-channel chunks of the tile go through a swizzled [128 px][64 ch] staging buffer and one TMA
@@ -274,9 +275,10 @@ conv_tc_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       if (grp != 0) continue;   // the scattered-store form is served by the first group alone
       if (!mbar_wait(smem_u32(&ctl->tfull[acc]), acc_phase, abortf)) break;
       tc_fence_after();
-      const uint32_t oy = ty * p.TH + m / p.TW, ox = tx * p.TW + m % p.TW;
-      const bool valid = oy < p.OP && ox < p.OQ;
-      __nv_bfloat16* orow = p.out + (long long)n * p.out_plane + (long long)oy * p.out_pitch + (long long)ox * p.OC;
+      const uint32_t mi = m / (p.TW * p.TH), mr = m - mi * (p.TW * p.TH);   // image inside the tile, pixel inside the image
+      const uint32_t oy = ty * p.TH + mr / p.TW, ox = tx * p.TW + mr % p.TW, on = n + mi;
+      const bool valid = oy < p.OP && ox < p.OQ && on < p.NI;
+      __nv_bfloat16* orow = p.out + (long long)on * p.out_plane + (long long)oy * p.out_pitch + (long long)ox * p.OC;
 #pragma unroll 1
       for (uint32_t ch = 0; ch < BN / 32; ++ch) {
         uint32_t v[32];
@@ -353,6 +355,7 @@ struct WgParams {
   uint32_t kh, kw, sh, sw, dh, dw;
   int32_t offy, offx;
   uint32_t TH, TW, tiles_y, tiles_x;
+  uint32_t TN, tiles_b;  // a tile spans TN images (small maps); tiles_b = ceil(NI / TN)
   uint32_t ktiles, ctiles, splits;
   float* partial;       // [splits][KO][kh*kw][CI]
   int32_t* status;
@@ -375,7 +378,7 @@ conv_tc_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_co
   const uint32_t ct = rem % p.ctiles; rem /= p.ctiles;
   const uint32_t kt = rem % p.ktiles; rem /= p.ktiles;
   const uint32_t tap = rem, r = tap / p.kw, s = tap % p.kw;
-  const uint32_t sp_tiles = p.NI * p.tiles_y * p.tiles_x;
+  const uint32_t sp_tiles = p.tiles_b * p.tiles_y * p.tiles_x;
   const uint32_t my_tiles = split < sp_tiles ? (sp_tiles - split + p.splits - 1) / p.splits : 0;
 
   if (threadIdx.x == 0) {
@@ -404,7 +407,7 @@ conv_tc_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_co
       uint32_t stage = 0, phase = 0;
       for (uint32_t j = 0; j < my_tiles; ++j) {
         const uint32_t tm = split + j * p.splits;
-        const uint32_t tx = tm % p.tiles_x, ty = (tm / p.tiles_x) % p.tiles_y, n = tm / (p.tiles_x * p.tiles_y);
+        const uint32_t tx = tm % p.tiles_x, ty = (tm / p.tiles_x) % p.tiles_y, n = tm / (p.tiles_x * p.tiles_y) * p.TN;
         if (!mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1u, abortf)) break;
         const uint32_t full = smem_u32(&ctl->full[stage]);
         uint8_t* st = smem + (size_t)stage * kStageBytes;
@@ -596,16 +599,19 @@ static int conv_geo(const ad_conv2d_args* a, Geo& g) {
   return AD_OK;
 }
 
-// Spatial patch of 128 output pixels wasting the fewest lanes on partial tiles.
-static void pick_tile(uint32_t OP, uint32_t OQ, uint32_t sh, uint32_t sw, uint32_t& TH, uint32_t& TW) {
+// Patch of 128 output pixels (TN images x TH rows x TW columns) wasting the fewest lanes on partial tiles: large
+// maps get one image per tile, small feature maps (7 x 7, 14 x 14) several, which otherwise leave most of a
+// 128-pixel tile empty.
+static void pick_tile3(uint32_t NI, uint32_t OP, uint32_t OQ, uint32_t sh, uint32_t sw, uint32_t& TN, uint32_t& TH, uint32_t& TW) {
   unsigned long long best = ~0ull;
-  TH = 1; TW = 128;
-  for (uint32_t tw = 128; tw >= 8; tw >>= 1) {
-    const uint32_t th = 128 / tw;
-    if (tw * sw > 256 || th * sh > 256) continue;
-    const unsigned long long cost = (unsigned long long)((OQ + tw - 1) / tw * tw) * ((OP + th - 1) / th * th);
-    if (cost < best) { best = cost; TH = th; TW = tw; }
-  }
+  TN = 1; TH = 1; TW = 128;
+  for (uint32_t tn = 1; tn <= 16; tn <<= 1)
+    for (uint32_t tw = 128 / tn; tw >= 8; tw >>= 1) {
+      const uint32_t th = 128 / tn / tw;
+      if (th == 0 || tw * sw > 256 || th * sh > 256) continue;
+      const unsigned long long cost = (unsigned long long)((OQ + tw - 1) / tw * tw) * ((OP + th - 1) / th * th) * ((NI + tn - 1) / tn * tn);
+      if (cost < best) { best = cost; TN = tn; TH = th; TW = tw; }
+    }
 }
 
 template <int BN>
@@ -624,7 +630,7 @@ static int launch_fwd(const CUtensorMap& ma, const CUtensorMap& mb, const CUtens
     }
     attr_done |= 1u << (dev & 31);
   }
-  const uint32_t total = p.NI * p.tiles_y * p.tiles_x * p.tiles_n;
+  const uint32_t total = p.tiles_b * p.tiles_y * p.tiles_x * p.tiles_n;
   const unsigned grid = total < (uint32_t)kNumSMs ? total : kNumSMs;
   conv_tc_fwd_kernel<BN, STAGES><<<grid, kFwdThreads, smem, s>>>(ma, mb, mo, p);
   count_launch();
@@ -659,9 +665,10 @@ static int run_fwd_gemm(const void* act, uint32_t NI, uint32_t IH, uint32_t IW, 
   FwdParams p{};
   p.NI = NI; p.OP = OP; p.OQ = OQ; p.OC = OC; p.CK = CK;
   p.kh = kh; p.kw = kw; p.sh = sh; p.sw = sw; p.dh = dh; p.dw = dw; p.offy = offy; p.offx = offx;
-  pick_tile(OP, OQ, sh, sw, p.TH, p.TW);
+  pick_tile3(NI, OP, OQ, sh, sw, p.TN, p.TH, p.TW);
   p.tiles_y = (OP + p.TH - 1) / p.TH;
   p.tiles_x = (OQ + p.TW - 1) / p.TW;
+  p.tiles_b = (NI + p.TN - 1) / p.TN;
   const int BN = OC > 128 ? 256 : (OC > 64 ? 128 : (OC > 32 ? 64 : 32));
   p.tiles_n = (OC + BN - 1) / BN;
   p.out_pitch = out_pitch ? out_pitch : (long long)OQ * OC;
@@ -676,7 +683,7 @@ static int run_fwd_gemm(const void* act, uint32_t NI, uint32_t IH, uint32_t IW, 
   {
     uint64_t dims[4] = {CK, IW, IH, NI};
     uint64_t str[4] = {0, (uint64_t)CK * 2, (uint64_t)IW * CK * 2, (uint64_t)IH * IW * CK * 2};
-    uint32_t box[4] = {64, p.TW * sw, p.TH * sh, 1};
+    uint32_t box[4] = {64, p.TW * sw, p.TH * sh, p.TN};
     uint32_t es[4] = {1, sw, sh, 1};
     int st = make_tmap_bf16(&ma, act, 4, dims, str, box, es);
     if (st != AD_OK) return st;
@@ -695,7 +702,7 @@ static int run_fwd_gemm(const void* act, uint32_t NI, uint32_t IH, uint32_t IW, 
   if (p.tma_store) {
     uint64_t dims[4] = {OC, OQ, OP, NI};
     uint64_t str[4] = {0, (uint64_t)OC * 2, (uint64_t)p.out_pitch * 2, (uint64_t)p.out_plane * 2};
-    uint32_t box[4] = {64, p.TW, p.TH, 1};
+    uint32_t box[4] = {64, p.TW, p.TH, p.TN};
     uint32_t es[4] = {1, 1, 1, 1};
     int st = make_tmap_bf16(&mo, out, 4, dims, str, box, es);
     if (st != AD_OK) return st;
@@ -764,9 +771,9 @@ size_t conv_tc_scratch_bytes(const ad_conv2d_args* a, int pass) {
   if (pass == 2) {
     const uint32_t Kp = wgrad_kp(a->K);
     const size_t wcount = (size_t)Kp * a->kh * a->kw * a->C;
-    uint32_t TH, TW;
-    pick_tile(g.P, g.Q, 1, 1, TH, TW);
-    const uint32_t sp = a->N * ((g.P + TH - 1) / TH) * ((g.Q + TW - 1) / TW);
+    uint32_t TN, TH, TW;
+    pick_tile3(a->N, g.P, g.Q, a->stride_h, a->stride_w, TN, TH, TW);
+    const uint32_t sp = ((a->N + TN - 1) / TN) * ((g.P + TH - 1) / TH) * ((g.Q + TW - 1) / TW);
     const uint32_t BN = a->C > 64 ? 128 : 64;
     const uint32_t outer = a->kh * a->kw * ((Kp + 127) / 128) * ((a->C + BN - 1) / BN);
     size_t general = (size_t)wgrad_splits(sp, outer) * wcount * 4;
@@ -885,18 +892,14 @@ int conv_tc_wgrad(const ad_conv2d_args* a, cudaStream_t s) {
   p.kh = a->kh; p.kw = a->kw; p.sh = a->stride_h; p.sw = a->stride_w; p.dh = a->dil_h; p.dw = a->dil_w;
   p.offy = -(int)a->pad_h; p.offx = -(int)a->pad_w;
   // The tile is chosen for the dy grid; the x box is the same patch scaled by the stride.
-  pick_tile(g.P, g.Q, a->stride_h, a->stride_w, p.TH, p.TW);
-  {
-    uint32_t th, tw;
-    pick_tile(g.P, g.Q, 1, 1, th, tw);
-    if (th * a->stride_h <= 256 && tw * a->stride_w <= 256) { p.TH = th; p.TW = tw; }
-  }
+  pick_tile3(a->N, g.P, g.Q, a->stride_h, a->stride_w, p.TN, p.TH, p.TW);
   p.tiles_y = (g.P + p.TH - 1) / p.TH;
   p.tiles_x = (g.Q + p.TW - 1) / p.TW;
+  p.tiles_b = (a->N + p.TN - 1) / p.TN;
   const int BN = a->C > 64 ? 128 : 64;
   p.ktiles = (Kp + 127) / 128;
   p.ctiles = (a->C + BN - 1) / BN;
-  const uint32_t sp_tiles = p.NI * p.tiles_y * p.tiles_x;
+  const uint32_t sp_tiles = p.tiles_b * p.tiles_y * p.tiles_x;
   p.splits = wgrad_splits(sp_tiles, p.kh * p.kw * p.ktiles * p.ctiles);
   p.status = (int32_t*)a->scratch;
   p.partial = (float*)part_base;
@@ -907,7 +910,7 @@ int conv_tc_wgrad(const ad_conv2d_args* a, cudaStream_t s) {
   {
     uint64_t dims[4] = {Kp, g.Q, g.P, a->N};
     uint64_t str[4] = {0, (uint64_t)Kp * 2, (uint64_t)g.Q * Kp * 2, (uint64_t)g.P * g.Q * Kp * 2};
-    uint32_t box[4] = {64, p.TW, p.TH, 1};
+    uint32_t box[4] = {64, p.TW, p.TH, p.TN};
     uint32_t es[4] = {1, 1, 1, 1};
     st = make_tmap_bf16(&mdy, dy, 4, dims, str, box, es);
     if (st != AD_OK) return st;
@@ -915,7 +918,7 @@ int conv_tc_wgrad(const ad_conv2d_args* a, cudaStream_t s) {
   {
     uint64_t dims[4] = {a->C, a->W, a->H, a->N};
     uint64_t str[4] = {0, (uint64_t)a->C * 2, (uint64_t)a->W * a->C * 2, (uint64_t)a->H * a->W * a->C * 2};
-    uint32_t box[4] = {64, p.TW * a->stride_w, p.TH * a->stride_h, 1};
+    uint32_t box[4] = {64, p.TW * a->stride_w, p.TH * a->stride_h, p.TN};
     uint32_t es[4] = {1, a->stride_w, a->stride_h, 1};
     st = make_tmap_bf16(&mx, a->x, 4, dims, str, box, es);
     if (st != AD_OK) return st;

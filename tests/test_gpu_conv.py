@@ -81,6 +81,9 @@ TC_CASES = [
     (1, 192, 12, 140, 64, 1, 1, 1, 0),   # the 7x7 stem after im2col: K = 147 padded to 192
     (1, 64, 8, 8, 19, 1, 1, 1, 0),       # 19-class head (ragged output channels)
     (2, 128, 10, 12, 19, 1, 1, 1, 0),    # 19-class head, 2 channel slabs
+    (8, 64, 7, 7, 128, 3, 1, 1, 1),      # 7x7 maps: a tile spans 16 images (here 8 real ones)
+    (5, 128, 14, 14, 64, 1, 1, 1, 0),    # 14x14 maps: 4 images per tile, ragged last block of images
+    (3, 64, 9, 9, 19, 3, 1, 1, 1),       # small maps through the scattered-store epilogue (ragged channels)
 ]
 
 
