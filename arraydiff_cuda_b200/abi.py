@@ -46,6 +46,7 @@ class Conv2dArgs(C.Structure):
         ("scratch", vp), ("scratch_bytes", sz),
         ("out_row_begin", u32), ("out_row_count", u32),
         ("dx_col_begin", u32), ("dx_col_count", u32),
+        ("dw_kcrs", i32), ("reserved_tail", i32),
     ]
 
 

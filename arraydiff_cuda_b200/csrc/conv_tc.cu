@@ -485,8 +485,10 @@ conv_tc_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_co
 }
 
 // dw[i] (+)= sum over splits of partial[s][i], fixed order.
+// taps, C: filter geometry; kcrs != 0 stores element (k, tap, c) at (k*C + c)*taps + tap instead of index i
 __global__ void __launch_bounds__(256) wgrad_reduce_kernel(size_t n, size_t part_stride, uint32_t splits,
-                                                           const float* __restrict__ partial, float* dw, int accumulate) {
+                                                           const float* __restrict__ partial, float* dw, int accumulate,
+                                                           uint32_t taps, uint32_t C, int kcrs) {
   // 64 outputs x 4 split lanes per block: lane l sums splits l, l+4, ... (8 loads in flight), lanes combine in order
   const uint32_t tx = threadIdx.x & 63, pl = threadIdx.x >> 6;
   const size_t i = (size_t)blockIdx.x * 64 + tx;
@@ -504,7 +506,14 @@ __global__ void __launch_bounds__(256) wgrad_reduce_kernel(size_t n, size_t part
   __syncthreads();
   if (pl != 0 || i >= n) return;
   t = ((sh[0][tx] + sh[1][tx]) + sh[2][tx]) + sh[3][tx];
-  dw[i] = accumulate ? dw[i] + t : t;
+  size_t o = i;
+  if (kcrs) {
+    const uint32_t c = (uint32_t)(i % C);
+    const size_t r = i / C;
+    const uint32_t tap = (uint32_t)(r % taps);
+    o = ((r / taps) * C + c) * taps + tap;
+  }
+  dw[o] = accumulate ? dw[o] + t : t;
 }
 
 // up[n][y][x][:] = dy[n][y/sh][x/sw][:] where both divisions are exact, else 0  (16-byte groups of channels)
@@ -646,7 +655,7 @@ size_t conv_tc_row_wgrad_scratch(uint32_t NI, uint32_t CI, uint32_t KO, uint32_t
                                  uint32_t dh, uint32_t dw, uint32_t OP, uint32_t OQ);
 int conv_tc_row_wgrad(const void* x, uint32_t NI, uint32_t IH, uint32_t IW, uint32_t CI, const void* dy, uint32_t KO,
                       uint32_t kh, uint32_t kw, uint32_t sh, uint32_t sw, uint32_t dh, uint32_t dw, int offy, int offx,
-                      uint32_t OP, uint32_t OQ, float* dwt, int accumulate, void* partial, size_t partial_bytes,
+                      uint32_t OP, uint32_t OQ, float* dwt, int accumulate, int kcrs, void* partial, size_t partial_bytes,
                       int32_t* status, cudaStream_t s);
 
 // Generic forward-style implicit GEMM launch (fprop, or dgrad expressed as fprop).
@@ -882,7 +891,7 @@ int conv_tc_wgrad(const ad_conv2d_args* a, cudaStream_t s) {
   if (Kp == a->K && !getenv("ARRAYDIFF_B200_NO_ROW_KERNEL")) {
     // 64-channel layers: one CTA serves all taps from one fetch of x and dy (conv_tc_row.cu)
     st = conv_tc_row_wgrad(a->x, a->N, a->H, a->W, a->C, a->y, a->K, a->kh, a->kw, a->stride_h, a->stride_w, a->dil_h,
-                           a->dil_w, -(int)a->pad_h, -(int)a->pad_w, g.P, g.Q, (float*)a->dw, a->accumulate,
+                           a->dil_w, -(int)a->pad_h, -(int)a->pad_w, g.P, g.Q, (float*)a->dw, a->accumulate, a->dw_kcrs,
                            part_base, part_bytes, (int32_t*)a->scratch, s);
     if (st == AD_OK && a->db) launch_bias_grad((size_t)a->N * g.P * g.Q, a->K, a->y, a->db, a->accumulate, (float*)part_base, s);
     if (st != AD_ERR_UNSUPPORTED) return st;
@@ -925,7 +934,8 @@ int conv_tc_wgrad(const ad_conv2d_args* a, cudaStream_t s) {
   }
   st = BN == 128 ? launch_wgrad<128>(mdy, mx, p, s) : launch_wgrad<64>(mdy, mx, p, s);
   if (st != AD_OK) return st;
-  wgrad_reduce_kernel<<<(unsigned)((wcount + 63) / 64), 256, 0, s>>>(wcount, wcount_p, p.splits, p.partial, (float*)a->dw, a->accumulate);
+  wgrad_reduce_kernel<<<(unsigned)((wcount + 63) / 64), 256, 0, s>>>(wcount, wcount_p, p.splits, p.partial, (float*)a->dw, a->accumulate,
+                                                                      a->kh * a->kw, a->C, a->dw_kcrs);
   count_launch();
   if (a->db) launch_bias_grad((size_t)a->N * g.P * g.Q, a->K, a->y, a->db, a->accumulate, p.partial, s);
   return launch_status();

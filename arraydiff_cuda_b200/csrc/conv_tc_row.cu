@@ -520,7 +520,7 @@ conv_tc_row_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __gri
 // lane sums parts lane, lane+4, ... with 8 loads in flight, the lanes are combined in order.
 __global__ void __launch_bounds__(256) wgrad_row_reduce_kernel(uint32_t nparts, uint32_t naccs, uint32_t KO, uint32_t kh,
                                                                uint32_t kw, const float* __restrict__ partial, float* dw,
-                                                               int accumulate) {
+                                                               int accumulate, int kcrs) {
   const uint32_t tx = threadIdx.x & 63, pl = threadIdx.x >> 6;
   const uint32_t item = blockIdx.x * 64 + tx, nitems = naccs * 128 * 16;
   float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -552,7 +552,7 @@ __global__ void __launch_bounds__(256) wgrad_row_reduce_kernel(uint32_t nparts, 
 #pragma unroll
   for (int j = 0; j < 4; ++j)
     if (k0 + j < KO) {
-      float* d = dw + ((size_t)(k0 + j) * taps + tap) * 64 + c;
+      float* d = kcrs ? dw + ((size_t)(k0 + j) * 64 + c) * taps + tap : dw + ((size_t)(k0 + j) * taps + tap) * 64 + c;
       *d = accumulate ? *d + o[j] : o[j];
     }
 }
@@ -576,7 +576,7 @@ size_t conv_tc_row_wgrad_scratch(uint32_t NI, uint32_t CI, uint32_t KO, uint32_t
 
 int conv_tc_row_wgrad(const void* x, uint32_t NI, uint32_t IH, uint32_t IW, uint32_t CI, const void* dy, uint32_t KO,
                       uint32_t kh, uint32_t kw, uint32_t sh, uint32_t sw, uint32_t dh, uint32_t dw, int offy, int offx,
-                      uint32_t OP, uint32_t OQ, float* dwt, int accumulate, void* partial, size_t partial_bytes,
+                      uint32_t OP, uint32_t OQ, float* dwt, int accumulate, int kcrs, void* partial, size_t partial_bytes,
                       int32_t* status, cudaStream_t s) {
   if (!row_wgrad_ok(CI, KO, kh, kw, sh, sw, dh, dw, OQ)) return AD_ERR_UNSUPPORTED;
   RowWgParams p{};
@@ -623,7 +623,7 @@ int conv_tc_row_wgrad(const void* x, uint32_t NI, uint32_t IH, uint32_t IW, uint
   kern<<<grid, kRowThreads, smem, s>>>(mdy, mx, p);
   count_launch();
   const size_t wcount = (size_t)KO * kh * kw * 64;
-  wgrad_row_reduce_kernel<<<(p.naccs * 128 * 16 + 63) / 64, 256, 0, s>>>(grid, p.naccs, KO, kh, kw, p.partial, dwt, accumulate);
+  wgrad_row_reduce_kernel<<<(p.naccs * 128 * 16 + 63) / 64, 256, 0, s>>>(grid, p.naccs, KO, kh, kw, p.partial, dwt, accumulate, kcrs);
   count_launch();
   return launch_status();
 }

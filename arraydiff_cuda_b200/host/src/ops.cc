@@ -538,8 +538,14 @@ void CudnnConv2DOpF::_backward(TxnId txn) {
       g->reserve_scratch(need);
       b.scratch = g->get_scratch(); b.scratch_bytes = g->scratch_size();
       AD_CHECK(ad_fill_zero(b.scratch, 16, s));
-      // the filter gradient is produced KRSC and then added into the KCRS variable; the bias gradient
-      // is written straight into its variable (this op is the bias's only consumer, so = equals +=)
+      if (!use_im2col_) {
+        // the fixed-order reduction of the partials adds straight into the (zero-initialised) KCRS variables
+        b.dw = dw.dptr(); b.db = db; b.accumulate = 1; b.dw_kcrs = 1;
+        AD_CHECK(ad_conv2d_wgrad(&b, s));
+      } else {
+      // patch-matrix layer: the filter gradient is produced with padded rows and then added into the KCRS
+      // variable; the bias gradient is written straight into its variable (this op is the bias's only
+      // consumer, so = equals +=)
       b.dw = dw_krsc_; b.db = db; b.accumulate = 0;
       AD_CHECK(ad_conv2d_wgrad(&b, s));
       const long long K = (long long)shape_.filters, C = (long long)in_dim_.shape[2], kh = (long long)shape_.kernel[1], kw = (long long)shape_.kernel[0];
@@ -547,6 +553,7 @@ void CudnnConv2DOpF::_backward(TxnId txn) {
       ad_tensor4 src = {dw_krsc_, AD_F32, (uint32_t)K, (uint32_t)C, (uint32_t)kh, (uint32_t)kw, row, 1, kw * C, C};
       ad_tensor4 dst = {dw.dptr(), AD_F32, (uint32_t)K, (uint32_t)C, (uint32_t)kh, (uint32_t)kw, C * kh * kw, kh * kw, kw, 1};
       AD_CHECK(ad_convert(&src, &dst, 1, s));
+      }
     }
   }
   // data gradient over the whole padded extent, halo rows included (reference src/op.cc:1687-1724)

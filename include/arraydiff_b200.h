@@ -388,6 +388,11 @@ typedef struct {
    * the interior, src/op.cc:2705-2710; the halo reduce takes interior columns, src/kernels/spatial.cu:191-205),
    * and leaving them out keeps rows of W = k * 128 pixels free of a nearly empty trailing tile. */
   uint32_t dx_col_begin, dx_col_count;
+  /* wgrad on the tensor-core path only: non-zero = write dw in the reference's KCRS order (kernel variables are
+   * Shape4D(kw,kh,C,K), src/zoo.cc:102) instead of KRSC, so that the fixed-order reduction of the partials adds
+   * straight into the fp32 master gradient and no layout pass follows. */
+  int32_t dw_kcrs;
+  int32_t reserved_tail;
 } ad_conv2d_args;
 
 size_t ad_conv2d_scratch_bytes(const ad_conv2d_args* a, int32_t pass /* 0 fprop, 1 dgrad, 2 wgrad */);

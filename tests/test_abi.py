@@ -37,7 +37,7 @@ def test_struct_sizes_match_header_layout():
     # 12 x 4 bytes, 8 + 8 pointers, u64, pointer
     assert C.sizeof(abi.HaloArgs) == 48 + 64 + 64 + 8 + 8 + 8
     assert C.sizeof(abi.Tensor4) == 8 + 4 + 16 + 4 + 32
-    assert C.sizeof(abi.Conv2dArgs) == 17 * 4 + 4 + 4 * 8 + 16 + 3 * 8 + 16 + 8 + 8
+    assert C.sizeof(abi.Conv2dArgs) == 17 * 4 + 4 + 4 * 8 + 16 + 3 * 8 + 16 + 8 + 8 + 8
 
 
 def test_missing_library_fails_loudly(tmp_path):
@@ -55,7 +55,7 @@ def test_ctypes_layout_matches_c_compiler(tmp_path):
     fields = {
         "ad_halo_args": (abi.HaloArgs, ["dtype", "bufs", "signal_flags", "epoch", "block_counter", "epoch_base"]),
         "ad_tensor4": (abi.Tensor4, ["base", "dtype", "N", "sn", "sx"]),
-        "ad_conv2d_args": (abi.Conv2dArgs, ["K", "relu", "x", "y_pitch", "dx", "scratch", "scratch_bytes", "out_row_begin", "out_row_count", "dx_col_begin", "dx_col_count"]),
+        "ad_conv2d_args": (abi.Conv2dArgs, ["K", "relu", "x", "y_pitch", "dx", "scratch", "scratch_bytes", "out_row_begin", "out_row_count", "dx_col_begin", "dx_col_count", "dw_kcrs"]),
     }
     body = ['#include <stdio.h>', '#include <stddef.h>', '#include "arraydiff_b200.h"', "int main(void){"]
     for cname, (_, fl) in fields.items():

@@ -181,6 +181,12 @@ def test_conv_tc_wgrad(case):
     abi.check(L.ad_conv2d_wgrad(C.byref(a), H.stream()))
     H.sync()
     assert np.array_equal(H.host(dw), first)  # fixed-order split reduction: bit-reproducible
+    # the same gradient written in the reference's KCRS order, added onto what the buffer holds
+    dw2 = torch.full((K, Cc, k, k), 1.0, device="cuda")
+    a.dw, a.db, a.dw_kcrs, a.accumulate = dw2.data_ptr(), None, 1, 1
+    abi.check(L.ad_conv2d_wgrad(C.byref(a), H.stream()))
+    H.sync()
+    assert np.array_equal(H.host(dw2) - 1.0, (np.transpose(first, (0, 3, 1, 2)) + 1.0) - 1.0)
 
 
 def test_conv_rejects_bad_arguments():
