@@ -139,6 +139,16 @@ public:
   void set_allreduce_hook(AllreduceHook fn, void* user) { ar_hook_ = fn; ar_user_ = user; }
   bool has_allreduce_hook() const { return ar_hook_ != nullptr; }
   void allreduce_sum(float* local_buf_rank0_offset_base, size_t count);
+  // Data-parallel replicas around the spatial group (one process per GPU): this process is `world_rank` of
+  // `world_size` processes that all hold the same net, so the same allocation sits at the same arena offset in
+  // each; their arena bases are supplied with set_world_peer_arena().  The built-in gradient exchange then sums
+  // over all of them instead of over the spatial group only (4 data groups x 2 strips = 8 processes).
+  void set_world(size_t world_rank, size_t world_size) {
+    world_rank_ = world_rank; world_size_ = world_size;
+    world_bases_.assign(world_size, nullptr);
+    world_bases_.at(world_rank) = arena_bases_.at(my_rank_);
+  }
+  void set_world_peer_arena(size_t world_rank, void* base) { world_bases_.at(world_rank) = (uint8_t*)base; }
   // Between processes: advances every local rank's flag base by the signalling operations issued since the
   // last call (Spatial2DComm::end_phase).  Call it where a unit of work that may be replayed as a CUDA graph ends.
   void end_phase();
@@ -154,6 +164,8 @@ private:
   void* ar_user_;
   float* ar_stage_ = nullptr;    // between processes without a hook: this rank's gradient as its peers read it
   size_t ar_stage_count_ = 0;
+  size_t world_rank_ = 0, world_size_ = 0;   // 0: the gradient exchange spans the spatial group
+  vector<uint8_t*> world_bases_;
 };
 
 }  // namespace arraydiff

@@ -50,6 +50,30 @@ int adh_context_set_peer_handle(void* c, int rank, const uint8_t handle[64]) {
   m->set_peer_arena((size_t)rank, p);
   return AD_OK;
 }
+// data-parallel replicas around the spatial group: this process is world_rank of world_size (see
+// MultiGPUContext::set_world); then one call per other process with its arena's IPC handle
+int adh_context_set_world(void* c, int world_rank, int world_size) {
+  if (world_rank < 0 || world_size <= 0 || world_rank >= world_size || world_size > ARRAYDIFF_MAX_PEERS) return AD_ERR_BAD_ARG;
+  ((Ctx*)c)->ctx->set_world((size_t)world_rank, (size_t)world_size);
+  return AD_OK;
+}
+int adh_context_set_world_peer_handle(void* c, int world_rank, const uint8_t handle[64]) {
+  auto& m = ((Ctx*)c)->ctx;
+  void* p = nullptr;
+  GPUConn conn = m->device_context(m->my_rank())->conn();
+  int st = ad_ipc_open_handle(handle, &p);
+  if (st != AD_OK) return st;
+  m->set_world_peer_arena((size_t)world_rank, p);
+  return AD_OK;
+}
+// a world peer that is also a member of this process's spatial group: reuse the mapping made for the group
+// (an IPC handle is opened once per process)
+int adh_context_set_world_peer_from_group(void* c, int world_rank, int group_rank) {
+  auto& m = ((Ctx*)c)->ctx;
+  if (group_rank < 0 || (size_t)group_rank >= m->num_ranks() || !m->arena_base((size_t)group_rank)) return AD_ERR_BAD_ARG;
+  m->set_world_peer_arena((size_t)world_rank, m->arena_base((size_t)group_rank));
+  return AD_OK;
+}
 void adh_context_set_allreduce_hook(void* c, void (*fn)(float*, size_t, cudaStream_t, void*), void* user) {
   ((Ctx*)c)->ctx->set_allreduce_hook(fn, user);
 }

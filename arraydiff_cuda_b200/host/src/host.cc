@@ -142,11 +142,19 @@ void MultiGPUContext::allreduce_sum(float* buf, size_t count) {
     // No hook: reduce-scatter + all-gather with peer loads, ordered by flag words with bounded waits.  Every
     // kernel and copy is on this rank's stream and every flag value is relative, so the whole exchange can be
     // captured in a CUDA graph; each slice is summed once, in rank order, so all ranks end with the same bits.
-    const size_t r = my_rank_, R = num_ranks_;
-    GPUContext* g = dev_ctxs_[r].get();
+    // the exchange spans the spatial group, or all data-parallel replicas when set_world() was called
+    const bool wide = world_size_ > 0;
+    const size_t r = wide ? world_rank_ : my_rank_, R = wide ? world_size_ : num_ranks_;
+    GPUContext* g = dev_ctxs_[my_rank_].get();
     GPUConn conn = g->conn();
     cudaStream_t s = conn.stream();
-    Spatial2DComm* comm = &spatial_comms_[r];
+    Spatial2DComm* comm = &spatial_comms_[my_rank_];
+    uint8_t* my_base = arena_bases_.at(my_rank_);
+    auto at = [&](const void* p, size_t q) -> void* {      // the same allocation in participant q's arena
+      uint8_t* base = wide ? world_bases_.at(q) : arena_bases_.at(q);
+      assert(base && "peer arena not set");
+      return base + ((const uint8_t*)p - my_base);
+    };
     if (ar_stage_count_ < count) {
       ar_stage_ = (float*)g->arena().alloc(count * sizeof(float));   // same offset on every rank: all ranks get here alike
       ar_stage_count_ = count;
@@ -155,7 +163,7 @@ void MultiGPUContext::allreduce_sum(float* buf, size_t count) {
     auto round = [&]() {
       const uint64_t k = comm->next_phase_epoch();
       for (size_t q = 0; q < R; ++q)
-        if (q != r) AD_CHECK(ad_flag_signal_rel((uint64_t*)peer_ptr(comm->allreduce_flags() + r, r, q), comm->epoch_base(), k, s));
+        if (q != r) AD_CHECK(ad_flag_signal_rel((uint64_t*)at(comm->allreduce_flags() + r, q), comm->epoch_base(), k, s));
       for (size_t q = 0; q < R; ++q)
         if (q != r) AD_CHECK(ad_flag_wait_rel(comm->allreduce_flags() + q, comm->epoch_base(), k, kTimeoutNs, g->status_word(), s));
     };
@@ -164,12 +172,12 @@ void MultiGPUContext::allreduce_sum(float* buf, size_t count) {
     const size_t per = ((count + R - 1) / R + 3) / 4 * 4;
     auto lo = [&](size_t q) { return std::min(count, q * per); };
     const float* srcs[ARRAYDIFF_MAX_PEERS];
-    for (size_t q = 0; q < R; ++q) srcs[q] = (const float*)peer_ptr(ar_stage_, r, q);
+    for (size_t q = 0; q < R; ++q) srcs[q] = (const float*)at(ar_stage_, q);
     AD_CHECK(ad_peer_sum((uint32_t)R, srcs, buf, lo(r), lo(r + 1), s));   // my slice of the sum
     round();                                                       // every rank's slice is final
     for (size_t q = 0; q < R; ++q) {
       if (q == r || lo(q) == lo(q + 1)) continue;
-      CUDA_CHECK(cudaMemcpyAsync(buf + lo(q), (const float*)peer_ptr(buf, r, q) + lo(q), (lo(q + 1) - lo(q)) * sizeof(float),
+      CUDA_CHECK(cudaMemcpyAsync(buf + lo(q), (const float*)at(buf, q) + lo(q), (lo(q + 1) - lo(q)) * sizeof(float),
                                  cudaMemcpyDeviceToDevice, s));
     }
     round();                                                       // nobody still reads my slice or my staged copy

@@ -28,6 +28,9 @@ def load():
         L.adh_context_arena_handle.argtypes = [vp, C.c_char_p]
         L.adh_context_set_peer_handle.argtypes = [vp, C.c_int, C.c_char_p]
         L.adh_context_set_allreduce_hook.argtypes = [vp, vp, vp]
+        L.adh_context_set_world.argtypes = [vp, C.c_int, C.c_int]
+        L.adh_context_set_world_peer_handle.argtypes = [vp, C.c_int, C.c_char_p]
+        L.adh_context_set_world_peer_from_group.argtypes = [vp, C.c_int, C.c_int]
         L.adh_context_stream.restype = vp
         L.adh_context_stream.argtypes = [vp, C.c_int]
         L.adh_net_create.restype = vp

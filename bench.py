@@ -577,8 +577,19 @@ def run_net_workload(args, kind):
             with torch.cuda.stream(torch.cuda.ExternalStream(stream)):
                 dist.all_reduce(t)
 
-        if args.nccl_allreduce or D > 1:      # several data groups: the sum spans all GPUs
+        if hyb and D > 1 and not args.world_exchange:
             args.nccl_allreduce = True
+        if hyb and D > 1 and not args.nccl_allreduce:
+            # several data groups: the built-in gradient exchange spans all processes (same net, same arena offsets)
+            assert Lh.adh_context_set_world(h, rank, world) == 0
+            for wr in range(world):
+                if wr == rank:
+                    continue
+                if wr // Sg == group:
+                    assert Lh.adh_context_set_world_peer_from_group(h, wr, wr % Sg) == 0
+                else:
+                    assert Lh.adh_context_set_world_peer_handle(h, wr, bytes(allh[wr].cpu().numpy().tobytes())) == 0
+        if args.nccl_allreduce:
             # filter gradients over NCCL (torch.distributed) instead of the built-in peer exchange; such a
             # step is launched eagerly
             hook = HOOK(allreduce)
@@ -693,7 +704,7 @@ def run_net_workload(args, kind):
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "images_per_s": NB * D / step_s,
             "config": {"workload": "resnet50_dilated_segnet" if seg else f"resnet50_hybrid_{D}x{strips}" if hyb else "resnet50_stem_stage1",
                        "image": [NB * D, 3, Hh, Ww], "strips": strips, "data_groups": D, "layout": "NHWC",
-                       "bn_statistics": "per strip (as the reference)", "update": "allreduce (%s) + Nesterov SGD" % ("nccl" if world > 1 and args.nccl_allreduce else "peer loads" if strips > 1 else "single rank"), "launch": "cuda graph" if use_graph else "eager",
+                       "bn_statistics": "per strip (as the reference)", "update": "allreduce (%s) + Nesterov SGD" % ("nccl" if world > 1 and args.nccl_allreduce else "peer loads" if strips > 1 or D > 1 else "single rank"), "launch": "cuda graph" if use_graph else "eager",
                        "l2": "activations of one step total more than 1 GB, larger than L2", "parallelism": f"data{D}-spatial-h{strips}" if hyb else f"spatial-h{strips}"},
             "e2e": {"value": flops / t_e2e / 1e12, "unit": UNIT, "h2d_bytes_per_step": int(x.nbytes // (Sg if world > 1 else 1) + (labels.nbytes if hyb else labels.nbytes // world if seg else sum(d.nbytes for d in dy))),
                     "d2h_bytes_per_step": int(NB * 4 if hyb else np.prod(net.strip_shape[2:]) * NB * 4 if seg else np.prod(net.strip_shape) * 4), "steps": k_e2e, "timing": "host clock between synchronisations"},
@@ -719,6 +730,9 @@ def main():
                          "resnet50_hybrid: ResNet-50 classifier, 224 x 224, batch 256, data-parallel groups of 2 strips (config 5)")
     ap.add_argument("--strips", type=int, default=1, help="stem_stage1 on one GPU: ranks sharing the device")
     ap.add_argument("--image", type=int, default=1024, help="stem_stage1: image height = width")
+    ap.add_argument("--world-exchange", action="store_true",
+                    help="resnet50_hybrid with several data groups: sum the filter gradients over ALL processes with the built-in "
+                         "peer exchange (and replay the step from a CUDA graph) instead of NCCL")
     ap.add_argument("--nccl-allreduce", action="store_true",
                     help="stem_stage1 / segnet on several GPUs: sum the filter gradients with NCCL instead of the built-in peer exchange")
     ap.add_argument("--no-graph", action="store_true", help="stem_stage1: launch every kernel eagerly instead of replaying a CUDA graph")

@@ -215,11 +215,89 @@ def classifier_part(ctx, rank, world):
     dist.barrier()
 
 
+def hybrid_part(rank, world, local):
+    """Data-parallel replicas of 2-strip spatial groups (world 4 = 2 x 2): the built-in gradient exchange spans
+    all processes; after a few SGD steps on different data per group the parameters equal those of the same run
+    with the gradients summed by NCCL (up to the summation order)."""
+    Sg = 2
+    D, srank, group = world // Sg, rank % Sg, rank // Sg
+    N, Cc, Hh, W, classes = 2, 3, 128, 64, 10
+    x = H.uniform(900 + group, (N, Cc, Hh, W), 0.0, 1.0)
+    labels = np.array([group, classes - 1 - group], np.uint32).reshape(N, 1, 1)
+    results = []
+    for use_nccl in (False, True):
+        Lh = hostlib.load()
+        ctxh = Lh.adh_context_create_distributed(srank, Sg, local, hostlib.F32_NCHW, 1024)
+        hb = C.create_string_buffer(64)
+        assert Lh.adh_context_arena_handle(ctxh, hb) == 0
+        mine = torch.from_numpy(np.frombuffer(hb.raw, dtype=np.uint8).copy()).cuda()
+        allh = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(allh, mine)
+        handle = lambda r: bytes(allh[r].cpu().numpy().tobytes())
+        for q in range(Sg):
+            if q != srank:
+                assert Lh.adh_context_set_peer_handle(ctxh, q, handle(group * Sg + q)) == 0
+        if use_nccl:
+            HOOK = C.CFUNCTYPE(None, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p)
+
+            def allreduce(buf, count, stream, user):
+                t = torch.as_tensor(_Raw(buf, count * 4), device="cuda").view(torch.float32)
+                with torch.cuda.stream(torch.cuda.ExternalStream(stream)):
+                    dist.all_reduce(t)
+
+            hook = HOOK(allreduce)
+            _keep.append(hook)
+            Lh.adh_context_set_allreduce_hook(ctxh, C.cast(hook, C.c_void_p), None)
+        else:
+            assert Lh.adh_context_set_world(ctxh, rank, world) == 0
+            for wr in range(world):
+                if wr == rank:
+                    continue
+                if wr // Sg == group:
+                    assert Lh.adh_context_set_world_peer_from_group(ctxh, wr, wr % Sg) == 0
+                else:
+                    assert Lh.adh_context_set_world_peer_handle(ctxh, wr, handle(wr)) == 0
+
+        class Ctx:
+            pass
+        ctx = Ctx()
+        ctx.L, ctx.h, ctx.num_ranks = Lh, ctxh, Sg
+        net = hostlib.Net(ctx, "parallel_resnet18", Hh, W, Cc, N, filters=classes, seed=37)
+        net.configure_sgd(1e-2, 0.9, l2=1e-4, nesterov=True)
+        net.set_loss_weight(1.0 / (N * D * Sg))
+        start = torch.from_numpy(net.params(srank)).cuda()
+        dist.broadcast(start, 0)                      # every replica starts from rank 0's draw
+        net.set_params(start.cpu().numpy())
+        net.set_labels(srank, labels)
+        net.forward(x)
+        net.backward()
+        net.sgd_step()
+        for _ in range(3):
+            net.step_graph(True)                      # replays a graph without the hook, runs eagerly with it
+        net.sync()
+        assert net.status() == 0
+        if not use_nccl:
+            assert net.graph_launches() > 100, "the step was not captured"
+        p = torch.from_numpy(net.params(srank)).cuda()
+        ref = p.clone()
+        dist.broadcast(ref, 0)
+        assert torch.equal(p, ref), "replicas diverged"
+        results.append(p.cpu().numpy())
+        dist.barrier()
+    assert H.max_rel(results[0], results[1]) < 1e-4, H.max_rel(results[0], results[1])
+
+
 def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if os.environ.get("AD_MULTI_PART") == "hybrid":
+        hybrid_part(rank, world, local)
+        if rank == 0:
+            print("HYBRID_OK", world)
+        dist.destroy_process_group()
+        return
     halo_part(rank, world)
     host_part(rank, world, local)
     if rank == 0:

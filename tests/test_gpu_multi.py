@@ -26,3 +26,15 @@ def test_multi_gpu_halo_and_host_layer(world):
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert f"MULTI_OK {world}" in out.stdout
+
+
+def test_data_parallel_groups_of_spatial_pairs():
+    """2 data-parallel groups x 2 strips on 4 GPUs: built-in world-wide gradient exchange (graph replay) against NCCL."""
+    if _ngpu() < 4:
+        pytest.skip("needs 4 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", AD_MULTI_PART="hybrid")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr", "127.0.0.1",
+           "--master-port", "29611", os.path.join(ROOT, "tests", "multi_worker.py")]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    assert "HYBRID_OK 4" in out.stdout
