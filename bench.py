@@ -604,8 +604,6 @@ def run_net_workload(args, kind):
             with torch.cuda.stream(torch.cuda.ExternalStream(stream)):
                 dist.all_reduce(t)
 
-        if hyb and D > 1 and not args.world_exchange:
-            args.nccl_allreduce = True
         if hyb and D > 1 and not args.nccl_allreduce:
             # several data groups: the built-in gradient exchange spans all processes (same net, same arena offsets)
             assert Lh.adh_context_set_world(h, rank, world) == 0
@@ -757,9 +755,6 @@ def main():
                          "resnet50_hybrid: ResNet-50 classifier, 224 x 224, batch 256, data-parallel groups of 2 strips (config 5)")
     ap.add_argument("--strips", type=int, default=1, help="stem_stage1 on one GPU: ranks sharing the device")
     ap.add_argument("--image", type=int, default=1024, help="stem_stage1: image height = width")
-    ap.add_argument("--world-exchange", action="store_true",
-                    help="resnet50_hybrid with several data groups: sum the filter gradients over ALL processes with the built-in "
-                         "peer exchange (and replay the step from a CUDA graph) instead of NCCL")
     ap.add_argument("--nccl-allreduce", action="store_true",
                     help="stem_stage1 / segnet on several GPUs: sum the filter gradients with NCCL instead of the built-in peer exchange")
     ap.add_argument("--no-graph", action="store_true", help="stem_stage1: launch every kernel eagerly instead of replaying a CUDA graph")
