@@ -124,6 +124,48 @@ def test_halo_signal_and_bounded_wait():
     assert flags[1].item() == 99
 
 
+def test_relative_flag_values_and_peer_sum():
+    """Flag values relative to a device-resident base (what lets a recorded step replay): signal / wait / advance,
+    the exchange's published value, and the fixed-order sum over buffers that the gradient exchange is built from."""
+    import torch
+    L = abi.lib()
+    base = torch.full((1,), 10, dtype=torch.int64, device="cuda")
+    flags = torch.zeros(2, dtype=torch.int64, device="cuda")
+    status = torch.zeros(2, dtype=torch.int32, device="cuda")
+    vp = lambda t, off=0: C.c_void_p(t.data_ptr() + off)
+    for _ in range(3):       # the same three calls "replayed": the base moves, the offsets stay
+        abi.check(L.ad_flag_signal_rel(vp(flags), vp(base), 2, H.stream()))
+        abi.check(L.ad_flag_wait_rel(vp(flags), vp(base), 2, 100_000_000, vp(status), H.stream()))
+        abi.check(L.ad_flag_advance(vp(base), 2, H.stream()))
+    H.sync()
+    assert flags[0].item() == 16 and base.item() == 16 and status[0].item() == 0
+    abi.check(L.ad_flag_wait_rel(vp(flags, 8), vp(base), 1, 20_000_000, vp(status, 4), H.stream()))   # nobody sets it
+    H.sync()
+    assert status[1].item() == abi.AD_ERR_TIMEOUT
+    R, (p, W, h, Cc, N) = 2, (1, 16, 4, 2, 1)
+    d = [H.dev(s) for s in H.split_strips(H.uniform(32, (N, Cc, h * R, W)), R, p)]
+    counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+    a = H.halo_args(d, abi.AD_F32, abi.AD_NCHW, p, W, h, Cc, N)
+    for r in range(R):
+        a.signal_flags[r] = flags.data_ptr() + 8 * r
+    a.epoch, a.epoch_base, a.block_counter = 3, base.data_ptr(), counter.data_ptr()
+    abi.check(L.ad_halo_exchange(C.byref(a), H.stream()))
+    H.sync()
+    assert flags.tolist() == [19, 19]
+    # sum over 3 buffers of a ragged range, in buffer order; elements outside the range are not touched
+    n = 1003
+    bufs = [H.dev(H.uniform(40 + q, (n,))) for q in range(3)]
+    out = torch.full((n,), 7.0, device="cuda")
+    ptrs = (C.c_void_p * 3)(*[b.data_ptr() for b in bufs])
+    abi.check(L.ad_peer_sum(3, ptrs, vp(out), 5, 998, H.stream()))
+    H.sync()
+    want = (H.host(bufs[0]) + H.host(bufs[1])) + H.host(bufs[2])
+    got = H.host(out)
+    assert np.array_equal(got[5:998], want[5:998]) and np.all(got[:5] == 7.0) and np.all(got[998:] == 7.0)
+    assert L.ad_peer_sum(9, ptrs, vp(out), 0, n, H.stream()) == abi.AD_ERR_BAD_ARG
+    assert L.ad_peer_sum(3, ptrs, vp(out, 4), 0, n, H.stream()) == abi.AD_ERR_ALIGN
+
+
 def test_halo_bad_arguments_rejected_before_launch():
     d = [H.dev(np.zeros((1, 1, 4, 6), np.float32)) for _ in range(2)]
     L = abi.lib()
