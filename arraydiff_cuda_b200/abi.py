@@ -10,6 +10,7 @@ AD_OK, AD_ERR_BAD_ARG, AD_ERR_UNSUPPORTED, AD_ERR_CUDA, AD_ERR_TIMEOUT, AD_ERR_A
 AD_ERR_LIMIT = -7
 AD_F32, AD_BF16 = 0, 3
 AD_NCHW, AD_NHWC = 0, 1
+CONV_NONE, CONV_DIRECT_F32, CONV_TC_GENERAL, CONV_TC_ROW = 0, 1, 2, 3
 
 vp, u32, i32, u64, i64, f32, sz = C.c_void_p, C.c_uint32, C.c_int32, C.c_uint64, C.c_int64, C.c_float, C.c_size_t
 
@@ -105,6 +106,7 @@ SIGNATURES = {
     "ad_conv2d_fprop": (C.c_int, [C.POINTER(Conv2dArgs), vp]),
     "ad_conv2d_dgrad": (C.c_int, [C.POINTER(Conv2dArgs), vp]),
     "ad_conv2d_wgrad": (C.c_int, [C.POINTER(Conv2dArgs), vp]),
+    "ad_conv2d_last_kernel": (i32, []),
 }
 
 

@@ -14,6 +14,10 @@ namespace adk {
 extern unsigned long long g_launch_count;
 inline void count_launch(unsigned long long n = 1) { __atomic_fetch_add(&g_launch_count, n, __ATOMIC_RELAXED); }
 
+// Which kernel family the calling thread's most recent ad_conv2d_* call launched (ad_conv2d_last_kernel).
+enum { kConvNone = 0, kConvDirectF32 = 1, kConvTcGeneral = 2, kConvTcRow = 3 };
+extern thread_local int g_last_conv_kernel;
+
 inline int launch_status() {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? AD_OK : AD_ERR_CUDA;

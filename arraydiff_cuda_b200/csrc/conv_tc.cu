@@ -669,8 +669,12 @@ static int run_fwd_gemm(const void* act, uint32_t NI, uint32_t IH, uint32_t IW, 
     // 64-channel layers: the row-tile kernel fetches each activation patch once (conv_tc_row.cu)
     int st = conv_tc_row_fwd(act, NI, IH, IW, CK, filt, OC, kh, kw, sh, sw, dh, dw, offy, offx, OP, OQ, out, out_pitch,
                              out_plane, bias, relu, accumulate, status, s);
-    if (st != AD_ERR_UNSUPPORTED) return st;
+    if (st != AD_ERR_UNSUPPORTED) {
+      g_last_conv_kernel = kConvTcRow;
+      return st;
+    }
   }
+  g_last_conv_kernel = kConvTcGeneral;
   FwdParams p{};
   p.NI = NI; p.OP = OP; p.OQ = OQ; p.OC = OC; p.CK = CK;
   p.kh = kh; p.kw = kw; p.sh = sh; p.sw = sw; p.dh = dh; p.dw = dw; p.offy = offy; p.offx = offx;
@@ -894,8 +898,12 @@ int conv_tc_wgrad(const ad_conv2d_args* a, cudaStream_t s) {
                            a->dil_w, -(int)a->pad_h, -(int)a->pad_w, g.P, g.Q, (float*)a->dw, a->accumulate, a->dw_kcrs,
                            part_base, part_bytes, (int32_t*)a->scratch, s);
     if (st == AD_OK && a->db) launch_bias_grad((size_t)a->N * g.P * g.Q, a->K, a->y, a->db, a->accumulate, (float*)part_base, s);
-    if (st != AD_ERR_UNSUPPORTED) return st;
+    if (st != AD_ERR_UNSUPPORTED) {
+      g_last_conv_kernel = kConvTcRow;
+      return st;
+    }
   }
+  g_last_conv_kernel = kConvTcGeneral;
   WgParams p{};
   p.NI = a->N; p.OP = g.P; p.OQ = g.Q; p.KO = Kp; p.CI = a->C;
   p.kh = a->kh; p.kw = a->kw; p.sh = a->stride_h; p.sw = a->stride_w; p.dh = a->dil_h; p.dw = a->dil_w;
@@ -966,21 +974,21 @@ extern "C" size_t ad_conv2d_scratch_bytes(const ad_conv2d_args* a, int32_t pass)
 
 extern "C" int ad_conv2d_fprop(const ad_conv2d_args* a, void* stream) {
   switch (path_of(a)) {
-    case 0: return conv_direct_fprop(a, as_stream(stream));
+    case 0: g_last_conv_kernel = kConvDirectF32; return conv_direct_fprop(a, as_stream(stream));
     case 1: return tc::conv_tc_fprop(a, as_stream(stream));
     default: return a ? AD_ERR_UNSUPPORTED : AD_ERR_BAD_ARG;
   }
 }
 extern "C" int ad_conv2d_dgrad(const ad_conv2d_args* a, void* stream) {
   switch (path_of(a)) {
-    case 0: return conv_direct_dgrad(a, as_stream(stream));
+    case 0: g_last_conv_kernel = kConvDirectF32; return conv_direct_dgrad(a, as_stream(stream));
     case 1: return tc::conv_tc_dgrad(a, as_stream(stream));
     default: return a ? AD_ERR_UNSUPPORTED : AD_ERR_BAD_ARG;
   }
 }
 extern "C" int ad_conv2d_wgrad(const ad_conv2d_args* a, void* stream) {
   switch (path_of(a)) {
-    case 0: return conv_direct_wgrad(a, as_stream(stream));
+    case 0: g_last_conv_kernel = kConvDirectF32; return conv_direct_wgrad(a, as_stream(stream));
     case 1: return tc::conv_tc_wgrad(a, as_stream(stream));
     default: return a ? AD_ERR_UNSUPPORTED : AD_ERR_BAD_ARG;
   }

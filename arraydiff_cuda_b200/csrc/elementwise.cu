@@ -6,6 +6,7 @@
 namespace adk {
 
 unsigned long long g_launch_count = 0;
+thread_local int g_last_conv_kernel = kConvNone;
 
 // ---------------------------------------------------------------- packed fp32 arrays
 // The rounding of each expression is written out (explicit fmaf / __fmul_rn) so that the
@@ -237,6 +238,7 @@ extern "C" const char* ad_status_string(int status) {
   }
 }
 
+extern "C" int32_t ad_conv2d_last_kernel(void) { return g_last_conv_kernel; }
 extern "C" uint64_t ad_launch_count(void) { return __atomic_load_n(&g_launch_count, __ATOMIC_RELAXED); }
 
 extern "C" int ad_array_set_constant(size_t n, float c, float* x, void* stream) {

@@ -399,6 +399,13 @@ size_t ad_conv2d_scratch_bytes(const ad_conv2d_args* a, int32_t pass /* 0 fprop,
 int ad_conv2d_fprop(const ad_conv2d_args* a, void* stream);
 int ad_conv2d_dgrad(const ad_conv2d_args* a, void* stream);
 int ad_conv2d_wgrad(const ad_conv2d_args* a, void* stream);
+/*
+ * Which kernel family the calling thread's most recent ad_conv2d_fprop / dgrad / wgrad call launched:
+ * 0 none yet, 1 fp32 direct, 2 general tensor-core tiles, 3 row-streaming tensor-core kernels (64-channel
+ * layers).  The reference picks its cuDNN algorithm per batch size behind the caller's back
+ * (CudnnConv2DSize, src/op.cc:1424-1510); here a caller (and the parity tests) can ask which path served a shape.
+ */
+int32_t ad_conv2d_last_kernel(void);
 
 #ifdef __cplusplus
 }

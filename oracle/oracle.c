@@ -54,6 +54,16 @@ int orc_num_threads(void) {
 #endif
 }
 
+/* Sets the OpenMP team size for later calls, whatever OMP_NUM_THREADS said when the library was
+ * loaded (a process launcher may export OMP_NUM_THREADS=1 to every rank).  No-op without OpenMP. */
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 /* ------------------------------------------------------------------ bf16 */
 
 /* Round-to-nearest-even float -> bfloat16 (NaN kept quiet). */

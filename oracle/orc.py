@@ -35,6 +35,15 @@ def num_threads(omp=False):
     return _load(omp).orc_num_threads()
 
 
+def set_num_threads(n=None):
+    """Give the OpenMP build `n` threads (default: every core this process may run on), overriding an inherited
+    OMP_NUM_THREADS.  Returns the thread count now in force."""
+    if n is None:
+        n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    _load(True).orc_set_num_threads(C.c_int(int(n)))
+    return num_threads(True)
+
+
 def _p(a):
     return a.ctypes.data_as(C.c_void_p) if a is not None else None
 

@@ -15,11 +15,21 @@ TOL_F32 = 1e-5
 TOL_BF16 = 2e-2
 
 
+def _khw(k):
+    return (k, k) if isinstance(k, int) else tuple(k)
+
+
+def _out_dims(Hh, W, k, s, d, pd):
+    kh, kw = _khw(k)
+    return (Hh + 2 * pd - d * (kh - 1) - 1) // s + 1, (W + 2 * pd - d * (kw - 1) - 1) // s + 1
+
+
 def conv_args(dtype, layout, x_shape_nchw, K, k, stride, dil, pad):
     N, Cc, Hh, W = x_shape_nchw
+    kh, kw = _khw(k)
     a = abi.Conv2dArgs()
     a.dtype, a.layout = dtype, layout
-    a.N, a.C, a.H, a.W, a.K, a.kh, a.kw = N, Cc, Hh, W, K, k, k
+    a.N, a.C, a.H, a.W, a.K, a.kh, a.kw = N, Cc, Hh, W, K, kh, kw
     a.stride_h = a.stride_w = stride
     a.dil_h = a.dil_w = dil
     a.pad_h = a.pad_w = pad
@@ -87,17 +97,50 @@ TC_CASES = [
 ]
 
 
+# Shapes served by the row-streaming kernels (64 input channels, at most 64 output channels, stride 1, rows of at
+# least 96 output pixels): the kernels behind every wide 64-channel layer.  The last three entries name the kernel
+# family (abi.CONV_TC_*) that forward, data gradient and filter gradient must report for the shape.
+ROW, GEN = abi.CONV_TC_ROW, abi.CONV_TC_GENERAL
+ROW_CASES = [
+    # N, C, H, W, K, k, stride, dil, pad, (fprop, dgrad, wgrad kernel family)
+    (2, 64, 22, 140, 64, 3, 1, 3, 0, (ROW, ROW, ROW)),      # 3x3 dilation 3 on a halo-3 strip, one ragged tile pair
+    (1, 64, 12, 200, 64, 3, 1, 1, 1, (ROW, ROW, ROW)),      # 3x3 with implicit zero padding (out-of-bounds fill)
+    (1, 64, 14, 300, 64, 3, 1, 2, 0, (ROW, ROW, ROW)),      # 3x3 dilation 2, three tiles per row
+    (1, 64, 11, 98, 64, 3, 1, 1, 0, (ROW, ROW, ROW)),       # the narrowest row the kernels take (96 output pixels)
+    (1, 64, 7, 263, 64, 3, 1, 1, 0, (ROW, ROW, ROW)),       # 261 output pixels: a 5-pixel trailing tile
+    (3, 64, 8, 100, 8, 3, 1, 1, 0, (ROW, ROW, ROW)),        # 8 output channels, 3 images
+    (1, 64, 9, 130, 32, 1, 1, 1, 0, (ROW, ROW, ROW)),       # 1x1, 32 output channels
+    (3, 64, 5, 257, 64, 1, 1, 1, 0, (ROW, ROW, ROW)),       # 1x1, ragged width
+    (1, 64, 10, 131, 24, 2, 1, 1, 0, (ROW, ROW, ROW)),      # 2x2: the filter-extent-at-run-time instantiation
+    (1, 64, 12, 140, 64, (3, 1), 1, 2, 0, (ROW, ROW, ROW)), # 3x1 column filter, dilation 2
+    (1, 64, 9, 150, 48, (1, 3), 1, 1, 0, (ROW, ROW, ROW)),  # 1x3 row filter
+    (1, 64, 6, 160, 19, 1, 1, 1, 0, (ROW, ROW, GEN)),       # 19-class head on a wide map: ragged output channels
+    (1, 64, 22, 518, 64, 3, 1, 3, 0, (ROW, ROW, ROW)),      # one image of the benchmark strip: 16 x 512 out, dil 3
+    (2, 64, 19, 1030, 64, 3, 1, 1, 0, (ROW, ROW, ROW)),     # stage-1 3x3 of a 1024-wide strip
+]
+
+
+def _kinds(case):
+    return case[9] if len(case) > 9 else (None, None, None)
+
+
 def _tc_setup(case, seed=10):
-    N, Cc, Hh, W, K, k, s, d, pd = case
+    N, Cc, Hh, W, K, k, s, d, pd = case[:9]
+    kh, kw = _khw(k)
     x = orc.round_bf16(H.uniform(seed, (N, Cc, Hh, W)))
-    w = orc.round_bf16(H.normal(seed + 1, (K, Cc, k, k), float(np.sqrt(2.0 / (k * k * Cc)))))
+    w = orc.round_bf16(H.normal(seed + 1, (K, Cc, kh, kw), float(np.sqrt(2.0 / (kh * kw * Cc)))))
     return x, w
 
 
-@pytest.mark.parametrize("case", TC_CASES)
+def _check_kind(L, want):
+    if want is not None:
+        assert L.ad_conv2d_last_kernel() == want, (L.ad_conv2d_last_kernel(), want)
+
+
+@pytest.mark.parametrize("case", TC_CASES + ROW_CASES)
 def test_conv_tc_fprop(case):
     import torch
-    N, Cc, Hh, W, K, k, s, d, pd = case
+    N, Cc, Hh, W, K, k, s, d, pd = case[:9]
     x, w = _tc_setup(case)
     b = H.normal(12, (K,))
     y_w = orc.conv2d_fprop(x, w, b, (s, s), (d, d), (pd, pd), omp=True)
@@ -112,6 +155,7 @@ def test_conv_tc_fprop(case):
     a.x, a.w, a.bias, a.y = dx_.data_ptr(), dw_.data_ptr(), db_.data_ptr(), y.data_ptr()
     a.scratch, a.scratch_bytes = status.data_ptr(), 16
     abi.check(L.ad_conv2d_fprop(C.byref(a), H.stream()))
+    _check_kind(L, _kinds(case)[0])
     H.sync()
     assert status[0].item() == 0
     got = orc.nhwc_to_nchw(H.host(y))
@@ -121,15 +165,20 @@ def test_conv_tc_fprop(case):
     abi.check(L.ad_conv2d_fprop(C.byref(a), H.stream()))
     H.sync()
     assert H.max_rel(orc.nhwc_to_nchw(H.host(y)), np.maximum(y_w, 0)) < TOL_BF16
+    assert status[0].item() == 0
+    # no bias: the epilogue's other uniform branch
+    a.relu, a.bias = 0, None
+    abi.check(L.ad_conv2d_fprop(C.byref(a), H.stream()))
+    H.sync()
+    assert H.max_rel(orc.nhwc_to_nchw(H.host(y)), y_w - b.reshape(1, -1, 1, 1)) < TOL_BF16
 
 
-@pytest.mark.parametrize("case", TC_CASES)
+@pytest.mark.parametrize("case", TC_CASES + ROW_CASES)
 def test_conv_tc_dgrad(case):
     import torch
-    N, Cc, Hh, W, K, k, s, d, pd = case
+    N, Cc, Hh, W, K, k, s, d, pd = case[:9]
     x, w = _tc_setup(case)
-    P = (Hh + 2 * pd - d * (k - 1) - 1) // s + 1
-    Q = (W + 2 * pd - d * (k - 1) - 1) // s + 1
+    P, Q = _out_dims(Hh, W, k, s, d, pd)
     dy = orc.round_bf16(H.uniform(13, (N, K, P, Q)))
     dx_w = orc.conv2d_dgrad(dy, w, x.shape, (s, s), (d, d), (pd, pd), omp=True)
     L = abi.lib()
@@ -141,6 +190,7 @@ def test_conv_tc_dgrad(case):
     scratch = torch.zeros(nscr, dtype=torch.uint8, device="cuda")
     a.w, a.y, a.dx, a.scratch, a.scratch_bytes = dw_.data_ptr(), ddy.data_ptr(), dx.data_ptr(), scratch.data_ptr(), nscr
     abi.check(L.ad_conv2d_dgrad(C.byref(a), H.stream()))
+    _check_kind(L, _kinds(case)[1])
     H.sync()
     assert scratch[:4].view(torch.int32).item() == 0
     err = H.max_rel(orc.nhwc_to_nchw(H.host(dx)), dx_w)
@@ -151,13 +201,13 @@ def test_conv_tc_dgrad(case):
     assert H.max_rel(orc.nhwc_to_nchw(H.host(dx)), 2 * dx_w) < 2 * TOL_BF16
 
 
-@pytest.mark.parametrize("case", TC_CASES)
+@pytest.mark.parametrize("case", TC_CASES + ROW_CASES)
 def test_conv_tc_wgrad(case):
     import torch
-    N, Cc, Hh, W, K, k, s, d, pd = case
+    N, Cc, Hh, W, K, k, s, d, pd = case[:9]
+    kh, kw = _khw(k)
     x, w = _tc_setup(case)
-    P = (Hh + 2 * pd - d * (k - 1) - 1) // s + 1
-    Q = (W + 2 * pd - d * (k - 1) - 1) // s + 1
+    P, Q = _out_dims(Hh, W, k, s, d, pd)
     dy = orc.round_bf16(H.uniform(14, (N, K, P, Q)))
     db_w = np.zeros(K, np.float32)
     dw_w = orc.conv2d_wgrad(x, dy, w.shape, (s, s), (d, d), (pd, pd), db=db_w, omp=True)
@@ -165,12 +215,13 @@ def test_conv_tc_wgrad(case):
     a = conv_args(abi.AD_BF16, abi.AD_NHWC, x.shape, K, k, s, d, pd)
     dx_ = H.dev_bf16(orc.nchw_to_nhwc(x))
     ddy = H.dev_bf16(orc.nchw_to_nhwc(dy))
-    dw = torch.full((K, k, k, Cc), 5.0, device="cuda")
+    dw = torch.full((K, kh, kw, Cc), 5.0, device="cuda")
     db = torch.full((K,), 5.0, device="cuda")
     nscr = L.ad_conv2d_scratch_bytes(C.byref(a), 2)
     scratch = torch.zeros(nscr, dtype=torch.uint8, device="cuda")
     a.x, a.y, a.dw, a.db, a.scratch, a.scratch_bytes = dx_.data_ptr(), ddy.data_ptr(), dw.data_ptr(), db.data_ptr(), scratch.data_ptr(), nscr
     abi.check(L.ad_conv2d_wgrad(C.byref(a), H.stream()))
+    _check_kind(L, _kinds(case)[2])
     H.sync()
     assert scratch[:4].view(torch.int32).item() == 0
     got = np.transpose(H.host(dw), (0, 3, 1, 2))  # KRSC -> KCRS
@@ -182,11 +233,12 @@ def test_conv_tc_wgrad(case):
     H.sync()
     assert np.array_equal(H.host(dw), first)  # fixed-order split reduction: bit-reproducible
     # the same gradient written in the reference's KCRS order, added onto what the buffer holds
-    dw2 = torch.full((K, Cc, k, k), 1.0, device="cuda")
+    dw2 = torch.full((K, Cc, kh, kw), 1.0, device="cuda")
     a.dw, a.db, a.dw_kcrs, a.accumulate = dw2.data_ptr(), None, 1, 1
     abi.check(L.ad_conv2d_wgrad(C.byref(a), H.stream()))
     H.sync()
     assert np.array_equal(H.host(dw2) - 1.0, (np.transpose(first, (0, 3, 1, 2)) + 1.0) - 1.0)
+    assert scratch[:4].view(torch.int32).item() == 0
 
 
 def test_conv_rejects_bad_arguments():
@@ -202,19 +254,20 @@ def test_conv_rejects_bad_arguments():
     assert L.ad_conv2d_fprop(None, H.stream()) == abi.AD_ERR_BAD_ARG
 
 
-@pytest.mark.parametrize("case", [(2, 64, 22, 140, 64, 3, 1, 3, 0), (1, 128, 20, 24, 128, 3, 1, 1, 0), (1, 64, 34, 34, 128, 3, 2, 1, 0)])
+@pytest.mark.parametrize("case", [(2, 64, 22, 140, 64, 3, 1, 3, 0), (1, 128, 20, 24, 128, 3, 1, 1, 0), (1, 64, 34, 34, 128, 3, 2, 1, 0),
+                                  (1, 64, 14, 300, 32, 3, 1, 2, 0)])
 def test_conv_tc_fprop_row_ranges_compose(case):
     """Interior rows first, boundary rows later (what the halo overlap does) == one full call, bit for bit,
     and rows outside a range are not touched."""
     import torch
     N, Cc, Hh, W, K, k, s, d, pd = case
     x, w = _tc_setup(case)
+    y_w = orc.conv2d_fprop(x, w, None, (s, s), (d, d), (pd, pd), omp=True)
     L = abi.lib()
     a = conv_args(abi.AD_BF16, abi.AD_NHWC, x.shape, K, k, s, d, pd)
     dx_ = H.dev_bf16(orc.nchw_to_nhwc(x))
     dw_ = H.dev_bf16(np.ascontiguousarray(np.transpose(w, (0, 2, 3, 1))))
-    P = (Hh + 2 * pd - d * (k - 1) - 1) // s + 1
-    Q = (W + 2 * pd - d * (k - 1) - 1) // s + 1
+    P, Q = _out_dims(Hh, W, k, s, d, pd)
     full = torch.zeros((N, P, Q, K), dtype=torch.bfloat16, device="cuda")
     parts = torch.full((N, P, Q, K), 9.0, dtype=torch.bfloat16, device="cuda")
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
@@ -233,20 +286,22 @@ def test_conv_tc_fprop_row_ranges_compose(case):
     abi.check(L.ad_conv2d_fprop(C.byref(a), H.stream()))
     H.sync()
     assert torch.equal(parts, full) and status[0].item() == 0
+    assert H.max_rel(orc.nhwc_to_nchw(H.host(parts)), y_w) < TOL_BF16
     a.out_row_begin, a.out_row_count = P - 1, 2
     assert L.ad_conv2d_fprop(C.byref(a), H.stream()) == abi.AD_ERR_BAD_ARG
 
 
-@pytest.mark.parametrize("case", [(2, 64, 22, 140, 64, 3, 1, 3, 0), (1, 128, 20, 40, 128, 3, 1, 1, 0), (1, 64, 34, 34, 128, 3, 2, 1, 0)])
+@pytest.mark.parametrize("case", [(2, 64, 22, 140, 64, 3, 1, 3, 0), (1, 128, 20, 40, 128, 3, 1, 1, 0), (1, 64, 34, 34, 128, 3, 2, 1, 0),
+                                  (1, 64, 14, 300, 32, 3, 1, 2, 0)])
 def test_conv_tc_dgrad_column_range(case):
     """The data gradient restricted to the interior columns of a halo-padded buffer == those columns of the
     full gradient, bit for bit, and the pad columns are not touched."""
     import torch
     N, Cc, Hh, W, K, k, s, d, pd = case
     x, w = _tc_setup(case)
-    P = (Hh + 2 * pd - d * (k - 1) - 1) // s + 1
-    Q = (W + 2 * pd - d * (k - 1) - 1) // s + 1
+    P, Q = _out_dims(Hh, W, k, s, d, pd)
     dy = orc.round_bf16(H.uniform(14, (N, K, P, Q)))
+    dx_w = orc.conv2d_dgrad(dy, w, x.shape, (s, s), (d, d), (pd, pd), omp=True)
     L = abi.lib()
     a = conv_args(abi.AD_BF16, abi.AD_NHWC, x.shape, K, k, s, d, pd)
     dw_ = H.dev_bf16(np.ascontiguousarray(np.transpose(w, (0, 2, 3, 1))))
@@ -265,6 +320,7 @@ def test_conv_tc_dgrad_column_range(case):
     H.sync()
     assert scratch[:4].view(torch.int32).item() == 0
     assert torch.equal(part[:, :, p:W - p], full[:, :, p:W - p])
+    assert H.max_rel(orc.nhwc_to_nchw(H.host(part))[:, :, :, p:W - p], dx_w[:, :, :, p:W - p]) < TOL_BF16
     assert torch.all(part[:, :, :p] == 5.0) and torch.all(part[:, :, W - p:] == 5.0)
     a.dx_col_begin, a.dx_col_count = W - 1, 2
     assert L.ad_conv2d_dgrad(C.byref(a), H.stream()) == abi.AD_ERR_BAD_ARG
@@ -273,3 +329,49 @@ def test_conv_tc_dgrad_column_range(case):
     z = torch.zeros(1024, device="cuda")
     a32.y = a32.w = a32.dx = z.data_ptr()
     assert L.ad_conv2d_dgrad(C.byref(a32), H.stream()) == abi.AD_ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("case", ROW_CASES[:6] + ROW_CASES[8:10])
+def test_conv_tc_row_kernels_agree_with_general_kernels(case, monkeypatch):
+    """The same call served by the row-streaming kernels and, with ARRAYDIFF_B200_NO_ROW_KERNEL set, by the general
+    tile kernels: two independent implementations of one contraction must agree to rounding (both accumulate in
+    fp32; outputs are bf16 for fprop / dgrad, fp32 for the filter gradient) and report different kernel families."""
+    import os
+    import torch
+    N, Cc, Hh, W, K, k, s, d, pd = case[:9]
+    kh, kw = _khw(k)
+    x, w = _tc_setup(case)
+    P, Q = _out_dims(Hh, W, k, s, d, pd)
+    dy = orc.round_bf16(H.uniform(21, (N, K, P, Q)))
+    L = abi.lib()
+    a = conv_args(abi.AD_BF16, abi.AD_NHWC, x.shape, K, k, s, d, pd)
+    dx_ = H.dev_bf16(orc.nchw_to_nhwc(x))
+    dw_ = H.dev_bf16(np.ascontiguousarray(np.transpose(w, (0, 2, 3, 1))))
+    ddy = H.dev_bf16(orc.nchw_to_nhwc(dy))
+    nscr = max(L.ad_conv2d_scratch_bytes(C.byref(a), 1), L.ad_conv2d_scratch_bytes(C.byref(a), 2))
+    scratch = torch.zeros(nscr, dtype=torch.uint8, device="cuda")
+    a.scratch, a.scratch_bytes = scratch.data_ptr(), nscr
+    res, kinds = {}, {}
+    for mode in ("row", "general"):
+        if mode == "general":
+            monkeypatch.setenv("ARRAYDIFF_B200_NO_ROW_KERNEL", "1")
+        else:
+            monkeypatch.delenv("ARRAYDIFF_B200_NO_ROW_KERNEL", raising=False)
+        y = torch.zeros((N, P, Q, K), dtype=torch.bfloat16, device="cuda")
+        gx = torch.zeros((N, Hh, W, Cc), dtype=torch.bfloat16, device="cuda")
+        gw = torch.zeros((K, kh, kw, Cc), device="cuda")
+        a.x, a.w, a.y = dx_.data_ptr(), dw_.data_ptr(), y.data_ptr()
+        abi.check(L.ad_conv2d_fprop(C.byref(a), H.stream()))
+        kf = L.ad_conv2d_last_kernel()
+        a.y, a.dx, a.dw = ddy.data_ptr(), gx.data_ptr(), gw.data_ptr()
+        abi.check(L.ad_conv2d_dgrad(C.byref(a), H.stream()))
+        kd = L.ad_conv2d_last_kernel()
+        abi.check(L.ad_conv2d_wgrad(C.byref(a), H.stream()))
+        kw_ = L.ad_conv2d_last_kernel()
+        H.sync()
+        assert scratch[:4].view(torch.int32).item() == 0
+        res[mode], kinds[mode] = (H.host(y), H.host(gx), H.host(gw)), (kf, kd, kw_)
+    monkeypatch.delenv("ARRAYDIFF_B200_NO_ROW_KERNEL", raising=False)
+    assert kinds["row"] == tuple(_kinds(case)) and kinds["general"] == (GEN, GEN, GEN), kinds
+    for got, ref, tol in zip(res["row"], res["general"], (TOL_BF16, TOL_BF16, 1e-4)):
+        assert H.max_rel(got, ref) < tol
