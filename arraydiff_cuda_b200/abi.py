@@ -51,6 +51,12 @@ class Conv2dArgs(C.Structure):
     ]
 
 
+class ConvProfileEntry(C.Structure):
+    _fields_ = [("pass_", i32), ("kernel", i32), ("status", i32),
+                ("N", u32), ("C", u32), ("H", u32), ("W", u32), ("K", u32), ("kh", u32), ("kw", u32),
+                ("stride", u32), ("dil", u32), ("pad", u32), ("out_rows", u32), ("ms", f32)]
+
+
 # name -> (restype, argtypes); every symbol the header declares.
 SIGNATURES = {
     "ad_status_string": (C.c_char_p, [C.c_int]),
@@ -107,6 +113,8 @@ SIGNATURES = {
     "ad_conv2d_dgrad": (C.c_int, [C.POINTER(Conv2dArgs), vp]),
     "ad_conv2d_wgrad": (C.c_int, [C.POINTER(Conv2dArgs), vp]),
     "ad_conv2d_last_kernel": (i32, []),
+    "ad_conv2d_profile": (C.c_int, [i32]),
+    "ad_conv2d_profile_read": (sz, [C.POINTER(ConvProfileEntry), sz]),
 }
 
 
@@ -139,6 +147,15 @@ def load(path=None):
 
 def lib():
     return load()
+
+
+def conv_profile_read():
+    """Records of the convolution calls made since ad_conv2d_profile(1), as ConvProfileEntry objects."""
+    L = load()
+    n = L.ad_conv2d_profile_read(None, 0)
+    buf = (ConvProfileEntry * max(1, n))()
+    n = L.ad_conv2d_profile_read(buf, n)
+    return [buf[i] for i in range(n)]
 
 
 def check(status, what="arraydiff_b200 call"):

@@ -5,6 +5,8 @@
 // to caller scratch, stage 2 combines them in double.  No atomics, so results are
 // reproducible run to run.  Threads walk the tensor along its fastest axis (x for
 // NCHW-like views, channel for NHWC-like views) so that warps read whole sectors.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace adk {
@@ -759,17 +761,19 @@ static __device__ __align__(256) unsigned char g_bn_static_scratch[kBnStaticByte
 
 // In host code the array's name is only a handle for the runtime, never a device address:
 // the address has to be asked for, once per device, with that device current.
+// The per-device cache is a table of atomics: host threads that make the first call on one device at the
+// same time each look the symbol up and store the same value; none can read a half-written pointer.
 static int bn_static_scratch_address(void** out) {
   constexpr int kMaxDevices = 64;
-  static void* addr[kMaxDevices] = {};
+  static std::atomic<void*> addr[kMaxDevices];
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return AD_ERR_CUDA; }
-  if (!addr[dev]) {
-    void* p = nullptr;
+  void* p = addr[dev].load(std::memory_order_acquire);
+  if (!p) {
     if (cudaGetSymbolAddress(&p, g_bn_static_scratch) != cudaSuccess || !p) { cudaGetLastError(); return AD_ERR_CUDA; }
-    addr[dev] = p;
+    addr[dev].store(p, std::memory_order_release);
   }
-  *out = addr[dev];
+  *out = p;
   return AD_OK;
 }
 

@@ -972,24 +972,85 @@ extern "C" size_t ad_conv2d_scratch_bytes(const ad_conv2d_args* a, int32_t pass)
   return tc::conv_tc_scratch_bytes(a, pass);
 }
 
-extern "C" int ad_conv2d_fprop(const ad_conv2d_args* a, void* stream) {
-  switch (path_of(a)) {
-    case 0: g_last_conv_kernel = kConvDirectF32; return conv_direct_fprop(a, as_stream(stream));
-    case 1: return tc::conv_tc_fprop(a, as_stream(stream));
-    default: return a ? AD_ERR_UNSUPPORTED : AD_ERR_BAD_ARG;
+// ---------------------------------------------------------------- per-call timing (ad_conv2d_profile)
+#include <mutex>
+#include <vector>
+namespace {
+struct ProfRec {
+  ad_conv2d_profile_entry e;
+  cudaEvent_t e0, e1;
+};
+std::mutex g_prof_mu;
+bool g_prof_on = false;
+std::vector<ProfRec> g_prof;
+
+template <typename F>
+int profiled(int pass, const ad_conv2d_args* a, void* stream, F&& call) {
+  if (!g_prof_on || !a) return call();
+  ProfRec r{};
+  if (cudaEventCreate(&r.e0) != cudaSuccess || cudaEventCreate(&r.e1) != cudaSuccess) {
+    cudaGetLastError();
+    return call();
   }
+  cudaEventRecord(r.e0, as_stream(stream));
+  const int st = call();
+  cudaEventRecord(r.e1, as_stream(stream));
+  r.e.pass = pass; r.e.kernel = g_last_conv_kernel; r.e.status = st;
+  r.e.N = a->N; r.e.C = a->C; r.e.H = a->H; r.e.W = a->W; r.e.K = a->K; r.e.kh = a->kh; r.e.kw = a->kw;
+  r.e.stride = a->stride_h; r.e.dil = a->dil_h; r.e.pad = a->pad_h;
+  r.e.out_rows = pass == 0 ? a->out_row_count : 0;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  g_prof.push_back(r);
+  return st;
+}
+}  // namespace
+
+extern "C" int ad_conv2d_profile(int32_t enable) {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  for (auto& r : g_prof) { cudaEventDestroy(r.e0); cudaEventDestroy(r.e1); }
+  g_prof.clear();
+  g_prof_on = enable != 0;
+  return AD_OK;
+}
+extern "C" size_t ad_conv2d_profile_read(ad_conv2d_profile_entry* out, size_t max_entries) {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  if (!out) return g_prof.size();
+  size_t n = 0;
+  for (auto& r : g_prof) {
+    if (n == max_entries) break;
+    cudaEventSynchronize(r.e1);
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, r.e0, r.e1) != cudaSuccess) { cudaGetLastError(); ms = -1.f; }
+    r.e.ms = ms;
+    out[n++] = r.e;
+  }
+  return n;
+}
+
+extern "C" int ad_conv2d_fprop(const ad_conv2d_args* a, void* stream) {
+  return profiled(0, a, stream, [&] {
+    switch (path_of(a)) {
+      case 0: g_last_conv_kernel = kConvDirectF32; return conv_direct_fprop(a, as_stream(stream));
+      case 1: return tc::conv_tc_fprop(a, as_stream(stream));
+      default: return (int)(a ? AD_ERR_UNSUPPORTED : AD_ERR_BAD_ARG);
+    }
+  });
 }
 extern "C" int ad_conv2d_dgrad(const ad_conv2d_args* a, void* stream) {
-  switch (path_of(a)) {
-    case 0: g_last_conv_kernel = kConvDirectF32; return conv_direct_dgrad(a, as_stream(stream));
-    case 1: return tc::conv_tc_dgrad(a, as_stream(stream));
-    default: return a ? AD_ERR_UNSUPPORTED : AD_ERR_BAD_ARG;
-  }
+  return profiled(1, a, stream, [&] {
+    switch (path_of(a)) {
+      case 0: g_last_conv_kernel = kConvDirectF32; return conv_direct_dgrad(a, as_stream(stream));
+      case 1: return tc::conv_tc_dgrad(a, as_stream(stream));
+      default: return (int)(a ? AD_ERR_UNSUPPORTED : AD_ERR_BAD_ARG);
+    }
+  });
 }
 extern "C" int ad_conv2d_wgrad(const ad_conv2d_args* a, void* stream) {
-  switch (path_of(a)) {
-    case 0: g_last_conv_kernel = kConvDirectF32; return conv_direct_wgrad(a, as_stream(stream));
-    case 1: return tc::conv_tc_wgrad(a, as_stream(stream));
-    default: return a ? AD_ERR_UNSUPPORTED : AD_ERR_BAD_ARG;
-  }
+  return profiled(2, a, stream, [&] {
+    switch (path_of(a)) {
+      case 0: g_last_conv_kernel = kConvDirectF32; return conv_direct_wgrad(a, as_stream(stream));
+      case 1: return tc::conv_tc_wgrad(a, as_stream(stream));
+      default: return (int)(a ? AD_ERR_UNSUPPORTED : AD_ERR_BAD_ARG);
+    }
+  });
 }

@@ -301,6 +301,11 @@ conv_tc_row_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 }
 
 
+int conv_tc_stream_fwd(const void* act, uint32_t NI, uint32_t IH, uint32_t IW, uint32_t CK, const void* filt, uint32_t OC,
+                       uint32_t kh, uint32_t kw, uint32_t sh, uint32_t sw, uint32_t dh, uint32_t dw, int offy, int offx,
+                       uint32_t OP, uint32_t OQ, void* out, long long out_pitch, long long out_plane, const float* bias,
+                       int relu, int accumulate, int32_t* status, cudaStream_t s);
+
 // Returns AD_ERR_UNSUPPORTED when the shape is outside what this variant serves, so that the
 // caller falls back to the general kernel.
 int conv_tc_row_fwd(const void* act, uint32_t NI, uint32_t IH, uint32_t IW, uint32_t CK, const void* filt, uint32_t OC,
@@ -308,6 +313,12 @@ int conv_tc_row_fwd(const void* act, uint32_t NI, uint32_t IH, uint32_t IW, uint
                     uint32_t OP, uint32_t OQ, void* out, long long out_pitch, long long out_plane, const float* bias,
                     int relu, int accumulate, int32_t* status, cudaStream_t s) {
   if (sh != 1 || sw != 1 || CK != 64 || OC > 64 || OQ < 96) return AD_ERR_UNSUPPORTED;
+  if (!getenv("ARRAYDIFF_B200_ROW_TILES")) {
+    // the row-streaming kernel (below) serves every shape it can; the one-row tile kernel takes the rest
+    int st = conv_tc_stream_fwd(act, NI, IH, IW, CK, filt, OC, kh, kw, sh, sw, dh, dw, offy, offx, OP, OQ, out, out_pitch,
+                                out_plane, bias, relu, accumulate, status, s);
+    if (st != AD_ERR_UNSUPPORTED) return st;
+  }
   const uint32_t taps = kh * kw;
   const uint32_t pw = (128 + (kw - 1) * dw + 7) / 8 * 8;
   if (pw > 256 || (kh - 1) * dh + 1 > 256 || taps > 16) return AD_ERR_UNSUPPORTED;
@@ -361,6 +372,409 @@ int conv_tc_row_fwd(const void* act, uint32_t NI, uint32_t IH, uint32_t IW, uint
       (kh == 3 && kw == 3) ? conv_tc_row_fwd_kernel<3, 3> : (kh == 1 && kw == 1) ? conv_tc_row_fwd_kernel<1, 1>
                                                                                  : conv_tc_row_fwd_kernel<0, 0>;
   // the attribute is per function and per device; setting it is cheap enough to do per launch
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem) != cudaSuccess) {
+    cudaGetLastError();
+    return AD_ERR_CUDA;
+  }
+  kern<<<grid, kRowThreads, smem, s>>>(ma, mb, mo, p);
+  count_launch();
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- row-streaming forward kernel
+// The tile kernel above still fetches every input row kh times (once per output row that uses it) and issues
+// kh*kw*4 MMAs of N = 64 per output row -- and an N = 64 MMA cannot keep the tensor pipe busy: its A operand
+// (128 pixels x 16 channels) is re-read from shared memory for only 64 output columns.  Here a CTA walks DOWN a
+// 128-pixel-wide column of the image instead.  Each input row j is fetched once into a ring of row slots and used
+// at once for ALL the output rows it contributes to: output row i = j - r takes tap row r, so one MMA with
+//   A = input row j shifted by s*dil pixels            (128 px x 16 ch, K-major, shared-memory descriptor offset)
+//   B = [W(r=kh-1,s); ...; W(r=0,s)]                    (kh x 64 output channels stacked along N, K-major)
+//   D = accumulators of output rows j-kh+1 .. j         (kh adjacent 64-column slots of tensor memory)
+// serves kh taps: N = 64*kh (192 for a 3x3), a third of the instructions, and the A operand is read once for
+// three taps.  Rows of a dilated filter interact only within a residue class (row index mod dil), so a work item
+// is (image, 128-pixel column tile, residue class, chunk of L rows of that class); input rows are single-row TMA
+// boxes.  Eight 64-column accumulator slots form a ring in tensor memory: a row's slot is drained by the epilogue
+// warps (bias / ReLU / bf16 / swizzled staging / one TMA tile store, as above) while later rows accumulate.  The
+// new row's slot must be overwritten, the older rows' slots accumulated: the first MMA of an input row is split
+// in two for that reason; an MMA whose slots would wrap around the ring is split at the wrap.
+struct StreamCtl {
+  unsigned long long full[8], empty[8], afull[8], aempty[8], wbar, stg_full[2], stg_free[2];
+  uint32_t tmem_base;
+  volatile int abort_flag;
+};
+
+struct StreamParams {
+  uint32_t NI, OP, OQ, OC;
+  uint32_t kh, kw, dh, dw;
+  int32_t offy, offx;
+  uint32_t tiles_x, pw, row_bytes, stages;
+  uint32_t L, nchunks, items;
+  long long out_pitch, out_plane;
+  __nv_bfloat16* out;
+  const float* bias;
+  int32_t relu, accumulate;
+  int32_t* status;
+  int32_t tma_store;
+};
+
+struct StreamItem {
+  uint32_t n, tx, rho, i0;
+  int32_t Lc;
+};
+__device__ __forceinline__ StreamItem stream_item(const StreamParams& p, uint32_t item) {
+  StreamItem it;
+  it.tx = item % p.tiles_x;
+  uint32_t q = item / p.tiles_x;
+  it.rho = q % p.dh;
+  q /= p.dh;
+  it.i0 = (q % p.nchunks) * p.L;
+  it.n = q / p.nchunks;
+  const int32_t rows = p.OP > it.rho ? (int32_t)((p.OP - it.rho + p.dh - 1) / p.dh) : 0;   // rows of this residue class
+  const int32_t left = rows - (int32_t)it.i0;
+  it.Lc = left < (int32_t)p.L ? left : (int32_t)p.L;
+  return it;
+}
+
+template <int KH, int KW>
+__global__ void __launch_bounds__(kRowThreads, 1)
+conv_tc_stream_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                          const __grid_constant__ CUtensorMap map_o, const StreamParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t kh = KH > 0 ? (uint32_t)KH : p.kh, kw = KW > 0 ? (uint32_t)KW : p.kw;
+  const uint32_t taps = kh * kw;
+  uint8_t* wsm = smem;
+  uint8_t* psm = smem + (size_t)taps * kTapBytes;
+  uint8_t* osm = psm + (size_t)p.stages * p.row_bytes;          // 2 x 16 KiB output staging (TMA store path)
+  StreamCtl* ctl = (StreamCtl*)(osm + (p.tma_store ? 2 * 16384 : 0));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr uint32_t kSlots = 8, kTmemCols = 512;
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&ctl->full[s]), 1);
+      mbar_init(smem_u32(&ctl->empty[s]), 1);
+    }
+    for (uint32_t a = 0; a < kSlots; ++a) {
+      mbar_init(smem_u32(&ctl->afull[a]), 1);
+      mbar_init(smem_u32(&ctl->aempty[a]), 4);
+    }
+    mbar_init(smem_u32(&ctl->wbar), 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&ctl->stg_full[b]), 4);
+      mbar_init(smem_u32(&ctl->stg_free[b]), 1);
+    }
+    ctl->abort_flag = 0;
+    mbar_init_fence();
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+    if (p.tma_store) tma_prefetch_desc(&map_o);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  volatile int* abortf = &ctl->abort_flag;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // the filter, once: per column tap s the kh row taps in DESCENDING r, so that ascending output rows
+      // (ascending accumulator slots) meet ascending filter blocks
+      const uint32_t wbar = smem_u32(&ctl->wbar);
+      mbar_expect_tx(wbar, taps * kTapBytes);
+      for (uint32_t s = 0; s < kw; ++s)
+        for (uint32_t r = 0; r < kh; ++r)
+          tma_load_2d(smem_u32(wsm + (size_t)(s * kh + (kh - 1 - r)) * kTapBytes), &map_b, wbar, (int)((r * kw + s) * 64), 0);
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (uint32_t item = blockIdx.x; ok && item < p.items && !*abortf; item += gridDim.x) {
+        const StreamItem it = stream_item(p, item);
+        if (it.Lc <= 0) continue;
+        const int32_t rows_in = it.Lc + (int32_t)kh - 1;
+        for (int32_t j = 0; j < rows_in; ++j) {
+          if (!mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1u, abortf)) { ok = false; break; }
+          const uint32_t full = smem_u32(&ctl->full[stage]);
+          mbar_expect_tx(full, p.row_bytes);
+          tma_load_4d(smem_u32(psm + (size_t)stage * p.row_bytes), &map_a, full, 0, (int)(it.tx * 128) + p.offx,
+                      (int)(it.rho + (it.i0 + (uint32_t)j) * p.dh) + p.offy, (int)it.n);
+          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0, t = 0;      // t: output rows this CTA has started before the current item
+      bool ok = mbar_wait(smem_u32(&ctl->wbar), 0, abortf);
+      const uint64_t db0 = smem_desc_sw128(smem_u32(wsm), 16, 1024);
+      for (uint32_t item = blockIdx.x; ok && item < p.items && !*abortf; item += gridDim.x) {
+        const StreamItem it = stream_item(p, item);
+        if (it.Lc <= 0) continue;
+        const int32_t rows_in = it.Lc + (int32_t)kh - 1;
+        for (int32_t j = 0; j < rows_in; ++j) {
+          const int32_t i_lo = j >= (int32_t)kh - 1 ? j - ((int32_t)kh - 1) : 0;
+          const int32_t i_hi = j < it.Lc ? j : it.Lc - 1;
+          const bool new_row = j < it.Lc;
+          if (new_row) {
+            const uint32_t tt = t + (uint32_t)j;
+            if (!mbar_wait(smem_u32(&ctl->aempty[tt & 7u]), ((tt >> 3) & 1u) ^ 1u, abortf)) { ok = false; break; }
+          }
+          if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abortf)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t da0 = smem_desc_sw128(smem_u32(psm + (size_t)stage * p.row_bytes), 16, 1024);
+          // D columns of output rows [a, b] (+)= A * (filter blocks of taps r = j - a down to j - b); split at the ring's wrap
+          auto issue = [&](int32_t a, int32_t b, uint64_t da, uint64_t dbs, uint32_t acc) {
+            const uint32_t c0 = (t + (uint32_t)a) & 7u, n = (uint32_t)(b - a + 1);
+            const uint64_t db = dbs + (uint64_t)((kh - 1u - (uint32_t)(j - a)) * 512u);
+            if (c0 + n <= kSlots) {
+              umma_bf16(tmem_base + c0 * 64u, da, db, idesc_bf16(64u * n, 0, 0), acc);
+            } else {
+              const uint32_t n1 = kSlots - c0;
+              umma_bf16(tmem_base + c0 * 64u, da, db, idesc_bf16(64u * n1, 0, 0), acc);
+              umma_bf16(tmem_base, da, db + (uint64_t)(n1 * 512u), idesc_bf16(64u * (n - n1), 0, 0), acc);
+            }
+          };
+#pragma unroll
+          for (uint32_t s = 0; s < kw; ++s) {
+#pragma unroll
+            for (uint32_t kk = 0; kk < 4; ++kk) {
+              // descriptor address fields count 16-byte units: one pixel row = 8, one filter tap = 512
+              const uint64_t da = da0 + (uint64_t)(s * p.dw * 8u + 2u * kk);
+              const uint64_t dbs = db0 + (uint64_t)(s * kh * 512u + 2u * kk);
+              if (s == 0 && kk == 0 && new_row) {
+                if (j > i_lo) issue(i_lo, j - 1, da, dbs, 1u);
+                issue(j, j, da, dbs, 0u);            // the row that starts here: overwrite its slot
+              } else {
+                issue(i_lo, i_hi, da, dbs, 1u);
+              }
+            }
+          }
+          umma_commit(smem_u32(&ctl->empty[stage]));
+          if (j >= (int32_t)kh - 1) umma_commit(smem_u32(&ctl->afull[(t + (uint32_t)(j - ((int32_t)kh - 1))) & 7u]));
+          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+        }
+        t += (uint32_t)it.Lc;
+      }
+    }
+  } else {
+    const uint32_t q = (uint32_t)warp & 3u;
+    uint32_t tt = 0;
+    bool go = true;
+    for (uint32_t item = blockIdx.x; go && item < p.items && !*abortf; item += gridDim.x) {
+      const StreamItem it = stream_item(p, item);
+      if (it.Lc <= 0) continue;
+      for (int32_t i = 0; i < it.Lc; ++i, ++tt) {
+        const uint32_t slot = tt & 7u;
+        const uint32_t oy = it.rho + (it.i0 + (uint32_t)i) * p.dh, n = it.n, tx = it.tx;
+        bool ok = mbar_wait(smem_u32(&ctl->afull[slot]), (tt >> 3) & 1u, abortf);
+        if (!__all_sync(0xffffffffu, ok)) { go = false; break; }
+        tc_fence_after();
+        if (p.tma_store) {
+          const uint32_t b = tt & 1u;
+          const uint32_t m = q * 32 + lane;
+          uint8_t* stg = osm + (size_t)b * 16384;
+          if (tt >= 2) ok = mbar_wait(smem_u32(&ctl->stg_free[b]), ((tt >> 1) - 1u) & 1u, abortf);
+          if (!__all_sync(0xffffffffu, ok)) { go = false; break; }   // leave together: the tensor-memory loads below are warp-wide
+          {
+            uint32_t v[64];
+            const uint32_t taddr = tmem_base + ((q * 32u) << 16) + slot * 64u;
+            tmem_ld32(taddr, *(uint32_t(*)[32])&v[0]);
+            tmem_ld32(taddr + 32, *(uint32_t(*)[32])&v[32]);
+            tmem_ld_wait();
+            if (p.bias) {
+#pragma unroll
+              for (int j = 0; j < 64; ++j)
+                if ((uint32_t)j < p.OC) v[j] = __float_as_uint(__uint_as_float(v[j]) + p.bias[j]);
+            }
+            if (p.relu) {
+#pragma unroll
+              for (int j = 0; j < 64; ++j) v[j] = __float_as_uint(fmaxf(__uint_as_float(v[j]), 0.f));
+            }
+            uint8_t* srow = stg + m * 128u;
+            const uint32_t m7 = m & 7u;
+#pragma unroll
+            for (uint32_t g8 = 0; g8 < 8; ++g8) {
+              uint4 pk;
+              __nv_bfloat162* p2 = (__nv_bfloat162*)&pk;
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                p2[j] = __floats2bfloat162_rn(__uint_as_float(v[g8 * 8 + 2 * j]), __uint_as_float(v[g8 * 8 + 2 * j + 1]));
+              *(uint4*)(srow + ((g8 ^ m7) * 16u)) = pk;
+            }
+          }
+          // accumulator slot drained: hand it back to the MMA warp
+          tc_fence_before();
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(smem_u32(&ctl->aempty[slot]));
+            mbar_arrive(smem_u32(&ctl->stg_full[b]));
+          }
+          if (q == 0 && lane == 0) {
+            // on a failed wait the abort flag is up and every warp leaves at its next wait
+            if (mbar_wait(smem_u32(&ctl->stg_full[b]), (tt >> 1) & 1u, abortf)) {
+              asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(&map_o),
+                           "r"(smem_u32(stg)), "r"(0), "r"((int)(tx * 128)), "r"((int)oy), "r"((int)n)
+                           : "memory");
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+              // every store but the newest has finished reading its staging buffer: free the other one
+              asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+              if (tt >= 1) mbar_arrive(smem_u32(&ctl->stg_free[b ^ 1u]));
+            }
+          }
+          __syncwarp();
+          continue;
+        }
+        const uint32_t ox = tx * 128 + q * 32 + lane;
+        const bool valid = ox < p.OQ;
+        __nv_bfloat16* orow = p.out + (long long)n * p.out_plane + (long long)oy * p.out_pitch + (long long)ox * p.OC;
+#pragma unroll 1
+        for (uint32_t ch = 0; ch < 2; ++ch) {
+          uint32_t v[32];
+          tmem_ld32(tmem_base + ((q * 32u) << 16) + slot * 64u + ch * 32, v);
+          tmem_ld_wait();
+          const uint32_t c0 = ch * 32;
+          if (valid && c0 < p.OC) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const uint32_t cg = c0 + g * 8;
+              float f[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                f[j] = __uint_as_float(v[g * 8 + j]);
+                if (p.bias && cg + j < p.OC) f[j] += p.bias[cg + j];
+              }
+              if (cg + 8 <= p.OC && (p.OC & 7u) == 0) {
+                if (p.accumulate) {
+                  uint4 old = *(const uint4*)(orow + cg);
+                  const __nv_bfloat162* o2 = (const __nv_bfloat162*)&old;
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    float2 tv = __bfloat1622float2(o2[j]);
+                    f[2 * j] += tv.x; f[2 * j + 1] += tv.y;
+                  }
+                }
+                if (p.relu) {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) f[j] = fmaxf(f[j], 0.f);
+                }
+                uint4 pk;
+                __nv_bfloat162* p2 = (__nv_bfloat162*)&pk;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) p2[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+                *(uint4*)(orow + cg) = pk;
+              } else {
+                for (int j = 0; j < 8; ++j)
+                  if (cg + j < p.OC) {
+                    float tv = f[j];
+                    if (p.accumulate) tv += __bfloat162float(orow[cg + j]);
+                    if (p.relu) tv = fmaxf(tv, 0.f);
+                    orow[cg + j] = __float2bfloat16_rn(tv);
+                  }
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&ctl->aempty[slot]));
+      }
+    }
+    // all tile stores of this thread complete before shared memory is given up
+    if (p.tma_store && q == 0 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abortf) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(500);
+    if (threadIdx.x == 0 && p.status) *p.status = AD_ERR_TIMEOUT;
+  }
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// Rows per chunk: few enough items per CTA leave the last wave half empty, short chunks re-fetch kh - 1 rows each.
+static void stream_chunks(uint32_t NI, uint32_t tiles_x, uint32_t dh, uint32_t OP, uint32_t kh, uint32_t& L, uint32_t& nchunks) {
+  const uint32_t rpr = (OP + dh - 1) / dh;          // rows of the largest residue class
+  double best = 1e300;
+  L = rpr < 4 ? (rpr ? rpr : 1) : 4; nchunks = (rpr + L - 1) / L;
+  for (uint32_t l = 4; l <= 32; ++l) {
+    const uint32_t nch = (rpr + l - 1) / l, leff = (rpr + nch - 1) / nch;
+    const unsigned long long items = (unsigned long long)NI * tiles_x * dh * nch;
+    const unsigned long long waves = (items + kNumSMs - 1) / kNumSMs;
+    const double cost = (double)waves * (leff + 0.5 * (kh - 1) + 0.5);
+    if (cost < best - 1e-9 || (cost < best + 1e-9 && leff > L)) { best = cost; L = leff; nchunks = nch; }
+    if (l >= rpr) break;
+  }
+}
+
+int conv_tc_stream_fwd(const void* act, uint32_t NI, uint32_t IH, uint32_t IW, uint32_t CK, const void* filt, uint32_t OC,
+                       uint32_t kh, uint32_t kw, uint32_t sh, uint32_t sw, uint32_t dh, uint32_t dw, int offy, int offx,
+                       uint32_t OP, uint32_t OQ, void* out, long long out_pitch, long long out_plane, const float* bias,
+                       int relu, int accumulate, int32_t* status, cudaStream_t s) {
+  if (sh != 1 || sw != 1 || CK != 64 || OC > 64 || OQ < 96) return AD_ERR_UNSUPPORTED;
+  const uint32_t taps = kh * kw;
+  const uint32_t pw = (128 + (kw - 1) * dw + 7) / 8 * 8;
+  if (pw > 256 || kh > 4 || taps > 16) return AD_ERR_UNSUPPORTED;
+  const uint32_t row_bytes = pw * 128;
+  const long long op_ = out_pitch ? out_pitch : (long long)OQ * OC, opl_ = out_plane ? out_plane : (long long)OP * OQ * OC;
+  const bool tma_store = !accumulate && (OC & 7u) == 0 && !((uintptr_t)out & 15u) && (op_ % 8) == 0 && (opl_ % 8) == 0;
+  const long long avail = (long long)kMaxDynSmem - 1024 - (long long)sizeof(StreamCtl) - (long long)taps * kTapBytes -
+                          (tma_store ? 2 * 16384 : 0);
+  long long stages = avail / row_bytes;
+  if (stages < (long long)kh + 1) return AD_ERR_UNSUPPORTED;
+  if (stages > 8) stages = 8;
+  StreamParams p{};
+  p.NI = NI; p.OP = OP; p.OQ = OQ; p.OC = OC;
+  p.kh = kh; p.kw = kw; p.dh = dh; p.dw = dw; p.offy = offy; p.offx = offx;
+  p.tiles_x = (OQ + 127) / 128; p.pw = pw; p.row_bytes = row_bytes; p.stages = (uint32_t)stages;
+  stream_chunks(NI, p.tiles_x, dh, OP, kh, p.L, p.nchunks);
+  const unsigned long long items = (unsigned long long)NI * p.tiles_x * dh * p.nchunks;
+  if (items > 0xffffffffull) return AD_ERR_UNSUPPORTED;
+  p.items = (uint32_t)items;
+  p.out_pitch = op_; p.out_plane = opl_;
+  if ((OC & 7u) == 0 && (((uintptr_t)out & 15u) || (p.out_pitch % 8) || (p.out_plane % 8))) return AD_ERR_ALIGN;
+  p.out = (__nv_bfloat16*)out; p.bias = bias; p.relu = relu; p.accumulate = accumulate; p.status = status;
+  p.tma_store = tma_store ? 1 : 0;
+  CUtensorMap ma, mb, mo;
+  {
+    uint64_t dims[4] = {CK, IW, IH, NI};
+    uint64_t str[4] = {0, (uint64_t)CK * 2, (uint64_t)IW * CK * 2, (uint64_t)IH * IW * CK * 2};
+    uint32_t box[4] = {64, pw, 1, 1};
+    uint32_t es[4] = {1, 1, 1, 1};
+    int st = make_tmap_bf16(&ma, act, 4, dims, str, box, es);
+    if (st != AD_OK) return st;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)taps * CK, OC};
+    uint64_t str[2] = {0, (uint64_t)taps * CK * 2};
+    uint32_t box[2] = {64, 64};
+    uint32_t es[2] = {1, 1};
+    int st = make_tmap_bf16(&mb, filt, 2, dims, str, box, es);
+    if (st != AD_OK) return st;
+  }
+  mo = ma;
+  if (tma_store) {
+    uint64_t dims[4] = {OC, OQ, OP, NI};
+    uint64_t str[4] = {0, (uint64_t)OC * 2, (uint64_t)p.out_pitch * 2, (uint64_t)p.out_plane * 2};
+    uint32_t box[4] = {64, 128, 1, 1};
+    uint32_t es[4] = {1, 1, 1, 1};
+    int st = make_tmap_bf16(&mo, out, 4, dims, str, box, es);
+    if (st != AD_OK) return st;
+  }
+  const int smem = (int)(taps * kTapBytes + stages * row_bytes + (tma_store ? 2 * 16384 : 0) + 1024 + sizeof(StreamCtl));
+  const unsigned grid = p.items < (uint32_t)kNumSMs ? p.items : kNumSMs;
+  void (*kern)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const StreamParams) =
+      (kh == 3 && kw == 3) ? conv_tc_stream_fwd_kernel<3, 3> : (kh == 1 && kw == 1) ? conv_tc_stream_fwd_kernel<1, 1>
+                                                                                     : conv_tc_stream_fwd_kernel<0, 0>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem) != cudaSuccess) {
     cudaGetLastError();
     return AD_ERR_CUDA;

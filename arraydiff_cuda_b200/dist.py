@@ -66,12 +66,19 @@ class SymmetricArena:
         """Pointer to the same allocation on every rank (usable from this rank's kernels)."""
         return [b + offset for b in self.peer_base]
 
-    def close(self):
+    def close(self, barrier=None):
+        """Unmap the peers' arenas, then free this rank's.  `barrier` (a callable every rank runs) keeps a
+        rank from freeing memory a peer still has mapped or is still writing: it is called before the unmapping
+        and again before the free."""
         L = abi.lib()
+        if barrier:
+            barrier()
         for q in self._opened:
             L.ad_ipc_close_handle(C.c_void_p(q))
         self._opened = []
         self.bytes = None
+        if barrier:
+            barrier()
         L.ad_device_free(C.c_void_p(self.base))
 
 

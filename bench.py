@@ -5,21 +5,27 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port P bench.py --gpus N --steps K --warmup W      # one rank per GPU
 
-Workload (`config.workload` = "microbench_spatial_conv"): the shape the reference fixes for its
-own measurement of this path -- 3x3 convolution, dilation 3, halo 3, batch 32, 64 -> 64 channels,
-512 x 512 pixels, the H axis cut into one strip per GPU (tools/microbench_spatial_conv.cc:25-41,
-:101-107).  One step = halo exchange + forward conv + data gradient + filter gradient +
-halo-gradient accumulate-back + filter-gradient allreduce.  The total work is fixed as GPUs are
-added ("strong" scaling).  bf16 operands, fp32 accumulate; synthetic seeded inputs.
+Headline workload (`config.workload` = "resnet50_dilated_segnet"): the semantic-segmentation net on
+2 x 3 x 1024 x 2048 images -- ResNet-50 backbone at output stride 8 (dilated 3x3 in stages 3-4), 1x1 to
+19 classes, bilinear x8, per-pixel softmax cross-entropy -- H-partitioned over the GPUs; one step =
+forward + backward + filter-gradient allreduce + SGD through the C++ op-graph layer.  The total work
+is fixed as GPUs are added ("strong" scaling).  bf16 operands, fp32 accumulate; synthetic seeded inputs.
 
-metric  = spatial conv fwd+bwd TFLOP/s, FLOPs = 3 x 2*N*K*C*9*P*Q counted on the unpartitioned
-          output (halo recompute and padding are not credited).
-value   = with inputs resident in HBM;  e2e = same step fed from pinned host buffers through the
-          C ABI, with the host->device copies of x and dy and the device->host read of dw timed.
+metric  = spatial conv fwd+bwd TFLOP/s: the convolution FLOPs of one step by the layer table in
+          segnet_flops() (2*N*K*C*kh*kw*P*Q per pass on the unpartitioned output) over the step time.
+value   = resident step (inputs in HBM), median of individually timed steps run back to back for >= 2 s;
+e2e     = the same step fed from pinned host NCHW fp32 images and labels through the host layer's public
+          calls (host->device copy, layout / dtype conversion, device->host read of the loss inside).
+also    = one result per other workload of the benchmark configuration list, measured in the same run:
+          conv (the reference's own spatial-conv microbenchmark shape, with its roofline and an oracle check of
+          the partitioned results), halo (exchange / accumulate GB/s), stem_stage1 and resnet50_hybrid (images/s).
+`--workload NAME` runs one of them alone and prints its line.
 """
 import argparse
 import ctypes as C
+import datetime
 import json
+import math
 import os
 import subprocess
 import sys
@@ -33,15 +39,17 @@ sys.path.insert(0, ROOT)
 
 BATCH, CH, SIZE, KS, DIL, PAD = 32, 64, 512, 3, 3, 3
 METRIC, UNIT = "spatial_conv_fwd_bwd_tflops", "TFLOP/s"
+MIN_SECONDS = 2.0          # every arm's timed region lasts at least this long
+MAX_TIMED_STEPS = 20000
 
 
 def flops_per_pass(n=None, rows=SIZE, cols=SIZE):
     return 2.0 * (BATCH if n is None else n) * CH * CH * KS * KS * rows * cols
 
 
-# DRAM traffic per launch (dram__bytes_read + dram__bytes_write) of the three conv kernels, from the ncu
-# capture summarised in profiles/conv_tc_microbench_spatial_conv.md: measured at batch 4 on one GPU; traffic
-# grows in proportion to the pixels a launch processes, so it is scaled by batch / 4 / strips.
+# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the three conv kernels of the
+# microbenchmark shape, from an `ncu --set full --clock-control none` capture of one launch each at batch 4 on
+# one GPU; traffic grows in proportion to the pixels a launch processes, so it is scaled by batch / 4 / strips.
 NCU_TRAFFIC_BATCH4 = {"fprop": 233.7e6, "dgrad": 232.9e6, "wgrad": 276.1e6}
 
 
@@ -102,86 +110,175 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+class Env:
+    """Rank / world of this process and the one process group every workload shares."""
+
+    def __init__(self, gpus):
+        import torch
+        self.rank, self.world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        if self.world != gpus:
+            raise SystemExit(f"--gpus {gpus} but WORLD_SIZE={self.world}: launch with torch.distributed.run --nproc-per-node {gpus}")
+        torch.cuda.set_device(self.local)
+        self.dist = None
+        if self.world > 1:
+            import torch.distributed as dist
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local),
+                                    timeout=datetime.timedelta(seconds=300))
+            self.dist = dist
+
+    def barrier(self):
+        if self.dist:
+            self.dist.barrier()
+
+    def max_over_ranks(self, values):
+        """element-wise maximum of a list of floats over all ranks"""
+        import torch
+        t = torch.tensor(list(values), device="cuda", dtype=torch.float64)
+        if self.dist:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return t.cpu().numpy()
+
+    def close(self):
+        if self.dist:
+            self.dist.barrier()
+            self.dist.destroy_process_group()
+
+
+def timed_steps(env, run_step, marks, steps, min_seconds=None):
+    """Barrier + synchronize, then n = max(steps, ceil(min_seconds / step)) steps back to back with CUDA events
+    after every step on the launching stream(s); synchronize + barrier.  `marks()` records one event per stream
+    the step ends on and returns them.  Returns (per-step ms as the max over ranks, n, region seconds)."""
+    import torch
+    if min_seconds is None:
+        min_seconds = MIN_SECONDS
+    env.barrier()
+    torch.cuda.synchronize()
+    t0 = marks()
+    for _ in range(3):
+        run_step()
+    t1 = marks()
+    torch.cuda.synchronize()
+    est = float(env.max_over_ranks([max(a.elapsed_time(b) for a in t0 for b in t1) / 3.0])[0])
+    n = int(min(MAX_TIMED_STEPS, max(steps, math.ceil(min_seconds * 1e3 / max(est, 1e-3)))))
+    env.barrier()
+    torch.cuda.synchronize()
+    ev = [marks()]
+    for _ in range(n):
+        run_step()
+        ev.append(marks())
+    torch.cuda.synchronize()
+    origin = ev[0][0]
+    ends = [max(origin.elapsed_time(e) for e in evs) for evs in ev]
+    per = [ends[i + 1] - ends[i] for i in range(n)]
+    per = env.max_over_ranks(per)
+    env.barrier()
+    return per, n, float(np.sum(per)) * 1e-3
+
+
+def step_stats(per):
+    v = np.sort(np.asarray(per))
+    n = len(v)
+    return {"median": float(np.median(v)), "p10": float(v[int(0.1 * (n - 1))]), "p90": float(v[int(round(0.9 * (n - 1)))]),
+            "mean": float(np.mean(v)), "samples": n}
+
+
 # ----------------------------------------------------------------------------- CPU arm
-def cpu_conv_sample(target_seconds, threads_omp=True):
-    """Times the oracle's conv fwd + dgrad + wgrad on a strip sample of the workload (one image,
-    `rows` output rows, full width, dilation 3, halo-padded input) sized for ~target_seconds."""
+def cpu_conv_sample(target_seconds, ch_in=CH, ch_out=CH, width=SIZE, dil=DIL, max_rows=SIZE):
+    """Times the oracle's conv fwd + dgrad + wgrad (3x3, given dilation, halo-padded input) on a strip sample of a
+    layer (one image, `rows` output rows, full width) sized for ~target_seconds, on every core this process may
+    use -- the OpenMP team is set explicitly, an inherited OMP_NUM_THREADS=1 does not apply."""
     from oracle import orc
     from tests import helpers as H
+    threads = orc.set_num_threads()
 
     def run(rows):
-        x = H.uniform(1, (1, CH, rows + 2 * PAD, SIZE + 2 * PAD))
-        w = H.normal(2, (CH, CH, KS, KS), float(np.sqrt(2.0 / (KS * KS * CH))))
-        dy = H.uniform(3, (1, CH, rows, SIZE))
+        x = H.uniform(1, (1, ch_in, rows + 2 * dil, width + 2 * dil))
+        w = H.normal(2, (ch_out, ch_in, KS, KS), float(np.sqrt(2.0 / (KS * KS * ch_in))))
+        dy = H.uniform(3, (1, ch_out, rows, width))
         t0 = time.perf_counter()
-        y = orc.conv2d_fprop(x, w, None, dil=(DIL, DIL), omp=threads_omp)
-        orc.conv2d_dgrad(dy, w, x.shape, dil=(DIL, DIL), omp=threads_omp)
-        orc.conv2d_wgrad(x, dy, w.shape, dil=(DIL, DIL), omp=threads_omp)
+        y = orc.conv2d_fprop(x, w, None, dil=(dil, dil), omp=True)
+        orc.conv2d_dgrad(dy, w, x.shape, dil=(dil, dil), omp=True)
+        orc.conv2d_wgrad(x, dy, w.shape, dil=(dil, dil), omp=True)
         dt = time.perf_counter() - t0
-        assert y.shape == (1, CH, rows, SIZE)
-        return dt, 3 * flops_per_pass(1, rows, SIZE)
+        assert y.shape == (1, ch_out, rows, width)
+        return dt, 3 * 2.0 * ch_in * ch_out * KS * KS * rows * width
 
     dt, fl = run(2)                       # calibration
-    rows = int(max(2, min(SIZE, 2 * target_seconds / max(dt, 1e-6))))
+    rows = int(max(2, min(max_rows, 2 * target_seconds / max(dt, 1e-6))))
     dt, fl = run(rows)
-    return fl / dt / 1e12, dt, rows, orc.num_threads(threads_omp)
+    return fl / dt / 1e12, dt, rows, threads
+
+
+# the layer the CPU arm samples for the segmentation net: a stage-3 3x3 (256 -> 256, dilation 2) on its
+# 128 x 256 map -- the most frequent conv of the net (6 blocks)
+SEG_CPU_LAYER = dict(ch_in=256, ch_out=256, width=256, dil=2, max_rows=128)
 
 
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    conv = args.workload == "conv"
     budget = 120.0 / max(1, args.steps + args.warmup)
     vals, rows, cores, secs = [], 0, 1, 0.0
     for i in range(args.warmup + args.steps):
-        v, dt, rows, cores = cpu_conv_sample(min(20.0, budget))
+        v, dt, rows, cores = cpu_conv_sample(min(20.0, budget)) if conv else cpu_conv_sample(min(20.0, budget), **SEG_CPU_LAYER)
         if i >= args.warmup:
             vals.append(v); secs += dt
     value = float(np.mean(vals))
-    sample = f"oracle conv fwd+dgrad+wgrad on a {rows}-row x {SIZE}-col strip of one image per step (of 32 x 512 rows)"
+    if conv:
+        sample = f"oracle conv fwd+dgrad+wgrad on a {rows}-row x {SIZE}-col strip of one image per step (of 32 x 512 rows)"
+        config = {"workload": "microbench_spatial_conv", "batch": BATCH, "channels": CH, "image": [SIZE, SIZE],
+                  "kernel": KS, "dilation": DIL, "halo": PAD, "bounded_sample": sample}
+    else:
+        sample = (f"oracle conv fwd+dgrad+wgrad of one stage-3 layer of the net (3x3, 256->256, dilation 2) on a {rows}-row x 256-col "
+                  "strip of one image per step; the net's other operators are not timed on the CPU")
+        config = {"workload": "resnet50_dilated_segnet", "image": [2, 3, 1024, 2048], "bounded_sample": sample}
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * secs / max(1, args.steps), "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "microbench_spatial_conv", "batch": BATCH, "channels": CH, "image": [SIZE, SIZE],
-                   "kernel": KS, "dilation": DIL, "halo": PAD, "bounded_sample": sample},
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
 
 
-# ----------------------------------------------------------------------------- GPU arm
+# ----------------------------------------------------------------------------- conv microbenchmark step
 class Step:
-    """Buffers and the per-step call sequence of one rank (one H-strip)."""
+    """Buffers and the per-step call sequence of one rank (one H-strip) of the spatial conv microbenchmark."""
 
-    def __init__(self, rank, world):
+    def __init__(self, env, batch=None):
         import torch
         from arraydiff_cuda_b200 import abi, dist as addist
-        self.torch, self.abi = torch, abi
+        self.torch, self.abi, self.env = torch, abi, env
         self.L = abi.load()
+        rank, world = env.rank, env.world
         self.rank, self.world = rank, world
+        self.batch = B = BATCH if batch is None else batch
         self.h = SIZE // world
         h, Wp, Hp = self.h, SIZE + 2 * PAD, SIZE // world + 2 * PAD
         bf = torch.bfloat16
-        xbytes = BATCH * Hp * Wp * CH * 2
+        xbytes = B * Hp * Wp * CH * 2
         self.arena = addist.SymmetricArena(2 * xbytes + (1 << 20), rank, world)
-        self.x, self.x_off = self.arena.alloc((BATCH, Hp, Wp, CH), bf)       # halo-padded input strip
-        self.gx, self.gx_off = self.arena.alloc((BATCH, Hp, Wp, CH), bf)     # halo-padded input gradient
+        self.x, self.x_off = self.arena.alloc((B, Hp, Wp, CH), bf)       # halo-padded input strip
+        self.gx, self.gx_off = self.arena.alloc((B, Hp, Wp, CH), bf)     # halo-padded input gradient
         self.flags, self.flags_off = self.arena.alloc((8,), torch.int64)      # 0 from_prev 1 from_next 2 gprev 3 gnext
         self.counter = torch.zeros(1, dtype=torch.int32, device="cuda")
         self.status = torch.zeros(4, dtype=torch.int32, device="cuda")
         g = torch.Generator(device="cuda").manual_seed(1234 + rank)
         self.x.zero_()
-        self.x[:, PAD:PAD + h, PAD:PAD + SIZE] = (torch.rand((BATCH, h, SIZE, CH), device="cuda", generator=g) * 2 - 1).to(bf)
+        self.x[:, PAD:PAD + h, PAD:PAD + SIZE] = (torch.rand((B, h, SIZE, CH), device="cuda", generator=g) * 2 - 1).to(bf)
         gw = torch.Generator(device="cuda").manual_seed(99)
         self.w = (torch.randn((CH, KS, KS, CH), device="cuda", generator=gw) * float(np.sqrt(2.0 / (KS * KS * CH)))).to(bf)
-        self.y = torch.empty((BATCH, h, SIZE, CH), dtype=bf, device="cuda")
-        self.dy = (torch.rand((BATCH, h, SIZE, CH), device="cuda", generator=g) * 2 - 1).to(bf)
+        self.y = torch.empty((B, h, SIZE, CH), dtype=bf, device="cuda")
+        self.dy = (torch.rand((B, h, SIZE, CH), device="cuda", generator=g) * 2 - 1).to(bf)
         self.dw = torch.zeros((CH, KS, KS, CH), device="cuda")
         a = abi.Conv2dArgs()
         a.dtype, a.layout = abi.AD_BF16, abi.AD_NHWC
-        a.N, a.C, a.H, a.W, a.K, a.kh, a.kw = BATCH, CH, Hp, Wp, CH, KS, KS
+        a.N, a.C, a.H, a.W, a.K, a.kh, a.kw = B, CH, Hp, Wp, CH, KS, KS
         a.stride_h = a.stride_w = 1
         a.dil_h = a.dil_w = DIL
         nscr = max(self.L.ad_conv2d_scratch_bytes(C.byref(a), 1), self.L.ad_conv2d_scratch_bytes(C.byref(a), 2), 16)
@@ -193,7 +290,7 @@ class Step:
         self.marks = None      # a list: run() brackets every conv call with CUDA events and appends (name, e0, e1)
         ha = abi.HaloArgs()
         ha.dtype, ha.layout = abi.AD_BF16, abi.AD_NHWC
-        ha.halo_pad, ha.base_width, ha.base_height, ha.num_channels, ha.batch_size = PAD, SIZE, h, CH, BATCH
+        ha.halo_pad, ha.base_width, ha.base_height, ha.num_channels, ha.batch_size = PAD, SIZE, h, CH, B
         ha.num_ranks, ha.rank_first, ha.rank_count, ha.push = world, rank, 1, 1
         self.hx, self.hg = ha, abi.HaloArgs.from_buffer_copy(ha)
         xp, gp, fp = self.arena.peers(self.x_off), self.arena.peers(self.gx_off), self.arena.peers(self.flags_off)
@@ -205,12 +302,26 @@ class Step:
             self.hx.signal_flags[peer] = fp[peer] + 8 * slot
         self.hx.block_counter = self.counter.data_ptr()
         self.fp = fp
-        # pinned host copies for the end-to-end variant
-        self.hx_host = torch.empty(self.x.shape, dtype=bf).pin_memory()
-        self.hx_host.copy_(self.x.cpu())
-        self.dy_host = torch.empty(self.dy.shape, dtype=bf).pin_memory()
-        self.dy_host.copy_(self.dy.cpu())
+        self.host = None
+
+    def make_host_buffers(self):
+        """Pinned host tensors in the reference's boundary format (NCHW fp32, unpadded strip) and the device staging
+        buffers the end-to-end step converts from."""
+        torch, B, h = self.torch, self.batch, self.h
+        from tests import helpers as H
+        self.H = H
+        self.x32 = torch.empty((B, CH, h, SIZE), device="cuda")
+        self.dy32 = torch.empty((B, CH, h, SIZE), device="cuda")
+        self.x32.copy_(self.x[:, PAD:PAD + h, PAD:PAD + SIZE].permute(0, 3, 1, 2))
+        self.dy32.copy_(self.dy.permute(0, 3, 1, 2))
+        self.x_host = torch.empty(self.x32.shape, dtype=torch.float32).pin_memory()
+        self.dy_host = torch.empty(self.dy32.shape, dtype=torch.float32).pin_memory()
+        self.x_host.copy_(self.x32)
+        self.dy_host.copy_(self.dy32)
         self.dw_host = torch.empty(self.dw.shape, dtype=torch.float32).pin_memory()
+        self.cv = [(H.view_nchw(self.x32), H.view_nhwc(self.x, interior=(PAD, h, SIZE))),
+                   (H.view_nchw(self.dy32), H.view_nhwc(self.dy))]
+        self.host = True
 
     def _s(self):
         return C.c_void_p(self.torch.cuda.current_stream().cuda_stream)
@@ -237,8 +348,11 @@ class Step:
         self.epoch += 1
         ep = self.epoch
         if e2e:
-            self.x.copy_(self.hx_host, non_blocking=True)
-            self.dy.copy_(self.dy_host, non_blocking=True)
+            # host NCHW fp32 -> device staging -> bf16 NHWC (into the interior of the halo-padded strip)
+            self.x32.copy_(self.x_host, non_blocking=True)
+            self.dy32.copy_(self.dy_host, non_blocking=True)
+            for src, dst in self.cv:
+                abi.check(L.ad_convert(C.byref(src), C.byref(dst), 0, s), "convert")
         # forward: push my edge rows into the neighbours' halo rows on a side stream and wait there for
         # theirs, while the main stream already convolves the interior rows; the PAD boundary rows at
         # either end follow once the halo has landed
@@ -280,8 +394,7 @@ class Step:
                 abi.check(L.ad_halo_reduce(C.byref(self.hg), s2), "halo reduce")
         self._timed("wgrad", lambda: abi.check(L.ad_conv2d_wgrad(C.byref(a), s), "wgrad"))
         if R > 1:
-            import torch.distributed as dist
-            dist.all_reduce(self.dw)       # filter-gradient allreduce over NCCL / NVLink
+            self.env.dist.all_reduce(self.dw)       # filter-gradient allreduce over NCCL / NVLink
             self.torch.cuda.current_stream().wait_stream(self.side)
         if e2e:
             self.dw_host.copy_(self.dw, non_blocking=True)
@@ -291,51 +404,103 @@ class Step:
         if any(v != 0 for v in st):
             raise RuntimeError(f"device-side bounded wait reported {st}")
 
+    def close(self):
+        self.arena.close(barrier=self.env.barrier)
 
-def timed_loop(torch, dist, step, steps, e2e, world):
-    """Barrier + synchronize on both sides, device time by CUDA events, max over ranks."""
-    if world > 1:
-        dist.barrier()
+
+def verify_conv_step(env, step):
+    """After one resident step: results of the partitioned step against the CPU oracle evaluated on windows of the
+    UNPARTITIONED seeded tensors (edge rows of every rank are gathered first).  Ranks 0 and R-1 check, for the first
+    and last image: the PAD output rows at each strip edge (they read the neighbour's halo rows), PAD interior
+    rows, and the PAD first / last interior rows of the input gradient after the halo accumulate-back.  Every rank
+    checks 32 sampled entries of the all-reduced filter gradient against float64 dot products of the resident tensors
+    summed over ranks.  Tolerance: max-relative 2e-2 (bf16 outputs), 1e-3 for the fp32 filter gradient."""
+    import torch
+    from oracle import orc
+    torch_, dist, r, R, p, h, B = torch, env.dist, step.rank, step.world, PAD, step.h, step.batch
+    step.run()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        step.run(e2e=e2e)
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-        dist.barrier()
-    return ms
+    env.barrier()
+    step.check_status()
+    imgs = sorted({0, B - 1})
+    e = 3 * p
+
+    def gather(t):
+        t = t.contiguous()
+        if R == 1:
+            return [t]
+        out = [torch.empty_like(t) for _ in range(R)]
+        dist.all_gather(out, t)
+        return out
+
+    xi = step.x[imgs][:, p:p + h, p:p + SIZE]
+    x_top, x_bot = gather(xi[:, :e]), gather(xi[:, h - e:])
+    dyi = step.dy[imgs]
+    dy_top, dy_bot = gather(dyi[:, :e]), gather(dyi[:, h - e:])
+
+    def nchw(t):     # [n][rows][W][C] bf16 device -> float32 NCHW host
+        return np.ascontiguousarray(t.float().cpu().numpy().transpose(0, 3, 1, 2))
+
+    w = np.ascontiguousarray(step.w.float().cpu().numpy().transpose(0, 3, 1, 2))      # KRSC -> KCRS
+    zeros = np.zeros((len(imgs), CH, e, SIZE), np.float32)
+    errs = {}
+
+    def rel(a, b):
+        return float(np.max(np.abs(a.astype(np.float64) - b)) / max(float(np.max(np.abs(b))), 1e-30))
+
+    def padw(a):
+        return np.pad(a, ((0, 0), (0, 0), (0, 0), (p, p)))
+
+    if r in (0, R - 1):
+        orc.set_num_threads()
+        y = step.y[imgs]
+        gx = step.gx[imgs][:, :, p:p + SIZE]
+        for side in ("top", "bottom"):
+            if side == "top":
+                xa = nchw(x_bot[r - 1]) if r > 0 else zeros
+                xw = np.concatenate([xa, nchw(x_top[r])], axis=2)
+                da = nchw(dy_bot[r - 1]) if r > 0 else zeros
+                dw_ = np.concatenate([da, nchw(dy_top[r])], axis=2)
+                yo, go = slice(2 * p, 3 * p), slice(4 * p, 5 * p)
+                y_got, g_got = nchw(y[:, :p]), nchw(gx[:, p:2 * p])
+            else:
+                xb = nchw(x_top[r + 1]) if r + 1 < R else zeros
+                xw = np.concatenate([nchw(x_bot[r]), xb], axis=2)
+                db = nchw(dy_top[r + 1]) if r + 1 < R else zeros
+                dw_ = np.concatenate([nchw(dy_bot[r]), db], axis=2)
+                yo, go = slice(p, 2 * p), slice(3 * p, 4 * p)
+                y_got, g_got = nchw(y[:, h - p:]), nchw(gx[:, h:h + p])
+            y_w = orc.conv2d_fprop(padw(xw), w, None, dil=(DIL, DIL), omp=True)
+            errs[f"y_{side}_rows"] = rel(y_got, y_w[:, :, yo])
+            g_w = orc.conv2d_dgrad(dw_, w, (len(imgs), CH, 2 * e + 2 * p, SIZE + 2 * p), dil=(DIL, DIL), omp=True)
+            errs[f"dx_{side}_rows"] = rel(g_got, g_w[:, :, go, p:p + SIZE])
+        m = h // 2
+        xw = nchw(step.x[imgs][:, m:m + 3 * p])
+        y_w = orc.conv2d_fprop(xw, w, None, dil=(DIL, DIL), omp=True)
+        errs["y_interior_rows"] = rel(nchw(step.y[imgs][:, m:m + p]), y_w)
+    # sampled filter-gradient entries: dw[k,r,s,c] = sum over images and pixels of x[.., q + r*dil, t + s*dil, c] * dy[.., q, t, k]
+    rng = np.random.default_rng(5)
+    ks = [(int(rng.integers(CH)), int(rng.integers(KS)), int(rng.integers(KS)), int(rng.integers(CH))) for _ in range(32)]
+    part = torch.stack([(step.x[:, rr * DIL:rr * DIL + h, ss * DIL:ss * DIL + SIZE, c].double() * step.dy[:, :, :, k].double()).sum()
+                        for (k, rr, ss, c) in ks])
+    if R > 1:
+        dist.all_reduce(part)
+    got = torch.stack([step.dw[k, rr, ss, c] for (k, rr, ss, c) in ks]).double()
+    errs["dw_sampled"] = float((got - part).abs().max() / part.abs().max().clamp_min(1e-30))
+    tol = {k: (1e-3 if k == "dw_sampled" else 2e-2) for k in errs}
+    ok = all(v < tol[k] for k, v in errs.items())
+    flags = env.max_over_ranks([0.0 if ok else 1.0, max(errs.values())])
+    # the edge checks of the last rank, for the record on rank 0
+    worst = {k: float(v) for k, v in errs.items()}
+    return {"ok": bool(flags[0] == 0.0), "max_rel": float(flags[1]), "rank0": worst,
+            "checked_by_ranks": sorted({0, R - 1}), "oracle": "CPU restatement on windows of the unpartitioned tensors"}
 
 
-def step_distribution(torch, dist, step, n, world):
-    """n individually timed steps (CUDA events around each, no host synchronisation in between); per step
-    the max over ranks; returns (median, p10, p90) in ms."""
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(n + 1)]
-    ev[0].record()
-    for i in range(n):
-        step.run()
-        ev[i + 1].record()
-    torch.cuda.synchronize()
-    t = torch.tensor([ev[i].elapsed_time(ev[i + 1]) for i in range(n)], device="cuda", dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    v = np.sort(t.cpu().numpy())
-    return float(np.median(v)), float(v[int(0.1 * (n - 1))]), float(v[int(round(0.9 * (n - 1)))])
-
-
-def kernel_times_in_step(torch, dist, step, steps, world):
+def kernel_times_in_step(env, step, steps):
     """Average device time per step of each conv pass, from CUDA events around its launches inside `steps` full
     steps run back to back (the conditions of the timed region: warm clocks, halo traffic alongside)."""
-    if world > 1:
-        dist.barrier()
+    import torch
+    env.barrier()
     torch.cuda.synchronize()
     step.marks = []
     for _ in range(steps):
@@ -378,31 +543,115 @@ def kernel_times(torch, step, iters=10):
     return {"fprop": t(fprop), "dgrad": t(dgrad), "wgrad": t(wgrad)}
 
 
+def run_conv_workload(env, args, with_cpu=True):
+    """`--workload conv`: the shape the reference fixes for its own measurement of this path -- 3x3 convolution,
+    dilation 3, halo 3, batch 32, 64 -> 64 channels, 512 x 512 pixels, the H axis cut into one strip per GPU
+    (tools/microbench_spatial_conv.cc:25-41, :101-107).  One step = halo exchange + forward conv + data gradient +
+    filter gradient + halo-gradient accumulate-back + filter-gradient allreduce, driven through the C ABI."""
+    import torch
+    from arraydiff_cuda_b200 import abi
+    world, rank = env.world, env.rank
+    if SIZE % world:
+        raise SystemExit("image height must divide by the number of GPUs")
+    L = abi.load()   # raises if the CUDA library is missing: no fallback
+    step = Step(env)
+    for _ in range(max(3, args.warmup)):
+        step.run()
+    torch.cuda.synchronize()
+    step.check_status()
+
+    def marks():
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        return [e]
+
+    sampler = ClockSampler(env.local)
+    if rank == 0:
+        sampler.start()
+    launches0 = L.ad_launch_count()
+    per, n, secs = timed_steps(env, step.run, marks, args.steps)
+    launches = L.ad_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    step.check_status()
+    st = step_stats(per)
+
+    ms_nohalo = None
+    if world > 1:
+        step.halo = False
+        per_nh, _, _ = timed_steps(env, step.run, marks, args.steps, min_seconds=0.5)
+        ms_nohalo = float(np.median(per_nh))
+        step.halo = True
+    kt_step = kernel_times_in_step(env, step, max(20, args.steps))
+    step.check_status()
+    verify = verify_conv_step(env, step)
+
+    step.make_host_buffers()
+    for _ in range(2):
+        step.run(e2e=True)
+    per_e2e, n_e2e, _ = timed_steps(env, lambda: step.run(e2e=True), marks, 3, min_seconds=0.5)
+    step.check_status()
+
+    total_flops = 3 * flops_per_pass()
+    med = st["median"]
+    line = None
+    if rank == 0:
+        peaks = measured_peaks()
+        kt = kernel_times(torch, step)
+        top = max(kt_step, key=kt_step.get)
+        per_launch_flops = flops_per_pass(BATCH, step.h, SIZE)
+        achieved = per_launch_flops / kt_step[top] / 1e12
+        hbytes = step.x_host.numel() * 4 + step.dy_host.numel() * 4
+        line = {
+            "metric": METRIC, "value": total_flops / (med * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": med, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "timing": f"median of {n} individually timed steps run back to back over {secs:.2f} s (CUDA events, max over ranks per step)",
+            "config": {"workload": "microbench_spatial_conv", "batch": BATCH, "channels": CH, "image": [SIZE, SIZE],
+                       "kernel": KS, "dilation": DIL, "halo": PAD, "strips": world, "layout": "NHWC",
+                       "l2": "inputs larger than L2 (%.2f GB activations per pass)" % (BATCH * SIZE * SIZE * CH * 2 / 1e9), "parallelism": f"spatial-h{world}"},
+            "e2e": {"value": total_flops / (float(np.median(per_e2e)) * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": hbytes,
+                    "d2h_bytes_per_step": step.dw_host.numel() * 4, "steps": n_e2e,
+                    "boundary": "pinned host NCHW fp32 strips (the reference's boundary format); the conversion to bf16 NHWC is inside the timed step"},
+            "gpu_launches": int(launches), "timed_steps": n, "timed_region_s": secs,
+            "step_ms": st,
+            "halo_exposed_ms": None if ms_nohalo is None else med - ms_nohalo,
+            "roofline": {"bound": "tensor", "kernel": f"conv_tc_row_{top}", "achieved": achieved, "peak": peaks["tf_sustained"],
+                         "unit": "TFLOP/s", "frac": achieved / peaks["tf_sustained"],
+                         "traffic": NCU_TRAFFIC_BATCH4[top] * BATCH / 4 / world,
+                         "peak_source": peaks["source"] + " (sustained: the kernel is timed with CUDA events inside full steps run back to back)",
+                         "kernels_us": {k: v * 1e6 for k, v in kt_step.items()},
+                         "kernels_alone_us": {k: v * 1e6 for k, v in kt.items()},
+                         "frac_alone_of_burst": per_launch_flops / kt[top] / 1e12 / peaks["tf_burst"]},
+            "verify": verify,
+            "clocks": clocks,
+        }
+        if world == 1 and with_cpu:
+            v, dt, rows, cores = cpu_conv_sample(args.cpu_seconds)
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
+                                    "sample": f"oracle conv fwd+dgrad+wgrad on a {rows}-row x {SIZE}-col strip of one image ({dt:.1f} s)"}
+    step.close()
+    return line
+
+
 # ----------------------------------------------------------------------------- halo microbenchmark
-def run_halo_workload(args):
+def run_halo_workload(env, args):
     """`--workload halo`: benchmark config 2 -- NCHW tensors N=8, C=256, 224x224 cut into H-strips, halo
     1 and 3, fp32 and bf16; forward exchange and backward accumulate.  On one GPU the R strips share the
     device and move in ONE launch (HBM-bound: payload read + written); on N GPUs each rank pushes to /
     pulls from its neighbours over NVLink, with NCCL send/recv of packed faces timed beside it."""
     import torch
-    import torch.distributed as dist
     from arraydiff_cuda_b200 import abi, dist as addist
-    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    rank, world, dist = env.rank, env.world, env.dist
     L = abi.load()
     N, Cc, Hh, W = 8, 256, 224, 224
+    iters = max(args.steps, 50)
     cases = []
     s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
     def timed(fn, iters):
         for _ in range(max(3, args.warmup)):
             fn()
-        if world > 1:
-            dist.barrier()
+        env.barrier()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -410,12 +659,7 @@ def run_halo_workload(args):
             fn()
         e1.record()
         torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / iters
-        if world > 1:
-            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms * 1e-3
+        return float(env.max_over_ranks([e0.elapsed_time(e1) / iters])[0]) * 1e-3
 
     launches0 = L.ad_launch_count()
     for R in ([world] if world > 1 else [2, 4, 8]):
@@ -434,8 +678,8 @@ def run_halo_workload(args):
                     a.rank_first, a.rank_count, a.push = 0, R, 1
                     for r in range(R):
                         a.bufs[r] = bufs[r].data_ptr()
-                    te = timed(lambda: abi.check(L.ad_halo_exchange(C.byref(a), s)), args.steps)
-                    tr = timed(lambda: abi.check(L.ad_halo_reduce(C.byref(a), s)), args.steps)
+                    te = timed(lambda: abi.check(L.ad_halo_exchange(C.byref(a), s)), iters)
+                    tr = timed(lambda: abi.check(L.ad_halo_reduce(C.byref(a), s)), iters)
                 else:
                     arena = addist.SymmetricArena(int(np.prod(shape)) * es + (1 << 20), rank, world)
                     buf, off = arena.alloc(shape, tdt)
@@ -483,15 +727,15 @@ def run_halo_workload(args):
                         for recv, dst in recvs:
                             buf[:, :, dst:dst + p, p:p + W] = recv
 
-                    te, tr, tn = timed(exch, args.steps), timed(red, args.steps), timed(nccl, args.steps)
+                    te, tr, tn = timed(exch, iters), timed(red, iters), timed(nccl, min(iters, 50))
                     if int(status.item()) != 0:
                         raise RuntimeError("bounded flag wait timed out")
                     rec["nccl_sendrecv_us"] = tn * 1e6
                     rec["nccl_sendrecv_gbs"] = payload / tn / 1e9
-                    dist.barrier()
-                    arena.close()
+                    arena.close(barrier=env.barrier)
                 rec.update(exchange_us=te * 1e6, exchange_gbs=payload / te / 1e9, reduce_us=tr * 1e6, reduce_gbs=payload / tr / 1e9)
                 cases.append(rec)
+    line = None
     if rank == 0:
         peaks = measured_peaks()
         top = max(cases, key=lambda c: c["payload_bytes"])
@@ -501,21 +745,21 @@ def run_halo_workload(args):
         else:
             per_gpu = top["payload_bytes"] / (world - 1)      # two faces land in an interior rank
             achieved, peak, bound = per_gpu / (top["exchange_us"] * 1e-6) / 1e9, 770.0, "nvlink"
-        print(json.dumps({
-            "metric": "halo_exchange_gbs", "value": top["exchange_gbs"], "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        line = {
+            "metric": "halo_exchange_gbs", "value": top["exchange_gbs"], "unit": "GB/s", "n_gpus": world, "steps": iters,
             "warmup": max(3, args.warmup), "ms_per_step": top["exchange_us"] / 1e3, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "halo_microbench", "tensor": [N, Cc, Hh, W], "layout": "NCHW",
                        "l2": "same buffers every iteration (payload smaller than L2; launch-latency dominated below ~10 MiB)"},
             "gpu_launches": int(L.ad_launch_count() - launches0),
-            "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None},
+            "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "peak_source": "measured copy bandwidth" if world == 1 else "peer copy rate measured on this pool, per direction"},
             "cases": cases,
-        }))
-    if world > 1:
-        dist.destroy_process_group()
+        }
+    return line
 
 
-# ----------------------------------------------------------------------------- config 3 through the C++ op graph
+# ----------------------------------------------------------------------------- nets through the C++ op graph
 def segnet_flops(N, Hh, W, classes=19, blocks=(3, 4, 6, 3), base=64):
     """fwd + dgrad + wgrad FLOPs of the dilated ResNet-50 segmentation net (2*N*K*C*kh*kw*P*Q per pass on the
     unpartitioned output, stem data gradient excluded)."""
@@ -552,24 +796,65 @@ def resnet50_flops(N, Hh, W, classes=1000):
     return total + 3.0 * 2.0 * N * classes * cin
 
 
-def run_net_workload(args, kind):
-    """`--workload stem_stage1`: benchmark config 3 -- ResNet-50 stem + stage 1 on one 3x1024x1024 image,
-    H-partitioned over the GPUs (or over `--strips` ranks sharing one GPU), bf16 operands, forward +
-    backward against an upstream gradient N(0,1), filter-gradient allreduce and SGD update, all through
-    the C++ host layer (zoo builder -> op graph -> C ABI kernels).  93.6 GFLOP per step (stem dgrad excluded).
-    `--workload segnet`: benchmark config 4 -- dilated ResNet-50 at output stride 8 on 2x3x1024x2048 with a
-    19-class head, x8 bilinear upsample and per-pixel softmax NLL against uniform random labels.
-    `--workload resnet50_hybrid`: benchmark config 5 -- ResNet-50 classifier on 224 x 224, global batch 256, the
-    GPUs in data-parallel groups of 2 H-strips each (8 GPUs: 4 data x 2 spatial; halos and the all-gather by peer
-    loads inside a group, filter gradients summed over all GPUs with NCCL).  On one GPU: one group (batch 64) as
-    2 strips sharing the device."""
+def conv_profile_of_step(abi, eager_step, sync, step_ms):
+    """One eagerly launched step with every convolution call bracketed by CUDA events on its stream (the library's
+    per-call timing): returns the roofline record of the shape that takes the most time and a short table."""
+    L = abi.load()
+    eager_step(); sync()
+    L.ad_conv2d_profile(1)
+    eager_step(); sync()
+    recs = abi.conv_profile_read()
+    L.ad_conv2d_profile(0)
+    groups = {}
+    for e in recs:
+        if e.ms < 0 or e.status != 0:
+            continue
+        key = (e.pass_, e.kernel, e.N, e.C, e.H, e.W, e.K, e.kh, e.kw, e.stride, e.dil, e.pad, e.out_rows)
+        g = groups.setdefault(key, [0.0, 0])
+        g[0] += e.ms; g[1] += 1
+    if not groups:
+        return None
+    names = {0: "fprop", 1: "dgrad", 2: "wgrad"}
+    fam = {1: "conv_direct_f32", 2: "conv_tc (general tiles)", 3: "conv_tc_row (row streaming)"}
+
+    def flops(key):
+        ps, kern, N, Cc, Hh, W, K, kh, kw, st, dil, pad, rows = key
+        P = (Hh + 2 * pad - dil * (kh - 1) - 1) // st + 1
+        Q = (W + 2 * pad - dil * (kw - 1) - 1) // st + 1
+        if rows:
+            P = rows
+        return 2.0 * N * K * Cc * kh * kw * P * Q
+
+    total = sum(g[0] for g in groups.values())
+    ranked = sorted(groups.items(), key=lambda kv: -kv[1][0])
+    peaks = measured_peaks()
+    table = []
+    for key, (ms, cnt) in ranked[:4]:
+        table.append({"pass": names[key[0]], "kernel": fam.get(key[1], "?"), "shape": {"N": key[2], "C": key[3], "H": key[4], "W": key[5], "K": key[6],
+                      "k": [key[7], key[8]], "stride": key[9], "dil": key[10]}, "launches": cnt, "us_per_launch": ms / cnt * 1e3,
+                      "tflops": flops(key) / (ms / cnt * 1e-3) / 1e12, "share_of_conv_time": ms / total})
+    key, (ms, cnt) = ranked[0]
+    achieved = flops(key) / (ms / cnt * 1e-3) / 1e12
+    return {"bound": "tensor", "kernel": f"{fam.get(key[1], '?')} {names[key[0]]} {key[3]}->{key[6]} {key[7]}x{key[8]} dil {key[10]} on {key[2]}x{key[4]}x{key[5]}",
+            "achieved": achieved, "peak": peaks["tf_sustained"], "unit": "TFLOP/s", "frac": achieved / peaks["tf_sustained"], "traffic": None,
+            "peak_source": peaks["source"] + " (sustained); kernel timed by CUDA events around its launches inside an eagerly launched step",
+            "conv_ms_per_step": total, "conv_share_of_step": total / step_ms if step_ms else None, "top": table}
+
+
+def run_net_workload(env, args, kind):
+    """`segnet`: benchmark config 4 -- dilated ResNet-50 at output stride 8 on 2x3x1024x2048 with a 19-class head, x8
+    bilinear upsample and per-pixel softmax NLL against uniform random labels.
+    `stem_stage1`: benchmark config 3 -- ResNet-50 stem + stage 1 on one 3x1024x1024 image, forward + backward against an
+    upstream gradient N(0,1).  93.6 GFLOP per step (stem dgrad excluded).
+    `resnet50_hybrid`: benchmark config 5 -- ResNet-50 classifier on 224 x 224, global batch 256, the GPUs in
+    data-parallel groups of 2 H-strips each (8 GPUs: 4 data x 2 spatial).  On one GPU: one group (batch 64) as 2 strips
+    sharing the device.
+    All H-partitioned over the GPUs (or over `--strips` ranks sharing one GPU), bf16 operands, filter-gradient allreduce and
+    SGD update, through the C++ host layer (zoo builder -> op graph -> C ABI kernels)."""
     import torch
-    import torch.distributed as dist
     from arraydiff_cuda_b200 import abi, hostlib
     from arraydiff_cuda_b200.dist import _Raw
-    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
+    rank, world, local, dist = env.rank, env.world, env.local, env.dist
     seg, hyb = kind == "segnet", kind == "resnet50_hybrid"
     S = 224 if hyb and args.image == 1024 else args.image
     Hh, Ww, NB = (S, 2 * S, 2) if seg else (S, S, 1)
@@ -584,8 +869,6 @@ def run_net_workload(args, kind):
     Lh = hostlib.load()
     keep = []
     if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         h = Lh.adh_context_create_distributed(srank, Sg, local, hostlib.BF16_NHWC,
                                               24576 if hyb else (40960 // world + 2048) if seg else 4096)
         hb = C.create_string_buffer(64)
@@ -681,186 +964,156 @@ def run_net_workload(args, kind):
     net.sync()
     assert net.status() == 0, "a bounded device wait timed out"
     streams = [torch.cuda.ExternalStream(Lh.adh_context_stream(ctx.h, r)) for r in ranks]
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
+
+    def marks():
+        out = []
+        for st in streams:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record(st)
+            out.append(e)
+        return out
+
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     launches0 = L.ad_launch_count()
-    e0 = torch.cuda.Event(enable_timing=True)
-    e0.record(streams[0])
-    for _ in range(args.steps):
-        step()
-    ends = []
-    for st in streams:
-        e = torch.cuda.Event(enable_timing=True)
-        e.record(st)
-        ends.append(e)
-    torch.cuda.synchronize()
-    ms = max(e0.elapsed_time(e) for e in ends)
-    launches = net.graph_launches() * args.steps if use_graph else L.ad_launch_count() - launches0
+    per, n, secs = timed_steps(env, step, marks, args.steps)
+    launches = net.graph_launches() * n if use_graph else L.ad_launch_count() - launches0
     clocks = sampler.stop() if rank == 0 else None
-    if world > 1:
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
     assert net.status() == 0
-    k_e2e = max(3, args.steps // 4)
-    if world > 1:
-        dist.barrier()
+    st = step_stats(per)
+    med = st["median"]
+
+    # end to end: host clock between synchronisations around k full steps
+    k_e2e = max(3, min(args.steps, int(1.0 / max(med * 3e-3, 1e-3))))
+    env.barrier()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     for _ in range(k_e2e):
-        e2e_step()
+        res = e2e_step()
     net.sync()
-    t_e2e = (time.perf_counter() - t0) / k_e2e
-    if world > 1:
-        t = torch.tensor([t_e2e], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        t_e2e = float(t.item())
+    t_e2e = float(env.max_over_ranks([(time.perf_counter() - t0) / k_e2e])[0])
+
+    # which convolution dominates, and how close to the tensor peak it runs
+    roof = conv_profile_of_step(abi, lambda: net.step_resident(True), net.sync, med)
+
+    # consistency record: no bounded wait ran out, the loss is finite, every replica holds the same parameters
+    loss = None
+    if seg or hyb:
+        lsum, lcnt = res
+        loss = lsum / max(1, lcnt)
+    sums = [float(np.sum(net.params(r).astype(np.float64))) for r in ranks]
+    lo = -env.max_over_ranks([-min(sums)])[0]
+    hi = env.max_over_ranks([max(sums)])[0]
+    verify = {"ok": bool(net.status() == 0 and lo == hi and (loss is None or math.isfinite(loss))),
+              "status_word": int(net.status()), "loss_per_pixel": loss, "param_sum_identical_on_all_ranks": bool(lo == hi),
+              "param_sum": float(hi)}
+
     scale = (S / 1024.0) ** 2
     flops = segnet_flops(NB, Hh, Ww) if seg else resnet50_flops(NB * D, Hh, Ww) if hyb else 93.6e9 * scale
+    line = None
     if rank == 0:
-        step_s = ms / args.steps * 1e-3
-        print(json.dumps({
+        step_s = med * 1e-3
+        line = {
             "metric": METRIC, "value": flops / step_s / 1e12, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "warmup": max(3, args.warmup), "ms_per_step": med, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "images_per_s": NB * D / step_s,
+            "timing": f"median of {n} individually timed steps run back to back over {secs:.2f} s (CUDA events, max over ranks per step)",
             "config": {"workload": "resnet50_dilated_segnet" if seg else f"resnet50_hybrid_{D}x{strips}" if hyb else "resnet50_stem_stage1",
                        "image": [NB * D, 3, Hh, Ww], "strips": strips, "data_groups": D, "layout": "NHWC",
                        "bn_statistics": "per strip (as the reference)", "update": "allreduce (%s) + Nesterov SGD" % ("nccl" if world > 1 and args.nccl_allreduce else "peer loads" if strips > 1 or D > 1 else "single rank"), "launch": "cuda graph" if use_graph else "eager",
+                       "flops_per_step": flops,
                        "l2": "activations of one step total more than 1 GB, larger than L2", "parallelism": f"data{D}-spatial-h{strips}" if hyb else f"spatial-h{strips}"},
-            "e2e": {"value": flops / t_e2e / 1e12, "unit": UNIT, "h2d_bytes_per_step": int(x.nbytes // (Sg if world > 1 else 1) + (labels.nbytes if hyb else labels.nbytes // world if seg else sum(d.nbytes for d in dy))),
-                    "d2h_bytes_per_step": int(NB * 4 if hyb else np.prod(net.strip_shape[2:]) * NB * 4 if seg else np.prod(net.strip_shape) * 4), "steps": k_e2e, "timing": "host clock between synchronisations"},
-            "gpu_launches": int(launches), "clocks": clocks,
-        }))
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+            "e2e": {"value": flops / t_e2e / 1e12, "unit": UNIT, "images_per_s": NB * D / t_e2e,
+                    "h2d_bytes_per_step": int(x.nbytes // (Sg if world > 1 else 1) + (labels.nbytes if hyb else labels.nbytes // world if seg else sum(d.nbytes for d in dy))),
+                    "d2h_bytes_per_step": int(NB * 4 * len(ranks) if hyb else np.prod(net.strip_shape[2:]) * NB * 4 * len(ranks) if seg else np.prod(net.strip_shape) * 4), "steps": k_e2e,
+                    "timing": "host clock between synchronisations",
+                    "boundary": "pinned host NCHW fp32 images and uint32 labels through the host layer's public calls; copies and the conversion to bf16 NHWC are inside"},
+            "gpu_launches": int(launches), "timed_steps": n, "timed_region_s": secs, "step_ms": st,
+            "roofline": roof, "verify": verify, "clocks": clocks,
+        }
+    env.barrier()
+    _KEEP_ALIVE.append((net, ctx, keep))     # arenas stay mapped in the peers until the process ends
+    return line
+
+
+_KEEP_ALIVE = []
+
+
+def compact(line):
+    """What an `also` entry keeps of a workload's line."""
+    if line is None:
+        return None
+    keep = ("metric", "value", "unit", "ms_per_step", "images_per_s", "timing", "timed_region_s", "gpu_launches", "step_ms",
+            "halo_exposed_ms", "roofline", "verify", "e2e", "cpu_baseline", "cases", "error")
+    out = {k: line[k] for k in keep if k in line}
+    out["workload"] = line.get("config", {}).get("workload")
+    return out
 
 
 def main():
-    global BATCH
+    global BATCH, MIN_SECONDS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
-    ap.add_argument("--workload", default="conv", choices=["conv", "halo", "stem_stage1", "segnet", "resnet50_hybrid"],
-                    help="conv: the headline spatial conv step; halo: the halo-exchange microbenchmark (config 2); "
-                         "stem_stage1: ResNet-50 stem + stage 1 through the C++ op graph (config 3); "
-                         "segnet: dilated ResNet-50 segmentation net, 2x3x1024x2048 (config 4; --image = height); "
+    ap.add_argument("--workload", default="all", choices=["all", "segnet", "conv", "halo", "stem_stage1", "resnet50_hybrid"],
+                    help="all: segnet as the headline with the others under `also`; segnet: dilated ResNet-50 segmentation net, "
+                         "2x3x1024x2048 (config 4; --image = height); conv: the spatial conv microbenchmark step; halo: the "
+                         "halo-exchange microbenchmark (config 2); stem_stage1: ResNet-50 stem + stage 1 (config 3); "
                          "resnet50_hybrid: ResNet-50 classifier, 224 x 224, batch 256, data-parallel groups of 2 strips (config 5)")
-    ap.add_argument("--strips", type=int, default=1, help="stem_stage1 on one GPU: ranks sharing the device")
-    ap.add_argument("--image", type=int, default=1024, help="stem_stage1: image height = width")
+    ap.add_argument("--strips", type=int, default=1, help="net workloads on one GPU: ranks sharing the device")
+    ap.add_argument("--image", type=int, default=1024, help="net workloads: image height")
     ap.add_argument("--nccl-allreduce", action="store_true",
-                    help="stem_stage1 / segnet on several GPUs: sum the filter gradients with NCCL instead of the built-in peer exchange")
-    ap.add_argument("--no-graph", action="store_true", help="stem_stage1: launch every kernel eagerly instead of replaying a CUDA graph")
+                    help="net workloads on several GPUs: sum the filter gradients with NCCL instead of the built-in peer exchange")
+    ap.add_argument("--no-graph", action="store_true", help="net workloads: launch every kernel eagerly instead of replaying a CUDA graph")
     ap.add_argument("--batch", type=int, default=BATCH,
-                    help="images per step; the default is the workload's, smaller values are for profiler captures")
+                    help="conv: images per step; the default is the workload's, smaller values are for profiler captures")
+    ap.add_argument("--min-seconds", type=float, default=MIN_SECONDS, help="least length of every timed region")
     args = ap.parse_args()
     BATCH = args.batch
+    MIN_SECONDS = args.min_seconds
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference_arm(args)
         return
-    if args.workload == "halo":
-        run_halo_workload(args)
+
+    env = Env(args.gpus)
+    runners = {
+        "segnet": lambda: run_net_workload(env, args, "segnet"),
+        "conv": lambda: run_conv_workload(env, args),
+        "halo": lambda: run_halo_workload(env, args),
+        "stem_stage1": lambda: run_net_workload(env, args, "stem_stage1"),
+        "resnet50_hybrid": lambda: run_net_workload(env, args, "resnet50_hybrid"),
+    }
+    if args.workload != "all":
+        line = runners[args.workload]()
+        if env.rank == 0:
+            print(json.dumps(line))
+        env.close()
         return
-    if args.workload in ("stem_stage1", "segnet", "resnet50_hybrid"):
-        run_net_workload(args, args.workload)
-        return
 
-    import torch
-    import torch.distributed as dist
-    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
-    if SIZE % world:
-        raise SystemExit("image height must divide by the number of GPUs")
-    torch.cuda.set_device(local)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-
-    from arraydiff_cuda_b200 import abi
-    L = abi.load()   # raises if the CUDA library is missing: no fallback
-    step = Step(rank, world)
-    for _ in range(args.warmup):
-        step.run()
-    torch.cuda.synchronize()
-    step.check_status()
-
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    launches0 = L.ad_launch_count()
-    ms = timed_loop(torch, dist, step, args.steps, False, world)
-    launches = L.ad_launch_count() - launches0
-    clocks = sampler.stop() if rank == 0 else None
-    step.check_status()
-    for _ in range(2):
-        step.run(e2e=True)
-    e2e_steps = max(3, args.steps // 4)
-    ms_e2e = timed_loop(torch, dist, step, e2e_steps, True, world)
-    step.check_status()
-
-    med, p10, p90 = step_distribution(torch, dist, step, max(100, args.steps), world)
-    ms_nohalo = None
-    if world > 1:
-        step.halo = False
-        for _ in range(3):
-            step.run()
-        ms_nohalo = timed_loop(torch, dist, step, args.steps, False, world)
-        step.halo = True
-    kt_step = kernel_times_in_step(torch, dist, step, args.steps, world)
-    step.check_status()
-
-    total_flops = 3 * flops_per_pass()
-    value = total_flops / (ms / args.steps * 1e-3) / 1e12
-    e2e_value = total_flops / (ms_e2e / e2e_steps * 1e-3) / 1e12
-    if rank == 0:
-        peaks = measured_peaks()
-        kt = kernel_times(torch, step)
-        top = max(kt_step, key=kt_step.get)
-        per_launch_flops = flops_per_pass(BATCH, step.h, SIZE)
-        achieved = per_launch_flops / kt_step[top] / 1e12
-        cpu = None
-        if world == 1:
-            v, dt, rows, cores = cpu_conv_sample(args.cpu_seconds)
-            cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
-                   "sample": f"oracle conv fwd+dgrad+wgrad on a {rows}-row x {SIZE}-col strip of one image ({dt:.1f} s)"}
-        hbytes = step.hx_host.numel() * 2 + step.dy_host.numel() * 2
-        line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "microbench_spatial_conv", "batch": BATCH, "channels": CH, "image": [SIZE, SIZE],
-                       "kernel": KS, "dilation": DIL, "halo": PAD, "strips": world, "layout": "NHWC",
-                       "l2": "inputs larger than L2 (%.2f GB activations per pass)" % (BATCH * SIZE * SIZE * CH * 2 / 1e9), "parallelism": f"spatial-h{world}"},
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": hbytes,
-                    "d2h_bytes_per_step": step.dw_host.numel() * 4, "steps": e2e_steps},
-            "gpu_launches": int(launches),
-            "step_ms": {"median": med, "p10": p10, "p90": p90, "samples": max(100, args.steps)},
-            "halo_exposed_ms": None if ms_nohalo is None else ms / args.steps - ms_nohalo / args.steps,
-            "roofline": {"bound": "tensor", "kernel": f"conv_tc_{top}", "achieved": achieved, "peak": peaks["tf_sustained"],
-                         "unit": "TFLOP/s", "frac": achieved / peaks["tf_sustained"],
-                         "traffic": NCU_TRAFFIC_BATCH4[top] * BATCH / 4 / world,
-                         "peak_source": peaks["source"] + " (sustained: the kernel is timed with CUDA events inside full steps run back to back)",
-                         "kernels_us": {k: v * 1e6 for k, v in kt_step.items()},
-                         "kernels_alone_us": {k: v * 1e6 for k, v in kt.items()},
-                         "frac_alone_of_burst": per_launch_flops / kt[top] / 1e12 / peaks["tf_burst"]},
-            "clocks": clocks,
-        }
-        if cpu:
-            line["cpu_baseline"] = cpu
+    line = runners["segnet"]()
+    also = {}
+    for name in ("conv", "halo", "stem_stage1", "resnet50_hybrid"):
+        if name == "resnet50_hybrid" and env.world > 1 and env.world % 2:
+            continue
+        try:
+            also[name] = compact(runners[name]())
+        except Exception as e:      # keep the headline; say what failed
+            also[name] = {"error": f"{type(e).__name__}: {e}"}
+    if env.rank == 0:
+        if env.world == 1:
+            v, dt, rows, cores = cpu_conv_sample(args.cpu_seconds, **SEG_CPU_LAYER)
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
+                                    "sample": f"oracle conv fwd+dgrad+wgrad of one stage-3 layer of the net (3x3, 256->256, dilation 2) on a {rows}-row x 256-col strip of one image ({dt:.1f} s)"}
+        conv_v = (also.get("conv") or {}).get("verify") or {}
+        line["verify"] = {"ok": bool(line["verify"]["ok"] and conv_v.get("ok", False)), "net": line["verify"], "conv_step": conv_v}
+        line["also"] = also
         print(json.dumps(line))
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    env.close()
 
 
 if __name__ == "__main__":

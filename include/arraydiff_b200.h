@@ -253,7 +253,9 @@ int ad_bn_bwd(const ad_tensor4* x, const ad_tensor4* dy, const ad_tensor4* dx, c
  * ends); more channels are refused with AD_ERR_LIMIT.  Inputs and outputs are still the
  * caller's.  Nothing is allocated or freed, here or in anything this calls.
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
- * that device current); make that first call before any stream capture starts.
+ * that device current); make that first call before any stream capture starts.  The address is
+ * the one of the CURRENT device: the device that owns `stream` and the tensors must be current, as
+ * for every entry point.  First calls from several host threads at once are safe.
  * All calls share the one array: two calls that can overlap on the GPU (different streams
  * without an ordering between them) race on it and give wrong statistics -- order them.
  */
@@ -406,6 +408,25 @@ int ad_conv2d_wgrad(const ad_conv2d_args* a, void* stream);
  * (CudnnConv2DSize, src/op.cc:1424-1510); here a caller (and the parity tests) can ask which path served a shape.
  */
 int32_t ad_conv2d_last_kernel(void);
+/*
+ * Per-call device timing of the three convolution entry points, for measurement runs.  While enabled every
+ * ad_conv2d_* call is bracketed by two CUDA events on its stream (so the figure is what the call cost inside the
+ * step it ran in: warm clocks, neighbouring work alongside); ad_conv2d_profile_read waits for the recorded events
+ * and copies out up to max_entries records in call order (NULL: just the count).  ad_conv2d_profile(0 or 1) drops
+ * what was recorded.  This is the one place the library creates CUDA events; nothing is recorded while disabled,
+ * and a stream under capture must not be profiled.  The reference has no per-operator timing (its tools time whole
+ * loops with the host clock, tools/microbench_spatial_conv.cc:161-214).
+ */
+typedef struct {
+  int32_t pass;    /* 0 fprop, 1 dgrad, 2 wgrad */
+  int32_t kernel;  /* as ad_conv2d_last_kernel */
+  int32_t status;  /* what the call returned */
+  uint32_t N, C, H, W, K, kh, kw, stride, dil, pad;
+  uint32_t out_rows; /* fprop: out_row_count of the call (0 = all rows) */
+  float ms;        /* device time between the two events */
+} ad_conv2d_profile_entry;
+int ad_conv2d_profile(int32_t enable);
+size_t ad_conv2d_profile_read(ad_conv2d_profile_entry* out, size_t max_entries);
 
 #ifdef __cplusplus
 }

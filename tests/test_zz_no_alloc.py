@@ -54,6 +54,16 @@ def test_noalloc_batch_norm_matches_existing_entry_point_twice_in_a_row():
             assert H.max_rel(b, a) < 1e-5
 
 
+@pytest.mark.parametrize("shape", [(2, 64, 31, 20), (1, 256, 9, 33), (1, 2048, 6, 7)])
+def test_noalloc_batch_norm_vector_kernels_and_channel_limit(shape):
+    # 64 and 256 channels take the 16-byte vector kernels; 2048 channels use the built-in array to its last byte
+    N, Cc, Hh, W = shape
+    for seed, relu in ((300, 0), (400, 1)):
+        ref, got = _run_pair(seed + Cc, N, Cc, Hh, W, relu)
+        for a, b in zip(ref, got):
+            assert H.max_rel(b, a) < 1e-5
+
+
 def test_noalloc_batch_norm_refuses_more_channels_than_its_array_holds():
     import torch
     L = abi.lib()
