@@ -92,6 +92,7 @@ SIGNATURES = {
     "ad_bn_scratch_bytes": (sz, [u32]),
     "ad_bn_fwd_train": (C.c_int, [C.POINTER(Tensor4), C.POINTER(Tensor4), vp, vp, vp, vp, vp, f32, i32, vp, sz, vp]),
     "ad_bn_fwd_train_noalloc": (C.c_int, [C.POINTER(Tensor4), C.POINTER(Tensor4), vp, vp, vp, vp, vp, f32, i32, vp]),
+    "ad_bn_fwd_inference": (C.c_int, [C.POINTER(Tensor4), C.POINTER(Tensor4), vp, vp, vp, vp, vp, f32, i32, vp]),
     "ad_bn_bwd": (C.c_int, [C.POINTER(Tensor4)] * 3 + [vp, vp, vp, vp, vp, vp, i32, i32, vp, sz, vp]),
     "ad_bn_partial_stats": (C.c_int, [C.POINTER(Tensor4), vp, vp, sz, vp]),
     "ad_bn_finalize_apply": (C.c_int, [C.POINTER(Tensor4), C.POINTER(Tensor4), vp, C.c_double, vp, vp, vp, vp, vp, f32, i32, vp]),

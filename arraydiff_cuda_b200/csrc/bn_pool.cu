@@ -670,6 +670,30 @@ extern "C" int ad_bn_fwd_train(const ad_tensor4* x, const ad_tensor4* y, const f
   return launch_status();
 }
 
+// invstd[c] = 1 / sqrt(var[c] + eps), in double as the training path does
+__global__ void bn_invstd_kernel(uint32_t C, const float* __restrict__ var, float eps, float* __restrict__ invstd) {
+  const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c < C) invstd[c] = (float)(1.0 / sqrt((double)var[c] + (double)eps));
+}
+
+extern "C" int ad_bn_fwd_inference(const ad_tensor4* x, const ad_tensor4* y, const float* gamma, const float* beta,
+                                   const float* mean, const float* var, float* invstd_out, float eps, int32_t relu,
+                                   void* stream) {
+  if (!x || !y || !x->base || !y->base || !gamma || !beta || !mean || !var || !invstd_out) return AD_ERR_BAD_ARG;
+  if (!dims_eq(x, y)) return AD_ERR_BAD_ARG;
+  const size_t total = (size_t)x->N * x->C * x->H * x->W;
+  if (total == 0) return AD_OK;
+  cudaStream_t s = as_stream(stream);
+  bn_invstd_kernel<<<(x->C + 255) / 256, 256, 0, s>>>(x->C, var, eps, invstd_out);
+  count_launch();
+  BnApply a{bview(x), bview(x), bview(y), x->N, x->C, x->H, x->W, y->sc == 1 && y->C > 1, relu, 0,
+            gamma, beta, mean, invstd_out, nullptr, 1, (double)x->N * x->H * x->W};
+  if (vec_view_ok(x) && vec_view_ok(y)) bn_apply_vec<0><<<kNumSMs * 4, 256, 0, s>>>(a);
+  else AD_DISPATCH_DTYPE(x->dtype, (bn_apply<T, 0><<<grid_for(total, 256, 16), 256, 0, s>>>(a)));
+  count_launch();
+  return launch_status();
+}
+
 extern "C" int ad_bn_bwd(const ad_tensor4* x, const ad_tensor4* dy, const ad_tensor4* dx, const float* gamma,
                          const float* beta, const float* save_mean, const float* save_invstd, float* dgamma,
                          float* dbeta, int32_t relu, int32_t accumulate_dx, void* scratch, size_t scratch_bytes,

@@ -15,7 +15,9 @@ def _stale():
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
-    deps = [os.path.join(HERE, "src", s) for s in SOURCES]
+    deps = [os.path.join(HERE, "src", s) for s in SOURCES] + [os.path.join(HERE, "tools", "train_dummy.cc")]
+    if not os.path.exists(os.path.join(HERE, "tools", "train_dummy")):
+        return True
     inc = os.path.join(HERE, "include", "arraydiff")
     deps += [os.path.join(inc, f) for f in os.listdir(inc)] + [os.path.join(ROOT, "include", "arraydiff_b200.h")]
     return any(os.path.getmtime(d) > t for d in deps)
@@ -33,6 +35,12 @@ def build(force=False):
            *[os.path.join(HERE, "src", s) for s in SOURCES], "-o", LIB,
            "-L", PKG, "-larraydiff_b200", "-L", os.path.join(cuda, "lib64"), "-lcudart", "-Wl,-rpath,$ORIGIN"]
     subprocess.check_call(cmd)
+    # the training driver on synthetic data (the reference's tools/train_imagenet.cc loop over DummyData)
+    tool = os.path.join(HERE, "tools", "train_dummy")
+    subprocess.check_call([cxx, "-O2", "-std=c++17", "-Wall", "-Wno-unused-function", "-I", os.path.join(HERE, "include"),
+                           "-I", os.path.join(ROOT, "include"), "-I", os.path.join(cuda, "include"),
+                           os.path.join(HERE, "tools", "train_dummy.cc"), "-o", tool, "-L", PKG, "-larraydiff_host",
+                           "-larraydiff_b200", "-L", os.path.join(cuda, "lib64"), "-lcudart", "-Wl,-rpath,$ORIGIN/../.."])
     return LIB
 
 

@@ -110,6 +110,9 @@ public:
   // rows [row0, row0 + h) of a packed NCHW fp32 host tensor of full_h rows: one pitched copy, so that a rank
   // receives its strip and nothing else
   void load_host_nchw_rows(const float* src_full, size_t full_h, size_t row0, GPUContext* ctx) const;
+  // rows [row0, row0 + h) of a batch of full_h-row images stored [image][row][column][channel] fp32 on the host, every
+  // element multiplied by `scale` on the way in
+  void load_host_nhwc_rows(const T* src_full, size_t full_h, size_t row0, float scale, GPUContext* ctx) const;
   void store_host_nchw(float* dst, GPUContext* ctx) const;
 private:
   Shape3D dim_, offset_, stride_;

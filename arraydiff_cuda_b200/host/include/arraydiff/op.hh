@@ -30,6 +30,7 @@
 
 #include "arraydiff/array_gpu.hh"
 #include "arraydiff/context.hh"
+#include "arraydiff/slice.hh"
 #include "arraydiff/spatial.hh"
 
 namespace arraydiff {
@@ -269,7 +270,18 @@ public:
   string _debug_op_label() override { return "IOOp"; }
   void set_name(const string& n) { name_ = n; }
   const string& name() const { return name_; }
+  // An activation input that holds rows [row0, row0 + h) of a batch of full_h-row images: a reader that carries the
+  // WHOLE batch (float* / Slice<float>) is then cut on load -- every rank takes its rows of the same host buffer and
+  // the flat offset advances by the strip's share, so that all ranks' inputs together account for the batch once.
+  // nhwc: the host batch is [image][row][column][channel] (the reference's raw input, Shape3D(3, w, h), src/zoo.cc:1503);
+  // host_scale multiplies every element on the way in (its ScaleOp(1/255), src/zoo.cc:1515).
+  void set_rows_of_full(size_t full_h, size_t row0, bool nhwc, float host_scale) {
+    full_h_ = full_h; row0_ = row0; host_nhwc_ = nhwc; host_scale_ = host_scale;
+  }
 private:
+  size_t full_h_ = 0, row0_ = 0;
+  bool host_nhwc_ = false;
+  float host_scale_ = 1.0f;
   string name_;
   typename A::Shape dim_;
   size_t batch_, rank_;
@@ -437,8 +449,10 @@ private:
   ActVar x_;
 };
 
-// Spatial batch norm with batch statistics of THIS rank's strip (the reference's behaviour,
-// src/op.cc:3988-4003) or, with set_sync_stats(true), of all ranks' strips together.
+// Spatial batch norm with batch statistics of THIS rank's strip (the reference's behaviour, src/op.cc:3988-4003).
+// When the net's switch variable is set the forward pass normalises with the fixed (running) statistics instead
+// (src/op.cc:3964-3978); like the reference, that mode has no backward pass.  Statistics over all ranks' strips
+// together are available at the C ABI (ad_bn_partial_stats / ad_bn_finalize_apply), not through this operator.
 class CudnnBatchNorm2DOpF : public ActOp {
 public:
   typedef GPUArray1D<float> Stat;
@@ -455,7 +469,7 @@ public:
 private:
   shared_ptr<bool> switch_var_;
   ActVar x_;
-  shared_ptr<IOOp<Stat>> scale_, shift_, batch_mean_, batch_variance_;
+  shared_ptr<IOOp<Stat>> scale_, shift_, batch_mean_, batch_variance_, fixed_mean_, fixed_variance_;
   float *save_mean_ = nullptr, *save_invstd_ = nullptr;
   bool relu_ = false;
 };
@@ -564,6 +578,15 @@ public:
   string _debug_op_label() override { return "CudnnSoftmaxNLLLossOp"; }
   size_t rank() const { return x_->rank(); }
   size_t pixels() const { return n_ * hw_; }
+  // Labels and per-pixel losses as graph variables, so that load_val / store_val reach them the way the reference's
+  // tools do (net.labels with a Slice<uint32_t> reader, net.losses with a Slice<float> writer,
+  // tools/train_imagenet.cc:220-243).  With `replica` set this operator is a copy of another rank's (every rank scores
+  // the whole batch): it loads the same labels but does not advance the flat offset, and stores nothing.
+  VarId label_var() const { return label_var_; }
+  VarId loss_var() const { return loss_var_; }
+  void set_replica(bool r) { replica_ = r; }
+  size_t _load_val(TxnId txn, VarIdSet& vars, size_t offset, any* reader) override;
+  size_t _store_val(TxnId txn, VarIdSet& vars, size_t offset, any* writer) override;
   void load_labels(const uint32_t* host);      // synchronous host -> device copy
   void set_loss_weight(float w);
   double loss_sum();                           // synchronous: sum of the per-pixel losses of the last forward
@@ -574,6 +597,8 @@ private:
   size_t n_, hw_, classes_;
   uint32_t* labels_ = nullptr;
   float *loss_ = nullptr, *dloss_ = nullptr;
+  VarId label_var_, loss_var_;
+  bool replica_ = false;
 };
 
 // Joins the per-rank sub-graphs under one root so that a single walk orders every rank's operators

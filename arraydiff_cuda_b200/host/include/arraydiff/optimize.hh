@@ -8,6 +8,7 @@
 #define ARRAYDIFF_OPTIMIZE_HH
 
 #include <map>
+#include <utility>
 
 #include "arraydiff/op.hh"
 
@@ -27,19 +28,41 @@ public:
 private:
   T v_;
 };
-// value changes at the given iterations: {0: a, 1000: b, ...}
+// `init` until the first step, then each value from its step on: PiecewiseStepSchedule(0.1, 150000, 0.01, 300000, 0.001)
+// (the argument forms of the reference, include/arraydiff/optimize.hh:44-90), or a map {step: value}.
 template <typename T>
 class PiecewiseStepSchedule : public Schedule<T> {
 public:
+  explicit PiecewiseStepSchedule(T init) : init_(init) {}
   PiecewiseStepSchedule(T init, std::map<size_t, T> steps) : init_(init), steps_(steps) {}
+  PiecewiseStepSchedule(T init, vector<std::pair<size_t, T>> pieces) : init_(init) { for (auto& p : pieces) steps_[p.first] = p.second; }
+  template <typename... Rest>
+  PiecewiseStepSchedule(T init, size_t step1, T val1, Rest... rest) : init_(init) { add(step1, val1, rest...); }
   T at(size_t it) override {
     T v = init_;
     for (auto& kv : steps_) if (it >= kv.first) v = kv.second;
     return v;
   }
 private:
+  void add() {}
+  template <typename... Rest> void add(size_t step, T val, Rest... rest) { steps_[step] = val; add(rest...); }
   T init_;
   std::map<size_t, T> steps_;
+};
+// linear from `init` at step 0 to `val1` at `step1`, constant afterwards (reference :92-130)
+template <typename T>
+class PiecewiseLinearSchedule : public Schedule<T> {
+public:
+  explicit PiecewiseLinearSchedule(T init) : init_(init), step1_(0), val1_(init) {}
+  PiecewiseLinearSchedule(T init, size_t step1, T val1) : init_(init), step1_(step1), val1_(val1) {}
+  T at(size_t it) override {
+    if (step1_ == 0 || it >= step1_) return val1_;
+    return init_ + (val1_ - init_) * (T)it / (T)step1_;
+  }
+private:
+  T init_;
+  size_t step1_;
+  T val1_;
 };
 
 class SGDConfig {
@@ -59,6 +82,12 @@ public:
   // `sink` joins every rank's sub-graph; params / grads are the per-rank variable sets.
   ParallelSGDOptimizer(SGDConfig cfg, shared_ptr<Op> sink, vector<VarIdSet> params, vector<VarIdSet> grads)
       : cfg_(cfg), sink_(sink), params_(params), grads_(grads), param_dim_(0), iter_count_(0) {}
+  // The reference's constructor (include/arraydiff/optimize.hh:265): batch_stats are the per-rank sets of the batch
+  // normalisation layers' batch mean / variance variables, fixed_stats the matching running statistics.
+  ParallelSGDOptimizer(SGDConfig cfg, shared_ptr<Op> sum_loss, vector<VarIdSet> params, vector<VarIdSet> grads,
+                       vector<VarIdSet> batch_stats, vector<VarIdSet> fixed_stats)
+      : cfg_(cfg), sink_(sum_loss), params_(params), grads_(grads), batch_stats_(batch_stats), fixed_stats_(fixed_stats),
+        param_dim_(0), iter_count_(0) {}
 
   size_t param_dim() const { return param_dim_; }
   size_t iteration() const { return iter_count_; }
@@ -75,6 +104,22 @@ public:
   // Draws the initial parameters, makes every rank's replica equal to rank 0's and sets up the flat
   // parameter / gradient / momentum buffers (reference :314-386).
   void reset(shared_ptr<Context> ctx, std::mt19937_64* rng);
+  // The reference's form (:314-386): the graph was initialised by the caller (op->init); rank 0's parameters and
+  // running statistics become every rank's, the flat buffers are set up.
+  void reset(shared_ptr<Context> parallel_ctx);
+  // The reference's training step (:389-564): ceil(minibatch / compute batch) micro-batches, each a fresh transaction
+  // handed to `compute_batch_fn(txn, batch size, loss)` (which persists the parameters, loads data and calls
+  // loss->gradient(txn)); gradients are summed over micro-batches, batch statistics averaged; then the gradient is
+  // summed over ranks, L2 + (Nesterov) momentum SGD is applied, the running statistics move towards the step's
+  // average batch statistics by batch_norm_rate, and parameters / statistics are loaded back into the graph.
+  // Differs from the reference in the data movement only: all-reduce and update on every rank instead of
+  // reduce -> update on rank 0 -> broadcast.
+  void step(function<void(TxnId, size_t, shared_ptr<Op>)>& compute_batch_fn, shared_ptr<Context> parallel_ctx);
+  void step(function<void(TxnId, size_t, shared_ptr<Op>)>&& compute_batch_fn, shared_ptr<Context> parallel_ctx) {
+    step(compute_batch_fn, parallel_ctx);
+  }
+  size_t stat_dim() const { return stat_dim_; }
+  void store_fixed_stats(size_t rank, float* host);
   // To be called after the gradients of transaction `txn` exist on every rank: gathers them into the
   // flat buffer, sums over ranks, applies L2 + (Nesterov) momentum SGD on every rank, and loads the
   // new parameters back into the graph (reference :407-561).
@@ -89,8 +134,9 @@ public:
 private:
   SGDConfig cfg_;
   shared_ptr<Op> sink_;
-  vector<VarIdSet> params_, grads_;
-  size_t param_dim_, iter_count_;
+  vector<VarIdSet> params_, grads_, batch_stats_, fixed_stats_;
+  size_t param_dim_, iter_count_, stat_dim_ = 0;
+  vector<GPUMemory<T>> batch_grad_, batch_stat_, avg_stat_, running_stat_;
   MultiGPUContext* mgpu_ = nullptr;
   shared_ptr<Context> ctx_;
   vector<GPUMemory<T>> param_, sum_grad_, momentum_;

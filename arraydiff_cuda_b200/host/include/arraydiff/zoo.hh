@@ -65,6 +65,40 @@ struct SpatialParallelNet {
   vector<VarIdSet> dev_params, dev_grads, dev_batch_stats, dev_fixed_stats;
 };
 
+// What the reference's builders hand to a training tool (include/arraydiff/zoo.hh:140-158): the graph's root, the
+// variable sets a tool loads and stores through (one batch of inputs and labels in, logits and per-image losses out),
+// and the per-rank parameter / gradient / statistics sets the optimizer walks.  The three class parameters of the
+// reference (array types of logits, losses and the summed loss) are kept for spelling only: every variable here is
+// reached through shared_ptr<Op>.
+template <typename Logit = Act, typename Loss = Act, typename SumLoss = Act>
+class ParallelCategoricalNLLBatchNormLoss {
+public:
+  shared_ptr<bool> batch_norm_use_fixed;
+  shared_ptr<Op> op;          // where a tool starts op->init from: the root, so that every rank's variables are drawn
+  shared_ptr<Op> loss;        // rank 0's per-image loss
+  shared_ptr<Op> sum_loss;    // the root of the whole graph: persist / load_val / gradient / store_val start here
+  VarIdSet inputs;            // every rank's input strip: together one batch of whole images
+  VarIdSet labels;
+  VarIdSet logits;
+  VarIdSet losses;
+  vector<VarIdSet> dev_params;
+  vector<VarIdSet> dev_grads;
+  vector<VarIdSet> dev_batch_stats;
+  vector<VarIdSet> dev_fixed_stats;
+  SpatialParallelNet net;     // the underlying per-rank view
+};
+
+// The reference's entry points for its training tools (include/arraydiff/zoo.hh:175-183, src/zoo.cc:1475-1909,
+// :2200-2484): 1000 classes; host images are read as [image][row][column][channel] floats in 0..255 and scaled by
+// 1/255 on load (the reference's TransposeNHWCToNCHWOp + ScaleOp in front of the net), each rank taking its rows; the
+// loss is the mean over config.minibatch_size images.
+template <typename T>
+class ResNet {
+public:
+  static ParallelCategoricalNLLBatchNormLoss<> MakeParallelResNet18(const ConvNetConfig& config, shared_ptr<Context> ctx);
+  static ParallelCategoricalNLLBatchNormLoss<> MakeParallelResNet50(const ConvNetConfig& config, shared_ptr<Context> ctx);
+};
+
 template <typename T>
 class SpatialParallelResNet {
 public:

@@ -2,6 +2,7 @@
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <sstream>
 
 #include "arraydiff/op.hh"
@@ -90,7 +91,13 @@ shared_ptr<MultiGPUContext> MultiGPUContext::Make() {
     CUDA_CHECK(cudaGetDeviceCount(&n));
     for (int i = 0; i < n; ++i) devs.push_back(i);
   }
-  return Make(devs);
+  // ARRAYDIFF_B200_MODE=bf16 selects the tensor-core path (default: the reference's fp32 NCHW arithmetic);
+  // ARRAYDIFF_B200_ARENA_MB sizes each rank's arena
+  ComputeMode mode = COMPUTE_F32_NCHW;
+  if (const char* m = std::getenv("ARRAYDIFF_B200_MODE")) if (!std::strcmp(m, "bf16")) mode = COMPUTE_BF16_NHWC;
+  size_t arena = 0;
+  if (const char* a = std::getenv("ARRAYDIFF_B200_ARENA_MB")) arena = (size_t)std::strtoull(a, nullptr, 10) << 20;
+  return Make(devs, mode, arena);
 }
 shared_ptr<MultiGPUContext> MultiGPUContext::Make(const vector<int>& devices, ComputeMode mode, size_t arena_bytes) {
   return make_shared<MultiGPUContext>(devices, mode, arena_bytes, false, 0, devices.size());
@@ -413,6 +420,24 @@ void GPUBatchArray3D<float>::load_host_nchw_rows(const float* src_full, size_t f
   CUDA_CHECK(cudaMemcpy2DAsync(tmp, (size_t)(H * W) * sizeof(float), src_full + row0 * (size_t)W, full_h * (size_t)W * sizeof(float),
                                (size_t)(H * W) * sizeof(float), (size_t)C * batch_, cudaMemcpyHostToDevice, conn.stream()));
   ad_tensor4 s = {tmp, AD_F32, (uint32_t)batch_, (uint32_t)C, (uint32_t)H, (uint32_t)W, C * H * W, H * W, W, 1};
+  ad_tensor4 d = view_interior();
+  AD_CHECK(ad_convert(&s, &d, 0, conn.stream()));
+  conn.sync();
+}
+template <>
+void GPUBatchArray3D<float>::load_host_nhwc_rows(const float* src_full, size_t full_h, size_t row0, float scale, GPUContext* ctx) const {
+  const size_t n = dim_.flat_size() * batch_;
+  GPUConn conn = ctx->conn();
+  ctx->reserve_scratch(n * sizeof(float));
+  float* tmp = (float*)ctx->get_scratch();
+  const long long W = dim_.shape[0], H = dim_.shape[1], C = dim_.shape[2];
+  assert(row0 + (size_t)H <= full_h);
+  // one contiguous block of H*W*C floats per image
+  CUDA_CHECK(cudaMemcpy2DAsync(tmp, (size_t)(H * W * C) * sizeof(float), src_full + row0 * (size_t)(W * C),
+                               full_h * (size_t)(W * C) * sizeof(float), (size_t)(H * W * C) * sizeof(float), batch_,
+                               cudaMemcpyHostToDevice, conn.stream()));
+  if (scale != 1.0f) AD_CHECK(ad_array_scale(n, scale, tmp, tmp, conn.stream()));
+  ad_tensor4 s = {tmp, AD_F32, (uint32_t)batch_, (uint32_t)C, (uint32_t)H, (uint32_t)W, H * W * C, 1, W * C, C};
   ad_tensor4 d = view_interior();
   AD_CHECK(ad_convert(&s, &d, 0, conn.stream()));
   conn.sync();

@@ -21,6 +21,12 @@ static size_t num_ranks_of(const shared_ptr<Context>& ctx, size_t fallback) {
   if (auto m = dynamic_cast<MultiGPUContext*>(ctx.get())) return m->num_ranks();
   return fallback;
 }
+// the host float range behind a reader / writer: float* or Slice<float>
+static float* host_floats(any* a) {
+  if (auto hp = std::any_cast<float*>(a)) return *hp;
+  if (auto sp = std::any_cast<Slice<float>>(a)) return sp->ptr;
+  return nullptr;
+}
 GPUContext* ActOp::gpu() { return gpu_of(ctx_, rank_); }
 MultiGPUContext* ActOp::mgpu() { return dynamic_cast<MultiGPUContext*>(ctx_.get()); }
 
@@ -38,19 +44,19 @@ size_t ActOp::_load_grad(TxnId txn, VarIdSet& vars, size_t offset, any* reader) 
   if (!vars.mask(y_.grad.var())) return offset;
   y_.grad.stamp(txn);
   Act& a = y_.grad.raw();
-  if (reader) { auto hp = std::any_cast<float*>(reader); assert(hp); a.load_host_nchw(*hp + offset, gpu()); }
+  if (reader) { float* hp = host_floats(reader); assert(hp); a.load_host_nchw(hp + offset, gpu()); }
   return offset + a.dim().flat_size() * a.batch_size();
 }
 size_t ActOp::_store_val(TxnId, VarIdSet& vars, size_t offset, any* writer) {
   if (!vars.mask(y_.val.var())) return offset;
   Act& a = y_.val.raw();
-  if (writer) { auto hp = std::any_cast<float*>(writer); assert(hp); a.store_host_nchw(*hp + offset, gpu()); }
+  if (writer) { float* hp = host_floats(writer); assert(hp); a.store_host_nchw(hp + offset, gpu()); }
   return offset + a.dim().flat_size() * a.batch_size();
 }
 size_t ActOp::_store_grad(TxnId, VarIdSet& vars, size_t offset, any* writer) {
   if (!vars.mask(y_.grad.var())) return offset;
   Act& a = y_.grad.raw();
-  if (writer) { auto hp = std::any_cast<float*>(writer); assert(hp); a.store_host_nchw(*hp + offset, gpu()); }
+  if (writer) { float* hp = host_floats(writer); assert(hp); a.store_host_nchw(hp + offset, gpu()); }
   return offset + a.dim().flat_size() * a.batch_size();
 }
 
@@ -152,8 +158,8 @@ static void io_move(A& a, any* flat, size_t offset, bool to_device, GPUContext* 
       return;
     }
   }
-  if (auto hp = std::any_cast<float*>(flat)) {
-    float* host = *hp + offset;
+  if (float* hbase = host_floats(flat)) {
+    float* host = hbase + offset;
     if constexpr (std::is_same<A, Act>::value) {
       if (to_device) a.load_host_nchw(host, g); else a.store_host_nchw(host, g);
     } else {
@@ -180,6 +186,17 @@ size_t IOOp<A>::_load_val(TxnId txn, VarIdSet& vars, size_t offset, any* reader)
   if (!vars.mask(data_.val.var())) return offset;
   data_.val.stamp(txn);
   A& a = data_.val.raw();
+  if constexpr (std::is_same<A, Act>::value) {
+    if (reader && full_h_ && !std::any_cast<HostRows>(reader)) {
+      // the reader holds the whole batch: take this rank's rows of it (see set_rows_of_full)
+      float* base = host_floats(reader);
+      assert(base && "an activation input reads float* or Slice<float>");
+      GPUContext* g = gpu_of(ctx_, rank_);
+      if (host_nhwc_) a.load_host_nhwc_rows(base, full_h_, row0_, host_scale_, g);
+      else a.load_host_nchw_rows(base, full_h_, row0_, g);
+      return offset + IOTraits<A>::size(a);
+    }
+  }
   if (reader) io_move(a, reader, offset, true, gpu_of(ctx_, rank_));
   return offset + IOTraits<A>::size(a);
 }
@@ -658,10 +675,16 @@ CudnnBatchNorm2DOpF::Parts CudnnBatchNorm2DOpF::Make(size_t channels, shared_ptr
 }
 CudnnBatchNorm2DOpF::CudnnBatchNorm2DOpF(shared_ptr<bool> switch_var, ActVar x, Parts* parts, shared_ptr<Context> ctx)
     : ActOp(x->rank(), ctx), switch_var_(switch_var), x_(x), scale_(parts->scale), shift_(parts->shift),
-      batch_mean_(parts->batch_mean), batch_variance_(parts->batch_variance) {
+      batch_mean_(parts->batch_mean), batch_variance_(parts->batch_variance), fixed_mean_(parts->fixed_mean),
+      fixed_variance_(parts->fixed_variance) {
   inputs_.push_back(x);
   inputs_.push_back(scale_);
   inputs_.push_back(shift_);
+  // statistics are graph variables too: the optimizer reads the batch statistics and loads the running ones
+  inputs_.push_back(batch_mean_);
+  inputs_.push_back(batch_variance_);
+  inputs_.push_back(fixed_mean_);
+  inputs_.push_back(fixed_variance_);
   alloc_output(x->shape(), 0, 0, x->batch_shape());
   const size_t C = x->shape().shape[2];
   save_mean_ = (float*)gpu()->arena().alloc(C * 4);
@@ -669,7 +692,6 @@ CudnnBatchNorm2DOpF::CudnnBatchNorm2DOpF(shared_ptr<bool> switch_var, ActVar x, 
 }
 void CudnnBatchNorm2DOpF::_forward(TxnId txn) {
   if (!y_.val.overwrite(txn, id())) return;
-  assert(!(switch_var_ && *switch_var_) && "fixed-statistics (inference) mode is not built");
   GPUContext* g = gpu();
   GPUConn conn = g->conn();
   Act& x = x_->data().val.get(txn, id());
@@ -677,6 +699,13 @@ void CudnnBatchNorm2DOpF::_forward(TxnId txn) {
   const uint32_t C = (uint32_t)dim_.shape[2];
   g->reserve_scratch(ad_bn_scratch_bytes(C));
   ad_tensor4 xv = x.view_interior(), yv = y.view_interior();
+  if (switch_var_ && *switch_var_) {
+    // validation: normalise with the running statistics (reference src/op.cc:3964-3978)
+    AD_CHECK(ad_bn_fwd_inference(&xv, &yv, scale_->data().val.get(txn, id()).dptr(), shift_->data().val.get(txn, id()).dptr(),
+                                 fixed_mean_->data().val.raw().dptr(), fixed_variance_->data().val.raw().dptr(), save_invstd_, 1.0e-5f,
+                                 relu_ ? 1 : 0, conn.stream()));
+    return;
+  }
   batch_mean_->data().val.stamp(txn);
   batch_variance_->data().val.stamp(txn);
   AD_CHECK(ad_bn_fwd_train(&xv, &yv, scale_->data().val.get(txn, id()).dptr(), shift_->data().val.get(txn, id()).dptr(), save_mean_,
@@ -686,6 +715,7 @@ void CudnnBatchNorm2DOpF::_forward(TxnId txn) {
   CUDA_CHECK(cudaMemcpyAsync(batch_mean_->data().val.raw().dptr(), save_mean_, C * 4, cudaMemcpyDeviceToDevice, conn.stream()));
 }
 void CudnnBatchNorm2DOpF::_backward(TxnId txn) {
+  assert(!(switch_var_ && *switch_var_) && "no backward pass with fixed statistics (reference src/op.cc:4078-4080)");
   GPUContext* g = gpu();
   auto xd = x_->data();
   auto zero1 = [g](Stat* a) { GPUConn c = g->conn(); AD_CHECK(ad_fill_zero(a->dptr(), a->flat_size() * 4, c.stream())); };
@@ -974,6 +1004,27 @@ CudnnSoftmaxNLLLoss2DOpF::CudnnSoftmaxNLLLoss2DOpF(ActVar x, shared_ptr<Context>
   AD_CHECK(ad_fill_zero(loss_, n_ * hw_ * sizeof(float), conn.stream()));
   AD_CHECK(ad_array_set_constant(n_ * hw_, 1.0f, dloss_, conn.stream()));
   conn.sync();
+}
+size_t CudnnSoftmaxNLLLoss2DOpF::_load_val(TxnId, VarIdSet& vars, size_t offset, any* reader) {
+  if (!vars.mask(label_var_)) return offset;
+  if (reader) {
+    const uint32_t* host = nullptr;
+    if (auto sp = std::any_cast<Slice<uint32_t>>(reader)) host = sp->ptr;
+    else if (auto hp = std::any_cast<uint32_t*>(reader)) host = *hp;
+    assert(host && "labels are read from uint32_t* or Slice<uint32_t>");
+    load_labels(host + (replica_ ? 0 : offset));
+  }
+  return replica_ ? offset : offset + n_ * hw_;
+}
+size_t CudnnSoftmaxNLLLoss2DOpF::_store_val(TxnId, VarIdSet& vars, size_t offset, any* writer) {
+  if (!vars.mask(loss_var_)) return offset;
+  if (replica_) return offset;
+  if (writer) {
+    float* host = host_floats(writer);
+    assert(host);
+    store_loss(host + offset);
+  }
+  return offset + n_ * hw_;
 }
 void CudnnSoftmaxNLLLoss2DOpF::load_labels(const uint32_t* host) {
   GPUConn conn = gpu_of(ctx_, x_->rank())->conn();

@@ -80,6 +80,130 @@ void ParallelSGDOptimizer<float>::step(TxnId txn) {
   ++iter_count_;
 }
 
+// ------------------------------------------------------------------ the reference's calling convention
+// reset(ctx) / step(compute_batch_fn, ctx): include/arraydiff/optimize.hh:314-564 of the reference.
+template <>
+void ParallelSGDOptimizer<float>::reset(shared_ptr<Context> parallel_ctx) {
+  ctx_ = parallel_ctx;
+  mgpu_ = dynamic_cast<MultiGPUContext*>(parallel_ctx.get());
+  assert(mgpu_);
+  const size_t R = mgpu_->num_ranks();
+  if (batch_stats_.empty()) batch_stats_.resize(R);
+  if (fixed_stats_.empty()) fixed_stats_.resize(R);
+  TxnId init_txn;
+  for (size_t r = 0; r < R; ++r) {
+    if (!mgpu_->is_local(r)) continue;
+    sink_->persist(init_txn, params_[r]);
+    sink_->persist(init_txn, fixed_stats_[r]);
+  }
+  param_dim_ = 0; stat_dim_ = 0;
+  bool have = false;
+  for (size_t r = 0; r < R; ++r) {
+    if (!mgpu_->is_local(r)) continue;
+    const size_t d = sink_->store_val(init_txn, params_[r], 0, nullptr);
+    const size_t sd = sink_->store_val(init_txn, fixed_stats_[r], 0, nullptr);
+    assert(!have || (param_dim_ == d && stat_dim_ == sd));   // per-rank sub-graphs are built alike (reference :323-333)
+    param_dim_ = d; stat_dim_ = sd; have = true;
+    assert(sink_->store_grad(init_txn, grads_[r], 0, nullptr) == d);
+    assert(sink_->store_val(init_txn, batch_stats_[r], 0, nullptr) == sd);
+  }
+  param_.resize(R); sum_grad_.resize(R); momentum_.resize(R);
+  batch_grad_.resize(R); batch_stat_.resize(R); avg_stat_.resize(R); running_stat_.resize(R);
+  for (size_t r = 0; r < R; ++r) {
+    if (!mgpu_->is_local(r)) continue;
+    GPUContext* g = mgpu_->device_context(r).get();
+    param_[r] = GPUMemory<float>(param_dim_, g);
+    sum_grad_[r] = GPUMemory<float>(param_dim_, g);
+    momentum_[r] = GPUMemory<float>(param_dim_, g);
+    batch_grad_[r] = GPUMemory<float>(param_dim_, g);
+    const size_t sd = stat_dim_ ? stat_dim_ : 1;
+    batch_stat_[r] = GPUMemory<float>(sd, g);
+    avg_stat_[r] = GPUMemory<float>(sd, g);
+    running_stat_[r] = GPUMemory<float>(sd, g);
+  }
+  // rank 0's initial point and running statistics become everybody's (reference :358-386); ranks in other
+  // processes drew from an equally seeded generator and hold the same values already
+  const size_t first = mgpu_->distributed() ? mgpu_->my_rank() : 0;
+  {
+    any w = param_[first];
+    sink_->store_val(init_txn, params_[first], 0, &w);
+    any ws = running_stat_[first];
+    if (stat_dim_) sink_->store_val(init_txn, fixed_stats_[first], 0, &ws);
+  }
+  mgpu_->device_context(first)->sync();
+  for (size_t r = 0; r < R; ++r) {
+    if (!mgpu_->is_local(r) || r == first) continue;
+    GPUConn conn = mgpu_->device_context(r)->conn();
+    CUDA_CHECK(cudaMemcpyAsync(param_[r].dptr(), param_[first].dptr(), param_dim_ * 4, cudaMemcpyDeviceToDevice, conn.stream()));
+    if (stat_dim_)
+      CUDA_CHECK(cudaMemcpyAsync(running_stat_[r].dptr(), running_stat_[first].dptr(), stat_dim_ * 4, cudaMemcpyDeviceToDevice, conn.stream()));
+  }
+  TxnId load_txn;
+  for (size_t r = 0; r < R; ++r) {
+    if (!mgpu_->is_local(r)) continue;
+    any rd = param_[r];
+    sink_->load_val(load_txn, params_[r], 0, &rd);
+    any rs = running_stat_[r];
+    if (stat_dim_) sink_->load_val(load_txn, fixed_stats_[r], 0, &rs);
+  }
+  iter_count_ = 0;
+  mgpu_->sync();
+}
+
+template <>
+void ParallelSGDOptimizer<float>::step(function<void(TxnId, size_t, shared_ptr<Op>)>& compute_batch_fn, shared_ptr<Context> parallel_ctx) {
+  assert(mgpu_ && dynamic_cast<MultiGPUContext*>(parallel_ctx.get()) == mgpu_ && "reset(parallel_ctx) first");
+  const size_t R = mgpu_->num_ranks();
+  const size_t num_batches = (cfg_.minibatch_size + cfg_.compute_batch_size - 1) / cfg_.compute_batch_size;
+  for (size_t b = 0; b < num_batches; ++b) {
+    TxnId batch_txn;
+    const size_t left = cfg_.minibatch_size - b * cfg_.compute_batch_size;
+    compute_batch_fn(batch_txn, left < cfg_.compute_batch_size ? left : cfg_.compute_batch_size, sink_);
+    for (size_t r = 0; r < R; ++r) {
+      if (!mgpu_->is_local(r)) continue;
+      GPUConn conn = mgpu_->device_context(r)->conn();
+      // the first micro-batch writes the sums, the others add (reference :425-437)
+      any gw = b == 0 ? sum_grad_[r] : batch_grad_[r];
+      sink_->store_grad(batch_txn, grads_[r], 0, &gw);
+      if (b) AD_CHECK(ad_array_add(param_dim_, batch_grad_[r].dptr(), sum_grad_[r].dptr(), conn.stream()));
+      if (stat_dim_) {
+        any sw = b == 0 ? avg_stat_[r] : batch_stat_[r];
+        sink_->store_val(batch_txn, batch_stats_[r], 0, &sw);
+        if (b) AD_CHECK(ad_array_add_online(stat_dim_, 1.0f / (float)(b + 1), batch_stat_[r].dptr(), avg_stat_[r].dptr(), conn.stream()));
+      }
+    }
+  }
+  // sum over ranks: each rank's filter gradient covers only its strip
+  const size_t first = mgpu_->distributed() ? mgpu_->my_rank() : 0;
+  mgpu_->allreduce_sum(sum_grad_[first].dptr(), param_dim_);
+  const float mu = (float)cfg_.momentum->at(iter_count_);
+  const float alpha = (float)cfg_.step_size->at(iter_count_);
+  const float next_alpha = (float)cfg_.step_size->at(iter_count_ + 1);
+  TxnId update_txn;
+  for (size_t r = 0; r < R; ++r) {
+    if (!mgpu_->is_local(r)) continue;
+    GPUConn conn = mgpu_->device_context(r)->conn();
+    AD_CHECK(ad_sgd_step(param_dim_, param_[r].dptr(), sum_grad_[r].dptr(), momentum_[r].dptr(), (float)cfg_.l2_reg, mu, alpha,
+                         next_alpha, cfg_.nesterov ? 1 : 0, nullptr, conn.stream()));
+    any rd = param_[r];
+    sink_->load_val(update_txn, params_[r], 0, &rd);
+    if (stat_dim_) {
+      // running += rate * (average batch statistic - running)   (reference :501-508)
+      AD_CHECK(ad_array_add_online(stat_dim_, (float)cfg_.batch_norm_rate, avg_stat_[r].dptr(), running_stat_[r].dptr(), conn.stream()));
+      any rs = running_stat_[r];
+      sink_->load_val(update_txn, fixed_stats_[r], 0, &rs);
+    }
+  }
+  ++iter_count_;
+  mgpu_->end_phase();
+}
+
+template <>
+void ParallelSGDOptimizer<float>::store_fixed_stats(size_t rank, float* host) {
+  GPUConn conn = mgpu_->device_context(rank)->conn();
+  if (stat_dim_) running_stat_[rank].store_sync(host, stat_dim_, 0, conn);
+}
+
 template <>
 void ParallelSGDOptimizer<float>::store_params(size_t rank, float* host) {
   GPUConn conn = mgpu_->device_context(rank)->conn();

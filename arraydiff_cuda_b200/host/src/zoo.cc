@@ -521,4 +521,48 @@ SpatialParallelNet SpatialParallelResNet<float>::MakeParallelResNet50(const Conv
   return net;
 }
 
+
+// ------------------------------------------------------------------ the reference's tool-facing builders
+static ParallelCategoricalNLLBatchNormLoss<> package_classifier(SpatialParallelNet net, const ConvNetConfig& cfg, shared_ptr<Context> ctx) {
+  ParallelCategoricalNLLBatchNormLoss<> out;
+  const size_t R = ranks_of(ctx);
+  const size_t h = cfg.input_h / R;
+  bool first = true;
+  for (size_t r = 0; r < R; ++r) {
+    if (!local_rank(ctx, r)) continue;
+    // one batch of whole NHWC images in 0..255: each rank takes its rows, scaled to 0..1
+    net.inputs[r]->set_rows_of_full(cfg.input_h, r * h, true, 1.0f / 255.0f);
+    out.inputs.insert(net.inputs[r]->data().val.var());
+  }
+  for (auto& l : net.losses) {
+    // every rank scores the whole batch: the mean over the minibatch, shared out over the R copies of the head
+    l->set_loss_weight(1.0f / (float)((cfg.minibatch_size ? cfg.minibatch_size : cfg.batch_size) * R));
+    l->set_replica(!first);
+    out.labels.insert(l->label_var());
+    if (first) {
+      out.losses.insert(l->loss_var());
+      out.loss = l;
+      for (auto& o : net.outputs)
+        if (o->rank() == l->rank()) out.logits.insert(o->data().val.var());
+    }
+    first = false;
+  }
+  out.batch_norm_use_fixed = net.batch_norm_use_fixed;
+  // `op` is what a tool initialises from (op->init): the root, so that every rank's variables are reached
+  out.sum_loss = net.sink;
+  out.op = net.sink;
+  out.dev_params = net.dev_params; out.dev_grads = net.dev_grads;
+  out.dev_batch_stats = net.dev_batch_stats; out.dev_fixed_stats = net.dev_fixed_stats;
+  out.net = net;
+  return out;
+}
+template <>
+ParallelCategoricalNLLBatchNormLoss<> ResNet<float>::MakeParallelResNet18(const ConvNetConfig& cfg, shared_ptr<Context> ctx) {
+  return package_classifier(SpatialParallelResNet<float>::MakeParallelResNet18(cfg, 1000, ctx), cfg, ctx);
+}
+template <>
+ParallelCategoricalNLLBatchNormLoss<> ResNet<float>::MakeParallelResNet50(const ConvNetConfig& cfg, shared_ptr<Context> ctx) {
+  return package_classifier(SpatialParallelResNet<float>::MakeParallelResNet50(cfg, 1000, ctx), cfg, ctx);
+}
+
 }  // namespace arraydiff

@@ -916,7 +916,9 @@ def run_net_workload(env, args, kind):
         ranks = list(range(strips))
     net = hostlib.Net(ctx, "segnet50" if seg else "parallel_resnet50" if hyb else "stem_stage1", Hh, Ww, 3, NB,
                       filters=1000 if hyb else 64, seed=1)
-    net.configure_sgd(0.01, 0.9, l2=1e-4, nesterov=True)
+    # the stem workload has no loss: its upstream gradient is a fixed random tensor, so thousands of timed steps at a
+    # training-sized rate would walk the weights off to infinity; the rate does not change what the step costs
+    net.configure_sgd(0.01 if (seg or hyb) else 1e-6, 0.9, l2=1e-4, nesterov=True)
     if hyb:
         net.set_loss_weight(1.0 / (NB * D * strips))     # mean over the global batch, shared out over a group's replicas of the head
     rng = np.random.default_rng(7 + group)

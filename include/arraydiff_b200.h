@@ -245,6 +245,14 @@ int ad_bn_bwd(const ad_tensor4* x, const ad_tensor4* dy, const ad_tensor4* dx, c
               float* dbeta, int32_t relu, int32_t accumulate_dx, void* scratch, size_t scratch_bytes,
               void* stream);
 /*
+ * Batch normalisation with FIXED statistics (the running mean / variance an optimizer keeps), optional fused ReLU:
+ *   y = relu?(gamma * (x - mean) / sqrt(var + eps) + beta).
+ * Replaces cudnnBatchNormalizationForwardInference, src/op.cc:3964-3978 (taken when the net's switch variable is
+ * set: validation).  invstd_out [C] receives 1 / sqrt(var + eps) (device scratch the caller owns).
+ */
+int ad_bn_fwd_inference(const ad_tensor4* x, const ad_tensor4* y, const float* gamma, const float* beta,
+                        const float* mean, const float* var, float* invstd_out, float eps, int32_t relu, void* stream);
+/*
  * ad_bn_fwd_train without any scratch argument, for callers that cannot allocate device memory
  * (an op running under a framework that owns the whole device through its own pool, or a loop
  * that must not meet cudaMalloc's device synchronisation).  This entry point has no counterpart

@@ -179,6 +179,33 @@ def test_batch_norm_fwd_bwd(layout, dtype, relu, Cc):
                              f32(1e-5), relu, H.ptr(scratch), 8, H.stream()) == abi.AD_ERR_SCRATCH
 
 
+@pytest.mark.parametrize("layout", [abi.AD_NCHW, abi.AD_NHWC])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("relu", [0, 1])
+def test_batch_norm_fixed_statistics(layout, dtype, relu):
+    """Inference form (cudnnBatchNormalizationForwardInference at the reference's call site): fixed mean / variance."""
+    import torch
+    N, Cc, Hh, W = 2, 64, 9, 11
+    x = H.normal(30, (N, Cc, Hh, W)) * 1.7 + 0.3
+    if dtype == "bf16":
+        x = orc.round_bf16(x)
+    gamma, beta = H.uniform(31, (Cc,), 0.5, 1.5), H.uniform(32, (Cc,), -0.5, 0.5)
+    mean, var = H.uniform(33, (Cc,), -0.4, 0.4), H.uniform(34, (Cc,), 0.2, 3.0)
+    sh = (1, Cc, 1, 1)
+    y_w = gamma.reshape(sh).astype(np.float64) * (x.astype(np.float64) - mean.reshape(sh)) / np.sqrt(var.reshape(sh).astype(np.float64) + 1e-5) + beta.reshape(sh)
+    if relu:
+        y_w = np.maximum(y_w, 0)
+    L = abi.lib()
+    tx, vx = _views(x, layout, dtype)
+    ty, vy = _views(np.zeros_like(x), layout, dtype, pad=1)
+    d = [H.dev(a) for a in (gamma, beta, mean, var)]
+    invstd = torch.empty(Cc, device="cuda")
+    abi.check(L.ad_bn_fwd_inference(C.byref(vx), C.byref(vy), *[H.ptr(t) for t in d], H.ptr(invstd), f32(1e-5), relu, H.stream()))
+    H.sync()
+    assert H.max_rel(_back(ty, layout, 1, Hh, W), y_w) < (1e-5 if dtype == "f32" else 2e-2)
+    assert H.max_rel(H.host(invstd), 1.0 / np.sqrt(var.astype(np.float64) + 1e-5)) < 1e-6
+
+
 def test_batch_norm_two_phase_matches_single_call_across_strips():
     """Statistics over R strips via partial sums + host-side sum == statistics over the whole tensor."""
     import torch

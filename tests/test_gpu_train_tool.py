@@ -1,0 +1,43 @@
+"""The C++ training driver on synthetic data (arraydiff_cuda_b200/host/tools/train_dummy.cc): the loop of the
+reference's tools/train_imagenet.cc over DummyData, written against the op-graph API with the reference's own calls
+(ResNet<float>::MakeParallelResNet18, ParallelSGDOptimizer's 6-argument constructor, reset(ctx), step(batch_fn, ctx),
+load_val / store_val with Slice readers).  Run as a child process on 1 and 2 H-strips sharing the GPU."""
+import os
+import re
+import subprocess
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TOOL = os.path.join(ROOT, "arraydiff_cuda_b200", "host", "tools", "train_dummy")
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not os.path.exists(TOOL), reason="training tool not built")]
+
+
+def run_tool(devices, mode, iters=12, image=64, batch=4, minibatch=8):
+    env = dict(os.environ, ARRAYDIFF_B200_DEVICES=devices, ARRAYDIFF_B200_MODE=mode, ARRAYDIFF_B200_ARENA_MB="3072")
+    out = subprocess.run([TOOL, str(iters), str(image), str(batch), str(minibatch)], env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    losses = [float(m.group(1)) for m in re.finditer(r"^iter \d+ loss ([-0-9.eE+naif]+)", out.stdout, re.M)]
+    tail = re.search(r"params (\d+) checksum (\S+) abs (\S+) stat_dim (\d+) stat_sum (\S+) status (-?\d+)", out.stdout)
+    val = re.search(r"validation_loss_fixed_stats (\S+)", out.stdout)
+    assert len(losses) == iters and tail and val, out.stdout[-2000:]
+    return losses, tail.groups(), float(val.group(1))
+
+
+@pytest.mark.parametrize("devices", ["0", "0,0"])
+@pytest.mark.parametrize("mode", ["f32", "bf16"])
+def test_training_tool_runs_and_learns(devices, mode):
+    losses, (nparam, checksum, abs_sum, stat_dim, stat_sum, status), val = run_tool(devices, mode)
+    assert int(status) == 0                          # no bounded device wait ran out
+    assert int(nparam) > 10_000_000 and int(stat_dim) > 0
+    assert all(l == l and l < 50 for l in losses)    # finite
+    assert sum(losses[-3:]) < sum(losses[:3])        # the loss goes down on the 10-class synthetic data
+    assert val == val and val < 50                   # the fixed-statistics (validation) forward pass works
+    # the batch-norm running statistics moved away from their initial values (means 0, variances 1)
+    assert abs(float(stat_sum) - int(stat_dim) / 2) > 1e-3
+
+
+def test_training_tool_is_reproducible():
+    a = run_tool("0,0", "bf16", iters=4)
+    b = run_tool("0,0", "bf16", iters=4)
+    assert a[0] == b[0] and a[1] == b[1]
