@@ -149,6 +149,14 @@ public:
     world_bases_.at(world_rank) = arena_bases_.at(my_rank_);
   }
   void set_world_peer_arena(size_t world_rank, void* base) { world_bases_.at(world_rank) = (uint8_t*)base; }
+  // this process's place in the gradient exchange: the world when set_world() was called, else the spatial group
+  size_t exchange_rank() const { return world_size_ ? world_rank_ : my_rank_; }
+  size_t exchange_size() const { return world_size_ ? world_size_ : num_ranks_; }
+  // Communicator handles for callers that run NCCL themselves (the reference's nccl_comm(rank),
+  // include/arraydiff/context.hh:92): opaque here -- this library never calls NCCL; whoever initialises the
+  // communicators hands them over with set_nccl_comm and reads them back (cast to ncclComm_t) inside an allreduce hook.
+  void set_nccl_comm(size_t rank, void* comm) { if (nccl_comms_.size() < num_ranks_) nccl_comms_.resize(num_ranks_, nullptr); nccl_comms_.at(rank) = comm; }
+  void* nccl_comm(size_t rank) const { return rank < nccl_comms_.size() ? nccl_comms_[rank] : nullptr; }
   // Between processes: advances every local rank's flag base by the signalling operations issued since the
   // last call (Spatial2DComm::end_phase).  Call it where a unit of work that may be replayed as a CUDA graph ends.
   void end_phase();
@@ -166,6 +174,7 @@ private:
   size_t ar_stage_count_ = 0;
   size_t world_rank_ = 0, world_size_ = 0;   // 0: the gradient exchange spans the spatial group
   vector<uint8_t*> world_bases_;
+  vector<void*> nccl_comms_;
 };
 
 }  // namespace arraydiff

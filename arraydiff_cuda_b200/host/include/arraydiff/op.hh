@@ -528,6 +528,66 @@ private:
   size_t num_ranks_;
 };
 
+// ---------------------------------------------------------------- collectives as graph operators
+// The reference's BroadcastOp (src/op.cc:1854-1966), AllreduceOp (:2284-2381) and ReduceOp (:1968-2174): one operator
+// shared by all ranks, results exposed per rank.  They serve graphs written the reference's way (broadcast the image,
+// cut strips inside the graph; gather strips into zeroed full tensors and all-reduce them; reduce the replicas'
+// logits to rank 0) inside ONE process, where ranks reach each other's buffers directly and are ordered by CUDA
+// events; the builders in zoo.hh use scatter-on-load and SpatialAllGather2DOp instead, which also work between
+// processes.  Sums run in rank order on every rank (same bits everywhere).  The backward passes ACCUMULATE into the
+// inputs' gradients (the reference overwrites them: FIXMEs at src/op.cc:1938, :2366, and passes a reduction operator
+// where a root rank belongs at :2057-2063).
+class CollectiveOutF : public ActOp {     // one rank's result buffer of a shared collective
+public:
+  CollectiveOutF(shared_ptr<Op> shared, ActVar like, size_t rank, shared_ptr<Context> ctx);
+  void _forward(TxnId) override {}
+  void _backward(TxnId) override {}
+};
+class BroadcastOpF : public virtual Op {
+public:
+  // y_r = x (which lives on `root`) for every rank r
+  static vector<ActVar> MakeParallel(size_t root, ActVar x, shared_ptr<Context> ctx);
+  BroadcastOpF(size_t root, ActVar x, shared_ptr<Context> ctx);
+  void _forward(TxnId txn) override;
+  void _backward(TxnId txn) override;
+  string _debug_op_label() override { return "BroadcastOp"; }
+private:
+  std::optional<uint64_t> done_fwd_, done_bwd_;
+  size_t root_;
+  ActVar x_;
+  vector<CollectiveOutF*> outs_;
+  shared_ptr<Context> ctx_;
+};
+class AllreduceOpF : public virtual Op {
+public:
+  // y_r = sum_q x_q on every rank
+  static vector<ActVar> MakeParallel(vector<ActVar> inputs, shared_ptr<Context> ctx);
+  AllreduceOpF(vector<ActVar> inputs, shared_ptr<Context> ctx);
+  void _forward(TxnId txn) override;
+  void _backward(TxnId txn) override;
+  string _debug_op_label() override { return "AllreduceOp"; }
+private:
+  std::optional<uint64_t> done_fwd_, done_bwd_;
+  vector<ActVar> xs_;
+  vector<CollectiveOutF*> outs_;
+  shared_ptr<Context> ctx_;
+};
+class ReduceOpF : public virtual Op {
+public:
+  // y = sum_q x_q on `root`
+  static ActVar MakeParallel(size_t root, vector<ActVar> inputs, shared_ptr<Context> ctx);
+  ReduceOpF(size_t root, vector<ActVar> inputs, shared_ptr<Context> ctx);
+  void _forward(TxnId txn) override;
+  void _backward(TxnId txn) override;
+  string _debug_op_label() override { return "ReduceOp"; }
+private:
+  std::optional<uint64_t> done_fwd_, done_bwd_;
+  size_t root_;
+  vector<ActVar> xs_;
+  CollectiveOutF* out_ = nullptr;
+  shared_ptr<Context> ctx_;
+};
+
 // y = x w^T + b on [batch][features] activations (1 x 1 spatial extent), w Shape4D(1,1,in,out) = [out][in] in
 // memory.  The reference's CublasLinearOp (src/op.cc:1199-1340) on GPUBatchArray1D.
 class CublasLinearOpF : public ActOp {
@@ -625,6 +685,9 @@ template <typename V> using CudnnActivationOp = CudnnActivationOpF;
 template <typename V, typename J = SumJoin> using JoinOp = SumJoinOpF;
 template <typename V> using UpsampleBilinear2DOp = UpsampleBilinear2DOpF;
 template <typename V> using SpatialAllGather2DOp = SpatialAllGather2DOpF;
+template <typename V> using BroadcastOp = BroadcastOpF;
+template <typename V> using AllreduceOp = AllreduceOpF;
+template <typename V> using ReduceOp = ReduceOpF;
 template <typename V, typename K = GPUArray4D<float>, typename B = GPUArray1D<float>> using CublasLinearOp = CublasLinearOpF;
 template <typename V> using CudnnSoftmaxNLLLossOp = CudnnSoftmaxNLLLoss2DOpF;
 

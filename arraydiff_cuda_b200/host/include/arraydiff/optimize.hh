@@ -120,6 +120,20 @@ public:
   }
   size_t stat_dim() const { return stat_dim_; }
   void store_fixed_stats(size_t rank, float* host);
+  // Flat-parameter checkpoint: the flat buffers the graph walk fills (parameters in store_val order, the momentum
+  // buffer, the running statistics; reference include/arraydiff/optimize.hh:146-165, :228-238 keeps exactly these
+  // as its optimizer state) written to one file with a header that names every variable:
+  //   "ADB2CKPT" | u32 version = 1 | u64 param_dim | u64 stat_dim | u64 iteration | u32 entries |
+  //   entries x { u32 name length | name bytes | u64 offset | u64 size } | fp32 params[param_dim] |
+  //   fp32 momentum[param_dim] | fp32 running statistics[stat_dim]          (little endian, no padding)
+  // save: the first local rank's copy (all replicas are identical).  load: checks the dimensions and the manifest,
+  // then gives every local rank the file's state (buffers, graph variables, iteration counter).  Both synchronise.
+  bool save_checkpoint(const string& path);
+  bool load_checkpoint(const string& path);
+  // Worker 0's parameters and running statistics become every process's (a context made with MakeDistributed, with
+  // or without set_world): the others contribute zeros to one sum over the gradient exchange, so the bits are worker
+  // 0's.  The broadcast-init of the reference's multi-process optimizer (include/arraydiff/optimize_mpi.hh:66-95).
+  void broadcast_from_worker0();
   // To be called after the gradients of transaction `txn` exist on every rank: gathers them into the
   // flat buffer, sums over ranks, applies L2 + (Nesterov) momentum SGD on every rank, and loads the
   // new parameters back into the graph (reference :407-561).
@@ -140,6 +154,40 @@ private:
   MultiGPUContext* mgpu_ = nullptr;
   shared_ptr<Context> ctx_;
   vector<GPUMemory<T>> param_, sum_grad_, momentum_;
+};
+
+// Data-parallel SGD over processes, one replica of the (possibly spatially partitioned) net per process: the
+// reference's MPIDataParallelSGDOptimizer (include/arraydiff/optimize_mpi.hh:20-205) with the built-in peer exchange
+// of MultiGPUContext (or an NCCL hook) in place of MPI_Bcast / MPI_Allreduce.  reset() makes worker 0's initial point
+// everyone's; step() sums the gradients of all workers (no averaging, as the reference) and applies the same update
+// everywhere.  The context must be one made with MultiGPUContext::MakeDistributed whose peers (set_peer_arena /
+// set_world_peer_arena) are the other workers.
+template <typename T>
+class DataParallelSGDOptimizer {
+public:
+  DataParallelSGDOptimizer(SGDConfig cfg, shared_ptr<Op> sum_loss, VarIdSet params, VarIdSet grads, VarIdSet batch_stats,
+                           VarIdSet fixed_stats)
+      : cfg_(cfg), sum_loss_(sum_loss), params_(params), grads_(grads), batch_stats_(batch_stats), fixed_stats_(fixed_stats) {}
+  size_t worker_rank() const { return worker_rank_; }
+  size_t num_workers() const { return num_workers_; }
+  void reset(shared_ptr<Context> ctx) {
+    auto* m = dynamic_cast<MultiGPUContext*>(ctx.get());
+    assert(m && m->distributed());
+    worker_rank_ = m->exchange_rank(); num_workers_ = m->exchange_size();
+    vector<VarIdSet> p(m->num_ranks()), g(m->num_ranks()), b(m->num_ranks()), f(m->num_ranks());
+    p[m->my_rank()] = params_; g[m->my_rank()] = grads_; b[m->my_rank()] = batch_stats_; f[m->my_rank()] = fixed_stats_;
+    inner_.reset(new ParallelSGDOptimizer<T>(cfg_, sum_loss_, p, g, b, f));
+    inner_->reset(ctx);
+    inner_->broadcast_from_worker0();
+  }
+  void step(function<void(TxnId, size_t, shared_ptr<Op>)>& compute_batch_fn, shared_ptr<Context> ctx) { inner_->step(compute_batch_fn, ctx); }
+  ParallelSGDOptimizer<T>& inner() { return *inner_; }
+private:
+  SGDConfig cfg_;
+  shared_ptr<Op> sum_loss_;
+  VarIdSet params_, grads_, batch_stats_, fixed_stats_;
+  size_t worker_rank_ = 0, num_workers_ = 1;
+  std::unique_ptr<ParallelSGDOptimizer<T>> inner_;
 };
 
 }  // namespace arraydiff

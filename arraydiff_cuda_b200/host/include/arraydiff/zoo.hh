@@ -105,6 +105,9 @@ public:
   // One 3x3 convolution (stride 1, pad 1, bias) over H-strips: scatter -> halo pad -> halo exchange ->
   // conv.  The plumbing case of the partitioned path.
   static SpatialParallelNet MakeConv3x3(const ConvNetConfig& config, size_t filters, shared_ptr<Context> ctx);
+  // The same layer between the reference's collective operators: BroadcastOp -> SpatialScatter2DOp -> pad / exchange /
+  // conv -> SpatialGather2DOp -> AllreduceOp -> ReduceOp.  One output on rank 0: R times the convolution.
+  static SpatialParallelNet MakeConv3x3Collectives(const ConvNetConfig& config, size_t filters, shared_ptr<Context> ctx);
   // ResNet-50 stem + stage 1: 7x7/2 conv to 64 channels, BN, ReLU, 3x3/2 max pool, then three
   // pre-activation bottleneck blocks (64-64-256), the first with a 1x1 projection.
   static SpatialParallelNet MakeStemStage1(const ConvNetConfig& config, shared_ptr<Context> ctx);

@@ -86,6 +86,7 @@ void* adh_net_create(void* c, const char* kind, int H, int W, int C, int batch, 
   n->cfg.input_h = (size_t)H; n->cfg.input_w = (size_t)W; n->cfg.input_c = (size_t)C; n->cfg.batch_size = (size_t)batch;
   n->rng.seed(seed);
   if (!std::strcmp(kind, "conv3x3")) n->net = SpatialParallelResNet<float>::MakeConv3x3(n->cfg, (size_t)filters, n->ctx);
+  else if (!std::strcmp(kind, "conv3x3_collectives")) n->net = SpatialParallelResNet<float>::MakeConv3x3Collectives(n->cfg, (size_t)filters, n->ctx);
   else if (!std::strcmp(kind, "stem_stage1")) n->net = SpatialParallelResNet<float>::MakeStemStage1(n->cfg, n->ctx);
   else if (!std::strcmp(kind, "parallel_resnet18")) n->net = SpatialParallelResNet<float>::MakeParallelResNet18(n->cfg, filters > 0 ? (size_t)filters : 1000, n->ctx);
   else if (!std::strcmp(kind, "parallel_resnet50")) n->net = SpatialParallelResNet<float>::MakeParallelResNet50(n->cfg, filters > 0 ? (size_t)filters : 1000, n->ctx);
@@ -106,6 +107,17 @@ void* adh_net_create(void* c, const char* kind, int H, int W, int C, int batch, 
   return n;
 }
 void adh_net_destroy(void* h) { delete (Net*)h; }
+// flat-parameter checkpoint of the net's optimizer state (parameters, momentum, running statistics, iteration)
+int adh_net_save_checkpoint(void* h, const char* path) { return ((Net*)h)->opt->save_checkpoint(path) ? AD_OK : AD_ERR_BAD_ARG; }
+int adh_net_load_checkpoint(void* h, const char* path) {
+  auto* n = (Net*)h;
+  if (!n->opt->load_checkpoint(path)) return AD_ERR_BAD_ARG;
+  if (n->gexec) { cudaGraphExecDestroy(n->gexec); n->gexec = nullptr; }   // schedule values may differ: record again
+  return AD_OK;
+}
+// worker 0's parameters become every process's (contexts made with adh_context_create_distributed)
+int adh_net_broadcast_params(void* h) { ((Net*)h)->opt->broadcast_from_worker0(); return AD_OK; }
+size_t adh_net_iteration(void* h) { return ((Net*)h)->opt->iteration(); }
 int adh_net_configure_sgd(void* h, double step_size, double momentum, double l2, int nesterov) {
   auto* n = (Net*)h;
   SGDConfig sc;

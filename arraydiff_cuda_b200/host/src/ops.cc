@@ -895,6 +895,138 @@ void SpatialAllGather2DOpF::_backward(TxnId txn) {
   }
 }
 
+// ------------------------------------------------------------------ broadcast / allreduce / reduce (one process)
+CollectiveOutF::CollectiveOutF(shared_ptr<Op> shared, ActVar like, size_t rank, shared_ptr<Context> ctx) : ActOp(rank, ctx) {
+  inputs_.push_back(shared);
+  alloc_output(like->shape(), 0, 0, like->batch_shape());
+}
+static MultiGPUContext* in_process(const shared_ptr<Context>& ctx) {
+  auto* m = dynamic_cast<MultiGPUContext*>(ctx.get());
+  assert(m && !m->distributed() && "graph collectives serve one-process contexts; between processes use scatter-on-load / SpatialAllGather2DOp");
+  return m;
+}
+// dst (=|+=) src on dst's rank, after everything issued so far on src's rank
+static void pull(MultiGPUContext* m, size_t dst_rank, Act& dst, size_t src_rank, Act& src, bool add) {
+  GPUConn conn = m->device_context(dst_rank)->conn();
+  if (src_rank != dst_rank) order_after(conn.stream(), m->device_context(src_rank)->stream());
+  ad_tensor4 s = src.view_interior(), d = dst.view_interior();
+  AD_CHECK(ad_convert(&s, &d, add ? 1 : 0, conn.stream()));
+}
+
+vector<ActVar> BroadcastOpF::MakeParallel(size_t root, ActVar x, shared_ptr<Context> ctx) {
+  auto shared = make_shared<BroadcastOpF>(root, x, ctx);
+  vector<ActVar> out;
+  for (size_t r = 0; r < in_process(ctx)->num_ranks(); ++r) {
+    auto o = make_shared<CollectiveOutF>(shared, x, r, ctx);
+    shared->outs_.push_back(o.get());
+    out.push_back(o);
+  }
+  return out;
+}
+BroadcastOpF::BroadcastOpF(size_t root, ActVar x, shared_ptr<Context> ctx) : root_(root), x_(x), ctx_(ctx) {
+  assert(x->rank() == root);
+  inputs_.push_back(x);
+}
+void BroadcastOpF::_forward(TxnId txn) {
+  if (done_fwd_ && *done_fwd_ == txn.raw_id()) return;
+  done_fwd_ = txn.raw_id();
+  auto* m = in_process(ctx_);
+  Act& x = x_->data().val.get(txn, id());
+  for (size_t r = 0; r < outs_.size(); ++r) {
+    auto yd = outs_[r]->data();
+    if (!yd.val.overwrite(txn, id())) continue;
+    pull(m, r, yd.val.get_excl(txn, id()), root_, x, false);
+  }
+}
+void BroadcastOpF::_backward(TxnId txn) {
+  if (done_bwd_ && *done_bwd_ == txn.raw_id()) return;
+  done_bwd_ = txn.raw_id();
+  auto* m = in_process(ctx_);
+  auto xd = x_->data();
+  const int mode = xd.grad.accumulate_full(txn, id(), unpadded, zero_init(m->device_context(root_).get()));
+  if (!mode) return;
+  bool add = mode == 1;
+  for (size_t r = 0; r < outs_.size(); ++r) {
+    if (!outs_[r]->data().grad.written_in(txn)) continue;   // a rank whose copy nobody used
+    pull(m, root_, xd.grad.get_mut(txn, id()), r, outs_[r]->data().grad.get(txn, id()), add);
+    add = true;
+  }
+}
+
+vector<ActVar> AllreduceOpF::MakeParallel(vector<ActVar> inputs, shared_ptr<Context> ctx) {
+  auto shared = make_shared<AllreduceOpF>(inputs, ctx);
+  vector<ActVar> out;
+  for (auto& x : inputs) {
+    auto o = make_shared<CollectiveOutF>(shared, x, x->rank(), ctx);
+    shared->outs_.push_back(o.get());
+    out.push_back(o);
+  }
+  return out;
+}
+AllreduceOpF::AllreduceOpF(vector<ActVar> inputs, shared_ptr<Context> ctx) : xs_(inputs), ctx_(ctx) {
+  in_process(ctx);
+  for (auto& x : inputs) inputs_.push_back(x);
+}
+void AllreduceOpF::_forward(TxnId txn) {
+  if (done_fwd_ && *done_fwd_ == txn.raw_id()) return;
+  done_fwd_ = txn.raw_id();
+  auto* m = in_process(ctx_);
+  for (size_t i = 0; i < xs_.size(); ++i) {
+    auto yd = outs_[i]->data();
+    if (!yd.val.overwrite(txn, id())) continue;
+    for (size_t j = 0; j < xs_.size(); ++j)    // rank order: the same bits on every rank
+      pull(m, xs_[i]->rank(), yd.val.get_excl(txn, id()), xs_[j]->rank(), xs_[j]->data().val.get(txn, id()), j != 0);
+  }
+}
+void AllreduceOpF::_backward(TxnId txn) {
+  if (done_bwd_ && *done_bwd_ == txn.raw_id()) return;
+  done_bwd_ = txn.raw_id();
+  auto* m = in_process(ctx_);
+  for (size_t i = 0; i < xs_.size(); ++i) {
+    auto xd = xs_[i]->data();
+    const int mode = xd.grad.accumulate_full(txn, id(), unpadded, zero_init(m->device_context(xs_[i]->rank()).get()));
+    if (!mode) continue;
+    bool add = mode == 1;
+    for (size_t j = 0; j < xs_.size(); ++j) {
+      if (!outs_[j]->data().grad.written_in(txn)) continue;
+      pull(m, xs_[i]->rank(), xd.grad.get_mut(txn, id()), xs_[j]->rank(), outs_[j]->data().grad.get(txn, id()), add);
+      add = true;
+    }
+  }
+}
+
+ActVar ReduceOpF::MakeParallel(size_t root, vector<ActVar> inputs, shared_ptr<Context> ctx) {
+  auto shared = make_shared<ReduceOpF>(root, inputs, ctx);
+  auto o = make_shared<CollectiveOutF>(shared, inputs.at(0), root, ctx);
+  shared->out_ = o.get();
+  return o;
+}
+ReduceOpF::ReduceOpF(size_t root, vector<ActVar> inputs, shared_ptr<Context> ctx) : root_(root), xs_(inputs), ctx_(ctx) {
+  in_process(ctx);
+  for (auto& x : inputs) inputs_.push_back(x);
+}
+void ReduceOpF::_forward(TxnId txn) {
+  if (done_fwd_ && *done_fwd_ == txn.raw_id()) return;
+  done_fwd_ = txn.raw_id();
+  auto* m = in_process(ctx_);
+  auto yd = out_->data();
+  if (!yd.val.overwrite(txn, id())) return;
+  for (size_t j = 0; j < xs_.size(); ++j)
+    pull(m, root_, yd.val.get_excl(txn, id()), xs_[j]->rank(), xs_[j]->data().val.get(txn, id()), j != 0);
+}
+void ReduceOpF::_backward(TxnId txn) {
+  if (done_bwd_ && *done_bwd_ == txn.raw_id()) return;
+  done_bwd_ = txn.raw_id();
+  auto* m = in_process(ctx_);
+  Act& dy = out_->data().grad.get(txn, id());
+  for (auto& x : xs_) {
+    auto xd = x->data();
+    const int mode = xd.grad.accumulate_full(txn, id(), unpadded, zero_init(m->device_context(x->rank()).get()));
+    if (!mode) continue;
+    pull(m, x->rank(), xd.grad.get_mut(txn, id()), root_, dy, mode == 1);
+  }
+}
+
 // ------------------------------------------------------------------ fully connected
 shared_ptr<CublasLinearOpF> CublasLinearOpF::Make(size_t filters, ActVar x, shared_ptr<Var<Kernel>> kernel, shared_ptr<Var<Bias>> bias,
                                                   shared_ptr<Context> ctx) {

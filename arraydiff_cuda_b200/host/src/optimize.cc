@@ -1,3 +1,6 @@
+#include <cstdio>
+#include <cstring>
+
 #include "arraydiff/optimize.hh"
 
 namespace arraydiff {
@@ -196,6 +199,122 @@ void ParallelSGDOptimizer<float>::step(function<void(TxnId, size_t, shared_ptr<O
   }
   ++iter_count_;
   mgpu_->end_phase();
+}
+
+// ------------------------------------------------------------------ checkpoint file
+namespace {
+struct File {
+  FILE* f;
+  explicit File(const string& path, const char* mode) : f(std::fopen(path.c_str(), mode)) {}
+  ~File() { if (f) std::fclose(f); }
+  template <typename V> bool put(const V& v) { return std::fwrite(&v, sizeof(V), 1, f) == 1; }
+  template <typename V> bool get(V& v) { return std::fread(&v, sizeof(V), 1, f) == 1; }
+};
+const char kMagic[8] = {'A', 'D', 'B', '2', 'C', 'K', 'P', 'T'};
+}  // namespace
+
+template <>
+bool ParallelSGDOptimizer<float>::save_checkpoint(const string& path) {
+  assert(mgpu_ && "reset first");
+  const size_t first = mgpu_->distributed() ? mgpu_->my_rank() : 0;
+  ParamManifest man;
+  {
+    any w = &man;
+    TxnId t;
+    sink_->store_val(t, params_[first], 0, &w);
+  }
+  vector<float> theta(param_dim_), mom(param_dim_), stat(stat_dim_);
+  {
+    GPUConn conn = mgpu_->device_context(first)->conn();
+    param_[first].store_sync(theta.data(), param_dim_, 0, conn);
+    momentum_[first].store_sync(mom.data(), param_dim_, 0, conn);
+    if (stat_dim_) running_stat_[first].store_sync(stat.data(), stat_dim_, 0, conn);
+  }
+  File out(path, "wb");
+  if (!out.f) return false;
+  bool ok = std::fwrite(kMagic, 1, 8, out.f) == 8 && out.put((uint32_t)1) && out.put((uint64_t)param_dim_) &&
+            out.put((uint64_t)stat_dim_) && out.put((uint64_t)iter_count_) && out.put((uint32_t)man.size());
+  for (auto& e : man) {
+    ok = ok && out.put((uint32_t)e.name.size()) && std::fwrite(e.name.data(), 1, e.name.size(), out.f) == e.name.size() &&
+         out.put((uint64_t)e.offset) && out.put((uint64_t)e.size);
+  }
+  ok = ok && std::fwrite(theta.data(), 4, param_dim_, out.f) == param_dim_ && std::fwrite(mom.data(), 4, param_dim_, out.f) == param_dim_ &&
+       std::fwrite(stat.data(), 4, stat_dim_, out.f) == stat_dim_;
+  return ok;
+}
+
+template <>
+bool ParallelSGDOptimizer<float>::load_checkpoint(const string& path) {
+  assert(mgpu_ && "reset first");
+  File in(path, "rb");
+  if (!in.f) return false;
+  char magic[8];
+  uint32_t version = 0, entries = 0;
+  uint64_t pd = 0, sd = 0, it = 0;
+  if (std::fread(magic, 1, 8, in.f) != 8 || std::memcmp(magic, kMagic, 8) || !in.get(version) || version != 1 || !in.get(pd) ||
+      !in.get(sd) || !in.get(it) || !in.get(entries))
+    return false;
+  if (pd != param_dim_ || sd != stat_dim_) return false;
+  const size_t first = mgpu_->distributed() ? mgpu_->my_rank() : 0;
+  ParamManifest man;
+  {
+    any w = &man;
+    TxnId t;
+    sink_->store_val(t, params_[first], 0, &w);
+  }
+  if (entries != man.size()) return false;
+  for (auto& e : man) {
+    uint32_t len = 0;
+    uint64_t off = 0, size = 0;
+    if (!in.get(len) || len > 4096) return false;
+    string name(len, ' ');
+    if (std::fread(&name[0], 1, len, in.f) != len || !in.get(off) || !in.get(size)) return false;
+    if (name != e.name || off != e.offset || size != e.size) return false;   // another net, or another build order
+  }
+  vector<float> theta(param_dim_), mom(param_dim_), stat(stat_dim_);
+  if (std::fread(theta.data(), 4, param_dim_, in.f) != param_dim_ || std::fread(mom.data(), 4, param_dim_, in.f) != param_dim_ ||
+      std::fread(stat.data(), 4, stat_dim_, in.f) != stat_dim_)
+    return false;
+  TxnId txn;
+  for (size_t r = 0; r < mgpu_->num_ranks(); ++r) {
+    if (!mgpu_->is_local(r)) continue;
+    GPUConn conn = mgpu_->device_context(r)->conn();
+    param_[r].load_sync(theta.data(), param_dim_, 0, conn);
+    momentum_[r].load_sync(mom.data(), param_dim_, 0, conn);
+    any rd = param_[r];
+    sink_->load_val(txn, params_[r], 0, &rd);
+    if (stat_dim_) {
+      running_stat_[r].load_sync(stat.data(), stat_dim_, 0, conn);
+      any rs = running_stat_[r];
+      sink_->load_val(txn, fixed_stats_[r], 0, &rs);
+    }
+    conn.sync();
+  }
+  iter_count_ = (size_t)it;
+  return true;
+}
+
+template <>
+void ParallelSGDOptimizer<float>::broadcast_from_worker0() {
+  assert(mgpu_ && mgpu_->distributed() && "reset first, on a context made with MakeDistributed");
+  const size_t me = mgpu_->my_rank();
+  GPUConn conn = mgpu_->device_context(me)->conn();
+  const bool root = mgpu_->exchange_rank() == 0;
+  if (!root) {
+    AD_CHECK(ad_fill_zero(param_[me].dptr(), param_dim_ * 4, conn.stream()));
+    if (stat_dim_) AD_CHECK(ad_fill_zero(running_stat_[me].dptr(), stat_dim_ * 4, conn.stream()));
+  }
+  mgpu_->allreduce_sum(param_[me].dptr(), param_dim_);       // x + 0 + ... + 0: worker 0's bits
+  if (stat_dim_) mgpu_->allreduce_sum(running_stat_[me].dptr(), stat_dim_);
+  TxnId txn;
+  any rd = param_[me];
+  sink_->load_val(txn, params_[me], 0, &rd);
+  if (stat_dim_) {
+    any rs = running_stat_[me];
+    sink_->load_val(txn, fixed_stats_[me], 0, &rs);
+  }
+  mgpu_->end_phase();
+  conn.sync();
 }
 
 template <>

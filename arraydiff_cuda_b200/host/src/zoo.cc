@@ -304,6 +304,39 @@ SpatialParallelNet SpatialParallelResNet<float>::MakeConv3x3(const ConvNetConfig
   return net;
 }
 
+// The same layer written the reference's way (src/zoo.cc:1522-1523, :1841-1842, :1873): the image lives on rank 0 and is
+// broadcast, every rank cuts out its strip inside the graph, the strips of the result are placed into zeroed full
+// tensors and all-reduced (= all-gathered), and the replicas are reduced to rank 0.  The single output is therefore
+// R times the convolution of the whole image.  One-process contexts only.
+template <>
+SpatialParallelNet SpatialParallelResNet<float>::MakeConv3x3Collectives(const ConvNetConfig& cfg, size_t filters, shared_ptr<Context> ctx) {
+  SpatialParallelNet net;
+  const size_t R = ranks_of(ctx);
+  net.batch_norm_use_fixed = make_shared<bool>(false);
+  net.dev_params.resize(R); net.dev_grads.resize(R); net.dev_batch_stats.resize(R); net.dev_fixed_stats.resize(R);
+  net.output_grad_vars.resize(R);
+  auto in = IOOp<Act>::Make(Shape3D(cfg.input_w, cfg.input_h, cfg.input_c), cfg.batch_size, nullptr, 0, ctx);
+  net.inputs.assign(R, nullptr);
+  net.inputs[0] = in;
+  net.input_vars.insert(in->data().val.var());
+  auto everywhere = BroadcastOp<Act>::MakeParallel(0, in, ctx);
+  auto strips = SpatialScatter2DOp<Act>::MakeParallel(everywhere, ctx);
+  Conv2DShape s;
+  s.filters = filters; s.kernel = {3, 3}; s.pad = {1, 1}; s.halo_padded_input = true;
+  auto pad = HaloPad2DOp<Act>::MakeParallel(1, strips, ctx);
+  auto exch = HaloExch2DOp<Act>::MakeParallel(1, pad, ctx);
+  ParallelParamOp<Act> conv;
+  { NameScope scope("conv"); conv = parallel_conv2d<Act>(s, exch, kaiming_init_gen<GPUArray4D<float>>(cfg.input_c * 9, filters), false, ctx); }
+  absorb(net, conv.ops, conv.params, conv.grads);
+  auto placed = SpatialGather2DOp<Act>::MakeParallel(conv.ops, ctx);
+  auto full = AllreduceOp<Act>::MakeParallel(placed, ctx);
+  ActVar total = ReduceOp<Act>::MakeParallel(0, full, ctx);
+  net.outputs = {total};
+  net.sink = make_shared<GroupSinkOp>(vector<shared_ptr<Op>>{total});
+  net.output_grad_vars[0].insert(total->data().grad.var());
+  return net;
+}
+
 // ResNet stem on H-strips: halo 3, 7x7/2 -> `width` channels, BN + ReLU, then a 3x3/2 max pool on a halo-1 strip
 static vector<ActVar> stem(SpatialParallelNet& net, const ConvNetConfig& cfg, size_t width, vector<ActVar> strips, shared_ptr<Context> ctx) {
   auto sw = net.batch_norm_use_fixed;

@@ -57,6 +57,11 @@ def load():
         L.adh_net_graph_launches.argtypes = [vp]
         for name in ("adh_net_backward", "adh_net_sgd_step", "adh_net_sync", "adh_net_status"):
             getattr(L, name).argtypes = [vp]
+        L.adh_net_save_checkpoint.argtypes = [vp, C.c_char_p]
+        L.adh_net_load_checkpoint.argtypes = [vp, C.c_char_p]
+        L.adh_net_broadcast_params.argtypes = [vp]
+        L.adh_net_iteration.restype = C.c_size_t
+        L.adh_net_iteration.argtypes = [vp]
         L.adh_net_arena_used.restype = C.c_size_t
         L.adh_net_arena_used.argtypes = [vp, C.c_int]
         _lib = L
@@ -181,6 +186,20 @@ class Net:
         """kernels one graph replay launches"""
         return int(self.L.adh_net_graph_launches(self.h))
 
+    def save_checkpoint(self, path):
+        """parameters, momentum, running statistics and the iteration counter -> one file (format: optimize.hh)"""
+        assert self.L.adh_net_save_checkpoint(self.h, str(path).encode()) == 0
+
+    def load_checkpoint(self, path):
+        return self.L.adh_net_load_checkpoint(self.h, str(path).encode()) == 0
+
+    def iteration(self):
+        return int(self.L.adh_net_iteration(self.h))
+
+    def broadcast_params(self):
+        """one process per GPU: worker 0's parameters become everyone's"""
+        assert self.L.adh_net_broadcast_params(self.h) == 0
+
     def sgd_step(self):
         self.L.adh_net_sgd_step(self.h)
 
@@ -194,3 +213,28 @@ class Net:
         if self.h:
             self.L.adh_net_destroy(self.h)
             self.h = None
+
+
+def read_checkpoint(path):
+    """Parses a checkpoint file written by Net.save_checkpoint (layout documented in host/include/arraydiff/optimize.hh):
+    returns dict(version, param_dim, stat_dim, iteration, manifest={name: (offset, size)}, params, momentum, stats)."""
+    import struct
+    with open(path, "rb") as f:
+        raw = f.read()
+    assert raw[:8] == b"ADB2CKPT", "not a checkpoint file"
+    version, pd, sd, it, n = struct.unpack_from("<IQQQI", raw, 8)
+    pos = 8 + 4 + 8 * 3 + 4
+    man = {}
+    for _ in range(n):
+        (ln,) = struct.unpack_from("<I", raw, pos)
+        pos += 4
+        name = raw[pos:pos + ln].decode()
+        pos += ln
+        off, size = struct.unpack_from("<QQ", raw, pos)
+        pos += 16
+        man[name] = (off, size)
+    theta = np.frombuffer(raw, np.float32, pd, pos)
+    mom = np.frombuffer(raw, np.float32, pd, pos + 4 * pd)
+    stats = np.frombuffer(raw, np.float32, sd, pos + 8 * pd)
+    assert pos + 8 * pd + 4 * sd == len(raw), "trailing or missing bytes"
+    return dict(version=version, param_dim=pd, stat_dim=sd, iteration=it, manifest=man, params=theta, momentum=mom, stats=stats)

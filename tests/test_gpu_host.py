@@ -74,6 +74,38 @@ def test_config1_partitioned_conv3x3_forward_backward_update(R, mode):
     net.close(); ctx.close()
 
 
+@pytest.mark.parametrize("R", [1, 2, 4])
+@pytest.mark.parametrize("mode", ["f32", "bf16"])
+def test_conv3x3_between_reference_collective_operators(R, mode):
+    """The reference's graph shape for a partitioned layer -- BroadcastOp, SpatialScatter2DOp, pad / exchange / conv,
+    SpatialGather2DOp, AllreduceOp, ReduceOp -- against the unsplit oracle conv: the single output on rank 0 is R times
+    the convolution, and the gradients carry the same factor back."""
+    from arraydiff_cuda_b200 import hostlib
+    N, Cc, K, Hh, W = 2, 64, 64, 32, 40
+    ctx = hostlib.Context([0] * R, hostlib.F32_NCHW if mode == "f32" else hostlib.BF16_NHWC, arena_mb=256)
+    net = hostlib.Net(ctx, "conv3x3_collectives", Hh, W, Cc, N, K, seed=7)
+    tol = 1e-5 if mode == "f32" else 2e-2
+    x = H.uniform(110, (N, Cc, Hh, W))
+    w = H.normal(111, (K, Cc, 3, 3), float(np.sqrt(2.0 / (9 * 64))))
+    dy = H.uniform(112, (N, K, Hh, W))
+    if mode == "bf16":
+        x, w, dy = orc.round_bf16(x), orc.round_bf16(w), orc.round_bf16(dy)
+    net.set_params(w.reshape(-1))
+    assert net.strip_shape == (N, K, Hh, W)
+    y_w = orc.conv2d_fprop(x, w, None, pad=(1, 1), omp=True)
+    net.forward(x)
+    assert H.max_rel(net.output(0), R * y_w) < tol
+    net.set_output_grad(0, dy)
+    net.backward()
+    dx_w = orc.conv2d_dgrad(dy, w, x.shape, pad=(1, 1), omp=True)
+    dw_w = orc.conv2d_wgrad(x, dy, w.shape, pad=(1, 1), omp=True)
+    assert H.max_rel(net.input_grad(0), R * dx_w) < (tol if R == 1 or mode == "f32" else 3e-2)
+    dw = sum(net.param_grads(r) for r in range(R)).reshape(w.shape)
+    assert H.max_rel(dw, R * dw_w) < (3e-5 if mode == "f32" else 3e-2)
+    assert net.status() == 0
+    net.close(); ctx.close()
+
+
 @pytest.mark.parametrize("R,mode", [(1, "f32"), (2, "f32"), (4, "f32"), (2, "bf16")])
 def test_stem_stage1_matches_oracle(R, mode):
     """ResNet-50 stem + stage 1 (benchmark config 3 at a reduced image size) through the op graph:
@@ -412,3 +444,56 @@ def test_parallel_resnet50_classifier_matches_oracle(R, mode):
             cos = float(np.dot(a, b) / max(np.linalg.norm(a) * np.linalg.norm(b), 1e-30))
             assert cos > 0.7, (name, cos)
     assert net.status() == 0
+
+
+@pytest.mark.parametrize("R", [1, 2])
+def test_flat_parameter_checkpoint_round_trip(R, tmp_path):
+    """save -> train on -> restore into a fresh net -> train the same steps: parameters equal bit for bit (momentum and
+    the iteration counter travel with the parameters); the file parses with the documented layout."""
+    from arraydiff_cuda_b200 import hostlib
+    Hh, W, Cc, N = 64, 64, 3, 1
+
+    def make():
+        ctx = hostlib.Context([0] * R, hostlib.BF16_NHWC, arena_mb=512)
+        net = hostlib.Net(ctx, "stem_stage1", Hh, W, Cc, N, seed=3)
+        net.configure_sgd(0.01, 0.9, l2=1e-4, nesterov=True)
+        return ctx, net
+
+    x = H.uniform(500, (N, Cc, Hh, W), 0, 1)
+
+    def steps(net, k):
+        dy = [H.normal(501 + r, net.strip_shape) for r in range(R)]
+        for _ in range(k):
+            net.forward(x)
+            for r in range(R):
+                net.set_output_grad(r, dy[r])
+            net.backward()
+            net.sgd_step()
+        net.sync()
+
+    ctx, net = make()
+    steps(net, 2)
+    path = tmp_path / "ckpt.bin"
+    net.save_checkpoint(path)
+    at_save = net.params(0).copy()
+    steps(net, 2)
+    want = net.params(0).copy()
+    ck = hostlib.read_checkpoint(path)
+    assert ck["version"] == 1 and ck["param_dim"] == net.nparam and ck["iteration"] == 2
+    assert np.array_equal(ck["params"], at_save) and np.any(ck["momentum"] != 0)
+    assert ck["manifest"] == net.manifest()
+    net.close(); ctx.close()
+
+    ctx2, net2 = make()
+    assert net2.load_checkpoint(path) and net2.iteration() == 2
+    for r in range(R):
+        assert np.array_equal(net2.params(r), at_save)
+    steps(net2, 2)
+    for r in range(R):
+        assert np.array_equal(net2.params(r), want)
+    # a file of another net is refused
+    ctx3 = hostlib.Context([0], hostlib.BF16_NHWC, arena_mb=256)
+    other = hostlib.Net(ctx3, "conv3x3", 32, 32, 64, 1, 64, seed=1)
+    assert not other.load_checkpoint(path)
+    assert not net2.load_checkpoint(tmp_path / "missing.bin")
+    net2.close(); ctx2.close(); other.close(); ctx3.close()
