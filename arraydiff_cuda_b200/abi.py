@@ -29,6 +29,20 @@ class HaloArgs(C.Structure):
     ]
 
 
+class Halo2dArgs(C.Structure):
+    _fields_ = [
+        ("dtype", i32), ("layout", i32),
+        ("halo_pad", u32), ("base_width", u32), ("base_height", u32), ("num_channels", u32), ("batch_size", u32),
+        ("grid_w", u32), ("grid_h", u32), ("rank_first", u32), ("rank_count", u32),
+        ("push", i32),
+        ("bufs", vp * AD_MAX_PEERS),
+        ("signal_flags", vp * AD_MAX_PEERS),
+        ("epoch", u64),
+        ("block_counter", vp),
+        ("epoch_base", vp),
+    ]
+
+
 class Tensor4(C.Structure):
     _fields_ = [("base", vp), ("dtype", i32), ("N", u32), ("C", u32), ("H", u32), ("W", u32),
                 ("sn", i64), ("sc", i64), ("sy", i64), ("sx", i64)]
@@ -63,6 +77,8 @@ SIGNATURES = {
     "ad_launch_count": (u64, []),
     "ad_halo_exchange": (C.c_int, [C.POINTER(HaloArgs), vp]),
     "ad_halo_reduce": (C.c_int, [C.POINTER(HaloArgs), vp]),
+    "ad_halo2d_exchange": (C.c_int, [C.POINTER(Halo2dArgs), vp]),
+    "ad_halo2d_reduce": (C.c_int, [C.POINTER(Halo2dArgs), vp]),
     "ad_flag_wait": (C.c_int, [vp, u64, u64, vp, vp]),
     "ad_flag_signal": (C.c_int, [vp, u64, vp]),
     "ad_ipc_get_handle": (C.c_int, [vp, C.c_char_p]),

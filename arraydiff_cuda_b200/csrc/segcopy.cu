@@ -26,6 +26,10 @@ struct SegJob {
   char* dst;
   uint32_t src_row0, dst_row0;
   int32_t signal_rank;  // -1: none
+  // geometry of this job's segments; zero rows = take the launch-wide values of SegParams (filled in by launch_seg)
+  uint32_t rows, seg_bytes, chunks_per_seg;
+  uint32_t src_xoff, dst_xoff;         // bytes
+  unsigned long long first_unit;       // work units (plane, row, chunk) of the jobs before this one
 };
 
 struct SegParams {
@@ -35,6 +39,7 @@ struct SegParams {
   int32_t accumulate;   // dst += src (fp32 add; bf16: fp32 add + RNE)
   uint32_t planes, rows;
   uint32_t seg_bytes, chunks_per_seg;
+  unsigned long long total_units;
   unsigned long long src_plane_stride, src_row_stride, src_xoff;  // bytes
   unsigned long long dst_plane_stride, dst_row_stride, dst_xoff;  // bytes
   // completion signal (halo exchange)
@@ -156,24 +161,24 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) seg_move_kernel(const Seg
   __shared__ __align__(16) char stage_all[kWarpsPerBlock][kStage];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   char* stage = stage_all[warp];
-  const unsigned long long per_job = (unsigned long long)prm.planes * prm.rows * prm.chunks_per_seg;
-  const unsigned long long total = per_job * (unsigned long long)prm.njobs;
+  const unsigned long long total = prm.total_units;
   const unsigned long long nwarps = (unsigned long long)gridDim.x * kWarpsPerBlock;
   for (unsigned long long u = (unsigned long long)blockIdx.x * kWarpsPerBlock + warp; u < total; u += nwarps) {
-    const uint32_t job = (uint32_t)(u / per_job);
-    unsigned long long r = u - (unsigned long long)job * per_job;
-    const uint32_t chunk = (uint32_t)(r % prm.chunks_per_seg);
-    r /= prm.chunks_per_seg;
-    const uint32_t row = (uint32_t)(r % prm.rows);
-    const unsigned long long plane = r / prm.rows;
+    uint32_t job = 0;
+    while (job + 1 < (uint32_t)prm.njobs && u >= prm.jobs[job + 1].first_unit) ++job;
     const SegJob& jb = prm.jobs[job];
+    unsigned long long r = u - jb.first_unit;
+    const uint32_t chunk = (uint32_t)(r % jb.chunks_per_seg);
+    r /= jb.chunks_per_seg;
+    const uint32_t row = (uint32_t)(r % jb.rows);
+    const unsigned long long plane = r / jb.rows;
     const uint32_t off = chunk * kChunk;
-    uint32_t len = prm.seg_bytes - off;
+    uint32_t len = jb.seg_bytes - off;
     if (len > (uint32_t)kChunk) len = kChunk;
     const char* s = jb.src + plane * prm.src_plane_stride + (unsigned long long)(jb.src_row0 + row) * prm.src_row_stride +
-                    prm.src_xoff + off;
+                    jb.src_xoff + off;
     char* d = jb.dst + plane * prm.dst_plane_stride + (unsigned long long)(jb.dst_row0 + row) * prm.dst_row_stride +
-              prm.dst_xoff + off;
+              jb.dst_xoff + off;
     warp_move<ELEM, ACC>(s, d, len, stage, lane);
   }
   if (prm.signal_mask != 0u) {
@@ -197,9 +202,19 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) seg_move_kernel(const Seg
   }
 }
 
-static int launch_seg(const SegParams& prm, cudaStream_t stream) {
-  const unsigned long long total =
-      (unsigned long long)prm.planes * prm.rows * prm.chunks_per_seg * (unsigned long long)prm.njobs;
+static int launch_seg(SegParams& prm, cudaStream_t stream) {
+  unsigned long long total = 0;
+  for (int j = 0; j < prm.njobs; ++j) {
+    SegJob& jb = prm.jobs[j];
+    if (jb.rows == 0) {      // a job without its own geometry takes the launch-wide one
+      jb.rows = prm.rows; jb.seg_bytes = prm.seg_bytes;
+      jb.src_xoff = (uint32_t)prm.src_xoff; jb.dst_xoff = (uint32_t)prm.dst_xoff;
+    }
+    jb.chunks_per_seg = (jb.seg_bytes + kChunk - 1) / kChunk;
+    jb.first_unit = total;
+    total += (unsigned long long)prm.planes * jb.rows * jb.chunks_per_seg;
+  }
+  prm.total_units = total;
   if (total == 0) return AD_OK;
   const unsigned grid = grid_for((size_t)total, kWarpsPerBlock, 8);
   dim3 block(kWarpsPerBlock * 32);
@@ -362,3 +377,114 @@ extern "C" int ad_slice2d_add_hw_nchw_packed(int32_t dtype, uint32_t count_w, ui
   return slice2d(1, dtype, count_w, count_h, src_width, src_height, dst_width, dst_height, channels, batch_size, src,
                  src_w_off, src_h_off, dst, dst_w_off, dst_h_off, stream);
 }
+
+
+// ------------------------------------------------------------------------------------------ 2-D rank grids
+namespace adk {
+// Faces and corners of rank (gy, gx) in a grid_h x grid_w grid.  Every padded buffer holds (h + 2p) x (w + 2p)
+// positions per plane with the interior at (p, p).  A region is (first row, row count, first column, column count)
+// in padded coordinates.
+struct Region { uint32_t y0, ny, x0, nx; };
+// what rank r SENDS towards neighbour direction (dy, dx) -- its interior edge -- and where that lands in the
+// neighbour's halo
+static void halo2d_regions(int dy, int dx, uint32_t p, uint32_t w, uint32_t h, Region& mine, Region& theirs) {
+  mine.y0 = dy < 0 ? p : dy > 0 ? h : p;           mine.ny = dy == 0 ? h : p;
+  mine.x0 = dx < 0 ? p : dx > 0 ? w : p;           mine.nx = dx == 0 ? w : p;
+  theirs.y0 = dy < 0 ? p + h : dy > 0 ? 0 : p;     theirs.ny = mine.ny;
+  theirs.x0 = dx < 0 ? p + w : dx > 0 ? 0 : p;     theirs.nx = mine.nx;
+}
+static int check_halo2d(const ad_halo2d_args* a) {
+  if (!a) return AD_ERR_BAD_ARG;
+  if (elem_size(a->dtype) == 0) return AD_ERR_UNSUPPORTED;
+  if (a->layout != AD_NCHW && a->layout != AD_NHWC) return AD_ERR_UNSUPPORTED;
+  const uint32_t R = a->grid_w * a->grid_h;
+  if (a->grid_w < 1 || a->grid_h < 1 || R > AD_MAX_PEERS) return AD_ERR_BAD_ARG;
+  if (a->rank_count == 0 || a->rank_first + a->rank_count > R) return AD_ERR_BAD_ARG;
+  if (a->base_width == 0 || a->base_height == 0 || a->num_channels == 0 || a->batch_size == 0) return AD_ERR_BAD_ARG;
+  if (a->grid_h > 1 && a->base_height < 2 * a->halo_pad) return AD_ERR_BAD_ARG;
+  if (a->grid_w > 1 && a->base_width < 2 * a->halo_pad) return AD_ERR_BAD_ARG;
+  for (uint32_t r = 0; r < R; ++r) {
+    if (!a->bufs[r]) return AD_ERR_BAD_ARG;
+    if (((uintptr_t)a->bufs[r] % (uintptr_t)elem_size(a->dtype)) != 0) return AD_ERR_ALIGN;
+  }
+  return AD_OK;
+}
+// One launch per served rank and per phase: phase 0 = the two row faces, 1 = the two column faces, 2 = the corners.
+// The exchange runs all phases in one launch (no two jobs write the same cells); the accumulate-back runs them one
+// after another, because a corner cell of the interior receives a row face, a column face and a corner.
+static int halo2d(const ad_halo2d_args* a, bool reduce, cudaStream_t stream) {
+  int st = check_halo2d(a);
+  if (st != AD_OK) return st;
+  const uint32_t p = a->halo_pad, w = a->base_width, h = a->base_height, gw = a->grid_w, gh = a->grid_h;
+  if (p == 0 || gw * gh == 1) return AD_OK;
+  const unsigned long long es = (unsigned long long)elem_size(a->dtype);
+  const unsigned long long Wp = w + 2ull * p, Hp = h + 2ull * p, C = a->num_channels, N = a->batch_size;
+  const unsigned long long px = a->layout == AD_NCHW ? es : C * es;     // bytes of one pixel step along x
+  bool want_signal = false;
+  if (!reduce)
+    for (uint32_t q = 0; q < gw * gh; ++q) want_signal |= (a->signal_flags[q] != nullptr);
+  if (want_signal && !a->block_counter) return AD_ERR_BAD_ARG;
+  for (uint32_t r = a->rank_first; r < a->rank_first + a->rank_count; ++r) {
+    const int gy = (int)(r / gw), gx = (int)(r % gw);
+    for (int phase = 0; phase < (reduce ? 3 : 1); ++phase) {
+      SegParams prm{};
+      prm.elem = (int)es;
+      prm.accumulate = reduce ? 1 : 0;
+      if (a->layout == AD_NCHW) { prm.planes = (uint32_t)(N * C); prm.src_plane_stride = Hp * Wp * es; prm.src_row_stride = Wp * es; }
+      else { prm.planes = (uint32_t)N; prm.src_plane_stride = Hp * Wp * C * es; prm.src_row_stride = Wp * C * es; }
+      prm.dst_plane_stride = prm.src_plane_stride;
+      prm.dst_row_stride = prm.src_row_stride;
+      int nj = 0;
+      for (int dy = -1; dy <= 1; ++dy)
+        for (int dx = -1; dx <= 1; ++dx) {
+          if (!dy && !dx) continue;
+          const int kind = (dy && dx) ? 2 : (dy ? 0 : 1);
+          if (reduce && kind != phase) continue;
+          const int ny = gy + dy, nx = gx + dx;
+          if (ny < 0 || nx < 0 || ny >= (int)gh || nx >= (int)gw) continue;
+          const uint32_t q = (uint32_t)ny * gw + (uint32_t)nx;
+          Region mine, theirs;
+          halo2d_regions(dy, dx, p, w, h, mine, theirs);
+          SegJob jb{};
+          if (!reduce && a->push) {            // my edge -> the neighbour's halo
+            jb.src = (const char*)a->bufs[r]; jb.dst = (char*)a->bufs[q];
+            jb.src_row0 = mine.y0; jb.dst_row0 = theirs.y0;
+            jb.src_xoff = (uint32_t)(mine.x0 * px); jb.dst_xoff = (uint32_t)(theirs.x0 * px);
+            jb.signal_rank = (int)q;
+          } else if (!reduce) {                // pull: the neighbour's edge (towards me) -> my halo
+            Region his, here;
+            halo2d_regions(-dy, -dx, p, w, h, his, here);
+            jb.src = (const char*)a->bufs[q]; jb.dst = (char*)a->bufs[r];
+            jb.src_row0 = his.y0; jb.dst_row0 = here.y0;
+            jb.src_xoff = (uint32_t)(his.x0 * px); jb.dst_xoff = (uint32_t)(here.x0 * px);
+            jb.signal_rank = (int)r;
+          } else {                             // accumulate-back: the neighbour's halo copy of my edge adds into my edge
+            jb.src = (const char*)a->bufs[q]; jb.dst = (char*)a->bufs[r];
+            jb.src_row0 = theirs.y0; jb.dst_row0 = mine.y0;
+            jb.src_xoff = (uint32_t)(theirs.x0 * px); jb.dst_xoff = (uint32_t)(mine.x0 * px);
+            jb.signal_rank = -1;
+          }
+          jb.rows = mine.ny;
+          jb.seg_bytes = (uint32_t)(mine.nx * px);
+          prm.jobs[nj++] = jb;
+        }
+      prm.njobs = nj;
+      if (want_signal) {
+        for (int j = 0; j < nj; ++j) {
+          const int q = prm.jobs[j].signal_rank;
+          if (q >= 0 && a->signal_flags[q]) { prm.signal_flags[q] = a->signal_flags[q]; prm.signal_mask |= 1u << q; }
+        }
+        prm.epoch = a->epoch;
+        prm.epoch_base = (const unsigned long long*)a->epoch_base;
+        prm.block_counter = a->block_counter;
+      }
+      st = launch_seg(prm, stream);
+      if (st != AD_OK) return st;
+    }
+  }
+  return AD_OK;
+}
+}  // namespace adk
+
+extern "C" int ad_halo2d_exchange(const ad_halo2d_args* a, void* stream) { return adk::halo2d(a, false, as_stream(stream)); }
+extern "C" int ad_halo2d_reduce(const ad_halo2d_args* a, void* stream) { return adk::halo2d(a, true, as_stream(stream)); }

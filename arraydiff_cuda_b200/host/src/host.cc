@@ -140,7 +140,7 @@ shared_ptr<GPUContext> MultiGPUContext::device_context(size_t rank) { assert(dev
 Spatial2DComm* MultiGPUContext::spatial_comm(size_t rank) { return &spatial_comms_[rank]; }
 
 void MultiGPUContext::allreduce_sum(float* buf, size_t count) {
-  if (num_ranks_ == 1) return;
+  if (num_ranks_ == 1 && world_size_ <= 1 && !(distributed_ && ar_hook_)) return;
   if (distributed_ && ar_hook_) {
     ar_hook_(buf, count, dev_ctxs_[my_rank_]->stream(), ar_user_);   // e.g. ncclAllReduce
     return;

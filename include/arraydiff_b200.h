@@ -101,6 +101,33 @@ int ad_halo_exchange(const ad_halo_args* args, void* stream);
 int ad_halo_reduce(const ad_halo_args* args, void* stream);
 
 /*
+ * The same two operations on a 2-D grid of grid_h x grid_w ranks (rank = gy * grid_w + gx): row faces (p x w), column
+ * faces (h x p) and the four p x p corners move between the up-to-8 neighbours of every served rank, so that after
+ * the exchange each padded buffer equals its window of the zero-padded whole tensor.  Covers the reference's W-split
+ * exchange (2 x 1 ranks, src/kernels/spatial.cu:654-768; host dispatch src/spatial.cc:105-131, :166-196) and the 2 x 2
+ * grid it wrote but never linked (:782-1021), for every grid of at most AD_MAX_PEERS ranks.  base_width / base_height
+ * are one rank's interior dims.  The exchange is one launch per served rank; the accumulate-back is three (row faces,
+ * then column faces, then corners: an interior corner cell receives one addend from each, summed in that order).
+ * With a signal flag set the exchange publishes `epoch` to the ranks it wrote to, as ad_halo_exchange does; when one
+ * call serves several ranks that write to the same neighbour, give each its own call or wait for all of them.
+ * Requires h >= 2p when grid_h > 1 and w >= 2p when grid_w > 1.
+ */
+typedef struct {
+  int32_t dtype, layout;
+  uint32_t halo_pad, base_width, base_height, num_channels, batch_size;
+  uint32_t grid_w, grid_h;
+  uint32_t rank_first, rank_count;
+  int32_t push;
+  void* bufs[AD_MAX_PEERS];
+  uint64_t* signal_flags[AD_MAX_PEERS];
+  uint64_t epoch;
+  uint32_t* block_counter;
+  const uint64_t* epoch_base;
+} ad_halo2d_args;
+int ad_halo2d_exchange(const ad_halo2d_args* args, void* stream);
+int ad_halo2d_reduce(const ad_halo2d_args* args, void* stream);
+
+/*
  * Bounded wait for *flag >= epoch (system-scope acquire).  Gives up after timeout_ns nanoseconds
  * of device time and then stores AD_ERR_TIMEOUT to *status_word (device memory, caller zeroes it)
  * instead of spinning on; the host reads the status word at its next synchronisation point.

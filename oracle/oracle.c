@@ -180,6 +180,58 @@ void orc_halo_reduce(int R, void** bufs, int dtype, int layout,
   }
 }
 
+/*
+ * The same two operations on a grid of grid_h x grid_w ranks (rank = gy * grid_w + gx), each holding a padded
+ * (h + 2p) x (w + 2p) buffer: every rank's halo cells take the value of the interior cell of the neighbour (one of
+ * up to 8: sides and corners) that owns that position of the whole tensor; halo cells beyond the tensor are left
+ * untouched.  The reference has the W-split 2 x 1 case (src/kernels/spatial.cu:654-768, column offsets
+ * Src/Dst{Next,Prev}Width :175-205) and an unlinked 2 x 2 kernel (:782-1021); the rule restated here is the one
+ * all of them implement: cell (Y, X) of the whole tensor lives at padded (p + Y - gy*h, p + X - gx*w) of its owner.
+ */
+static void halo2d_walk(int reduce, int gw, int gh, void** bufs, int elem_or_dtype, int layout, int p, int w, int h, int C, int N) {
+  /* the accumulate-back adds in the order row faces, column faces, corners (the order the device uses) */
+  for (int phase = 0; phase < (reduce ? 3 : 1); ++phase)
+    for (int r = 0; r < gw * gh; ++r) {
+      int gy = r / gw, gx = r % gw;
+      for (int dy = -1; dy <= 1; ++dy)
+        for (int dx = -1; dx <= 1; ++dx) {
+          if (!dy && !dx) continue;
+          int kind = (dy && dx) ? 2 : (dy ? 0 : 1);
+          if (reduce && kind != phase) continue;
+          int ny = gy + dy, nx = gx + dx;
+          if (ny < 0 || nx < 0 || ny >= gh || nx >= gw) continue;
+          int q = ny * gw + nx;
+          /* my halo cells on side (dy, dx) <-> the neighbour's interior cells next to the shared edge */
+          int y0 = dy < 0 ? 0 : dy > 0 ? p + h : p, cy = dy == 0 ? h : p;
+          int x0 = dx < 0 ? 0 : dx > 0 ? p + w : p, cx = dx == 0 ? w : p;
+          int qy0 = dy < 0 ? h : dy > 0 ? p : p, qx0 = dx < 0 ? w : dx > 0 ? p : p;
+          for (int n = 0; n < N; ++n)
+            for (int c = 0; c < C; ++c)
+              for (int y = 0; y < cy; ++y)
+                for (int x = 0; x < cx; ++x) {
+                  size_t mine = strip_off(layout, p, w, h, C, n, c, y0 + y, x0 + x);
+                  size_t his = strip_off(layout, p, w, h, C, n, c, qy0 + y, qx0 + x);
+                  if (!reduce) {
+                    memcpy((char*)bufs[r] + mine * elem_or_dtype, (const char*)bufs[q] + his * elem_or_dtype, (size_t)elem_or_dtype);
+                  } else if (elem_or_dtype == ORC_DTYPE_F32) {
+                    /* the neighbour's interior edge cell += my halo copy of it */
+                    ((float*)bufs[q])[his] += ((const float*)bufs[r])[mine];
+                  } else {
+                    uint16_t* D = (uint16_t*)bufs[q];
+                    const uint16_t* S = (const uint16_t*)bufs[r];
+                    D[his] = orc_f32_to_bf16(orc_bf16_to_f32(D[his]) + orc_bf16_to_f32(S[mine]));
+                  }
+                }
+        }
+    }
+}
+void orc_halo2d_exchange(int gw, int gh, void** bufs, int elem_size, int layout, int p, int w, int h, int C, int N) {
+  halo2d_walk(0, gw, gh, bufs, elem_size, layout, p, w, h, C, N);
+}
+void orc_halo2d_reduce(int gw, int gh, void** bufs, int dtype, int layout, int p, int w, int h, int C, int N) {
+  halo2d_walk(1, gw, gh, bufs, dtype, layout, p, w, h, C, N);
+}
+
 /* ------------------------------------------------------------ slice / pad */
 
 /*

@@ -90,6 +90,16 @@ def halo_reduce(bufs, layout, p, W, h, Cc, N):
     _load().orc_halo_reduce(len(bufs), _ptr_array(bufs), dt, layout, p, W, h, Cc, N)
 
 
+def halo2d_exchange(bufs, layout, gw, gh, p, w, h, Cc, N):
+    """In place on the padded buffers of a gh x gw rank grid (rank = gy * gw + gx); float32 or uint16 (bf16 bits)."""
+    _load().orc_halo2d_exchange(gw, gh, _ptr_array(bufs), bufs[0].dtype.itemsize, layout, p, w, h, Cc, N)
+
+
+def halo2d_reduce(bufs, layout, gw, gh, p, w, h, Cc, N):
+    dt = F32 if bufs[0].dtype == np.float32 else BF16
+    _load().orc_halo2d_reduce(gw, gh, _ptr_array(bufs), dt, layout, p, w, h, Cc, N)
+
+
 def slice2d(add, count_w, count_h, src, src_w_off, src_h_off, dst, dst_w_off, dst_h_off):
     """src, dst: [N][C][H][W] float32; dst updated in place."""
     N, Cc, sh, sw = src.shape

@@ -31,6 +31,17 @@ int ref_halo_1x4(int reduce, uint32_t rank, uint32_t p, uint32_t W, uint32_t h, 
   return (int)cudaGetLastError();
 }
 
+// kernels.hh:168-190: the W-split pair (2 ranks side by side), src/kernels/spatial.cu:654-768.  Callers keep
+// halo_pad * base_height * channels * batch <= 16384 so that the launcher picks one block: its per-block work split
+// (total / blocks, rounded up) can run past the end for other block counts.
+int ref_halo_2x1(int reduce, uint32_t rank, uint32_t p, uint32_t W, uint32_t h, uint32_t C, uint32_t N,
+                 float* x0, float* x1, cudaStream_t s) {
+  if ((unsigned long long)p * h * C * N > 16384ull) return -2;
+  if (reduce) spatial2d_2x1_halo_reduce_nchw<float>(rank, p, W, h, C, N, x0, x1, s);
+  else spatial2d_2x1_halo_exch_nchw<float>(rank, p, W, h, C, N, x0, x1, s);
+  return (int)cudaGetLastError();
+}
+
 // kernels.hh:222-256
 int ref_slice2d(int add, uint32_t count_w, uint32_t count_h, uint32_t src_width, uint32_t src_height,
                 uint32_t dst_width, uint32_t dst_height, uint32_t channels, uint32_t batch_size,

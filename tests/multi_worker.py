@@ -287,11 +287,79 @@ def hybrid_part(rank, world, local):
     assert H.max_rel(results[0], results[1]) < 1e-4, H.max_rel(results[0], results[1])
 
 
+def dp_part(rank, world, local):
+    """Pure data parallelism, one unpartitioned replica per process (the reference's multi-process optimizer,
+    include/arraydiff/optimize_mpi.hh): worker 0's parameters are broadcast over the built-in exchange (bit for bit),
+    every worker trains on its own data, gradients are summed over all workers; replicas stay identical and match the
+    same run with the gradients summed by NCCL."""
+    N, Cc, Hh, W = 1, 3, 64, 64
+    x = H.uniform(1000 + rank, (N, Cc, Hh, W), 0.0, 1.0)
+    results = []
+    for use_nccl in (False, True):
+        Lh = hostlib.load()
+        ctxh = Lh.adh_context_create_distributed(0, 1, local, hostlib.F32_NCHW, 512)
+        hb = C.create_string_buffer(64)
+        assert Lh.adh_context_arena_handle(ctxh, hb) == 0
+        mine = torch.from_numpy(np.frombuffer(hb.raw, dtype=np.uint8).copy()).cuda()
+        allh = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(allh, mine)
+        assert Lh.adh_context_set_world(ctxh, rank, world) == 0
+        for wr in range(world):
+            if wr != rank:
+                assert Lh.adh_context_set_world_peer_handle(ctxh, wr, bytes(allh[wr].cpu().numpy().tobytes())) == 0
+
+        class Ctx:
+            pass
+        ctx = Ctx()
+        ctx.L, ctx.h, ctx.num_ranks = Lh, ctxh, 1
+        net = hostlib.Net(ctx, "stem_stage1", Hh, W, Cc, N, seed=50 + rank)      # every worker draws its own start
+        net.configure_sgd(1e-3, 0.9, l2=1e-4, nesterov=True)
+        own = torch.from_numpy(net.params(0)).cuda()
+        root = own.clone()
+        dist.broadcast(root, 0)
+        assert rank == 0 or not torch.equal(own, root)
+        net.broadcast_params()                        # built-in exchange: the others add zeros to worker 0's values
+        assert torch.equal(torch.from_numpy(net.params(0)).cuda(), root), "broadcast is not bit-exact"
+        if use_nccl:
+            HOOK = C.CFUNCTYPE(None, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p)
+
+            def allreduce(buf, count, stream, user):
+                t = torch.as_tensor(_Raw(buf, count * 4), device="cuda").view(torch.float32)
+                with torch.cuda.stream(torch.cuda.ExternalStream(stream)):
+                    dist.all_reduce(t)
+
+            hook = HOOK(allreduce)
+            _keep.append(hook)
+            Lh.adh_context_set_allreduce_hook(ctxh, C.cast(hook, C.c_void_p), None)
+        dy = H.normal(1100 + rank, net.strip_shape)
+        for _ in range(3):
+            net.forward(x)
+            net.set_output_grad(0, dy)
+            net.backward()
+            net.sgd_step()
+        net.sync()
+        assert net.status() == 0
+        p = torch.from_numpy(net.params(0)).cuda()
+        ref = p.clone()
+        dist.broadcast(ref, 0)
+        assert torch.equal(p, ref), "replicas diverged"
+        assert not torch.equal(p, root), "nothing was learnt"
+        results.append(p.cpu().numpy())
+        dist.barrier()
+    assert H.max_rel(results[0], results[1]) < 1e-5, H.max_rel(results[0], results[1])
+
+
 def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if os.environ.get("AD_MULTI_PART") == "dp":
+        dp_part(rank, world, local)
+        if rank == 0:
+            print("DP_OK", world)
+        dist.destroy_process_group()
+        return
     if os.environ.get("AD_MULTI_PART") == "hybrid":
         hybrid_part(rank, world, local)
         if rank == 0:

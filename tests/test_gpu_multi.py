@@ -16,7 +16,7 @@ def _ngpu():
     return torch.cuda.device_count()
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_multi_gpu_halo_and_host_layer(world):
     if _ngpu() < world:
         pytest.skip(f"needs {world} GPUs")
@@ -38,3 +38,16 @@ def test_data_parallel_groups_of_spatial_pairs():
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert "HYBRID_OK 4" in out.stdout
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_data_parallel_workers_broadcast_and_gradient_sum(world):
+    """One unpartitioned replica per GPU: broadcast init and gradient sums over the built-in exchange."""
+    if _ngpu() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", AD_MULTI_PART="dp")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(29620 + world), os.path.join(ROOT, "tests", "multi_worker.py")]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    assert f"DP_OK {world}" in out.stdout

@@ -39,6 +39,40 @@ def test_reference_halo_kernels_match_oracle(ref, R, geom):
             assert np.array_equal(d[r].cpu().numpy(), want[r]), (reduce, r)
 
 
+@pytest.mark.parametrize("geom", [(1, 8, 6, 5, 2), (3, 7, 7, 3, 2), (2, 33, 4, 1, 3)])
+def test_reference_w_split_kernels_match_oracle_and_library(ref, geom):
+    """The reference's W-split pair (2 ranks side by side, src/kernels/spatial.cu:654-768) against the 2-D grid oracle
+    and against ad_halo2d_*, bit for bit.  Sizes keep the reference launcher at one block."""
+    import torch
+    from arraydiff_cuda_b200 import abi
+    if not hasattr(ref, "ref_halo_2x1"):
+        pytest.skip("shim built without the W-split entry")
+    p, w, h, Cc, N = geom
+    u = C.c_uint32
+    for reduce in (0, 1):
+        bufs = [H.uniform(40 + 2 * reduce + r, (N, Cc, h + 2 * p, w + 2 * p)) for r in range(2)]
+        d = [torch.from_numpy(b.copy()).cuda() for b in bufs]
+        ptrs = [C.c_void_p(t.data_ptr()) for t in d]
+        for r in range(2):
+            assert ref.ref_halo_2x1(reduce, u(r), u(p), u(w), u(h), u(Cc), u(N), *ptrs, None) == 0
+        torch.cuda.synchronize()
+        want = [b.copy() for b in bufs]
+        (orc.halo2d_reduce if reduce else orc.halo2d_exchange)(want, orc.NCHW, 2, 1, p, w, h, Cc, N)
+        ours = [torch.from_numpy(b.copy()).cuda() for b in bufs]
+        a = abi.Halo2dArgs()
+        a.dtype, a.layout = abi.AD_F32, abi.AD_NCHW
+        a.halo_pad, a.base_width, a.base_height, a.num_channels, a.batch_size = p, w, h, Cc, N
+        a.grid_w, a.grid_h, a.rank_first, a.rank_count, a.push = 2, 1, 0, 2, 1
+        for r in range(2):
+            a.bufs[r] = ours[r].data_ptr()
+        fn = abi.lib().ad_halo2d_reduce if reduce else abi.lib().ad_halo2d_exchange
+        abi.check(fn(C.byref(a), H.stream()))
+        torch.cuda.synchronize()
+        for r in range(2):
+            assert np.array_equal(d[r].cpu().numpy(), want[r]), ("reference vs oracle", reduce, r)
+            assert np.array_equal(ours[r].cpu().numpy(), want[r]), ("library vs oracle", reduce, r)
+
+
 @pytest.mark.parametrize("R,p", [(2, 1), (4, 3)])
 def test_speed_against_reference_halo_kernels(ref, R, p):
     """Same GPU, same tensors (benchmark config 2, fp32): this library's exchange against the reference's
