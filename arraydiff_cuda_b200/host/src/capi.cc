@@ -3,6 +3,7 @@
 // results back.  Handles are opaque pointers; functions return 0 or a negative ad_status.
 #include <cstring>
 #include <memory>
+#include <vector>
 
 #include "arraydiff/optimize.hh"
 #include "arraydiff/zoo.hh"
@@ -76,6 +77,30 @@ int adh_context_set_world_peer_from_group(void* c, int world_rank, int group_ran
 }
 void adh_context_set_allreduce_hook(void* c, void (*fn)(float*, size_t, cudaStream_t, void*), void* user) {
   ((Ctx*)c)->ctx->set_allreduce_hook(fn, user);
+}
+// One halo exchange (op 0) or accumulate-back (op 1) through Spatial2DComm on a grid_h x grid_w grid laid over the
+// context's ranks (one process): bufs[r] is rank r's padded device buffer.  Runs the reference's call sequence --
+// group_start, halo_exchange / halo_reduce, group_end on every rank (src/op.cc:2977-3000) -- with a communicator array
+// made by Spatial2DComm::InitAll(comms, grid_w, grid_h).
+int adh_context_halo2d(void* c, int grid_w, int grid_h, int op, int nhwc, int bf16, uint32_t p, uint32_t w, uint32_t h, uint32_t ch,
+                       uint32_t n, void** bufs) {
+  auto& m = ((Ctx*)c)->ctx;
+  if (m->distributed() || (size_t)(grid_w * grid_h) != m->num_ranks()) return AD_ERR_BAD_ARG;
+  std::vector<Spatial2DComm> comms(m->num_ranks());
+  Spatial2DComm::InitAll(comms.data(), (uint32_t)grid_w, (uint32_t)grid_h, m.get());
+  const auto fmt = nhwc ? SPATIAL2D_TENSOR_NHWC : SPATIAL2D_TENSOR_NCHW;
+  const auto dt = bf16 ? SPATIAL2D_DATA_BFLOAT16 : SPATIAL2D_DATA_FLOAT;
+  for (size_t r = 0; r < m->num_ranks(); ++r) comms[r].group_start();
+  for (size_t r = 0; r < m->num_ranks(); ++r) {
+    if (op == 0) comms[r].halo_exchange(bufs[r], p, w, h, ch, n, fmt, dt);
+    else comms[r].halo_reduce(bufs[r], p, w, h, ch, n, fmt, dt);
+  }
+  for (size_t r = 0; r < m->num_ranks(); ++r) {
+    GPUConn conn = m->device_context(r)->conn();
+    comms[r].group_end(conn);
+  }
+  m->sync();
+  return AD_OK;
 }
 void* adh_context_stream(void* c, int rank) { return (void*)((Ctx*)c)->ctx->device_context((size_t)rank)->stream(); }
 

@@ -228,12 +228,15 @@ void Spatial2DComm::InitAll(Spatial2DComm* comms, uint32_t num_w_ranks, uint32_t
   InitAll(comms, num_w_ranks, num_h_ranks, nullptr);
 }
 void Spatial2DComm::InitAll(Spatial2DComm* comms, uint32_t num_w_ranks, uint32_t num_h_ranks, MultiGPUContext* ctx) {
-  assert(num_w_ranks == 1 && "only H-strip (1 x R) grids are built");
+  // rank = rank_h * num_w_ranks + rank_w (row-major over the grid).  1 x R grids (H-strips) work inside one process and
+  // between processes; grids with num_w_ranks > 1 (W-split, 2 x 2, 2 x 4 ...; reference src/spatial.cc:105-131,
+  // :166-196 for 2 x 1) inside one process.
+  assert((num_w_ranks == 1 || !ctx || !ctx->distributed()) && "grids with a W split are built for one-process contexts");
   const uint32_t R = num_w_ranks * num_h_ranks;
   assert(R >= 1 && R <= ARRAYDIFF_MAX_PEERS);
   for (uint32_t r = 0; r < R; ++r) {
     Spatial2DComm& c = comms[r];
-    c.rank = r; c.rank_w = 0; c.rank_h = r;
+    c.rank = r; c.rank_w = r % num_w_ranks; c.rank_h = r / num_w_ranks;
     c.num_ranks = R; c.num_w_ranks = num_w_ranks; c.num_h_ranks = num_h_ranks;
     c.epoch = 0;
     c.ctx_ = ctx;
@@ -326,6 +329,26 @@ void Spatial2DComm::group_end(GPUConn& conn) {
     }
   }
   cudaStream_t s = conn.stream();
+  if (num_w_ranks > 1) {
+    // 2-D grid (one process): pull from the up-to-8 neighbours once each has handed its buffer over
+    assert(!dist);
+    ad_halo2d_args b = {};
+    b.dtype = a.dtype; b.layout = a.layout;
+    b.halo_pad = arg.halo_pad; b.base_width = arg.base_width; b.base_height = arg.base_height;
+    b.num_channels = arg.num_channels; b.batch_size = arg.batch_size;
+    b.grid_w = num_w_ranks; b.grid_h = num_h_ranks; b.rank_first = rank; b.rank_count = 1; b.push = 0;
+    for (uint32_t q = 0; q < num_ranks; ++q) b.bufs[q] = a.bufs[q];
+    for (int dy = -1; dy <= 1; ++dy)
+      for (int dx = -1; dx <= 1; ++dx) {
+        const int ny = (int)rank_h + dy, nx = (int)rank_w + dx;
+        if ((!dy && !dx) || ny < 0 || nx < 0 || ny >= (int)num_h_ranks || nx >= (int)num_w_ranks) continue;
+        Spatial2DComm* q = peer_comms[(uint32_t)ny * num_w_ranks + (uint32_t)nx];
+        if (q->ready_) CUDA_CHECK(cudaStreamWaitEvent(s, q->ready_, 0));
+      }
+    if (arg.operation == SPATIAL2D_OP_HXEXCH) AD_CHECK(ad_halo2d_exchange(&b, s));
+    else AD_CHECK(ad_halo2d_reduce(&b, s));
+    return;
+  }
   if (!dist) {
     // Pull: my kernel reads my neighbours' rows once they have handed their buffers over.
     if (rank > 0 && peer_comms[rank - 1]->ready_) CUDA_CHECK(cudaStreamWaitEvent(s, peer_comms[rank - 1]->ready_, 0));

@@ -31,6 +31,7 @@ def load():
         L.adh_context_set_world.argtypes = [vp, C.c_int, C.c_int]
         L.adh_context_set_world_peer_handle.argtypes = [vp, C.c_int, C.c_char_p]
         L.adh_context_set_world_peer_from_group.argtypes = [vp, C.c_int, C.c_int]
+        L.adh_context_halo2d.argtypes = [vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int] + [C.c_uint32] * 5 + [C.POINTER(vp)]
         L.adh_context_stream.restype = vp
         L.adh_context_stream.argtypes = [vp, C.c_int]
         L.adh_net_create.restype = vp
@@ -78,6 +79,11 @@ class Context:
         arr = (C.c_int * len(devices))(*devices)
         self.h = self.L.adh_context_create(arr, len(devices), mode, arena_mb)
         self.num_ranks = len(devices)
+
+    def halo2d(self, grid_w, grid_h, reduce, bufs, nhwc, bf16, p, w, h, ch, n):
+        """Spatial2DComm group call on a grid_h x grid_w grid over this context's ranks; bufs: device pointers."""
+        arr = (C.c_void_p * len(bufs))(*bufs)
+        assert self.L.adh_context_halo2d(self.h, grid_w, grid_h, int(reduce), int(nhwc), int(bf16), p, w, h, ch, n, arr) == 0
 
     def close(self):
         if self.h:

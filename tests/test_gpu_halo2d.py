@@ -118,3 +118,28 @@ def test_halo2d_rejects_bad_arguments():
     a = args2d(b[:3], abi.AD_F32, abi.AD_NCHW, 2, 2, 1, 4, 4, 1, 1, count=3)   # a missing buffer
     assert L.ad_halo2d_reduce(C.byref(a), H.stream()) == abi.AD_ERR_BAD_ARG
     assert L.ad_halo2d_exchange(None, H.stream()) == abi.AD_ERR_BAD_ARG
+
+
+@pytest.mark.parametrize("grid", [(2, 1), (2, 2), (2, 4)])
+@pytest.mark.parametrize("reduce", [0, 1])
+def test_spatial2dcomm_group_calls_on_a_2d_grid(grid, reduce):
+    """The host-side communicator (Spatial2DComm::InitAll(comms, R_w, R_h), group_start / halo_* / group_end) on grids
+    with a W split, ranks sharing the GPU: same bits as the oracle."""
+    from arraydiff_cuda_b200 import hostlib
+    gw, gh = grid
+    p, N, Cc, h, w = 2, 2, 8, 6, 8
+    ctx = hostlib.Context([0] * (gw * gh), hostlib.BF16_NHWC, arena_mb=64)
+    if reduce:
+        host = [orc.round_bf16(H.uniform(60 + r, (N, Cc, h + 2 * p, w + 2 * p))) for r in range(gw * gh)]
+        ref = [orc.f32_to_bf16(g) for g in host]
+        orc.halo2d_reduce(ref, orc.NCHW, gw, gh, p, w, h, Cc, N)
+        want = [orc.bf16_to_f32(g) for g in ref]
+    else:
+        full = orc.round_bf16(H.uniform(61, (N, Cc, gh * h, gw * w)))
+        host, want = split2d(full, gw, gh, p), windows2d(full, gw, gh, p)
+    bufs = to_dev(host, abi.AD_NHWC, True)
+    H.sync()
+    ctx.halo2d(gw, gh, reduce, [b.data_ptr() for b in bufs], True, True, p, w, h, Cc, N)
+    for r, b in enumerate(bufs):
+        assert np.array_equal(to_host(b, abi.AD_NHWC), want[r]), r
+    ctx.close()
