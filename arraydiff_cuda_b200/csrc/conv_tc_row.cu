@@ -854,10 +854,9 @@ int conv_tc_stream_fwd(const void* act, uint32_t NI, uint32_t IH, uint32_t IW, u
 // Per tile (128 consecutive dy pixels of one row): ONE load of the dy tile [128 px][64 k] and ONE
 // load of the x patch [kh rows][pw px][64 c].  Every tap is an MMA over the same two buffers:
 //   D[(tap, c)][k] += sum_px x[px + shift(tap)][c] * dy[px][k]
-// A = x (MN-major, M = 128 = two taps (r, s) and (r+1, s) stacked: the second 64-channel block is
-// one patch row, pw*128 bytes, further on, a multiple of 1024 so both blocks share a swizzle phase),
-// B = dy (MN-major, N = 64).  ceil(kh/2)*kw accumulators of 64 columns live in tensor memory for the
-// whole kernel; each CTA walks its share of the tiles and writes ONE fp32 partial at the end, which
+// A = x (MN-major, M = 128 = two consecutive taps of the row-major tap order stacked: the second 64-channel
+// block starts where the second tap's pixels start), B = dy (MN-major, N = 64).  ceil(kh*kw/2) accumulators of
+// 64 columns live in tensor memory for the whole kernel; each CTA walks its share of the tiles and writes ONE fp32 partial at the end, which
 // wgrad_row_reduce_kernel sums over CTAs in a fixed order.  x and dy are read from DRAM once.
 struct RowWgParams {
   uint32_t NI, OP, OQ, KO;
@@ -925,29 +924,32 @@ conv_tc_row_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __gri
         tc_fence_after();
         const uint32_t sdy = smem_u32(smem + (size_t)stage * p.stage_bytes), sx = sdy + kDyBytes;
         const uint64_t db0 = smem_desc_sw128(sdy, 0, 1024);
+        // taps in row-major order, two per accumulator: rows 0-63 of accumulator a hold tap 2a, rows 64-127 tap 2a+1.
+        // The second 64-channel block of the A operand starts where tap 2a+1's pixels start, i.e. LBO =
+        // offset(2a+1) - offset(2a): any whole number of 128-byte pixel rows (the swizzle follows absolute
+        // shared-memory address bits, so the blocks need not share a swizzle phase).  An odd last tap is paired
+        // with itself (LBO 0); the reduction drops that half.
         if (KH > 0) {
+          constexpr int kTaps = KH * KW;
 #pragma unroll
-          for (int r = 0; r < KH; r += 2)
+          for (int t = 0; t < kTaps; t += 2) {
+            const uint32_t o0 = ((uint32_t)(t / KW) * p.pw + (uint32_t)(t % KW) * p.dw) * 128u;
+            const uint32_t o1 = t + 1 < kTaps ? ((uint32_t)((t + 1) / KW) * p.pw + (uint32_t)((t + 1) % KW) * p.dw) * 128u : o0;
+            const uint64_t da0 = smem_desc_sw128(sx + o0, o1 - o0, 1024);
 #pragma unroll
-            for (int sx_ = 0; sx_ < KW; ++sx_) {
-              const uint32_t acc = (uint32_t)((r / 2) * KW + sx_);
-              const uint32_t a0 = sx + ((uint32_t)r * p.pw + (uint32_t)sx_ * p.dw) * 128u;
-              const uint64_t da0 = smem_desc_sw128(a0, (r + 1 < KH) ? p.pw * 128u : 0u, 1024);
-#pragma unroll
-              for (int ks = 0; ks < 8; ++ks)   // 8 x 16 pixels; 16 rows of 128 B = 128 units of 16 B
-                umma_bf16(tmem_base + acc * 64, da0 + 128u * ks, db0 + 128u * ks, idesc, (first && ks == 0) ? 0u : 1u);
-            }
+            for (int ks = 0; ks < 8; ++ks)   // 8 x 16 pixels; 16 rows of 128 B = 128 units of 16 B
+              umma_bf16(tmem_base + (uint32_t)(t / 2) * 64, da0 + 128u * ks, db0 + 128u * ks, idesc, (first && ks == 0) ? 0u : 1u);
+          }
         } else {
-          uint32_t acc = 0;
-          for (uint32_t r = 0; r < p.kh; r += 2)
-            for (uint32_t s = 0; s < p.kw; ++s, ++acc) {
-              const uint32_t a0 = sx + (r * p.pw + s * p.dw) * 128u;
-              const uint32_t lbo = (r + 1 < p.kh) ? p.pw * 128u : 0u;   // unpaired tap: both halves read the same rows
-              const uint64_t da0 = smem_desc_sw128(a0, lbo, 1024);
+          const uint32_t taps = p.kh * p.kw;
+          for (uint32_t t = 0; t < taps; t += 2) {
+            const uint32_t o0 = ((t / p.kw) * p.pw + (t % p.kw) * p.dw) * 128u;
+            const uint32_t o1 = t + 1 < taps ? (((t + 1) / p.kw) * p.pw + ((t + 1) % p.kw) * p.dw) * 128u : o0;
+            const uint64_t da0 = smem_desc_sw128(sx + o0, o1 - o0, 1024);
 #pragma unroll
-              for (uint32_t ks = 0; ks < 8; ++ks)
-                umma_bf16(tmem_base + acc * 64, da0 + 128u * ks, db0 + 128u * ks, idesc, (first && ks == 0) ? 0u : 1u);
-            }
+            for (uint32_t ks = 0; ks < 8; ++ks)
+              umma_bf16(tmem_base + (t / 2) * 64, da0 + 128u * ks, db0 + 128u * ks, idesc, (first && ks == 0) ? 0u : 1u);
+          }
         }
         first = 0;
         umma_commit(smem_u32(&ctl->empty[stage]));
@@ -1025,9 +1027,8 @@ __global__ void __launch_bounds__(256) wgrad_row_reduce_kernel(uint32_t nparts, 
 #pragma unroll
   for (int w = 1; w < 4; ++w) { const float4 o = sh[w][tx]; t.x += o.x; t.y += o.y; t.z += o.z; t.w += o.w; }
   const uint32_t k0 = (item & 15u) * 4, row = (item >> 4) & 127u, acc = item >> 11;
-  const uint32_t c = row & 63u, r = (acc / kw) * 2 + (row >> 6), sx = acc % kw;
-  if (r >= kh) return;   // the unused half of an odd last row pair
-  const uint32_t taps = kh * kw, tap = r * kw + sx;
+  const uint32_t c = row & 63u, taps = kh * kw, tap = acc * 2 + (row >> 6);
+  if (tap >= taps) return;   // the unused half of an odd last tap
   const float o[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
   for (int j = 0; j < 4; ++j)
@@ -1044,14 +1045,14 @@ static uint32_t row_wgrad_grid(uint32_t NI, uint32_t OP, uint32_t OQ) {
 static bool row_wgrad_ok(uint32_t CI, uint32_t KO, uint32_t kh, uint32_t kw, uint32_t sh, uint32_t sw, uint32_t dh,
                          uint32_t dw, uint32_t OQ) {
   if (sh != 1 || sw != 1 || CI != 64 || KO > 64 || (KO & 7u) || OQ < 96) return false;
-  if (((kh + 1) / 2) * kw > 8) return false;
+  if ((kh * kw + 1) / 2 > 8) return false;
   const uint32_t pw = (128 + (kw - 1) * dw + 7) / 8 * 8;
   return pw <= 256 && (kh - 1) * dh + 1 <= 256;
 }
 size_t conv_tc_row_wgrad_scratch(uint32_t NI, uint32_t CI, uint32_t KO, uint32_t kh, uint32_t kw, uint32_t sh, uint32_t sw,
                                  uint32_t dh, uint32_t dw, uint32_t OP, uint32_t OQ) {
   if (!row_wgrad_ok(CI, KO, kh, kw, sh, sw, dh, dw, OQ)) return 0;
-  return (size_t)row_wgrad_grid(NI, OP, OQ) * (((kh + 1) / 2) * kw) * 128 * 64 * 4;
+  return (size_t)row_wgrad_grid(NI, OP, OQ) * ((kh * kw + 1) / 2) * 128 * 64 * 4;
 }
 
 int conv_tc_row_wgrad(const void* x, uint32_t NI, uint32_t IH, uint32_t IW, uint32_t CI, const void* dy, uint32_t KO,
@@ -1066,7 +1067,7 @@ int conv_tc_row_wgrad(const void* x, uint32_t NI, uint32_t IH, uint32_t IW, uint
   p.pw = (128 + (kw - 1) * dw + 7) / 8 * 8;
   p.patch_bytes = kh * p.pw * 128;
   p.stage_bytes = 16384 + p.patch_bytes;
-  p.naccs = ((kh + 1) / 2) * kw;
+  p.naccs = (kh * kw + 1) / 2;
   long long stages = ((long long)kMaxDynSmem - 1024 - (long long)sizeof(RowCtl)) / p.stage_bytes;
   if (stages < 2) return AD_ERR_UNSUPPORTED;
   if (stages > 4) stages = 4;

@@ -275,7 +275,12 @@ class Step:
         self.w = (torch.randn((CH, KS, KS, CH), device="cuda", generator=gw) * float(np.sqrt(2.0 / (KS * KS * CH)))).to(bf)
         self.y = torch.empty((B, h, SIZE, CH), dtype=bf, device="cuda")
         self.dy = (torch.rand((B, h, SIZE, CH), device="cuda", generator=g) * 2 - 1).to(bf)
-        self.dw = torch.zeros((CH, KS, KS, CH), device="cuda")
+        # two filter-gradient buffers: the allreduce of one step's gradient runs on its own stream underneath the
+        # next step, so consecutive steps must not share the buffer
+        self.dws = [torch.zeros((CH, KS, KS, CH), device="cuda") for _ in range(2)]
+        self.dw = self.dws[0]
+        self.ar_stream = torch.cuda.Stream()
+        self.ar_done = [None, None]
         a = abi.Conv2dArgs()
         a.dtype, a.layout = abi.AD_BF16, abi.AD_NHWC
         a.N, a.C, a.H, a.W, a.K, a.kh, a.kw = B, CH, Hp, Wp, CH, KS, KS
@@ -392,10 +397,25 @@ class Step:
                 for slot in self.plan.reduce_waits():
                     self._wait(slot, ep)
                 abi.check(L.ad_halo_reduce(C.byref(self.hg), s2), "halo reduce")
+        if R > 1:
+            # this step's gradient buffer: free again once the allreduce that last used it (two steps ago) is done
+            k = ep & 1
+            self.dw = self.dws[k]
+            a.dw = self.dw.data_ptr()
+            if self.ar_done[k] is not None:
+                self.torch.cuda.current_stream().wait_event(self.ar_done[k])
         self._timed("wgrad", lambda: abi.check(L.ad_conv2d_wgrad(C.byref(a), s), "wgrad"))
         if R > 1:
-            self.env.dist.all_reduce(self.dw)       # filter-gradient allreduce over NCCL / NVLink
-            self.torch.cuda.current_stream().wait_stream(self.side)
+            # filter-gradient allreduce over NCCL / NVLink on its own stream: it overlaps the next step's exchange and
+            # forward pass (an optimizer would consume it after that step's backward pass)
+            main = self.torch.cuda.current_stream()
+            self.ar_stream.wait_stream(main)
+            with self.torch.cuda.stream(self.ar_stream):
+                self.env.dist.all_reduce(self.dw)
+                self.ar_done[ep & 1] = self.ar_stream.record_event()
+            main.wait_stream(self.side)
+            if e2e:
+                main.wait_stream(self.ar_stream)
         if e2e:
             self.dw_host.copy_(self.dw, non_blocking=True)
 
@@ -419,7 +439,7 @@ def verify_conv_step(env, step):
     from oracle import orc
     torch_, dist, r, R, p, h, B = torch, env.dist, step.rank, step.world, PAD, step.h, step.batch
     step.run()
-    torch.cuda.synchronize()
+    torch.cuda.synchronize()     # includes the gradient allreduce on its own stream
     env.barrier()
     step.check_status()
     imgs = sorted({0, B - 1})
@@ -608,6 +628,7 @@ def run_conv_workload(env, args, with_cpu=True):
             "timing": f"median of {n} individually timed steps run back to back over {secs:.2f} s (CUDA events, max over ranks per step)",
             "config": {"workload": "microbench_spatial_conv", "batch": BATCH, "channels": CH, "image": [SIZE, SIZE],
                        "kernel": KS, "dilation": DIL, "halo": PAD, "strips": world, "layout": "NHWC",
+                       "filter_gradient_allreduce": "none (one strip)" if world == 1 else "NCCL on its own stream, double-buffered: overlaps the next step's exchange and forward pass",
                        "l2": "inputs larger than L2 (%.2f GB activations per pass)" % (BATCH * SIZE * SIZE * CH * 2 / 1e9), "parallelism": f"spatial-h{world}"},
             "e2e": {"value": total_flops / (float(np.median(per_e2e)) * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": hbytes,
                     "d2h_bytes_per_step": step.dw_host.numel() * 4, "steps": n_e2e,
