@@ -101,6 +101,7 @@ SIGNATURES = {
     "ad_array_scale_add": (C.c_int, [sz, f32, vp, vp, vp]),
     "ad_fill_zero": (C.c_int, [vp, sz, vp]),
     "ad_sgd_step": (C.c_int, [sz, vp, vp, vp, f32, f32, f32, f32, i32, vp, vp]),
+    "ad_sgd_step_guarded": (C.c_int, [sz, vp, vp, vp, f32, f32, f32, f32, i32, vp, vp, vp]),
     "ad_softmax_nll_loss_fwd": (C.c_int, [u32, u32, vp, vp, vp, vp]),
     "ad_softmax_nll_loss_bwd": (C.c_int, [u32, u32, vp, vp, vp, vp, vp]),
     "ad_softmax_ce_pixel_fwd": (C.c_int, [i32, i32, u32, u32, u32, vp, vp, vp, vp, vp]),

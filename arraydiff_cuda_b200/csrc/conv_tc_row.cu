@@ -509,7 +509,7 @@ conv_tc_stream_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         const int32_t rows_in = it.Lc + (int32_t)kh - 1;
         for (int32_t j = 0; j < rows_in; ++j) {
           TSTART(tp);
-          if (!mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1u, abortf)) { ok = false; break; }
+          if (!mbar_wait_relaxed(smem_u32(&ctl->empty[stage]), phase ^ 1u, abortf)) { ok = false; break; }
           TADD(0, tp);
           const uint32_t full = smem_u32(&ctl->full[stage]);
 #ifdef AD_VAR_NOTMA
@@ -604,10 +604,10 @@ conv_tc_stream_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         TSTART(te0);
 #ifdef AD_VAR_LANE0WAIT
         bool ok = true;
-        if (lane == 0) ok = mbar_wait(smem_u32(&ctl->afull[slot]), (tt >> 3) & 1u, abortf);
+        if (lane == 0) ok = mbar_wait_relaxed(smem_u32(&ctl->afull[slot]), (tt >> 3) & 1u, abortf);
         __syncwarp();
 #else
-        bool ok = mbar_wait(smem_u32(&ctl->afull[slot]), (tt >> 3) & 1u, abortf);
+        bool ok = mbar_wait_relaxed(smem_u32(&ctl->afull[slot]), (tt >> 3) & 1u, abortf);
 #endif
         TADD(6, te0);
 #ifdef AD_VAR_NOEPI
@@ -624,7 +624,7 @@ conv_tc_stream_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
           const uint32_t m = q * 32 + lane;
           uint8_t* stg = osm + (size_t)b * 16384;
           TSTART(te2);
-          if (tt >= 2) ok = mbar_wait(smem_u32(&ctl->stg_free[b]), ((tt >> 1) - 1u) & 1u, abortf);
+          if (tt >= 2) ok = mbar_wait_relaxed(smem_u32(&ctl->stg_free[b]), ((tt >> 1) - 1u) & 1u, abortf);
           TADD(7, te2);
           if (!__all_sync(0xffffffffu, ok)) { go = false; break; }   // leave together: the tensor-memory loads below are warp-wide
           {
@@ -666,7 +666,7 @@ conv_tc_stream_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
           }
           if (q == 0 && lane == 0) {
             // on a failed wait the abort flag is up and every warp leaves at its next wait
-            if (mbar_wait(smem_u32(&ctl->stg_full[b]), (tt >> 1) & 1u, abortf)) {
+            if (mbar_wait_relaxed(smem_u32(&ctl->stg_full[b]), (tt >> 1) & 1u, abortf)) {
 #ifndef AD_VAR_NOSTORE
               asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(&map_o),
                            "r"(smem_u32(stg)), "r"(0), "r"((int)(tx * 128)), "r"((int)oy), "r"((int)n)

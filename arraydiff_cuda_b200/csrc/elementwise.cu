@@ -59,7 +59,9 @@ static int arr_launch(size_t n, float a, float b, const float* x, float* y, void
 // ---------------------------------------------------------------- fused SGD
 __global__ void __launch_bounds__(256) sgd_kernel(size_t n, float* theta, float* g, float* m, float l2, float mu,
                                                   float alpha, float alpha_next, int nesterov,
-                                                  __nv_bfloat16* shadow) {
+                                                  __nv_bfloat16* shadow, const int32_t* guard) {
+  // a step whose bounded waits ran out worked on stale halo rows or gradients: leave the parameters alone
+  if (guard && *guard != 0) return;
   const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nt = (size_t)gridDim.x * blockDim.x;
   const float nmu = __fmul_rn(-alpha_next, mu);
   for (size_t i = tid; i < n; i += nt) {
@@ -272,7 +274,17 @@ extern "C" int ad_sgd_step(size_t n, float* theta, float* g, float* m, float l2,
   if (n == 0) return AD_OK;
   if (!theta || !g || !m) return AD_ERR_BAD_ARG;
   sgd_kernel<<<grid_for(n, 256), 256, 0, as_stream(stream)>>>(n, theta, g, m, l2, mu, alpha, alpha_next, nesterov,
-                                                               (__nv_bfloat16*)bf16_shadow);
+                                                               (__nv_bfloat16*)bf16_shadow, nullptr);
+  count_launch();
+  return launch_status();
+}
+extern "C" int ad_sgd_step_guarded(size_t n, float* theta, float* g, float* m, float l2, float mu, float alpha,
+                                   float alpha_next, int32_t nesterov, void* bf16_shadow, const int32_t* status_word,
+                                   void* stream) {
+  if (n == 0) return AD_OK;
+  if (!theta || !g || !m) return AD_ERR_BAD_ARG;
+  sgd_kernel<<<grid_for(n, 256), 256, 0, as_stream(stream)>>>(n, theta, g, m, l2, mu, alpha, alpha_next, nesterov,
+                                                               (__nv_bfloat16*)bf16_shadow, status_word);
   count_launch();
   return launch_status();
 }

@@ -41,6 +41,9 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // given up (*abort_flag != 0); the caller then leaves its loop.  The limit is generous
 // (two seconds of device time) -- it only exists so that a protocol bug can never hang the GPU.
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+#ifndef AD_RELAXED_SLEEP_NS
+#define AD_RELAXED_SLEEP_NS 64
+#endif
 __device__ __forceinline__ unsigned long long timer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -59,6 +62,29 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
   *abort_flag = 1;
   return false;
+}
+
+// The same wait for roles that are NOT on the critical path of the tensor pipe (TMA producer waiting for a free
+// stage, epilogue warps waiting for an accumulator): between polls the warp sleeps, so that its polling does not
+// compete with the MMA-issuing thread for the SM's memory-instruction queue (mbarrier polls, shared-memory accesses
+// and tcgen05.mma issue all go through it; with 4 epilogue warps spinning flat out the MMA issue rate halves).
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+#ifdef AD_VAR_NOBACKOFF
+  return mbar_wait(bar, parity, abort_flag);
+#else
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = timer_ns();
+  for (uint32_t i = 0; i < (1u << 28); ++i) {
+    __nanosleep(AD_RELAXED_SLEEP_NS);
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 15u) == 15u) {
+      if (*abort_flag) return false;
+      if (timer_ns() - t0 > kWaitLimitNs) break;
+    }
+  }
+  *abort_flag = 1;
+  return false;
+#endif
 }
 
 // ---------------------------------------------------------------- TMA (tiled, no multicast)

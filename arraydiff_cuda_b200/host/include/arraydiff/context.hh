@@ -14,6 +14,7 @@
 #include <cuda_runtime.h>
 
 #include <cassert>
+#include <functional>
 #include <cstddef>
 #include <cstdint>
 #include <memory>
@@ -77,7 +78,15 @@ public:
   explicit GPUContext(int device, size_t arena_bytes = 0);
   virtual ~GPUContext() {}
   virtual void sync();
+  // Scoped access to this rank's device and stream.  Work that was deferred on the stream (set_pending: the waits for the
+  // neighbours' halo rows of the last exchange) is issued first, so that whatever the caller launches next sees the
+  // halo rows; conn_deferred() skips that step for a caller that launches work which does not read them and then calls
+  // finish_pending() itself (the convolution operator: interior rows, wait, boundary rows).
   GPUConn conn();
+  GPUConn conn_deferred();
+  void set_pending(std::function<void(cudaStream_t)> f) { finish_pending(); pending_ = f; }
+  bool has_pending() const { return (bool)pending_; }
+  void finish_pending();
   int device() const { return device_; }
   cudaStream_t stream() const { return stream_; }
   DeviceArena& arena() { return arena_; }
@@ -97,6 +106,7 @@ private:
   void* scratch_;
   size_t scratch_size_;
   int32_t* status_;
+  std::function<void(cudaStream_t)> pending_;
 };
 
 class MultiGPUContext : public virtual Context {

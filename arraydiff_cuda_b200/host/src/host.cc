@@ -65,7 +65,18 @@ GPUContext::GPUContext(int device, size_t arena_bytes)
   CUDA_CHECK(cudaSetDevice(prev));
 }
 void GPUContext::sync() { GPUConn c = conn(); c.sync(); }
-GPUConn GPUContext::conn() { return GPUConn(device_, stream_); }
+GPUConn GPUContext::conn() {
+  GPUConn c(device_, stream_);
+  finish_pending();
+  return c;
+}
+GPUConn GPUContext::conn_deferred() { return GPUConn(device_, stream_); }
+void GPUContext::finish_pending() {
+  if (!pending_) return;
+  auto f = pending_;
+  pending_ = nullptr;
+  f(stream_);   // issued with this context's device current: callers hold a GPUConn
+}
 void GPUContext::reserve_scratch(size_t min_scratch_size) {
   if (scratch_size_ >= min_scratch_size) return;
   size_t want = min_scratch_size < (1u << 20) ? (1u << 20) : min_scratch_size;
@@ -133,7 +144,10 @@ void MultiGPUContext::sync() {
 void MultiGPUContext::end_phase() {
   if (!distributed_) return;
   for (size_t r = 0; r < num_ranks_; ++r)
-    if (is_local(r)) spatial_comms_[r].end_phase(dev_ctxs_[r]->stream());
+    if (is_local(r)) {
+      GPUConn c = dev_ctxs_[r]->conn();     // issues waits still pending on the rank: they use this phase's values
+      spatial_comms_[r].end_phase(c.stream());
+    }
 }
 void MultiGPUContext::sync_rank(size_t rank) { dev_ctxs_.at(rank)->sync(); }
 shared_ptr<GPUContext> MultiGPUContext::device_context(size_t rank) { assert(dev_ctxs_.at(rank)); return dev_ctxs_.at(rank); }
@@ -371,8 +385,18 @@ void Spatial2DComm::group_end(GPUConn& conn) {
     if (rank + 1 < num_ranks) AD_CHECK(ad_flag_wait_rel(flags_ + 4, ebase_, arg.epoch, kTimeoutNs, g->status_word(), s));
     if (rank > 0) AD_CHECK(ad_flag_wait_rel(flags_ + 5, ebase_, arg.epoch, kTimeoutNs, g->status_word(), s));
     AD_CHECK(ad_halo_exchange(&a, s));
-    if (rank > 0) AD_CHECK(ad_flag_wait_rel(flags_ + 0, ebase_, arg.epoch, kTimeoutNs, g->status_word(), s));
-    if (rank + 1 < num_ranks) AD_CHECK(ad_flag_wait_rel(flags_ + 1, ebase_, arg.epoch, kTimeoutNs, g->status_word(), s));
+    // The waits for the neighbours' rows are left pending on the rank's context: they are issued in front of the next
+    // launch that goes through GPUContext::conn() -- or, by a consumer that knows which of its work needs the halo
+    // rows (the convolution: interior rows first), after that work.
+    const uint64_t ep = arg.epoch;
+    uint64_t* const fl = flags_;
+    uint64_t* const eb = ebase_;
+    int32_t* const st = g->status_word();
+    const bool has_prev = rank > 0, has_next = rank + 1 < num_ranks;
+    g->set_pending([=](cudaStream_t ws) {
+      if (has_prev) AD_CHECK(ad_flag_wait_rel(fl + 0, eb, ep, kTimeoutNs, st, ws));
+      if (has_next) AD_CHECK(ad_flag_wait_rel(fl + 1, eb, ep, kTimeoutNs, st, ws));
+    });
   } else {
     if (rank > 0) AD_CHECK(ad_flag_wait_rel(flags_ + 2, ebase_, arg.epoch, kTimeoutNs, g->status_word(), s));
     if (rank + 1 < num_ranks) AD_CHECK(ad_flag_wait_rel(flags_ + 3, ebase_, arg.epoch, kTimeoutNs, g->status_word(), s));

@@ -495,7 +495,14 @@ void CudnnConv2DOpF::refresh_filter(TxnId txn, cudaStream_t s) {
 void CudnnConv2DOpF::_forward(TxnId txn) {
   if (!y_.val.overwrite(txn, id())) return;
   GPUContext* g = gpu();
-  GPUConn conn = g->conn();
+  // Between processes the waits for the neighbours' halo rows of the exchange in front of this layer may still be
+  // pending on the context: a stride-1 tensor-core layer convolves the output rows that need no halo first, then lets
+  // the waits go, then adds the p rows at either edge -- the interior work overlaps the halo's flight, which the
+  // reference forgoes by synchronising every device around each exchange (src/op.cc:2976, :3001).
+  const size_t ph = shape_.pad[1], oh = dim_.shape[1];
+  const bool split = g->has_pending() && g->mode() == COMPUTE_BF16_NHWC && shape_.halo_padded_input && !use_im2col_ &&
+                     shape_.stride[0] == 1 && shape_.stride[1] == 1 && ph > 0 && oh > 2 * ph;
+  GPUConn conn = split ? g->conn_deferred() : g->conn();
   Act& x = x_->data().val.get(txn, id());
   Act& y = y_.val.get_excl(txn, id());
   ad_conv2d_args a;
@@ -519,6 +526,16 @@ void CudnnConv2DOpF::_forward(TxnId txn) {
   }
   g->reserve_scratch(16);
   a.scratch = g->status_word(); a.scratch_bytes = 16;
+  if (split) {
+    a.out_row_begin = (uint32_t)ph; a.out_row_count = (uint32_t)(oh - 2 * ph);
+    AD_CHECK(ad_conv2d_fprop(&a, conn.stream()));
+    g->finish_pending();
+    a.out_row_begin = 0; a.out_row_count = (uint32_t)ph;
+    AD_CHECK(ad_conv2d_fprop(&a, conn.stream()));
+    a.out_row_begin = (uint32_t)(oh - ph);
+    AD_CHECK(ad_conv2d_fprop(&a, conn.stream()));
+    return;
+  }
   AD_CHECK(ad_conv2d_fprop(&a, conn.stream()));
 }
 

@@ -75,8 +75,8 @@ void ParallelSGDOptimizer<float>::step(TxnId txn) {
   for (size_t r = 0; r < R; ++r) {
     if (!mgpu_->is_local(r)) continue;
     GPUConn conn = mgpu_->device_context(r)->conn();
-    AD_CHECK(ad_sgd_step(param_dim_, param_[r].dptr(), sum_grad_[r].dptr(), momentum_[r].dptr(), (float)cfg_.l2_reg, mu, alpha,
-                         next_alpha, cfg_.nesterov ? 1 : 0, nullptr, conn.stream()));
+    AD_CHECK(ad_sgd_step_guarded(param_dim_, param_[r].dptr(), sum_grad_[r].dptr(), momentum_[r].dptr(), (float)cfg_.l2_reg, mu, alpha,
+                                 next_alpha, cfg_.nesterov ? 1 : 0, nullptr, mgpu_->device_context(r)->status_word(), conn.stream()));
     any rd = param_[r];
     sink_->load_val(next, params_[r], 0, &rd);
   }
@@ -186,8 +186,8 @@ void ParallelSGDOptimizer<float>::step(function<void(TxnId, size_t, shared_ptr<O
   for (size_t r = 0; r < R; ++r) {
     if (!mgpu_->is_local(r)) continue;
     GPUConn conn = mgpu_->device_context(r)->conn();
-    AD_CHECK(ad_sgd_step(param_dim_, param_[r].dptr(), sum_grad_[r].dptr(), momentum_[r].dptr(), (float)cfg_.l2_reg, mu, alpha,
-                         next_alpha, cfg_.nesterov ? 1 : 0, nullptr, conn.stream()));
+    AD_CHECK(ad_sgd_step_guarded(param_dim_, param_[r].dptr(), sum_grad_[r].dptr(), momentum_[r].dptr(), (float)cfg_.l2_reg, mu, alpha,
+                                 next_alpha, cfg_.nesterov ? 1 : 0, nullptr, mgpu_->device_context(r)->status_word(), conn.stream()));
     any rd = param_[r];
     sink_->load_val(update_txn, params_[r], 0, &rd);
     if (stat_dim_) {

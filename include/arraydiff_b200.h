@@ -211,6 +211,12 @@ int ad_fill_zero(void* x, size_t bytes, void* stream);
  */
 int ad_sgd_step(size_t n, float* theta, float* g, float* m, float l2, float mu, float alpha,
                 float alpha_next, int32_t nesterov, void* bf16_shadow, void* stream);
+/* The same update, skipped entirely when *status_word != 0 at the time the kernel runs: status_word is the device word
+ * the step's bounded waits report into (ad_flag_wait ...), so a step that ran on stale halo rows or an incomplete
+ * gradient sum leaves the parameters untouched.  The reference has no such case: its waits never give up
+ * (src/spatial.cc:59-70). */
+int ad_sgd_step_guarded(size_t n, float* theta, float* g, float* m, float l2, float mu, float alpha,
+                        float alpha_next, int32_t nesterov, void* bf16_shadow, const int32_t* status_word, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Softmax / loss.

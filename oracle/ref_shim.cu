@@ -31,14 +31,15 @@ int ref_halo_1x4(int reduce, uint32_t rank, uint32_t p, uint32_t W, uint32_t h, 
   return (int)cudaGetLastError();
 }
 
-// kernels.hh:168-190: the W-split pair (2 ranks side by side), src/kernels/spatial.cu:654-768.  Callers keep
-// halo_pad * base_height * channels * batch <= 16384 so that the launcher picks one block: its per-block work split
-// (total / blocks, rounded up) can run past the end for other block counts.
+// kernels.hh:168-178: the W-split pair (2 ranks side by side), exchange only -- src/kernels/spatial.cu:654-733.  The
+// float specialisation of the matching reduce is declared (:770-780) but never defined, so the reference cannot link
+// it; reduce != 0 returns -3.  Callers keep halo_pad * base_height * channels * batch <= 16384 so that the launcher
+// picks one block: its per-block work split (total / blocks, rounded up) can run past the end for other block counts.
 int ref_halo_2x1(int reduce, uint32_t rank, uint32_t p, uint32_t W, uint32_t h, uint32_t C, uint32_t N,
                  float* x0, float* x1, cudaStream_t s) {
+  if (reduce) return -3;
   if ((unsigned long long)p * h * C * N > 16384ull) return -2;
-  if (reduce) spatial2d_2x1_halo_reduce_nchw<float>(rank, p, W, h, C, N, x0, x1, s);
-  else spatial2d_2x1_halo_exch_nchw<float>(rank, p, W, h, C, N, x0, x1, s);
+  spatial2d_2x1_halo_exch_nchw<float>(rank, p, W, h, C, N, x0, x1, s);
   return (int)cudaGetLastError();
 }
 

@@ -421,3 +421,25 @@ def test_linear_layer(dtype, B, I, O):
     assert H.max_rel(H.host(ty), y_w) < tol
     assert H.max_rel(H.host(tdx), dx_w + 2.0) < tol
     assert H.max_rel(H.host(tdw), dw_w) < 2e-6 and H.max_rel(H.host(tdb), db_w) < 2e-6
+
+
+def test_sgd_step_guard_skips_the_update_after_a_timed_out_wait():
+    import torch
+    L = abi.lib()
+    n = 1000
+    theta0, g0 = H.normal(70, (n,)), H.normal(71, (n,))
+    for flag, changed in ((0, True), (abi.AD_ERR_TIMEOUT, False)):
+        theta, g, m = H.dev(theta0), H.dev(g0), torch.zeros(n, device="cuda")
+        status = torch.tensor([flag], dtype=torch.int32, device="cuda")
+        abi.check(L.ad_sgd_step_guarded(n, H.ptr(theta), H.ptr(g), H.ptr(m), f32(1e-4), f32(0.9), f32(0.1), f32(0.1), 1, None,
+                                        H.ptr(status), H.stream()))
+        H.sync()
+        assert (not np.array_equal(H.host(theta), theta0)) == changed
+        if changed:
+            ref = H.dev(theta0)
+            g2, m2 = H.dev(g0), torch.zeros(n, device="cuda")
+            abi.check(L.ad_sgd_step(n, H.ptr(ref), H.ptr(g2), H.ptr(m2), f32(1e-4), f32(0.9), f32(0.1), f32(0.1), 1, None, H.stream()))
+            H.sync()
+            assert torch.equal(ref, theta)
+        else:
+            assert np.array_equal(H.host(m), np.zeros(n, np.float32))

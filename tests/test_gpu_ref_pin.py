@@ -41,8 +41,9 @@ def test_reference_halo_kernels_match_oracle(ref, R, geom):
 
 @pytest.mark.parametrize("geom", [(1, 8, 6, 5, 2), (3, 7, 7, 3, 2), (2, 33, 4, 1, 3)])
 def test_reference_w_split_kernels_match_oracle_and_library(ref, geom):
-    """The reference's W-split pair (2 ranks side by side, src/kernels/spatial.cu:654-768) against the 2-D grid oracle
-    and against ad_halo2d_*, bit for bit.  Sizes keep the reference launcher at one block."""
+    """The reference's W-split exchange (2 ranks side by side, src/kernels/spatial.cu:654-733) against the 2-D grid oracle
+    and against ad_halo2d_exchange, bit for bit; the reference never defines the float form of the matching reduce, so
+    the accumulate-back is compared between library and oracle only.  Sizes keep the reference launcher at one block."""
     import torch
     from arraydiff_cuda_b200 import abi
     if not hasattr(ref, "ref_halo_2x1"):
@@ -54,7 +55,7 @@ def test_reference_w_split_kernels_match_oracle_and_library(ref, geom):
         d = [torch.from_numpy(b.copy()).cuda() for b in bufs]
         ptrs = [C.c_void_p(t.data_ptr()) for t in d]
         for r in range(2):
-            assert ref.ref_halo_2x1(reduce, u(r), u(p), u(w), u(h), u(Cc), u(N), *ptrs, None) == 0
+            assert ref.ref_halo_2x1(reduce, u(r), u(p), u(w), u(h), u(Cc), u(N), *ptrs, None) == (-3 if reduce else 0)
         torch.cuda.synchronize()
         want = [b.copy() for b in bufs]
         (orc.halo2d_reduce if reduce else orc.halo2d_exchange)(want, orc.NCHW, 2, 1, p, w, h, Cc, N)
@@ -69,7 +70,8 @@ def test_reference_w_split_kernels_match_oracle_and_library(ref, geom):
         abi.check(fn(C.byref(a), H.stream()))
         torch.cuda.synchronize()
         for r in range(2):
-            assert np.array_equal(d[r].cpu().numpy(), want[r]), ("reference vs oracle", reduce, r)
+            if not reduce:
+                assert np.array_equal(d[r].cpu().numpy(), want[r]), ("reference vs oracle", r)
             assert np.array_equal(ours[r].cpu().numpy(), want[r]), ("library vs oracle", reduce, r)
 
 
