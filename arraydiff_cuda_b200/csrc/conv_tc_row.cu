@@ -435,14 +435,6 @@ __device__ __forceinline__ StreamItem stream_item(const StreamParams& p, uint32_
   return it;
 }
 
-#ifdef AD_STREAM_TIMING
-__device__ unsigned long long g_stream_timing[16];
-#define TSTART(v) long long v = clock64()
-#define TADD(idx, v) tacc[idx] += clock64() - v
-#else
-#define TSTART(v)
-#define TADD(idx, v)
-#endif
 template <int KH, int KW>
 __global__ void __launch_bounds__(kRowThreads, 1)
 conv_tc_stream_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -457,10 +449,6 @@ conv_tc_stream_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   StreamCtl* ctl = (StreamCtl*)(osm + (p.tma_store ? 2 * 16384 : 0));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr uint32_t kSlots = 8, kTmemCols = 512;
-#ifdef AD_STREAM_TIMING
-  long long tacc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-  const long long tkernel = clock64();
-#endif
 
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < p.stages; ++s) {
@@ -508,13 +496,8 @@ conv_tc_stream_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         if (it.Lc <= 0) continue;
         const int32_t rows_in = it.Lc + (int32_t)kh - 1;
         for (int32_t j = 0; j < rows_in; ++j) {
-          TSTART(tp);
           if (!mbar_wait_relaxed(smem_u32(&ctl->empty[stage]), phase ^ 1u, abortf)) { ok = false; break; }
-          TADD(0, tp);
           const uint32_t full = smem_u32(&ctl->full[stage]);
-#ifdef AD_VAR_NOTMA
-          if (phase != 0 || item != blockIdx.x) { mbar_arrive(full); } else
-#endif
           {
           mbar_expect_tx(full, p.row_bytes);
           tma_load_4d(smem_u32(psm + (size_t)stage * p.row_bytes), &map_a, full, 0, (int)(it.tx * 128) + p.offx,
@@ -537,19 +520,12 @@ conv_tc_stream_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
           const int32_t i_lo = j >= (int32_t)kh - 1 ? j - ((int32_t)kh - 1) : 0;
           const int32_t i_hi = j < it.Lc ? j : it.Lc - 1;
           const bool new_row = j < it.Lc;
-          TSTART(tm0);
           if (new_row) {
             const uint32_t tt = t + (uint32_t)j;
             if (!mbar_wait(smem_u32(&ctl->aempty[tt & 7u]), ((tt >> 3) & 1u) ^ 1u, abortf)) { ok = false; break; }
           }
-          TADD(2, tm0);
-          TSTART(tm1);
           if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abortf)) { ok = false; break; }
-          TADD(3, tm1);
-          TSTART(tm2);
-#ifndef AD_VAR_NOFENCEAFTER
           tc_fence_after();
-#endif
           const uint64_t da0 = smem_desc_sw128(smem_u32(psm + (size_t)stage * p.row_bytes), 16, 1024);
           // The accumulate range [i_lo, i_hi] as one or two runs of adjacent slots (two when it wraps around the
           // ring), worked out once per input row: D column, filter block offset and instruction descriptor.
@@ -586,7 +562,6 @@ conv_tc_stream_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
           umma_commit(smem_u32(&ctl->empty[stage]));
           if (j >= (int32_t)kh - 1) umma_commit(smem_u32(&ctl->afull[(t + (uint32_t)(j - ((int32_t)kh - 1))) & 7u]));
           if (++stage == p.stages) { stage = 0; phase ^= 1u; }
-          TADD(4, tm2);
         }
         t += (uint32_t)it.Lc;
       }
@@ -601,31 +576,14 @@ conv_tc_stream_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
       for (int32_t i = 0; i < it.Lc; ++i, ++tt) {
         const uint32_t slot = tt & 7u;
         const uint32_t oy = it.rho + (it.i0 + (uint32_t)i) * p.dh, n = it.n, tx = it.tx;
-        TSTART(te0);
-#ifdef AD_VAR_LANE0WAIT
-        bool ok = true;
-        if (lane == 0) ok = mbar_wait_relaxed(smem_u32(&ctl->afull[slot]), (tt >> 3) & 1u, abortf);
-        __syncwarp();
-#else
         bool ok = mbar_wait_relaxed(smem_u32(&ctl->afull[slot]), (tt >> 3) & 1u, abortf);
-#endif
-        TADD(6, te0);
-#ifdef AD_VAR_NOEPI
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&ctl->aempty[slot]));
-        continue;
-#endif
         if (!__all_sync(0xffffffffu, ok)) { go = false; break; }
-        TSTART(te1);
         tc_fence_after();
         if (p.tma_store) {
           const uint32_t b = tt & 1u;
           const uint32_t m = q * 32 + lane;
           uint8_t* stg = osm + (size_t)b * 16384;
-          TSTART(te2);
           if (tt >= 2) ok = mbar_wait_relaxed(smem_u32(&ctl->stg_free[b]), ((tt >> 1) - 1u) & 1u, abortf);
-          TADD(7, te2);
           if (!__all_sync(0xffffffffu, ok)) { go = false; break; }   // leave together: the tensor-memory loads below are warp-wide
           {
             uint32_t v[64];
@@ -656,9 +614,7 @@ conv_tc_stream_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
           }
           // accumulator slot drained: hand it back to the MMA warp
           tc_fence_before();
-#ifndef AD_VAR_NOFENCE
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-#endif
           __syncwarp();
           if (lane == 0) {
             mbar_arrive(smem_u32(&ctl->aempty[slot]));
@@ -667,11 +623,9 @@ conv_tc_stream_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
           if (q == 0 && lane == 0) {
             // on a failed wait the abort flag is up and every warp leaves at its next wait
             if (mbar_wait_relaxed(smem_u32(&ctl->stg_full[b]), (tt >> 1) & 1u, abortf)) {
-#ifndef AD_VAR_NOSTORE
               asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(&map_o),
                            "r"(smem_u32(stg)), "r"(0), "r"((int)(tx * 128)), "r"((int)oy), "r"((int)n)
                            : "memory");
-#endif
               asm volatile("cp.async.bulk.commit_group;" ::: "memory");
               // every store but the newest has finished reading its staging buffer: free the other one
               asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
@@ -679,7 +633,6 @@ conv_tc_stream_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             }
           }
           __syncwarp();
-          TADD(8, te1);
           continue;
         }
         const uint32_t ox = tx * 128 + q * 32 + lane;
@@ -741,12 +694,6 @@ conv_tc_stream_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     if (p.tma_store && q == 0 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
-#ifdef AD_STREAM_TIMING
-  if (blockIdx.x == 0 && lane == 0 && (warp == 0 || warp == 1 || warp == 2)) {
-    for (int i = 0; i < 12; ++i) if (tacc[i]) g_stream_timing[i] = (unsigned long long)tacc[i];
-    if (warp == 1) g_stream_timing[12] = (unsigned long long)(clock64() - tkernel);
-  }
-#endif
   tc_fence_before();
   __syncthreads();
   if (*abortf) {
@@ -761,11 +708,6 @@ conv_tc_stream_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   }
 }
 
-#ifdef AD_STREAM_TIMING
-extern "C" int ad_debug_stream_timing(unsigned long long* out) {
-  return cudaMemcpyFromSymbol(out, g_stream_timing, sizeof(unsigned long long) * 16) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 // Rows per chunk: few enough items per CTA leave the last wave half empty, short chunks re-fetch kh - 1 rows each.
 static void stream_chunks(uint32_t NI, uint32_t tiles_x, uint32_t dh, uint32_t OP, uint32_t kh, uint32_t& L, uint32_t& nchunks) {

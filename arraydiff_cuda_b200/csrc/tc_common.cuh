@@ -65,13 +65,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 }
 
 // The same wait for roles that are NOT on the critical path of the tensor pipe (TMA producer waiting for a free
-// stage, epilogue warps waiting for an accumulator): between polls the warp sleeps, so that its polling does not
-// compete with the MMA-issuing thread for the SM's memory-instruction queue (mbarrier polls, shared-memory accesses
-// and tcgen05.mma issue all go through it; with 4 epilogue warps spinning flat out the MMA issue rate halves).
+// stage, epilogue warps waiting for an accumulator): between polls the warp sleeps instead of spinning flat out.
 __device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-#ifdef AD_VAR_NOBACKOFF
-  return mbar_wait(bar, parity, abort_flag);
-#else
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = timer_ns();
   for (uint32_t i = 0; i < (1u << 28); ++i) {
@@ -84,7 +79,6 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity,
   }
   *abort_flag = 1;
   return false;
-#endif
 }
 
 // ---------------------------------------------------------------- TMA (tiled, no multicast)

@@ -68,10 +68,10 @@ def halo_part(rank, world):
 _keep = []
 
 
-def host_part(rank, world, local):
+def make_dist_ctx(rank, world, local, mode, arena_mb):
+    """One rank of a distributed host-layer context: arena handles exchanged through torch.distributed."""
     Lh = hostlib.load()
-    ctxh = Lh.adh_context_create_distributed(rank, world, local, hostlib.F32_NCHW, 1536)
-    # exchange arena handles
+    ctxh = Lh.adh_context_create_distributed(rank, world, local, mode, arena_mb)
     hb = C.create_string_buffer(64)
     assert Lh.adh_context_arena_handle(ctxh, hb) == 0
     mine = torch.from_numpy(np.frombuffer(hb.raw, dtype=np.uint8).copy()).cuda()
@@ -80,6 +80,18 @@ def host_part(rank, world, local):
     for r in range(world):
         if r != rank:
             assert Lh.adh_context_set_peer_handle(ctxh, r, bytes(allh[r].cpu().numpy().tobytes())) == 0
+
+    class Ctx:  # minimal stand-in for hostlib.Context around the distributed handle
+        pass
+    ctx = Ctx()
+    ctx.L, ctx.h, ctx.num_ranks = Lh, ctxh, world
+    return ctx
+
+
+def host_part(rank, world, local):
+    Lh = hostlib.load()
+    ctx0 = make_dist_ctx(rank, world, local, hostlib.F32_NCHW, 1536)
+    ctxh = ctx0.h
     # filter-gradient allreduce over NCCL on the host layer's own stream
     HOOK = C.CFUNCTYPE(None, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p)
 
@@ -92,10 +104,7 @@ def host_part(rank, world, local):
     _keep.append(hook)
     Lh.adh_context_set_allreduce_hook(ctxh, C.cast(hook, C.c_void_p), None)
 
-    class Ctx:  # minimal stand-in for hostlib.Context around the distributed handle
-        pass
-    ctx = Ctx()
-    ctx.L, ctx.h, ctx.num_ranks = Lh, ctxh, world
+    ctx = ctx0
     N, Cc, K, Hh, W = 1, 64, 64, 64, 64
     net = hostlib.Net(ctx, "conv3x3", Hh, W, Cc, N, K, seed=3)
     x = H.uniform(100, (N, Cc, Hh, W))
@@ -122,10 +131,12 @@ def host_part(rank, world, local):
     assert H.max_rel(net.params(rank), theta) < 1e-5, "update after allreduce mismatch"
     dist.barrier()
     classifier_part(ctx, rank, world)
-    graph_part(ctx, rank, world, local)
+    graph_part(ctx, rank, world, local, hostlib.F32_NCHW)
+    # the tensor-core path: between processes the convolutions run their interior rows before the halo waits
+    graph_part(make_dist_ctx(rank, world, local, hostlib.BF16_NHWC, 1536), rank, world, local, hostlib.BF16_NHWC)
 
 
-def graph_part(ctx, rank, world, local):
+def graph_part(ctx, rank, world, local, mode):
     """Without an allreduce hook the filter gradients are summed by the built-in peer exchange and the whole
     training step replays from a CUDA graph in every process; after the same steps the parameters equal, bit
     for bit, those of the same net run as `world` strips inside one process (eagerly, on rank 0's GPU)."""
@@ -161,7 +172,7 @@ def graph_part(ctx, rank, world, local):
     dist.broadcast(ref, 0)
     assert torch.equal(got, ref), "replicas diverged"
     if rank == 0:
-        local_ctx = hostlib.Context([local] * world, hostlib.F32_NCHW, arena_mb=512)
+        local_ctx = hostlib.Context([local] * world, mode, arena_mb=512)
         want = train(hostlib.Net(local_ctx, "stem_stage1", Hh, W, Cc, N, seed=29), list(range(world)), False, init=start)
         assert np.array_equal(mine, want), float(np.abs(mine - want).max())
     dist.barrier()

@@ -13,7 +13,7 @@ TOOL = os.path.join(ROOT, "arraydiff_cuda_b200", "host", "tools", "train_dummy")
 pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not os.path.exists(TOOL), reason="training tool not built")]
 
 
-def run_tool(devices, mode, iters=12, image=64, batch=4, minibatch=8):
+def run_tool(devices, mode, iters=12, image=128, batch=4, minibatch=8):
     env = dict(os.environ, ARRAYDIFF_B200_DEVICES=devices, ARRAYDIFF_B200_MODE=mode, ARRAYDIFF_B200_ARENA_MB="3072")
     out = subprocess.run([TOOL, str(iters), str(image), str(batch), str(minibatch)], env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
