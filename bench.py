@@ -211,6 +211,36 @@ def cpu_conv_sample(target_seconds, ch_in=CH, ch_out=CH, width=SIZE, dil=DIL, ma
     return fl / dt / 1e12, dt, rows, threads
 
 
+def cpu_small_configs():
+    """The two configurations small enough to run whole on the host cores: config 1 (3x3 conv, 64 -> 64, 64 x 64, two
+    H-strips with 1-row halos exchanged in host memory: fwd + dgrad + wgrad, 0.906 GFLOP) and config 2 (halo exchange +
+    accumulate-back, N=8, C=256, 224 x 224, 8 strips, halo 3, fp32), through the oracle."""
+    from oracle import orc
+    from tests import helpers as H
+    orc.set_num_threads()
+    x, w = H.uniform(1, (1, 64, 64, 64)), H.normal(2, (64, 64, 3, 3), float(np.sqrt(2.0 / 576)))
+    dy = H.uniform(3, (1, 64, 64, 64))
+    t0 = time.perf_counter()
+    strips = H.split_strips(x, 2, 1)
+    orc.halo_exchange(strips, orc.NCHW, 1, 64, 32, 64, 1)
+    for r in range(2):
+        orc.conv2d_fprop(strips[r], w, None, omp=True)
+        orc.conv2d_dgrad(dy[:, :, r * 32:(r + 1) * 32], w, strips[r].shape, omp=True)
+        orc.conv2d_wgrad(strips[r], dy[:, :, r * 32:(r + 1) * 32], w.shape, omp=True)
+    t1 = time.perf_counter() - t0
+    R, p, N, Cc, Hh, W = 8, 3, 8, 256, 224, 224
+    bufs = [np.zeros((N, Cc, Hh // R + 2 * p, W + 2 * p), np.float32) for _ in range(R)]
+    t0 = time.perf_counter()
+    orc.halo_exchange(bufs, orc.NCHW, p, W, Hh // R, Cc, N)
+    t2 = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    orc.halo_reduce(bufs, orc.NCHW, p, W, Hh // R, Cc, N)
+    t3 = time.perf_counter() - t0
+    payload = 2 * (R - 1) * N * Cc * p * W * 4
+    return {"config1_conv3x3_2strips": {"seconds": t1, "tflops": 0.906e9 / t1 / 1e12},
+            "config2_halo_r8_p3_f32": {"exchange_gbs": payload / t2 / 1e9, "reduce_gbs": payload / t3 / 1e9, "payload_bytes": payload}}
+
+
 # the layer the CPU arm samples for the segmentation net: a stage-3 3x3 (256 -> 256, dilation 2) on its
 # 128 x 256 map -- the most frequent conv of the net (6 blocks)
 SEG_CPU_LAYER = dict(ch_in=256, ch_out=256, width=256, dil=2, max_rows=128)
@@ -636,7 +666,8 @@ def run_conv_workload(env, args, with_cpu=True):
             "gpu_launches": int(launches), "timed_steps": n, "timed_region_s": secs,
             "step_ms": st,
             "halo_exposed_ms": None if ms_nohalo is None else med - ms_nohalo,
-            "roofline": {"bound": "tensor", "kernel": f"conv_tc_row_{top}", "achieved": achieved, "peak": peaks["tf_sustained"],
+            "roofline": {"bound": "tensor", "kernel": {"fprop": "conv_tc_stream_fwd_kernel<3,3> (fprop)", "dgrad": "conv_tc_stream_fwd_kernel<3,3> (dgrad)",
+                                                        "wgrad": "conv_tc_row_wgrad_kernel<3,3>"}[top], "achieved": achieved, "peak": peaks["tf_sustained"],
                          "unit": "TFLOP/s", "frac": achieved / peaks["tf_sustained"],
                          "traffic": NCU_TRAFFIC_BATCH4[top] * BATCH / 4 / world,
                          "peak_source": peaks["source"] + " (sustained: the kernel is timed with CUDA events inside full steps run back to back)",
@@ -937,9 +968,10 @@ def run_net_workload(env, args, kind):
         ranks = list(range(strips))
     net = hostlib.Net(ctx, "segnet50" if seg else "parallel_resnet50" if hyb else "stem_stage1", Hh, Ww, 3, NB,
                       filters=1000 if hyb else 64, seed=1)
-    # the stem workload has no loss: its upstream gradient is a fixed random tensor, so thousands of timed steps at a
-    # training-sized rate would walk the weights off to infinity; the rate does not change what the step costs
-    net.configure_sgd(0.01 if (seg or hyb) else 1e-6, 0.9, l2=1e-4, nesterov=True)
+    # the stem workload has no loss: its objective <dy, y> with a fixed random dy is unbounded, so any positive rate
+    # walks the weights off to infinity over thousands of timed steps; rate 0 runs the same update kernel on the same
+    # bytes and keeps the parameters where they are
+    net.configure_sgd(0.01 if (seg or hyb) else 0.0, 0.9, l2=1e-4, nesterov=True)
     if hyb:
         net.set_loss_weight(1.0 / (NB * D * strips))     # mean over the global batch, shared out over a group's replicas of the head
     rng = np.random.default_rng(7 + group)
@@ -1131,7 +1163,8 @@ def main():
         if env.world == 1:
             v, dt, rows, cores = cpu_conv_sample(args.cpu_seconds, **SEG_CPU_LAYER)
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
-                                    "sample": f"oracle conv fwd+dgrad+wgrad of one stage-3 layer of the net (3x3, 256->256, dilation 2) on a {rows}-row x 256-col strip of one image ({dt:.1f} s)"}
+                                    "sample": f"oracle conv fwd+dgrad+wgrad of one stage-3 layer of the net (3x3, 256->256, dilation 2) on a {rows}-row x 256-col strip of one image ({dt:.1f} s)",
+                                    "small_configs": cpu_small_configs()}
         conv_v = (also.get("conv") or {}).get("verify") or {}
         line["verify"] = {"ok": bool(line["verify"]["ok"] and conv_v.get("ok", False)), "net": line["verify"], "conv_step": conv_v}
         line["also"] = also
