@@ -750,6 +750,10 @@ static int launch_wgrad(const CUtensorMap& mdy, const CUtensorMap& mx, const WgP
   return launch_status();
 }
 
+// Input channels per CTA of the general filter-gradient kernel.  (A 256-wide tile halves the L2 fetches of the dy
+// tile but leaves room for two pipeline stages only: measured 15 % slower on the 512 -> 512 layers.)
+static int wgrad_bn(uint32_t C) { return C > 64 ? 128 : 64; }
+
 static uint32_t wgrad_splits(uint32_t sp_tiles, uint32_t outer) {
   uint32_t want = (2 * kNumSMs + outer - 1) / outer;
   if (want > sp_tiles) want = sp_tiles;
@@ -787,7 +791,7 @@ size_t conv_tc_scratch_bytes(const ad_conv2d_args* a, int pass) {
     uint32_t TN, TH, TW;
     pick_tile3(a->N, g.P, g.Q, a->stride_h, a->stride_w, TN, TH, TW);
     const uint32_t sp = ((a->N + TN - 1) / TN) * ((g.P + TH - 1) / TH) * ((g.Q + TW - 1) / TW);
-    const uint32_t BN = a->C > 64 ? 128 : 64;
+    const uint32_t BN = (uint32_t)wgrad_bn(a->C);
     const uint32_t outer = a->kh * a->kw * ((Kp + 127) / 128) * ((a->C + BN - 1) / BN);
     size_t general = (size_t)wgrad_splits(sp, outer) * wcount * 4;
     size_t row = conv_tc_row_wgrad_scratch(a->N, a->C, a->K, a->kh, a->kw, a->stride_h, a->stride_w, a->dil_h, a->dil_w, g.P, g.Q);
@@ -913,7 +917,7 @@ int conv_tc_wgrad(const ad_conv2d_args* a, cudaStream_t s) {
   p.tiles_y = (g.P + p.TH - 1) / p.TH;
   p.tiles_x = (g.Q + p.TW - 1) / p.TW;
   p.tiles_b = (a->N + p.TN - 1) / p.TN;
-  const int BN = a->C > 64 ? 128 : 64;
+  const int BN = wgrad_bn(a->C);
   p.ktiles = (Kp + 127) / 128;
   p.ctiles = (a->C + BN - 1) / BN;
   const uint32_t sp_tiles = p.tiles_b * p.tiles_y * p.tiles_x;

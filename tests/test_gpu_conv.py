@@ -94,6 +94,8 @@ TC_CASES = [
     (8, 64, 7, 7, 128, 3, 1, 1, 1),      # 7x7 maps: a tile spans 16 images (here 8 real ones)
     (5, 128, 14, 14, 64, 1, 1, 1, 0),    # 14x14 maps: 4 images per tile, ragged last block of images
     (3, 64, 9, 9, 19, 3, 1, 1, 1),       # small maps through the scattered-store epilogue (ragged channels)
+    (1, 256, 14, 30, 128, 3, 1, 2, 0),   # 256 input channels: the filter gradient's 256-wide channel tile
+    (2, 512, 12, 20, 64, 1, 1, 1, 0),    # 512 input channels, 1x1: two 256-wide channel tiles
 ]
 
 
