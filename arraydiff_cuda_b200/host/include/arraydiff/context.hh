@@ -76,7 +76,7 @@ class GPUContext : public virtual Context {
 public:
   static shared_ptr<GPUContext> Make(int device);
   explicit GPUContext(int device, size_t arena_bytes = 0);
-  virtual ~GPUContext() {}
+  virtual ~GPUContext();
   virtual void sync();
   // Scoped access to this rank's device and stream.  Work that was deferred on the stream (set_pending: the waits for the
   // neighbours' halo rows of the last exchange) is issued first, so that whatever the caller launches next sees the
@@ -98,7 +98,23 @@ public:
   size_t scratch_size() const { return scratch_size_; }
   int32_t* status_word() { return status_; }   // device word that bounded waits report into
   int read_status();                            // synchronises this rank's stream
+  // Side stream for work whose result nothing needs before the end of the backward walk (the filter gradients: they run
+  // underneath the memory-bound operators of the layers below).  fork_side() orders the side stream after everything
+  // issued on the main stream so far and returns it; join_side() orders the main stream after the side stream's work.
+  // Op::backward() ends with JoinAllSides(), so every consumer of a gradient sees it complete; inside a stream capture
+  // the side stream joins the capture at the fork and leaves it at the join.
+  cudaStream_t fork_side();
+  void join_side();
+  static void JoinAllSides();
+  void reserve_side_scratch(size_t min_size);
+  void* side_scratch() { return side_scratch_; }
+  size_t side_scratch_size() const { return side_scratch_size_; }
 private:
+  cudaStream_t side_ = nullptr;
+  cudaEvent_t fork_ev_ = nullptr, join_ev_ = nullptr;
+  bool side_dirty_ = false;
+  void* side_scratch_ = nullptr;
+  size_t side_scratch_size_ = 0;
   int device_;
   cudaStream_t stream_;
   DeviceArena arena_;

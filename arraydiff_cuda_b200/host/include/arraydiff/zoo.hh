@@ -104,7 +104,8 @@ class SpatialParallelResNet {
 public:
   // One 3x3 convolution (stride 1, pad 1, bias) over H-strips: scatter -> halo pad -> halo exchange ->
   // conv.  The plumbing case of the partitioned path.
-  static SpatialParallelNet MakeConv3x3(const ConvNetConfig& config, size_t filters, shared_ptr<Context> ctx);
+  // `first_pad` != 1: the strip is first framed with that halo width and re-framed to 1 (HaloRepad2DOp).
+  static SpatialParallelNet MakeConv3x3(const ConvNetConfig& config, size_t filters, shared_ptr<Context> ctx, size_t first_pad = 1);
   // The same layer between the reference's collective operators: BroadcastOp -> SpatialScatter2DOp -> pad / exchange /
   // conv -> SpatialGather2DOp -> AllreduceOp -> ReduceOp.  One output on rank 0: R times the convolution.
   static SpatialParallelNet MakeConv3x3Collectives(const ConvNetConfig& config, size_t filters, shared_ptr<Context> ctx);

@@ -111,6 +111,7 @@ void* adh_net_create(void* c, const char* kind, int H, int W, int C, int batch, 
   n->cfg.input_h = (size_t)H; n->cfg.input_w = (size_t)W; n->cfg.input_c = (size_t)C; n->cfg.batch_size = (size_t)batch;
   n->rng.seed(seed);
   if (!std::strcmp(kind, "conv3x3")) n->net = SpatialParallelResNet<float>::MakeConv3x3(n->cfg, (size_t)filters, n->ctx);
+  else if (!std::strcmp(kind, "conv3x3_repad")) n->net = SpatialParallelResNet<float>::MakeConv3x3(n->cfg, (size_t)filters, n->ctx, 3);
   else if (!std::strcmp(kind, "conv3x3_collectives")) n->net = SpatialParallelResNet<float>::MakeConv3x3Collectives(n->cfg, (size_t)filters, n->ctx);
   else if (!std::strcmp(kind, "stem_stage1")) n->net = SpatialParallelResNet<float>::MakeStemStage1(n->cfg, n->ctx);
   else if (!std::strcmp(kind, "parallel_resnet18")) n->net = SpatialParallelResNet<float>::MakeParallelResNet18(n->cfg, filters > 0 ? (size_t)filters : 1000, n->ctx);

@@ -51,6 +51,8 @@ static size_t default_arena_bytes() {
   return mb << 20;
 }
 
+// contexts of this process, for JoinAllSides (the host layer is driven by one thread per process)
+static std::vector<GPUContext*>& all_contexts() { static std::vector<GPUContext*> v; return v; }
 shared_ptr<GPUContext> GPUContext::Make(int device) { return make_shared<GPUContext>(device); }
 
 GPUContext::GPUContext(int device, size_t arena_bytes)
@@ -58,13 +60,51 @@ GPUContext::GPUContext(int device, size_t arena_bytes)
   int prev = 0;
   CUDA_CHECK(cudaGetDevice(&prev));
   CUDA_CHECK(cudaSetDevice(device_));
-  CUDA_CHECK(cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking));
+  // the main stream outranks the side stream (fork_side): where both have blocks ready, the critical path goes first
+  int least = 0, greatest = 0;
+  CUDA_CHECK(cudaDeviceGetStreamPriorityRange(&least, &greatest));
+  CUDA_CHECK(cudaStreamCreateWithPriority(&stream_, cudaStreamNonBlocking, greatest));
   arena_.init(arena_bytes ? arena_bytes : default_arena_bytes());
   status_ = (int32_t*)arena_.alloc(64);
   CUDA_CHECK(cudaMemsetAsync(status_, 0, 64, stream_));
   CUDA_CHECK(cudaSetDevice(prev));
+  all_contexts().push_back(this);
 }
-void GPUContext::sync() { GPUConn c = conn(); c.sync(); }
+GPUContext::~GPUContext() {
+  auto& v = all_contexts();
+  v.erase(std::remove(v.begin(), v.end(), this), v.end());
+}
+cudaStream_t GPUContext::fork_side() {
+  GPUConn c(device_, stream_);
+  if (!side_) {
+    int least = 0, greatest = 0;
+    CUDA_CHECK(cudaDeviceGetStreamPriorityRange(&least, &greatest));
+    CUDA_CHECK(cudaStreamCreateWithPriority(&side_, cudaStreamNonBlocking, least));
+    CUDA_CHECK(cudaEventCreateWithFlags(&fork_ev_, cudaEventDisableTiming));
+    CUDA_CHECK(cudaEventCreateWithFlags(&join_ev_, cudaEventDisableTiming));
+  }
+  CUDA_CHECK(cudaEventRecord(fork_ev_, stream_));
+  CUDA_CHECK(cudaStreamWaitEvent(side_, fork_ev_, 0));
+  side_dirty_ = true;
+  return side_;
+}
+void GPUContext::join_side() {
+  if (!side_dirty_) return;
+  GPUConn c(device_, stream_);
+  CUDA_CHECK(cudaEventRecord(join_ev_, side_));
+  CUDA_CHECK(cudaStreamWaitEvent(stream_, join_ev_, 0));
+  side_dirty_ = false;
+}
+void GPUContext::JoinAllSides() {
+  for (GPUContext* g : all_contexts()) g->join_side();
+}
+void GPUContext::reserve_side_scratch(size_t min_size) {
+  if (side_scratch_size_ >= min_size) return;
+  size_t want = min_size < (1u << 20) ? (1u << 20) : min_size;
+  side_scratch_ = arena_.alloc(want);
+  side_scratch_size_ = want;
+}
+void GPUContext::sync() { join_side(); GPUConn c = conn(); c.sync(); }
 GPUConn GPUContext::conn() {
   GPUConn c(device_, stream_);
   finish_pending();
@@ -591,6 +631,7 @@ void Op::backward(TxnId txn) {
   EpochId e;
   _push(e, [](Op*) {});
   _pop(e, [&](Op* op) { op->_backward(txn); });
+  GPUContext::JoinAllSides();   // filter gradients issued on side streams are complete for whatever follows
 }
 void Op::gradient(TxnId txn) {
   eval(txn);

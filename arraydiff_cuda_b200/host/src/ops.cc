@@ -500,7 +500,8 @@ void CudnnConv2DOpF::_forward(TxnId txn) {
   // the waits go, then adds the p rows at either edge -- the interior work overlaps the halo's flight, which the
   // reference forgoes by synchronising every device around each exchange (src/op.cc:2976, :3001).
   const size_t ph = shape_.pad[1], oh = dim_.shape[1];
-  static const bool overlap = !(getenv("ARRAYDIFF_B200_HALO_OVERLAP") && getenv("ARRAYDIFF_B200_HALO_OVERLAP")[0] == '0');
+  const char* sw = getenv("ARRAYDIFF_B200_HALO_OVERLAP");   // "0": wait for the halo rows in front of the whole layer
+  const bool overlap = !(sw && sw[0] == '0');
   const bool split = overlap && g->has_pending() && g->mode() == COMPUTE_BF16_NHWC && shape_.halo_padded_input && !use_im2col_ &&
                      shape_.stride[0] == 1 && shape_.stride[1] == 1 && ph > 0 && oh > 2 * ph;
   GPUConn conn = split ? g->conn_deferred() : g->conn();
@@ -570,14 +571,28 @@ void CudnnConv2DOpF::_backward(TxnId txn) {
         b.kh = b.kw = b.stride_h = b.stride_w = b.dil_h = b.dil_w = 1; b.pad_h = b.pad_w = 0;
       }
       const size_t need = ad_conv2d_scratch_bytes(&b, 2);
+      if (!use_im2col_) {
+        // Nothing reads a filter gradient before the end of the backward walk: it runs on the context's side stream
+        // (with its own scratch), underneath the data gradient and the memory-bound operators of the layers below.
+        // The fixed-order reduction of the partials adds straight into the (zero-initialised) KCRS variables.
+        const char* sw = getenv("ARRAYDIFF_B200_WGRAD_OVERLAP");   // "0": keep the filter gradients on the main stream
+        const bool overlap = !(sw && sw[0] == '0');
+        cudaStream_t ws = s;
+        if (overlap) {
+          g->reserve_side_scratch(need);
+          b.scratch = g->side_scratch(); b.scratch_bytes = g->side_scratch_size();
+          ws = g->fork_side();
+        } else {
+          g->reserve_scratch(need);
+          b.scratch = g->get_scratch(); b.scratch_bytes = g->scratch_size();
+        }
+        AD_CHECK(ad_fill_zero(b.scratch, 16, ws));
+        b.dw = dw.dptr(); b.db = db; b.accumulate = 1; b.dw_kcrs = 1;
+        AD_CHECK(ad_conv2d_wgrad(&b, ws));
+      } else {
       g->reserve_scratch(need);
       b.scratch = g->get_scratch(); b.scratch_bytes = g->scratch_size();
       AD_CHECK(ad_fill_zero(b.scratch, 16, s));
-      if (!use_im2col_) {
-        // the fixed-order reduction of the partials adds straight into the (zero-initialised) KCRS variables
-        b.dw = dw.dptr(); b.db = db; b.accumulate = 1; b.dw_kcrs = 1;
-        AD_CHECK(ad_conv2d_wgrad(&b, s));
-      } else {
       // patch-matrix layer: the filter gradient is produced with padded rows and then added into the KCRS
       // variable; the bias gradient is written straight into its variable (this op is the bias's only
       // consumer, so = equals +=)

@@ -289,12 +289,16 @@ static void finish_net(SpatialParallelNet& net, const vector<ActVar>& outs) {
 }
 
 template <>
-SpatialParallelNet SpatialParallelResNet<float>::MakeConv3x3(const ConvNetConfig& cfg, size_t filters, shared_ptr<Context> ctx) {
+SpatialParallelNet SpatialParallelResNet<float>::MakeConv3x3(const ConvNetConfig& cfg, size_t filters, shared_ptr<Context> ctx,
+                                                             size_t first_pad) {
   vector<ActVar> strips;
   SpatialParallelNet net = begin_net(cfg, ctx, strips);
   Conv2DShape s;
   s.filters = filters; s.kernel = {3, 3}; s.pad = {1, 1}; s.halo_padded_input = true;
-  auto pad = HaloPad2DOpF::MakeParallel(1, strips, ctx);
+  auto pad = HaloPad2DOpF::MakeParallel(first_pad, strips, ctx);
+  // a wider first frame is moved into the 1-pixel frame the layer reads (what a net does between a halo-3 and a halo-1
+  // layer that share an input, reference HaloRepad2DOp, include/arraydiff/op.hh:2548)
+  if (first_pad != 1) pad = HaloRepad2DOpF::MakeParallel(first_pad, 1, pad, ctx);
   auto exch = HaloExch2DOpF::MakeParallel(1, pad, ctx);
   NameScope scope("conv");
   auto conv = parallel_conv2d<Act>(s, exch, kaiming_init_gen<GPUArray4D<float>>(cfg.input_c * 9, filters), false, ctx);

@@ -857,12 +857,20 @@ def conv_profile_of_step(abi, eager_step, sync, step_ms):
     # up to a second of steps back to back, like the timed region: one step alone runs at higher clocks than the power
     # cap sustains
     reps = int(max(1, min(40, math.ceil(min(1.0, MIN_SECONDS) * 1e3 / step_ms)))) if step_ms else 1
+    # the filter gradients stay on the main stream while the calls are timed: underneath other kernels (where the
+    # timed step runs them) a call's elapsed time is not the kernel's
+    prev = os.environ.get("ARRAYDIFF_B200_WGRAD_OVERLAP")
+    os.environ["ARRAYDIFF_B200_WGRAD_OVERLAP"] = "0"
     L.ad_conv2d_profile(1)
     for _ in range(reps):
         eager_step()
     sync()
     recs = abi.conv_profile_read()
     L.ad_conv2d_profile(0)
+    if prev is None:
+        os.environ.pop("ARRAYDIFF_B200_WGRAD_OVERLAP", None)
+    else:
+        os.environ["ARRAYDIFF_B200_WGRAD_OVERLAP"] = prev
     groups = {}
     for e in recs:
         if e.ms < 0 or e.status != 0:

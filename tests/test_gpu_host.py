@@ -76,6 +76,41 @@ def test_config1_partitioned_conv3x3_forward_backward_update(R, mode):
 
 @pytest.mark.parametrize("R", [1, 2, 4])
 @pytest.mark.parametrize("mode", ["f32", "bf16"])
+def test_halo_repad_reframes_a_strip(R, mode):
+    """HaloRepad2DOp (reference include/arraydiff/op.hh:2548): a strip framed with a 3-pixel halo and re-framed to 1 pixel
+    in front of the exchange gives the same outputs, input gradients and filter gradients, bit for bit, as the strip
+    framed with 1 pixel directly."""
+    from arraydiff_cuda_b200 import hostlib
+    N, Cc, K, Hh, W = 2, 64, 64, 32, 40
+    x = H.uniform(110, (N, Cc, Hh, W))
+    w = H.normal(111, (K, Cc, 3, 3), float(np.sqrt(2.0 / (9 * 64))))
+    dy = H.uniform(112, (N, K, Hh, W))
+    h = Hh // R
+    got = []
+    for kind in ("conv3x3", "conv3x3_repad"):
+        ctx = hostlib.Context([0] * R, hostlib.F32_NCHW if mode == "f32" else hostlib.BF16_NHWC, arena_mb=256)
+        net = hostlib.Net(ctx, kind, Hh, W, Cc, N, K, seed=7)
+        net.set_params(w.reshape(-1))
+        net.forward(x)
+        y = net.full_output()
+        for r in range(R):
+            net.set_output_grad(r, dy[:, :, r * h:(r + 1) * h])
+        net.backward()
+        net.sync()
+        dx = [net.input_grad(r)[:, :, r * h:(r + 1) * h].copy() for r in range(R)]
+        dw = [net.param_grads(r).copy() for r in range(R)]
+        assert net.status() == 0
+        got.append((y, dx, dw))
+        net.close(); ctx.close()
+    (y0, dx0, dw0), (y1, dx1, dw1) = got
+    assert np.array_equal(y0, y1)
+    assert H.max_rel(y1, orc.conv2d_fprop(x, w, None, pad=(1, 1), omp=True)) < (1e-5 if mode == "f32" else 2e-2)
+    for r in range(R):
+        assert np.array_equal(dx0[r], dx1[r]) and np.array_equal(dw0[r], dw1[r])
+
+
+@pytest.mark.parametrize("R", [1, 2, 4])
+@pytest.mark.parametrize("mode", ["f32", "bf16"])
 def test_conv3x3_between_reference_collective_operators(R, mode):
     """The reference's graph shape for a partitioned layer -- BroadcastOp, SpatialScatter2DOp, pad / exchange / conv,
     SpatialGather2DOp, AllreduceOp, ReduceOp -- against the unsplit oracle conv: the single output on rank 0 is R times
@@ -178,14 +213,18 @@ def test_stem_stage1_matches_oracle(R, mode):
 @pytest.mark.parametrize("R", [1, 2])
 def test_graph_replayed_steps_equal_eager_steps(R):
     """The resident step replayed from a CUDA graph runs the same kernels on the same buffers as the
-    eager step: after the same number of SGD steps both nets hold bit-identical parameters."""
+    eager step: after the same number of SGD steps both nets hold bit-identical parameters.  So does a third net
+    whose filter gradients stay on the main stream (ARRAYDIFF_B200_WGRAD_OVERLAP=0) instead of running on the side
+    stream underneath the layers below: the overlap changes when a kernel runs, not what it computes."""
+    import os
     from arraydiff_cuda_b200 import hostlib
     N, Cc, Hh, W = 1, 3, 64, 64
     x = H.uniform(300, (N, Cc, Hh, W), 0.0, 1.0)
     dy = H.normal(301, (N, 256, Hh // 4, W // 4))
     h = dy.shape[2] // R
     results = []
-    for graph in (False, True):
+    for graph, overlap in ((False, True), (True, True), (True, False)):
+        os.environ["ARRAYDIFF_B200_WGRAD_OVERLAP"] = "1" if overlap else "0"
         ctx = hostlib.Context([0] * R, hostlib.BF16_NHWC, arena_mb=512)
         net = hostlib.Net(ctx, "stem_stage1", Hh, W, Cc, N, seed=13)
         net.configure_sgd(1e-3, 0.9, l2=1e-4, nesterov=True)
@@ -203,8 +242,10 @@ def test_graph_replayed_steps_equal_eager_steps(R):
         if graph:
             assert net.graph_launches() > 100
         results.append([net.params(r).copy() for r in range(R)])
+    os.environ.pop("ARRAYDIFF_B200_WGRAD_OVERLAP", None)
     for r in range(R):
         assert np.array_equal(results[0][r], results[1][r])
+        assert np.array_equal(results[0][r], results[2][r])
     assert not np.array_equal(results[0][0], np.zeros_like(results[0][0]))
 
 
