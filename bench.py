@@ -298,6 +298,9 @@ class Step:
         self.flags, self.flags_off = self.arena.alloc((8,), torch.int64)      # 0 from_prev 1 from_next 2 gprev 3 gnext
         self.counter = torch.zeros(1, dtype=torch.int32, device="cuda")
         self.status = torch.zeros(4, dtype=torch.int32, device="cuda")
+        # flag values are *ebase + 1 in every step and the base advances by one at the end of the step (on the device), so
+        # that a step recorded into a CUDA graph replays with fresh values; all ranks advance in lockstep
+        self.ebase = torch.zeros(1, dtype=torch.int64, device="cuda")
         g = torch.Generator(device="cuda").manual_seed(1234 + rank)
         self.x.zero_()
         self.x[:, PAD:PAD + h, PAD:PAD + SIZE] = (torch.rand((B, h, SIZE, CH), device="cuda", generator=g) * 2 - 1).to(bf)
@@ -322,6 +325,7 @@ class Step:
         self.conv = a
         self.epoch = 0
         self.halo = True       # False: the same step without halo transfers (measures what they cost exposed)
+        self.use_graph = True  # the resident step replays CUDA graphs (False: every call launched from the host)
         self.marks = None      # a list: run() brackets every conv call with CUDA events and appends (name, e0, e1)
         ha = abi.HaloArgs()
         ha.dtype, ha.layout = abi.AD_BF16, abi.AD_NHWC
@@ -336,8 +340,11 @@ class Step:
         for peer, slot in self.plan.exchange_signals():
             self.hx.signal_flags[peer] = fp[peer] + 8 * slot
         self.hx.block_counter = self.counter.data_ptr()
+        self.hx.epoch, self.hx.epoch_base = 1, self.ebase.data_ptr()
         self.fp = fp
         self.host = None
+        self.graphs = {}       # (halo, dw buffer) -> (captured step, kernel launches in it)
+        self.replayed_launches = 0
 
     def make_host_buffers(self):
         """Pinned host tensors in the reference's boundary format (NCHW fp32, unpadded strip) and the device staging
@@ -361,12 +368,13 @@ class Step:
     def _s(self):
         return C.c_void_p(self.torch.cuda.current_stream().cuda_stream)
 
-    def _wait(self, slot, epoch):
-        self.abi.check(self.L.ad_flag_wait(C.c_void_p(self.flags.data_ptr() + 8 * slot), epoch, 2_000_000_000,
-                                           C.c_void_p(self.status.data_ptr()), self._s()), "flag wait")
+    def _wait(self, slot):
+        self.abi.check(self.L.ad_flag_wait_rel(C.c_void_p(self.flags.data_ptr() + 8 * slot), C.c_void_p(self.ebase.data_ptr()), 1,
+                                               2_000_000_000, C.c_void_p(self.status.data_ptr()), self._s()), "flag wait")
 
-    def _signal(self, rank, slot, epoch):
-        self.abi.check(self.L.ad_flag_signal(C.c_void_p(self.fp[rank] + 8 * slot), epoch, self._s()), "flag signal")
+    def _signal(self, rank, slot):
+        self.abi.check(self.L.ad_flag_signal_rel(C.c_void_p(self.fp[rank] + 8 * slot), C.c_void_p(self.ebase.data_ptr()), 1,
+                                                 self._s()), "flag signal")
 
     def _timed(self, name, fn):
         if self.marks is None:
@@ -378,16 +386,53 @@ class Step:
         self.marks.append((name, e0, e1))
 
     def run(self, e2e=False):
-        L, abi, a, s = self.L, self.abi, self.conv, self._s()
-        r, R = self.rank, self.world
+        """One step.  The resident step (no host buffers, no per-call events) replays a CUDA graph of everything but the
+        filter-gradient allreduce: one graph per gradient buffer and halo mode, recorded on first use."""
+        torch = self.torch
         self.epoch += 1
-        ep = self.epoch
+        k = self.epoch & 1
+        main = torch.cuda.current_stream()
         if e2e:
             # host NCHW fp32 -> device staging -> bf16 NHWC (into the interior of the halo-padded strip)
             self.x32.copy_(self.x_host, non_blocking=True)
             self.dy32.copy_(self.dy_host, non_blocking=True)
             for src, dst in self.cv:
-                abi.check(L.ad_convert(C.byref(src), C.byref(dst), 0, s), "convert")
+                self.abi.check(self.L.ad_convert(C.byref(src), C.byref(dst), 0, self._s()), "convert")
+        if self.world > 1 and self.ar_done[k] is not None:
+            # this step's gradient buffer: free again once the allreduce that last used it (two steps ago) is done
+            main.wait_event(self.ar_done[k])
+        self.dw = self.dws[k]
+        if self.use_graph and not e2e and self.marks is None and self.epoch > 4:   # the first steps run eagerly
+            key = (self.halo, k)
+            if key not in self.graphs:
+                l0 = self.L.ad_launch_count()
+                g = torch.cuda.CUDAGraph()
+                # thread-local: the process group's watchdog thread may query events while this thread records
+                with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                    self._body(k)
+                self.graphs[key] = (g, int(self.L.ad_launch_count() - l0))
+            g, n = self.graphs[key]
+            g.replay()
+            self.replayed_launches += n
+        else:
+            self._body(k)
+        if self.world > 1:
+            # filter-gradient allreduce over NCCL / NVLink on its own stream: it overlaps the next step's exchange and
+            # forward pass (an optimizer would consume it after that step's backward pass)
+            self.ar_stream.wait_stream(main)
+            with torch.cuda.stream(self.ar_stream):
+                self.env.dist.all_reduce(self.dws[k])
+                self.ar_done[k] = self.ar_stream.record_event()
+            if e2e:
+                main.wait_stream(self.ar_stream)
+        if e2e:
+            self.dw_host.copy_(self.dws[k], non_blocking=True)
+
+    def _body(self, k):
+        """Halo exchange, forward, data gradient, halo-gradient accumulate-back and filter gradient into buffer k, on the
+        current stream and the side stream forked from it (joined again at the end)."""
+        L, abi, a, s = self.L, self.abi, self.conv, self._s()
+        r, R = self.rank, self.world
         # forward: push my edge rows into the neighbours' halo rows on a side stream and wait there for
         # theirs, while the main stream already convolves the interior rows; the PAD boundary rows at
         # either end follow once the halo has landed
@@ -397,10 +442,9 @@ class Step:
             self.side.wait_stream(main)
             with self.torch.cuda.stream(self.side):
                 s2 = self._s()
-                self.hx.epoch = ep
                 abi.check(L.ad_halo_exchange(C.byref(self.hx), s2), "halo exchange")
                 for slot in self.plan.exchange_waits():
-                    self._wait(slot, ep)
+                    self._wait(slot)
                 landed = self.side.record_event()
             a.out_row_begin, a.out_row_count = PAD, self.h - 2 * PAD
             self._timed("fprop", lambda: abi.check(L.ad_conv2d_fprop(C.byref(a), s), "fprop interior"))
@@ -412,6 +456,7 @@ class Step:
         else:
             self._timed("fprop", lambda: abi.check(L.ad_conv2d_fprop(C.byref(a), s), "fprop"))
         # backward: data gradient over the whole padded strip, filter gradient, halo-gradient accumulate-back
+        self.dw = self.dws[k]
         a.y, a.dx, a.dw = self.dy.data_ptr(), self.gx.data_ptr(), self.dw.data_ptr()
         a.dx_col_begin, a.dx_col_count = PAD, SIZE     # the W-pad columns of the gradient buffer are never read
         self._timed("dgrad", lambda: abi.check(L.ad_conv2d_dgrad(C.byref(a), s), "dgrad"))
@@ -423,31 +468,15 @@ class Step:
             with self.torch.cuda.stream(self.side):
                 s2 = self._s()
                 for peer, slot in self.plan.reduce_signals():
-                    self._signal(peer, slot, ep)
+                    self._signal(peer, slot)
                 for slot in self.plan.reduce_waits():
-                    self._wait(slot, ep)
+                    self._wait(slot)
                 abi.check(L.ad_halo_reduce(C.byref(self.hg), s2), "halo reduce")
-        if R > 1:
-            # this step's gradient buffer: free again once the allreduce that last used it (two steps ago) is done
-            k = ep & 1
-            self.dw = self.dws[k]
-            a.dw = self.dw.data_ptr()
-            if self.ar_done[k] is not None:
-                self.torch.cuda.current_stream().wait_event(self.ar_done[k])
         self._timed("wgrad", lambda: abi.check(L.ad_conv2d_wgrad(C.byref(a), s), "wgrad"))
-        if R > 1:
-            # filter-gradient allreduce over NCCL / NVLink on its own stream: it overlaps the next step's exchange and
-            # forward pass (an optimizer would consume it after that step's backward pass)
-            main = self.torch.cuda.current_stream()
-            self.ar_stream.wait_stream(main)
-            with self.torch.cuda.stream(self.ar_stream):
-                self.env.dist.all_reduce(self.dw)
-                self.ar_done[ep & 1] = self.ar_stream.record_event()
-            main.wait_stream(self.side)
-            if e2e:
-                main.wait_stream(self.ar_stream)
-        if e2e:
-            self.dw_host.copy_(self.dw, non_blocking=True)
+        if R > 1 and self.halo:
+            self.torch.cuda.current_stream().wait_stream(self.side)
+            # all of this step's flag values are used up: the next step's are one higher
+            abi.check(L.ad_flag_advance(C.c_void_p(self.ebase.data_ptr()), 1, s), "flag advance")
 
     def check_status(self):
         st = self.status.cpu().tolist() + self.scratch[:4].view(self.torch.int32).cpu().tolist()
@@ -605,7 +634,8 @@ def run_conv_workload(env, args, with_cpu=True):
         raise SystemExit("image height must divide by the number of GPUs")
     L = abi.load()   # raises if the CUDA library is missing: no fallback
     step = Step(env)
-    for _ in range(max(3, args.warmup)):
+    step.use_graph = not args.no_graph
+    for _ in range(max(8, args.warmup)):     # the first 4 run eagerly, the next two record the graphs
         step.run()
     torch.cuda.synchronize()
     step.check_status()
@@ -618,19 +648,23 @@ def run_conv_workload(env, args, with_cpu=True):
     sampler = ClockSampler(env.local)
     if rank == 0:
         sampler.start()
-    launches0 = L.ad_launch_count()
+    launches0, replayed0 = L.ad_launch_count(), step.replayed_launches
     per, n, secs = timed_steps(env, step.run, marks, args.steps)
-    launches = L.ad_launch_count() - launches0
+    launches = L.ad_launch_count() - launches0 + step.replayed_launches - replayed0
     clocks = sampler.stop() if rank == 0 else None
     step.check_status()
     st = step_stats(per)
 
-    ms_nohalo = None
+    # what the halo transfers cost exposed: the same step with and without them, both launched call by call (the two
+    # recorded graphs differ in more than the transfers: one forward launch instead of three)
+    halo_exposed = None
     if world > 1:
+        recorded, step.use_graph = step.use_graph, False
+        per_h, _, _ = timed_steps(env, step.run, marks, args.steps, min_seconds=0.5)
         step.halo = False
         per_nh, _, _ = timed_steps(env, step.run, marks, args.steps, min_seconds=0.5)
-        ms_nohalo = float(np.median(per_nh))
-        step.halo = True
+        step.halo, step.use_graph = True, recorded
+        halo_exposed = float(np.median(per_h)) - float(np.median(per_nh))
     # as long as a second, like the timed region: a short burst runs at higher clocks than the power cap sustains
     kt_step = kernel_times_in_step(env, step, int(min(MAX_TIMED_STEPS, max(20, args.steps, math.ceil(min(1.0, MIN_SECONDS) * 1e3 / st["median"])))))
     step.check_status()
@@ -660,13 +694,14 @@ def run_conv_workload(env, args, with_cpu=True):
             "config": {"workload": "microbench_spatial_conv", "batch": BATCH, "channels": CH, "image": [SIZE, SIZE],
                        "kernel": KS, "dilation": DIL, "halo": PAD, "strips": world, "layout": "NHWC",
                        "filter_gradient_allreduce": "none (one strip)" if world == 1 else "NCCL on its own stream, double-buffered: overlaps the next step's exchange and forward pass",
-                       "l2": "inputs larger than L2 (%.2f GB activations per pass)" % (BATCH * SIZE * SIZE * CH * 2 / 1e9), "parallelism": f"spatial-h{world}"},
+                       "l2": "inputs larger than L2 (%.2f GB activations per pass)" % (BATCH * SIZE * SIZE * CH * 2 / 1e9), "parallelism": f"spatial-h{world}",
+                       "launch": "cuda graph per step (the NCCL allreduce is launched beside it)" if step.use_graph else "eager"},
             "e2e": {"value": total_flops / (float(np.median(per_e2e)) * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": hbytes,
                     "d2h_bytes_per_step": step.dw_host.numel() * 4, "steps": n_e2e,
                     "boundary": "pinned host NCHW fp32 strips (the reference's boundary format); the conversion to bf16 NHWC is inside the timed step"},
             "gpu_launches": int(launches), "timed_steps": n, "timed_region_s": secs,
             "step_ms": st,
-            "halo_exposed_ms": None if ms_nohalo is None else med - ms_nohalo,
+            "halo_exposed_ms": halo_exposed,
             "roofline": {"bound": "tensor", "kernel": {"fprop": "conv_tc_stream_fwd_kernel<3,3> (fprop)", "dgrad": "conv_tc_stream_fwd_kernel<3,3> (dgrad)",
                                                         "wgrad": "conv_tc_row_wgrad_kernel<3,3>"}[top], "achieved": achieved, "peak": peaks["tf_sustained"],
                          "unit": "TFLOP/s", "frac": achieved / peaks["tf_sustained"],
