@@ -241,12 +241,15 @@ __global__ void __launch_bounds__(256, 2) bn_reduce_vec(BnRed p, float* partial)
     a[j] = b[j] = 0.f;
     if (MODE == 1) { mean[j] = p.mean[cg * 8 + j]; invstd[j] = p.invstd[cg * 8 + j]; gam[j] = p.gamma[cg * 8 + j]; bet[j] = p.beta[cg * 8 + j]; }
   }
+  // Pixels are walked from the last to the first: the tensor was just written front to back by its producer, so its
+  // tail is what the L2 still holds; the apply pass that follows walks front to back and meets what this pass read last.
   for (uint32_t i0 = blockIdx.x * PL + pl; i0 < per; i0 += kBnUnroll * stride) {
     uint4 xr[kBnUnroll], gr[kBnUnroll];
 #pragma unroll
     for (int u = 0; u < kBnUnroll; ++u) {
-      const uint32_t i = i0 + u * stride;
-      if (i < per) {
+      const uint32_t k = i0 + u * stride;
+      if (k < per) {
+        const uint32_t i = per - 1u - k;
         xr[u] = ld16(p.x, pix_off(p.x, i, p.H, p.W) + cg * 8);
         if (MODE == 1) gr[u] = ld16(p.dy, pix_off(p.dy, i, p.H, p.W) + cg * 8);
       }

@@ -19,7 +19,7 @@ def _unflatten(net, flat):
     return out
 
 
-@pytest.mark.parametrize("R", [1, 2, 4])
+@pytest.mark.parametrize("R", [1, 2, 4, 8])
 @pytest.mark.parametrize("mode", ["f32", "bf16"])
 def test_config1_partitioned_conv3x3_forward_backward_update(R, mode):
     """benchmark config 1: 3x3 conv, stride 1, pad 1, N=1, C=K=64, 64x64, H-strips with 1-row halos:
@@ -141,7 +141,7 @@ def test_conv3x3_between_reference_collective_operators(R, mode):
     net.close(); ctx.close()
 
 
-@pytest.mark.parametrize("R,mode", [(1, "f32"), (2, "f32"), (4, "f32"), (2, "bf16")])
+@pytest.mark.parametrize("R,mode", [(1, "f32"), (2, "f32"), (4, "f32"), (8, "f32"), (2, "bf16")])
 def test_stem_stage1_matches_oracle(R, mode):
     """ResNet-50 stem + stage 1 (benchmark config 3 at a reduced image size) through the op graph:
     output, every parameter gradient (summed over ranks) vs the CPU composition of oracle ops."""
