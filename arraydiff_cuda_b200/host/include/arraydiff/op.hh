@@ -649,14 +649,14 @@ public:
   size_t _store_val(TxnId txn, VarIdSet& vars, size_t offset, any* writer) override;
   void load_labels(const uint32_t* host);      // synchronous host -> device copy
   void set_loss_weight(float w);
-  double loss_sum();                           // synchronous: sum of the per-pixel losses of the last forward
+  double loss_sum();                           // synchronous: sum of the per-pixel losses of the last forward (summed on the device, 8 bytes read back)
   void store_loss(float* host);                // synchronous: the per-pixel losses
 private:
   ActVar x_;
   shared_ptr<Context> ctx_;
   size_t n_, hw_, classes_;
   uint32_t* labels_ = nullptr;
-  float *loss_ = nullptr, *dloss_ = nullptr;
+  float *loss_ = nullptr, *dloss_ = nullptr, *loss_sum_dev_ = nullptr;
   VarId label_var_, loss_var_;
   bool replica_ = false;
 };

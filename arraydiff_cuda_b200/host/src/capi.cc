@@ -184,7 +184,9 @@ void adh_net_output_dims(void* h, int dims[4]) {
   dims[0] = (int)o->batch_shape(); dims[1] = (int)d.shape[2]; dims[2] = (int)d.shape[1]; dims[3] = (int)d.shape[0];
 }
 // full image, packed NCHW fp32 on the host; starts a new transaction and runs the forward pass
-int adh_net_forward(void* h, const float* image_nchw) {
+// host image (packed NCHW fp32) -> the input variable of every local rank (its H-strip, or the whole image), in a new
+// transaction; nothing is evaluated.  adh_net_step_resident / adh_net_step_graph then run on what was loaded.
+int adh_net_load_input(void* h, const float* image_nchw) {
   auto* n = (Net*)h;
   n->txn.reset(new TxnId());
   n->opt->persist(*n->txn);
@@ -197,6 +199,11 @@ int adh_net_forward(void* h, const float* image_nchw) {
     else rd = const_cast<float*>(image_nchw);                                             // the whole image on every rank
     n->net.sink->load_val(*n->txn, v, 0, &rd);
   }
+  return AD_OK;
+}
+int adh_net_forward(void* h, const float* image_nchw) {
+  auto* n = (Net*)h;
+  adh_net_load_input(h, image_nchw);
   n->net.sink->eval(*n->txn);
   n->ctx->end_phase();
   return AD_OK;

@@ -1207,11 +1207,18 @@ void CudnnSoftmaxNLLLoss2DOpF::store_loss(float* host) {
   conn.sync();
 }
 double CudnnSoftmaxNLLLoss2DOpF::loss_sum() {
-  vector<float> h(n_ * hw_);
-  store_loss(h.data());
-  double s = 0.0;
-  for (float v : h) s += (double)v;
-  return s;
+  // summed on the device by the two-stage statistics reduction (fixed order; fp32 partial sums of a few dozen terms,
+  // combined in double) over the losses viewed as a one-channel tensor
+  GPUContext* g = gpu_of(ctx_, x_->rank());
+  GPUConn conn = g->conn();
+  if (!loss_sum_dev_) loss_sum_dev_ = (float*)g->arena().alloc(64);
+  g->reserve_scratch(ad_bn_scratch_bytes(1));
+  ad_tensor4 t = {loss_, AD_F32, (uint32_t)n_, 1u, 1u, (uint32_t)hw_, (long long)hw_, (long long)hw_, (long long)hw_, 1};
+  AD_CHECK(ad_bn_partial_stats(&t, loss_sum_dev_, g->get_scratch(), g->scratch_size(), conn.stream()));
+  float h[2] = {0.f, 0.f};
+  CUDA_CHECK(cudaMemcpyAsync(h, loss_sum_dev_, sizeof h, cudaMemcpyDeviceToHost, conn.stream()));
+  conn.sync();
+  return (double)h[0];
 }
 void CudnnSoftmaxNLLLoss2DOpF::_forward(TxnId txn) {
   GPUConn conn = gpu_of(ctx_, x_->rank())->conn();

@@ -48,6 +48,7 @@ def load():
         L.adh_net_set_params.argtypes = [vp, vp]
         L.adh_net_output_dims.argtypes = [vp, C.POINTER(C.c_int)]
         L.adh_net_forward.argtypes = [vp, vp]
+        L.adh_net_load_input.argtypes = [vp, vp]
         L.adh_net_step_resident.argtypes = [vp, C.c_int]
         L.adh_net_set_labels.argtypes = [vp, C.c_int, vp]
         L.adh_net_set_loss_weight.argtypes = [vp, C.c_float]
@@ -128,6 +129,13 @@ class Net:
         x = np.ascontiguousarray(x, np.float32)
         assert x.shape == self.in_shape
         self.L.adh_net_forward(self.h, _p(x))
+
+    def load_input(self, x):
+        """Host image -> the local ranks' input buffers, without evaluating anything: the next step_resident() /
+        step_graph() runs on it."""
+        x = np.ascontiguousarray(x, np.float32)
+        assert x.shape == self.in_shape
+        assert self.L.adh_net_load_input(self.h, _p(x)) == 0
 
     def output(self, rank, out=None):
         """`out`: a float32 array of strip_shape to fill (e.g. in pinned memory) instead of a fresh one"""

@@ -1047,24 +1047,39 @@ def run_net_workload(env, args, kind):
         labels = pinned(labels)
     out_host = pinned(np.empty(net.strip_shape, np.float32))
 
+    use_graph = not args.no_graph and not (world > 1 and args.nccl_allreduce)
+
     def e2e_step():
-        net.forward(x)                       # host image -> every local rank (H2D inside)
+        # host image -> every local rank (H2D and the conversion to bf16 NHWC inside), host labels / upstream gradient ->
+        # device, then the step itself: replayed from the CUDA graph like the resident step (or launched call by call)
+        net.load_input(x) if use_graph else net.forward(x)
         for r in ranks:
             if seg:
-                net.set_labels(r, labels[:, r * hs:(r + 1) * hs])   # host labels -> device
+                net.set_labels(r, labels[:, r * hs:(r + 1) * hs])
             elif hyb:
                 net.set_labels(r, labels)
             else:
-                net.set_output_grad(r, dy[r])    # host upstream gradient -> device
-        net.backward()
-        net.sgd_step()
+                net.set_output_grad(r, dy[r])
+        if use_graph:
+            net.step_graph(True)
+        else:
+            net.backward()
+            net.sgd_step()
         return net.loss() if (seg or hyb) else net.output(ranks[0], out=out_host)          # D2H read of a result
 
     # steady-state step: the resident step replayed from a CUDA graph (flag values between processes are
     # relative to a device-resident base, the gradient allreduce is the built-in peer exchange)
-    use_graph = not args.no_graph and not (world > 1 and args.nccl_allreduce)
     step = (lambda: net.step_graph(True)) if use_graph else (lambda: net.step_resident(True))
-    e2e_step()
+    net.forward(x)                           # first step call by call: every lazily allocated buffer exists afterwards
+    for r in ranks:
+        if seg:
+            net.set_labels(r, labels[:, r * hs:(r + 1) * hs])
+        elif hyb:
+            net.set_labels(r, labels)
+        else:
+            net.set_output_grad(r, dy[r])
+    net.backward()
+    net.sgd_step()
     net.step_resident(True)
     for _ in range(max(3, args.warmup)):
         step()
@@ -1133,7 +1148,7 @@ def run_net_workload(env, args, kind):
                        "l2": "activations of one step total more than 1 GB, larger than L2", "parallelism": f"data{D}-spatial-h{strips}" if hyb else f"spatial-h{strips}"},
             "e2e": {"value": flops / t_e2e / 1e12, "unit": UNIT, "images_per_s": NB * D / t_e2e,
                     "h2d_bytes_per_step": int(x.nbytes // (Sg if world > 1 else 1) + (labels.nbytes if hyb else labels.nbytes // world if seg else sum(d.nbytes for d in dy))),
-                    "d2h_bytes_per_step": int(NB * 4 * len(ranks) if hyb else np.prod(net.strip_shape[2:]) * NB * 4 * len(ranks) if seg else np.prod(net.strip_shape) * 4), "steps": k_e2e,
+                    "d2h_bytes_per_step": int(8 * len(ranks) if (hyb or seg) else np.prod(net.strip_shape) * 4), "steps": k_e2e,
                     "timing": "host clock between synchronisations",
                     "boundary": "pinned host NCHW fp32 images and uint32 labels through the host layer's public calls; copies and the conversion to bf16 NHWC are inside"},
             "gpu_launches": int(launches), "timed_steps": n, "timed_region_s": secs, "step_ms": st,

@@ -249,6 +249,40 @@ def test_graph_replayed_steps_equal_eager_steps(R):
     assert not np.array_equal(results[0][0], np.zeros_like(results[0][0]))
 
 
+def test_load_input_then_graph_step_equals_forward_backward_update():
+    """`load_input` puts a new host image into the ranks' input buffers without evaluating anything; the replayed
+    step that follows equals forward + backward + update launched call by call on the same image, bit for bit."""
+    from arraydiff_cuda_b200 import hostlib
+    R, N, Cc, Hh, W = 2, 1, 3, 64, 64
+    xs = [H.uniform(310 + i, (N, Cc, Hh, W), 0.0, 1.0) for i in range(3)]
+    dy = H.normal(320, (N, 256, Hh // 4, W // 4))
+    h = dy.shape[2] // R
+    results = []
+    for graph in (False, True):
+        ctx = hostlib.Context([0] * R, hostlib.BF16_NHWC, arena_mb=512)
+        net = hostlib.Net(ctx, "stem_stage1", Hh, W, Cc, N, seed=17)
+        net.configure_sgd(1e-3, 0.9, l2=1e-4, nesterov=True)
+        for i, x in enumerate(xs):
+            if graph and i > 0:
+                net.load_input(x)
+                for r in range(R):
+                    net.set_output_grad(r, dy[:, :, r * h:(r + 1) * h])
+                net.step_graph(True)
+            else:
+                net.forward(x)
+                for r in range(R):
+                    net.set_output_grad(r, dy[:, :, r * h:(r + 1) * h])
+                net.backward()
+                net.sgd_step()
+            if i == 0:
+                net.step_resident(True)        # every lazily allocated buffer exists from here on
+        net.sync()
+        assert net.status() == 0
+        results.append(net.params(0).copy())
+        net.close(); ctx.close()
+    assert np.array_equal(results[0], results[1])
+
+
 def _segnet_shapes(man, base, classes):
     """KCRS shapes of the conv kernels named in the manifest of a 'segnet_small' net."""
     shapes = {"stem.conv.kernel": (base, 3, 7, 7), "head.conv.kernel": (classes, base * 32, 1, 1)}
