@@ -512,6 +512,7 @@ conv_tc_stream_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
       uint32_t stage = 0, phase = 0, t = 0;      // t: output rows this CTA has started before the current item
       bool ok = mbar_wait(smem_u32(&ctl->wbar), 0, abortf);
       const uint64_t db0 = smem_desc_sw128(smem_u32(wsm), 16, 1024);
+      const uint32_t db_lo = (uint32_t)db0, d_hi = (uint32_t)(db0 >> 32), a_step = p.dw * 8u;
       for (uint32_t item = blockIdx.x; ok && item < p.items && !*abortf; item += gridDim.x) {
         const StreamItem it = stream_item(p, item);
         if (it.Lc <= 0) continue;
@@ -534,30 +535,44 @@ conv_tc_stream_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
           const uint32_t q0 = kh - 1u - (uint32_t)(j - i_lo);
           const uint32_t n1 = nr < kSlots - c0 ? nr : kSlots - c0, n2 = nr - n1;
           const uint32_t d1 = tmem_base + c0 * 64u, id1 = idesc_bf16(64u * n1, 0, 0), id2 = idesc_bf16(64u * (n2 ? n2 : 1u), 0, 0);
-          const uint64_t b1 = db0 + (uint64_t)(q0 * 512u), b2 = b1 + (uint64_t)(n1 * 512u);
+          // From here on only the low descriptor words move (start addresses, in 16-byte units: one pixel row = 8,
+          // one filter tap = 512); A and B share the high word.  This thread executes an instruction only every few
+          // cycles, so the loop below is kept to two adds per MMA.
+          const uint32_t a0 = (uint32_t)da0, b1 = db_lo + q0 * 512u, b2 = b1 + n1 * 512u;
           if (new_row) {
             // first MMA of the row: the slot of output row j is overwritten, the older rows accumulate
             const uint32_t cj = (t + (uint32_t)j) & 7u;
             if (j > i_lo) {
               const uint32_t no = (uint32_t)(j - i_lo);
               const uint32_t m1 = no < kSlots - c0 ? no : kSlots - c0, m2 = no - m1;
-              umma_bf16(d1, da0, b1, idesc_bf16(64u * m1, 0, 0), 1u);
-              if (m2) umma_bf16(tmem_base, da0, b1 + (uint64_t)(m1 * 512u), idesc_bf16(64u * m2, 0, 0), 1u);
+              umma_bf16_acc_lo(d1, a0, b1, d_hi, idesc_bf16(64u * m1, 0, 0));
+              if (m2) umma_bf16_acc_lo(tmem_base, a0, b1 + m1 * 512u, d_hi, idesc_bf16(64u * m2, 0, 0));
             }
-            umma_bf16(tmem_base + cj * 64u, da0, db0 + (uint64_t)((kh - 1u) * 512u), idesc_bf16(64u, 0, 0), 0u);
+            umma_bf16_ovw_lo(tmem_base + cj * 64u, a0, db_lo + (kh - 1u) * 512u, d_hi, idesc_bf16(64u, 0, 0));
           }
-          uint64_t da_s = da0;
+          uint32_t a_s = a0;
+          if (n2 == 0) {
 #pragma unroll
-          for (uint32_t s = 0; s < kw; ++s) {
+            for (uint32_t s = 0; s < kw; ++s) {
 #pragma unroll
-            for (uint32_t kk = 0; kk < 4; ++kk) {
-              if (s == 0 && kk == 0 && new_row) continue;
-              // descriptor address fields count 16-byte units: one pixel row = 8, one filter tap = 512
-              const uint32_t boff = s * kh * 512u + 2u * kk;
-              umma_bf16(d1, da_s + 2u * kk, b1 + boff, id1, 1u);
-              if (n2) umma_bf16(tmem_base, da_s + 2u * kk, b2 + boff, id2, 1u);
+              for (uint32_t kk = 0; kk < 4; ++kk) {
+                if (s == 0 && kk == 0 && new_row) continue;
+                umma_bf16_acc_lo(d1, a_s + 2u * kk, b1 + (s * kh * 512u + 2u * kk), d_hi, id1);
+              }
+              a_s += a_step;
             }
-            da_s += (uint64_t)(p.dw * 8u);
+          } else {
+#pragma unroll
+            for (uint32_t s = 0; s < kw; ++s) {
+#pragma unroll
+              for (uint32_t kk = 0; kk < 4; ++kk) {
+                if (s == 0 && kk == 0 && new_row) continue;
+                const uint32_t boff = s * kh * 512u + 2u * kk;
+                umma_bf16_acc_lo(d1, a_s + 2u * kk, b1 + boff, d_hi, id1);
+                umma_bf16_acc_lo(tmem_base, a_s + 2u * kk, b2 + boff, d_hi, id2);
+              }
+              a_s += a_step;
+            }
           }
           umma_commit(smem_u32(&ctl->empty[stage]));
           if (j >= (int32_t)kh - 1) umma_commit(smem_u32(&ctl->afull[(t + (uint32_t)(j - ((int32_t)kh - 1))) & 7u]));
