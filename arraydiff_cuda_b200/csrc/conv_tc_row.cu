@@ -397,7 +397,25 @@ int conv_tc_row_fwd(const void* act, uint32_t NI, uint32_t IH, uint32_t IW, uint
 // warps (bias / ReLU / bf16 / swizzled staging / one TMA tile store, as above) while later rows accumulate.  The
 // new row's slot must be overwritten, the older rows' slots accumulated: the first MMA of an input row is split
 // in two for that reason; an MMA whose slots would wrap around the ring is split at the wrap.
+// What the MMA thread needs to know about an input row, worked out by the producer thread when it fetches the row (one
+// record per stage, visible to the MMA thread through the stage's `full` barrier).  All descriptor entries are the low
+// 32-bit words (start address in 16-byte units); A and B share the high word.
+struct StreamRow {
+  uint32_t a0;           // input row
+  uint32_t d1, id1;      // accumulate run 1: D column, instruction descriptor (N = 64 * slots)
+  uint32_t id2, n2;      // run 2 (slots wrapped to column 0): instruction descriptor, slot count (0: none)
+  uint32_t b1, b2;       // filter blocks of run 1 / run 2 (tap column 0, k block 0)
+  uint32_t flags;        // bit 0: the row starts an output row; bit 1: older rows accumulate in its first MMA; bit 2: ... in two runs
+  uint32_t idm1, idm2;   // first MMA of a new row: instruction descriptors of the older rows' run(s)
+  uint32_t bm2, dj;      // ... filter block of the second run; D column of the new row's own slot
+  uint32_t abar;         // unused
+  uint32_t ebar, epar;   // unused
+  uint32_t sbar;         // the ONE barrier to commit behind the row's MMAs: `afull` of the output row it completes (the
+                         // producer thread takes the stage back on the same barrier), else the stage's `empty` barrier
+};
 struct StreamCtl {
+  alignas(16) StreamRow row[8];
+  uint32_t swait_bar[8], swait_par[8], ecount[8];   // producer thread only: what frees each stage, uses of empty[]
   unsigned long long full[8], empty[8], afull[8], aempty[8], wbar, stg_full[2], stg_free[2];
   uint32_t tmem_base;
   volatile int abort_flag;
@@ -464,6 +482,7 @@ conv_tc_stream_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
       mbar_init(smem_u32(&ctl->stg_full[b]), 4);
       mbar_init(smem_u32(&ctl->stg_free[b]), 1);
     }
+    for (int a = 0; a < 8; ++a) ctl->swait_bar[a] = ctl->swait_par[a] = ctl->ecount[a] = 0;
     ctl->abort_flag = 0;
     mbar_init_fence();
     tma_prefetch_desc(&map_a);
@@ -489,97 +508,163 @@ conv_tc_stream_fwd_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
       for (uint32_t s = 0; s < kw; ++s)
         for (uint32_t r = 0; r < kh; ++r)
           tma_load_2d(smem_u32(wsm + (size_t)(s * kh + (kh - 1 - r)) * kTapBytes), &map_b, wbar, (int)((r * kw + s) * 64), 0);
-      uint32_t stage = 0, phase = 0;
+      uint32_t stage = 0, phase = 0, t = 0;      // t: output rows this CTA has started before the current item
       bool ok = true;
+      const uint32_t db_lo = (uint32_t)smem_desc_sw128(smem_u32(wsm), 16, 1024);
       for (uint32_t item = blockIdx.x; ok && item < p.items && !*abortf; item += gridDim.x) {
         const StreamItem it = stream_item(p, item);
         if (it.Lc <= 0) continue;
         const int32_t rows_in = it.Lc + (int32_t)kh - 1;
         for (int32_t j = 0; j < rows_in; ++j) {
-          if (!mbar_wait_relaxed(smem_u32(&ctl->empty[stage]), phase ^ 1u, abortf)) { ok = false; break; }
+          // the stage is free once the MMAs of the row that used it last are done: that row's one commit
+          if (ctl->swait_bar[stage] && !mbar_wait_relaxed(ctl->swait_bar[stage], ctl->swait_par[stage], abortf)) { ok = false; break; }
           const uint32_t full = smem_u32(&ctl->full[stage]);
           {
-          mbar_expect_tx(full, p.row_bytes);
-          tma_load_4d(smem_u32(psm + (size_t)stage * p.row_bytes), &map_a, full, 0, (int)(it.tx * 128) + p.offx,
-                      (int)(it.rho + (it.i0 + (uint32_t)j) * p.dh) + p.offy, (int)it.n);
-          }
-          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
-        }
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      uint32_t stage = 0, phase = 0, t = 0;      // t: output rows this CTA has started before the current item
-      bool ok = mbar_wait(smem_u32(&ctl->wbar), 0, abortf);
-      const uint64_t db0 = smem_desc_sw128(smem_u32(wsm), 16, 1024);
-      const uint32_t db_lo = (uint32_t)db0, d_hi = (uint32_t)(db0 >> 32), a_step = p.dw * 8u;
-      for (uint32_t item = blockIdx.x; ok && item < p.items && !*abortf; item += gridDim.x) {
-        const StreamItem it = stream_item(p, item);
-        if (it.Lc <= 0) continue;
-        const int32_t rows_in = it.Lc + (int32_t)kh - 1;
-        for (int32_t j = 0; j < rows_in; ++j) {
-          const int32_t i_lo = j >= (int32_t)kh - 1 ? j - ((int32_t)kh - 1) : 0;
-          const int32_t i_hi = j < it.Lc ? j : it.Lc - 1;
-          const bool new_row = j < it.Lc;
-          if (new_row) {
-            const uint32_t tt = t + (uint32_t)j;
-            if (!mbar_wait(smem_u32(&ctl->aempty[tt & 7u]), ((tt >> 3) & 1u) ^ 1u, abortf)) { ok = false; break; }
-          }
-          if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abortf)) { ok = false; break; }
-          tc_fence_after();
-          const uint64_t da0 = smem_desc_sw128(smem_u32(psm + (size_t)stage * p.row_bytes), 16, 1024);
-          // The accumulate range [i_lo, i_hi] as one or two runs of adjacent slots (two when it wraps around the
-          // ring), worked out once per input row: D column, filter block offset and instruction descriptor.
-          // Filter blocks of column tap s start at s*kh; within them output row i takes block kh-1-(j-i).
-          const uint32_t c0 = (t + (uint32_t)i_lo) & 7u, nr = (uint32_t)(i_hi - i_lo + 1);
-          const uint32_t q0 = kh - 1u - (uint32_t)(j - i_lo);
-          const uint32_t n1 = nr < kSlots - c0 ? nr : kSlots - c0, n2 = nr - n1;
-          const uint32_t d1 = tmem_base + c0 * 64u, id1 = idesc_bf16(64u * n1, 0, 0), id2 = idesc_bf16(64u * (n2 ? n2 : 1u), 0, 0);
-          // From here on only the low descriptor words move (start addresses, in 16-byte units: one pixel row = 8,
-          // one filter tap = 512); A and B share the high word.  This thread executes an instruction only every few
-          // cycles, so the loop below is kept to two adds per MMA.
-          const uint32_t a0 = (uint32_t)da0, b1 = db_lo + q0 * 512u, b2 = b1 + n1 * 512u;
-          if (new_row) {
-            // first MMA of the row: the slot of output row j is overwritten, the older rows accumulate
-            const uint32_t cj = (t + (uint32_t)j) & 7u;
-            if (j > i_lo) {
-              const uint32_t no = (uint32_t)(j - i_lo);
+            // The row's record for the MMA thread (that thread executes an instruction only every few cycles and must
+            // keep the tensor pipe fed, so the arithmetic is done here).  Input row j of the item adds to the output
+            // rows [i_lo, i_hi]: one or two runs of adjacent accumulator slots (two when the range wraps around the
+            // ring).  Filter blocks of column tap s start at s*kh; within them output row i takes block kh-1-(j-i).
+            const int32_t i_lo = j >= (int32_t)kh - 1 ? j - ((int32_t)kh - 1) : 0;
+            const int32_t i_hi = j < it.Lc ? j : it.Lc - 1;
+            const bool new_row = j < it.Lc;
+            const uint32_t c0 = (t + (uint32_t)i_lo) & 7u, nr = (uint32_t)(i_hi - i_lo + 1);
+            const uint32_t q0 = kh - 1u - (uint32_t)(j - i_lo);
+            const uint32_t n1 = nr < kSlots - c0 ? nr : kSlots - c0, n2 = nr - n1;
+            StreamRow r;
+            r.a0 = (uint32_t)smem_desc_sw128(smem_u32(psm + (size_t)stage * p.row_bytes), 16, 1024);
+            r.d1 = tmem_base + c0 * 64u;
+            r.id1 = idesc_bf16(64u * n1, 0, 0);
+            r.id2 = idesc_bf16(64u * (n2 ? n2 : 1u), 0, 0);
+            r.n2 = n2;
+            r.b1 = db_lo + q0 * 512u;
+            r.b2 = r.b1 + n1 * 512u;
+            r.flags = new_row ? 1u : 0u;
+            r.idm1 = r.idm2 = r.bm2 = r.dj = r.ebar = r.epar = 0;
+            if (new_row) {
+              const uint32_t tt = t + (uint32_t)j, no = (uint32_t)(j - i_lo);
               const uint32_t m1 = no < kSlots - c0 ? no : kSlots - c0, m2 = no - m1;
-              umma_bf16_acc_lo(d1, a0, b1, d_hi, idesc_bf16(64u * m1, 0, 0));
-              if (m2) umma_bf16_acc_lo(tmem_base, a0, b1 + m1 * 512u, d_hi, idesc_bf16(64u * m2, 0, 0));
+              if (no) r.flags |= 2u;
+              if (m2) r.flags |= 4u;
+              r.idm1 = idesc_bf16(64u * (m1 ? m1 : 1u), 0, 0);
+              r.idm2 = idesc_bf16(64u * (m2 ? m2 : 1u), 0, 0);
+              r.bm2 = r.b1 + m1 * 512u;
+              r.dj = tmem_base + (tt & 7u) * 64u;
+              // The new output row's accumulator slot must have been drained by the epilogue warps.  This thread waits
+              // for that (the MMA thread then learns it through the stage's `full` barrier, one wait instead of two);
+              // the slot was last used eight output rows ago, whose MMAs are behind rows this thread fetched long ago.
+              if (!mbar_wait_relaxed(smem_u32(&ctl->aempty[tt & 7u]), ((tt >> 3) & 1u) ^ 1u, abortf)) { ok = false; break; }
             }
-            umma_bf16_ovw_lo(tmem_base + cj * 64u, a0, db_lo + (kh - 1u) * 512u, d_hi, idesc_bf16(64u, 0, 0));
+            r.abar = 0;
+            uint32_t cpar;
+            if (j >= (int32_t)kh - 1) {
+              const uint32_t to = t + (uint32_t)(j - ((int32_t)kh - 1));   // the output row this input row completes
+              r.sbar = smem_u32(&ctl->afull[to & 7u]);
+              cpar = (to >> 3) & 1u;
+            } else {
+              r.sbar = smem_u32(&ctl->empty[stage]);
+              cpar = ctl->ecount[stage]++ & 1u;
+            }
+            ctl->swait_bar[stage] = r.sbar;
+            ctl->swait_par[stage] = cpar;
+            uint4* dst = (uint4*)&ctl->row[stage];
+            const uint4* src = (const uint4*)&r;
+            dst[0] = src[0]; dst[1] = src[1]; dst[2] = src[2]; dst[3] = src[3];
+            // the arrive below releases these stores to the thread that waits on the barrier
+            mbar_expect_tx(full, p.row_bytes);
+            tma_load_4d(smem_u32(psm + (size_t)stage * p.row_bytes), &map_a, full, 0, (int)(it.tx * 128) + p.offx,
+                        (int)(it.rho + (it.i0 + (uint32_t)j) * p.dh) + p.offy, (int)it.n);
           }
-          uint32_t a_s = a0;
-          if (n2 == 0) {
-#pragma unroll
-            for (uint32_t s = 0; s < kw; ++s) {
-#pragma unroll
-              for (uint32_t kk = 0; kk < 4; ++kk) {
-                if (s == 0 && kk == 0 && new_row) continue;
-                umma_bf16_acc_lo(d1, a_s + 2u * kk, b1 + (s * kh * 512u + 2u * kk), d_hi, id1);
-              }
-              a_s += a_step;
-            }
-          } else {
-#pragma unroll
-            for (uint32_t s = 0; s < kw; ++s) {
-#pragma unroll
-              for (uint32_t kk = 0; kk < 4; ++kk) {
-                if (s == 0 && kk == 0 && new_row) continue;
-                const uint32_t boff = s * kh * 512u + 2u * kk;
-                umma_bf16_acc_lo(d1, a_s + 2u * kk, b1 + boff, d_hi, id1);
-                umma_bf16_acc_lo(tmem_base, a_s + 2u * kk, b2 + boff, d_hi, id2);
-              }
-              a_s += a_step;
-            }
-          }
-          umma_commit(smem_u32(&ctl->empty[stage]));
-          if (j >= (int32_t)kh - 1) umma_commit(smem_u32(&ctl->afull[(t + (uint32_t)(j - ((int32_t)kh - 1))) & 7u]));
           if (++stage == p.stages) { stage = 0; phase ^= 1u; }
         }
         t += (uint32_t)it.Lc;
       }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // This thread executes an instruction only every few cycles and the tensor pipe queues only about three MMAs, so
+      // whatever it does besides issuing MMAs leaves the pipe idle unless MMAs are queued behind it.  Hence: the
+      // per-row arithmetic comes ready-made from the producer thread (StreamRow); only the low descriptor words move
+      // (two adds per MMA); the accumulate predicate is fixed at compile time; wrapped rows have a loop of their own;
+      // one commit per row; and the loop is software-pipelined by hand -- the commit of a row is issued behind the first
+      // tap column of the NEXT row, and the next row's waits and record loads sit in front of the last tap column of the current one.
+      struct Rec { uint4 r0, r1, r2, r3; };   // r0: a0 d1 id1 id2 | r1: n2 b1 b2 flags | r2: idm1 idm2 bm2 dj | r3: abar ebar epar sbar
+      uint32_t stage = 0, phase = 0, total = 0, prepared = 0;
+      bool ok = mbar_wait(smem_u32(&ctl->wbar), 0, abortf);
+      const uint64_t db0 = smem_desc_sw128(smem_u32(wsm), 16, 1024);
+      const uint32_t db_lo = (uint32_t)db0, d_hi = (uint32_t)(db0 >> 32), a_step = p.dw * 8u;
+      for (uint32_t item = blockIdx.x; item < p.items; item += gridDim.x) {   // input rows this CTA will see
+        const StreamItem it = stream_item(p, item);
+        if (it.Lc > 0) total += (uint32_t)it.Lc + kh - 1u;
+      }
+      // waits for the next input row and loads its record
+      auto prep = [&](Rec& R) -> bool {
+        if (!ok || prepared == total) return false;
+        if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abortf)) { ok = false; return false; }
+        const uint4* rp = (const uint4*)&ctl->row[stage];
+        R.r0 = rp[0]; R.r1 = rp[1]; R.r2 = rp[2]; R.r3 = rp[3];
+        tc_fence_after();   // the accumulator slot of a new output row was drained with tcgen05.ld (the producer thread waited for it)
+        if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+        ++prepared;
+        return true;
+      };
+      uint32_t pend_s = 0;
+      const uint32_t s_prep = kw >= 3 ? kw - 2u : 0u;   // the next row is prepared behind this tap column
+      auto body = [&](const Rec& C, Rec& Nx, bool& have_next) {
+        const uint32_t a0 = C.r0.x, d1 = C.r0.y, id1 = C.r0.z, b1 = C.r1.y, flags = C.r1.w;
+        if (flags & 1u) {
+          // first MMA of the row: the slot of output row j is overwritten, the older rows accumulate
+          if (flags & 2u) umma_bf16_acc_lo(d1, a0, b1, d_hi, C.r2.x);
+          if (flags & 4u) umma_bf16_acc_lo(tmem_base, a0, C.r2.z, d_hi, C.r2.y);
+          umma_bf16_ovw_lo(C.r2.w, a0, db_lo + (kh - 1u) * 512u, d_hi, idesc_bf16(64u, 0, 0));
+        }
+        auto after_column = [&](uint32_t s) {
+          if (s == 0 && pend_s) {
+            // the previous row's commit (it also covers the MMAs just issued, which only delays it a little)
+            umma_commit(pend_s);
+            pend_s = 0;
+          }
+          if (s == s_prep) have_next = prep(Nx);
+        };
+        uint32_t a_s = a0;
+        if (C.r1.x == 0) {
+#pragma unroll
+          for (uint32_t s = 0; s < kw; ++s) {
+#pragma unroll
+            for (uint32_t kk = 0; kk < 4; ++kk) {
+              if (s == 0 && kk == 0 && (flags & 1u)) continue;
+              // descriptor address fields count 16-byte units: one pixel row = 8, one filter tap = 512
+              umma_bf16_acc_lo(d1, a_s + 2u * kk, b1 + (s * kh * 512u + 2u * kk), d_hi, id1);
+            }
+            a_s += a_step;
+            after_column(s);
+          }
+        } else {
+          const uint32_t b2 = C.r1.z, id2 = C.r0.w;
+#pragma unroll
+          for (uint32_t s = 0; s < kw; ++s) {
+#pragma unroll
+            for (uint32_t kk = 0; kk < 4; ++kk) {
+              if (s == 0 && kk == 0 && (flags & 1u)) continue;
+              const uint32_t boff = s * kh * 512u + 2u * kk;
+              umma_bf16_acc_lo(d1, a_s + 2u * kk, b1 + boff, d_hi, id1);
+              umma_bf16_acc_lo(tmem_base, a_s + 2u * kk, b2 + boff, d_hi, id2);
+            }
+            a_s += a_step;
+            after_column(s);
+          }
+        }
+        pend_s = C.r3.w;
+      };
+      Rec A = {}, B = {};
+      bool have_a = prep(A), have_b = false;
+      while (have_a) {
+        have_b = false;
+        body(A, B, have_b);
+        if (!have_b) break;
+        have_a = false;
+        body(B, A, have_a);
+      }
+      if (pend_s) umma_commit(pend_s);
     }
   } else {
     const uint32_t q = (uint32_t)warp & 3u;
