@@ -814,11 +814,12 @@ static void stream_chunks(uint32_t NI, uint32_t tiles_x, uint32_t dh, uint32_t O
   const uint32_t rpr = (OP + dh - 1) / dh;          // rows of the largest residue class
   double best = 1e300;
   L = rpr < 4 ? (rpr ? rpr : 1) : 4; nchunks = (rpr + L - 1) / L;
-  for (uint32_t l = 4; l <= 32; ++l) {
+  for (uint32_t l = 4; l <= 128; ++l) {
     const uint32_t nch = (rpr + l - 1) / l, leff = (rpr + nch - 1) / nch;
     const unsigned long long items = (unsigned long long)NI * tiles_x * dh * nch;
     const unsigned long long waves = (items + kNumSMs - 1) / kNumSMs;
-    const double cost = (double)waves * (leff + 0.5 * (kh - 1) + 0.5);
+    // an input row costs the issuing thread about the same whether it feeds one output row or kh
+    const double cost = (double)waves * (leff + (kh - 1) + 0.5);
     if (cost < best - 1e-9 || (cost < best + 1e-9 && leff > L)) { best = cost; L = leff; nchunks = nch; }
     if (l >= rpr) break;
   }
