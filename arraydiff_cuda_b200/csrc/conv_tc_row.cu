@@ -1040,6 +1040,191 @@ conv_tc_row_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __gri
   }
 }
 
+// ---------------------------------------------------------------- filter gradient with the filter rows on N
+// The kernel above issues kh*kw/2 MMAs of N = 64 per 16 pixels, and an N = 64 MMA costs ~50 cycles to issue for 32
+// cycles of math.  Here the filter ROWS go onto N instead: with oy' = oy - r*dil,
+//   dw[k][r][s][c] = sum_px dy[oy'][px][k] * x[oy' + r*dil][px + s*dil][c] = sum_px dy[oy - r*dil][px][k] * x[oy][px + s*dil][c],
+// so one input row x[oy] meets the kh output-gradient rows dy[oy], dy[oy - dil], ... in ONE MMA:
+//   A = x[oy] shifted by s*dil pixels, two column taps stacked along M (as above)          (128 = 2 x 64 input channels)
+//   B = [dy[oy]; dy[oy - dil]; ...]  (kh tiles 16 KiB apart = the descriptor's LBO)          (N = 64 * kh output channels)
+//   D[(s, c)][(r, k)]: ceil(kw / 2) accumulators of 64 * kh columns.
+// A 3x3 needs 2 MMAs of N = 192 (math-bound, 96 cycles) per 16 pixels instead of 5 of N = 64, fetches one input row
+// instead of three, and walks oy over OP + (kh - 1)*dil rows (output-gradient rows outside [0, OP) are zero-filled by TMA).
+struct RowsWgParams {
+  uint32_t NI, OP, OQ, KO;
+  uint32_t kh, kw, dh, dw;
+  int32_t offy, offx;
+  uint32_t tiles_x, rows_ext, pw, stage_bytes, stages, naccs;
+  float* partial;   // [grid][naccs][128][64 * kh]
+  int32_t* status;
+};
+
+template <int KH, int KW>
+__global__ void __launch_bounds__(kRowThreads, 1)
+conv_tc_rows_wgrad_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_constant__ CUtensorMap map_x,
+                          const RowsWgParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  RowCtl* ctl = (RowCtl*)(smem + (size_t)p.stages * p.stage_bytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t total_tiles = p.NI * p.rows_ext * p.tiles_x;
+  constexpr uint32_t kTmemCols = 512, kDyBytes = 16384, kN = 64u * KH, kAccs = (KW + 1) / 2;
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&ctl->full[s]), 1);
+      mbar_init(smem_u32(&ctl->empty[s]), 1);
+    }
+    mbar_init(smem_u32(&ctl->tfull[0]), 1);
+    ctl->abort_flag = 0;
+    mbar_init_fence();
+    tma_prefetch_desc(&map_dy);
+    tma_prefetch_desc(&map_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  volatile int* abortf = &ctl->abort_flag;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      for (uint32_t tile = blockIdx.x; tile < total_tiles && !*abortf; tile += gridDim.x) {
+        const uint32_t tx = tile % p.tiles_x, oy = (tile / p.tiles_x) % p.rows_ext, n = tile / (p.tiles_x * p.rows_ext);
+        if (!mbar_wait_relaxed(smem_u32(&ctl->empty[stage]), phase ^ 1u, abortf)) break;
+        const uint32_t full = smem_u32(&ctl->full[stage]);
+        uint8_t* st = smem + (size_t)stage * p.stage_bytes;
+        mbar_expect_tx(full, KH * kDyBytes + p.pw * 128u);
+#pragma unroll
+        for (int r = 0; r < KH; ++r)   // rows outside the gradient (oy - r*dil < 0 or >= OP) arrive as zeros
+          tma_load_4d(smem_u32(st + r * kDyBytes), &map_dy, full, 0, (int)(tx * 128), (int)oy - r * (int)p.dh, (int)n);
+        tma_load_4d(smem_u32(st + KH * kDyBytes), &map_x, full, 0, (int)(tx * 128) + p.offx, (int)oy + p.offy, (int)n);
+        if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // The issuing thread executes an instruction only every few cycles and the tensor pipe queues only about three
+      // MMAs, so the loop is kept short: low descriptor words only (start address in 16-byte units + LBO; A and B share
+      // the high word), offsets worked out once, accumulate predicate fixed at compile time.
+      constexpr uint32_t idesc = idesc_bf16(kN, 1, 1);
+      const uint64_t proto = smem_desc_sw128(0, kDyBytes, 1024);
+      const uint32_t d_hi = (uint32_t)(proto >> 32), b_bits = (uint32_t)proto;   // B: LBO = one dy tile
+      uint32_t aoff[kAccs];   // A: column taps 2a and 2a+1 stacked along M (an odd last tap is paired with itself: LBO 0)
+#pragma unroll
+      for (uint32_t a = 0; a < kAccs; ++a)
+        aoff[a] = (uint32_t)smem_desc_sw128((2u * a * p.dw) * 128u + KH * kDyBytes, 2u * a + 1u < (uint32_t)KW ? p.dw * 128u : 0u, 1024);
+      const uint32_t base16 = (smem_u32(smem) >> 4) & 0x3FFFu, step16 = p.stage_bytes >> 4;
+      uint32_t stage = 0, phase = 0, first = 1, s16 = base16;
+      bool ok = true;
+      for (uint32_t tile = blockIdx.x; tile < total_tiles && !*abortf; tile += gridDim.x) {
+        if (!mbar_wait(smem_u32(&ctl->full[stage]), phase, abortf)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t b_lo = s16 + b_bits;
+        if (first) {
+#pragma unroll
+          for (uint32_t a = 0; a < kAccs; ++a) umma_bf16_ovw_lo(tmem_base + a * kN, s16 + aoff[a], b_lo, d_hi, idesc);
+          first = 0;
+        } else {
+#pragma unroll
+          for (uint32_t a = 0; a < kAccs; ++a) umma_bf16_acc_lo(tmem_base + a * kN, s16 + aoff[a], b_lo, d_hi, idesc);
+        }
+#pragma unroll
+        for (uint32_t ks = 1; ks < 8; ++ks)   // 8 x 16 pixels; 16 rows of 128 B = 128 units of 16 B
+#pragma unroll
+          for (uint32_t a = 0; a < kAccs; ++a)
+            umma_bf16_acc_lo(tmem_base + a * kN, s16 + aoff[a] + 128u * ks, b_lo + 128u * ks, d_hi, idesc);
+        umma_commit(smem_u32(&ctl->empty[stage]));
+        s16 += step16;
+        if (++stage == p.stages) { stage = 0; phase ^= 1u; s16 = base16; }
+      }
+      if (ok) umma_commit(smem_u32(&ctl->tfull[0]));
+    }
+  } else {
+    const uint32_t q = (uint32_t)warp & 3u;
+    const uint32_t row = q * 32 + lane;
+    float* out = p.partial + ((size_t)blockIdx.x * kAccs * 128 + row) * kN;
+    const bool have = blockIdx.x < total_tiles;
+    if (!have) {
+      for (uint32_t a = 0; a < kAccs; ++a)
+        for (uint32_t c = 0; c < kN; c += 4) *(float4*)(out + (size_t)a * 128 * kN + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+    } else if (mbar_wait(smem_u32(&ctl->tfull[0]), 0, abortf)) {
+      tc_fence_after();
+#pragma unroll 1
+      for (uint32_t a = 0; a < kAccs; ++a)
+#pragma unroll 1
+        for (uint32_t ch = 0; ch < kN / 32; ++ch) {
+          uint32_t v[32];
+          tmem_ld32(tmem_base + ((q * 32u) << 16) + a * kN + ch * 32, v);
+          tmem_ld_wait();
+          float* o = out + (size_t)a * 128 * kN + ch * 32;
+#pragma unroll
+          for (int g = 0; g < 8; ++g)
+            *(float4*)(o + g * 4) = make_float4(__uint_as_float(v[g * 4]), __uint_as_float(v[g * 4 + 1]),
+                                                __uint_as_float(v[g * 4 + 2]), __uint_as_float(v[g * 4 + 3]));
+        }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abortf) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(500);
+    if (threadIdx.x == 0 && p.status) *p.status = AD_ERR_TIMEOUT;
+  }
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// dw[k][r*kw + s][c] (+)= sum over CTAs of partial[cta][s / 2][(s % 2)*64 + c][r*64 + k], fixed order (as below).
+__global__ void __launch_bounds__(256) wgrad_rows_reduce_kernel(uint32_t nparts, uint32_t naccs, uint32_t KO, uint32_t kh,
+                                                                uint32_t kw, const float* __restrict__ partial, float* dw,
+                                                                int accumulate, int kcrs) {
+  const uint32_t tx = threadIdx.x & 63, pl = threadIdx.x >> 6;
+  const uint32_t cols4 = 16 * kh, item = blockIdx.x * 64 + tx, nitems = naccs * 128 * cols4;
+  float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (item < nitems) {
+    const size_t part_stride = (size_t)naccs * 128 * 64 * kh;
+    const float* src = partial + (size_t)item * 4;
+    for (uint32_t p0 = pl; p0 < nparts; p0 += 32) {
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const uint32_t pi = p0 + 4 * u;
+        v[u] = pi < nparts ? *(const float4*)(src + pi * part_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) { t.x += v[u].x; t.y += v[u].y; t.z += v[u].z; t.w += v[u].w; }
+    }
+  }
+  __shared__ float4 sh[4][64];
+  sh[pl][tx] = t;
+  __syncthreads();
+  if (pl != 0 || item >= nitems) return;
+#pragma unroll
+  for (int w = 1; w < 4; ++w) { const float4 o = sh[w][tx]; t.x += o.x; t.y += o.y; t.z += o.z; t.w += o.w; }
+  const uint32_t col = (item % cols4) * 4, row = (item / cols4) & 127u, acc = item / (cols4 * 128);
+  const uint32_t r = col >> 6, k0 = col & 63u, c = row & 63u, sx = acc * 2 + (row >> 6), taps = kh * kw;
+  if (sx >= kw) return;   // the unused half of an odd last column tap
+  const uint32_t tap = r * kw + sx;
+  const float o[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    if (k0 + j < KO) {
+      float* d = kcrs ? dw + ((size_t)(k0 + j) * 64 + c) * taps + tap : dw + ((size_t)(k0 + j) * taps + tap) * 64 + c;
+      *d = accumulate ? *d + o[j] : o[j];
+    }
+}
+
 // dw[k][tap][c] (+)= sum over CTAs of partial[cta][acc(tap)][half(tap)*64 + c][k], fixed order.
 // A block is 64 float4 items (4 adjacent k of one accumulator row: coalesced reads) x 4 part lanes; every
 // lane sums parts lane, lane+4, ... with 8 loads in flight, the lanes are combined in order.
@@ -1092,10 +1277,71 @@ static bool row_wgrad_ok(uint32_t CI, uint32_t KO, uint32_t kh, uint32_t kw, uin
   const uint32_t pw = (128 + (kw - 1) * dw + 7) / 8 * 8;
   return pw <= 256 && (kh - 1) * dh + 1 <= 256;
 }
+// the 3x3 form with the filter rows on N (ARRAYDIFF_B200_WGRAD_PAIRS=1 keeps the tap-pair kernel: the parity tests compare the two)
+static bool rows_wgrad_ok(uint32_t kh, uint32_t kw) {
+  const char* e = getenv("ARRAYDIFF_B200_WGRAD_PAIRS");
+  return kh == 3 && kw == 3 && !(e && e[0] == '1');
+}
+static uint32_t rows_wgrad_grid(uint32_t NI, uint32_t OP, uint32_t OQ, uint32_t kh, uint32_t dh) {
+  const unsigned long long total = (unsigned long long)NI * (OP + (kh - 1) * dh) * ((OQ + 127) / 128);
+  return total < (unsigned long long)kNumSMs ? (uint32_t)total : (uint32_t)kNumSMs;
+}
 size_t conv_tc_row_wgrad_scratch(uint32_t NI, uint32_t CI, uint32_t KO, uint32_t kh, uint32_t kw, uint32_t sh, uint32_t sw,
                                  uint32_t dh, uint32_t dw, uint32_t OP, uint32_t OQ) {
   if (!row_wgrad_ok(CI, KO, kh, kw, sh, sw, dh, dw, OQ)) return 0;
-  return (size_t)row_wgrad_grid(NI, OP, OQ) * ((kh * kw + 1) / 2) * 128 * 64 * 4;
+  const size_t pairs = (size_t)row_wgrad_grid(NI, OP, OQ) * ((kh * kw + 1) / 2) * 128 * 64 * 4;
+  const size_t rows = kh == 3 && kw == 3 ? (size_t)rows_wgrad_grid(NI, OP, OQ, kh, dh) * ((kw + 1) / 2) * 128 * 64 * kh * 4 : 0;
+  return pairs > rows ? pairs : rows;
+}
+
+static int conv_tc_rows_wgrad(const void* x, uint32_t NI, uint32_t IH, uint32_t IW, uint32_t CI, const void* dy, uint32_t KO,
+                              uint32_t kh, uint32_t kw, uint32_t dh, uint32_t dw, int offy, int offx, uint32_t OP, uint32_t OQ,
+                              float* dwt, int accumulate, int kcrs, void* partial, size_t partial_bytes, int32_t* status,
+                              cudaStream_t s) {
+  RowsWgParams p{};
+  p.NI = NI; p.OP = OP; p.OQ = OQ; p.KO = KO;
+  p.kh = kh; p.kw = kw; p.dh = dh; p.dw = dw; p.offy = offy; p.offx = offx;
+  p.tiles_x = (OQ + 127) / 128;
+  p.rows_ext = OP + (kh - 1) * dh;
+  p.pw = (128 + (kw - 1) * dw + 7) / 8 * 8;
+  p.stage_bytes = kh * 16384 + p.pw * 128;
+  p.naccs = (kw + 1) / 2;
+  if ((unsigned long long)NI * p.rows_ext * p.tiles_x > 0xffffffffull) return AD_ERR_UNSUPPORTED;
+  long long stages = ((long long)kMaxDynSmem - 1024 - (long long)sizeof(RowCtl)) / p.stage_bytes;
+  if (stages < 2) return AD_ERR_UNSUPPORTED;
+  if (stages > 4) stages = 4;
+  p.stages = (uint32_t)stages;
+  const uint32_t grid = rows_wgrad_grid(NI, OP, OQ, kh, dh);
+  if (partial_bytes < (size_t)grid * p.naccs * 128 * 64 * kh * 4) return AD_ERR_SCRATCH;
+  p.partial = (float*)partial;
+  p.status = status;
+  CUtensorMap mdy, mx;
+  {
+    uint64_t dims[4] = {KO, OQ, OP, NI};
+    uint64_t str[4] = {0, (uint64_t)KO * 2, (uint64_t)OQ * KO * 2, (uint64_t)OP * OQ * KO * 2};
+    uint32_t box[4] = {64, 128, 1, 1};
+    uint32_t es[4] = {1, 1, 1, 1};
+    int st = make_tmap_bf16(&mdy, dy, 4, dims, str, box, es);
+    if (st != AD_OK) return st;
+  }
+  {
+    uint64_t dims[4] = {CI, IW, IH, NI};
+    uint64_t str[4] = {0, (uint64_t)CI * 2, (uint64_t)IW * CI * 2, (uint64_t)IH * IW * CI * 2};
+    uint32_t box[4] = {64, p.pw, 1, 1};
+    uint32_t es[4] = {1, 1, 1, 1};
+    int st = make_tmap_bf16(&mx, x, 4, dims, str, box, es);
+    if (st != AD_OK) return st;
+  }
+  const int smem = (int)(stages * p.stage_bytes + 1024 + sizeof(RowCtl));
+  if (cudaFuncSetAttribute(conv_tc_rows_wgrad_kernel<3, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynSmem) != cudaSuccess) {
+    cudaGetLastError();
+    return AD_ERR_CUDA;
+  }
+  conv_tc_rows_wgrad_kernel<3, 3><<<grid, kRowThreads, smem, s>>>(mdy, mx, p);
+  count_launch();
+  wgrad_rows_reduce_kernel<<<(p.naccs * 128 * 16 * kh + 63) / 64, 256, 0, s>>>(grid, p.naccs, KO, kh, kw, p.partial, dwt, accumulate, kcrs);
+  count_launch();
+  return launch_status();
 }
 
 int conv_tc_row_wgrad(const void* x, uint32_t NI, uint32_t IH, uint32_t IW, uint32_t CI, const void* dy, uint32_t KO,
@@ -1103,6 +1349,11 @@ int conv_tc_row_wgrad(const void* x, uint32_t NI, uint32_t IH, uint32_t IW, uint
                       uint32_t OP, uint32_t OQ, float* dwt, int accumulate, int kcrs, void* partial, size_t partial_bytes,
                       int32_t* status, cudaStream_t s) {
   if (!row_wgrad_ok(CI, KO, kh, kw, sh, sw, dh, dw, OQ)) return AD_ERR_UNSUPPORTED;
+  if (rows_wgrad_ok(kh, kw)) {
+    const int st = conv_tc_rows_wgrad(x, NI, IH, IW, CI, dy, KO, kh, kw, dh, dw, offy, offx, OP, OQ, dwt, accumulate, kcrs, partial,
+                                      partial_bytes, status, s);
+    if (st != AD_ERR_UNSUPPORTED) return st;
+  }
   RowWgParams p{};
   p.NI = NI; p.OP = OP; p.OQ = OQ; p.KO = KO;
   p.kh = kh; p.kw = kw; p.dh = dh; p.dw = dw; p.offy = offy; p.offx = offx;

@@ -703,7 +703,7 @@ def run_conv_workload(env, args, with_cpu=True):
             "step_ms": st,
             "halo_exposed_ms": halo_exposed,
             "roofline": {"bound": "tensor", "kernel": {"fprop": "conv_tc_stream_fwd_kernel<3,3> (fprop)", "dgrad": "conv_tc_stream_fwd_kernel<3,3> (dgrad)",
-                                                        "wgrad": "conv_tc_row_wgrad_kernel<3,3>"}[top], "achieved": achieved, "peak": peaks["tf_sustained"],
+                                                        "wgrad": "conv_tc_rows_wgrad_kernel<3,3>"}[top], "achieved": achieved, "peak": peaks["tf_sustained"],
                          "unit": "TFLOP/s", "frac": achieved / peaks["tf_sustained"],
                          "traffic": NCU_TRAFFIC_BATCH4[top] * BATCH / 4 / world,
                          "peak_source": peaks["source"] + " (sustained: the kernel is timed with CUDA events inside full steps run back to back)",

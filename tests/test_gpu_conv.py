@@ -377,3 +377,45 @@ def test_conv_tc_row_kernels_agree_with_general_kernels(case, monkeypatch):
     assert kinds["row"] == tuple(_kinds(case)) and kinds["general"] == (GEN, GEN, GEN), kinds
     for got, ref, tol in zip(res["row"], res["general"], (TOL_BF16, TOL_BF16, 1e-4)):
         assert H.max_rel(got, ref) < tol
+
+
+@pytest.mark.parametrize("case", [(2, 64, 22, 140, 64, 3, 1, 3, 0), (1, 64, 18, 262, 64, 3, 1, 1, 0), (3, 64, 12, 104, 32, 3, 1, 2, 0),
+                                  (1, 64, 9, 132, 8, 3, 1, 3, 1)])
+@pytest.mark.parametrize("kcrs,accumulate", [(0, 0), (1, 1)])
+def test_conv_tc_filter_gradient_forms_agree(case, kcrs, accumulate, monkeypatch):
+    """The 3x3 filter gradient of a 64-channel layer has two tensor-core forms: filter rows stacked on the MMA's N axis
+    (default) and, with ARRAYDIFF_B200_WGRAD_PAIRS=1, tap pairs stacked on M.  Both accumulate in fp32 over the same
+    pixels in different orders: they agree to rounding, with each other and with the oracle, for dense and KCRS
+    outputs, overwrite and accumulate, ragged widths, fewer than 64 output channels and implicit zero padding."""
+    import torch
+    N, Cc, Hh, W, K, k, s, d, pd = case
+    x, w = _tc_setup(case)
+    P, Q = _out_dims(Hh, W, k, s, d, pd)
+    dy = orc.round_bf16(H.uniform(33, (N, K, P, Q)))
+    dw_w = orc.conv2d_wgrad(x, dy, w.shape, (s, s), (d, d), (pd, pd), omp=True)      # KCRS
+    L = abi.lib()
+    a = conv_args(abi.AD_BF16, abi.AD_NHWC, x.shape, K, k, s, d, pd)
+    dx_ = H.dev_bf16(orc.nchw_to_nhwc(x))
+    ddy = H.dev_bf16(orc.nchw_to_nhwc(dy))
+    nscr = L.ad_conv2d_scratch_bytes(C.byref(a), 2)
+    scratch = torch.zeros(nscr, dtype=torch.uint8, device="cuda")
+    a.x, a.y, a.scratch, a.scratch_bytes = dx_.data_ptr(), ddy.data_ptr(), scratch.data_ptr(), nscr
+    a.dw_kcrs, a.accumulate = kcrs, accumulate
+    shape = (K, Cc, 3, 3) if kcrs else (K, 3, 3, Cc)
+    got = {}
+    for form in ("rows", "pairs"):
+        if form == "pairs":
+            monkeypatch.setenv("ARRAYDIFF_B200_WGRAD_PAIRS", "1")
+        else:
+            monkeypatch.delenv("ARRAYDIFF_B200_WGRAD_PAIRS", raising=False)
+        gw = torch.full(shape, 0.5 if accumulate else 7.0, device="cuda")
+        a.dw = gw.data_ptr()
+        abi.check(L.ad_conv2d_wgrad(C.byref(a), H.stream()))
+        _check_kind(L, ROW)
+        H.sync()
+        assert scratch[:4].view(torch.int32)[0].item() == 0
+        g = H.host(gw) - (0.5 if accumulate else 0.0)
+        got[form] = g if kcrs else np.transpose(g, (0, 3, 1, 2))
+    monkeypatch.delenv("ARRAYDIFF_B200_WGRAD_PAIRS", raising=False)
+    assert H.max_rel(got["rows"], dw_w) < 1e-4 and H.max_rel(got["pairs"], dw_w) < 1e-4
+    assert H.max_rel(got["rows"], got["pairs"]) < 1e-5
