@@ -50,7 +50,7 @@ def flops_per_pass(n=None, rows=SIZE, cols=SIZE):
 # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the three conv kernels of the
 # microbenchmark shape, from an `ncu --set full --clock-control none` capture of one launch each at batch 4 on
 # one GPU; traffic grows in proportion to the pixels a launch processes, so it is scaled by batch / 4 / strips.
-NCU_TRAFFIC_BATCH4 = {"fprop": 230.6e6, "dgrad": 227.9e6, "wgrad": 275.2e6}
+NCU_TRAFFIC_BATCH4 = {"fprop": 226.1e6, "dgrad": 223.3e6, "wgrad": 275.6e6}
 
 
 def measured_peaks():
