@@ -500,8 +500,14 @@ void CudnnConv2DOpF::_forward(TxnId txn) {
   // the waits go, then adds the p rows at either edge -- the interior work overlaps the halo's flight, which the
   // reference forgoes by synchronising every device around each exchange (src/op.cc:2976, :3001).
   const size_t ph = shape_.pad[1], oh = dim_.shape[1];
-  const char* sw = getenv("ARRAYDIFF_B200_HALO_OVERLAP");   // "0": wait for the halo rows in front of the whole layer
-  const bool overlap = !(sw && sw[0] == '0');
+  // The split costs two more launches (the boundary rows), ~25 us each on a persistent tensor-core kernel; the exchange
+  // it hides is 15-25 us in flight.  It pays for layers of >= 150 GFLOP per strip (the 64-channel microbenchmark layer);
+  // on the 1024 x 2048 segmentation net cut into 4 strips every layer is below that and the split step measured 3.5 %
+  // slower.  ARRAYDIFF_B200_HALO_OVERLAP: "0" never splits, "2" always (the tests use it), anything else decides by size.
+  const char* sw = getenv("ARRAYDIFF_B200_HALO_OVERLAP");
+  const double gflop = 2e-9 * (double)batch_ * (double)shape_.filters * (double)in_dim_.shape[2] * (double)shape_.kernel[0] *
+                       (double)shape_.kernel[1] * (double)dim_.shape[0] * (double)dim_.shape[1];
+  const bool overlap = sw && sw[0] == '0' ? false : sw && sw[0] == '2' ? true : gflop >= 150.0;
   const bool split = overlap && g->has_pending() && g->mode() == COMPUTE_BF16_NHWC && shape_.halo_padded_input && !use_im2col_ &&
                      shape_.stride[0] == 1 && shape_.stride[1] == 1 && ph > 0 && oh > 2 * ph;
   GPUConn conn = split ? g->conn_deferred() : g->conn();
