@@ -847,7 +847,7 @@ SpatialAllGather2DOpF::SpatialAllGather2DOpF(vector<ActVar> inputs, shared_ptr<C
     : xs_(inputs), ctx_(ctx), num_ranks_(num_ranks_of(ctx, inputs.size())) {
   for (auto& x : inputs) inputs_.push_back(x);
 }
-// Between processes: tell every peer that my strip (or my gradient) of this round may be read, then wait
+// Between processes: tell every peer that my strip (or my gradient) of this exchange may be read, then wait
 // (bounded) for theirs.  Every rank calls the gathers in the same order, so the round number agrees.
 void SpatialAllGather2DOpF::wait_peers(size_t rank, cudaStream_t s) {
   auto* m = dynamic_cast<MultiGPUContext*>(ctx_.get());
